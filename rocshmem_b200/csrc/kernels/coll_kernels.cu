@@ -1,0 +1,394 @@
+// Multi-block collectives on the symmetric heap: barrier, allreduce (one-shot, two-shot, NVLS),
+// broadcast, fcollect (all-gather), alltoall. These are the standalone kernels behind the host API
+// collectives and the PyTorch ops; the block-collective device API inside user kernels lives in
+// rocshmem/device/collectives.cuh.
+//
+// The reference has no kernels of its own (its collectives are __device__ functions run by one
+// work-group inside a user kernel: src/ipc/context_ipc_tmpl_device.hpp:166-531) and performs host
+// collectives with MPI (src/host/host_templates.hpp:88-392). Here each collective is one kernel
+// over up to 128 blocks per PE:
+//   * block b of every PE pairs up through block_pair_barrier, so no block ever waits for another
+//     block of its own GPU and the kernels need no grid-wide synchronisation;
+//   * data moves as 16-byte NVLink peer loads / stores, with one load per team member in flight per
+//     thread (allreduce) or four independent vectors per thread (copies);
+//   * allreduce: ONE_SHOT = every PE pulls every source and reduces locally (3 hops, small payloads);
+//     TWO_SHOT = PE i reduces slice i from all sources and pushes the result to every dest, which
+//     moves (n-1)/n of the payload per direction per GPU, the minimum over point-to-point links;
+//     NVLS = multimem.ld_reduce on slice i (the NVSwitch adds the n copies) followed by multimem.st
+//     (the switch replicates the result), roughly halving the bytes each GPU puts on its links.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "kernels.hpp"
+#include "launch.cuh"
+#include "lib_common.cuh"
+
+namespace rocshmem {
+namespace kernels {
+
+namespace {
+
+constexpr unsigned kThreads = 512;
+constexpr int OP_RUNTIME = -1;
+
+using detail::Acc;
+using detail::from_acc;
+using detail::remote_ptr;
+using detail::team_pe_to_world;
+using detail::to_acc;
+
+template <typename A>
+__device__ __forceinline__ A apply_runtime(A a, A b, int op) {
+  switch (op) {
+    case ROCSHMEM_SUM: return a + b;
+    case ROCSHMEM_PROD: return a * b;
+    case ROCSHMEM_MIN: return a < b ? a : b;
+    case ROCSHMEM_MAX: return a > b ? a : b;
+    default: break;
+  }
+  if constexpr (std::is_integral<A>::value) {
+    if (op == ROCSHMEM_AND) return a & b;
+    if (op == ROCSHMEM_OR) return a | b;
+    if (op == ROCSHMEM_XOR) return a ^ b;
+  }
+  return b;
+}
+
+template <typename T, int OP>
+__device__ __forceinline__ typename Acc<T>::type combine(typename Acc<T>::type a,
+                                                         typename Acc<T>::type b, int op) {
+  if constexpr (OP == ROCSHMEM_SUM) {
+    return a + b;
+  } else {
+    return apply_runtime<typename Acc<T>::type>(a, b, op);
+  }
+}
+
+// Reduce elements [lo, hi) over all members; the result goes to the local dest only (ALL == false)
+// or to every member's dest (ALL == true). `tid`/`nthr` enumerate the threads working on the range.
+template <typename T, int OP, bool ALL>
+__device__ __forceinline__ void reduce_range(const rocshmem_team_dev *t, T *dest, const T *source,
+                                             size_t lo, size_t hi, size_t tid, size_t nthr, int op,
+                                             bool aligned) {
+  using A = typename Acc<T>::type;
+  constexpr int VEC = 16 / sizeof(T);
+  const int n = t->size;
+  size_t scalar_from = lo;
+  if (aligned && (lo % VEC) == 0) {
+    const size_t nvec = (hi - lo) / VEC;
+    for (size_t v = tid; v < nvec; v += nthr) {
+      const size_t e = lo + v * VEC;
+      // Start with my own copy, then the peers in rotated order so that at any moment the members
+      // read from different sources.
+      int4 raw[ROCSHMEM_MAX_PES > 8 ? 8 : ROCSHMEM_MAX_PES];
+      A acc[VEC];
+      int done = 0;
+      bool first = true;
+      while (done < n) {
+        const int batch = (n - done) < 8 ? (n - done) : 8;
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (k < batch) {
+            int j = (t->my_pe + done + k) % n;
+            raw[k] = ld_global_16(remote_ptr(source + e, team_pe_to_world(t, j)));
+          }
+        }
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+          if (k < batch) {
+            const T *x = reinterpret_cast<const T *>(&raw[k]);
+            if (first) {
+#pragma unroll
+              for (int q = 0; q < VEC; ++q) acc[q] = to_acc<T>(x[q]);
+              first = false;
+            } else {
+#pragma unroll
+              for (int q = 0; q < VEC; ++q) acc[q] = combine<T, OP>(acc[q], to_acc<T>(x[q]), op);
+            }
+          }
+        }
+        done += batch;
+      }
+      int4 out;
+      T *o = reinterpret_cast<T *>(&out);
+#pragma unroll
+      for (int q = 0; q < VEC; ++q) o[q] = from_acc<T>(acc[q]);
+      if (ALL) {
+        for (int d = 0; d < n; ++d) {
+          int j = (t->my_pe + d) % n;
+          st_global_16(remote_ptr(dest + e, team_pe_to_world(t, j)), out);
+        }
+      } else {
+        st_global_16(dest + e, out);
+      }
+    }
+    scalar_from = lo + nvec * VEC;
+  }
+  for (size_t e = scalar_from + tid; e < hi; e += nthr) {
+    A acc = to_acc<T>(*remote_ptr(source + e, team_pe_to_world(t, 0)));
+    for (int j = 1; j < n; ++j) {
+      acc = combine<T, OP>(acc, to_acc<T>(*remote_ptr(source + e, team_pe_to_world(t, j))), op);
+    }
+    T out = from_acc<T>(acc);
+    if (ALL) {
+      for (int j = 0; j < n; ++j) *remote_ptr(dest + e, team_pe_to_world(t, j)) = out;
+    } else {
+      dest[e] = out;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(64) barrier_kernel(rocshmem_team_t team) {
+  const rocshmem_team_dev *t = detail::team_of(team);
+  if (t->my_pe < 0) return;
+  // Reuses the device API's block barrier so host- and device-initiated barriers share one epoch.
+  detail::team_barrier(const_cast<rocshmem_team_dev *>(t));
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads)
+allreduce_one_shot_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg, size_t nelems, int op) {
+  const rocshmem_team_dev *t = detail::team_of(team);
+  if (t->my_pe < 0) return;
+  T *dest = detail::local_ptr(dest_arg);
+  const T *source = detail::local_ptr(const_cast<T *>(source_arg));
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 15u) == 0;
+  if (!block_pair_barrier(t, blockIdx.x)) return;
+  reduce_range<T, OP, false>(t, dest, source, 0, nelems, size_t(blockIdx.x) * blockDim.x + threadIdx.x,
+                             size_t(gridDim.x) * blockDim.x, op, aligned);
+  // Nobody overwrites a source while a peer may still be reading it.
+  block_pair_barrier(t, blockIdx.x);
+}
+
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads)
+allreduce_two_shot_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg, size_t nelems, int op) {
+  const rocshmem_team_dev *t = detail::team_of(team);
+  if (t->my_pe < 0) return;
+  T *dest = detail::local_ptr(dest_arg);
+  const T *source = detail::local_ptr(const_cast<T *>(source_arg));
+  constexpr size_t VEC = 16 / sizeof(T);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 15u) == 0;
+  const size_t n = static_cast<size_t>(t->size);
+  size_t per = ((nelems + n - 1) / n + VEC - 1) / VEC * VEC;
+  size_t lo = per * static_cast<size_t>(t->my_pe), hi = lo + per;
+  if (lo > nelems) lo = nelems;
+  if (hi > nelems) hi = nelems;
+  if (!block_pair_barrier(t, blockIdx.x)) return;
+  reduce_range<T, OP, true>(t, dest, source, lo, hi, size_t(blockIdx.x) * blockDim.x + threadIdx.x,
+                            size_t(gridDim.x) * blockDim.x, op, aligned);
+  block_pair_barrier(t, blockIdx.x);
+}
+
+// ---- NVLS ---------------------------------------------------------------------------------------------
+
+template <typename T>
+__device__ __forceinline__ int4 multimem_ld_reduce_add(const void *mc);
+template <>
+__device__ __forceinline__ int4 multimem_ld_reduce_add<float>(const void *mc) {
+  int4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.v4.f32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+  return r;
+}
+template <>
+__device__ __forceinline__ int4 multimem_ld_reduce_add<__nv_bfloat16>(const void *mc) {
+  int4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.bf16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+  return r;
+}
+template <>
+__device__ __forceinline__ int4 multimem_ld_reduce_add<__half>(const void *mc) {
+  int4 r;
+  asm volatile("multimem.ld_reduce.relaxed.sys.global.add.acc::f32.v4.f16x2 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w) : "l"(mc) : "memory");
+  return r;
+}
+__device__ __forceinline__ void multimem_st(void *mc, int4 v) {
+  asm volatile("multimem.st.relaxed.sys.global.v4.f32 [%0], {%1,%2,%3,%4};"
+               ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
+}
+
+// World team only: the multicast object spans every PE. Requires 16-byte aligned buffers and a
+// multiple of 16 bytes per slice; the launcher falls back to TWO_SHOT otherwise.
+template <typename T>
+__global__ void __launch_bounds__(kThreads)
+allreduce_nvls_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg, size_t nelems) {
+  const rocshmem_device_state &s = st();
+  const rocshmem_team_dev *t = detail::team_of(team);
+  if (t->my_pe < 0 || s.mc_base == nullptr) return;
+  constexpr size_t VEC = 16 / sizeof(T);
+  const size_t n = static_cast<size_t>(t->size);
+  const size_t nvec_total = nelems / VEC;  // the launcher guarantees nelems % VEC == 0
+  size_t per = (nvec_total + n - 1) / n;
+  size_t lo = per * static_cast<size_t>(t->my_pe), hi = lo + per;
+  if (lo > nvec_total) lo = nvec_total;
+  if (hi > nvec_total) hi = nvec_total;
+  const char *src_mc = s.mc_base + (reinterpret_cast<const char *>(detail::local_ptr(const_cast<T *>(source_arg))) - s.heap_base);
+  char *dst_mc = s.mc_base + (reinterpret_cast<char *>(detail::local_ptr(dest_arg)) - s.heap_base);
+  if (!block_pair_barrier(t, blockIdx.x)) return;
+  const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, nthr = size_t(gridDim.x) * blockDim.x;
+  size_t v = lo + tid;
+  for (; v + 3 * nthr < hi; v += 4 * nthr) {
+    int4 a = multimem_ld_reduce_add<T>(src_mc + v * 16);
+    int4 b = multimem_ld_reduce_add<T>(src_mc + (v + nthr) * 16);
+    int4 c = multimem_ld_reduce_add<T>(src_mc + (v + 2 * nthr) * 16);
+    int4 d = multimem_ld_reduce_add<T>(src_mc + (v + 3 * nthr) * 16);
+    multimem_st(dst_mc + v * 16, a);
+    multimem_st(dst_mc + (v + nthr) * 16, b);
+    multimem_st(dst_mc + (v + 2 * nthr) * 16, c);
+    multimem_st(dst_mc + (v + 3 * nthr) * 16, d);
+  }
+  for (; v < hi; v += nthr) multimem_st(dst_mc + v * 16, multimem_ld_reduce_add<T>(src_mc + v * 16));
+  block_pair_barrier(t, blockIdx.x);
+}
+
+// ---- copies -----------------------------------------------------------------------------------------------
+
+// mode 0: broadcast (root pushes source to every other member's dest)
+// mode 1: fcollect  (my source -> dest[my_pe * bytes] on every member)
+// mode 2: alltoall  (source[j * bytes] -> dest[my_pe * bytes] on member j)
+__global__ void __launch_bounds__(kThreads)
+push_kernel(rocshmem_team_t team, char *dest_arg, const char *source_arg, size_t bytes, int root, int mode) {
+  const rocshmem_team_dev *t = detail::team_of(team);
+  if (t->my_pe < 0) return;
+  char *dest = detail::local_ptr(dest_arg);
+  const char *source = detail::local_ptr(const_cast<char *>(source_arg));
+  const int n = t->size;
+  // Optional entry barrier: destinations on every member are known to be free (their previous
+  // consumers have finished) before anybody writes into them.
+  if (mode & 0x100) {
+    if (!block_pair_barrier(t, blockIdx.x)) return;
+    mode &= 0xff;
+  }
+  const bool sender = mode != 0 || t->my_pe == root;
+  if (sender) {
+    // Each block owns a contiguous share of the payload (multiple of 16 bytes) and sends it to every
+    // destination, rotating the order so that the members hit different targets at the same time.
+    const size_t share = ((bytes + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+    size_t lo = share * blockIdx.x, hi = lo + share;
+    if (lo > bytes) lo = bytes;
+    if (hi > bytes) hi = bytes;
+    detail::Group<detail::Scope::BLOCK> g;
+    for (int d = 0; d < n && hi > lo; ++d) {
+      const int j = (t->my_pe + d) % n;
+      if (mode == 0 && j == root) continue;  // the root's own dest stays untouched
+      const char *src = source + (mode == 2 ? size_t(j) * bytes : 0) + lo;
+      char *dst = dest + (mode == 0 ? 0 : size_t(t->my_pe) * bytes) + lo;
+      detail::copy_bytes<detail::Scope::BLOCK>(remote_ptr(dst, team_pe_to_world(t, j)), src, hi - lo, g);
+    }
+  }
+  block_pair_barrier(t, blockIdx.x);
+}
+
+template <typename K>
+unsigned clamp_blocks(K kernel, unsigned want) {
+  Runtime &rt = Runtime::instance();
+  unsigned b = std::min<unsigned>(want, ROCSHMEM_LIB_MAX_BLOCKS);
+  if (rt.n_local() > 1) b = std::min(b, coresident_blocks_per_pe(kernel, kThreads, 0, rt.n_local()));
+  return std::max(1u, b);
+}
+
+template <typename T>
+int launch_allreduce_typed(rocshmem_team_t team, void *dest, const void *source, size_t nelems, int op,
+                           int algo, cudaStream_t stream) {
+  const size_t bytes = nelems * sizeof(T);
+  Runtime &rt = Runtime::instance();
+  HostTeam *ht = rt.team_from_handle(team);
+  const int n = ht ? ht->world.size : rt.n_pes();
+  if (algo == ALLREDUCE_AUTO) {
+    const bool nvls_ok = rt.mc_base() != nullptr && ht == rt.team_world() && op == ROCSHMEM_SUM &&
+                         (std::is_same<T, float>::value || std::is_same<T, __half>::value ||
+                          std::is_same<T, __nv_bfloat16>::value);
+    if (bytes <= (size_t(256) << 10) && dest != source) algo = ALLREDUCE_ONE_SHOT;
+    else algo = nvls_ok ? ALLREDUCE_NVLS : ALLREDUCE_TWO_SHOT;
+  }
+  if (algo == ALLREDUCE_ONE_SHOT && dest == source) algo = ALLREDUCE_TWO_SHOT;
+  if (algo == ALLREDUCE_NVLS) {
+    constexpr bool supported = std::is_same<T, float>::value || std::is_same<T, __half>::value ||
+                               std::is_same<T, __nv_bfloat16>::value;
+    const bool aligned = ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 15u) == 0 &&
+                         bytes % 16 == 0;
+    if (!supported || rt.mc_base() == nullptr || ht != rt.team_world() || op != ROCSHMEM_SUM || !aligned) {
+      algo = ALLREDUCE_TWO_SHOT;
+    }
+  }
+  const unsigned want = static_cast<unsigned>(coll_blocks_for(algo == ALLREDUCE_ONE_SHOT ? bytes : bytes / n));
+  T *d = static_cast<T *>(dest);
+  const T *s = static_cast<const T *>(source);
+  if (algo == ALLREDUCE_NVLS) {
+    if constexpr (std::is_same<T, float>::value || std::is_same<T, __half>::value ||
+                  std::is_same<T, __nv_bfloat16>::value) {
+      auto k = allreduce_nvls_kernel<T>;
+      return launch_pes(k, clamp_blocks(k, want), kThreads, 0, stream, false, team, d, s, nelems);
+    }
+  }
+  const bool sum = op == ROCSHMEM_SUM;
+  if (algo == ALLREDUCE_ONE_SHOT) {
+    auto k = sum ? allreduce_one_shot_kernel<T, ROCSHMEM_SUM> : allreduce_one_shot_kernel<T, OP_RUNTIME>;
+    return launch_pes(k, clamp_blocks(k, want), kThreads, 0, stream, false, team, d, s, nelems, op);
+  }
+  auto k = sum ? allreduce_two_shot_kernel<T, ROCSHMEM_SUM> : allreduce_two_shot_kernel<T, OP_RUNTIME>;
+  return launch_pes(k, clamp_blocks(k, want), kThreads, 0, stream, false, team, d, s, nelems, op);
+}
+
+}  // namespace
+
+int coll_blocks_for(size_t bytes) {
+  // One block per 64 KiB of payload it has to move, between 1 and 128: small payloads stay
+  // latency-bound on few blocks, large ones spread over most of the GPU.
+  size_t b = (bytes + (size_t(64) << 10) - 1) / (size_t(64) << 10);
+  if (b < 1) b = 1;
+  if (b > ROCSHMEM_LIB_MAX_BLOCKS) b = ROCSHMEM_LIB_MAX_BLOCKS;
+  return static_cast<int>(b);
+}
+
+bool nvls_available() { return Runtime::initialized() && Runtime::instance().mc_base() != nullptr; }
+
+int coll_barrier(rocshmem_team_t team, void *stream) {
+  return launch_pes(barrier_kernel, 1, 64, 0, static_cast<cudaStream_t>(stream), false, team);
+}
+
+int coll_allreduce(rocshmem_team_t team, void *dest, const void *source, size_t nelems, int dtype, int op,
+                   int algo, void *stream_v) {
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (nelems == 0) return 0;
+  switch (dtype) {
+    case ROCSHMEM_I16: return launch_allreduce_typed<short>(team, dest, source, nelems, op, algo, stream);
+    case ROCSHMEM_I32: return launch_allreduce_typed<int>(team, dest, source, nelems, op, algo, stream);
+    case ROCSHMEM_I64: return launch_allreduce_typed<long long>(team, dest, source, nelems, op, algo, stream);
+    case ROCSHMEM_U32: return launch_allreduce_typed<unsigned int>(team, dest, source, nelems, op, algo, stream);
+    case ROCSHMEM_U64: return launch_allreduce_typed<unsigned long long>(team, dest, source, nelems, op, algo, stream);
+    case ROCSHMEM_F32: return launch_allreduce_typed<float>(team, dest, source, nelems, op, algo, stream);
+    case ROCSHMEM_F64: return launch_allreduce_typed<double>(team, dest, source, nelems, op, algo, stream);
+    case ROCSHMEM_F16: return launch_allreduce_typed<__half>(team, dest, source, nelems, op, algo, stream);
+    case ROCSHMEM_BF16: return launch_allreduce_typed<__nv_bfloat16>(team, dest, source, nelems, op, algo, stream);
+    default: return cudaErrorInvalidValue;
+  }
+}
+
+static int launch_push(rocshmem_team_t team, void *dest, const void *source, size_t bytes, int root,
+                       int mode, void *stream, int flags) {
+  if (bytes == 0) return 0;
+  if (flags & COLL_PRE_SYNC) mode |= 0x100;
+  unsigned blocks = clamp_blocks(push_kernel, static_cast<unsigned>(coll_blocks_for(bytes)));
+  return launch_pes(push_kernel, blocks, kThreads, 0, static_cast<cudaStream_t>(stream), false, team,
+                    static_cast<char *>(dest), static_cast<const char *>(source), bytes, root, mode);
+}
+
+int coll_broadcast(rocshmem_team_t team, void *dest, const void *source, size_t bytes, int root,
+                   void *stream, int flags) {
+  return launch_push(team, dest, source, bytes, root, 0, stream, flags);
+}
+int coll_fcollect(rocshmem_team_t team, void *dest, const void *source, size_t bytes, void *stream,
+                  int flags) {
+  return launch_push(team, dest, source, bytes, 0, 1, stream, flags);
+}
+int coll_alltoall(rocshmem_team_t team, void *dest, const void *source, size_t bytes, void *stream,
+                  int flags) {
+  return launch_push(team, dest, source, bytes, 0, 2, stream, flags);
+}
+
+}  // namespace kernels
+}  // namespace rocshmem

@@ -1,0 +1,65 @@
+// Memory providers: where the symmetric heap physically lives and how a peer's heap becomes
+// addressable.
+//
+// The reference owns one hipMalloc'd (or managed / host / fine-grained) allocation per PE
+// (src/memory/heap_memory.hpp:40-129, src/memory/heap_type.hpp:41-51) and maps peers with
+// hipIpcGetMemHandle / hipIpcOpenMemHandle into unrelated addresses that it keeps in a table
+// (src/ipc_policy.cpp:34-118). Here a provider reserves ONE virtual window of n_pes * stride bytes
+// and maps PE p's allocation at window + p * stride, so a remote address is
+// local + (pe - my_pe) * stride with no table lookup:
+//   * CudaVmmProvider: cuMemCreate physical allocations exported as POSIX file descriptors,
+//     cuMemImportFromShareableHandle + cuMemMap + cuMemSetAccess on the importing side. Optionally
+//     binds the allocations to an NVLink multicast object (NVLS) mapped at a second window.
+//   * HostShmProvider: memfd + mmap(MAP_SHARED | MAP_FIXED). It plays the role of the reference's
+//     USE_HOST_HEAP build and lets the whole host runtime run, multi-process, on a machine with no
+//     GPU.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <memory>
+#include <string>
+#include <vector>
+
+namespace rocshmem {
+
+struct MemHandle {
+  uint64_t opaque = 0;  // CUmemGenericAllocationHandle, or the memfd for host memory
+  int fd = -1;          // shareable descriptor (owned; -1 once closed or if never exported)
+  size_t bytes = 0;
+  bool imported = false;
+};
+
+class MemProvider {
+ public:
+  virtual ~MemProvider() = default;
+  virtual bool is_cuda() const = 0;
+  virtual const char *name() const = 0;
+  virtual size_t granularity() const = 0;
+
+  virtual char *reserve(size_t bytes) = 0;
+  virtual void release(char *va, size_t bytes) = 0;
+  // `shareable`: the handle will be exported to other processes.
+  virtual MemHandle create(size_t bytes, bool shareable) = 0;
+  virtual MemHandle import_fd(int fd, size_t bytes) = 0;
+  virtual void map(char *va, const MemHandle &h) = 0;
+  virtual void unmap(char *va, size_t bytes) = 0;
+  virtual void destroy(MemHandle &h) = 0;
+
+  // Host access to mapped memory (device memory is not CPU-addressable).
+  virtual void write(void *dst, const void *src, size_t bytes) = 0;
+  virtual void read(void *dst, const void *src, size_t bytes) = 0;
+  virtual void zero(void *dst, size_t bytes) = 0;
+
+  // NVLS. Returns false when multicast is unsupported; never throws for "not available".
+  virtual bool multicast_supported() const { return false; }
+};
+
+std::unique_ptr<MemProvider> make_host_shm_provider();
+// Returns nullptr (and sets *why) when no CUDA device / driver is usable.
+std::unique_ptr<MemProvider> make_cuda_vmm_provider(int device, std::string *why);
+
+// Number of CUDA devices visible to this process, 0 when CUDA is unusable.
+int cuda_device_count();
+
+}  // namespace rocshmem

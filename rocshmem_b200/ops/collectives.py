@@ -1,0 +1,85 @@
+"""Collectives on symmetric tensors.
+
+Two flavours of every operation:
+
+* host-blocking (``broadcast``, ``reduce``, ``fcollect``, ``alltoall``): the OpenSHMEM host API, which
+  returns when the collective has completed on this PE (reference: the host collectives of
+  ``include/rocshmem/rocshmem_COLL.hpp``, implemented there with MPI);
+* stream-ordered (``*_async``): the library's multi-block kernels enqueued on a CUDA stream, for use
+  next to other GPU work. They need the CUDA backend.
+
+All tensors must come from :func:`rocshmem_b200.empty` / :func:`rocshmem_b200.zeros` (symmetric heap).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import runtime as rt
+
+
+def _team(team: Optional[rt.Team]) -> int:
+    return (team or rt.team_world()).handle
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+# ---- host-blocking -----------------------------------------------------------------------------------
+
+def broadcast(dest: torch.Tensor, source: torch.Tensor, root: int, team: Optional[rt.Team] = None) -> int:
+    """``dest`` on every member except the root receives the root's ``source``."""
+    return rt._C().broadcast(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source), root)
+
+
+def reduce(dest: torch.Tensor, source: torch.Tensor, op: int = rt.OP_SUM,
+           team: Optional[rt.Team] = None) -> int:
+    """All-reduce: every member's ``dest`` receives the element-wise reduction of all ``source``s."""
+    return rt._C().reduce(_team(team), dest.data_ptr(), source.data_ptr(), source.numel(),
+                          rt.dtype_code(source.dtype), op)
+
+
+def fcollect(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None) -> int:
+    """All-gather: member *i*'s ``source`` lands at ``dest[i * source.numel():]`` on every member."""
+    return rt._C().fcollect(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source))
+
+
+def alltoall(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None) -> int:
+    """Member *i* sends chunk *j* of ``source`` to member *j*, which stores it as chunk *i* of ``dest``."""
+    n = (team or rt.team_world()).n_pes()
+    return rt._C().alltoall(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source) // n)
+
+
+# ---- stream-ordered ---------------------------------------------------------------------------------------
+
+def barrier_async(team: Optional[rt.Team] = None, stream=None) -> None:
+    rt._C().k_barrier(_team(team), _stream(stream))
+
+
+def allreduce_async(dest: torch.Tensor, source: torch.Tensor, op: int = rt.OP_SUM,
+                    team: Optional[rt.Team] = None, algo: int = rt.ALLREDUCE_AUTO, stream=None) -> None:
+    rt._C().k_allreduce(_team(team), dest.data_ptr(), source.data_ptr(), source.numel(),
+                        rt.dtype_code(source.dtype), op, algo, _stream(stream))
+
+
+def broadcast_async(dest: torch.Tensor, source: torch.Tensor, root: int, team: Optional[rt.Team] = None,
+                    stream=None, pre_sync: bool = True) -> None:
+    rt._C().k_broadcast(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source), root,
+                        _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)
+
+
+def fcollect_async(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None, stream=None,
+                   pre_sync: bool = True) -> None:
+    rt._C().k_fcollect(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source),
+                       _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)
+
+
+def alltoall_async(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None, stream=None,
+                   pre_sync: bool = True) -> None:
+    n = (team or rt.team_world()).n_pes()
+    rt._C().k_alltoall(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source) // n,
+                       _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)

@@ -1,0 +1,460 @@
+"""Python face of the runtime: initialisation over a ``torch.distributed`` store, the symmetric heap
+as torch tensors, teams, contexts and the host-side OpenSHMEM calls.
+
+Reference counterparts: ``rocshmem_init`` / ``rocshmem_malloc`` / teams / contexts and the host API of
+``include/rocshmem/rocshmem.hpp``; MPI is replaced by a key-value store (``TCPStore`` or the store of the
+default process group) that the native runtime uses for every bootstrap exchange.
+
+The symmetric heap is GPU memory, so this layer is also what replaces the reference examples' habit
+of dereferencing ``rocshmem_malloc`` pointers on the CPU: tensors returned by :func:`empty` /
+:func:`zeros` live on the heap, at the same offset on every PE.
+"""
+from __future__ import annotations
+
+import ctypes
+import datetime
+import os
+from dataclasses import dataclass
+from typing import Dict, Optional, Sequence
+
+import torch
+
+from . import _native
+
+# ---- constants mirrored from rocshmem_common.h -------------------------------------------------------
+CMP_EQ, CMP_NE, CMP_GT, CMP_GE, CMP_LT, CMP_LE = range(6)
+OP_SUM, OP_MAX, OP_MIN, OP_PROD, OP_AND, OP_OR, OP_XOR = range(7)
+SIGNAL_SET, SIGNAL_ADD = 0, 1
+AMO_FETCH, AMO_SWAP, AMO_CAS, AMO_ADD, AMO_AND, AMO_OR, AMO_XOR = range(7)
+CTX_NOSTORE, CTX_SERIALIZED, CTX_WG_PRIVATE, CTX_SHARED = 1, 2, 4, 8
+ALLREDUCE_AUTO, ALLREDUCE_ONE_SHOT, ALLREDUCE_TWO_SHOT, ALLREDUCE_NVLS = range(4)
+COLL_PRE_SYNC = 1
+SUCCESS, ERROR = 0, 1
+
+_DTYPE_CODE = {
+    torch.int8: 0, torch.uint8: 1, torch.int16: 2, torch.int32: 4, torch.int64: 6,
+    torch.float32: 8, torch.float64: 9, torch.float16: 10, torch.bfloat16: 11,
+}
+for _name, _code in (("uint16", 3), ("uint32", 5), ("uint64", 7)):
+    if hasattr(torch, _name):
+        _DTYPE_CODE[getattr(torch, _name)] = _code
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    try:
+        return _DTYPE_CODE[dtype]
+    except KeyError:
+        raise TypeError(f"rocshmem_b200: unsupported dtype {dtype}") from None
+
+
+@dataclass
+class _State:
+    initialised: bool = False
+    device: Optional[torch.device] = None
+    store: object = None
+    prefix: str = ""
+    allocations: Dict[int, int] = None  # data_ptr -> bytes
+
+
+_state = _State(allocations={})
+_init_count = 0
+
+
+def _C():
+    return _native.load()
+
+
+# ---- lifecycle ---------------------------------------------------------------------------------------------
+
+def init(store=None, rank: Optional[int] = None, world_size: Optional[int] = None, *,
+         n_local: int = 1, device: Optional[int] = None, heap_size=None, backend: Optional[str] = None,
+         timeout_s: float = 120.0, **overrides) -> None:
+    """Collective initialisation.
+
+    ``store`` is any ``torch.distributed`` store; when omitted, the store of the default process group
+    is used if there is one, else a ``TCPStore`` is created from ``MASTER_ADDR`` / ``MASTER_PORT``
+    (``RANK`` / ``WORLD_SIZE`` as set by torchrun), else the process runs alone. ``n_local > 1`` hosts
+    several PEs in this process on one GPU. Keyword overrides use the names of the environment
+    variables (``ROCSHMEM_HEAP_SIZE='64M'`` ...); ``heap_size`` and ``backend`` are shorthands.
+    """
+    global _init_count
+    C = _C()
+    if C.is_initialized():
+        raise RuntimeError("rocshmem_b200.init: already initialised")
+    rank = int(os.environ.get("RANK", "0")) if rank is None else rank
+    world_size = int(os.environ.get("WORLD_SIZE", "1")) if world_size is None else world_size
+    ov = {str(k): str(v) for k, v in overrides.items()}
+    if heap_size is not None:
+        ov["ROCSHMEM_HEAP_SIZE"] = str(heap_size)
+    if backend is not None:
+        ov["ROCSHMEM_BACKEND"] = backend
+    want_cuda = ov.get("ROCSHMEM_BACKEND", os.environ.get("ROCSHMEM_BACKEND", "auto")) != "host"
+    if device is None:
+        device = int(os.environ.get("LOCAL_RANK", "0"))
+    if want_cuda and torch.cuda.is_available():
+        device = device % torch.cuda.device_count()
+        torch.cuda.set_device(device)
+        _state.device = torch.device("cuda", device)
+    else:
+        _state.device = torch.device("cpu")
+    timeout_ms = int(timeout_s * 1000)
+    if world_size > 1:
+        if store is None:
+            import torch.distributed as dist
+            if dist.is_available() and dist.is_initialized():
+                store = dist.distributed_c10d._get_default_store()
+            else:
+                store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"),
+                                      int(os.environ.get("MASTER_PORT", "29500")), world_size,
+                                      rank == 0, timeout=datetime.timedelta(seconds=timeout_s))
+        _init_count += 1
+        prefix = f"rocshmem_b200/{_init_count}/"
+        wait = datetime.timedelta(milliseconds=timeout_ms)
+
+        def put(key: str, value: bytes) -> None:
+            store.set(prefix + key, value)
+
+        def get(key: str, ms: int) -> bytes:
+            store.wait([prefix + key], datetime.timedelta(milliseconds=ms) if ms > 0 else wait)
+            return bytes(store.get(prefix + key))
+
+        _state.store = store
+        _state.prefix = prefix
+        C.init_with_store(rank, world_size, put, get, ov, n_local, device, timeout_ms)
+    else:
+        C.init_file(0, 1, "", ov, n_local, device, timeout_ms)
+    _state.initialised = True
+    _state.allocations = {}
+
+
+def finalize() -> None:
+    C = _C()
+    if C.is_initialized():
+        if C.is_cuda():
+            torch.cuda.synchronize()
+        C.finalize()
+    _state.initialised = False
+    _state.allocations = {}
+
+
+def is_initialized() -> bool:
+    return _C().is_initialized()
+
+
+def my_pe() -> int:
+    return _C().my_pe()
+
+
+def n_pes() -> int:
+    return _C().n_pes()
+
+
+def n_local_pes() -> int:
+    return _C().n_local()
+
+
+def set_local_pe(index: int) -> None:
+    """With several PEs per process: choose the PE that later host calls of this thread act for."""
+    _C().set_local_pe(index)
+
+
+def is_cuda() -> bool:
+    return _C().is_cuda()
+
+
+def device() -> torch.device:
+    return _state.device
+
+
+def nvls_available() -> bool:
+    return _C().nvls_available()
+
+
+# ---- heap as tensors ------------------------------------------------------------------------------------------
+
+class _CudaBlob:
+    """Exposes a raw device address through ``__cuda_array_interface__`` so torch can wrap it."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {
+            "shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3, "strides": None,
+        }
+
+
+def tensor_from_address(ptr: int, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+    """A tensor view of heap memory at ``ptr`` (no ownership)."""
+    numel = 1
+    for s in shape:
+        numel *= int(s)
+    nbytes = numel * torch.empty((), dtype=dtype).element_size()
+    if nbytes == 0:
+        return torch.empty(tuple(shape), dtype=dtype, device=_state.device)
+    if _C().is_cuda():
+        raw = torch.as_tensor(_CudaBlob(ptr, nbytes), device=_state.device)
+    else:
+        buf = (ctypes.c_uint8 * nbytes).from_address(ptr)
+        raw = torch.frombuffer(buf, dtype=torch.uint8)
+    return raw.view(dtype).view(tuple(shape))
+
+
+def empty(shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Collective ``rocshmem_malloc``: a tensor at the same heap offset on every PE."""
+    if isinstance(shape, int):
+        shape = (shape,)
+    numel = 1
+    for s in shape:
+        numel *= int(s)
+    nbytes = max(1, numel * torch.empty((), dtype=dtype).element_size())
+    ptr = _C().malloc(nbytes)
+    if ptr == 0:
+        raise MemoryError(f"rocshmem_b200: symmetric heap exhausted ({nbytes} bytes requested, "
+                          f"{_C().heap_avail()} available)")
+    _state.allocations[ptr] = nbytes
+    return tensor_from_address(ptr, shape, dtype)
+
+
+def zeros(shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    t = empty(shape, dtype)
+    for l in range(n_local_pes()):
+        local_view(t, l).zero_()
+    if is_cuda():
+        torch.cuda.current_stream().synchronize()
+    barrier_all()
+    return t
+
+
+def free(t: torch.Tensor) -> None:
+    """Collective ``rocshmem_free`` of a tensor obtained from :func:`empty` / :func:`zeros`."""
+    ptr = t.data_ptr()
+    if ptr not in _state.allocations:
+        raise ValueError("rocshmem_b200.free: tensor does not start a symmetric allocation")
+    del _state.allocations[ptr]
+    _C().free(ptr)
+
+
+def local_view(t: torch.Tensor, local_index: int) -> torch.Tensor:
+    """The copy of symmetric tensor ``t`` that belongs to local PE ``local_index`` of this process."""
+    if local_index == 0:
+        return t
+    C = _C()
+    ptr = C.ptr(t.data_ptr(), C.first_pe() + local_index)
+    return tensor_from_address(ptr, t.shape, t.dtype)
+
+
+def peer_address(t: torch.Tensor, pe: int) -> int:
+    """Address of ``t`` on ``pe`` inside this process's mapping of the window (``rocshmem_ptr``)."""
+    return _C().ptr(t.data_ptr(), pe)
+
+
+def heap_info() -> dict:
+    C = _C()
+    return {"size": C.heap_size(), "stride": C.heap_stride(), "used": C.heap_used(),
+            "avail": C.heap_avail(), "backend": C.backend_name(), "nvls": C.nvls_available()}
+
+
+# ---- teams and contexts -------------------------------------------------------------------------------------------
+
+class Team:
+    """A strided set of PEs (``rocshmem_team_t``)."""
+
+    def __init__(self, handle: int):
+        self.handle = handle
+
+    @property
+    def valid(self) -> bool:
+        return self.handle != 0
+
+    def n_pes(self) -> int:
+        return _C().team_n_pes(self.handle)
+
+    def my_pe(self) -> int:
+        return _C().team_my_pe(self.handle)
+
+    def translate_pe(self, pe: int, dst: "Team") -> int:
+        return _C().team_translate_pe(self.handle, pe, dst.handle)
+
+    def split_strided(self, start: int, stride: int, size: int) -> "Team":
+        """Collective over this team. Returns an invalid team on PEs that are not members; raises
+        ``ValueError`` for an impossible request and ``RuntimeError`` when no team slot is free."""
+        rc, h = _C().team_split_strided(self.handle, start, stride, size)
+        if rc != 0:
+            if _C().num_user_teams() >= team_capacity() - 1:
+                raise RuntimeError("rocshmem_b200: no free team slot")
+            raise ValueError(f"rocshmem_b200: invalid team split ({start}, {stride}, {size})")
+        return Team(h)
+
+    def sync(self) -> int:
+        return _C().team_sync(self.handle)
+
+    def destroy(self) -> None:
+        if self.handle:
+            _C().team_destroy(self.handle)
+            self.handle = 0
+
+    def __repr__(self) -> str:
+        return f"Team(handle=0x{self.handle:x})"
+
+
+def team_world() -> Team:
+    return Team(_C().team_world())
+
+
+def team_capacity() -> int:
+    return _C().config_from_env({})["max_teams"]
+
+
+class Context:
+    """A host context: an ordering and completion domain backed by its own stream."""
+
+    def __init__(self, options: int = 0, team: Optional[Team] = None):
+        if team is None:
+            rc, c, t = _C().ctx_create(options)
+        else:
+            rc, c, t = _C().team_create_ctx(team.handle, options)
+        if rc != 0:
+            raise RuntimeError("rocshmem_b200: host context pool exhausted")
+        self.handle, self.team_handle = c, t
+
+    def quiet(self) -> None:
+        _C().quiet(self.handle, self.team_handle)
+
+    def destroy(self) -> None:
+        if self.handle:
+            _C().ctx_destroy(self.handle, self.team_handle)
+            self.handle = 0
+
+
+def _ctx_args(ctx: Optional[Context]):
+    return (ctx.handle, ctx.team_handle) if ctx is not None else (0, 0)
+
+
+# ---- host-side OpenSHMEM calls -----------------------------------------------------------------------------------------
+
+def _nbytes(t: torch.Tensor) -> int:
+    return t.numel() * t.element_size()
+
+
+def _check_contig(*ts: torch.Tensor) -> None:
+    for t in ts:
+        if not t.is_contiguous():
+            raise ValueError("rocshmem_b200: tensors must be contiguous")
+
+
+def putmem(dest: torch.Tensor, source: torch.Tensor, pe: int, ctx: Optional[Context] = None,
+           nbi: bool = False) -> None:
+    """Copy ``source`` (any local tensor) into symmetric ``dest`` on ``pe``."""
+    _check_contig(dest, source)
+    n = min(_nbytes(dest), _nbytes(source))
+    fn = _C().putmem_nbi if nbi else _C().putmem
+    fn(dest.data_ptr(), source.data_ptr(), n, pe, *_ctx_args(ctx))
+
+
+def getmem(dest: torch.Tensor, source: torch.Tensor, pe: int, ctx: Optional[Context] = None,
+           nbi: bool = False) -> None:
+    """Copy symmetric ``source`` on ``pe`` into local ``dest``."""
+    _check_contig(dest, source)
+    n = min(_nbytes(dest), _nbytes(source))
+    fn = _C().getmem_nbi if nbi else _C().getmem
+    fn(dest.data_ptr(), source.data_ptr(), n, pe, *_ctx_args(ctx))
+
+
+def _bits(value, dtype: torch.dtype) -> int:
+    t = torch.tensor([value], dtype=dtype)
+    width = t.element_size()
+    view = {1: torch.uint8, 2: torch.int16, 4: torch.int32, 8: torch.int64}[width]
+    return int(t.view(view).item()) & ((1 << (8 * width)) - 1)
+
+
+def _from_bits(bits: int, dtype: torch.dtype):
+    width = torch.empty((), dtype=dtype).element_size()
+    bits &= (1 << (8 * width)) - 1
+    view = {1: torch.uint8, 2: torch.int16, 4: torch.int32, 8: torch.int64}[width]
+    signed = bits - (1 << (8 * width)) if (view != torch.uint8 and bits >> (8 * width - 1)) else bits
+    return torch.tensor([signed], dtype=view).view(dtype).item()
+
+
+def _element_ptr(t: torch.Tensor, index: int) -> int:
+    return t.data_ptr() + index * t.element_size()
+
+
+def atomic(op: int, target: torch.Tensor, value=0, pe: int = 0, cond=0, index: int = 0,
+           ctx: Optional[Context] = None):
+    """Atomic ``op`` (``AMO_*``) on element ``index`` of symmetric ``target`` at ``pe``; returns the
+    previous value."""
+    code = dtype_code(target.dtype)
+    old = _C().amo(op, code, _element_ptr(target, index), _bits(value, target.dtype),
+                   _bits(cond, target.dtype), pe, *_ctx_args(ctx))
+    return _from_bits(old, target.dtype)
+
+
+def atomic_fetch_add(target, value, pe, index=0, ctx=None):
+    return atomic(AMO_ADD, target, value, pe, index=index, ctx=ctx)
+
+
+def atomic_compare_swap(target, cond, value, pe, index=0, ctx=None):
+    return atomic(AMO_CAS, target, value, pe, cond=cond, index=index, ctx=ctx)
+
+
+def atomic_swap(target, value, pe, index=0, ctx=None):
+    return atomic(AMO_SWAP, target, value, pe, index=index, ctx=ctx)
+
+
+def atomic_fetch(target, pe, index=0, ctx=None):
+    return atomic(AMO_FETCH, target, 0, pe, index=index, ctx=ctx)
+
+
+def wait_until(ivar: torch.Tensor, cmp: int, value, index: int = 0) -> int:
+    """Bounded wait on a local symmetric variable; ``SUCCESS`` or ``ERROR`` (time-out)."""
+    return _C().wait_until(_element_ptr(ivar, index), dtype_code(ivar.dtype), cmp, _bits(value, ivar.dtype))
+
+
+def test(ivar: torch.Tensor, cmp: int, value, index: int = 0) -> bool:
+    return bool(_C().test(_element_ptr(ivar, index), dtype_code(ivar.dtype), cmp, _bits(value, ivar.dtype)))
+
+
+def wait_until_all(ivars: torch.Tensor, cmp: int, values, status: Sequence[int] = ()) -> None:
+    vec = isinstance(values, (list, tuple))
+    vals = [_bits(v, ivars.dtype) for v in (values if vec else [values])]
+    _C().wait_until_all(ivars.data_ptr(), ivars.numel(), list(status), dtype_code(ivars.dtype), cmp, vals, vec)
+
+
+def wait_until_any(ivars: torch.Tensor, cmp: int, values, status: Sequence[int] = ()) -> int:
+    vec = isinstance(values, (list, tuple))
+    vals = [_bits(v, ivars.dtype) for v in (values if vec else [values])]
+    r = _C().wait_until_any(ivars.data_ptr(), ivars.numel(), list(status), dtype_code(ivars.dtype), cmp, vals, vec)
+    return -1 if r >= (1 << 63) else r
+
+
+def wait_until_some(ivars: torch.Tensor, cmp: int, values, status: Sequence[int] = ()):
+    vec = isinstance(values, (list, tuple))
+    vals = [_bits(v, ivars.dtype) for v in (values if vec else [values])]
+    return _C().wait_until_some(ivars.data_ptr(), ivars.numel(), list(status), dtype_code(ivars.dtype), cmp, vals, vec)
+
+
+def fence() -> None:
+    _C().fence()
+
+
+def quiet(ctx: Optional[Context] = None) -> None:
+    _C().quiet(*_ctx_args(ctx))
+
+
+def barrier_all() -> None:
+    _C().barrier_all()
+
+
+def sync_all() -> None:
+    _C().sync_all()
+
+
+def get_error(local: int = -1) -> dict:
+    """First error recorded by a bounded wait or debug check on this PE (``kind == 0``: none)."""
+    return _C().get_error(local)
+
+
+def clear_error() -> None:
+    _C().clear_error()
+
+
+def set_wait_timeout_ms(ms: int) -> None:
+    _C().set_wait_timeout_ms(ms)
