@@ -23,6 +23,9 @@ static __constant__ rocshmem_device_state g_state[ROCSHMEM_MAX_LOCAL_PES];
 static __constant__ int g_n_local = 1;
 
 static void upload_state(const rocshmem_device_state *states, int n_local) {
+  // Each shared object may carry its own copy of the CUDA runtime; make sure this one works on the
+  // device that hosts the PEs before touching the module's symbols.
+  cudaSetDevice(states[0].device_ordinal);
   cudaMemcpyToSymbol(g_state, states, sizeof(rocshmem_device_state) * n_local);
   cudaMemcpyToSymbol(g_n_local, &n_local, sizeof(int));
 }

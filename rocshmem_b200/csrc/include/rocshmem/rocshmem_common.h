@@ -243,6 +243,7 @@ struct rocshmem_device_state {
   unsigned long long wait_timeout_ns;  // budget of every device-side wait
   int debug_checks;                    // 1: validate pe / symmetric addresses on the device
   int use_proxy;                       // 1: route thread-level RMA/AMO through the host proxy
+  int device_ordinal;                  // CUDA device that hosts this PE
 };
 
 // Library (multi-block) collectives: block b of a PE synchronises with block b of every peer, so

@@ -286,6 +286,7 @@ void Runtime::build_states() {
     s.max_teams = cfg_.max_teams;
     s.max_ctxs = cfg_.max_contexts;
     s.wait_timeout_ns = cfg_.wait_timeout_ms * 1000000ull;
+    s.device_ordinal = device_;
     s.debug_checks = cfg_.debug_checks;
     s.use_proxy = (proxy_ && proxy_->running()) ? cfg_.use_proxy : 0;
   }

@@ -1,0 +1,320 @@
+"""One PE process of a multi-process test scenario (started by mp_util.run_ranks).
+
+Environment: RANK / WORLD_SIZE / MASTER_ADDR / MASTER_PORT as torchrun sets them, ROCSHMEM_TEST_TMP a
+scratch directory shared by the ranks, ROCSHMEM_TEST_BACKEND 'host' (default) or 'cuda'.
+"""
+import os
+import sys
+import time
+
+import torch
+
+import rocshmem_b200 as shm
+from rocshmem_b200.ops import collectives as coll
+
+RANK = int(os.environ["RANK"])
+WORLD = int(os.environ["WORLD_SIZE"])
+TMP = os.environ.get("ROCSHMEM_TEST_TMP", "/tmp")
+BACKEND = os.environ.get("ROCSHMEM_TEST_BACKEND", "host")
+
+
+def init(heap="64M", **kw):
+    shm.init(heap_size=heap, backend=BACKEND, timeout_s=float(os.environ.get("ROCSHMEM_TEST_TIMEOUT", "60")), **kw)
+    assert shm.n_pes() == WORLD and shm.my_pe() == RANK
+
+
+def dev():
+    return shm.device()
+
+
+def host_plumbing():
+    """64 MiB heap, 1 MiB int64 buffers filled with pe * 2^32 + i: put to the right neighbour, get it
+    back, fetch-add on a symmetric counter, barrier; everything bit-exact."""
+    init("64M")
+    n = (1 << 20) // 8
+    me, npes = shm.my_pe(), shm.n_pes()
+    src = shm.empty(n, torch.int64)
+    dst = shm.zeros(n, torch.int64)
+    back = torch.zeros(n, dtype=torch.int64, device=dev())
+    counter = shm.zeros(1, torch.int64)
+    src.copy_(torch.arange(n, dtype=torch.int64, device=dev()) + (me << 32))
+    if shm.is_cuda():
+        torch.cuda.synchronize()
+    shm.barrier_all()
+    right, left = (me + 1) % npes, (me - 1) % npes
+    shm.putmem(dst, src, right)
+    shm.barrier_all()
+    expect = torch.arange(n, dtype=torch.int64) + (left << 32)
+    assert torch.equal(dst.cpu(), expect), "put pattern mismatch"
+    shm.getmem(back, dst, right)
+    assert torch.equal(back.cpu(), torch.arange(n, dtype=torch.int64) + (me << 32)), "get pattern mismatch"
+    olds = [shm.atomic_fetch_add(counter, 1, 0) for _ in range(10)]
+    assert all(0 <= o < 10 * npes for o in olds) and len(set(olds)) == 10
+    shm.barrier_all()
+    if me == 0:
+        assert int(counter.cpu()[0]) == 10 * npes
+    # compare-and-swap election: exactly one PE wins
+    flag = shm.zeros(1, torch.int64)
+    won = shm.atomic_compare_swap(flag, 0, me + 1, 0) == 0
+    shm.barrier_all()
+    winner = shm.atomic_fetch(flag, 0)
+    assert (winner == me + 1) == won
+    shm.free(flag)
+    shm.finalize()
+
+
+def store_bootstrap():
+    """Same runtime, bootstrapped through a torch.distributed TCPStore."""
+    import datetime
+    import torch.distributed as dist
+    store = dist.TCPStore("127.0.0.1", int(os.environ["MASTER_PORT"]), WORLD, RANK == 0,
+                          timeout=datetime.timedelta(seconds=60))
+    shm.init(store=store, heap_size="8M", backend=BACKEND)
+    x = shm.zeros(16, torch.float32)
+    x.fill_(float(RANK + 1))
+    if shm.is_cuda():
+        torch.cuda.synchronize()
+    shm.barrier_all()
+    got = torch.zeros(16, dtype=torch.float32, device=dev())
+    shm.getmem(got, x, (RANK + 1) % WORLD)
+    assert float(got.cpu()[0]) == float((RANK + 1) % WORLD + 1)
+    shm.barrier_all()
+    shm.finalize()
+
+
+def teams():
+    init("16M")
+    me, npes = shm.my_pe(), shm.n_pes()
+    world = shm.team_world()
+    assert world.n_pes() == npes and world.my_pe() == me
+    even = world.split_strided(0, 2, (npes + 1) // 2)
+    if me % 2 == 0:
+        assert even.valid and even.my_pe() == me // 2 and even.n_pes() == (npes + 1) // 2
+        assert even.translate_pe(even.my_pe(), world) == me
+        a = None
+    else:
+        assert not even.valid
+    src = shm.zeros(64, torch.int64)
+    dst = shm.zeros(64, torch.int64)
+    src.fill_(me + 1)
+    if shm.is_cuda():
+        torch.cuda.synchronize()
+    shm.barrier_all()
+    if even.valid:
+        assert coll.reduce(dst, src, shm.OP_SUM, even) == 0
+        expect = sum(p + 1 for p in range(0, npes, 2))
+        assert int(dst.cpu()[0]) == expect and int(dst.cpu()[-1]) == expect
+    shm.barrier_all()
+    # invalid requests
+    for bad in ((0, 1, npes + 1), (npes, 1, 1), (0, 0, 1), (-1, 1, 1)):
+        try:
+            world.split_strided(*bad)
+            raise AssertionError(f"split {bad} should have been rejected")
+        except ValueError:
+            pass
+    # sub-split of the even team: its first member alone
+    if even.valid:
+        solo = even.split_strided(0, 1, 1)
+        assert solo.valid == (even.my_pe() == 0)
+        if solo.valid:
+            assert solo.n_pes() == 1 and solo.translate_pe(0, world) == 0
+            solo.destroy()
+        even.destroy()
+    # 39 duplicates of the world fit (slot 0 is TEAM_WORLD), the 40th is refused
+    dups = [world.split_strided(0, 1, npes) for _ in range(39)]
+    assert all(d.valid for d in dups)
+    try:
+        world.split_strided(0, 1, npes)
+        raise AssertionError("40th team should fail")
+    except RuntimeError:
+        pass
+    # every duplicate is usable and independent
+    assert coll.reduce(dst, src, shm.OP_MAX, dups[17]) == 0
+    assert int(dst.cpu()[3]) == npes
+    for d in dups:
+        d.destroy()
+    again = world.split_strided(0, 1, npes)
+    assert again.valid
+    again.destroy()
+    shm.barrier_all()
+    shm.finalize()
+
+
+def collectives_host():
+    init("64M")
+    me, npes = shm.my_pe(), shm.n_pes()
+    world = shm.team_world()
+    for dtype, n in ((torch.float32, 1000), (torch.int32, 17), (torch.float64, 4096), (torch.int64, 1),
+                     (torch.bfloat16, 513), (torch.int16, 129)):
+        src = shm.zeros(n, dtype)
+        dst = shm.zeros(n, dtype)
+        gen = torch.Generator().manual_seed(1234 + me)
+        if dtype.is_floating_point:
+            host = torch.randn(n, generator=gen, dtype=torch.float64).to(dtype)
+        else:
+            host = torch.randint(-50, 50, (n,), generator=gen, dtype=torch.int64).to(dtype)
+        src.copy_(host.to(dev()))
+        if shm.is_cuda():
+            torch.cuda.synchronize()
+        shm.barrier_all()
+        alls = []
+        for p in range(npes):
+            g = torch.Generator().manual_seed(1234 + p)
+            if dtype.is_floating_point:
+                alls.append(torch.randn(n, generator=g, dtype=torch.float64).to(dtype))
+            else:
+                alls.append(torch.randint(-50, 50, (n,), generator=g, dtype=torch.int64).to(dtype))
+        ops = [(shm.OP_SUM, lambda xs: torch.stack(xs).sum(0)), (shm.OP_MAX, lambda xs: torch.stack(xs).max(0).values),
+               (shm.OP_MIN, lambda xs: torch.stack(xs).min(0).values)]
+        if not dtype.is_floating_point:
+            def fold(fn):
+                def f(xs):
+                    acc = xs[0].clone()
+                    for x in xs[1:]:
+                        acc = fn(acc, x)
+                    return acc
+                return f
+            ops += [(shm.OP_AND, fold(torch.bitwise_and)), (shm.OP_OR, fold(torch.bitwise_or)),
+                    (shm.OP_XOR, fold(torch.bitwise_xor))]
+        for op, ref_fn in ops:
+            assert coll.reduce(dst, src, op, world) == 0
+            ref = ref_fn([a.to(torch.float64) if dtype.is_floating_point else a.to(torch.int64) for a in alls])
+            got = dst.cpu().to(ref.dtype)
+            if dtype.is_floating_point:
+                tol = 2e-2 if dtype == torch.bfloat16 else 1e-5
+                assert torch.allclose(got, ref, rtol=tol, atol=tol * npes), (dtype, op)
+            else:
+                assert torch.equal(got, ref.to(torch.int64)), (dtype, op)
+        # in place
+        assert coll.reduce(src, src, shm.OP_SUM, world) == 0
+        shm.free(dst)
+        shm.free(src)
+    # broadcast: the root's dest stays untouched
+    src = shm.zeros(300, torch.int32)
+    dst = shm.zeros(300, torch.int32)
+    src.fill_(1000 + me)
+    dst.fill_(-1)
+    if shm.is_cuda():
+        torch.cuda.synchronize()
+    shm.barrier_all()
+    root = npes - 1
+    assert coll.broadcast(dst, src, root) == 0
+    want = -1 if me == root else 1000 + root
+    assert torch.all(dst.cpu() == want)
+    # fcollect and alltoall
+    gat = shm.zeros(300 * npes, torch.int32)
+    assert coll.fcollect(gat, src) == 0
+    g = gat.cpu().view(npes, 300)
+    assert all(torch.all(g[p] == 1000 + p) for p in range(npes))
+    a2a_src = shm.zeros(npes * 7, torch.int32)
+    a2a_dst = shm.zeros(npes * 7, torch.int32)
+    a2a_src.copy_((torch.arange(npes * 7, dtype=torch.int32) + 100 * me).to(dev()))
+    if shm.is_cuda():
+        torch.cuda.synchronize()
+    shm.barrier_all()
+    assert coll.alltoall(a2a_dst, a2a_src) == 0
+    got = a2a_dst.cpu().view(npes, 7)
+    for p in range(npes):
+        assert torch.equal(got[p], torch.arange(7, dtype=torch.int32) + me * 7 + 100 * p)
+    # active-set reduction over PEs {0, 2, ...}: only the members call
+    if me % 2 == 0 and npes >= 2:
+        s2 = src  # 1000 + me
+        rc = shm.runtime._C().reduce_active_set(dst.data_ptr(), s2.data_ptr(), 300, shm.runtime.dtype_code(torch.int32),
+                                                shm.OP_SUM, 0, 1, (npes + 1) // 2)
+        assert rc == 0
+        assert int(dst.cpu()[0]) == sum(1000 + p for p in range(0, npes, 2))
+    shm.barrier_all()
+    shm.finalize()
+
+
+def wait_and_signal():
+    """Host wait_until / test family between processes."""
+    init("8M")
+    me, npes = shm.my_pe(), shm.n_pes()
+    flags = shm.zeros(npes, torch.int64)
+    one = torch.ones(1, dtype=torch.int64, device=dev()) * (me + 1)
+    for p in range(npes):
+        shm.putmem(flags[me:me + 1], one, p)
+    shm.wait_until_all(flags, shm.CMP_GT, 0)
+    assert shm.test(flags, shm.CMP_EQ, 1, index=0)
+    assert shm.wait_until_any(flags, shm.CMP_EQ, npes) == npes - 1
+    assert sorted(shm.wait_until_some(flags, shm.CMP_GE, 1)) == list(range(npes))
+    shm.wait_until_all(flags, shm.CMP_EQ, [p + 1 for p in range(npes)])
+    assert shm.wait_until_any(flags, shm.CMP_EQ, 1, status=[1] * npes) == -1
+    shm.barrier_all()
+    # a wait that nobody satisfies gives up after the configured budget
+    shm.set_wait_timeout_ms(200)
+    t0 = time.time()
+    assert shm.wait_until(flags, shm.CMP_EQ, 424242) == shm.ERROR
+    assert 0.15 < time.time() - t0 < 5.0
+    err = shm.get_error()
+    assert err["kind"] == 1 and err["expected"] == 424242
+    shm.clear_error()
+    assert shm.get_error()["count"] == 0
+    shm.barrier_all()
+    shm.finalize()
+
+
+def late_rank():
+    """Rank 1 never joins: the others' init must raise within the bootstrap time-out, not hang."""
+    if RANK == 1:
+        time.sleep(float(sys.argv[2]) if len(sys.argv) > 2 else 4.0)
+        return
+    os.environ["ROCSHMEM_TEST_TIMEOUT"] = "2"
+    t0 = time.time()
+    try:
+        init("8M")
+    except Exception as e:  # BootstrapError surfaces as RuntimeError
+        assert "timed out" in str(e) or "Timeout" in str(e) or "wait" in str(e).lower(), str(e)
+        assert time.time() - t0 < 30
+        print("detected:", str(e)[:120])
+        return
+    raise AssertionError("init succeeded although a rank never joined")
+
+
+def rank_leaves():
+    """A rank leaves between steps; the others learn of it from the membership record in the store
+    before their next collective and shrink to a team without it."""
+    from rocshmem_b200.parallel.membership import Membership
+    init("8M")
+    me, npes = shm.my_pe(), shm.n_pes()
+    mem = Membership.from_env(prefix="t1")
+    x = shm.zeros(8, torch.int64)
+    y = shm.zeros(8, torch.int64)
+    x.fill_(me + 1)
+    if shm.is_cuda():
+        torch.cuda.synchronize()
+    shm.barrier_all()
+    assert coll.reduce(y, x) == 0
+    leaver = npes - 1
+    if me == leaver:
+        # Leaves with nothing in flight: after the step, before the next one starts.
+        mem.announce_leave()
+        shm.runtime._C().quiet()
+        # The process stays until the others have stopped using its memory.
+        mem.wait_for("survivors-done", timeout_s=60)
+        return
+    alive = mem.wait_for_change(expected_alive=npes - 1, timeout_s=30)
+    assert alive == list(range(npes - 1)), alive
+    team = shm.team_world().split_strided(0, 1, npes - 1) if False else None
+    # Survivors use a team that excludes the leaver; the split involves the survivors only
+    # (an active-set style collective), so the absent rank is not needed.
+    rc = shm.runtime._C().reduce_active_set(y.data_ptr(), x.data_ptr(), 8, shm.runtime.dtype_code(torch.int64),
+                                            shm.OP_SUM, 0, 0, npes - 1)
+    assert rc == 0 and int(y.cpu()[0]) == sum(range(1, npes))
+    if me == 0:
+        mem.post("survivors-done")
+    del team
+
+
+SCENARIOS = {f.__name__: f for f in (host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+                                     late_rank, rank_leaves)}
+
+if __name__ == "__main__":
+    name = sys.argv[1]
+    if name.startswith("gpu_"):
+        import mp_gpu_scenarios
+        mp_gpu_scenarios.SCENARIOS[name]()
+    else:
+        SCENARIOS[name]()
+    print(f"rank {RANK}: {name} ok")

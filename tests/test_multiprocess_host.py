@@ -1,0 +1,27 @@
+"""Multi-process scenarios on the host-memory backend: real processes, real descriptor passing,
+the same runtime code as on GPUs."""
+import pytest
+
+from mp_util import assert_all_ok, run_ranks
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_host_api_plumbing(world):
+    assert_all_ok(run_ranks("host_plumbing", world))
+
+
+def test_torch_store_bootstrap():
+    assert_all_ok(run_ranks("store_bootstrap", 3))
+
+
+def test_teams_split_translate_capacity():
+    assert_all_ok(run_ranks("teams", 4))
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_host_collectives(world):
+    assert_all_ok(run_ranks("collectives_host", world))
+
+
+def test_wait_family_between_processes():
+    assert_all_ok(run_ranks("wait_and_signal", 3))
