@@ -152,7 +152,7 @@ __device__ __forceinline__ T *remote_ptr(const T *p, int pe) {
 template <typename T>
 __device__ __forceinline__ T *local_ptr(T *p) {
   const rocshmem_device_state &s = st();
-  return reinterpret_cast<T *>(reinterpret_cast<char *>(p) + size_t(s.local_index) * s.heap_stride);
+  return reinterpret_cast<T *>(reinterpret_cast<uintptr_t>(p) + size_t(s.local_index) * s.heap_stride);
 }
 
 __device__ __forceinline__ bool check_pe(int pe, int where) {

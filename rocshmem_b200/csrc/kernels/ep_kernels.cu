@@ -1,0 +1,565 @@
+// Expert-parallel MoE dispatch and combine as two fused kernels over NVLink peer memory.
+//
+// Dispatch (one cooperative kernel per rank):
+//   A. every block scans its share of the tokens: destination-rank bitmask per token (a token that
+//      selects several experts of one rank is sent to that rank once), per-block per-rank counts,
+//      per-expert counts;
+//   B. after one grid barrier each block derives its write offsets; block 0 publishes this rank's row
+//      of the rank-to-rank count matrix, and the per-expert counts, to every peer as single 64-bit
+//      words that carry the call's epoch in their upper half (data and "ready" flag in one store, so
+//      no fence and no separate flag);
+//   C. one warp per token: the bf16 row is loaded once, quantised to e4m3 with one fp32 scale per 128
+//      elements in registers (amax by shuffles inside 8-lane groups), and stored with 16-byte peer
+//      stores straight into its final row of every destination's receive buffer, together with the
+//      scales and a 128-byte metadata record. There is no staging buffer and no receiver-side copy;
+//   D. blocks pair up with the same block of every peer (release/acquire flags), so when the kernel
+//      has finished on a rank, everything sent to that rank is visible to its next kernel.
+// With the SLOTTED layout the write offset does not depend on other ranks' counts, so step C starts
+// right after the local count and the count exchange overlaps the payload (low-latency mode).
+//
+// Combine (one kernel per rank) is a pull: for each of its tokens a warp reads the result rows from
+// the (up to top_k) ranks the token went to, 16 bytes per lane with the loads of all sources in
+// flight together, accumulates in fp32 with the per-rank gate weight, and writes the bf16 row once.
+// Pulling needs no staging memory and no receive-side reduction pass.
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+
+#include "ep_kernels.hpp"
+#include "launch.cuh"
+#include "lib_common.cuh"
+
+namespace rocshmem {
+namespace kernels {
+
+namespace {
+
+constexpr unsigned kEpThreads = 512;
+constexpr int kMaxIters = EP_MAX_HIDDEN / 512;  // 16 iterations of 512 elements per warp
+
+using detail::remote_ptr;
+using detail::team_pe_to_world;
+
+// Symmetric arguments are given as addresses on the process's first local PE. Plain device pointers
+// (ordinary torch tensors) are passed through, which is what a process with one PE uses.
+template <typename T>
+__device__ __forceinline__ T *rebase(T *p) {
+  const rocshmem_device_state &s = st();
+  const char *c = reinterpret_cast<const char *>(p);
+  if (c >= s.window_base && c < s.window_base + size_t(s.n_pes) * s.heap_stride) return detail::local_ptr(p);
+  return p;
+}
+
+__device__ __forceinline__ unsigned long long pack(unsigned epoch, unsigned value) {
+  return (static_cast<unsigned long long>(epoch) << 32) | value;
+}
+
+// Spin (bounded) until the word carries `epoch`; returns its payload, or 0 with *ok = false.
+__device__ __forceinline__ unsigned wait_packed(const unsigned long long *p, unsigned epoch, int peer, bool *ok) {
+  unsigned long long v = detail::ld_relaxed_sys(p);
+  if (static_cast<unsigned>(v >> 32) != epoch) {
+    detail::SpinBudget budget(st().wait_timeout_ns);
+    while (static_cast<unsigned>((v = detail::ld_relaxed_sys(p)) >> 32) != epoch) {
+      if (!budget.keep_going()) {
+        detail::record_error(ROCSHMEM_ERR_BARRIER_TIMEOUT, peer, 70, p, epoch, v);
+        *ok = false;
+        return 0;
+      }
+    }
+  }
+  return static_cast<unsigned>(v & 0xffffffffu);
+}
+
+struct DispatchArgs {
+  EpConfig cfg;
+  EpBuffers buf;
+  const __nv_bfloat16 *x;
+  const int *topk_idx;
+  const float *topk_w;
+  int num_tokens;
+  unsigned epoch;
+  rocshmem_team_t team;
+};
+
+__device__ __forceinline__ float group8_max(float v) {
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 1));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 2));
+  v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, 4));
+  return v;
+}
+
+__device__ __forceinline__ unsigned pack_fp8x4(float a, float b, float c, float d) {
+  unsigned lo = __nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+  unsigned hi = __nv_cvt_float2_to_fp8x2(make_float2(c, d), __NV_SATFINITE, __NV_E4M3);
+  return lo | (hi << 16);
+}
+
+// Quantises the 16 bf16 values held by a lane (two int4) with the scale of its 8-lane group.
+__device__ __forceinline__ int4 quantize16(const int4 &a, const int4 &b, float *scale_out) {
+  const __nv_bfloat162 *pa = reinterpret_cast<const __nv_bfloat162 *>(&a);
+  const __nv_bfloat162 *pb = reinterpret_cast<const __nv_bfloat162 *>(&b);
+  float v[16];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float2 fa = __bfloat1622float2(pa[i]), fb = __bfloat1622float2(pb[i]);
+    v[2 * i] = fa.x; v[2 * i + 1] = fa.y;
+    v[8 + 2 * i] = fb.x; v[8 + 2 * i + 1] = fb.y;
+  }
+  float amax = 0.f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = group8_max(amax);
+  // e4m3 represents magnitudes up to 448. An all-zero block keeps scale 1 so that 0 * scale == 0.
+  const float scale = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+  const float inv = amax > 0.f ? 448.0f / amax : 1.0f;
+  *scale_out = scale;
+  int4 q;
+  q.x = pack_fp8x4(v[0] * inv, v[1] * inv, v[2] * inv, v[3] * inv);
+  q.y = pack_fp8x4(v[4] * inv, v[5] * inv, v[6] * inv, v[7] * inv);
+  q.z = pack_fp8x4(v[8] * inv, v[9] * inv, v[10] * inv, v[11] * inv);
+  q.w = pack_fp8x4(v[12] * inv, v[13] * inv, v[14] * inv, v[15] * inv);
+  return q;
+}
+
+__global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs a) {
+  extern __shared__ int s_rank_in_block[];  // [tokens_per_block][P]
+  __shared__ int s_rank_cnt[ROCSHMEM_MAX_PES];
+  __shared__ int s_blk_base[ROCSHMEM_MAX_PES];
+  __shared__ int s_total[ROCSHMEM_MAX_PES];
+  __shared__ int s_base[ROCSHMEM_MAX_PES];
+  __shared__ int s_exp_cnt[1024];
+  __shared__ float s_scales[kEpThreads / 32][EP_MAX_HIDDEN / 128];
+  __shared__ int s_ok;
+
+  const rocshmem_team_dev *t = detail::team_of(a.team);
+  if (t->my_pe < 0) return;
+  const int P = t->size, me = t->my_pe;
+  const int E = a.cfg.num_experts, epr = E / P, K = a.cfg.top_k, H = a.cfg.hidden;
+  const int T = a.num_tokens;
+  const unsigned tid = threadIdx.x, nthr = blockDim.x, b = blockIdx.x, B = gridDim.x;
+  const unsigned epoch = a.epoch;
+  const int parity = epoch & 1;
+
+  const __nv_bfloat16 *x = rebase(a.x);
+  const int *topk_idx = rebase(a.topk_idx);
+  const float *topk_w = rebase(a.topk_w);
+  char *recv_x = static_cast<char *>(rebase(a.buf.recv_x));
+  float *recv_scales = rebase(a.buf.recv_scales);
+  int *recv_meta = rebase(a.buf.recv_meta);
+  unsigned long long *cnt_in = rebase(a.buf.cnt_in);
+  unsigned long long *exp_in = rebase(a.buf.exp_in);
+  int *sent_slot = rebase(a.buf.sent_slot);
+  unsigned long long *tok_mask = rebase(a.buf.tok_mask);
+  int *blk_cnt = rebase(a.buf.blk_cnt);
+  int *exp_cnt = rebase(a.buf.exp_cnt);
+  unsigned long long *grid_counter = rebase(a.buf.grid_counter);
+  int *recv_info = rebase(a.buf.recv_info);
+
+  const int tpb = (a.cfg.max_tokens + B - 1) / B;  // tokens per block, fixed for the buffer's life
+  const int t0 = min(T, int(b) * tpb), t1 = min(T, t0 + tpb);
+
+  // ---- A: routing scan ------------------------------------------------------------------------------
+  for (unsigned i = tid; i < ROCSHMEM_MAX_PES; i += nthr) s_rank_cnt[i] = 0;
+  for (unsigned i = tid; i < unsigned(E); i += nthr) s_exp_cnt[i] = 0;
+  if (tid == 0) s_ok = 1;
+  __syncthreads();
+  for (int tok = t0 + tid; tok < t1; tok += nthr) {
+    unsigned long long mask = 0;
+    for (int k = 0; k < K; ++k) {
+      const int e = topk_idx[size_t(tok) * K + k];
+      if (e >= 0 && e < E) {
+        mask |= 1ull << (e / epr);
+        atomicAdd(&s_exp_cnt[e], 1);
+      }
+    }
+    tok_mask[tok] = mask;
+    for (unsigned long long m = mask; m; m &= m - 1) atomicAdd(&s_rank_cnt[__ffsll(static_cast<long long>(m)) - 1], 1);
+  }
+  __syncthreads();
+  for (unsigned d = tid; d < unsigned(P); d += nthr) blk_cnt[b * P + d] = s_rank_cnt[d];
+  for (unsigned e = tid; e < unsigned(E); e += nthr) {
+    if (s_exp_cnt[e]) atomicAdd(&exp_cnt[parity * E + e], s_exp_cnt[e]);
+  }
+  if (!grid_barrier(grid_counter, epoch, B)) return;
+
+  // ---- B: offsets and count exchange -------------------------------------------------------------------
+  for (unsigned d = tid; d < unsigned(P); d += nthr) {
+    int before = 0, total = 0;
+    for (unsigned bb = 0; bb < B; ++bb) {
+      const int c = blk_cnt[bb * P + d];
+      if (bb < b) before += c;
+      total += c;
+    }
+    s_blk_base[d] = before;
+    s_total[d] = total;
+  }
+  // Position of every token of the block among the block's tokens that go to the same rank.
+  for (unsigned d = tid; d < unsigned(P); d += nthr) {
+    int running = 0;
+    for (int tok = t0; tok < t1; ++tok) {
+      s_rank_in_block[(tok - t0) * P + d] = running;
+      running += static_cast<int>((tok_mask[tok] >> d) & 1ull);
+    }
+  }
+  __syncthreads();
+  if (b == 0) {
+    // Row `me` of the count matrix goes to everybody; expert counts go to the expert's owner.
+    for (unsigned i = tid; i < unsigned(P * P); i += nthr) {
+      const int j = i / P, d = i % P;
+      detail::st_relaxed_sys(remote_ptr(cnt_in + me * P + d, team_pe_to_world(t, j)), pack(epoch, s_total[d]));
+    }
+    for (unsigned e = tid; e < unsigned(E); e += nthr) {
+      const int owner = e / epr;
+      detail::st_relaxed_sys(remote_ptr(exp_in + me * epr + (e % epr), team_pe_to_world(t, owner)),
+                             pack(epoch, static_cast<unsigned>(exp_cnt[parity * E + e])));
+      exp_cnt[(parity ^ 1) * E + e] = 0;  // cleared for the next call
+    }
+  }
+  if (a.cfg.layout == EP_LAYOUT_SLOTTED) {
+    for (unsigned d = tid; d < unsigned(P); d += nthr) s_base[d] = me * a.cfg.max_tokens;
+  } else {
+    // base[d] = rows that ranks before me send to d. Needs rows 0 .. me-1 of the matrix.
+    bool ok = true;
+    for (unsigned d = tid; d < unsigned(P); d += nthr) {
+      int base = 0;
+      for (int s = 0; s < me; ++s) base += static_cast<int>(wait_packed(cnt_in + s * P + d, epoch, s, &ok));
+      s_base[d] = base;
+    }
+    if (!ok) atomicExch(&s_ok, 0);
+  }
+  __syncthreads();
+  if (!s_ok) return;
+
+  // ---- C: quantise and send, one warp per token ----------------------------------------------------------
+  const unsigned warp = tid / 32, lane = tid % 32, nwarps = nthr / 32;
+  const int iters = H / 512;
+  const int nscale = H / 128;
+  for (int tok = t0 + warp; tok < t1; tok += nwarps) {
+    const unsigned long long mask = tok_mask[tok];
+    if (lane < unsigned(P)) sent_slot[size_t(tok) * P + lane] = -1;
+    if (mask == 0) continue;
+    int4 q[kMaxIters];
+    const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
+    if (a.cfg.quantize) {
+#pragma unroll
+      for (int i = 0; i < kMaxIters; ++i) {
+        if (i < iters) {
+          // 512 elements per iteration: lane l holds elements [i*512 + l*16, +16) = two int4
+          const int4 lo = row[(i * 512 + lane * 16) / 8];
+          const int4 hi = row[(i * 512 + lane * 16) / 8 + 1];
+          float scale;
+          q[i] = quantize16(lo, hi, &scale);
+          if ((lane & 7) == 0) s_scales[warp][i * 4 + lane / 8] = scale;
+        }
+      }
+      __syncwarp();
+    }
+    int k_idx = -1;
+    float k_w = 0.f;
+    if (lane < unsigned(K)) {
+      k_idx = topk_idx[size_t(tok) * K + lane];
+      k_w = topk_w[size_t(tok) * K + lane];
+    }
+    for (int dd = 0; dd < P; ++dd) {
+      const int d = (me + dd) % P;  // rotate so the ranks do not all start on the same destination
+      if (!((mask >> d) & 1ull)) continue;
+      const int slot = s_base[d] + s_blk_base[d] + s_rank_in_block[(tok - t0) * P + d];
+      const int w = team_pe_to_world(t, d);
+      if (a.cfg.quantize) {
+        int4 *dst = reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H, w));
+#pragma unroll
+        for (int i = 0; i < kMaxIters; ++i) {
+          if (i < iters) dst[i * 32 + lane] = q[i];
+        }
+        if (lane < unsigned(nscale / 4)) {
+          float4 sc = reinterpret_cast<const float4 *>(s_scales[warp])[lane];
+          reinterpret_cast<float4 *>(remote_ptr(recv_scales + size_t(slot) * nscale, w))[lane] = sc;
+        }
+      } else {
+        int4 *dst = reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H * 2, w));
+        const int nvec = H / 8;
+        for (int v = lane; v < nvec; v += 32) dst[v] = row[v];
+      }
+      int *meta = remote_ptr(recv_meta + size_t(slot) * EP_META_WORDS, w);
+      if (lane < unsigned(K)) {
+        meta[EP_META_IDX + lane] = (k_idx >= 0 && k_idx / epr == d) ? k_idx % epr : -1;
+        meta[EP_META_WEIGHT + lane] = __float_as_int(k_w);
+      } else if (lane == 16) {
+        meta[EP_META_SRC_TOKEN] = tok;
+      } else if (lane == 17) {
+        meta[EP_META_SRC_RANK] = me;
+      }
+      if (lane == 0) sent_slot[size_t(tok) * P + d] = slot;
+    }
+    __syncwarp();
+  }
+
+  // ---- D: completion ------------------------------------------------------------------------------------------
+  bool ok = block_pair_barrier(t, b);
+  if (b == 0 && ok) {
+    // Receive-side bookkeeping: rows per source, first row per source, rows per local expert.
+    for (unsigned s = tid; s < unsigned(P); s += nthr) {
+      bool good = true;
+      int start = 0, mine = 0;
+      for (int s2 = 0; s2 <= int(s); ++s2) {
+        const int c = static_cast<int>(wait_packed(cnt_in + s2 * P + me, epoch, s2, &good));
+        if (s2 < int(s)) start += c; else mine = c;
+      }
+      recv_info[1 + s] = a.cfg.layout == EP_LAYOUT_SLOTTED ? int(s) * a.cfg.max_tokens : start;
+      recv_info[1 + P + s] = mine;
+      if (s == unsigned(P - 1)) recv_info[0] = start + mine;
+    }
+    for (unsigned e = tid; e < unsigned(epr); e += nthr) {
+      bool good = true;
+      int sum = 0;
+      for (int s = 0; s < P; ++s) sum += static_cast<int>(wait_packed(exp_in + s * epr + e, epoch, s, &good));
+      recv_info[1 + 2 * P + e] = sum;
+    }
+  }
+}
+
+struct CombineArgs {
+  EpConfig cfg;
+  EpBuffers buf;
+  const __nv_bfloat16 *y;
+  __nv_bfloat16 *out;
+  const int *topk_idx;
+  const float *topk_w;
+  int num_tokens;
+  int weighted;
+  rocshmem_team_t team;
+};
+
+__global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(CombineArgs a) {
+  const rocshmem_team_dev *t = detail::team_of(a.team);
+  if (t->my_pe < 0) return;
+  const int P = t->size;
+  const int E = a.cfg.num_experts, epr = E / P, K = a.cfg.top_k, H = a.cfg.hidden;
+  const __nv_bfloat16 *y = rebase(a.y);
+  __nv_bfloat16 *out = rebase(a.out);
+  const int *sent_slot = rebase(a.buf.sent_slot);
+  const int *topk_idx = rebase(a.topk_idx);
+  const float *topk_w = rebase(a.topk_w);
+
+  // Every member's result rows are complete (its producers ran before this kernel on its stream).
+  if (!block_pair_barrier(t, blockIdx.x)) return;
+
+  const unsigned lane = threadIdx.x % 32;
+  const unsigned gwarp = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
+  const unsigned nwarps = gridDim.x * (blockDim.x / 32);
+  const int nvec = H / 8;  // int4 vectors of 8 bf16 per row
+  for (int tok = gwarp; tok < a.num_tokens; tok += nwarps) {
+    // Lane d owns destination rank d: its row index there and the gate weight of that rank.
+    int my_slot = -1;
+    float my_w = 1.f;
+    if (lane < unsigned(P)) {
+      my_slot = sent_slot[size_t(tok) * P + lane];
+      if (a.weighted) {
+        my_w = 0.f;
+        for (int k = 0; k < K; ++k) {
+          const int e = topk_idx[size_t(tok) * K + k];
+          if (e >= 0 && e / epr == int(lane)) my_w += topk_w[size_t(tok) * K + k];
+        }
+      }
+    }
+    const unsigned active = __ballot_sync(0xffffffffu, my_slot >= 0);
+    const __nv_bfloat16 *src[EP_MAX_TOPK];
+    float wgt[EP_MAX_TOPK];
+    int n_src = 0;
+    for (unsigned m = active; m && n_src < EP_MAX_TOPK; m &= m - 1) {
+      const int d = __ffs(m) - 1;
+      const int slot = __shfl_sync(0xffffffffu, my_slot, d);
+      wgt[n_src] = __shfl_sync(0xffffffffu, my_w, d);
+      src[n_src] = remote_ptr(y + size_t(slot) * H, team_pe_to_world(t, d));
+      ++n_src;
+    }
+    int4 *dst = reinterpret_cast<int4 *>(out + size_t(tok) * H);
+    for (int v = lane; v < nvec; v += 32) {
+      int4 raw[EP_MAX_TOPK];
+#pragma unroll
+      for (int s = 0; s < EP_MAX_TOPK; ++s) {
+        if (s < n_src) raw[s] = reinterpret_cast<const int4 *>(src[s])[v];
+      }
+      float acc[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+      for (int s = 0; s < EP_MAX_TOPK; ++s) {
+        if (s < n_src) {
+          const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[s]);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(p2[i]);
+            acc[2 * i] = fmaf(f.x, wgt[s], acc[2 * i]);
+            acc[2 * i + 1] = fmaf(f.y, wgt[s], acc[2 * i + 1]);
+          }
+        }
+      }
+      int4 o;
+      __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+      dst[v] = o;
+    }
+  }
+  // Nobody reuses its result rows while a peer may still be reading them.
+  block_pair_barrier(t, blockIdx.x);
+}
+
+// ---- stand-alone block-scaled fp8 helpers ----------------------------------------------------------------------
+
+__global__ void __launch_bounds__(256) fp8_quantize_kernel(const __nv_bfloat16 *x, unsigned char *q, float *scales,
+                                                           size_t rows, int hidden) {
+  const unsigned lane = threadIdx.x % 32;
+  const size_t gwarp = size_t(blockIdx.x) * (blockDim.x / 32) + threadIdx.x / 32;
+  const size_t nwarps = size_t(gridDim.x) * (blockDim.x / 32);
+  const int iters = hidden / 512, nscale = hidden / 128;
+  for (size_t r = gwarp; r < rows; r += nwarps) {
+    const int4 *row = reinterpret_cast<const int4 *>(x + r * hidden);
+    int4 *dst = reinterpret_cast<int4 *>(q + r * hidden);
+    for (int i = 0; i < iters; ++i) {
+      const int4 lo = row[(i * 512 + lane * 16) / 8], hi = row[(i * 512 + lane * 16) / 8 + 1];
+      float scale;
+      dst[i * 32 + lane] = quantize16(lo, hi, &scale);
+      if ((lane & 7) == 0) scales[r * nscale + i * 4 + lane / 8] = scale;
+    }
+  }
+}
+
+__global__ void __launch_bounds__(256) fp8_dequantize_kernel(const unsigned char *q, const float *scales,
+                                                             __nv_bfloat16 *x, size_t rows, int hidden) {
+  const size_t total = rows * size_t(hidden) / 16;  // 16 fp8 values per thread step
+  const int nscale = hidden / 128;
+  for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+    const size_t elem = i * 16, r = elem / hidden, c = elem % hidden;
+    const float scale = scales[r * nscale + c / 128];
+    const int4 raw = reinterpret_cast<const int4 *>(q)[i];
+    const unsigned short *p = reinterpret_cast<const unsigned short *>(&raw);
+    int4 o[2];
+    __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(o);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p[k], __NV_E4M3);
+      const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&h));
+      o2[k] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+    }
+    reinterpret_cast<int4 *>(x)[2 * i] = o[0];
+    reinterpret_cast<int4 *>(x)[2 * i + 1] = o[1];
+  }
+}
+
+// ---- rows grouped by local expert ---------------------------------------------------------------------------------
+
+__global__ void ep_expert_offsets_kernel(const int *recv_info_a, int n_ranks, int experts_per_rank, int *offsets_a,
+                                         int *cursor_a) {
+  const int *recv_info = rebase(recv_info_a);
+  int *offsets = rebase(offsets_a), *cursor = rebase(cursor_a);
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    int run = 0;
+    for (int e = 0; e < experts_per_rank; ++e) {
+      offsets[e] = run;
+      cursor[e] = 0;
+      run += recv_info[1 + 2 * n_ranks + e];
+    }
+    offsets[experts_per_rank] = run;
+  }
+}
+
+__global__ void ep_expert_layout_kernel(const int *recv_meta_a, const int *recv_info_a, int n_ranks, int top_k,
+                                        const int *offsets_a, int *row_index_a, int *pair_k_a, int *cursor_a) {
+  const int *recv_meta = rebase(recv_meta_a), *recv_info = rebase(recv_info_a), *offsets = rebase(offsets_a);
+  int *row_index = rebase(row_index_a), *pair_k = rebase(pair_k_a), *cursor = rebase(cursor_a);
+  for (int s = 0; s < n_ranks; ++s) {
+    const int start = recv_info[1 + s], count = recv_info[1 + n_ranks + s];
+    for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count * top_k; i += gridDim.x * blockDim.x) {
+      const int row = start + i / top_k, k = i % top_k;
+      const int e = recv_meta[size_t(row) * EP_META_WORDS + EP_META_IDX + k];
+      if (e >= 0) {
+        const int pos = offsets[e] + atomicAdd(&cursor[e], 1);
+        row_index[pos] = row;
+        pair_k[pos] = k;
+      }
+    }
+  }
+}
+
+int validate(const EpConfig &cfg, int team_size, int num_tokens) {
+  if (team_size < 1 || team_size > ROCSHMEM_MAX_PES) return cudaErrorInvalidValue;
+  if (cfg.num_experts < team_size || cfg.num_experts % team_size || cfg.num_experts > 1024) return cudaErrorInvalidValue;
+  if (cfg.top_k < 1 || cfg.top_k > EP_MAX_TOPK) return cudaErrorInvalidValue;
+  if (cfg.hidden < 512 || cfg.hidden % 512 || cfg.hidden > EP_MAX_HIDDEN) return cudaErrorInvalidValue;
+  if (num_tokens < 0 || num_tokens > cfg.max_tokens) return cudaErrorInvalidValue;
+  if (cfg.blocks < 1) return cudaErrorInvalidValue;
+  return 0;
+}
+
+}  // namespace
+
+int ep_default_blocks() {
+  Runtime &rt = Runtime::instance();
+  // One block per SM (the kernels are written for one resident block of 512 threads per SM), shared
+  // between the PEs of the process when it hosts several.
+  int per_pe = device_sm_count() / std::max(1, rt.n_local());
+  return std::max(1, per_pe);
+}
+
+int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *x,
+                const int *topk_idx, const float *topk_w, int num_tokens, unsigned epoch, void *stream) {
+  Runtime &rt = Runtime::instance();
+  HostTeam *ht = rt.team_from_handle(team);
+  if (!ht) return cudaErrorInvalidValue;
+  if (int rc = validate(cfg, ht->world.size, num_tokens)) return rc;
+  DispatchArgs a{cfg, buf, static_cast<const __nv_bfloat16 *>(x), topk_idx, topk_w, num_tokens, epoch, team};
+  const int tpb = (cfg.max_tokens + cfg.blocks - 1) / cfg.blocks;
+  const size_t smem = size_t(tpb) * ht->world.size * sizeof(int);
+  if (smem > 40 * 1024) return cudaErrorInvalidValue;  // use more blocks for this many tokens
+  return launch_pes(ep_dispatch_kernel, cfg.blocks, kEpThreads, smem, static_cast<cudaStream_t>(stream), true, a);
+}
+
+int ep_combine(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *y, void *out,
+               const int *topk_idx, const float *topk_w, int num_tokens, int weighted, void *stream) {
+  Runtime &rt = Runtime::instance();
+  HostTeam *ht = rt.team_from_handle(team);
+  if (!ht) return cudaErrorInvalidValue;
+  if (int rc = validate(cfg, ht->world.size, num_tokens)) return rc;
+  CombineArgs a{cfg, buf, static_cast<const __nv_bfloat16 *>(y), static_cast<__nv_bfloat16 *>(out), topk_idx,
+                topk_w, num_tokens, weighted, team};
+  return launch_pes(ep_combine_kernel, cfg.blocks, kEpThreads, 0, static_cast<cudaStream_t>(stream), false, a);
+}
+
+int fp8_quantize_1x128(const void *x, void *q, float *scales, size_t rows, int hidden, void *stream) {
+  if (hidden % 512 || hidden <= 0) return cudaErrorInvalidValue;
+  if (rows == 0) return 0;
+  unsigned blocks = static_cast<unsigned>(std::min<size_t>((rows + 7) / 8, size_t(device_sm_count()) * 8));
+  fp8_quantize_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16 *>(x), static_cast<unsigned char *>(q), scales, rows, hidden);
+  return cudaGetLastError();
+}
+
+int fp8_dequantize_1x128(const void *q, const float *scales, void *x, size_t rows, int hidden, void *stream) {
+  if (hidden % 128 || hidden <= 0) return cudaErrorInvalidValue;
+  if (rows == 0) return 0;
+  size_t steps = rows * size_t(hidden) / 16;
+  unsigned blocks = static_cast<unsigned>(std::min<size_t>((steps + 255) / 256, size_t(device_sm_count()) * 8));
+  fp8_dequantize_kernel<<<blocks, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const unsigned char *>(q), scales, static_cast<__nv_bfloat16 *>(x), rows, hidden);
+  return cudaGetLastError();
+}
+
+int ep_expert_layout(const int *recv_meta, const int *recv_info, int n_ranks, int max_tokens, int layout,
+                     int experts_per_rank, int top_k, int *offsets, int *row_index, int *pair_k,
+                     int *cursor_scratch, void *stream_v) {
+  (void)max_tokens;
+  (void)layout;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (int rc = launch_pes(ep_expert_offsets_kernel, 1, 32, 0, stream, false, recv_info, n_ranks, experts_per_rank,
+                          offsets, cursor_scratch)) {
+    return rc;
+  }
+  Runtime &rt = Runtime::instance();
+  unsigned blocks = static_cast<unsigned>(std::max(1, device_sm_count() / std::max(1, rt.n_local())));
+  return launch_pes(ep_expert_layout_kernel, blocks, 256, 0, stream, false, recv_meta, recv_info, n_ranks, top_k,
+                    static_cast<const int *>(offsets), row_index, pair_k, cursor_scratch);
+}
+
+}  // namespace kernels
+}  // namespace rocshmem

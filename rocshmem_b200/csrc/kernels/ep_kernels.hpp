@@ -1,0 +1,84 @@
+// Expert-parallel MoE dispatch / combine on the symmetric heap, and the block-scaled fp8 helpers.
+// Host-callable launchers; pointers to symmetric memory are addresses on the process's first local PE.
+//
+// No counterpart exists in the reference (its nearest primitive is the fixed-size alltoall,
+// src/ipc/context_ipc_tmpl_device.hpp:474-501); the operations are built from the same ingredients
+// the reference exposes - peer stores, signals, bounded waits, teams - fused into two kernels.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include "rocshmem/rocshmem_common.h"
+
+namespace rocshmem {
+namespace kernels {
+
+constexpr int EP_META_WORDS = 32;      // 128-byte metadata record per received row
+constexpr int EP_META_IDX = 0;         // [0, top_k): expert index local to the receiver, -1 if elsewhere
+constexpr int EP_META_WEIGHT = 8;      // [8, 8 + top_k): gate weights (float bits)
+constexpr int EP_META_SRC_TOKEN = 16;  // token index on the source rank
+constexpr int EP_META_SRC_RANK = 17;   // source rank (team numbering)
+constexpr int EP_MAX_TOPK = 8;
+constexpr int EP_MAX_HIDDEN = 8192;
+
+enum EpLayout : int {
+  EP_LAYOUT_COMPACT = 0,  // rows of source s start at the sum of the counts of sources < s
+  EP_LAYOUT_SLOTTED = 1,  // rows of source s start at s * max_tokens: no count round-trip before
+                          // sending (low-latency mode), at the price of gaps in the receive buffer
+};
+
+struct EpConfig {
+  int num_experts;     // global, divisible by the team size
+  int top_k;           // <= 8
+  int hidden;          // multiple of 128, <= 8192
+  int max_tokens;      // per rank and call
+  int quantize;        // 1: dispatch carries e4m3 rows + one fp32 scale per 128 elements; 0: bf16 rows
+  int layout;          // EpLayout
+  int blocks;          // blocks per PE (the same on every member)
+};
+
+// Symmetric buffers of one dispatcher (all allocated by the caller on the symmetric heap).
+struct EpBuffers {
+  void *recv_x;             // [P * max_tokens, hidden] uint8 (quantize) or bf16
+  float *recv_scales;       // [P * max_tokens, hidden / 128]
+  int *recv_meta;           // [P * max_tokens, EP_META_WORDS]
+  unsigned long long *cnt_in;   // [P][P] packed (epoch << 32 | tokens source s sends to rank d), full matrix
+  unsigned long long *exp_in;   // [P][experts_per_rank] packed (epoch << 32 | rows for local expert e from s)
+  // local scratch (symmetric allocation for simplicity, only ever accessed by its owner)
+  int *sent_slot;           // [max_tokens][P] row index at destination d, -1 if not sent
+  unsigned long long *tok_mask;  // [max_tokens] bit d set: token goes to rank d
+  int *blk_cnt;             // [blocks][P]
+  int *exp_cnt;             // [2][num_experts] double-buffered by call parity
+  unsigned long long *grid_counter;  // [1]
+  // outputs, local
+  int *recv_info;           // [0] total rows, [1 + s] first row of source s (P + 1 entries), then
+                            // [2 + P + e] rows whose top-k contains local expert e
+};
+
+// x [T, hidden] bf16, topk_idx [T, top_k] int32 (global expert ids, -1 = unused), topk_w [T, top_k] fp32.
+// `epoch` must increase by one per dispatch call on these buffers (the same value on every member).
+int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *x,
+                const int *topk_idx, const float *topk_w, int num_tokens, unsigned epoch, void *stream);
+
+// y: symmetric [P * max_tokens, hidden] bf16 in the row layout produced by dispatch. out [T, hidden]
+// bf16 (local). Every token receives the sum over the ranks it was sent to of that rank's row,
+// scaled (weighted != 0) by the sum of the token's gate weights of the experts living on that rank.
+int ep_combine(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *y, void *out,
+               const int *topk_idx, const float *topk_w, int num_tokens, int weighted, void *stream);
+
+// Stand-alone 1x128 block-scaled e4m3 quantisation of [rows, hidden] bf16 and its inverse.
+int fp8_quantize_1x128(const void *x_bf16, void *q_u8, float *scales, size_t rows, int hidden, void *stream);
+int fp8_dequantize_1x128(const void *q_u8, const float *scales, void *x_bf16, size_t rows, int hidden, void *stream);
+
+// Groups received rows by local expert for a grouped GEMM: for every local expert e, the indices of
+// the rows whose top-k contains e, written contiguously; offsets[e] .. offsets[e + 1]. `pair_k`
+// receives the top-k position inside the row's metadata. Returns through `offsets` (E_local + 1).
+int ep_expert_layout(const int *recv_meta, const int *recv_info, int n_ranks, int max_tokens, int layout,
+                     int experts_per_rank, int top_k, int *offsets, int *row_index, int *pair_k,
+                     int *cursor_scratch, void *stream);
+
+int ep_default_blocks();
+
+}  // namespace kernels
+}  // namespace rocshmem

@@ -104,9 +104,12 @@ def init(store=None, rank: Optional[int] = None, world_size: Optional[int] = Non
             if dist.is_available() and dist.is_initialized():
                 store = dist.distributed_c10d._get_default_store()
             else:
+                # Under torchrun the agent already serves a store on MASTER_PORT; workers only connect.
+                agent_store = os.environ.get("TORCHELASTIC_USE_AGENT_STORE", "") == "True"
                 store = dist.TCPStore(os.environ.get("MASTER_ADDR", "127.0.0.1"),
                                       int(os.environ.get("MASTER_PORT", "29500")), world_size,
-                                      rank == 0, timeout=datetime.timedelta(seconds=timeout_s))
+                                      rank == 0 and not agent_store,
+                                      timeout=datetime.timedelta(seconds=timeout_s))
         _init_count += 1
         prefix = f"rocshmem_b200/{_init_count}/"
         wait = datetime.timedelta(milliseconds=timeout_ms)

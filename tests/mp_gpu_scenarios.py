@@ -1,0 +1,165 @@
+"""Multi-process GPU scenarios: one PE per process and per GPU, device API from user kernels and
+the library's stream-ordered collectives over real NVLink peer mappings."""
+import os
+
+import torch
+
+import rocshmem_b200 as shm
+from rocshmem_b200 import _native
+from rocshmem_b200.ops import collectives as coll
+
+RANK = int(os.environ["RANK"])
+WORLD = int(os.environ["WORLD_SIZE"])
+
+
+def _init(heap="512M", **kw):
+    shm.init(heap_size=heap, backend="cuda", ROCSHMEM_WAIT_TIMEOUT_MS=5000, **kw)
+    assert shm.is_cuda() and shm.n_pes() == WORLD and shm.my_pe() == RANK
+    return _native.load_test_kernels()
+
+
+def _stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _ok():
+    torch.cuda.synchronize()
+    err = shm.get_error()
+    assert err["count"] == 0, err
+
+
+def gpu_device_suite():
+    k = _init()
+    me, n = RANK, WORLD
+    dev = shm.device()
+    # put / get, all scopes
+    for op in range(4):
+        for scope in range(3):
+            nbytes = 1 << 20
+            src = shm.zeros(nbytes, torch.uint8)
+            dst = shm.zeros(nbytes, torch.uint8)
+            g = torch.Generator().manual_seed(100 + me)
+            src.copy_(torch.randint(0, 256, (nbytes,), generator=g, dtype=torch.uint8).to(dev))
+            torch.cuda.synchronize()
+            shm.barrier_all()
+            k.rma(op, scope, dst.data_ptr(), src.data_ptr(), nbytes, 1, 1, 256 if scope else 64, _stream())
+            _ok()
+            origin = (me - 1) % n if op < 2 else (me + 1) % n
+            g = torch.Generator().manual_seed(100 + origin)
+            assert torch.equal(dst.cpu(), torch.randint(0, 256, (nbytes,), generator=g, dtype=torch.uint8)), (op, scope)
+            shm.free(dst)
+            shm.free(src)
+    # atomics from every PE onto PE 0
+    target = shm.zeros(1, torch.int64)
+    ret = shm.zeros(128, torch.int64)
+    k.amo(0, target.data_ptr(), ret.data_ptr(), 10, 2, 64, _stream())
+    _ok()
+    shm.barrier_all()
+    if me == 0:
+        assert int(target.cpu()[0]) == 2 * n * 128 * 10
+    # signals, ping-pong, ping-all, barrier stress
+    nbytes = 8192
+    src = shm.zeros(nbytes, torch.uint8)
+    dst = shm.zeros(nbytes, torch.uint8)
+    sig = shm.zeros(1, torch.int64)
+    fetched = shm.zeros(2, torch.int64)
+    src.fill_(ord("0") + me)
+    torch.cuda.synchronize()
+    shm.barrier_all()
+    k.signal(2, 0, dst.data_ptr(), src.data_ptr(), nbytes, sig.data_ptr(), 7, 7, fetched.data_ptr(), 64, _stream())
+    _ok()
+    assert fetched.cpu().tolist() == [7, 0] and torch.all(dst.cpu() == ord("0") + (me - 1) % n)
+    flag = shm.zeros(1, torch.int32)
+    ns = shm.zeros(1, torch.int64)
+    k.pingpong(flag.data_ptr(), 1000, ns.data_ptr(), _stream())
+    _ok()
+    if me == 0:
+        print(f"ping-pong round trip: {int(ns.cpu()[0]) / 1000:.0f} ns")
+    slots = shm.zeros(n, torch.int64)
+    result = shm.zeros(8, torch.int64)
+    k.pingall(slots.data_ptr(), result.data_ptr(), _stream())
+    _ok()
+    assert slots.cpu().tolist() == [p + 1 for p in range(n)]
+    errors = shm.zeros(1, torch.int32)
+    k.barrier_stress(slots.data_ptr(), 500, errors.data_ptr(), 64, _stream())
+    _ok()
+    assert int(errors.cpu()[0]) == 0
+    # block collectives from user kernels
+    x = shm.zeros(5000, torch.float32)
+    y = shm.zeros(5000, torch.float32)
+    rc = shm.zeros(1, torch.int32)
+    x.copy_((torch.arange(5000, dtype=torch.float32) * (me + 1)).to(dev))
+    torch.cuda.synchronize()
+    shm.barrier_all()
+    k.coll(3, "float32", shm.team_world().handle, y.data_ptr(), x.data_ptr(), 5000, 0, 3, rc.data_ptr(), 512, _stream())
+    _ok()
+    assert torch.allclose(y.cpu(), torch.arange(5000, dtype=torch.float32) * (n * (n + 1) // 2))
+    shm.barrier_all()
+    shm.finalize()
+
+
+def gpu_library_collectives():
+    _init("2G")
+    me, n = RANK, WORLD
+    dev = shm.device()
+    for dtype in (torch.float32, torch.bfloat16, torch.float16, torch.int32, torch.float64):
+        for nelem in (1, 1000, 65536 + 8, 3 << 20):
+            src = shm.zeros(nelem, dtype)
+            dst = shm.zeros(nelem, dtype)
+            g = torch.Generator().manual_seed(9 + me)
+            ins = []
+            for p in range(n):
+                gp = torch.Generator().manual_seed(9 + p)
+                if dtype.is_floating_point:
+                    ins.append(torch.randn(nelem, generator=gp, dtype=torch.float32).to(dtype))
+                else:
+                    ins.append(torch.randint(-1000, 1000, (nelem,), generator=gp, dtype=torch.int64).to(dtype))
+            src.copy_(ins[me].to(dev))
+            torch.cuda.synchronize()
+            shm.barrier_all()
+            ref = torch.stack([i.to(torch.float64) for i in ins]).sum(0)
+            algos = [shm.ALLREDUCE_ONE_SHOT, shm.ALLREDUCE_TWO_SHOT, shm.ALLREDUCE_AUTO]
+            if shm.nvls_available() and dtype in (torch.float32, torch.bfloat16, torch.float16) and nelem % 8 == 0:
+                algos.append(shm.ALLREDUCE_NVLS)
+            for algo in algos:
+                dst.zero_()
+                coll.allreduce_async(dst, src, shm.OP_SUM, algo=algo)
+                _ok()
+                tol = {torch.bfloat16: 3e-2, torch.float16: 5e-3}.get(dtype, 1e-5)
+                assert torch.allclose(dst.cpu().to(torch.float64), ref, rtol=tol, atol=tol * n), (dtype, nelem, algo)
+            coll.allreduce_async(dst, src, shm.OP_MAX, algo=shm.ALLREDUCE_TWO_SHOT)
+            _ok()
+            refmax = torch.stack([i.to(torch.float64) for i in ins]).max(0).values
+            assert torch.allclose(dst.cpu().to(torch.float64), refmax), (dtype, nelem, "max")
+            shm.barrier_all()
+            shm.free(dst)
+            shm.free(src)
+    nbytes = 5 << 20
+    src = shm.zeros(nbytes * n, torch.uint8)
+    dst = shm.zeros(nbytes * n, torch.uint8)
+    src.fill_(me + 1)
+    torch.cuda.synchronize()
+    shm.barrier_all()
+    coll.fcollect_async(dst, src[:nbytes])
+    _ok()
+    got = dst.cpu().view(n, nbytes)
+    assert all(torch.all(got[p] == p + 1) for p in range(n))
+    for p in range(n):
+        src.view(n, nbytes)[p].fill_(10 * me + p)
+    torch.cuda.synchronize()
+    coll.alltoall_async(dst, src)
+    _ok()
+    got = dst.cpu().view(n, nbytes)
+    assert all(torch.all(got[p] == 10 * p + me) for p in range(n))
+    dst.zero_()
+    torch.cuda.synchronize()
+    coll.broadcast_async(dst[:nbytes], src[:nbytes], n - 1)
+    _ok()
+    if me != n - 1:
+        assert torch.all(dst.cpu()[:nbytes] == 10 * (n - 1))
+    shm.barrier_all()
+    print(f"nvls={shm.nvls_available()}")
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives)}

@@ -1,0 +1,30 @@
+"""One PE per process and per GPU. Skipped unless at least two GPUs are visible."""
+import pytest
+import torch
+
+from mp_util import assert_all_ok, run_ranks
+
+pytestmark = pytest.mark.gpu
+
+
+def gpus():
+    return torch.cuda.device_count() if torch.cuda.is_available() else 0
+
+
+def world_sizes():
+    return [w for w in (2, 4, 8) if w <= gpus()] or [0]
+
+
+CUDA_ENV = {"ROCSHMEM_TEST_BACKEND": "cuda", "NCCL_NVLS_ENABLE": "0"}
+
+
+@pytest.mark.parametrize("world", world_sizes())
+@pytest.mark.parametrize("scenario", ["host_plumbing", "store_bootstrap", "teams", "collectives_host",
+                                      "wait_and_signal", "gpu_device_suite", "gpu_library_collectives"])
+def test_scenario(scenario, world):
+    if world == 0:
+        pytest.skip("needs at least two GPUs")
+    results = run_ranks(scenario, world, timeout=300, env_extra=CUDA_ENV)
+    assert_all_ok(results)
+    if scenario == "gpu_device_suite":
+        print(results[0][1][-300:])
