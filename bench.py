@@ -52,24 +52,42 @@ class ClockSampler:
     def __init__(self, device_index: int):
         self.device_index = device_index
         self.proc = None
+        self.lines = []
+        self.thread = None
 
     def start(self):
+        """Starts nvidia-smi and returns once its first sample has arrived (it needs a moment to
+        start, and a short timed region would otherwise end before the first line)."""
+        import threading
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "100",
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "50",
                  "-i", str(self.device_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             self.proc = None
+            return
+
+        def pump():
+            for line in self.proc.stdout:
+                self.lines.append(line)
+
+        self.thread = threading.Thread(target=pump, daemon=True)
+        self.thread.start()
+        deadline = time.time() + 5.0
+        while not self.lines and time.time() < deadline and self.proc.poll() is None:
+            time.sleep(0.01)
 
     def stop(self) -> dict:
         if self.proc is None:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-            out, _ = self.proc.communicate()
+        if self.thread is not None:
+            self.thread.join(timeout=2)
+        out = "".join(self.lines)
         sm, smax, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for line in out.splitlines():
@@ -161,15 +179,14 @@ def main() -> None:
     torch.cuda.synchronize()
     shm.barrier_all()
 
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
     for _ in range(args.warmup):
         flush.fill_(1)
         step()
     torch.cuda.synchronize()
     shm.barrier_all()
-
-    sampler = ClockSampler(local_rank)
-    if rank == 0:
-        sampler.start()
     ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
     launches_before = d.kernel_launches
     torch.cuda.synchronize()

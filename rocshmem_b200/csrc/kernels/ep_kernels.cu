@@ -127,7 +127,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   __shared__ int s_total[ROCSHMEM_MAX_PES];
   __shared__ int s_base[ROCSHMEM_MAX_PES];
   __shared__ int s_exp_cnt[1024];
-  __shared__ float s_scales[kEpThreads / 32][EP_MAX_HIDDEN / 128];
+  // Read back as float4 vectors, so the array needs 16-byte alignment (float alone guarantees 4).
+  __shared__ __align__(16) float s_scales[kEpThreads / 32][EP_MAX_HIDDEN / 128];
   __shared__ int s_ok;
 
   const rocshmem_team_dev *t = detail::team_of(a.team);
@@ -236,6 +237,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   for (int tok = t0 + warp; tok < t1; tok += nwarps) {
     const unsigned long long mask = tok_mask[tok];
     if (lane < unsigned(P)) sent_slot[size_t(tok) * P + lane] = -1;
+    __syncwarp();  // lane 0 overwrites some of these entries below
     if (mask == 0) continue;
     int4 q[kMaxIters];
     const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);

@@ -162,4 +162,55 @@ def gpu_library_collectives():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives)}
+def gpu_moe():
+    """Dispatch + combine across real GPUs: identity experts return the token, rank-constant rows
+    give exact sums, routing bookkeeping matches a CPU reference."""
+    from rocshmem_b200.ops import moe
+    _init("4G")
+    me, n = RANK, WORLD
+    dev = shm.device()
+    for layout, (T, H, E, K) in (("compact", (1000, 7168, 8 * n, 8 if n >= 2 else 4)), ("slotted", (128, 2048, 4 * n, 4))):
+        K = min(K, E)
+        d = moe.EpDispatcher(E, K, H, T, layout=layout)
+        epr = E // n
+        for rep in range(3):
+            g = torch.Generator().manual_seed(50 * rep + me)
+            x = torch.randn(T, H, generator=g).to(torch.bfloat16).to(dev)
+            routes = [moe.make_routing(T, E, K, 1000 * rep + p) for p in range(n)]
+            idx, w = routes[me][0].to(dev), routes[me][1].to(dev)
+            res = d.dispatch(x, idx, w)
+            _ok()
+            want_rows = moe.ref_dispatch([r[0] for r in routes], n, E)[me]
+            info = res.recv_info.cpu().tolist()
+            assert info[0] == len(want_rows), (info[0], len(want_rows))
+            meta = res.recv_meta.cpu()
+            pos = 0
+            for s in range(n):
+                first, count = info[1 + s], info[1 + n + s]
+                src = [t for ss, t in want_rows if ss == s]
+                assert count == len(src) and first == (s * T if layout == "slotted" else pos)
+                pos += count
+                assert meta[first:first + count, 16].tolist() == src
+                assert meta[first:first + count, 17].tolist() == [s] * count
+            y = d.result_buffer()
+            for s in range(n):
+                first, count = info[1 + s], info[1 + n + s]
+                if count:
+                    y[first:first + count].copy_(moe.fp8_dequantize_1x128(res.recv_x[first:first + count],
+                                                                          res.recv_scales[first:first + count]))
+            out = d.combine(y, idx, w, T, weighted=True)
+            _ok()
+            assert (out.float() - x.float()).abs().max().item() <= 0.08 * x.float().abs().max().item() + 2e-2
+            y.fill_(float(me + 1))
+            out = d.combine(y, idx, w, T, weighted=False)
+            _ok()
+            ranks = torch.where(routes[me][0] >= 0, routes[me][0] // epr, torch.full_like(routes[me][0], -1))
+            want = torch.zeros(T)
+            for r in range(n):
+                want += (ranks == r).any(dim=1).float() * (r + 1)
+            assert torch.equal(out[:, 0].float().cpu(), want) and torch.equal(out[:, -1].float().cpu(), want)
+            shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_moe)}

@@ -86,8 +86,8 @@ def test_dispatch_fp8_and_combine(shm, layout, T, H, E, K):
                 got = moe.ref_dequantize_1x128(qx[rows], sc[rows])
                 ref = moe.ref_dequantize_1x128(q_ref, s_ref)
                 # identical scales; allow one e4m3 rounding step of difference at ties
-                assert (got - ref).abs().max() <= 0.07 * xs[toks].float().abs().max()
-                assert (got - xs[toks].float()).abs().max() <= 0.07 * xs[toks].float().abs().max() + 1e-3
+                assert (got - ref).abs().max() <= 0.075 * xs[toks].float().abs().max()
+                assert (got - xs[toks].float()).abs().max() <= 0.075 * xs[toks].float().abs().max() + 1e-3
                 gi = is_[toks]
                 local = torch.where((gi >= 0) & (gi // epr == dst), gi % epr, torch.full_like(gi, -1))
                 assert torch.equal(meta[rows, 0:K], local)
@@ -176,8 +176,9 @@ def test_fp8_quantize_dequantize(shm, rows, hidden):
     assert torch.allclose(s.cpu(), s_ref, rtol=1e-6, atol=0)
     deq = moe.fp8_dequantize_1x128(q, s).float().cpu()
     ref = moe.ref_dequantize_1x128(q_ref, s_ref)
-    assert (deq - ref).abs().max() <= 0.07 * x.float().abs().max()
-    assert (deq - x.float()).abs().max() <= 0.07 * x.float().abs().max()
+    # one e4m3 step at the top of a block's range is amax * 32 / 448
+    assert (deq - ref).abs().max() <= 0.075 * x.float().abs().max()
+    assert (deq - x.float()).abs().max() <= 0.075 * x.float().abs().max()
     assert torch.all(deq[0, :128] == 0)
     # most elements must agree bit for bit with the reference rounding
     same = (q.cpu().view(torch.uint8) == q_ref.view(torch.uint8)).float().mean().item()

@@ -20,11 +20,11 @@ CUDA_ENV = {"ROCSHMEM_TEST_BACKEND": "cuda", "NCCL_NVLS_ENABLE": "0"}
 
 @pytest.mark.parametrize("world", world_sizes())
 @pytest.mark.parametrize("scenario", ["host_plumbing", "store_bootstrap", "teams", "collectives_host",
-                                      "wait_and_signal", "gpu_device_suite", "gpu_library_collectives"])
+                                      "wait_and_signal", "gpu_device_suite", "gpu_library_collectives", "gpu_moe"])
 def test_scenario(scenario, world):
     if world == 0:
         pytest.skip("needs at least two GPUs")
     results = run_ranks(scenario, world, timeout=300, env_extra=CUDA_ENV)
     assert_all_ok(results)
-    if scenario == "gpu_device_suite":
-        print(results[0][1][-300:])
+    if scenario in ("gpu_device_suite", "gpu_library_collectives"):
+        print(results[0][1][-400:])
