@@ -201,6 +201,7 @@ def main() -> None:
     torch.cuda.synchronize()
     shm.barrier_all()
     clocks = sampler.stop() if rank == 0 else None
+    phases = d.phase_times_us()
     launches = d.kernel_launches - launches_before
     disp_ms = sum(e[0].elapsed_time(e[1]) for e in ev)
     comb_ms = sum(e[1].elapsed_time(e[2]) for e in ev)
@@ -262,6 +263,7 @@ def main() -> None:
                       "dispatch_remote_gbs_per_rank": disp_bytes / (disp_us * 1e-6) / 1e9 if remote_rows else 0.0,
                       "combine_remote_gbs_per_rank": comb_bytes / (comb_us * 1e-6) / 1e9 if remote_rows else 0.0,
                       "remote_rows_rank0": remote_rows, "recv_rows_rank0": n_rows,
+                      "device_phase_us_last_step": phases,
                       "nvlink_roofline_frac_dispatch": (disp_bytes / 770e9) / (disp_us * 1e-6) if remote_rows else None,
                       "nvlink_roofline_frac_combine": (comb_bytes / 770e9) / (comb_us * 1e-6) if remote_rows else None},
         }

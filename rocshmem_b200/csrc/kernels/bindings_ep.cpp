@@ -46,6 +46,7 @@ void bind_ep(py::module_ &m) {
         h.buf.blk_cnt = P<int>(get("blk_cnt"));
         h.buf.exp_cnt = P<int>(get("exp_cnt"));
         h.buf.grid_counter = P<unsigned long long>(get("grid_counter"));
+        h.buf.phase_ns = P<unsigned long long>(get("phase_ns"));
         h.buf.recv_info = P<int>(get("recv_info"));
         return h;
       }))

@@ -34,6 +34,7 @@ namespace kernels {
 namespace {
 
 constexpr unsigned kEpThreads = 512;
+constexpr unsigned kCombineThreads = 384;  // 170 registers per thread: room for 16 loads in flight
 constexpr int kMaxIters = EP_MAX_HIDDEN / 512;  // 16 iterations of 512 elements per warp
 
 using detail::remote_ptr;
@@ -121,7 +122,7 @@ __device__ __forceinline__ int4 quantize16(const int4 &a, const int4 &b, float *
 }
 
 __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs a) {
-  extern __shared__ int s_rank_in_block[];  // [tokens_per_block][P]
+  extern __shared__ __align__(16) unsigned char s_dyn[];  // masks [tpb] u64, then ranks [tpb][P] int
   __shared__ int s_rank_cnt[ROCSHMEM_MAX_PES];
   __shared__ int s_blk_base[ROCSHMEM_MAX_PES];
   __shared__ int s_total[ROCSHMEM_MAX_PES];
@@ -157,6 +158,11 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
 
   const int tpb = (a.cfg.max_tokens + B - 1) / B;  // tokens per block, fixed for the buffer's life
   const int t0 = min(T, int(b) * tpb), t1 = min(T, t0 + tpb);
+  unsigned long long *s_mask = reinterpret_cast<unsigned long long *>(s_dyn);
+  int *s_rank_in_block = reinterpret_cast<int *>(s_dyn + size_t(tpb) * sizeof(unsigned long long));
+  unsigned long long *phase_ns = rebase(a.buf.phase_ns);
+  const bool stamp = (b == 0 && tid == 0);
+  if (stamp) phase_ns[0] = detail::now_ns();
 
   // ---- A: routing scan ------------------------------------------------------------------------------
   for (unsigned i = tid; i < ROCSHMEM_MAX_PES; i += nthr) s_rank_cnt[i] = 0;
@@ -173,6 +179,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
       }
     }
     tok_mask[tok] = mask;
+    s_mask[tok - t0] = mask;
     for (unsigned long long m = mask; m; m &= m - 1) atomicAdd(&s_rank_cnt[__ffsll(static_cast<long long>(m)) - 1], 1);
   }
   __syncthreads();
@@ -180,25 +187,29 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   for (unsigned e = tid; e < unsigned(E); e += nthr) {
     if (s_exp_cnt[e]) atomicAdd(&exp_cnt[parity * E + e], s_exp_cnt[e]);
   }
-  if (!grid_barrier(grid_counter, epoch, B)) return;
-
-  // ---- B: offsets and count exchange -------------------------------------------------------------------
-  for (unsigned d = tid; d < unsigned(P); d += nthr) {
-    int before = 0, total = 0;
-    for (unsigned bb = 0; bb < B; ++bb) {
-      const int c = blk_cnt[bb * P + d];
-      if (bb < b) before += c;
-      total += c;
-    }
-    s_blk_base[d] = before;
-    s_total[d] = total;
-  }
-  // Position of every token of the block among the block's tokens that go to the same rank.
+  // Position of every token of the block among the block's tokens that go to the same rank (does not
+  // depend on other blocks, so it is done before the grid barrier).
   for (unsigned d = tid; d < unsigned(P); d += nthr) {
     int running = 0;
-    for (int tok = t0; tok < t1; ++tok) {
-      s_rank_in_block[(tok - t0) * P + d] = running;
-      running += static_cast<int>((tok_mask[tok] >> d) & 1ull);
+    for (int i = 0; i < t1 - t0; ++i) {
+      s_rank_in_block[i * P + d] = running;
+      running += static_cast<int>((s_mask[i] >> d) & 1ull);
+    }
+    s_blk_base[d] = 0;
+    s_total[d] = 0;
+  }
+  if (stamp) phase_ns[1] = detail::now_ns();
+  if (!grid_barrier(grid_counter, epoch, B)) return;
+  if (stamp) phase_ns[2] = detail::now_ns();
+
+  // ---- B: offsets and count exchange -------------------------------------------------------------------
+  // All (block, rank) counts are read in one round of independent loads.
+  for (unsigned i = tid; i < B * unsigned(P); i += nthr) {
+    const int c = blk_cnt[i];
+    if (c) {
+      const unsigned bb = i / P, d = i % P;
+      atomicAdd(&s_total[d], c);
+      if (bb < b) atomicAdd(&s_blk_base[d], c);
     }
   }
   __syncthreads();
@@ -229,49 +240,70 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   }
   __syncthreads();
   if (!s_ok) return;
+  if (stamp) phase_ns[3] = detail::now_ns();
 
   // ---- C: quantise and send, one warp per token ----------------------------------------------------------
   const unsigned warp = tid / 32, lane = tid % 32, nwarps = nthr / 32;
   const int iters = H / 512;
   const int nscale = H / 128;
+  constexpr int kBatch = 8;  // iterations (of 512 elements) whose loads are issued together
   for (int tok = t0 + warp; tok < t1; tok += nwarps) {
-    const unsigned long long mask = tok_mask[tok];
-    if (lane < unsigned(P)) sent_slot[size_t(tok) * P + lane] = -1;
-    __syncwarp();  // lane 0 overwrites some of these entries below
-    if (mask == 0) continue;
-    int4 q[kMaxIters];
-    const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
-    if (a.cfg.quantize) {
-#pragma unroll
-      for (int i = 0; i < kMaxIters; ++i) {
-        if (i < iters) {
-          // 512 elements per iteration: lane l holds elements [i*512 + l*16, +16) = two int4
-          const int4 lo = row[(i * 512 + lane * 16) / 8];
-          const int4 hi = row[(i * 512 + lane * 16) / 8 + 1];
-          float scale;
-          q[i] = quantize16(lo, hi, &scale);
-          if ((lane & 7) == 0) s_scales[warp][i * 4 + lane / 8] = scale;
-        }
-      }
-      __syncwarp();
+    const unsigned long long mask = s_mask[tok - t0];
+    // Lane d keeps the row index on destination d; everybody reads it with a shuffle.
+    int my_slot = -1;
+    if (lane < unsigned(P) && ((mask >> lane) & 1ull)) {
+      my_slot = s_base[lane] + s_blk_base[lane] + s_rank_in_block[(tok - t0) * P + lane];
     }
+    if (lane < unsigned(P)) sent_slot[size_t(tok) * P + lane] = my_slot;
+    if (mask == 0) continue;
+    const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
     int k_idx = -1;
     float k_w = 0.f;
     if (lane < unsigned(K)) {
       k_idx = topk_idx[size_t(tok) * K + lane];
       k_w = topk_w[size_t(tok) * K + lane];
     }
+    if (a.cfg.quantize) {
+      for (int i0 = 0; i0 < iters; i0 += kBatch) {
+        // All loads of the batch are in flight before the first value is used: one memory round
+        // trip per 4096 elements instead of one per 512.
+        int4 raw[2 * kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+          if (i0 + i < iters) {
+            // lane l holds elements [(i0+i)*512 + l*16, +16) = two int4
+            raw[2 * i] = row[((i0 + i) * 512 + lane * 16) / 8];
+            raw[2 * i + 1] = row[((i0 + i) * 512 + lane * 16) / 8 + 1];
+          }
+        }
+        int4 q[kBatch];
+#pragma unroll
+        for (int i = 0; i < kBatch; ++i) {
+          if (i0 + i < iters) {
+            float scale;
+            q[i] = quantize16(raw[2 * i], raw[2 * i + 1], &scale);
+            if ((lane & 7) == 0) s_scales[warp][(i0 + i) * 4 + lane / 8] = scale;
+          }
+        }
+        for (int dd = 0; dd < P; ++dd) {
+          const int d = (me + dd) % P;  // rotate so the ranks do not all start on the same destination
+          const int slot = __shfl_sync(0xffffffffu, my_slot, d);
+          if (slot < 0) continue;
+          int4 *dst = reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H, team_pe_to_world(t, d)));
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i) {
+            if (i0 + i < iters) dst[(i0 + i) * 32 + lane] = q[i];
+          }
+        }
+      }
+      __syncwarp();
+    }
     for (int dd = 0; dd < P; ++dd) {
-      const int d = (me + dd) % P;  // rotate so the ranks do not all start on the same destination
-      if (!((mask >> d) & 1ull)) continue;
-      const int slot = s_base[d] + s_blk_base[d] + s_rank_in_block[(tok - t0) * P + d];
+      const int d = (me + dd) % P;
+      const int slot = __shfl_sync(0xffffffffu, my_slot, d);
+      if (slot < 0) continue;
       const int w = team_pe_to_world(t, d);
       if (a.cfg.quantize) {
-        int4 *dst = reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H, w));
-#pragma unroll
-        for (int i = 0; i < kMaxIters; ++i) {
-          if (i < iters) dst[i * 32 + lane] = q[i];
-        }
         if (lane < unsigned(nscale / 4)) {
           float4 sc = reinterpret_cast<const float4 *>(s_scales[warp])[lane];
           reinterpret_cast<float4 *>(remote_ptr(recv_scales + size_t(slot) * nscale, w))[lane] = sc;
@@ -279,7 +311,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
       } else {
         int4 *dst = reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H * 2, w));
         const int nvec = H / 8;
-        for (int v = lane; v < nvec; v += 32) dst[v] = row[v];
+        int v = lane;
+        for (; v + 96 < nvec; v += 128) {
+          const int4 r0 = row[v], r1 = row[v + 32], r2 = row[v + 64], r3 = row[v + 96];
+          dst[v] = r0; dst[v + 32] = r1; dst[v + 64] = r2; dst[v + 96] = r3;
+        }
+        for (; v < nvec; v += 32) dst[v] = row[v];
       }
       int *meta = remote_ptr(recv_meta + size_t(slot) * EP_META_WORDS, w);
       if (lane < unsigned(K)) {
@@ -290,13 +327,14 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
       } else if (lane == 17) {
         meta[EP_META_SRC_RANK] = me;
       }
-      if (lane == 0) sent_slot[size_t(tok) * P + d] = slot;
     }
     __syncwarp();
   }
 
   // ---- D: completion ------------------------------------------------------------------------------------------
+  if (stamp) phase_ns[4] = detail::now_ns();
   bool ok = block_pair_barrier(t, b);
+  if (stamp) phase_ns[5] = detail::now_ns();
   if (b == 0 && ok) {
     // Receive-side bookkeeping: rows per source, first row per source, rows per local expert.
     for (unsigned s = tid; s < unsigned(P); s += nthr) {
@@ -316,6 +354,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
       for (int s = 0; s < P; ++s) sum += static_cast<int>(wait_packed(exp_in + s * epr + e, epoch, s, &good));
       recv_info[1 + 2 * P + e] = sum;
     }
+    __syncthreads();
+    if (stamp) phase_ns[6] = detail::now_ns();
   }
 }
 
@@ -331,7 +371,51 @@ struct CombineArgs {
   rocshmem_team_t team;
 };
 
-__global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(CombineArgs a) {
+// Sums `n_src` rows (scaled by wgt) into dst. U vectors per source are loaded before any is used, so
+// up to S * U 16-byte loads are in flight per lane.
+template <int S, int U>
+__device__ __forceinline__ void combine_row(int4 *dst, const int4 **src, const float *wgt, int n_src,
+                                            int nvec, unsigned lane) {
+  for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
+    int4 raw[S][U];
+#pragma unroll
+    for (int s = 0; s < S; ++s) {
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        if (s < n_src && v0 + 32 * u < nvec) raw[s][u] = src[s][v0 + 32 * u];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (v0 + 32 * u < nvec) {
+        float acc[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+#pragma unroll
+        for (int s = 0; s < S; ++s) {
+          if (s < n_src) {
+            const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[s][u]);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(p2[i]);
+              acc[2 * i] = fmaf(f.x, wgt[s], acc[2 * i]);
+              acc[2 * i + 1] = fmaf(f.y, wgt[s], acc[2 * i + 1]);
+            }
+          }
+        }
+        int4 o;
+        __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        dst[v0 + 32 * u] = o;
+      }
+    }
+  }
+}
+
+__global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_kernel(CombineArgs a) {
+  __shared__ const int4 *s_src[kCombineThreads / 32][EP_MAX_TOPK];
+  __shared__ float s_wgt[kCombineThreads / 32][EP_MAX_TOPK];
   const rocshmem_team_dev *t = detail::team_of(a.team);
   if (t->my_pe < 0) return;
   const int P = t->size;
@@ -342,8 +426,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(CombineArgs a
   const int *topk_idx = rebase(a.topk_idx);
   const float *topk_w = rebase(a.topk_w);
 
+  unsigned long long *phase_ns = rebase(a.buf.phase_ns);
+  const bool stamp = (blockIdx.x == 0 && threadIdx.x == 0);
+  if (stamp) phase_ns[8] = detail::now_ns();
   // Every member's result rows are complete (its producers ran before this kernel on its stream).
   if (!block_pair_barrier(t, blockIdx.x)) return;
+  if (stamp) phase_ns[9] = detail::now_ns();
 
   const unsigned lane = threadIdx.x % 32;
   const unsigned gwarp = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
@@ -351,60 +439,51 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_combine_kernel(CombineArgs a
   const int nvec = H / 8;  // int4 vectors of 8 bf16 per row
   for (int tok = gwarp; tok < a.num_tokens; tok += nwarps) {
     // Lane d owns destination rank d: its row index there and the gate weight of that rank.
+    // Lanes < K fetch one (expert, weight) pair each, so all small loads are issued at once.
     int my_slot = -1;
+    if (lane < unsigned(P)) my_slot = sent_slot[size_t(tok) * P + lane];
+    int k_e = -1;
+    float k_w = 0.f;
+    if (a.weighted && lane < unsigned(K)) {
+      k_e = topk_idx[size_t(tok) * K + lane];
+      k_w = topk_w[size_t(tok) * K + lane];
+    }
     float my_w = 1.f;
-    if (lane < unsigned(P)) {
-      my_slot = sent_slot[size_t(tok) * P + lane];
-      if (a.weighted) {
-        my_w = 0.f;
-        for (int k = 0; k < K; ++k) {
-          const int e = topk_idx[size_t(tok) * K + k];
-          if (e >= 0 && e / epr == int(lane)) my_w += topk_w[size_t(tok) * K + k];
-        }
+    if (a.weighted) {
+      my_w = 0.f;
+      for (int k = 0; k < K; ++k) {
+        const int e = __shfl_sync(0xffffffffu, k_e, k);
+        const float w = __shfl_sync(0xffffffffu, k_w, k);
+        if (e >= 0 && e / epr == int(lane)) my_w += w;
       }
     }
     const unsigned active = __ballot_sync(0xffffffffu, my_slot >= 0);
-    const __nv_bfloat16 *src[EP_MAX_TOPK];
-    float wgt[EP_MAX_TOPK];
-    int n_src = 0;
-    for (unsigned m = active; m && n_src < EP_MAX_TOPK; m &= m - 1) {
-      const int d = __ffs(m) - 1;
-      const int slot = __shfl_sync(0xffffffffu, my_slot, d);
-      wgt[n_src] = __shfl_sync(0xffffffffu, my_w, d);
-      src[n_src] = remote_ptr(y + size_t(slot) * H, team_pe_to_world(t, d));
-      ++n_src;
+    // Source row pointers and weights live in shared memory (one set per warp): the registers are
+    // needed for the loads in flight.
+    const int4 **src = s_src[threadIdx.x / 32];
+    float *wgt = s_wgt[threadIdx.x / 32];
+    const int n_src = min(__popc(active), EP_MAX_TOPK);
+    if (my_slot >= 0) {
+      const int pos = __popc(active & ((1u << lane) - 1u));
+      if (pos < EP_MAX_TOPK) {
+        src[pos] = reinterpret_cast<const int4 *>(remote_ptr(y + size_t(my_slot) * H, team_pe_to_world(t, lane)));
+        wgt[pos] = my_w;
+      }
     }
+    __syncwarp();
     int4 *dst = reinterpret_cast<int4 *>(out + size_t(tok) * H);
-    for (int v = lane; v < nvec; v += 32) {
-      int4 raw[EP_MAX_TOPK];
-#pragma unroll
-      for (int s = 0; s < EP_MAX_TOPK; ++s) {
-        if (s < n_src) raw[s] = reinterpret_cast<const int4 *>(src[s])[v];
-      }
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-#pragma unroll
-      for (int s = 0; s < EP_MAX_TOPK; ++s) {
-        if (s < n_src) {
-          const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[s]);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(p2[i]);
-            acc[2 * i] = fmaf(f.x, wgt[s], acc[2 * i]);
-            acc[2 * i + 1] = fmaf(f.y, wgt[s], acc[2 * i + 1]);
-          }
-        }
-      }
-      int4 o;
-      __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&o);
-#pragma unroll
-      for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-      dst[v] = o;
+    if (n_src <= 4) {
+      combine_row<4, 4>(dst, src, wgt, n_src, nvec, lane);
+    } else {
+      combine_row<8, 2>(dst, src, wgt, n_src, nvec, lane);
     }
+    __syncwarp();
   }
-  // Nobody reuses its result rows while a peer may still be reading them.
-  block_pair_barrier(t, blockIdx.x);
+  if (stamp) phase_ns[10] = detail::now_ns();
+  // Nobody reuses its result rows while a peer may still be reading them. Nothing is handed over
+  // here (the output rows are local), so the relaxed form suffices.
+  block_pair_barrier(t, blockIdx.x, false);
+  if (stamp) phase_ns[11] = detail::now_ns();
 }
 
 // ---- stand-alone block-scaled fp8 helpers ----------------------------------------------------------------------
@@ -512,7 +591,7 @@ int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf,
   if (int rc = validate(cfg, ht->world.size, num_tokens)) return rc;
   DispatchArgs a{cfg, buf, static_cast<const __nv_bfloat16 *>(x), topk_idx, topk_w, num_tokens, epoch, team};
   const int tpb = (cfg.max_tokens + cfg.blocks - 1) / cfg.blocks;
-  const size_t smem = size_t(tpb) * ht->world.size * sizeof(int);
+  const size_t smem = size_t(tpb) * (ht->world.size * sizeof(int) + sizeof(unsigned long long));
   if (smem > 40 * 1024) return cudaErrorInvalidValue;  // use more blocks for this many tokens
   return launch_pes(ep_dispatch_kernel, cfg.blocks, kEpThreads, smem, static_cast<cudaStream_t>(stream), true, a);
 }
@@ -525,7 +604,7 @@ int ep_combine(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, 
   if (int rc = validate(cfg, ht->world.size, num_tokens)) return rc;
   CombineArgs a{cfg, buf, static_cast<const __nv_bfloat16 *>(y), static_cast<__nv_bfloat16 *>(out), topk_idx,
                 topk_w, num_tokens, weighted, team};
-  return launch_pes(ep_combine_kernel, cfg.blocks, kEpThreads, 0, static_cast<cudaStream_t>(stream), false, a);
+  return launch_pes(ep_combine_kernel, cfg.blocks, kCombineThreads, 0, static_cast<cudaStream_t>(stream), false, a);
 }
 
 int fp8_quantize_1x128(const void *x, void *q, float *scales, size_t rows, int hidden, void *stream) {

@@ -51,6 +51,9 @@ struct EpBuffers {
   int *blk_cnt;             // [blocks][P]
   int *exp_cnt;             // [2][num_experts] double-buffered by call parity
   unsigned long long *grid_counter;  // [1]
+  // [16] device timestamps (ns) written by block 0: dispatch phases in [0, 8), combine in [8, 16).
+  // Always on: eight 8-byte stores per kernel.
+  unsigned long long *phase_ns;
   // outputs, local
   int *recv_info;           // [0] total rows, [1 + s] first row of source s (P + 1 entries), then
                             // [2 + P + e] rows whose top-k contains local expert e

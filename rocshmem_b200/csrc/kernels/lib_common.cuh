@@ -18,11 +18,16 @@ using detail::st;
 // has its own GPU. All members must launch the same number of blocks for the same sequence of
 // library calls on a team, which keeps the per-(team, block) epochs in step without communication.
 // Returns false if a peer did not arrive within the wait budget (error record written).
-__device__ inline bool block_pair_barrier(const rocshmem_team_dev *t, unsigned block) {
+//
+// `publish` == false is the cheaper "I am done reading" form: the flags are written and polled with
+// relaxed accesses (no system-scope fence). It orders nothing the block wrote, so it may only be used
+// where the block has no data to hand over, e.g. before a source buffer is released for reuse.
+__device__ inline bool block_pair_barrier(const rocshmem_team_dev *t, unsigned block, bool publish = true) {
   __shared__ unsigned long long s_epoch;
   const rocshmem_device_state &s = st();
   const unsigned tid = detail::block_tid(), nthr = detail::block_threads();
   __syncthreads();
+  if (t->size == 1) return true;  // nobody to pair with (every member skips, so epochs stay in step)
   if (tid == 0) {
     unsigned long long *e = s.lib_state + size_t(t->slot) * ROCSHMEM_LIB_MAX_BLOCKS + block;
     s_epoch = *e + 1;
@@ -32,13 +37,32 @@ __device__ inline bool block_pair_barrier(const rocshmem_team_dev *t, unsigned b
   const unsigned long long epoch = s_epoch;
   unsigned long long *mine =
       s.lib_flags + (size_t(t->slot) * ROCSHMEM_LIB_MAX_BLOCKS + block) * ROCSHMEM_MAX_PES;
-  for (unsigned j = tid; j < static_cast<unsigned>(t->size); j += nthr) {
-    detail::st_release_sys(detail::remote_ptr(mine + t->my_pe, detail::team_pe_to_world(t, j)), epoch);
-  }
   bool ok = true;
-  for (unsigned j = tid; j < static_cast<unsigned>(t->size); j += nthr) {
-    ok = detail::wait_ge_sys(mine + j, epoch, detail::team_pe_to_world(t, j), 60,
-                             ROCSHMEM_ERR_BARRIER_TIMEOUT) && ok;
+  if (publish) {
+    for (unsigned j = tid; j < static_cast<unsigned>(t->size); j += nthr) {
+      detail::st_release_sys(detail::remote_ptr(mine + t->my_pe, detail::team_pe_to_world(t, j)), epoch);
+    }
+    for (unsigned j = tid; j < static_cast<unsigned>(t->size); j += nthr) {
+      ok = detail::wait_ge_sys(mine + j, epoch, detail::team_pe_to_world(t, j), 60,
+                               ROCSHMEM_ERR_BARRIER_TIMEOUT) && ok;
+    }
+  } else {
+    for (unsigned j = tid; j < static_cast<unsigned>(t->size); j += nthr) {
+      detail::st_relaxed_sys(detail::remote_ptr(mine + t->my_pe, detail::team_pe_to_world(t, j)), epoch);
+    }
+    for (unsigned j = tid; j < static_cast<unsigned>(t->size); j += nthr) {
+      unsigned long long seen = detail::ld_relaxed_sys(mine + j);
+      if (seen < epoch) {
+        detail::SpinBudget budget(s.wait_timeout_ns);
+        while ((seen = detail::ld_relaxed_sys(mine + j)) < epoch) {
+          if (!budget.keep_going()) {
+            detail::record_error(ROCSHMEM_ERR_BARRIER_TIMEOUT, detail::team_pe_to_world(t, j), 62, mine + j, epoch, seen);
+            ok = false;
+            break;
+          }
+        }
+      }
+    }
   }
   return __syncthreads_and(ok ? 1 : 0) != 0;
 }

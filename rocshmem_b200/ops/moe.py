@@ -105,11 +105,12 @@ class EpDispatcher:
         self.blk_cnt = z(self.blocks * P, torch.int32)
         self.exp_cnt = z(2 * num_experts, torch.int32)
         self.grid_counter = z(1, torch.int64)
+        self.phase_ns = z(16, torch.int64)
         self.recv_info = z(1 + 2 * P + self.experts_per_rank, torch.int32)
         self._y = None
         ptrs = {name: getattr(self, name).data_ptr() for name in (
             "recv_x", "recv_scales", "recv_meta", "cnt_in", "exp_in", "sent_slot", "tok_mask", "blk_cnt",
-            "exp_cnt", "grid_counter", "recv_info")}
+            "exp_cnt", "grid_counter", "phase_ns", "recv_info")}
         self._h = C.EpHandle(self.team.handle, num_experts, top_k, hidden, max_tokens, int(quantize),
                              self.layout, self.blocks, ptrs)
         self.kernel_launches = 0
@@ -158,6 +159,15 @@ class EpDispatcher:
                         int(weighted), _stream(stream))
         self.kernel_launches += 1
         return out
+
+    def phase_times_us(self) -> dict:
+        """Device timestamps of the last dispatch and combine (block 0), as microseconds since the
+        kernel's first timestamp. Synchronises."""
+        ns = self.phase_ns.cpu().tolist()
+        names_d = ["start", "scan", "grid_barrier", "offsets_counts", "sent", "peers_done", "outputs"]
+        names_c = ["start", "peers_ready", "summed", "peers_done"]
+        return {"dispatch": {n: (ns[i] - ns[0]) / 1e3 for i, n in enumerate(names_d)},
+                "combine": {n: (ns[8 + i] - ns[8]) / 1e3 for i, n in enumerate(names_c)}}
 
     def expert_layout(self, stream=None):
         """Row lists grouped by local expert for a grouped GEMM: ``offsets`` [E_local + 1], ``row_index``
