@@ -76,12 +76,19 @@ __device__ __forceinline__ void reduce_range(const rocshmem_team_dev *t, T *dest
   size_t scalar_from = lo;
   if (aligned && (lo % VEC) == 0) {
     const size_t nvec = (hi - lo) / VEC;
-    for (size_t v = tid; v < nvec; v += nthr) {
-      const size_t e = lo + v * VEC;
-      // Start with my own copy, then the peers in rotated order so that at any moment the members
-      // read from different sources.
-      int4 raw[ROCSHMEM_MAX_PES > 8 ? 8 : ROCSHMEM_MAX_PES];
-      A acc[VEC];
+    // Two vectors per thread and pass; the loads of both (one per member, up to 8 members at a
+    // time) are issued before any value is used.
+    constexpr int U = 2;
+    for (size_t v = tid; v < nvec; v += U * nthr) {
+      size_t e[U];
+      bool live[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        live[u] = v + u * nthr < nvec;
+        e[u] = lo + (v + u * nthr) * VEC;
+      }
+      int4 raw[U][8];
+      A acc[U][VEC];
       int done = 0;
       bool first = true;
       while (done < n) {
@@ -89,37 +96,52 @@ __device__ __forceinline__ void reduce_range(const rocshmem_team_dev *t, T *dest
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           if (k < batch) {
-            int j = (t->my_pe + done + k) % n;
-            raw[k] = ld_global_16(remote_ptr(source + e, team_pe_to_world(t, j)));
+            // Start with my own copy, then the peers in rotated order so that at any moment the
+            // members read from different sources.
+            const int j = (t->my_pe + done + k) % n;
+            const int w = team_pe_to_world(t, j);
+#pragma unroll
+            for (int u = 0; u < U; ++u) {
+              if (live[u]) raw[u][k] = ld_global_16(remote_ptr(source + e[u], w));
+            }
           }
         }
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           if (k < batch) {
-            const T *x = reinterpret_cast<const T *>(&raw[k]);
-            if (first) {
 #pragma unroll
-              for (int q = 0; q < VEC; ++q) acc[q] = to_acc<T>(x[q]);
-              first = false;
-            } else {
+            for (int u = 0; u < U; ++u) {
+              if (live[u]) {
+                const T *x = reinterpret_cast<const T *>(&raw[u][k]);
+                if (first && k == 0) {
 #pragma unroll
-              for (int q = 0; q < VEC; ++q) acc[q] = combine<T, OP>(acc[q], to_acc<T>(x[q]), op);
+                  for (int q = 0; q < VEC; ++q) acc[u][q] = to_acc<T>(x[q]);
+                } else {
+#pragma unroll
+                  for (int q = 0; q < VEC; ++q) acc[u][q] = combine<T, OP>(acc[u][q], to_acc<T>(x[q]), op);
+                }
+              }
             }
           }
         }
+        first = false;
         done += batch;
       }
-      int4 out;
-      T *o = reinterpret_cast<T *>(&out);
 #pragma unroll
-      for (int q = 0; q < VEC; ++q) o[q] = from_acc<T>(acc[q]);
-      if (ALL) {
-        for (int d = 0; d < n; ++d) {
-          int j = (t->my_pe + d) % n;
-          st_global_16(remote_ptr(dest + e, team_pe_to_world(t, j)), out);
+      for (int u = 0; u < U; ++u) {
+        if (!live[u]) continue;
+        int4 out;
+        T *o = reinterpret_cast<T *>(&out);
+#pragma unroll
+        for (int q = 0; q < VEC; ++q) o[q] = from_acc<T>(acc[u][q]);
+        if (ALL) {
+          for (int d = 0; d < n; ++d) {
+            const int j = (t->my_pe + d) % n;
+            st_global_16(remote_ptr(dest + e[u], team_pe_to_world(t, j)), out);
+          }
+        } else {
+          st_global_16(dest + e[u], out);
         }
-      } else {
-        st_global_16(dest + e, out);
       }
     }
     scalar_from = lo + nvec * VEC;
@@ -156,8 +178,9 @@ allreduce_one_shot_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg
   if (!block_pair_barrier(t, blockIdx.x)) return;
   reduce_range<T, OP, false>(t, dest, source, 0, nelems, size_t(blockIdx.x) * blockDim.x + threadIdx.x,
                              size_t(gridDim.x) * blockDim.x, op, aligned);
-  // Nobody overwrites a source while a peer may still be reading it.
-  block_pair_barrier(t, blockIdx.x);
+  // Nobody overwrites a source while a peer may still be reading it. The result is local, nothing is
+  // handed over, so the relaxed form of the barrier is enough.
+  block_pair_barrier(t, blockIdx.x, false);
 }
 
 template <typename T, int OP>
@@ -336,9 +359,10 @@ int launch_allreduce_typed(rocshmem_team_t team, void *dest, const void *source,
 }  // namespace
 
 int coll_blocks_for(size_t bytes) {
-  // One block per 64 KiB of payload it has to move, between 1 and 128: small payloads stay
-  // latency-bound on few blocks, large ones spread over most of the GPU.
-  size_t b = (bytes + (size_t(64) << 10) - 1) / (size_t(64) << 10);
+  // One block per 8 KiB of payload (one 16-byte vector per thread of a 512-thread block), between
+  // 1 and 128: a remote access costs about 2 us whatever its size, so a block should not have to
+  // make several dependent round trips while other SMs sit idle.
+  size_t b = (bytes + (size_t(8) << 10) - 1) / (size_t(8) << 10);
   if (b < 1) b = 1;
   if (b > ROCSHMEM_LIB_MAX_BLOCKS) b = ROCSHMEM_LIB_MAX_BLOCKS;
   return static_cast<int>(b);

@@ -237,7 +237,9 @@ size_t CudaVmmProvider::mc_granularity(size_t bytes, int n_devices) const {
   if (!multicast_) return 0;
   CUmulticastObjectProp p = mc_prop(bytes, n_devices);
   size_t g = 0;
-  if (drv.MulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_RECOMMENDED) != CUDA_SUCCESS) return 0;
+  // The minimum granularity is what bind offsets and sizes must respect; the recommended one can be
+  // hundreds of MiB and would bloat every heap.
+  if (drv.MulticastGetGranularity(&g, &p, CU_MULTICAST_GRANULARITY_MINIMUM) != CUDA_SUCCESS) return 0;
   return g;
 }
 

@@ -113,6 +113,13 @@ void Runtime::init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local
 
   layout_ = InternalLayout::build(cfg_);
   size_t gran = mem_->granularity();
+  if (mem_->is_cuda() && cfg_.enable_nvls && bs_->size() > 1 && n_local_ == 1) {
+    // A heap that is to be bound to an NVLink multicast object must be a multiple of the multicast
+    // granularity as well.
+    auto *cu = dynamic_cast<CudaVmmProvider *>(mem_.get());
+    size_t mg = cu ? cu->mc_granularity(align_up(cfg_.heap_size + layout_.total, gran), n_pes_) : 0;
+    if (mg > gran && mg % gran == 0) gran = mg;
+  }
   stride_ = align_up(cfg_.heap_size + layout_.total, gran);
   // All processes must agree on the stride (same configuration).
   {
@@ -215,6 +222,7 @@ void Runtime::setup_nvls() {
   bool ok = true;
   size_t g = cu->mc_granularity(stride_, n_pes_);
   ok = g != 0 && stride_ % g == 0;
+  if (cfg_.debug) std::fprintf(stderr, "[rocshmem pe %d] NVLS: granularity %zu, stride %zu\n", first_pe_, g, stride_);
   if (!all_ok("nvls-gran", ok)) return;
   MemHandle mc;
   if (bs_->rank() == 0) ok = cu->mc_create(stride_, n_pes_, &mc, &why);
