@@ -248,7 +248,7 @@ struct rocshmem_device_state {
 
 // Library (multi-block) collectives: block b of a PE synchronises with block b of every peer, so
 // flags are indexed [team slot][block][peer] and local epochs [team slot][block].
-constexpr int ROCSHMEM_LIB_MAX_BLOCKS = 128;
+constexpr int ROCSHMEM_LIB_MAX_BLOCKS = 256;
 constexpr int ROCSHMEM_LIB_FLAG_WORDS = ROCSHMEM_TEAM_SLOTS * ROCSHMEM_LIB_MAX_BLOCKS * ROCSHMEM_MAX_PES;
 constexpr int ROCSHMEM_LIB_STATE_WORDS = ROCSHMEM_TEAM_SLOTS * ROCSHMEM_LIB_MAX_BLOCKS;
 constexpr int ROCSHMEM_MAX_LOCAL_PES = 8;

@@ -1,8 +1,47 @@
 // Python bindings of the tcgen05 GEMM kernels and the fused GEMM + collective kernels.
 #include <pybind11/pybind11.h>
 
+#include <stdexcept>
+#include <string>
+
+#include "gemm_kernels.hpp"
+
+namespace py = pybind11;
+
 namespace rocshmem {
 namespace kernels {
-void bind_gemm(pybind11::module_ &) {}
+
+namespace {
+template <typename T>
+T *P(uintptr_t v) { return reinterpret_cast<T *>(v); }
+void check(int rc, const char *what) {
+  if (rc == -1) throw std::runtime_error(std::string(what) + ": cannot encode tensor maps (driver entry point missing or bad shape)");
+  if (rc != 0) throw std::runtime_error(std::string(what) + ": CUDA error " + std::to_string(rc));
+}
+}  // namespace
+
+void bind_gemm(py::module_ &m) {
+  m.def("gemm_bf16", [](uintptr_t a, uintptr_t b, uintptr_t c, int M, int N, int K, uintptr_t stream) {
+    check(gemm_bf16(P<void>(a), P<void>(b), P<void>(c), M, N, K, P<void>(stream)), "gemm_bf16");
+  });
+  m.def("grouped_gemm_bf16", [](uintptr_t a, uintptr_t b, uintptr_t c, uintptr_t offsets, int groups, int max_rows,
+                                int N, int K, int swiglu, uintptr_t stream) {
+    check(grouped_gemm_bf16(P<void>(a), P<void>(b), P<void>(c), P<int>(offsets), groups, max_rows, N, K, swiglu,
+                            P<void>(stream)), "grouped_gemm_bf16");
+  });
+  m.def("gemm_error_count", [] { return gemm_error_count(); });
+  m.def("ag_gemm_bf16", [](uintptr_t team, uintptr_t x, uintptr_t gathered, uintptr_t flags, uintptr_t b, uintptr_t c,
+                           int m_shard, int N, int K, unsigned epoch, int comm_blocks, uintptr_t stream) {
+    check(ag_gemm_bf16(reinterpret_cast<rocshmem_team_t>(team), P<void>(x), P<void>(gathered),
+                       P<unsigned long long>(flags), P<void>(b), P<void>(c), m_shard, N, K, epoch, comm_blocks,
+                       P<void>(stream)), "ag_gemm_bf16");
+  });
+  m.def("gemm_rs_bf16", [](uintptr_t team, uintptr_t a, uintptr_t b, uintptr_t staging, uintptr_t out, int m_shard,
+                           int N, int K, uintptr_t counter, unsigned epoch, uintptr_t stream) {
+    check(gemm_rs_bf16(reinterpret_cast<rocshmem_team_t>(team), P<void>(a), P<void>(b), P<void>(staging), P<void>(out),
+                       m_shard, N, K, P<unsigned long long>(counter), epoch, P<void>(stream)), "gemm_rs_bf16");
+  });
+}
+
 }  // namespace kernels
 }  // namespace rocshmem

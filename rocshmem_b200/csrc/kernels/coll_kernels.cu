@@ -29,6 +29,7 @@ namespace kernels {
 namespace {
 
 constexpr unsigned kThreads = 512;
+constexpr unsigned kMaxCollBlocks = 128;  // all blocks of a collective are resident at once on 148 SMs
 constexpr int OP_RUNTIME = -1;
 
 using detail::Acc;
@@ -308,7 +309,7 @@ push_kernel(rocshmem_team_t team, char *dest_arg, const char *source_arg, size_t
 template <typename K>
 unsigned clamp_blocks(K kernel, unsigned want) {
   Runtime &rt = Runtime::instance();
-  unsigned b = std::min<unsigned>(want, ROCSHMEM_LIB_MAX_BLOCKS);
+  unsigned b = std::min<unsigned>(want, kMaxCollBlocks);
   if (rt.n_local() > 1) b = std::min(b, coresident_blocks_per_pe(kernel, kThreads, 0, rt.n_local()));
   return std::max(1u, b);
 }
@@ -364,7 +365,7 @@ int coll_blocks_for(size_t bytes) {
   // make several dependent round trips while other SMs sit idle.
   size_t b = (bytes + (size_t(8) << 10) - 1) / (size_t(8) << 10);
   if (b < 1) b = 1;
-  if (b > ROCSHMEM_LIB_MAX_BLOCKS) b = ROCSHMEM_LIB_MAX_BLOCKS;
+  if (b > kMaxCollBlocks) b = kMaxCollBlocks;
   return static_cast<int>(b);
 }
 

@@ -40,16 +40,6 @@ constexpr int kMaxIters = EP_MAX_HIDDEN / 512;  // 16 iterations of 512 elements
 using detail::remote_ptr;
 using detail::team_pe_to_world;
 
-// Symmetric arguments are given as addresses on the process's first local PE. Plain device pointers
-// (ordinary torch tensors) are passed through, which is what a process with one PE uses.
-template <typename T>
-__device__ __forceinline__ T *rebase(T *p) {
-  const rocshmem_device_state &s = st();
-  const char *c = reinterpret_cast<const char *>(p);
-  if (c >= s.window_base && c < s.window_base + size_t(s.n_pes) * s.heap_stride) return detail::local_ptr(p);
-  return p;
-}
-
 __device__ __forceinline__ unsigned long long pack(unsigned epoch, unsigned value) {
   return (static_cast<unsigned long long>(epoch) << 32) | value;
 }

@@ -1,0 +1,190 @@
+// Plain and grouped bf16 GEMM on tcgen05 / TMEM (sm_100a). See gemm_core.cuh for the kernel structure.
+#include <cuda.h>
+#include <cuda_bf16.h>
+
+#include <algorithm>
+
+#include "../runtime/cuda_vmm_provider.hpp"
+#include "gemm_core.cuh"
+#include "gemm_kernels.hpp"
+#include "gemm_tmap.hpp"
+#include "launch.cuh"
+
+namespace rocshmem {
+namespace kernels {
+
+// ---- tensor maps -------------------------------------------------------------------------------------------
+
+bool encode_tmap_2d(CUtensorMap *map, const void *base, uint64_t rows, uint64_t cols_elems, int elem_bytes,
+                    uint32_t box_rows) {
+  const CudaDriver &drv = CudaDriver::get();
+  if (!drv.ok || drv.TensorMapEncodeTiled == nullptr) return false;
+  cuuint64_t dims[2] = {cols_elems, rows};
+  cuuint64_t strides[1] = {cols_elems * static_cast<uint64_t>(elem_bytes)};
+  cuuint32_t box[2] = {static_cast<cuuint32_t>(gemm::SLAB_BYTES / elem_bytes), box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUtensorMapDataType dt = elem_bytes == 2 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_UINT8;
+  CUresult r = drv.TensorMapEncodeTiled(map, dt, 2, const_cast<void *>(base), dims, strides, box, estr,
+                                        CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                        CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+namespace {
+
+// ---- plain GEMM ------------------------------------------------------------------------------------------------
+struct PlainScheduler {
+  int m, n, tiles_n, tiles;
+  __device__ bool get(int iter, gemm::Tile &t) const {
+    const int id = blockIdx.x + iter * gridDim.x;
+    if (id >= tiles) return false;
+    // Consecutive CTAs share an A row block and sweep B: the working set of a wave stays in L2.
+    const int mt = id / tiles_n, nt = id % tiles_n;
+    t.a_row = mt * gemm::BM;
+    t.b_row[0] = nt * gemm::BN;
+    t.b_row[1] = nt * gemm::BN + gemm::BN / 2;
+    t.rows = min(gemm::BM, m - t.a_row);
+    t.cols = min(gemm::BN, n - nt * gemm::BN);
+    t.c_row = t.a_row;
+    t.c_col = nt * gemm::BN;
+    return true;
+  }
+  __device__ bool ready(const gemm::Tile &) const { return true; }
+};
+
+struct RowMajorEpilogue {
+  __nv_bfloat16 *c;
+  size_t ldc;
+  __device__ __nv_bfloat16 *row_ptr(const gemm::Tile &t, int row) const {
+    return c + static_cast<size_t>(t.c_row + row) * ldc + t.c_col;
+  }
+};
+
+__global__ void __launch_bounds__(gemm::THREADS, 1)
+gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                 __nv_bfloat16 *c, int m, int n, int k) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ gemm::Shared sh;
+  PlainScheduler sched;
+  sched.m = m;
+  sched.n = n;
+  sched.tiles_n = (n + gemm::BN - 1) / gemm::BN;
+  sched.tiles = ((m + gemm::BM - 1) / gemm::BM) * sched.tiles_n;
+  RowMajorEpilogue epi{c, static_cast<size_t>(n)};
+  gemm::run<false, false>(&map_a, &map_b, k * 2, sched, epi, smem_raw, sh);
+}
+
+// ---- grouped GEMM ------------------------------------------------------------------------------------------------
+constexpr int kMaxGroups = 256;
+
+template <bool SWIGLU>
+struct GroupedScheduler {
+  const int *offsets;  // shared-memory copy, groups + 1 entries
+  int groups, n, tiles_n;
+  __device__ bool get(int iter, gemm::Tile &t) const {
+    int id = blockIdx.x + iter * gridDim.x;
+    for (int g = 0; g < groups; ++g) {
+      const int lo = offsets[g], rows = offsets[g + 1] - lo;
+      const int tiles_g = ((rows + gemm::BM - 1) / gemm::BM) * tiles_n;
+      if (id < tiles_g) {
+        const int mt = id / tiles_n, nt = id % tiles_n;
+        t.a_row = lo + mt * gemm::BM;
+        t.rows = min(gemm::BM, rows - mt * gemm::BM);
+        t.c_row = t.a_row;
+        if (SWIGLU) {
+          // 128 gate columns and the matching 128 up columns share one tile.
+          const int j0 = nt * (gemm::BN / 2);
+          t.b_row[0] = g * n + j0;
+          t.b_row[1] = g * n + n / 2 + j0;
+          t.cols = min(gemm::BN / 2, n / 2 - j0);
+          t.c_col = j0;
+        } else {
+          t.b_row[0] = g * n + nt * gemm::BN;
+          t.b_row[1] = t.b_row[0] + gemm::BN / 2;
+          t.cols = min(gemm::BN, n - nt * gemm::BN);
+          t.c_col = nt * gemm::BN;
+        }
+        return true;
+      }
+      id -= tiles_g;
+    }
+    return false;
+  }
+  __device__ bool ready(const gemm::Tile &) const { return true; }
+};
+
+template <bool SWIGLU>
+__global__ void __launch_bounds__(gemm::THREADS, 1)
+grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                         __nv_bfloat16 *c, const int *offsets, int groups, int n, int k) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ gemm::Shared sh;
+  __shared__ int s_offsets[kMaxGroups + 1];
+  for (int i = threadIdx.x; i <= groups; i += blockDim.x) s_offsets[i] = offsets[i];
+  __syncthreads();
+  GroupedScheduler<SWIGLU> sched;
+  sched.offsets = s_offsets;
+  sched.groups = groups;
+  sched.n = n;
+  sched.tiles_n = SWIGLU ? (n / 2 + gemm::BN / 2 - 1) / (gemm::BN / 2) : (n + gemm::BN - 1) / gemm::BN;
+  RowMajorEpilogue epi{c, static_cast<size_t>(SWIGLU ? n / 2 : n)};
+  gemm::run<false, SWIGLU>(&map_a, &map_b, k * 2, sched, epi, smem_raw, sh);
+}
+
+template <typename K>
+int prepare(K kernel) {
+  // Kernels of different instantiations share one function-pointer type, so the attribute is set
+  // on every call (it is a cheap host-side operation) rather than cached per type.
+  cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm::SMEM_BYTES);
+  return e == cudaSuccess ? 0 : static_cast<int>(e);
+}
+
+}  // namespace
+
+int fused_error_count();  // counter of the fused kernels' translation unit
+
+int gemm_error_count() {
+  unsigned int v = 0;
+  if (cudaMemcpyFromSymbol(&v, gemm::g_gemm_errors, sizeof(v)) != cudaSuccess) return -1;
+  const int fused = fused_error_count();
+  return static_cast<int>(v) + (fused > 0 ? fused : 0);
+}
+
+int gemm_bf16(const void *a, const void *b, void *c, int m, int n, int k, void *stream) {
+  if (m <= 0 || n <= 0 || k <= 0 || (k % 8) != 0) return cudaErrorInvalidValue;
+  CUtensorMap map_a, map_b;
+  if (!encode_tmap_2d(&map_a, a, m, k, 2, gemm::BM) || !encode_tmap_2d(&map_b, b, n, k, 2, gemm::BN / 2)) return -1;
+  if (int rc = prepare(gemm_bf16_kernel)) return rc;
+  const int tiles = ((m + gemm::BM - 1) / gemm::BM) * ((n + gemm::BN - 1) / gemm::BN);
+  const int grid = std::min(tiles, device_sm_count());
+  gemm_bf16_kernel<<<grid, gemm::THREADS, gemm::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+      map_a, map_b, static_cast<__nv_bfloat16 *>(c), m, n, k);
+  return cudaGetLastError();
+}
+
+int grouped_gemm_bf16(const void *a, const void *b, void *c, const int *offsets, int groups, int max_rows, int n,
+                      int k, int swiglu, void *stream) {
+  if (groups <= 0 || groups > kMaxGroups || max_rows <= 0 || n <= 0 || k <= 0 || (k % 8) != 0) return cudaErrorInvalidValue;
+  if (swiglu && (n % 2) != 0) return cudaErrorInvalidValue;
+  CUtensorMap map_a, map_b;
+  if (!encode_tmap_2d(&map_a, a, max_rows, k, 2, gemm::BM) ||
+      !encode_tmap_2d(&map_b, b, static_cast<uint64_t>(groups) * n, k, 2, gemm::BN / 2)) {
+    return -1;
+  }
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // The tile count depends on device-side offsets; every SM gets a CTA and idle ones exit at once.
+  const int grid = device_sm_count();
+  if (swiglu) {
+    if (int rc = prepare(grouped_gemm_bf16_kernel<true>)) return rc;
+    grouped_gemm_bf16_kernel<true><<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(
+        map_a, map_b, static_cast<__nv_bfloat16 *>(c), offsets, groups, n, k);
+  } else {
+    if (int rc = prepare(grouped_gemm_bf16_kernel<false>)) return rc;
+    grouped_gemm_bf16_kernel<false><<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(
+        map_a, map_b, static_cast<__nv_bfloat16 *>(c), offsets, groups, n, k);
+  }
+  return cudaGetLastError();
+}
+
+}  // namespace kernels
+}  // namespace rocshmem

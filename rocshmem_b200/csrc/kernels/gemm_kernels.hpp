@@ -1,0 +1,52 @@
+// tcgen05 / TMEM GEMM kernels for sm_100a and the fused GEMM + collective kernels built on them.
+// Host-callable launchers (plain C++). All matrices are row-major; "B" is always given as [N, K]
+// (the layout of a weight matrix [out_features, in_features]), so C = A * B^T.
+//
+// There is no GEMM in the reference; these kernels exist because the tensor-parallel and
+// expert-parallel paths fuse a GEMM with the collective that feeds or drains it.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+
+#include "rocshmem/rocshmem_common.h"
+
+namespace rocshmem {
+namespace kernels {
+
+// C[M, N] (bf16) = A[M, K] (bf16) * B[N, K]^T (bf16), fp32 accumulation in TMEM.
+// K must be a multiple of 8 (16-byte rows for TMA); M and N are arbitrary (edges are predicated).
+// Returns 0, a cudaError_t, or -1 when the driver cannot encode tensor maps.
+int gemm_bf16(const void *a, const void *b, void *c, int m, int n, int k, void *stream);
+
+// Grouped GEMM over row groups that share K and N but have their own weights:
+// for group g, C[offsets[g] : offsets[g+1], :] = A[offsets[g] : offsets[g+1], :] * B[g]^T, with
+// B [groups, N, K]. `offsets` (groups + 1 ints) lives in device memory, so the row counts need not
+// be known on the host (they come out of the MoE dispatch). `max_rows` bounds offsets[groups].
+// With swiglu != 0, N must be even and the output is [rows, N / 2]:
+// out[:, j] = silu(acc[:, j]) * acc[:, j + N/2]  (gate and up projections stacked in B).
+int grouped_gemm_bf16(const void *a, const void *b, void *c, const int *offsets, int groups, int max_rows,
+                      int n, int k, int swiglu, void *stream);
+
+// Device-side status of the last GEMM launched by this process: 0 ok, otherwise the number of
+// CTAs whose bounded wait expired (they released their TMEM and returned early).
+int gemm_error_count();
+
+// Tensor-parallel fused kernels on the symmetric heap (fused_kernels.cu).
+// All-gather -> GEMM: every rank holds x_shard [m_shard, K] (symmetric); computes
+// C[n_ranks * m_shard, N] = concat_ranks(x_shard) * B^T with its local B [N, K]. `gathered` is a
+// symmetric scratch [n_ranks * m_shard, K] that receives the shards; `flags` one u64 per rank
+// (symmetric, zero-initialised once), `epoch` increases by one per call.
+int ag_gemm_bf16(rocshmem_team_t team, const void *x_shard, void *gathered, unsigned long long *flags,
+                 const void *b, void *c, int m_shard, int n, int k, unsigned epoch, int comm_blocks,
+                 void *stream);
+// GEMM -> reduce-scatter: partial[M, N] = A[M, K_local] * B[N, K_local]^T is produced tile by tile and
+// every tile is stored into the staging buffer of the rank that owns its rows
+// (`staging` symmetric [n_ranks][m_shard, N] bf16); the owner then sums the n_ranks contributions into
+// out [m_shard, N]. M = n_ranks * m_shard. `grid_counter` is one zero-initialised u64 in device memory
+// reserved for this operation, `epoch` increases by one per call (1, 2, ...).
+int gemm_rs_bf16(rocshmem_team_t team, const void *a, const void *b, void *staging, void *out, int m_shard,
+                 int n, int k, unsigned long long *grid_counter, unsigned epoch, void *stream);
+
+}  // namespace kernels
+}  // namespace rocshmem

@@ -12,6 +12,17 @@ namespace kernels {
 
 using detail::st;
 
+// Symmetric kernel arguments are given as addresses on the process's first local PE and are rebased
+// to the block's own PE. Plain device pointers (ordinary torch tensors) are passed through, which
+// is what a process with one PE per GPU uses for its private inputs and outputs.
+template <typename T>
+__device__ __forceinline__ T *rebase(T *p) {
+  const rocshmem_device_state &s = st();
+  const char *c = reinterpret_cast<const char *>(p);
+  if (c >= s.window_base && c < s.window_base + size_t(s.n_pes) * s.heap_stride) return detail::local_ptr(p);
+  return p;
+}
+
 // Cross-PE barrier between "the same block" on every member of a team: block b of a PE signals
 // block b of every member and waits for all of them. Blocks of one PE never wait for each other, so
 // a kernel built on this needs no grid-wide synchronisation and no cooperative launch when each PE

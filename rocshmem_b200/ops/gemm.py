@@ -1,0 +1,135 @@
+"""tcgen05 / TMEM GEMMs (sm_100a) and the tensor-parallel kernels that fuse a GEMM with its collective.
+
+All matrices are row-major bf16 and weights are given as ``[out_features, in_features]``, so every
+operation computes ``A @ B.T`` with fp32 accumulation. The plain and grouped GEMMs work on ordinary
+CUDA tensors; the fused tensor-parallel kernels work on symmetric-heap tensors, one PE per process.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import runtime as rt
+
+
+def _stream(stream) -> int:
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return stream.cuda_stream if hasattr(stream, "cuda_stream") else int(stream)
+
+
+def _check(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16 or not t.is_contiguous() or not t.is_cuda:
+        raise ValueError(f"{name} must be a contiguous bf16 CUDA tensor")
+    if t.data_ptr() % 16:
+        raise ValueError(f"{name} must be 16-byte aligned")
+
+
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """``a [M, K] @ b [N, K].T -> [M, N]`` (bf16 in, fp32 accumulate in TMEM, bf16 out)."""
+    _check(a, "a")
+    _check(b, "b")
+    M, K = a.shape
+    N, K2 = b.shape
+    if K != K2 or K % 8:
+        raise ValueError("inner dimensions must match and be a multiple of 8")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    rt._C().gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, _stream(stream))
+    return out
+
+
+def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, swiglu: bool = False,
+                      out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """Rows ``offsets[g]:offsets[g+1]`` of ``a [rows, K]`` are multiplied with ``b[g] [N, K]``.
+
+    ``offsets`` is an int32 device tensor of ``groups + 1`` entries (its values are read on the GPU, so
+    no host synchronisation is needed when they come out of the MoE dispatch). With ``swiglu`` the
+    weight holds the gate projection in rows ``[0, N/2)`` and the up projection in ``[N/2, N)`` and the
+    result is ``silu(gate) * up`` of width ``N / 2``. Rows past ``offsets[-1]`` are left untouched.
+    """
+    _check(a, "a")
+    _check(b, "b")
+    rows, K = a.shape
+    G, N, K2 = b.shape
+    if K != K2 or offsets.dtype != torch.int32 or offsets.numel() != G + 1:
+        raise ValueError("grouped_gemm_bf16: shape mismatch")
+    width = N // 2 if swiglu else N
+    if out is None:
+        out = torch.empty((rows, width), dtype=torch.bfloat16, device=a.device)
+    rt._C().grouped_gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), offsets.data_ptr(), G, rows, N, K,
+                              int(swiglu), _stream(stream))
+    return out
+
+
+def gemm_error_count() -> int:
+    """Number of GEMM CTAs (since process start) whose bounded wait expired; 0 in a healthy run."""
+    return rt._C().gemm_error_count()
+
+
+class TensorParallelLinear:
+    """Buffers and calls of the fused tensor-parallel kernels for one (m_shard, K, N) shape.
+
+    * :meth:`ag_gemm`: ``concat_ranks(x_shard) @ w.T`` where every rank contributes ``x_shard
+      [m_shard, K]`` (all-gather fused into the GEMM's A-operand pipeline);
+    * :meth:`gemm_rs`: ``reduce_scatter_ranks(a @ w.T)`` where ``a [n_ranks * m_shard, K_local]`` and
+      the rank keeps rows ``[rank * m_shard, (rank + 1) * m_shard)`` of the sum.
+    """
+
+    def __init__(self, m_shard: int, team: Optional[rt.Team] = None, comm_blocks: int = 16):
+        if rt.n_local_pes() != 1:
+            raise RuntimeError("the fused tensor-parallel kernels need one PE per process")
+        self.team = team or rt.team_world()
+        self.n_ranks = self.team.n_pes()
+        self.m_shard = m_shard
+        self.comm_blocks = comm_blocks
+        self._ag = {}
+        self._rs = {}
+        self.kernel_launches = 0
+
+    def ag_input(self, k: int) -> torch.Tensor:
+        """The symmetric ``[m_shard, k]`` buffer that holds this rank's activation shard."""
+        return self._ag_buffers(k)[0]
+
+    def _ag_buffers(self, k: int):
+        if k not in self._ag:
+            x = rt.zeros((self.m_shard, k), torch.bfloat16)
+            gathered = rt.zeros((self.n_ranks * self.m_shard, k), torch.bfloat16)
+            flags = rt.zeros(max(16, self.n_ranks * self.m_shard // 128), torch.int64)
+            self._ag[k] = [x, gathered, flags, 0]
+        return self._ag[k]
+
+    def ag_gemm(self, w: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """Uses the current content of :meth:`ag_input` on every rank. ``w [N, K]`` local weight shard."""
+        _check(w, "w")
+        N, K = w.shape
+        buf = self._ag_buffers(K)
+        x, gathered, flags = buf[0], buf[1], buf[2]
+        buf[3] += 1
+        if out is None:
+            out = torch.empty((self.n_ranks * self.m_shard, N), dtype=torch.bfloat16, device=w.device)
+        rt._C().ag_gemm_bf16(self.team.handle, x.data_ptr(), gathered.data_ptr(), flags.data_ptr(), w.data_ptr(),
+                             out.data_ptr(), self.m_shard, N, K, buf[3], self.comm_blocks, _stream(stream))
+        self.kernel_launches += 1
+        return out
+
+    def gemm_rs(self, a: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """``a [n_ranks * m_shard, K_local]``, ``w [N, K_local]`` -> this rank's ``[m_shard, N]`` rows of the
+        sum over ranks of ``a @ w.T``."""
+        _check(a, "a")
+        _check(w, "w")
+        N, K = w.shape
+        if a.shape[0] != self.n_ranks * self.m_shard or a.shape[1] != K:
+            raise ValueError("gemm_rs: a must be [n_ranks * m_shard, K_local]")
+        if N not in self._rs:
+            self._rs[N] = [rt.zeros((self.n_ranks, self.m_shard, N), torch.bfloat16), rt.zeros(16, torch.int64), 0]
+        entry = self._rs[N]
+        staging, counter = entry[0], entry[1]
+        entry[2] += 1
+        if out is None:
+            out = torch.empty((self.m_shard, N), dtype=torch.bfloat16, device=a.device)
+        rt._C().gemm_rs_bf16(self.team.handle, a.data_ptr(), w.data_ptr(), staging.data_ptr(), out.data_ptr(),
+                             self.m_shard, N, K, counter.data_ptr(), entry[2], _stream(stream))
+        self.kernel_launches += 1
+        return out

@@ -213,4 +213,51 @@ def gpu_moe():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_moe)}
+def gpu_tp_fused():
+    """all-gather -> GEMM and GEMM -> reduce-scatter against a torch reference built from every rank's
+    (seeded) inputs."""
+    from rocshmem_b200.ops import gemm
+    _init("2G")
+    me, n = RANK, WORLD
+    dev = shm.device()
+    for m_shard, K, N in ((128, 512, 256), (256, 1024, 1000 // 8 * 8), (384, 2048, 1792)):
+        tp = gemm.TensorParallelLinear(m_shard, comm_blocks=4)
+        xs = []
+        for p in range(n):
+            g = torch.Generator().manual_seed(11 * p + m_shard)
+            xs.append((torch.randn(m_shard, K, generator=g) * 0.5).to(torch.bfloat16))
+        g = torch.Generator().manual_seed(500 + me)
+        w = (torch.randn(N, K, generator=g) * 0.2).to(torch.bfloat16).to(dev)
+        for rep in range(3):  # repeated calls exercise the epoch counters
+            tp.ag_input(K).copy_(xs[me].to(dev))
+            torch.cuda.synchronize()
+            shm.barrier_all()
+            before = gemm.gemm_error_count()
+            out = tp.ag_gemm(w)
+            _ok()
+            assert gemm.gemm_error_count() == before
+            want = torch.cat(xs).float().to(dev) @ w.float().t()
+            err = (out.float() - want).abs().max().item()
+            assert err <= 1e-2 * want.abs().max().item() + 0.05, ("ag_gemm", m_shard, K, N, rep, err)
+        # GEMM -> reduce-scatter: a is [n * m_shard, K_local] per rank with its own K slice
+        ws, as_ = [], []
+        for p in range(n):
+            g = torch.Generator().manual_seed(900 + p)
+            as_.append((torch.randn(n * m_shard, K, generator=g) * 0.5).to(torch.bfloat16))
+            ws.append((torch.randn(N, K, generator=g) * 0.2).to(torch.bfloat16))
+        a_dev, w_dev = as_[me].to(dev), ws[me].to(dev)
+        for rep in range(3):
+            before = gemm.gemm_error_count()
+            out = tp.gemm_rs(a_dev, w_dev)
+            _ok()
+            assert gemm.gemm_error_count() == before
+            total = sum(a.float() @ wv.float().t() for a, wv in zip(as_, ws))
+            want = total[me * m_shard:(me + 1) * m_shard].to(dev)
+            err = (out.float() - want).abs().max().item()
+            # every rank's partial is rounded to bf16 before the sum
+            assert err <= 2e-2 * want.abs().max().item() + 0.1, ("gemm_rs", m_shard, K, N, rep, err)
+        shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_moe, gpu_tp_fused)}
