@@ -322,6 +322,15 @@ void Runtime::finalize() {
     proxy_->stop();
     proxy_.reset();
   }
+  // Kernels launched after finalize (plain GEMMs, layout helpers on ordinary tensors) must not see
+  // the window of a heap that no longer exists: every module gets an all-zero state back.
+  if (is_cuda()) {
+    for (auto &s : states_) s = rocshmem_device_state{};
+    try {
+      upload_states();
+    } catch (...) {
+    }
+  }
   for (auto &c : ctxs_) ops_->ctx_fini(c.get());
   ctxs_.clear();
   default_ctx_ = nullptr;
