@@ -6,6 +6,7 @@
 #include <string>
 
 #include "ep_kernels.hpp"
+#include "moe_kernels.hpp"
 
 namespace py = pybind11;
 
@@ -74,6 +75,21 @@ void bind_ep(py::module_ &m) {
   });
   m.def("fp8_dequantize_1x128", [](uintptr_t q, uintptr_t scales, uintptr_t x, size_t rows, int hidden, uintptr_t stream) {
     check(fp8_dequantize_1x128(P<void>(q), P<float>(scales), P<void>(x), rows, hidden, P<void>(stream)), "fp8_dequantize");
+  });
+  m.def("moe_gather_rows", [](uintptr_t recv_x, uintptr_t scales, int fp8, uintptr_t offsets, int experts,
+                              uintptr_t row_index, int hidden, uintptr_t out, uintptr_t stream) {
+    check(moe_gather_rows(P<void>(recv_x), P<float>(scales), fp8, P<int>(offsets), experts, P<int>(row_index), hidden,
+                          P<void>(out), P<void>(stream)), "moe_gather_rows");
+  });
+  m.def("moe_inverse_map", [](uintptr_t offsets, int experts, uintptr_t row_index, uintptr_t pair_k, int top_k,
+                              uintptr_t inverse, uintptr_t stream) {
+    check(moe_inverse_map(P<int>(offsets), experts, P<int>(row_index), P<int>(pair_k), top_k, P<int>(inverse),
+                          P<void>(stream)), "moe_inverse_map");
+  });
+  m.def("moe_reduce_pairs", [](uintptr_t pairs, uintptr_t inverse, uintptr_t recv_meta, uintptr_t recv_info,
+                               int n_ranks, int top_k, int hidden, int weighted, uintptr_t y, uintptr_t stream) {
+    check(moe_reduce_pairs(P<void>(pairs), P<int>(inverse), P<int>(recv_meta), P<int>(recv_info), n_ranks, top_k,
+                           hidden, weighted, P<void>(y), P<void>(stream)), "moe_reduce_pairs");
   });
   m.attr("EP_META_WORDS") = EP_META_WORDS;
 }

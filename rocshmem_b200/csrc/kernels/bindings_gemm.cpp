@@ -31,10 +31,11 @@ void bind_gemm(py::module_ &m) {
   });
   m.def("gemm_error_count", [] { return gemm_error_count(); });
   m.def("ag_gemm_bf16", [](uintptr_t team, uintptr_t x, uintptr_t gathered, uintptr_t flags, uintptr_t b, uintptr_t c,
-                           int m_shard, int N, int K, unsigned epoch, int comm_blocks, uintptr_t stream) {
+                           int m_shard, int N, int K, unsigned epoch, int comm_blocks, int swiglu,
+                           uintptr_t stream) {
     check(ag_gemm_bf16(reinterpret_cast<rocshmem_team_t>(team), P<void>(x), P<void>(gathered),
                        P<unsigned long long>(flags), P<void>(b), P<void>(c), m_shard, N, K, epoch, comm_blocks,
-                       P<void>(stream)), "ag_gemm_bf16");
+                       swiglu, P<void>(stream)), "ag_gemm_bf16");
   });
   m.def("gemm_rs_bf16", [](uintptr_t team, uintptr_t a, uintptr_t b, uintptr_t staging, uintptr_t out, int m_shard,
                            int N, int K, uintptr_t counter, unsigned epoch, uintptr_t stream) {

@@ -48,6 +48,9 @@ struct AgArgs {
   int comm_blocks;
 };
 
+// With SWIGLU the weight holds gate rows [0, n / 2) and up rows [n / 2, n); one tile pairs 128 gate
+// columns with the matching up columns and the output is silu(gate) * up of width n / 2.
+template <bool SWIGLU>
 struct AgScheduler {
   int me, n_ranks, tiles_per_shard, tiles_n, tiles, m_shard, n, comm_blocks;
   const unsigned int *ready_count;
@@ -60,11 +63,19 @@ struct AgScheduler {
     const int mt = oi % tiles_per_shard;
     t.a_row = src * m_shard + mt * gemm::BM;
     t.rows = gemm::BM;
-    t.b_row[0] = nt * gemm::BN;
-    t.b_row[1] = nt * gemm::BN + gemm::BN / 2;
-    t.cols = min(gemm::BN, n - nt * gemm::BN);
+    if (SWIGLU) {
+      const int j0 = nt * (gemm::BN / 2);
+      t.b_row[0] = j0;
+      t.b_row[1] = n / 2 + j0;
+      t.cols = min(gemm::BN / 2, n / 2 - j0);
+      t.c_col = j0;
+    } else {
+      t.b_row[0] = nt * gemm::BN;
+      t.b_row[1] = nt * gemm::BN + gemm::BN / 2;
+      t.cols = min(gemm::BN, n - nt * gemm::BN);
+      t.c_col = nt * gemm::BN;
+    }
     t.c_row = t.a_row;
-    t.c_col = nt * gemm::BN;
     t.tag = oi;
     return true;
   }
@@ -162,6 +173,7 @@ __device__ void ag_comm_role(const AgArgs &a, const rocshmem_team_dev *t, unsign
   block_pair_barrier(t, blockIdx.x, false);
 }
 
+template <bool SWIGLU>
 __global__ void __launch_bounds__(gemm::THREADS, 1)
 ag_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, AgArgs a) {
   extern __shared__ unsigned char smem_raw[];
@@ -172,19 +184,19 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     ag_comm_role(a, t, smem_raw);
     return;
   }
-  AgScheduler sched;
+  AgScheduler<SWIGLU> sched;
   sched.me = t->my_pe;
   sched.n_ranks = t->size;
   sched.tiles_per_shard = a.m_shard / gemm::BM;
-  sched.tiles_n = (a.n + gemm::BN - 1) / gemm::BN;
+  sched.tiles_n = SWIGLU ? (a.n / 2 + gemm::BN / 2 - 1) / (gemm::BN / 2) : (a.n + gemm::BN - 1) / gemm::BN;
   sched.tiles = t->size * sched.tiles_per_shard * sched.tiles_n;
   sched.m_shard = a.m_shard;
   sched.n = a.n;
   sched.comm_blocks = a.comm_blocks;
   sched.ready_count = a.ready;
   sched.target = a.epoch * static_cast<unsigned>(a.comm_blocks);
-  PlainEpilogue epi{a.c, static_cast<size_t>(a.n)};
-  gemm::run<false, false>(&map_a, &map_b, a.k * 2, sched, epi, smem_raw, sh);
+  PlainEpilogue epi{a.c, static_cast<size_t>(SWIGLU ? a.n / 2 : a.n)};
+  gemm::run<false, SWIGLU>(&map_a, &map_b, a.k * 2, sched, epi, smem_raw, sh);
 }
 
 // ---- GEMM -> reduce-scatter ----------------------------------------------------------------------------------
@@ -306,7 +318,7 @@ int fused_error_count() {
 
 int ag_gemm_bf16(rocshmem_team_t team, const void *x_shard, void *gathered, unsigned long long *flags,
                  const void *b, void *c, int m_shard, int n, int k, unsigned epoch, int comm_blocks,
-                 void *stream) {
+                 int swiglu, void *stream) {
   Runtime &rt = Runtime::instance();
   HostTeam *ht = rt.team_from_handle(team);
   if (!ht || rt.n_local() != 1) return cudaErrorInvalidValue;
@@ -321,13 +333,18 @@ int ag_gemm_bf16(rocshmem_team_t team, const void *x_shard, void *gathered, unsi
       !encode_tmap_2d(&map_b, b, n, k, 2, gemm::BN / 2)) {
     return -1;
   }
-  if (int rc = prepare_smem(ag_gemm_kernel)) return rc;
+  if (swiglu && (n % 16) != 0) return cudaErrorInvalidValue;
+  if (int rc = swiglu ? prepare_smem(ag_gemm_kernel<true>) : prepare_smem(ag_gemm_kernel<false>)) return rc;
   AgArgs a{team, static_cast<const __nv_bfloat16 *>(x_shard), static_cast<__nv_bfloat16 *>(gathered),
            reinterpret_cast<unsigned int *>(flags), static_cast<__nv_bfloat16 *>(c), m_shard, n, k, epoch,
            comm_blocks};
   // Comm CTAs wait for peers, GEMM CTAs wait for comm CTAs: all of them must be resident.
-  return launch_pes(ag_gemm_kernel, sms, gemm::THREADS, gemm::SMEM_BYTES, static_cast<cudaStream_t>(stream), true,
-                    map_a, map_b, a);
+  if (swiglu) {
+    return launch_pes(ag_gemm_kernel<true>, sms, gemm::THREADS, gemm::SMEM_BYTES, static_cast<cudaStream_t>(stream),
+                      true, map_a, map_b, a);
+  }
+  return launch_pes(ag_gemm_kernel<false>, sms, gemm::THREADS, gemm::SMEM_BYTES, static_cast<cudaStream_t>(stream),
+                    true, map_a, map_b, a);
 }
 
 int gemm_rs_bf16(rocshmem_team_t team, const void *a_mat, const void *b, void *staging, void *out, int m_shard,

@@ -39,7 +39,7 @@ int gemm_error_count();
 // (symmetric, zero-initialised once), `epoch` increases by one per call.
 int ag_gemm_bf16(rocshmem_team_t team, const void *x_shard, void *gathered, unsigned long long *flags,
                  const void *b, void *c, int m_shard, int n, int k, unsigned epoch, int comm_blocks,
-                 void *stream);
+                 int swiglu, void *stream);
 // GEMM -> reduce-scatter: partial[M, N] = A[M, K_local] * B[N, K_local]^T is produced tile by tile and
 // every tile is stored into the staging buffer of the rank that owns its rows
 // (`staging` symmetric [n_ranks][m_shard, N] bf16); the owner then sums the n_ranks contributions into

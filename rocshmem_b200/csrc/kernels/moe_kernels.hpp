@@ -1,0 +1,23 @@
+// Host-callable launchers of the MoE feed-forward glue kernels (see moe_kernels.cu). All pointers are
+// device addresses on the current device; every call is stream-ordered and returns 0 or a CUDA error.
+#pragma once
+
+namespace rocshmem {
+namespace kernels {
+
+// out[pos, :] = row row_index[pos] of the receive buffer as bf16, for pos < offsets[experts].
+// fp8 != 0: recv_x holds e4m3 bytes with one fp32 scale per 128 elements; else bf16 rows.
+int moe_gather_rows(const void *recv_x, const float *recv_scales, int fp8, const int *offsets, int experts,
+                    const int *row_index, int hidden, void *out_bf16, void *stream);
+
+// inverse[row * top_k + k] = pos for every expert-sorted position (entries of unused pairs are left alone).
+int moe_inverse_map(const int *offsets, int experts, const int *row_index, const int *pair_k, int top_k,
+                    int *inverse, void *stream);
+
+// y[row, :] = sum over the row's local experts of (weighted ? gate weight : 1) * pairs[inverse[row, k], :]
+// for every received row listed in recv_info.
+int moe_reduce_pairs(const void *pairs_bf16, const int *inverse, const int *recv_meta, const int *recv_info,
+                     int n_ranks, int top_k, int hidden, int weighted, void *y_bf16, void *stream);
+
+}  // namespace kernels
+}  // namespace rocshmem

@@ -1,0 +1,107 @@
+"""Expert-parallel MoE feed-forward layer (SwiGLU experts) built from this package's kernels.
+
+One call runs, stream-ordered and without a host synchronisation::
+
+    dispatch (fp8 1x128 rows over NVLink)  ->  expert layout  ->  gather + de-quantise into expert order
+      ->  grouped GEMM [gate | up] with SwiGLU epilogue (tcgen05)  ->  grouped GEMM down (tcgen05)
+      ->  per-row sum over the row's local experts, gate-weighted  ->  combine (pull over NVLink)
+
+Experts are sharded over the team: rank r owns global experts ``[r * E_local, (r + 1) * E_local)``.
+The reference has no model code; its nearest building block is the fixed-size alltoall
+(src/ipc/context_ipc_tmpl_device.hpp:474-501).
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .. import runtime as rt
+from ..ops import gemm, moe
+
+
+def expert_weights(expert: int, hidden: int, inter: int, seed: int = 0, device="cpu"):
+    """Deterministic random weights of one global expert: ``w13 [2 * inter, hidden]`` (gate rows first,
+    then up rows) and ``w2 [hidden, inter]``, bf16. Any rank can rebuild any expert from its id."""
+    g = torch.Generator().manual_seed(seed * 100003 + expert)
+    w13 = (torch.randn(2 * inter, hidden, generator=g) * hidden ** -0.5).to(torch.bfloat16)
+    w2 = (torch.randn(hidden, inter, generator=g) * inter ** -0.5).to(torch.bfloat16)
+    return w13.to(device), w2.to(device)
+
+
+class MoEFeedForward:
+    """``num_experts`` SwiGLU experts of shape hidden -> inter -> hidden, top-k routing done by the caller.
+
+    ``pair_capacity`` bounds the number of (row, expert) pairs this rank can process in one call; the
+    default is the worst case ``n_ranks * max_tokens * top_k``. With balanced routing the expected number
+    is ``max_tokens * top_k``, and a tighter bound saves memory; exceeding it is the caller's error.
+    """
+
+    def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, max_tokens: int,
+                 team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact", seed: int = 0,
+                 pair_capacity: Optional[int] = None):
+        if rt.n_local_pes() != 1:
+            raise RuntimeError("MoEFeedForward needs one PE per process")
+        self.d = moe.EpDispatcher(num_experts, top_k, hidden, max_tokens, team=team, quantize=quantize, layout=layout)
+        self.hidden, self.inter, self.top_k = hidden, inter, top_k
+        self.n_ranks, self.e_local = self.d.n_ranks, self.d.experts_per_rank
+        dev = rt.device()
+        first = self.d.team.my_pe() * self.e_local
+        ws = [expert_weights(first + e, hidden, inter, seed) for e in range(self.e_local)]
+        self.w13 = torch.stack([w[0] for w in ws]).to(dev).contiguous()   # [E_local, 2 * inter, hidden]
+        self.w2 = torch.stack([w[1] for w in ws]).to(dev).contiguous()    # [E_local, hidden, inter]
+        cap = pair_capacity or self.n_ranks * max_tokens * top_k
+        self.pair_capacity = cap
+        bf = dict(dtype=torch.bfloat16, device=dev)
+        self.xs = torch.zeros((cap, hidden), **bf)      # rows in expert order
+        self.h = torch.zeros((cap, inter), **bf)        # silu(gate) * up
+        self.yp = torch.zeros((cap, hidden), **bf)      # expert outputs per pair
+        self.inverse = torch.zeros(self.n_ranks * max_tokens * top_k, dtype=torch.int32, device=dev)
+        self.kernel_launches = 0
+
+    def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
+                out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """x [T, hidden] bf16, topk_idx [T, top_k] int32 global expert ids (-1 = unused), topk_weights
+        [T, top_k] fp32. Returns [T, hidden] bf16: sum_k w_k * expert_k(x)."""
+        C = rt._C()
+        d = self.d
+        s = moe._stream(stream)
+        before = d.kernel_launches
+        d.dispatch(x, topk_idx, topk_weights, stream=stream)
+        offsets, row_index, pair_k = d.expert_layout(stream=stream)
+        C.moe_gather_rows(d.recv_x.data_ptr(), d.recv_scales.data_ptr(), int(d.quantize), offsets.data_ptr(),
+                          self.e_local, row_index.data_ptr(), self.hidden, self.xs.data_ptr(), s)
+        C.moe_inverse_map(offsets.data_ptr(), self.e_local, row_index.data_ptr(), pair_k.data_ptr(), self.top_k,
+                          self.inverse.data_ptr(), s)
+        gemm.grouped_gemm_bf16(self.xs, self.w13, offsets, swiglu=True, out=self.h, stream=stream)
+        gemm.grouped_gemm_bf16(self.h, self.w2, offsets, out=self.yp, stream=stream)
+        y = d.result_buffer()
+        C.moe_reduce_pairs(self.yp.data_ptr(), self.inverse.data_ptr(), d.recv_meta.data_ptr(),
+                           d.recv_info.data_ptr(), self.n_ranks, self.top_k, self.hidden, 1, y.data_ptr(), s)
+        out = d.combine(y, topk_idx, topk_weights, x.shape[0], weighted=False, out=out, stream=stream)
+        self.kernel_launches += (d.kernel_launches - before) + 5
+        return out
+
+    __call__ = forward
+
+
+def reference_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, hidden: int, inter: int,
+                      seed: int = 0, quantize: bool = True) -> torch.Tensor:
+    """Plain PyTorch fp32 evaluation of the same layer for the tokens of one rank (all experts rebuilt
+    locally). With ``quantize`` the input passes through the same 1x128 e4m3 quantisation as dispatch.
+    The intermediate activations are rounded to bf16 where the kernels store bf16."""
+    xin = x.float().cpu()
+    if quantize:
+        q, sc = moe.ref_quantize_1x128(x.cpu())
+        xin = moe.ref_dequantize_1x128(q, sc).float()
+    xin = xin.to(torch.bfloat16).float()
+    idx, w = topk_idx.cpu(), topk_weights.cpu()
+    out = torch.zeros(x.shape[0], hidden)
+    for e in idx[idx >= 0].unique().tolist():
+        w13, w2 = expert_weights(int(e), hidden, inter, seed)
+        tok, k = (idx == e).nonzero(as_tuple=True)
+        hcat = xin[tok] @ w13.float().t()
+        h = (torch.nn.functional.silu(hcat[:, :inter]) * hcat[:, inter:]).to(torch.bfloat16).float()
+        y = (h @ w2.float().t()).to(torch.bfloat16).float()
+        out.index_add_(0, tok, y * w[tok, k].unsqueeze(1))
+    return out

@@ -100,17 +100,23 @@ class TensorParallelLinear:
             self._ag[k] = [x, gathered, flags, 0]
         return self._ag[k]
 
-    def ag_gemm(self, w: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
-        """Uses the current content of :meth:`ag_input` on every rank. ``w [N, K]`` local weight shard."""
+    def ag_gemm(self, w: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
+                stream=None) -> torch.Tensor:
+        """Uses the current content of :meth:`ag_input` on every rank. ``w [N, K]`` local weight shard.
+
+        With ``swiglu`` the weight holds gate rows ``[0, N/2)`` and up rows ``[N/2, N)`` and the result
+        is ``silu(gate) * up`` of width ``N / 2`` (the activation is applied in the GEMM epilogue)."""
         _check(w, "w")
         N, K = w.shape
         buf = self._ag_buffers(K)
         x, gathered, flags = buf[0], buf[1], buf[2]
         buf[3] += 1
         if out is None:
-            out = torch.empty((self.n_ranks * self.m_shard, N), dtype=torch.bfloat16, device=w.device)
+            out = torch.empty((self.n_ranks * self.m_shard, N // 2 if swiglu else N), dtype=torch.bfloat16,
+                              device=w.device)
         rt._C().ag_gemm_bf16(self.team.handle, x.data_ptr(), gathered.data_ptr(), flags.data_ptr(), w.data_ptr(),
-                             out.data_ptr(), self.m_shard, N, K, buf[3], self.comm_blocks, _stream(stream))
+                             out.data_ptr(), self.m_shard, N, K, buf[3], self.comm_blocks, int(swiglu),
+                             _stream(stream))
         self.kernel_launches += 1
         return out
 

@@ -260,4 +260,46 @@ def gpu_tp_fused():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_moe, gpu_tp_fused)}
+def gpu_models():
+    """Tensor-parallel MLP and expert-parallel MoE feed-forward layer against plain fp32 PyTorch
+    evaluations of the same layers (weights are rebuilt from seeds on every rank)."""
+    from rocshmem_b200.models import moe_ffn, tp_mlp
+    from rocshmem_b200.ops import gemm, moe
+    _init("2G")
+    me, n = RANK, WORLD
+    dev = shm.device()
+    # -- TP MLP
+    d_model, d_ff, m_shard = 1024, 512 * n, 256
+    mlp = tp_mlp.TensorParallelMLP(d_model, d_ff, m_shard, seed=3, comm_blocks=4)
+    xs = [(torch.randn(m_shard, d_model, generator=torch.Generator().manual_seed(40 + p)) * 0.5).to(torch.bfloat16)
+          for p in range(n)]
+    want = tp_mlp.reference_forward(torch.cat(xs), n, d_model, d_ff, seed=3)[me * m_shard:(me + 1) * m_shard]
+    for rep in range(2):
+        before = gemm.gemm_error_count()
+        out = mlp(xs[me].to(dev))
+        _ok()
+        assert gemm.gemm_error_count() == before
+        err = (out.float().cpu() - want).abs().max().item()
+        assert err <= 2e-2 * want.abs().max().item() + 0.05, ("tp_mlp", rep, err)
+        shm.barrier_all()
+    # -- MoE feed-forward
+    E, K, H, I, T = 8 * n, 4, 1024, 512, 160 + 8 * me
+    layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=256, seed=5)
+    for rep in range(2):
+        g = torch.Generator().manual_seed(77 * rep + me)
+        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+        idx, w = moe.make_routing(T, E, K, 1000 * rep + me)
+        if rep == 1:
+            idx[::9, -1] = -1
+        before = gemm.gemm_error_count()
+        out = layer(x.to(dev), idx.to(dev), w.to(dev))
+        _ok()
+        assert gemm.gemm_error_count() == before
+        want = moe_ffn.reference_forward(x, idx, w, H, I, seed=5)
+        err = (out.float().cpu() - want).abs().max().item()
+        assert err <= 3e-2 * want.abs().max().item() + 0.02, ("moe_ffn", rep, err, want.abs().max().item())
+        shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_moe, gpu_tp_fused, gpu_models)}
