@@ -306,6 +306,59 @@ push_kernel(rocshmem_team_t team, char *dest_arg, const char *source_arg, size_t
   block_pair_barrier(t, blockIdx.x);
 }
 
+// Large broadcast through relays. A root that pushes the whole payload to every member is limited by
+// its own NVLink egress ((n - 1) x bytes over one port). Here the payload is cut into sub-chunks and
+// each sub-chunk into n - 1 parts, one per non-root member: the root sends part r only to relay r
+// (egress = bytes in total), and every relay forwards its part to the other non-root members. The loop
+// has one cross-PE barrier per sub-chunk, so the root's send of sub-chunk c + 1 overlaps the relays'
+// forwarding of sub-chunk c and all ports stay busy. The root's own dest is left untouched, like in
+// the direct variant.
+__global__ void __launch_bounds__(kThreads)
+broadcast_relay_kernel(rocshmem_team_t team, char *dest_arg, const char *source_arg, size_t bytes, int root,
+                       size_t sub_bytes, int pre_sync) {
+  const rocshmem_team_dev *t = detail::team_of(team);
+  if (t->my_pe < 0) return;
+  char *dest = detail::local_ptr(dest_arg);
+  const char *source = detail::local_ptr(const_cast<char *>(source_arg));
+  const int n = t->size, me = t->my_pe;
+  if (pre_sync && !block_pair_barrier(t, blockIdx.x)) return;
+  detail::Group<detail::Scope::BLOCK> g;
+  const int relays = n - 1;
+  const int my_relay = me < root ? me : me - 1;  // meaningless on the root
+  for (size_t base = 0; base < bytes; base += sub_bytes) {
+    const size_t len = bytes - base < sub_bytes ? bytes - base : sub_bytes;
+    const size_t part = ((len + relays - 1) / relays + 15) / 16 * 16;
+    const size_t share = ((part + gridDim.x - 1) / gridDim.x + 15) / 16 * 16;
+    if (me == root) {
+      for (int d = 0; d < relays; ++d) {
+        const int r = (d + blockIdx.x) % relays;  // blocks start on different relays
+        const int j = r < root ? r : r + 1;
+        size_t lo = size_t(r) * part + share * blockIdx.x, hi = lo + share;
+        const size_t end = size_t(r + 1) * part < len ? size_t(r + 1) * part : len;
+        if (hi > end) hi = end;
+        if (lo < hi) {
+          detail::copy_bytes<detail::Scope::BLOCK>(remote_ptr(dest + base + lo, team_pe_to_world(t, j)),
+                                                   source + base + lo, hi - lo, g);
+        }
+      }
+    }
+    // Part r of this sub-chunk has landed on relay r (block b's share of it, on every relay).
+    if (!block_pair_barrier(t, blockIdx.x)) return;
+    if (me != root) {
+      size_t lo = size_t(my_relay) * part + share * blockIdx.x, hi = lo + share;
+      const size_t end = size_t(my_relay + 1) * part < len ? size_t(my_relay + 1) * part : len;
+      if (hi > end) hi = end;
+      for (int d = 1; d < n && lo < hi; ++d) {
+        const int j = (me + d) % n;
+        if (j == root) continue;
+        detail::copy_bytes<detail::Scope::BLOCK>(remote_ptr(dest + base + lo, team_pe_to_world(t, j)),
+                                                 dest + base + lo, hi - lo, g);
+      }
+    }
+  }
+  block_pair_barrier(t, blockIdx.x);
+}
+
 template <typename K>
 unsigned clamp_blocks(K kernel, unsigned want) {
   Runtime &rt = Runtime::instance();
@@ -404,6 +457,22 @@ static int launch_push(rocshmem_team_t team, void *dest, const void *source, siz
 
 int coll_broadcast(rocshmem_team_t team, void *dest, const void *source, size_t bytes, int root,
                    void *stream, int flags) {
+  Runtime &rt = Runtime::instance();
+  HostTeam *ht = rt.team_from_handle(team);
+  const int n = ht ? ht->world.size : 0;
+  if (n >= 3 && bytes >= (size_t(512) << 10)) {
+    // Sub-chunks large enough that a sub-chunk's transfer time dwarfs the barrier that ends it.
+    size_t sub = bytes;
+    if (bytes > (size_t(4) << 20)) {
+      sub = std::max<size_t>(size_t(4) << 20, bytes / 8);
+      sub = std::min<size_t>(sub, size_t(16) << 20);
+      sub = (sub + 4095) / 4096 * 4096;
+    }
+    unsigned blocks = clamp_blocks(broadcast_relay_kernel, static_cast<unsigned>(coll_blocks_for(sub / (n - 1))));
+    return launch_pes(broadcast_relay_kernel, blocks, kThreads, 0, static_cast<cudaStream_t>(stream), false, team,
+                      static_cast<char *>(dest), static_cast<const char *>(source), bytes, root, sub,
+                      (flags & COLL_PRE_SYNC) ? 1 : 0);
+  }
   return launch_push(team, dest, source, bytes, root, 0, stream, flags);
 }
 int coll_fcollect(rocshmem_team_t team, void *dest, const void *source, size_t bytes, void *stream,

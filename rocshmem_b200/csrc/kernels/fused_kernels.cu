@@ -58,7 +58,8 @@ struct AgScheduler {
   __device__ bool get(int iter, gemm::Tile &t) const {
     const int id = (blockIdx.x - comm_blocks) + iter * (gridDim.x - comm_blocks);
     if (id >= tiles) return false;
-    const int oi = id / tiles_n, nt = id % tiles_n;          // row block in arrival order
+    int oi, nt;  // oi: row block in arrival order
+    gemm::raster(id, tiles / tiles_n, tiles_n, min(gemm::RASTER_GROUP, tiles_per_shard), oi, nt);
     const int src = (me + oi / tiles_per_shard) % n_ranks;   // the local shard comes first
     const int mt = oi % tiles_per_shard;
     t.a_row = src * m_shard + mt * gemm::BM;
@@ -215,7 +216,8 @@ struct RsScheduler {
   __device__ bool get(int iter, gemm::Tile &t) const {
     const int id = blockIdx.x + iter * gridDim.x;
     if (id >= tiles) return false;
-    const int oi = id / tiles_n, nt = id % tiles_n;
+    int oi, nt;
+    gemm::raster(id, tiles / tiles_n, tiles_n, min(gemm::RASTER_GROUP, tiles_per_shard), oi, nt);
     // Rows owned by the next rank first, my own rows last: at any time the ranks store to
     // different owners, and the tiles that need no transfer finish the kernel.
     const int owner = (me + 1 + oi / tiles_per_shard) % n_ranks;

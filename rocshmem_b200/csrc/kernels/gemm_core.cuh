@@ -44,6 +44,19 @@ struct Tile {
   int tag;        // scheduler-defined (e.g. index of the row block in arrival order)
 };
 
+// Maps a linear tile id to (row block, column tile). Row blocks are taken in groups of `group` and a
+// group is swept column by column: CTAs that run at the same time share `group` row blocks of A
+// (which stay in L2) and a handful of B tiles, and B is streamed from HBM once per group instead of
+// once per row block. Matters as soon as B is larger than L2.
+constexpr int RASTER_GROUP = 8;
+__device__ __forceinline__ void raster(int id, int row_blocks, int tiles_n, int group, int &rb, int &nt) {
+  const int per_group = group * tiles_n;
+  const int g = id / per_group, rem = id - g * per_group;
+  const int rows = min(group, row_blocks - g * group);
+  nt = rem / rows;
+  rb = g * group + rem % rows;
+}
+
 // One counter per translation unit (the kernels are not built as relocatable device code).
 static __device__ unsigned int g_gemm_errors = 0;
 

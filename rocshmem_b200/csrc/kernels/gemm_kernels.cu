@@ -38,8 +38,8 @@ struct PlainScheduler {
   __device__ bool get(int iter, gemm::Tile &t) const {
     const int id = blockIdx.x + iter * gridDim.x;
     if (id >= tiles) return false;
-    // Consecutive CTAs share an A row block and sweep B: the working set of a wave stays in L2.
-    const int mt = id / tiles_n, nt = id % tiles_n;
+    int mt, nt;
+    gemm::raster(id, tiles / tiles_n, tiles_n, gemm::RASTER_GROUP, mt, nt);
     t.a_row = mt * gemm::BM;
     t.b_row[0] = nt * gemm::BN;
     t.b_row[1] = nt * gemm::BN + gemm::BN / 2;
@@ -87,7 +87,8 @@ struct GroupedScheduler {
       const int lo = offsets[g], rows = offsets[g + 1] - lo;
       const int tiles_g = ((rows + gemm::BM - 1) / gemm::BM) * tiles_n;
       if (id < tiles_g) {
-        const int mt = id / tiles_n, nt = id % tiles_n;
+        int mt, nt;
+        gemm::raster(id, tiles_g / tiles_n, tiles_n, gemm::RASTER_GROUP, mt, nt);
         t.a_row = lo + mt * gemm::BM;
         t.rows = min(gemm::BM, rows - mt * gemm::BM);
         t.c_row = t.a_row;

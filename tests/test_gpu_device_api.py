@@ -467,3 +467,33 @@ def test_host_api_on_device_heap(env):
     assert torch.equal(shm.local_view(g, 2).cpu().view(NPES, 1000)[3], torch.arange(1000) + (3 << 32))
     for t in (g, r, ctr, b, a):
         shm.free(t)
+
+
+@pytest.mark.parametrize("nbytes,root", [((3 << 20) + 40, 1), ((9 << 20) + 16, 3), (600 << 10, 0)])
+def test_large_broadcast_through_relays(env, nbytes, root):
+    """Payloads of 512 KiB and more take the relay path (root -> one part per member -> forwarded): every
+    member but the root receives the root's bytes, the root's dest keeps its content."""
+    from rocshmem_b200.ops import collectives as coll
+    shm, _ = env
+    src = shm.zeros(nbytes + 16, torch.uint8)
+    dst = shm.zeros(nbytes + 16, torch.uint8)
+    pattern = (torch.arange(nbytes, dtype=torch.int64) * 2654435761 >> 7).to(torch.uint8)
+    for l, v in enumerate(views(shm, src)):
+        v[8:8 + nbytes].copy_(((pattern.to(torch.int32) + l) % 256).to(torch.uint8).cuda())
+    for v in views(shm, dst):
+        v.fill_(7)
+    torch.cuda.synchronize()
+    for rep in range(2):
+        assert coll.broadcast(dst[8:8 + nbytes], src[8:8 + nbytes], root) == 0
+        want = ((pattern.to(torch.int32) + root) % 256).to(torch.uint8)
+        for l, v in enumerate(views(shm, dst)):
+            got = v.cpu()
+            assert torch.all(got[:8] == 7) and torch.all(got[8 + nbytes:] == 7), "wrote outside the range"
+            if l == root:
+                assert torch.all(got[8:8 + nbytes] == 7), "the root's dest must stay untouched"
+            else:
+                assert torch.equal(got[8:8 + nbytes], want), (l, rep)
+    err = shm.get_error(0)
+    assert err["count"] == 0, err
+    shm.free(dst)
+    shm.free(src)
