@@ -103,6 +103,21 @@ def main():
                  "tflops": f1 / t1 / 1e6, "frac_of_peak": f1 / t1 / 1e6 / pk})
     rows.append({"op": "grouped_gemm", "groups": G, "rows": G * rows_g, "n": H, "k": I, "us": t2,
                  "tflops": f2 / t2 / 1e6, "frac_of_peak": f2 / t2 / 1e6 / pk})
+    del xs, w13, w2, h, y
+    # block-scaled e4m3 (1 x 128 activation scales, 128 x 128 weight scales); the fraction is still of the
+    # bf16 peak, so values above 1 are expected
+    from rocshmem_b200.ops import moe
+    for m, n, k in [(8192, 7168, 8192), (8192, 8192, 3584), (8192, 28672, 8192)]:
+        a = (torch.randn(m, k, device=dev) * 0.5).to(torch.bfloat16)
+        b = (torch.randn(n, k, device=dev) * 0.5).to(torch.bfloat16)
+        a_q, a_s = moe.fp8_quantize_1x128(a)
+        b_q, b_s = gemm.quantize_weight_128x128(b)
+        c = torch.empty(m, n, dtype=torch.bfloat16, device=dev)
+        t8 = timed(lambda: gemm.gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, out=c), args.iters, flush)
+        fl = 2.0 * m * n * k
+        rows.append({"op": "gemm_fp8_blockscaled", "m": m, "n": n, "k": k, "us": t8, "tflops": fl / t8 / 1e6,
+                     "frac_of_bf16_peak": fl / t8 / 1e6 / pk})
+        del a, b, a_q, a_s, b_q, b_s, c
     res = {"peak_tflops": pk, "peak_source": src, "gemm_errors": gemm.gemm_error_count(), "rows": rows}
     for r in rows:
         print(json.dumps(r))

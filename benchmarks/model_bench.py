@@ -86,6 +86,17 @@ def bench_tp_mlp(args, world, rank, res):
         "tflops_per_gpu": flops / t_fused / 1e6, "roofline_us": roof_us, "frac_of_roofline": roof_us / t_fused,
         "peak_source": src, "max_abs_diff_vs_baseline": err, "baseline_abs_max": scale,
         "gemm_errors": gemm.gemm_error_count()}
+    if args.d_model % 512 == 0 and ff % 512 == 0:
+        mlp8 = tp_mlp.TensorParallelMLPFp8(args.d_model, args.d_ff, m_shard, seed=1, comm_blocks=min(8, args.comm_blocks))
+        out8 = mlp8(x)
+        torch.cuda.synchronize()
+        err8 = (out8.float() - ref.float()).abs().max().item()
+        t8 = timed(lambda: mlp8(x), args.iters)
+        t8_ag = timed(lambda: mlp8.tp.ag_gemm(mlp8.w1_q, mlp8.w1_s, out=mlp8.h, swiglu=True), args.iters)
+        t8_rs = timed(lambda: mlp8.tp.gemm_rs(mlp8.h_q, mlp8.h_s, mlp8.w2_q, mlp8.w2_s), args.iters)
+        res["tp_mlp_fp8"] = {"fused_us": t8, "ag_gemm_us": t8_ag, "gemm_rs_us": t8_rs, "speedup_vs_nccl_cublas_bf16": t_base / t8,
+                             "tflops_per_gpu": flops / t8 / 1e6, "max_abs_diff_vs_bf16_baseline": err8,
+                             "gemm_errors": gemm.gemm_error_count()}
 
 
 def bench_moe(args, world, rank, res):
@@ -111,6 +122,13 @@ def bench_moe(args, world, rank, res):
         row["baseline_abs_max"] = ref.float().abs().max().item()
         row["nccl_cublas_us"] = timed(lambda: base(x, idx, w), max(2, args.iters // 2), warmup=2)
         row["speedup"] = row["nccl_cublas_us"] / t_layer
+    if H % 1024 == 0 and I % 512 == 0:
+        layer8 = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=2, pair_capacity=cap, fp8_experts=True)
+        out8 = layer8(x, idx, w)
+        torch.cuda.synchronize()
+        row["fp8_experts_max_abs_diff_vs_bf16_experts"] = (out8.float() - out.float()).abs().max().item()
+        row["fp8_experts_layer_us"] = timed(lambda: layer8(x, idx, w), args.iters)
+        row["fp8_experts_tokens_per_s_all_ranks"] = world * T / row["fp8_experts_layer_us"] * 1e6
     row["gemm_errors"] = gemm.gemm_error_count()
     res["moe_ffn"] = row
 

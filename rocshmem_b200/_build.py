@@ -35,7 +35,7 @@ RUNTIME_CPP = [
 ]
 LIB_CU = [
     "runtime/host_ops_cuda.cu", "kernels/coll_kernels.cu", "kernels/ep_kernels.cu",
-    "kernels/gemm_kernels.cu", "kernels/fused_kernels.cu", "kernels/no_alloc.cu", "kernels/moe_kernels.cu",
+    "kernels/gemm_kernels.cu", "kernels/fused_kernels.cu", "kernels/no_alloc.cu", "kernels/moe_kernels.cu", "kernels/gemm_fp8.cu",
 ]
 BIND_CPP = ["bindings.cpp", "kernels/bindings_ep.cpp", "kernels/bindings_gemm.cpp"]
 

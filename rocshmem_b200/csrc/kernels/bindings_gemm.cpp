@@ -30,12 +30,38 @@ void bind_gemm(py::module_ &m) {
                             P<void>(stream)), "grouped_gemm_bf16");
   });
   m.def("gemm_error_count", [] { return gemm_error_count(); });
+  m.def("gemm_fp8_blockscaled", [](uintptr_t a, uintptr_t a_s, uintptr_t b, uintptr_t b_s, uintptr_t c, int M, int N,
+                                   int K, uintptr_t stream) {
+    check(gemm_fp8_blockscaled(P<void>(a), P<float>(a_s), P<void>(b), P<float>(b_s), P<void>(c), M, N, K,
+                               P<void>(stream)), "gemm_fp8_blockscaled");
+  });
+  m.def("grouped_gemm_fp8_blockscaled", [](uintptr_t a, uintptr_t a_s, uintptr_t b, uintptr_t b_s, uintptr_t c,
+                                           uintptr_t offsets, int groups, int max_rows, int N, int K,
+                                           int swiglu, uintptr_t stream) {
+    check(grouped_gemm_fp8_blockscaled(P<void>(a), P<float>(a_s), P<void>(b), P<float>(b_s), P<void>(c),
+                                       P<int>(offsets), groups, max_rows, N, K, swiglu, P<void>(stream)),
+          "grouped_gemm_fp8_blockscaled");
+  });
   m.def("ag_gemm_bf16", [](uintptr_t team, uintptr_t x, uintptr_t gathered, uintptr_t flags, uintptr_t b, uintptr_t c,
                            int m_shard, int N, int K, unsigned epoch, int comm_blocks, int swiglu,
                            uintptr_t stream) {
     check(ag_gemm_bf16(reinterpret_cast<rocshmem_team_t>(team), P<void>(x), P<void>(gathered),
                        P<unsigned long long>(flags), P<void>(b), P<void>(c), m_shard, N, K, epoch, comm_blocks,
                        swiglu, P<void>(stream)), "ag_gemm_bf16");
+  });
+  m.def("ag_gemm_fp8", [](uintptr_t team, uintptr_t x_q, uintptr_t x_s, uintptr_t gq, uintptr_t gs, uintptr_t flags,
+                          uintptr_t b_q, uintptr_t b_s, uintptr_t c, int m_shard, int N, int K, unsigned epoch,
+                          int comm_blocks, int swiglu, uintptr_t stream) {
+    check(ag_gemm_fp8(reinterpret_cast<rocshmem_team_t>(team), P<void>(x_q), P<float>(x_s), P<void>(gq), P<float>(gs),
+                      P<unsigned long long>(flags), P<void>(b_q), P<float>(b_s), P<void>(c), m_shard, N, K, epoch,
+                      comm_blocks, swiglu, P<void>(stream)), "ag_gemm_fp8");
+  });
+  m.def("gemm_rs_fp8", [](uintptr_t team, uintptr_t a_q, uintptr_t a_s, uintptr_t b_q, uintptr_t b_s,
+                          uintptr_t staging, uintptr_t out, int m_shard, int N, int K, uintptr_t counter,
+                          unsigned epoch, uintptr_t stream) {
+    check(gemm_rs_fp8(reinterpret_cast<rocshmem_team_t>(team), P<void>(a_q), P<float>(a_s), P<void>(b_q), P<float>(b_s),
+                      P<void>(staging), P<void>(out), m_shard, N, K, P<unsigned long long>(counter), epoch,
+                      P<void>(stream)), "gemm_rs_fp8");
   });
   m.def("gemm_rs_bf16", [](uintptr_t team, uintptr_t a, uintptr_t b, uintptr_t staging, uintptr_t out, int m_shard,
                            int N, int K, uintptr_t counter, unsigned epoch, uintptr_t stream) {

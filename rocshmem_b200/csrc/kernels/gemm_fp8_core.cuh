@@ -1,0 +1,232 @@
+// Block-scaled fp8 (e4m3) GEMM core on tcgen05 / TMEM: C = (A * sa) (B * sb)^T with one fp32 scale per
+// 1 x 128 block of A (per row and 128-element K block) and one per 128 x 128 block of B.
+//
+// The tensor core cannot apply per-K-block scales while it accumulates, so the accumulation is split:
+//   warp 0      TMA producer, one 128-byte K block (128 e4m3) of a 128 x 256 tile per stage, 4 stages;
+//   warp 1      MMA issuer: the four tcgen05.mma (kind::f8f6f4, K = 32 each) of a K block overwrite one
+//               of two 256-column TMEM buffers, then commit to that buffer's mbarrier;
+//   warps 2..9  accumulate: each thread owns one row and 128 columns (one B scale block) in registers;
+//               per K block it reads the raw partial sums with tcgen05.ld and adds them multiplied by
+//               sa[row, kb] * sb[col block, kb]. Two buffers let the tensor core run one K block ahead.
+// At the end of a tile the registers are converted to bf16 and stored. The CUDA-core work per K block
+// (128 FMAs per thread) takes about half as long as the tensor core needs for the block's MMAs.
+// Waits are bounded as in gemm_core.cuh.
+#pragma once
+
+#include <cuda_bf16.h>
+
+#include "gemm_core.cuh"
+#include "sm100_ptx.cuh"
+
+namespace rocshmem {
+namespace kernels {
+namespace gemm8 {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int KB = 128;            // elements (= bytes) of K per block and per stage
+constexpr int STAGES = 4;
+constexpr int A_STAGE_BYTES = BM * KB;
+constexpr int B_STAGE_BYTES = BN * KB;
+constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
+constexpr int ACC_WARPS = 8;
+constexpr int THREADS = 64 + ACC_WARPS * 32;
+constexpr int TMEM_COLS = 512;
+constexpr unsigned long long WAIT_BUDGET_NS = gemm::WAIT_BUDGET_NS;
+
+struct Shared {
+  uint64_t full[STAGES];
+  uint64_t empty[STAGES];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  volatile int abort_flag;
+};
+
+// Scales: a_scale [rows of A][k_blocks] fp32 (row-major), b_scale [rows of B / 128][k_blocks] fp32.
+// Scheduler / Epilogue as in gemm_core.cuh; the tile's a_row / b_row also index the scale arrays,
+// and k_blocks must be a multiple of 4 (the scales are fetched four K blocks at a time). With SWIGLU
+// the tile's b_row[0] / b_row[1] are the gate and up rows of 128 output columns and the result is
+// silu(gate) * up (t.cols <= 128).
+template <bool SWIGLU, bool LATE_A = false, class Scheduler, class Epilogue>
+__device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap *map_b, const float *a_scale,
+                                    const float *b_scale, int k_blocks, Scheduler &sched, Epilogue &epi,
+                                    unsigned char *smem_raw, Shared &sh) {
+  const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+  unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  constexpr uint32_t IDESC = sm100::make_idesc(BM, BN, sm100::kFormatE4M3);
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      sm100::mbar_init(&sh.full[s], 1);
+      sm100::mbar_init(&sh.empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      sm100::mbar_init(&sh.tmem_full[a], 1);
+      sm100::mbar_init(&sh.tmem_empty[a], ACC_WARPS);
+    }
+    sh.abort_flag = 0;
+    sm100::mbar_fence_init();
+    sm100::tma_prefetch_desc(map_a);
+    sm100::tma_prefetch_desc(map_b);
+  }
+  if (warp == 1) sm100::tmem_alloc(&sh.tmem_base, TMEM_COLS);
+  sm100::tcgen05_fence_before();
+  __syncthreads();
+  sm100::tcgen05_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      gemm::Tile t;
+      for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
+        if (!sched.ready(t)) {
+          sh.abort_flag = 1;
+          break;
+        }
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) break;
+          unsigned char *sa = smem + stage * STAGE_BYTES;
+          unsigned char *sb = sa + A_STAGE_BYTES;
+          sm100::mbar_arrive_expect_tx(&sh.full[stage], STAGE_BYTES);
+          sm100::tma_load_2d(sa, map_a, &sh.full[stage], kb * KB, t.a_row);
+          sm100::tma_load_2d(sb, map_b, &sh.full[stage], kb * KB, t.b_row[0]);
+          sm100::tma_load_2d(sb + B_STAGE_BYTES / 2, map_b, &sh.full[stage], kb * KB, t.b_row[1]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+        if (sh.abort_flag) break;
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t buf = 0, buf_phase = 0;
+      gemm::Tile t;
+      for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
+        for (int kb = 0; kb < k_blocks; ++kb) {
+          if (!sm100::mbar_wait(&sh.tmem_empty[buf], buf_phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) break;
+          if (!sm100::mbar_wait(&sh.full[stage], phase, &sh.abort_flag, WAIT_BUDGET_NS)) break;
+          sm100::tcgen05_fence_after();
+          const uint32_t tmem_d = tmem_base + buf * BN;
+          const uint32_t sa = sm100::smem_u32(smem + stage * STAGE_BYTES);
+          const uint32_t sb = sa + A_STAGE_BYTES;
+          const uint64_t da = sm100::make_sw128_desc(sa), db = sm100::make_sw128_desc(sb);
+#pragma unroll
+          for (int kk = 0; kk < KB / 32; ++kk) sm100::mma_f8(tmem_d, da + 2 * kk, db + 2 * kk, IDESC, kk != 0);
+          sm100::mma_commit(&sh.empty[stage]);
+          sm100::mma_commit(&sh.tmem_full[buf]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          buf ^= 1u;
+          if (buf == 0) buf_phase ^= 1u;
+        }
+        if (sh.abort_flag) break;
+      }
+    }
+  } else {
+    const int aw = warp - 2;           // 0..7
+    const int quarter = warp & 3;      // TMEM lanes [32 * quarter, +32) are accessible to this warp
+    const int half = aw / 4;
+    // Plain: this thread owns TMEM columns [128 * half, +128), one B scale block.
+    // SwiGLU: columns [0, 128) hold gate and [128, 256) the matching up projections; the thread owns
+    // gate columns [64 * half, +64) in acc[0..63] and the same up columns in acc[64..127], so that
+    // silu(gate) * up needs no exchange between threads. Gate and up have their own B scale blocks.
+    const int row = quarter * 32 + lane;
+    uint32_t buf = 0, buf_phase = 0;
+    gemm::Tile t;
+    for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
+      float acc[128];
+#pragma unroll
+      for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+      const bool row_ok = row < t.rows;
+      const float4 *sa4 = reinterpret_cast<const float4 *>(a_scale + static_cast<size_t>(t.a_row + (row_ok ? row : 0)) * k_blocks);
+      const float4 *sb4 = reinterpret_cast<const float4 *>(b_scale + static_cast<size_t>(t.b_row[SWIGLU ? 0 : half] / 128) * k_blocks);
+      const float4 *su4 = reinterpret_cast<const float4 *>(b_scale + static_cast<size_t>(t.b_row[1] / 128) * k_blocks);
+      // LATE_A: the A scales of a tile may still be on their way from another GPU until the producer has
+      // seen the tile's rows arrive; the first finished K block proves it has. Read past L1 (__ldcg).
+      if (LATE_A && !sm100::mbar_wait(&sh.tmem_full[buf], buf_phase, &sh.abort_flag, WAIT_BUDGET_NS)) break;
+      float4 a_next = __ldcg(sa4), b_next = sb4[0], u_next = SWIGLU ? su4[0] : make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int kb4 = 0; kb4 < k_blocks / 4 && !sh.abort_flag; ++kb4) {
+        const float4 a_cur = a_next, b_cur = b_next, u_cur = u_next;
+        if (kb4 + 1 < k_blocks / 4) {  // fetched one group ahead of its use
+          a_next = __ldcg(sa4 + kb4 + 1);
+          b_next = sb4[kb4 + 1];
+          if (SWIGLU) u_next = su4[kb4 + 1];
+        }
+        const float scale[4] = {a_cur.x * b_cur.x, a_cur.y * b_cur.y, a_cur.z * b_cur.z, a_cur.w * b_cur.w};
+        const float scale_u[4] = {a_cur.x * u_cur.x, a_cur.y * u_cur.y, a_cur.z * u_cur.z, a_cur.w * u_cur.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (!sm100::mbar_wait(&sh.tmem_full[buf], buf_phase, &sh.abort_flag, WAIT_BUDGET_NS)) break;
+          sm100::tcgen05_fence_after();
+          const uint32_t tbuf = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
+#pragma unroll
+          for (int c = 0; c < 8; ++c) {
+            uint32_t v[16];
+            // SwiGLU: chunks 0..3 come from the gate columns, 4..7 from the up columns.
+            const uint32_t col = SWIGLU ? (c < 4 ? half * 64 + c * 16 : 128 + half * 64 + (c - 4) * 16) : half * 128 + c * 16;
+            const float s = (SWIGLU && c >= 4) ? scale_u[j] : scale[j];
+            sm100::tmem_ld_32x16(tbuf + col, v);
+            sm100::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(s, __uint_as_float(v[i]), acc[c * 16 + i]);
+          }
+          sm100::tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) sm100::mbar_arrive(&sh.tmem_empty[buf]);
+          buf ^= 1u;
+          if (buf == 0) buf_phase ^= 1u;
+        }
+      }
+      if (sh.abort_flag) break;
+      __nv_bfloat16 *out = row_ok ? epi.row_ptr(t, row) : nullptr;
+      constexpr int OUT = SWIGLU ? 64 : 128;   // output columns per thread
+      if (SWIGLU) {
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = gemm::silu(acc[i]) * acc[64 + i];
+      }
+      const int col0 = half * OUT;
+      if (out != nullptr && col0 < t.cols) {
+        __nv_bfloat16 *dst = out + col0;
+        const int n_ok = min(OUT, t.cols - col0);
+        if (n_ok == OUT && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+#pragma unroll
+          for (int q = 0; q < OUT / 8; ++q) {
+            int4 pk;
+            __nv_bfloat162 *p2 = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) p2[i] = __floats2bfloat162_rn(acc[q * 8 + 2 * i], acc[q * 8 + 2 * i + 1]);
+            reinterpret_cast<int4 *>(dst)[q] = pk;
+          }
+        } else {
+#pragma unroll
+          for (int i = 0; i < OUT; ++i) {
+            if (i < n_ok) dst[i] = __float2bfloat16_rn(acc[i]);
+          }
+        }
+      }
+    }
+  }
+  if (sh.abort_flag) {
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+    for (int i = 0; i < 4096; ++i) {
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+      if (now - t0 > 200000ull) break;
+      __nanosleep(200);
+    }
+  }
+  sm100::tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    sm100::tcgen05_fence_after();
+    sm100::tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+  if (threadIdx.x == 0 && sh.abort_flag) atomicAdd(&gemm::g_gemm_errors, 1u);
+}
+
+}  // namespace gemm8
+}  // namespace kernels
+}  // namespace rocshmem

@@ -143,12 +143,14 @@ int prepare(K kernel) {
 }  // namespace
 
 int fused_error_count();  // counter of the fused kernels' translation unit
+int fp8_error_count();    // counter of the fp8 kernels' translation unit
 
 int gemm_error_count() {
   unsigned int v = 0;
   if (cudaMemcpyFromSymbol(&v, gemm::g_gemm_errors, sizeof(v)) != cudaSuccess) return -1;
   const int fused = fused_error_count();
-  return static_cast<int>(v) + (fused > 0 ? fused : 0);
+  const int fp8 = fp8_error_count();
+  return static_cast<int>(v) + (fused > 0 ? fused : 0) + (fp8 > 0 ? fp8 : 0);
 }
 
 int gemm_bf16(const void *a, const void *b, void *c, int m, int n, int k, void *stream) {

@@ -32,6 +32,16 @@ int grouped_gemm_bf16(const void *a, const void *b, void *c, const int *offsets,
 // CTAs whose bounded wait expired (they released their TMEM and returned early).
 int gemm_error_count();
 
+// Block-scaled e4m3 GEMM: C[M, N] (bf16) = (A_q * a_scale) (B_q * b_scale)^T with a_scale [M, K / 128]
+// (one fp32 per row and 128-element K block) and b_scale [N / 128, K / 128] (one per 128 x 128 block).
+// K must be a multiple of 512 and N of 128. The grouped form multiplies rows offsets[g] .. offsets[g + 1]
+// with B_q[g] ([groups * N, K], scales [groups * N / 128, K / 128]).
+int gemm_fp8_blockscaled(const void *a_q, const float *a_scale, const void *b_q, const float *b_scale, void *c, int m,
+                         int n, int k, void *stream);
+int grouped_gemm_fp8_blockscaled(const void *a_q, const float *a_scale, const void *b_q, const float *b_scale, void *c,
+                                 const int *offsets, int groups, int max_rows, int n, int k, int swiglu,
+                                 void *stream);
+
 // Tensor-parallel fused kernels on the symmetric heap (fused_kernels.cu).
 // All-gather -> GEMM: every rank holds x_shard [m_shard, K] (symmetric); computes
 // C[n_ranks * m_shard, N] = concat_ranks(x_shard) * B^T with its local B [N, K]. `gathered` is a
@@ -47,6 +57,16 @@ int ag_gemm_bf16(rocshmem_team_t team, const void *x_shard, void *gathered, unsi
 // reserved for this operation, `epoch` increases by one per call (1, 2, ...).
 int gemm_rs_bf16(rocshmem_team_t team, const void *a, const void *b, void *staging, void *out, int m_shard,
                  int n, int k, unsigned long long *grid_counter, unsigned epoch, void *stream);
+
+// Block-scaled e4m3 forms of the two fused kernels. x_q [m_shard, K] e4m3 and x_s [m_shard, K / 128] fp32 are
+// symmetric; gathered_q / gathered_s are local buffers for all n_ranks shards; b_q [N, K] with b_scale
+// [N / 128, K / 128]. K must be a multiple of 512, N of 128 (256 with swiglu).
+int ag_gemm_fp8(rocshmem_team_t team, const void *x_q, const float *x_s, void *gathered_q, float *gathered_s,
+                unsigned long long *flags, const void *b_q, const float *b_scale, void *c, int m_shard, int n, int k,
+                unsigned epoch, int comm_blocks, int swiglu, void *stream);
+int gemm_rs_fp8(rocshmem_team_t team, const void *a_q, const float *a_scale, const void *b_q, const float *b_scale,
+                void *staging, void *out, int m_shard, int n, int k, unsigned long long *grid_counter, unsigned epoch,
+                void *stream);
 
 }  // namespace kernels
 }  // namespace rocshmem

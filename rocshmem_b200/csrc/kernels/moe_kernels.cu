@@ -121,7 +121,7 @@ __global__ void reduce_pairs_kernel(const __nv_bfloat16 *pairs, const int *inver
 
 int moe_gather_rows(const void *recv_x, const float *recv_scales, int fp8, const int *offsets, int experts,
                     const int *row_index, int hidden, void *out_bf16, void *stream) {
-  if (hidden <= 0 || hidden % 512 || experts < 1) return cudaErrorInvalidValue;
+  if (hidden <= 0 || (fp8 ? hidden % 512 : hidden % 8) || experts < 1) return cudaErrorInvalidValue;
   const unsigned blocks = static_cast<unsigned>(device_sm_count() * 4);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (fp8) {

@@ -39,7 +39,7 @@ class MoEFeedForward:
 
     def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, max_tokens: int,
                  team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact", seed: int = 0,
-                 pair_capacity: Optional[int] = None):
+                 pair_capacity: Optional[int] = None, fp8_experts: bool = False):
         if rt.n_local_pes() != 1:
             raise RuntimeError("MoEFeedForward needs one PE per process")
         self.d = moe.EpDispatcher(num_experts, top_k, hidden, max_tokens, team=team, quantize=quantize, layout=layout)
@@ -58,6 +58,18 @@ class MoEFeedForward:
         self.yp = torch.zeros((cap, hidden), **bf)      # expert outputs per pair
         self.inverse = torch.zeros(self.n_ranks * max_tokens * top_k, dtype=torch.int32, device=dev)
         self.kernel_launches = 0
+        # Block-scaled e4m3 experts: the received e4m3 rows feed the first grouped GEMM as they are (no
+        # de-quantisation), the hidden activation is re-quantised for the second one.
+        self.fp8_experts = bool(fp8_experts)
+        if self.fp8_experts:
+            if not quantize or hidden % 1024 or inter % 512:
+                raise ValueError("fp8 experts need an fp8 dispatch, hidden % 1024 == 0 and inter % 512 == 0")
+            self.w13_q, self.w13_s = gemm.quantize_weight_128x128(self.w13)
+            self.w2_q, self.w2_s = gemm.quantize_weight_128x128(self.w2)
+            self.xs_q = torch.zeros((cap, hidden), dtype=torch.uint8, device=dev)
+            self.xs_s = torch.zeros((cap, hidden // 128), dtype=torch.float32, device=dev)
+            self.h_q = torch.zeros((cap, inter), dtype=torch.uint8, device=dev)
+            self.h_s = torch.zeros((cap, inter // 128), dtype=torch.float32, device=dev)
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
                 out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
@@ -69,12 +81,25 @@ class MoEFeedForward:
         before = d.kernel_launches
         d.dispatch(x, topk_idx, topk_weights, stream=stream)
         offsets, row_index, pair_k = d.expert_layout(stream=stream)
-        C.moe_gather_rows(d.recv_x.data_ptr(), d.recv_scales.data_ptr(), int(d.quantize), offsets.data_ptr(),
-                          self.e_local, row_index.data_ptr(), self.hidden, self.xs.data_ptr(), s)
         C.moe_inverse_map(offsets.data_ptr(), self.e_local, row_index.data_ptr(), pair_k.data_ptr(), self.top_k,
                           self.inverse.data_ptr(), s)
-        gemm.grouped_gemm_bf16(self.xs, self.w13, offsets, swiglu=True, out=self.h, stream=stream)
-        gemm.grouped_gemm_bf16(self.h, self.w2, offsets, out=self.yp, stream=stream)
+        if self.fp8_experts:
+            # Rows and their scales are copied as raw bytes (the gather kernel's 2-byte element view).
+            C.moe_gather_rows(d.recv_x.data_ptr(), 0, 0, offsets.data_ptr(), self.e_local, row_index.data_ptr(),
+                              self.hidden // 2, self.xs_q.data_ptr(), s)
+            C.moe_gather_rows(d.recv_scales.data_ptr(), 0, 0, offsets.data_ptr(), self.e_local,
+                              row_index.data_ptr(), self.hidden // 128 * 2, self.xs_s.data_ptr(), s)
+            gemm.grouped_gemm_fp8_blockscaled(self.xs_q, self.xs_s, self.w13_q, self.w13_s, offsets, swiglu=True,
+                                              out=self.h, stream=stream)
+            gemm.quantize_1x128_into(self.h, self.h_q, self.h_s, stream)
+            gemm.grouped_gemm_fp8_blockscaled(self.h_q, self.h_s, self.w2_q, self.w2_s, offsets, out=self.yp,
+                                              stream=stream)
+            self.kernel_launches += 2
+        else:
+            C.moe_gather_rows(d.recv_x.data_ptr(), d.recv_scales.data_ptr(), int(d.quantize), offsets.data_ptr(),
+                              self.e_local, row_index.data_ptr(), self.hidden, self.xs.data_ptr(), s)
+            gemm.grouped_gemm_bf16(self.xs, self.w13, offsets, swiglu=True, out=self.h, stream=stream)
+            gemm.grouped_gemm_bf16(self.h, self.w2, offsets, out=self.yp, stream=stream)
         y = d.result_buffer()
         C.moe_reduce_pairs(self.yp.data_ptr(), self.inverse.data_ptr(), d.recv_meta.data_ptr(),
                            d.recv_info.data_ptr(), self.n_ranks, self.top_k, self.hidden, 1, y.data_ptr(), s)
@@ -86,7 +111,7 @@ class MoEFeedForward:
 
 
 def reference_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor, hidden: int, inter: int,
-                      seed: int = 0, quantize: bool = True) -> torch.Tensor:
+                      seed: int = 0, quantize: bool = True, fp8_experts: bool = False) -> torch.Tensor:
     """Plain PyTorch fp32 evaluation of the same layer for the tokens of one rank (all experts rebuilt
     locally). With ``quantize`` the input passes through the same 1x128 e4m3 quantisation as dispatch.
     The intermediate activations are rounded to bf16 where the kernels store bf16."""
@@ -94,14 +119,20 @@ def reference_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: tor
     if quantize:
         q, sc = moe.ref_quantize_1x128(x.cpu())
         xin = moe.ref_dequantize_1x128(q, sc).float()
-    xin = xin.to(torch.bfloat16).float()
+    if not fp8_experts:
+        xin = xin.to(torch.bfloat16).float()
     idx, w = topk_idx.cpu(), topk_weights.cpu()
     out = torch.zeros(x.shape[0], hidden)
     for e in idx[idx >= 0].unique().tolist():
         w13, w2 = expert_weights(int(e), hidden, inter, seed)
+        w13, w2 = w13.float(), w2.float()
+        if fp8_experts:
+            w13 = gemm.dequantize_weight_128x128(*gemm.quantize_weight_128x128(w13))
+            w2 = gemm.dequantize_weight_128x128(*gemm.quantize_weight_128x128(w2))
         tok, k = (idx == e).nonzero(as_tuple=True)
-        hcat = xin[tok] @ w13.float().t()
-        h = (torch.nn.functional.silu(hcat[:, :inter]) * hcat[:, inter:]).to(torch.bfloat16).float()
-        y = (h @ w2.float().t()).to(torch.bfloat16).float()
+        hcat = xin[tok] @ w13.t()
+        h = (torch.nn.functional.silu(hcat[:, :inter]) * hcat[:, inter:]).to(torch.bfloat16)
+        h = moe.ref_dequantize_1x128(*moe.ref_quantize_1x128(h)).float() if fp8_experts else h.float()
+        y = (h @ w2.t()).to(torch.bfloat16).float()
         out.index_add_(0, tok, y * w[tok, k].unsqueeze(1))
     return out

@@ -139,3 +139,148 @@ class TensorParallelLinear:
                              self.m_shard, N, K, counter.data_ptr(), entry[2], _stream(stream))
         self.kernel_launches += 1
         return out
+
+
+# ---- block-scaled fp8 ---------------------------------------------------------------------------------------------
+
+E4M3_MAX = 448.0
+
+
+def quantize_weight_128x128(w: torch.Tensor):
+    """``w [..., N, K]`` (N, K multiples of 128) -> (e4m3 ``[..., N, K]``, fp32 scales ``[..., N/128, K/128]``)
+    with one scale per 128 x 128 block (``w ~ q * scale``). Plain PyTorch: weights are quantised once."""
+    *lead, N, K = w.shape
+    blocks = w.float().reshape(*lead, N // 128, 128, K // 128, 128)
+    amax = blocks.abs().amax(dim=(-3, -1), keepdim=True)
+    scale = torch.where(amax > 0, amax / E4M3_MAX, torch.ones_like(amax))
+    q = (blocks / scale).clamp(-E4M3_MAX, E4M3_MAX).to(torch.float8_e4m3fn).reshape(*lead, N, K)
+    return q.contiguous(), scale.reshape(*lead, N // 128, K // 128).contiguous()
+
+
+def dequantize_weight_128x128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    *lead, N, K = q.shape
+    blocks = q.float().reshape(*lead, N // 128, 128, K // 128, 128)
+    return (blocks * scale.reshape(*lead, N // 128, 1, K // 128, 1)).reshape(*lead, N, K)
+
+
+def _check8(q: torch.Tensor, s: torch.Tensor, name: str) -> None:
+    if q.dtype not in (torch.float8_e4m3fn, torch.uint8) or not q.is_contiguous() or not q.is_cuda:
+        raise ValueError(f"{name} must be a contiguous e4m3 CUDA tensor")
+    if s.dtype != torch.float32 or not s.is_contiguous() or s.data_ptr() % 16 or q.data_ptr() % 16:
+        raise ValueError(f"{name} scales must be contiguous fp32, 16-byte aligned")
+
+
+def gemm_fp8_blockscaled(a_q: torch.Tensor, a_scale: torch.Tensor, b_q: torch.Tensor, b_scale: torch.Tensor,
+                         out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """``(a_q * a_scale) [M, K] @ (b_q * b_scale) [N, K].T -> [M, N]`` bf16. ``a_scale [M, K/128]`` (1 x 128
+    blocks, as produced by :func:`rocshmem_b200.ops.moe.fp8_quantize_1x128` and by the MoE dispatch),
+    ``b_scale [N/128, K/128]`` (128 x 128 blocks). K a multiple of 512, N of 128."""
+    _check8(a_q, a_scale, "a")
+    _check8(b_q, b_scale, "b")
+    M, K = a_q.shape
+    N, K2 = b_q.shape
+    if K != K2 or K % 512 or N % 128 or tuple(a_scale.shape) != (M, K // 128) or tuple(b_scale.shape) != (N // 128, K // 128):
+        raise ValueError("gemm_fp8_blockscaled: shape mismatch (K % 512 == 0, N % 128 == 0)")
+    if out is None:
+        out = torch.empty((M, N), dtype=torch.bfloat16, device=a_q.device)
+    rt._C().gemm_fp8_blockscaled(a_q.data_ptr(), a_scale.data_ptr(), b_q.data_ptr(), b_scale.data_ptr(),
+                                 out.data_ptr(), M, N, K, _stream(stream))
+    return out
+
+
+def grouped_gemm_fp8_blockscaled(a_q: torch.Tensor, a_scale: torch.Tensor, b_q: torch.Tensor, b_scale: torch.Tensor,
+                                 offsets: torch.Tensor, swiglu: bool = False, out: Optional[torch.Tensor] = None,
+                                 stream=None) -> torch.Tensor:
+    """Grouped form: rows ``offsets[g]:offsets[g+1]`` of ``a_q [rows, K]`` use ``b_q[g] [N, K]`` with
+    ``b_scale[g] [N/128, K/128]``; ``offsets`` int32 on the device. With ``swiglu`` (N a multiple of
+    256, gate rows first) the result is ``silu(gate) * up`` of width ``N / 2``."""
+    _check8(a_q, a_scale, "a")
+    _check8(b_q, b_scale, "b")
+    rows, K = a_q.shape
+    G, N, K2 = b_q.shape
+    if K != K2 or K % 512 or N % 128 or offsets.dtype != torch.int32 or offsets.numel() != G + 1:
+        raise ValueError("grouped_gemm_fp8_blockscaled: shape mismatch")
+    if out is None:
+        out = torch.empty((rows, N // 2 if swiglu else N), dtype=torch.bfloat16, device=a_q.device)
+    rt._C().grouped_gemm_fp8_blockscaled(a_q.data_ptr(), a_scale.data_ptr(), b_q.data_ptr(), b_scale.data_ptr(),
+                                         out.data_ptr(), offsets.data_ptr(), G, rows, N, K, int(swiglu),
+                                         _stream(stream))
+    return out
+
+
+def quantize_1x128_into(x: torch.Tensor, q: torch.Tensor, scales: torch.Tensor, stream=None) -> None:
+    """1 x 128 block-scaled e4m3 quantisation of ``x [rows, hidden]`` bf16 into caller-provided ``q``
+    (e4m3 / uint8, same shape) and ``scales [rows, hidden / 128]`` fp32 (e.g. symmetric-heap buffers)."""
+    rows, hidden = x.shape
+    rt._C().fp8_quantize_1x128(x.data_ptr(), q.data_ptr(), scales.data_ptr(), rows, hidden, _stream(stream))
+
+
+class TensorParallelLinearFp8:
+    """Block-scaled e4m3 versions of the fused tensor-parallel kernels (see :class:`TensorParallelLinear`).
+
+    Activations carry 1 x 128 scales and travel over NVLink as e4m3 (half the bytes of bf16); weights carry
+    128 x 128 scales (:func:`quantize_weight_128x128`). Outputs are bf16."""
+
+    def __init__(self, m_shard: int, team: Optional[rt.Team] = None, comm_blocks: int = 8):
+        if rt.n_local_pes() != 1:
+            raise RuntimeError("the fused tensor-parallel kernels need one PE per process")
+        self.team = team or rt.team_world()
+        self.n_ranks = self.team.n_pes()
+        self.m_shard = m_shard
+        self.comm_blocks = comm_blocks
+        self._ag = {}
+        self._rs = {}
+        self.kernel_launches = 0
+
+    def _ag_buffers(self, k: int):
+        if k not in self._ag:
+            M = self.n_ranks * self.m_shard
+            dev = rt.device()
+            self._ag[k] = [rt.zeros((self.m_shard, k), torch.uint8), rt.zeros((self.m_shard, k // 128), torch.float32),
+                           torch.zeros((M, k), dtype=torch.uint8, device=dev),
+                           torch.zeros((M, k // 128), dtype=torch.float32, device=dev),
+                           rt.zeros(max(16, M // 128), torch.int64), 0]
+        return self._ag[k]
+
+    def ag_input(self, k: int):
+        """The symmetric ``(e4m3 [m_shard, k] as uint8, scales [m_shard, k / 128])`` pair that holds this
+        rank's quantised activation shard."""
+        buf = self._ag_buffers(k)
+        return buf[0], buf[1]
+
+    def set_input(self, x_shard: torch.Tensor, stream=None) -> None:
+        """Quantises ``x_shard [m_shard, k]`` bf16 straight into :meth:`ag_input`."""
+        q, s = self.ag_input(x_shard.shape[1])
+        quantize_1x128_into(x_shard, q, s, stream)
+        self.kernel_launches += 1
+
+    def ag_gemm(self, w_q: torch.Tensor, w_s: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
+                stream=None) -> torch.Tensor:
+        N, K = w_q.shape
+        x_q, x_s, g_q, g_s, flags, _ = buf = self._ag_buffers(K)
+        buf[5] += 1
+        if out is None:
+            out = torch.empty((self.n_ranks * self.m_shard, N // 2 if swiglu else N), dtype=torch.bfloat16,
+                              device=w_q.device)
+        rt._C().ag_gemm_fp8(self.team.handle, x_q.data_ptr(), x_s.data_ptr(), g_q.data_ptr(), g_s.data_ptr(),
+                            flags.data_ptr(), w_q.data_ptr(), w_s.data_ptr(), out.data_ptr(), self.m_shard, N, K,
+                            buf[5], self.comm_blocks, int(swiglu), _stream(stream))
+        self.kernel_launches += 1
+        return out
+
+    def gemm_rs(self, a_q: torch.Tensor, a_s: torch.Tensor, w_q: torch.Tensor, w_s: torch.Tensor,
+                out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        N, K = w_q.shape
+        if a_q.shape[0] != self.n_ranks * self.m_shard or a_q.shape[1] != K:
+            raise ValueError("gemm_rs: a must be [n_ranks * m_shard, K_local]")
+        if N not in self._rs:
+            self._rs[N] = [rt.zeros((self.n_ranks, self.m_shard, N), torch.bfloat16), rt.zeros(16, torch.int64), 0]
+        entry = self._rs[N]
+        entry[2] += 1
+        if out is None:
+            out = torch.empty((self.m_shard, N), dtype=torch.bfloat16, device=a_q.device)
+        rt._C().gemm_rs_fp8(self.team.handle, a_q.data_ptr(), a_s.data_ptr(), w_q.data_ptr(), w_s.data_ptr(),
+                            entry[0].data_ptr(), out.data_ptr(), self.m_shard, N, K, entry[1].data_ptr(), entry[2],
+                            _stream(stream))
+        self.kernel_launches += 1
+        return out

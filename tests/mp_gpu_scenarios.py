@@ -282,6 +282,18 @@ def gpu_models():
         err = (out.float().cpu() - want).abs().max().item()
         assert err <= 2e-2 * want.abs().max().item() + 0.05, ("tp_mlp", rep, err)
         shm.barrier_all()
+    # -- TP MLP with block-scaled e4m3 GEMMs (e4m3 rows and their scales cross NVLink)
+    d_ff8 = 512 * n
+    mlp8 = tp_mlp.TensorParallelMLPFp8(d_model, d_ff8, m_shard, seed=8, comm_blocks=4)
+    want8 = tp_mlp.reference_forward_fp8(torch.cat(xs), n, d_model, d_ff8, seed=8)[me * m_shard:(me + 1) * m_shard]
+    for rep in range(2):
+        before = gemm.gemm_error_count()
+        out = mlp8(xs[me].to(dev))
+        _ok()
+        assert gemm.gemm_error_count() == before
+        err = (out.float().cpu() - want8).abs().max().item()
+        assert err <= 5e-2 * want8.abs().max().item() + 0.05, ("tp_mlp_fp8", rep, err)
+        shm.barrier_all()
     # -- MoE feed-forward
     E, K, H, I, T = 8 * n, 4, 1024, 512, 160 + 8 * me
     layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=256, seed=5)

@@ -87,3 +87,74 @@ def test_gemm_throughput_report(capsys):
     assert torch.allclose(c[:256].float(), ref.float(), rtol=2e-2, atol=1.0)
     with capsys.disabled():
         print(f"\n[gemm_bf16 {m}x{n}x{k}] {ms * 1e3:.1f} us, {2 * m * n * k / ms / 1e9:.0f} TFLOP/s")
+
+
+# ---- block-scaled fp8 ---------------------------------------------------------------------------------------------
+
+def _fp8_inputs(m, n, k, seed, groups=None):
+    from rocshmem_b200.ops import gemm, moe
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    a = (torch.randn(m, k, generator=g, device="cuda") * torch.rand(m, 1, generator=g, device="cuda") * 2).to(torch.bfloat16)
+    shape = (n, k) if groups is None else (groups, n, k)
+    b = (torch.randn(*shape, generator=g, device="cuda") * 0.3).to(torch.bfloat16)
+    a_q, a_s = moe.fp8_quantize_1x128(a)
+    b_q, b_s = gemm.quantize_weight_128x128(b)
+    a_deq = moe.ref_dequantize_1x128(a_q, a_s)
+    b_deq = gemm.dequantize_weight_128x128(b_q, b_s)
+    return a_q, a_s, b_q, b_s, a_deq, b_deq
+
+
+@pytest.mark.parametrize("m,n,k", [(128, 256, 512), (300, 384, 1024), (1024, 1280, 2048), (77, 128, 3584)])
+def test_gemm_fp8_blockscaled(m, n, k):
+    """Against fp32 matmul of the de-quantised operands: the only difference is summation order and
+    the bf16 rounding of the output."""
+    from rocshmem_b200.ops import gemm
+    a_q, a_s, b_q, b_s, a_deq, b_deq = _fp8_inputs(m, n, k, seed=m + n)
+    before = gemm.gemm_error_count()
+    c = gemm.gemm_fp8_blockscaled(a_q, a_s, b_q, b_s)
+    torch.cuda.synchronize()
+    assert gemm.gemm_error_count() == before, "a GEMM CTA hit its wait budget"
+    ok, err = close(c, a_deq @ b_deq.t(), k)
+    assert ok, f"max abs error {err}"
+
+
+def test_grouped_gemm_fp8_blockscaled():
+    from rocshmem_b200.ops import gemm
+    G, n, k = 5, 384, 1024
+    sizes = [200, 0, 128, 77, 300]
+    m = sum(sizes) + 9  # rows past offsets[-1] stay untouched
+    a_q, a_s, b_q, b_s, a_deq, b_deq = _fp8_inputs(m, n, k, seed=3, groups=G)
+    offsets = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
+    out = torch.full((m, n), 7.0, dtype=torch.bfloat16, device="cuda")
+    before = gemm.gemm_error_count()
+    gemm.grouped_gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, offsets, out=out)
+    torch.cuda.synchronize()
+    assert gemm.gemm_error_count() == before
+    lo = 0
+    for gi, sz in enumerate(sizes):
+        if sz:
+            ok, err = close(out[lo:lo + sz], a_deq[lo:lo + sz] @ b_deq[gi].t(), k)
+            assert ok, (gi, err)
+        lo += sz
+    assert torch.all(out[lo:] == 7.0)
+
+
+def test_grouped_gemm_fp8_swiglu():
+    from rocshmem_b200.ops import gemm
+    G, n, k = 3, 512, 1024   # 256 gate + 256 up rows per expert
+    sizes = [130, 256, 40]
+    m = sum(sizes)
+    a_q, a_s, b_q, b_s, a_deq, b_deq = _fp8_inputs(m, n, k, seed=5, groups=G)
+    offsets = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
+    before = gemm.gemm_error_count()
+    out = gemm.grouped_gemm_fp8_blockscaled(a_q, a_s, b_q, b_s, offsets, swiglu=True)
+    torch.cuda.synchronize()
+    assert gemm.gemm_error_count() == before
+    assert out.shape == (m, n // 2)
+    lo = 0
+    for gi, sz in enumerate(sizes):
+        hc = a_deq[lo:lo + sz] @ b_deq[gi].t()
+        want = torch.nn.functional.silu(hc[:, :n // 2]) * hc[:, n // 2:]
+        ok, err = close(out[lo:lo + sz], want, k)
+        assert ok, (gi, err)
+        lo += sz
