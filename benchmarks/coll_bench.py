@@ -54,6 +54,7 @@ def main():
     ap.add_argument("--out", default="gpurun_out/coll_bench.json")
     ap.add_argument("--max-bytes", type=int, default=512 << 20)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--only", default="allreduce,copies,rma", help="comma list of: allreduce, copies, rma")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -74,7 +75,8 @@ def main():
     shm.barrier_all()
     sizes = [1 << p for p in range(9, 40) if (1 << p) <= args.max_bytes]  # 512 B ... max
     busf = 2 * (world - 1) / world if world > 1 else 1.0
-    for nbytes in sizes:
+    only = set(args.only.split(","))
+    for nbytes in (sizes if "allreduce" in only else []):
         n = nbytes // esz
         iters = 50 if nbytes <= (1 << 20) else (10 if nbytes <= (64 << 20) else 4)
         row = {"bytes": nbytes}
@@ -95,7 +97,7 @@ def main():
     # all-gather / all-to-all / broadcast: per-peer payload 4 KiB ... 128 MiB (bounded by the buffers)
     per_peer = [1 << p for p in range(12, 28) if (1 << p) * world <= args.max_bytes]
     out_nccl = torch.empty(max_elems, dtype=dtype, device="cuda")
-    for nbytes in per_peer:
+    for nbytes in (per_peer if "copies" in only else []):
         n = nbytes // esz
         iters = 30 if nbytes <= (1 << 20) else 6
         for name, ours, theirs in (
@@ -114,7 +116,7 @@ def main():
             if rank == 0:
                 print(name, {kk: (round(v, 1) if isinstance(v, float) else v) for kk, v in row.items()}, flush=True)
     # put / get from PE 0 to PE 1 with the block-scope device API (device-timed inside the kernel)
-    if world >= 2:
+    if world >= 2 and "rma" in only:
         ns = shm.zeros(256, torch.int64)
         for nbytes in [1 << p for p in range(3, 27)]:
             for mode, name in ((0, "put_nbi_block+quiet"), (1, "get_block")):

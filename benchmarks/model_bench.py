@@ -86,6 +86,19 @@ def bench_tp_mlp(args, world, rank, res):
         "tflops_per_gpu": flops / t_fused / 1e6, "roofline_us": roof_us, "frac_of_roofline": roof_us / t_fused,
         "peak_source": src, "max_abs_diff_vs_baseline": err, "baseline_abs_max": scale,
         "gemm_errors": gemm.gemm_error_count()}
+    # How many CTAs the all-gather needs: fewer leave more SMs to the GEMM, too few starve it.
+    sweep = {}
+    for cb in (2, 4, 8, 16):
+        if cb == args.comm_blocks:
+            sweep[cb] = t_ag
+            continue
+        probe = tp_mlp.TensorParallelMLP(args.d_model, args.d_ff, m_shard, seed=1, comm_blocks=cb)
+        probe.input_buffer().copy_(x)
+        torch.cuda.synchronize()
+        shm.barrier_all()
+        sweep[cb] = timed(lambda: probe.tp.ag_gemm(probe.w_gate_up, out=probe.h, swiglu=True), max(3, args.iters // 2))
+        del probe
+    res["tp_mlp"]["ag_gemm_us_by_comm_blocks"] = sweep
     if args.d_model % 512 == 0 and ff % 512 == 0:
         mlp8 = tp_mlp.TensorParallelMLPFp8(args.d_model, args.d_ff, m_shard, seed=1, comm_blocks=min(8, args.comm_blocks))
         out8 = mlp8(x)
@@ -122,10 +135,16 @@ def bench_moe(args, world, rank, res):
         row["baseline_abs_max"] = ref.float().abs().max().item()
         row["nccl_cublas_us"] = timed(lambda: base(x, idx, w), max(2, args.iters // 2), warmup=2)
         row["speedup"] = row["nccl_cublas_us"] / t_layer
+    stages = {}
+    layer(x, idx, w, stage_us=stages)
+    row["stage_us_rank0"] = stages
     if H % 1024 == 0 and I % 512 == 0:
         layer8 = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=2, pair_capacity=cap, fp8_experts=True)
         out8 = layer8(x, idx, w)
         torch.cuda.synchronize()
+        stages8 = {}
+        layer8(x, idx, w, stage_us=stages8)
+        row["fp8_experts_stage_us_rank0"] = stages8
         row["fp8_experts_max_abs_diff_vs_bf16_experts"] = (out8.float() - out.float()).abs().max().item()
         row["fp8_experts_layer_us"] = timed(lambda: layer8(x, idx, w), args.iters)
         row["fp8_experts_tokens_per_s_all_ranks"] = world * T / row["fp8_experts_layer_us"] * 1e6
@@ -139,7 +158,7 @@ def main():
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--d-model", type=int, default=8192)
     ap.add_argument("--d-ff", type=int, default=28672)
-    ap.add_argument("--comm-blocks", type=int, default=16)
+    ap.add_argument("--comm-blocks", type=int, default=8)
     ap.add_argument("--experts", type=int, default=256)
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=7168)

@@ -72,39 +72,66 @@ class MoEFeedForward:
             self.h_s = torch.zeros((cap, inter // 128), dtype=torch.float32, device=dev)
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
-                out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+                out: Optional[torch.Tensor] = None, stream=None, stage_us: Optional[dict] = None) -> torch.Tensor:
         """x [T, hidden] bf16, topk_idx [T, top_k] int32 global expert ids (-1 = unused), topk_weights
-        [T, top_k] fp32. Returns [T, hidden] bf16: sum_k w_k * expert_k(x)."""
+        [T, top_k] fp32. Returns [T, hidden] bf16: sum_k w_k * expert_k(x).
+
+        With ``stage_us`` (a dict) the call synchronises and fills it with the device time of every stage in
+        microseconds (for profiling; the stages then run back to back without overlap of their launches)."""
         C = rt._C()
         d = self.d
         s = moe._stream(stream)
         before = d.kernel_launches
+        marks = []
+
+        def mark(name):
+            if stage_us is not None:
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+                marks.append((name, ev))
+
+        mark("start")
         d.dispatch(x, topk_idx, topk_weights, stream=stream)
+        mark("dispatch")
         offsets, row_index, pair_k = d.expert_layout(stream=stream)
         C.moe_inverse_map(offsets.data_ptr(), self.e_local, row_index.data_ptr(), pair_k.data_ptr(), self.top_k,
                           self.inverse.data_ptr(), s)
+        mark("layout")
         if self.fp8_experts:
             # Rows and their scales are copied as raw bytes (the gather kernel's 2-byte element view).
             C.moe_gather_rows(d.recv_x.data_ptr(), 0, 0, offsets.data_ptr(), self.e_local, row_index.data_ptr(),
                               self.hidden // 2, self.xs_q.data_ptr(), s)
             C.moe_gather_rows(d.recv_scales.data_ptr(), 0, 0, offsets.data_ptr(), self.e_local,
                               row_index.data_ptr(), self.hidden // 128 * 2, self.xs_s.data_ptr(), s)
+            mark("gather")
             gemm.grouped_gemm_fp8_blockscaled(self.xs_q, self.xs_s, self.w13_q, self.w13_s, offsets, swiglu=True,
                                               out=self.h, stream=stream)
+            mark("gemm_gate_up")
             gemm.quantize_1x128_into(self.h, self.h_q, self.h_s, stream)
+            mark("quantize_hidden")
             gemm.grouped_gemm_fp8_blockscaled(self.h_q, self.h_s, self.w2_q, self.w2_s, offsets, out=self.yp,
                                               stream=stream)
+            mark("gemm_down")
             self.kernel_launches += 2
         else:
             C.moe_gather_rows(d.recv_x.data_ptr(), d.recv_scales.data_ptr(), int(d.quantize), offsets.data_ptr(),
                               self.e_local, row_index.data_ptr(), self.hidden, self.xs.data_ptr(), s)
+            mark("gather")
             gemm.grouped_gemm_bf16(self.xs, self.w13, offsets, swiglu=True, out=self.h, stream=stream)
+            mark("gemm_gate_up")
             gemm.grouped_gemm_bf16(self.h, self.w2, offsets, out=self.yp, stream=stream)
+            mark("gemm_down")
         y = d.result_buffer()
         C.moe_reduce_pairs(self.yp.data_ptr(), self.inverse.data_ptr(), d.recv_meta.data_ptr(),
                            d.recv_info.data_ptr(), self.n_ranks, self.top_k, self.hidden, 1, y.data_ptr(), s)
+        mark("reduce_pairs")
         out = d.combine(y, topk_idx, topk_weights, x.shape[0], weighted=False, out=out, stream=stream)
+        mark("combine")
         self.kernel_launches += (d.kernel_launches - before) + 5
+        if stage_us is not None:
+            torch.cuda.synchronize()
+            for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                stage_us[name] = a.elapsed_time(b) * 1e3
         return out
 
     __call__ = forward

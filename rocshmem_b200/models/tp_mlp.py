@@ -33,7 +33,7 @@ def mlp_weights(rank: int, n_ranks: int, d_model: int, d_ff: int, seed: int = 0,
 
 class TensorParallelMLP:
     def __init__(self, d_model: int, d_ff: int, m_shard: int, team: Optional[rt.Team] = None, seed: int = 0,
-                 comm_blocks: int = 16):
+                 comm_blocks: int = 8):
         self.tp = TensorParallelLinear(m_shard, team=team, comm_blocks=comm_blocks)
         P = self.tp.n_ranks
         if d_ff % P:

@@ -77,7 +77,7 @@ class TensorParallelLinear:
       the rank keeps rows ``[rank * m_shard, (rank + 1) * m_shard)`` of the sum.
     """
 
-    def __init__(self, m_shard: int, team: Optional[rt.Team] = None, comm_blocks: int = 16):
+    def __init__(self, m_shard: int, team: Optional[rt.Team] = None, comm_blocks: int = 8):
         if rt.n_local_pes() != 1:
             raise RuntimeError("the fused tensor-parallel kernels need one PE per process")
         self.team = team or rt.team_world()
