@@ -60,7 +60,7 @@ def peaks():
 
 def bench_tp_mlp(args, world, rank, res):
     m_shard = args.tokens // world
-    mlp = tp_mlp.TensorParallelMLP(args.d_model, args.d_ff, m_shard, seed=1, comm_blocks=args.comm_blocks)
+    mlp = tp_mlp.TensorParallelMLP(args.d_model, args.d_ff, m_shard, seed=1)
     base = baselines.NcclTensorParallelMLP(args.d_model, args.d_ff, m_shard, seed=1)
     x = (torch.randn(m_shard, args.d_model, device="cuda") * 0.5).to(torch.bfloat16)
     mlp.input_buffer().copy_(x)
@@ -86,21 +86,8 @@ def bench_tp_mlp(args, world, rank, res):
         "tflops_per_gpu": flops / t_fused / 1e6, "roofline_us": roof_us, "frac_of_roofline": roof_us / t_fused,
         "peak_source": src, "max_abs_diff_vs_baseline": err, "baseline_abs_max": scale,
         "gemm_errors": gemm.gemm_error_count()}
-    # How many CTAs the all-gather needs: fewer leave more SMs to the GEMM, too few starve it.
-    sweep = {}
-    for cb in (2, 4, 8, 16):
-        if cb == args.comm_blocks:
-            sweep[cb] = t_ag
-            continue
-        probe = tp_mlp.TensorParallelMLP(args.d_model, args.d_ff, m_shard, seed=1, comm_blocks=cb)
-        probe.input_buffer().copy_(x)
-        torch.cuda.synchronize()
-        shm.barrier_all()
-        sweep[cb] = timed(lambda: probe.tp.ag_gemm(probe.w_gate_up, out=probe.h, swiglu=True), max(3, args.iters // 2))
-        del probe
-    res["tp_mlp"]["ag_gemm_us_by_comm_blocks"] = sweep
     if args.d_model % 512 == 0 and ff % 512 == 0:
-        mlp8 = tp_mlp.TensorParallelMLPFp8(args.d_model, args.d_ff, m_shard, seed=1, comm_blocks=min(8, args.comm_blocks))
+        mlp8 = tp_mlp.TensorParallelMLPFp8(args.d_model, args.d_ff, m_shard, seed=1)
         out8 = mlp8(x)
         torch.cuda.synchronize()
         err8 = (out8.float() - ref.float()).abs().max().item()
@@ -158,7 +145,6 @@ def main():
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--d-model", type=int, default=8192)
     ap.add_argument("--d-ff", type=int, default=28672)
-    ap.add_argument("--comm-blocks", type=int, default=8)
     ap.add_argument("--experts", type=int, default=256)
     ap.add_argument("--top-k", type=int, default=8)
     ap.add_argument("--hidden", type=int, default=7168)

@@ -43,18 +43,17 @@ void bind_gemm(py::module_ &m) {
           "grouped_gemm_fp8_blockscaled");
   });
   m.def("ag_gemm_bf16", [](uintptr_t team, uintptr_t x, uintptr_t gathered, uintptr_t flags, uintptr_t b, uintptr_t c,
-                           int m_shard, int N, int K, unsigned epoch, int comm_blocks, int swiglu,
-                           uintptr_t stream) {
+                           int m_shard, int N, int K, unsigned epoch, int swiglu, uintptr_t stream) {
     check(ag_gemm_bf16(reinterpret_cast<rocshmem_team_t>(team), P<void>(x), P<void>(gathered),
-                       P<unsigned long long>(flags), P<void>(b), P<void>(c), m_shard, N, K, epoch, comm_blocks,
-                       swiglu, P<void>(stream)), "ag_gemm_bf16");
+                       P<unsigned long long>(flags), P<void>(b), P<void>(c), m_shard, N, K, epoch, swiglu,
+                       P<void>(stream)), "ag_gemm_bf16");
   });
   m.def("ag_gemm_fp8", [](uintptr_t team, uintptr_t x_q, uintptr_t x_s, uintptr_t gq, uintptr_t gs, uintptr_t flags,
                           uintptr_t b_q, uintptr_t b_s, uintptr_t c, int m_shard, int N, int K, unsigned epoch,
-                          int comm_blocks, int swiglu, uintptr_t stream) {
+                          int swiglu, uintptr_t stream) {
     check(ag_gemm_fp8(reinterpret_cast<rocshmem_team_t>(team), P<void>(x_q), P<float>(x_s), P<void>(gq), P<float>(gs),
                       P<unsigned long long>(flags), P<void>(b_q), P<float>(b_s), P<void>(c), m_shard, N, K, epoch,
-                      comm_blocks, swiglu, P<void>(stream)), "ag_gemm_fp8");
+                      swiglu, P<void>(stream)), "ag_gemm_fp8");
   });
   m.def("gemm_rs_fp8", [](uintptr_t team, uintptr_t a_q, uintptr_t a_s, uintptr_t b_q, uintptr_t b_s,
                           uintptr_t staging, uintptr_t out, int m_shard, int N, int K, uintptr_t counter,

@@ -29,7 +29,10 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * SLAB_BYTES;        // 16 KiB
 constexpr int B_STAGE_BYTES = BN * SLAB_BYTES;        // 32 KiB
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;  // + slack for 1024-byte alignment
+constexpr int EPI_COLS = 64;                            // output columns staged per step
+constexpr int EPI_ROW_BYTES = EPI_COLS * 2 + 16;        // padded: conflict-free 16-byte accesses
+constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;      // one staging area per epilogue warp
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * EPI_WARP_BYTES + 1024;  // + slack for 1024-byte alignment
 constexpr int THREADS = 192;
 constexpr int TMEM_COLS = 512;     // two accumulators of 256 fp32 columns
 constexpr unsigned long long WAIT_BUDGET_NS = 2000000000ull;  // 2 s per wait
@@ -71,8 +74,10 @@ struct Shared {
 
 __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x)); }
 
-// Scheduler: struct with  __device__ bool get(int iter, Tile &t)  (false: no more tiles for this CTA)
-//            and          __device__ bool ready(const Tile &t)    (producer-side hook, bounded; false aborts).
+// Scheduler: struct with  __device__ bool get(int iter, Tile &t)  (false: no more tiles for this CTA),
+//                         __device__ bool ready(const Tile &t)    (producer-side hook, bounded; false aborts)
+//            and          __device__ void side_role()             (run by warps beyond the six of the GEMM,
+//                                                                  if the kernel is launched with any).
 // Epilogue:  struct with  __device__ __nv_bfloat16 *row_ptr(const Tile &t, int row_in_tile)
 //            returning the address of output element (row, t.c_col), or nullptr to skip the row.
 template <bool IS_FP8, bool SWIGLU, class Scheduler, class Epilogue>
@@ -159,51 +164,74 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         sm100::mma_commit(&sh.tmem_full[acc]);  // accumulator complete
       }
     }
+  } else if (warp >= 6) {
+    // ---- optional extra warps (kernels launched with more than THREADS threads) ------------------------------
+    sched.side_role();
   } else {
     // ---- epilogue -------------------------------------------------------------------------------------------
+    // A thread receives one accumulator row from TMEM. Stores of one row per thread would scatter 16-byte
+    // pieces over 32 rows per instruction (costly for local memory, ruinous over NVLink), so every warp
+    // passes 64 output columns at a time through its own padded staging rows in shared memory and writes
+    // them out with 8 lanes per row: 128 contiguous bytes per row, 4 rows per instruction.
     const int quarter = warp & 3;  // TMEM lanes [32 * quarter, +32) belong to this warp
+    unsigned char *stg = smem + STAGES * STAGE_BYTES + (warp - 2) * EPI_WARP_BYTES;
     Tile t;
     for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
       const int acc = iter & 1;
       const uint32_t acc_phase = (iter >> 1) & 1u;
       if (!sm100::mbar_wait(&sh.tmem_full[acc], acc_phase, &sh.abort_flag, WAIT_BUDGET_NS)) break;
       sm100::tcgen05_fence_after();
-      const int row = quarter * 32 + lane;
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
-      __nv_bfloat16 *out = (row < t.rows) ? epi.row_ptr(t, row) : nullptr;
-      constexpr int CHUNKS = SWIGLU ? BN / 64 : BN / 32;
+      constexpr int OUT_CHUNKS = (SWIGLU ? BN / 2 : BN) / EPI_COLS;
 #pragma unroll 1
-      for (int c = 0; c < CHUNKS; ++c) {
-        uint32_t v[32];
-        sm100::tmem_ld_32x32(taddr + c * 32, v);
-        float f[32];
-        if (SWIGLU) {
-          uint32_t u[32];
-          sm100::tmem_ld_32x32(taddr + BN / 2 + c * 32, u);
-          sm100::tmem_ld_wait();
+      for (int c = 0; c < OUT_CHUNKS; ++c) {
+        if (c * EPI_COLS >= t.cols) break;
 #pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = silu(__uint_as_float(v[i])) * __uint_as_float(u[i]);
-        } else {
-          sm100::tmem_ld_wait();
+        for (int h = 0; h < EPI_COLS / 32; ++h) {
+          uint32_t v[32];
+          float f[32];
+          sm100::tmem_ld_32x32(taddr + c * EPI_COLS + h * 32, v);
+          if (SWIGLU) {
+            uint32_t u[32];
+            sm100::tmem_ld_32x32(taddr + BN / 2 + c * EPI_COLS + h * 32, u);
+            sm100::tmem_ld_wait();
 #pragma unroll
-          for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
-        }
-        const int col = c * 32;
-        if (out != nullptr && col < t.cols) {
-          __nv_bfloat16 *dst = out + col;
-          if (col + 32 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-#pragma unroll
-            for (int q = 0; q < 4; ++q) {
-              int4 pk;
-              __nv_bfloat162 *p2 = reinterpret_cast<__nv_bfloat162 *>(&pk);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) p2[i] = __floats2bfloat162_rn(f[q * 8 + 2 * i], f[q * 8 + 2 * i + 1]);
-              reinterpret_cast<int4 *>(dst)[q] = pk;
-            }
+            for (int i = 0; i < 32; ++i) f[i] = silu(__uint_as_float(v[i])) * __uint_as_float(u[i]);
           } else {
-            for (int i = 0; i < 32 && col + i < t.cols; ++i) dst[i] = __float2bfloat16_rn(f[i]);
+            sm100::tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+          }
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            int4 pk;
+            __nv_bfloat162 *p2 = reinterpret_cast<__nv_bfloat162 *>(&pk);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) p2[i] = __floats2bfloat162_rn(f[q * 8 + 2 * i], f[q * 8 + 2 * i + 1]);
+            *reinterpret_cast<int4 *>(stg + lane * EPI_ROW_BYTES + h * 64 + q * 16) = pk;
           }
         }
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 8; ++it) {
+          const int r = it * 4 + lane / 8, seg = lane % 8;
+          const int row = quarter * 32 + r;
+          const int col = c * EPI_COLS + seg * 8;
+          if (row < t.rows && col < t.cols) {
+            __nv_bfloat16 *out = epi.row_ptr(t, row);
+            if (out != nullptr) {
+              const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
+              __nv_bfloat16 *dst = out + col;
+              if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(src);
+              } else {
+                const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
+                for (int i = 0; i < 8 && col + i < t.cols; ++i) dst[i] = s16[i];
+              }
+            }
+          }
+        }
+        __syncwarp();
       }
       sm100::tcgen05_fence_before();
       __syncwarp();

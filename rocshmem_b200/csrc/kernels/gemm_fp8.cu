@@ -31,6 +31,7 @@ struct PlainScheduler8 {
     return true;
   }
   __device__ bool ready(const gemm::Tile &) const { return true; }
+  __device__ void side_role() const {}
 };
 
 struct RowMajorEpilogue8 {
@@ -92,6 +93,7 @@ struct GroupedScheduler8 {
     return false;
   }
   __device__ bool ready(const gemm::Tile &) const { return true; }
+  __device__ void side_role() const {}
 };
 
 template <bool SWIGLU>

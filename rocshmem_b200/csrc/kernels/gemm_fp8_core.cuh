@@ -29,8 +29,10 @@ constexpr int STAGES = 4;
 constexpr int A_STAGE_BYTES = BM * KB;
 constexpr int B_STAGE_BYTES = BN * KB;
 constexpr int STAGE_BYTES = A_STAGE_BYTES + B_STAGE_BYTES;
-constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;
 constexpr int ACC_WARPS = 8;
+constexpr int EPI_ROW_BYTES = 32 * 2 + 16;              // 32 staged bf16 columns per row, padded
+constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + ACC_WARPS * EPI_WARP_BYTES + 1024;
 constexpr int THREADS = 64 + ACC_WARPS * 32;
 constexpr int TMEM_COLS = 512;
 constexpr unsigned long long WAIT_BUDGET_NS = gemm::WAIT_BUDGET_NS;
@@ -124,6 +126,8 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         if (sh.abort_flag) break;
       }
     }
+  } else if (warp >= 2 + ACC_WARPS) {
+    sched.side_role();  // optional extra warps (kernels launched with more than THREADS threads)
   } else {
     const int aw = warp - 2;           // 0..7
     const int quarter = warp & 3;      // TMEM lanes [32 * quarter, +32) are accessible to this warp
@@ -180,31 +184,46 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         }
       }
       if (sh.abort_flag) break;
-      __nv_bfloat16 *out = row_ok ? epi.row_ptr(t, row) : nullptr;
       constexpr int OUT = SWIGLU ? 64 : 128;   // output columns per thread
       if (SWIGLU) {
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = gemm::silu(acc[i]) * acc[64 + i];
       }
+      // Write-out through the warp's padded staging rows, 32 columns at a time: 4 lanes per row write 64
+      // contiguous bytes, 8 rows per instruction (instead of one row per thread in 16-byte pieces).
       const int col0 = half * OUT;
-      if (out != nullptr && col0 < t.cols) {
-        __nv_bfloat16 *dst = out + col0;
-        const int n_ok = min(OUT, t.cols - col0);
-        if (n_ok == OUT && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      unsigned char *stg = smem + STAGES * STAGE_BYTES + aw * EPI_WARP_BYTES;
 #pragma unroll
-          for (int q = 0; q < OUT / 8; ++q) {
-            int4 pk;
-            __nv_bfloat162 *p2 = reinterpret_cast<__nv_bfloat162 *>(&pk);
+      for (int c = 0; c < OUT / 32; ++c) {
 #pragma unroll
-            for (int i = 0; i < 4; ++i) p2[i] = __floats2bfloat162_rn(acc[q * 8 + 2 * i], acc[q * 8 + 2 * i + 1]);
-            reinterpret_cast<int4 *>(dst)[q] = pk;
-          }
-        } else {
+        for (int q = 0; q < 4; ++q) {
+          int4 pk;
+          __nv_bfloat162 *p2 = reinterpret_cast<__nv_bfloat162 *>(&pk);
 #pragma unroll
-          for (int i = 0; i < OUT; ++i) {
-            if (i < n_ok) dst[i] = __float2bfloat16_rn(acc[i]);
+          for (int i = 0; i < 4; ++i) p2[i] = __floats2bfloat162_rn(acc[c * 32 + q * 8 + 2 * i], acc[c * 32 + q * 8 + 2 * i + 1]);
+          *reinterpret_cast<int4 *>(stg + lane * EPI_ROW_BYTES + q * 16) = pk;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int r = it * 8 + lane / 4, seg = lane % 4;
+          const int orow = quarter * 32 + r;
+          const int col = col0 + c * 32 + seg * 8;
+          if (orow < t.rows && col < t.cols) {
+            __nv_bfloat16 *out = epi.row_ptr(t, orow);
+            if (out != nullptr) {
+              const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
+              __nv_bfloat16 *dst = out + col;
+              if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(src);
+              } else {
+                const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
+                for (int i = 0; i < 8 && col + i < t.cols; ++i) dst[i] = s16[i];
+              }
+            }
           }
         }
+        __syncwarp();
       }
     }
   }

@@ -50,6 +50,7 @@ struct PlainScheduler {
     return true;
   }
   __device__ bool ready(const gemm::Tile &) const { return true; }
+  __device__ void side_role() const {}
 };
 
 struct RowMajorEpilogue {
@@ -112,6 +113,7 @@ struct GroupedScheduler {
     return false;
   }
   __device__ bool ready(const gemm::Tile &) const { return true; }
+  __device__ void side_role() const {}
 };
 
 template <bool SWIGLU>

@@ -45,11 +45,10 @@ int grouped_gemm_fp8_blockscaled(const void *a_q, const float *a_scale, const vo
 // Tensor-parallel fused kernels on the symmetric heap (fused_kernels.cu).
 // All-gather -> GEMM: every rank holds x_shard [m_shard, K] (symmetric); computes
 // C[n_ranks * m_shard, N] = concat_ranks(x_shard) * B^T with its local B [N, K]. `gathered` is a
-// symmetric scratch [n_ranks * m_shard, K] that receives the shards; `flags` one u64 per rank
-// (symmetric, zero-initialised once), `epoch` increases by one per call.
+// symmetric scratch [n_ranks * m_shard, K] into which every member pushes its shard; `flags` holds one
+// 32-bit counter per 128-row block (symmetric, zero-initialised once), `epoch` increases by one per call.
 int ag_gemm_bf16(rocshmem_team_t team, const void *x_shard, void *gathered, unsigned long long *flags,
-                 const void *b, void *c, int m_shard, int n, int k, unsigned epoch, int comm_blocks,
-                 int swiglu, void *stream);
+                 const void *b, void *c, int m_shard, int n, int k, unsigned epoch, int swiglu, void *stream);
 // GEMM -> reduce-scatter: partial[M, N] = A[M, K_local] * B[N, K_local]^T is produced tile by tile and
 // every tile is stored into the staging buffer of the rank that owns its rows
 // (`staging` symmetric [n_ranks][m_shard, N] bf16); the owner then sums the n_ranks contributions into
@@ -59,11 +58,11 @@ int gemm_rs_bf16(rocshmem_team_t team, const void *a, const void *b, void *stagi
                  int n, int k, unsigned long long *grid_counter, unsigned epoch, void *stream);
 
 // Block-scaled e4m3 forms of the two fused kernels. x_q [m_shard, K] e4m3 and x_s [m_shard, K / 128] fp32 are
-// symmetric; gathered_q / gathered_s are local buffers for all n_ranks shards; b_q [N, K] with b_scale
+// the rank's quantised shard; gathered_q / gathered_s are symmetric buffers for all n_ranks shards; b_q [N, K] with b_scale
 // [N / 128, K / 128]. K must be a multiple of 512, N of 128 (256 with swiglu).
 int ag_gemm_fp8(rocshmem_team_t team, const void *x_q, const float *x_s, void *gathered_q, float *gathered_s,
                 unsigned long long *flags, const void *b_q, const float *b_scale, void *c, int m_shard, int n, int k,
-                unsigned epoch, int comm_blocks, int swiglu, void *stream);
+                unsigned epoch, int swiglu, void *stream);
 int gemm_rs_fp8(rocshmem_team_t team, const void *a_q, const float *a_scale, const void *b_q, const float *b_scale,
                 void *staging, void *out, int m_shard, int n, int k, unsigned long long *grid_counter, unsigned epoch,
                 void *stream);

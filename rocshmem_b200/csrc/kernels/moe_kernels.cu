@@ -86,32 +86,49 @@ __global__ void reduce_pairs_kernel(const __nv_bfloat16 *pairs, const int *inver
         pos[k] = live ? inverse[row * top_k + k] : -1;
         w[k] = live ? (weighted ? __int_as_float(meta[EP_META_WEIGHT + k]) : 1.0f) : 0.f;
       }
-      for (int v = lane; v < hidden / 8; v += 32) {
-        float acc[8];
+      // Two 16-byte columns per lane and step: twice the loads in flight (the kernel is latency-bound,
+      // a row has one or two live sources on average).
+      const int nvec = hidden / 8;
+      for (int v0 = lane; v0 < nvec; v0 += 64) {
+        const int v1 = v0 + 32;
+        const bool two = v1 < nvec;
+        float acc[2][8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-        int4 raw[EP_MAX_TOPK];
+        for (int i = 0; i < 8; ++i) acc[0][i] = acc[1][i] = 0.f;
+        int4 raw[2][EP_MAX_TOPK];
 #pragma unroll
         for (int k = 0; k < EP_MAX_TOPK; ++k) {
-          if (pos[k] >= 0) raw[k] = reinterpret_cast<const int4 *>(pairs + size_t(pos[k]) * hidden)[v];
+          if (pos[k] >= 0) {
+            const int4 *src = reinterpret_cast<const int4 *>(pairs + size_t(pos[k]) * hidden);
+            raw[0][k] = src[v0];
+            if (two) raw[1][k] = src[v1];
+          }
         }
 #pragma unroll
         for (int k = 0; k < EP_MAX_TOPK; ++k) {
           if (pos[k] >= 0) {
-            const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[k]);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(p2[i]);
-              acc[2 * i] += w[k] * f.x;
-              acc[2 * i + 1] += w[k] * f.y;
+            for (int u = 0; u < 2; ++u) {
+              if (u == 1 && !two) continue;
+              const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&raw[u][k]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p2[i]);
+                acc[u][2 * i] += w[k] * f.x;
+                acc[u][2 * i + 1] += w[k] * f.y;
+              }
             }
           }
         }
-        int4 o;
-        __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&o);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        reinterpret_cast<int4 *>(y + size_t(row) * hidden)[v] = o;
+        for (int u = 0; u < 2; ++u) {
+          if (u == 1 && !two) continue;
+          int4 o;
+          __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&o);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[u][2 * i], acc[u][2 * i + 1]);
+          reinterpret_cast<int4 *>(y + size_t(row) * hidden)[u ? v1 : v0] = o;
+        }
       }
     }
   }

@@ -32,9 +32,8 @@ def mlp_weights(rank: int, n_ranks: int, d_model: int, d_ff: int, seed: int = 0,
 
 
 class TensorParallelMLP:
-    def __init__(self, d_model: int, d_ff: int, m_shard: int, team: Optional[rt.Team] = None, seed: int = 0,
-                 comm_blocks: int = 8):
-        self.tp = TensorParallelLinear(m_shard, team=team, comm_blocks=comm_blocks)
+    def __init__(self, d_model: int, d_ff: int, m_shard: int, team: Optional[rt.Team] = None, seed: int = 0):
+        self.tp = TensorParallelLinear(m_shard, team=team)
         P = self.tp.n_ranks
         if d_ff % P:
             raise ValueError("d_ff must be divisible by the team size")
@@ -69,9 +68,8 @@ class TensorParallelMLPFp8:
     the all-gather, the hidden activation before the down projection), weights 128 x 128. Four kernels per
     forward: quantise, all-gather -> GEMM -> SwiGLU, quantise, GEMM -> reduce-scatter."""
 
-    def __init__(self, d_model: int, d_ff: int, m_shard: int, team: Optional[rt.Team] = None, seed: int = 0,
-                 comm_blocks: int = 8):
-        self.tp = gemm.TensorParallelLinearFp8(m_shard, team=team, comm_blocks=comm_blocks)
+    def __init__(self, d_model: int, d_ff: int, m_shard: int, team: Optional[rt.Team] = None, seed: int = 0):
+        self.tp = gemm.TensorParallelLinearFp8(m_shard, team=team)
         P = self.tp.n_ranks
         if d_ff % P or (d_ff // P) % 512 or d_model % 512:
             raise ValueError("d_model and d_ff / n_ranks must be multiples of 512")

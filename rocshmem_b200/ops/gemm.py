@@ -77,13 +77,12 @@ class TensorParallelLinear:
       the rank keeps rows ``[rank * m_shard, (rank + 1) * m_shard)`` of the sum.
     """
 
-    def __init__(self, m_shard: int, team: Optional[rt.Team] = None, comm_blocks: int = 8):
+    def __init__(self, m_shard: int, team: Optional[rt.Team] = None):
         if rt.n_local_pes() != 1:
             raise RuntimeError("the fused tensor-parallel kernels need one PE per process")
         self.team = team or rt.team_world()
         self.n_ranks = self.team.n_pes()
         self.m_shard = m_shard
-        self.comm_blocks = comm_blocks
         self._ag = {}
         self._rs = {}
         self.kernel_launches = 0
@@ -115,8 +114,7 @@ class TensorParallelLinear:
             out = torch.empty((self.n_ranks * self.m_shard, N // 2 if swiglu else N), dtype=torch.bfloat16,
                               device=w.device)
         rt._C().ag_gemm_bf16(self.team.handle, x.data_ptr(), gathered.data_ptr(), flags.data_ptr(), w.data_ptr(),
-                             out.data_ptr(), self.m_shard, N, K, buf[3], self.comm_blocks, int(swiglu),
-                             _stream(stream))
+                             out.data_ptr(), self.m_shard, N, K, buf[3], int(swiglu), _stream(stream))
         self.kernel_launches += 1
         return out
 
@@ -221,13 +219,12 @@ class TensorParallelLinearFp8:
     Activations carry 1 x 128 scales and travel over NVLink as e4m3 (half the bytes of bf16); weights carry
     128 x 128 scales (:func:`quantize_weight_128x128`). Outputs are bf16."""
 
-    def __init__(self, m_shard: int, team: Optional[rt.Team] = None, comm_blocks: int = 8):
+    def __init__(self, m_shard: int, team: Optional[rt.Team] = None):
         if rt.n_local_pes() != 1:
             raise RuntimeError("the fused tensor-parallel kernels need one PE per process")
         self.team = team or rt.team_world()
         self.n_ranks = self.team.n_pes()
         self.m_shard = m_shard
-        self.comm_blocks = comm_blocks
         self._ag = {}
         self._rs = {}
         self.kernel_launches = 0
@@ -235,10 +232,8 @@ class TensorParallelLinearFp8:
     def _ag_buffers(self, k: int):
         if k not in self._ag:
             M = self.n_ranks * self.m_shard
-            dev = rt.device()
             self._ag[k] = [rt.zeros((self.m_shard, k), torch.uint8), rt.zeros((self.m_shard, k // 128), torch.float32),
-                           torch.zeros((M, k), dtype=torch.uint8, device=dev),
-                           torch.zeros((M, k // 128), dtype=torch.float32, device=dev),
+                           rt.zeros((M, k), torch.uint8), rt.zeros((M, k // 128), torch.float32),
                            rt.zeros(max(16, M // 128), torch.int64), 0]
         return self._ag[k]
 
@@ -264,7 +259,7 @@ class TensorParallelLinearFp8:
                               device=w_q.device)
         rt._C().ag_gemm_fp8(self.team.handle, x_q.data_ptr(), x_s.data_ptr(), g_q.data_ptr(), g_s.data_ptr(),
                             flags.data_ptr(), w_q.data_ptr(), w_s.data_ptr(), out.data_ptr(), self.m_shard, N, K,
-                            buf[5], self.comm_blocks, int(swiglu), _stream(stream))
+                            buf[5], int(swiglu), _stream(stream))
         self.kernel_launches += 1
         return out
 

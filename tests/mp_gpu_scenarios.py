@@ -221,7 +221,7 @@ def gpu_tp_fused():
     me, n = RANK, WORLD
     dev = shm.device()
     for m_shard, K, N in ((128, 512, 256), (256, 1024, 1000 // 8 * 8), (384, 2048, 1792)):
-        tp = gemm.TensorParallelLinear(m_shard, comm_blocks=4)
+        tp = gemm.TensorParallelLinear(m_shard)
         xs = []
         for p in range(n):
             g = torch.Generator().manual_seed(11 * p + m_shard)
@@ -270,7 +270,7 @@ def gpu_models():
     dev = shm.device()
     # -- TP MLP
     d_model, d_ff, m_shard = 1024, 512 * n, 256
-    mlp = tp_mlp.TensorParallelMLP(d_model, d_ff, m_shard, seed=3, comm_blocks=4)
+    mlp = tp_mlp.TensorParallelMLP(d_model, d_ff, m_shard, seed=3)
     xs = [(torch.randn(m_shard, d_model, generator=torch.Generator().manual_seed(40 + p)) * 0.5).to(torch.bfloat16)
           for p in range(n)]
     want = tp_mlp.reference_forward(torch.cat(xs), n, d_model, d_ff, seed=3)[me * m_shard:(me + 1) * m_shard]
@@ -284,7 +284,7 @@ def gpu_models():
         shm.barrier_all()
     # -- TP MLP with block-scaled e4m3 GEMMs (e4m3 rows and their scales cross NVLink)
     d_ff8 = 512 * n
-    mlp8 = tp_mlp.TensorParallelMLPFp8(d_model, d_ff8, m_shard, seed=8, comm_blocks=4)
+    mlp8 = tp_mlp.TensorParallelMLPFp8(d_model, d_ff8, m_shard, seed=8)
     want8 = tp_mlp.reference_forward_fp8(torch.cat(xs), n, d_model, d_ff8, seed=8)[me * m_shard:(me + 1) * m_shard]
     for rep in range(2):
         before = gemm.gemm_error_count()

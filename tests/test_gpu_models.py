@@ -47,7 +47,7 @@ def test_moe_feed_forward(shm, quantize, E, K, H, I, T):
 def test_tp_mlp_single_rank(shm, d_model, d_ff, m):
     from rocshmem_b200.models import tp_mlp
     from rocshmem_b200.ops import gemm
-    mlp = tp_mlp.TensorParallelMLP(d_model, d_ff, m, seed=4, comm_blocks=4)
+    mlp = tp_mlp.TensorParallelMLP(d_model, d_ff, m, seed=4)
     x = (torch.randn(m, d_model, generator=torch.Generator().manual_seed(9)) * 0.5).to(torch.bfloat16)
     want = tp_mlp.reference_forward(x, 1, d_model, d_ff, seed=4)
     for rep in range(2):
@@ -82,7 +82,7 @@ def test_moe_feed_forward_fp8_experts(shm):
 def test_tp_mlp_fp8_single_rank(shm, d_model, d_ff, m):
     from rocshmem_b200.models import tp_mlp
     from rocshmem_b200.ops import gemm
-    mlp = tp_mlp.TensorParallelMLPFp8(d_model, d_ff, m, seed=4, comm_blocks=4)
+    mlp = tp_mlp.TensorParallelMLPFp8(d_model, d_ff, m, seed=4)
     x = (torch.randn(m, d_model, generator=torch.Generator().manual_seed(9)) * 0.5).to(torch.bfloat16)
     want = tp_mlp.reference_forward_fp8(x, 1, d_model, d_ff, seed=4)
     for rep in range(2):
