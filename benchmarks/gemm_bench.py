@@ -3,6 +3,7 @@
 
     python benchmarks/gemm_bench.py --out gpurun_out/gemm_bench.json          # the table
     python benchmarks/gemm_bench.py --profile                                   # one small shape, few launches
+    python benchmarks/gemm_bench.py --profile-fp8                               # the same for the e4m3 kernel
     ncu --set full --clock-control none -k regex:gemm_bf16_kernel -c 2 -o gpurun_out/gemm \
         python benchmarks/gemm_bench.py --profile
 
@@ -56,6 +57,7 @@ def main():
     ap.add_argument("--out", default="")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--profile", action="store_true")
+    ap.add_argument("--profile-fp8", action="store_true")
     args = ap.parse_args()
     torch.cuda.set_device(0)
     dev = "cuda"
@@ -68,6 +70,19 @@ def main():
         torch.cuda.synchronize()
         assert gemm.gemm_error_count() == 0
         print("profile run done", float(c[0, 0]))
+        return
+    if args.profile_fp8:
+        from rocshmem_b200.ops import moe
+        m, n, k = 4096, 4096, 8192
+        a = (torch.randn(m, k, device=dev) * 0.5).to(torch.bfloat16)
+        b = (torch.randn(n, k, device=dev) * 0.5).to(torch.bfloat16)
+        a_q, a_s = moe.fp8_quantize_1x128(a)
+        b_q, b_s = gemm.quantize_weight_128x128(b)
+        for _ in range(3):
+            c = gemm.gemm_fp8_blockscaled(a_q, a_s, b_q, b_s)
+        torch.cuda.synchronize()
+        assert gemm.gemm_error_count() == 0
+        print("fp8 profile run done", float(c[0, 0]))
         return
     flush = torch.zeros(64 << 20, dtype=torch.float32, device=dev)
     pk, src = peak()
