@@ -28,6 +28,7 @@
 
 #if defined(__CUDACC__)
 #include "device/collectives.cuh"
+#include "device/sync.cuh"
 #define ROCSHMEM_API __host__ __device__ inline
 #define ROCSHMEM_DEVICE_API __device__ inline
 #else

@@ -489,6 +489,35 @@ __global__ void api_surface_kernel(int run, void *p, rocshmem_team_t team) {
   (void)rocshmem_signal_fetch_wave((uint64_t *)p); int prov; rocshmem_query_thread(&prov); rocshmem_wg_init_thread(0, &prov);
 }
 
+// Every block adds to a plain (non-atomic) counter `rounds` times under the ticket lock and as many times
+// under the spin lock (thread 0 only); a grid barrier separates two phases whose order the host checks.
+__global__ void mutex_kernel(rocshmemx_ticket_mutex_t *ticket, rocshmemx_spin_mutex_t *spin, unsigned long long *counters,
+                             unsigned long long *grid_counter, int rounds, int *phase_errors) {
+  for (int r = 0; r < rounds; ++r) {
+    if (!rocshmemx_ticket_lock_block(ticket)) return;
+    if (threadIdx.x == 0) {
+      volatile unsigned long long *c = counters;
+      *c = *c + 1;
+    }
+    rocshmemx_ticket_unlock_block(ticket);
+  }
+  if (threadIdx.x == 0) {
+    for (int r = 0; r < rounds; ++r) {
+      if (!rocshmemx_spin_lock(spin)) return;
+      volatile unsigned long long *c = counters + 1;
+      *c = *c + 1;
+      rocshmemx_spin_unlock(spin);
+    }
+  }
+  if (!rocshmemx_grid_sync(grid_counter, 1, gridDim.x)) return;
+  // After the barrier every block must see all increments of the first phase.
+  if (threadIdx.x == 0) {
+    const unsigned long long want = static_cast<unsigned long long>(gridDim.x) * rounds;
+    if (*reinterpret_cast<volatile unsigned long long *>(counters) != want) atomicAdd(phase_errors, 1);
+    if (*reinterpret_cast<volatile unsigned long long *>(counters + 1) != want) atomicAdd(phase_errors, 1);
+  }
+}
+
 // ---- launch glue ---------------------------------------------------------------------------------------------------------------------
 
 template <typename T> T *P(uintptr_t v) { return reinterpret_cast<T *>(v); }
@@ -577,6 +606,13 @@ PYBIND11_MODULE(_testk, m) {
                  int threads, uintptr_t stream) {
     ok(kernels::launch_pes(bw_kernel, blocks, threads, 0, S(stream), false, mode, P<char>(dst), P<char>(src),
                            bytes, pe, iters, P<unsigned long long>(ns)), "bw_kernel");
+  });
+  m.def("mutex_test", [](uintptr_t ticket, uintptr_t spin, uintptr_t counters, uintptr_t grid_counter, int rounds,
+                         uintptr_t phase_errors, int blocks, int threads, uintptr_t stream) {
+    mutex_kernel<<<blocks, threads, 0, S(stream)>>>(P<rocshmemx_ticket_mutex_t>(ticket), P<rocshmemx_spin_mutex_t>(spin),
+                                                    P<unsigned long long>(counters), P<unsigned long long>(grid_counter),
+                                                    rounds, P<int>(phase_errors));
+    ok(cudaGetLastError(), "mutex_kernel");
   });
   m.def("api_surface", [](uintptr_t p, uintptr_t team, uintptr_t stream) {
     ok(kernels::launch_pes(api_surface_kernel, 1, 32, 0, S(stream), false, 0, P<void>(p),

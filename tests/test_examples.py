@@ -53,3 +53,15 @@ def test_python_example(script, tmp_path):
     world = 2 if torch.cuda.device_count() >= 2 else 1
     cmd = [os.path.join(EX, "python", script)]
     run(cmd if world > 1 else [sys.executable] + cmd, world, tmp_path)
+
+
+@pytest.mark.parametrize("test", ["put", "get", "amo_fadd", "pingpong", "barrier", "allreduce", "broadcast", "alltoall"])
+def test_functional_driver(test, tmp_path):
+    """The command-line performance driver prints one table row per message size (two PEs on one GPU)."""
+    cmd = [sys.executable, os.path.join(ROOT, "benchmarks", "functional_driver.py"), "-a", test, "-s", "65536", "-m", "4096",
+           "--local-pes", "2", "--loop", "3", "--skip", "1", "-z", "128"]
+    out = subprocess.run(cmd, capture_output=True, text=True, timeout=300, env=dict(os.environ, ROCSHMEM_BOOTSTRAP_DIR=str(tmp_path)))
+    assert out.returncode == 0, out.stdout[-2000:] + out.stderr[-2000:]
+    rows = [l for l in out.stdout.splitlines() if l.strip() and l.strip()[0].isdigit()]
+    assert len(rows) >= 1, out.stdout
+    assert all(len(r.split()) == 5 for r in rows), out.stdout

@@ -497,3 +497,22 @@ def test_large_broadcast_through_relays(env, nbytes, root):
     assert err["count"] == 0, err
     shm.free(dst)
     shm.free(src)
+
+
+def test_device_locks_and_grid_sync(env):
+    """Ticket lock (per block), spin lock (per thread) and the grid barrier of the rocshmemx extensions:
+    increments of a plain counter under each lock must all survive."""
+    shm, k = env
+    blocks, threads, rounds = 96, 128, 50   # 96 blocks are resident together on a B200 (grid barrier)
+    state = torch.zeros(64, dtype=torch.int64, device="cuda")
+    errs = torch.zeros(1, dtype=torch.int32, device="cuda")
+    base = state.data_ptr()
+    k.mutex_test(base, base + 64, base + 128, base + 256, rounds, errs.data_ptr(), blocks, threads,
+                 torch.cuda.current_stream().cuda_stream)
+    torch.cuda.synchronize()
+    got = state.cpu()
+    assert int(got[16]) == blocks * rounds, "ticket lock lost updates"
+    assert int(got[17]) == blocks * rounds, "spin lock lost updates"
+    assert int(got[32]) == blocks, "grid barrier counter"
+    assert int(errs.item()) == 0
+    assert shm.get_error(0)["count"] == 0
