@@ -118,7 +118,8 @@ def _ninja_text(with_tests: bool) -> str:
     if with_tests and tests_src.exists():
         obj = _rel(OBJ / "tests_test_kernels.cu.o")
         lines.append(f"build {obj}: nvcc {_rel(tests_src)}")
-        lines.append("  extra = -Xcompiler -fvisibility=hidden "
+        # The test kernels count their API calls (device statistics are compiled in per translation unit).
+        lines.append("  extra = -DROCSHMEM_PROFILE -Xcompiler -fvisibility=hidden "
                      f"-I{py_inc} -I{_pybind_include()}")
         text = _rel(PKG / f"_testk{EXT}")
         lines.append(f"build {text}: linkext {obj} | {lib}")

@@ -149,6 +149,7 @@ __device__ __forceinline__ void putmem(void *dest, const void *source, size_t by
   if (bytes == 0) return;
   if (!check_pe(pe, 10) || !check_symmetric(dest, bytes, 10)) return;
   Group<S> g;
+  if (g.leader()) stat_add(ROCSHMEM_STAT_BYTES_PUT, bytes);
   if (S == Scope::THREAD && st().use_proxy) {
     bool ok;
     proxy_submit(ROCSHMEM_PROXY_PUT, pe, dest, source, bytes, 0, 0, 1, blocking, &ok);
@@ -169,6 +170,7 @@ __device__ __forceinline__ void getmem(void *dest, const void *source, size_t by
   if (bytes == 0) return;
   if (!check_pe(pe, 11) || !check_symmetric(source, bytes, 11)) return;
   Group<S> g;
+  if (g.leader()) stat_add(ROCSHMEM_STAT_BYTES_GET, bytes);
   if (S == Scope::THREAD && st().use_proxy) {
     bool ok;
     proxy_submit(ROCSHMEM_PROXY_GET, pe, dest, source, bytes, 0, 0, 1, true, &ok);

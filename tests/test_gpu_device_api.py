@@ -516,3 +516,29 @@ def test_device_locks_and_grid_sync(env):
     assert int(got[32]) == blocks, "grid barrier counter"
     assert int(errs.item()) == 0
     assert shm.get_error(0)["count"] == 0
+
+
+def test_device_statistics_count_api_calls(env):
+    """Kernels built with -DROCSHMEM_PROFILE count their API calls per PE (reference: src/stats.hpp);
+    reset_stats() zeroes them, device_stats() reads them back."""
+    from rocshmem_b200 import runtime as rt
+    shm, k = env
+    C = rt._C()
+    nbytes = 4096
+    src = shm.zeros(nbytes, torch.uint8)
+    dst = shm.zeros(nbytes, torch.uint8)
+    torch.cuda.synchronize()
+    C.reset_stats()
+    assert sum(C.device_stats(0)) == 0
+    threads = 64
+    k.rma(RMA_PUT, SC_THREAD, dst.data_ptr(), src.data_ptr(), nbytes, 1, 0, threads, stream())
+    sync_ok(shm)
+    for l in range(NPES):
+        st = C.device_stats(l)
+        assert st[0] == threads, (l, st[:8])            # ROCSHMEM_STAT_PUT: one put per thread
+        assert st[26] == nbytes, (l, st[24:30])         # ROCSHMEM_STAT_BYTES_PUT
+    C.reset_stats()
+    assert sum(C.device_stats(1)) == 0
+    C.dump_stats()                                        # prints, must not fail
+    shm.free(dst)
+    shm.free(src)
