@@ -18,6 +18,7 @@ import torch
 
 from .. import runtime as rt
 from ..ops import gemm, moe
+from ..utils.trace import traced
 
 
 def expert_weights(expert: int, hidden: int, inter: int, seed: int = 0, device="cpu"):
@@ -71,6 +72,7 @@ class MoEFeedForward:
             self.h_q = torch.zeros((cap, inter), dtype=torch.uint8, device=dev)
             self.h_s = torch.zeros((cap, inter // 128), dtype=torch.float32, device=dev)
 
+    @traced("rocshmem_b200.moe_feed_forward")
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
                 out: Optional[torch.Tensor] = None, stream=None, stage_us: Optional[dict] = None) -> torch.Tensor:
         """x [T, hidden] bf16, topk_idx [T, top_k] int32 global expert ids (-1 = unused), topk_weights

@@ -18,6 +18,7 @@ import torch
 
 from .. import runtime as rt
 from ..ops import gemm
+from ..utils.trace import traced
 from ..ops.gemm import TensorParallelLinear
 
 
@@ -47,6 +48,7 @@ class TensorParallelMLP:
         :meth:`forward`."""
         return self.tp.ag_input(self.d_model)
 
+    @traced("rocshmem_b200.tp_mlp")
     def forward(self, x_shard: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                 stream=None) -> torch.Tensor:
         """Returns this rank's ``[m_shard, d_model]`` rows of the MLP output. ``x_shard=None`` uses
@@ -83,6 +85,7 @@ class TensorParallelMLPFp8:
         self.h_q = torch.empty((M, self.ff_local), dtype=torch.uint8, device=dev)
         self.h_s = torch.empty((M, self.ff_local // 128), dtype=torch.float32, device=dev)
 
+    @traced("rocshmem_b200.tp_mlp_fp8")
     def forward(self, x_shard: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
         self.tp.set_input(x_shard, stream)
         self.tp.ag_gemm(self.w1_q, self.w1_s, out=self.h, swiglu=True, stream=stream)

@@ -22,6 +22,7 @@ from typing import Optional
 import torch
 
 from .. import runtime as rt
+from ..utils.trace import trace_range
 
 E4M3_MAX = 448.0
 
@@ -142,7 +143,8 @@ class EpDispatcher:
         for t in (x, topk_idx, topk_weights):
             if not t.is_contiguous():
                 raise ValueError("dispatch: tensors must be contiguous")
-        self._h.dispatch(x.data_ptr(), topk_idx.data_ptr(), topk_weights.data_ptr(), T, _stream(stream))
+        with trace_range("rocshmem_b200.ep_dispatch"):
+            self._h.dispatch(x.data_ptr(), topk_idx.data_ptr(), topk_weights.data_ptr(), T, _stream(stream))
         self.kernel_launches += 1
         return self._result()
 
@@ -155,8 +157,9 @@ class EpDispatcher:
             raise ValueError("combine: y must be this dispatcher's result_buffer()")
         if out is None:
             out = torch.empty((num_tokens, self.hidden), dtype=torch.bfloat16, device=y.device)
-        self._h.combine(y.data_ptr(), out.data_ptr(), topk_idx.data_ptr(), topk_weights.data_ptr(), num_tokens,
-                        int(weighted), _stream(stream))
+        with trace_range("rocshmem_b200.ep_combine"):
+            self._h.combine(y.data_ptr(), out.data_ptr(), topk_idx.data_ptr(), topk_weights.data_ptr(), num_tokens,
+                            int(weighted), _stream(stream))
         self.kernel_launches += 1
         return out
 

@@ -1,0 +1,71 @@
+"""Utility modules on the CPU backend: heap snapshots, roofline arithmetic, tracing switches."""
+import json
+import os
+
+import pytest
+import torch
+
+
+@pytest.fixture()
+def shm_cpu(tmp_path):
+    import rocshmem_b200 as shm
+    if shm.is_initialized():
+        shm.finalize()
+    shm.init(backend="host", n_local=2, heap_size="8M", ROCSHMEM_BOOTSTRAP_DIR=str(tmp_path))
+    yield shm
+    shm.finalize()
+
+
+def test_snapshot_and_restore_round_trip(shm_cpu, tmp_path):
+    from rocshmem_b200.utils import checkpoint
+    shm = shm_cpu
+    a = shm.zeros(1000, torch.float32)
+    b = shm.zeros((16, 8), torch.int64)
+    a.copy_(torch.arange(1000, dtype=torch.float32))
+    b.fill_(7)
+    saved = checkpoint.snapshot({"a": a, "b": b})
+    a.zero_()
+    b.zero_()
+    checkpoint.restore({"a": a, "b": b}, saved)
+    assert torch.equal(a.cpu(), torch.arange(1000, dtype=torch.float32)) and torch.all(b.cpu() == 7)
+    path = str(tmp_path / "pe0.pt")
+    checkpoint.save(path, {"a": a})
+    a.fill_(-1)
+    checkpoint.load(path, {"a": a})
+    assert float(a[999]) == 999.0
+    with pytest.raises(ValueError):
+        checkpoint.restore({"a": b}, {"a": saved["a"]})
+    with pytest.raises(KeyError):
+        checkpoint.restore({"c": a}, saved)
+
+
+def test_roofline_uses_measured_peaks_or_fallback(tmp_path):
+    from rocshmem_b200.utils import roofline
+    p = roofline.measured_peaks(str(tmp_path))
+    assert p["source"] == "fallback" and p["hbm_gbs"] == 6650.0
+    (tmp_path / "MEASURED_PEAKS.json").write_text(json.dumps({"hbm_gbs": 6000, "bf16_tflops": 1500, "bf16_tflops_sustained": 1300}))
+    p = roofline.measured_peaks(str(tmp_path))
+    assert p["source"] == "measured"
+    assert roofline.memory_fraction(6e9, 1e-3, p) == pytest.approx(1.0)
+    assert roofline.compute_fraction(1.5e12, 1e-3, peaks=p) == pytest.approx(1.0)
+    # compute-bound and link-bound cases
+    assert roofline.fused_roofline_seconds(1.3e12, 1e6, peaks=p) == pytest.approx(1e-3)
+    assert roofline.fused_roofline_seconds(1e9, 770e6, peaks=p) == pytest.approx(1e-3)
+
+
+def test_trace_range_is_a_no_op_without_nvtx(monkeypatch):
+    from rocshmem_b200.utils import trace
+    monkeypatch.delenv("ROCSHMEM_NVTX", raising=False)
+    assert not trace.nvtx_enabled()
+    calls = []
+
+    @trace.traced("unit")
+    def f(x):
+        calls.append(x)
+        return x + 1
+
+    assert f(1) == 2 and calls == [1]
+    monkeypatch.setenv("ROCSHMEM_NVTX", "1")
+    assert trace.nvtx_enabled()
+    with trace.trace_range("still fine without a GPU"):
+        pass
