@@ -31,8 +31,8 @@ def _fd_worker(d, rank, size, q):
     fds = C.exchange_fds_file(d, rank, size, fd, 20000)
     seen = []
     for r, f in enumerate(fds):
-        os.lseek(f, 0, os.SEEK_SET)
-        seen.append(os.read(f, 64).decode())
+        # pread: descriptors passed between processes share one file offset, so lseek + read would race
+        seen.append(os.pread(f, 64, 0).decode())
         os.close(f)
     q.put((rank, seen))
 
