@@ -199,6 +199,14 @@ enum rocshmem_proxy_op : unsigned int {
   ROCSHMEM_PROXY_QUIET = 5,
   ROCSHMEM_PROXY_BARRIER = 6,
   ROCSHMEM_PROXY_SIGNAL = 7,
+  // Host-executed forms of the remaining operations (world team): `pe` is the root, `size` the payload in
+  // bytes (elements for REDUCE), `cond` the element type (rocshmem_dtype) and `op` the reduction operator.
+  ROCSHMEM_PROXY_FENCE = 8,
+  ROCSHMEM_PROXY_BROADCAST = 9,
+  ROCSHMEM_PROXY_REDUCE = 10,
+  ROCSHMEM_PROXY_FCOLLECT = 11,
+  ROCSHMEM_PROXY_ALLTOALL = 12,
+  ROCSHMEM_PROXY_P = 13,          // single element put by value: `size` holds the bits, dtype_size its width
 };
 
 struct rocshmem_proxy_ring {

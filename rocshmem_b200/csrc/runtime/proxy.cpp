@@ -167,6 +167,33 @@ void Proxy::execute(rocshmem_proxy_cmd &cmd, uint64_t) {
       case ROCSHMEM_PROXY_BARRIER:
         ops.barrier(ctx, rt_->team_world(), false);
         break;
+      case ROCSHMEM_PROXY_FENCE:
+        ops.fence(ctx);
+        break;
+      case ROCSHMEM_PROXY_P: {
+        // The value travels inside the command; stage it in host memory for the put.
+        unsigned long long bits = cmd.size;
+        ops.put(ctx, reinterpret_cast<void *>(cmd.dst), &bits, cmd.dtype_size, cmd.pe, true);
+        break;
+      }
+      case ROCSHMEM_PROXY_BROADCAST:
+        fetched = static_cast<unsigned long long>(ops.broadcast(
+            ctx, rt_->team_world(), reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src),
+            cmd.size, cmd.pe));
+        break;
+      case ROCSHMEM_PROXY_REDUCE:
+        fetched = static_cast<unsigned long long>(ops.reduce(
+            ctx, rt_->team_world(), reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src),
+            cmd.size, static_cast<DType>(cmd.cond), static_cast<ROCSHMEM_OP>(cmd.op)));
+        break;
+      case ROCSHMEM_PROXY_FCOLLECT:
+        fetched = static_cast<unsigned long long>(ops.fcollect(
+            ctx, rt_->team_world(), reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src), cmd.size));
+        break;
+      case ROCSHMEM_PROXY_ALLTOALL:
+        fetched = static_cast<unsigned long long>(ops.alltoall(
+            ctx, rt_->team_world(), reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src), cmd.size));
+        break;
       default:
         break;
     }

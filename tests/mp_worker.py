@@ -307,7 +307,61 @@ def rank_leaves():
     del team
 
 
-SCENARIOS = {f.__name__: f for f in (host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def proxy_collectives():
+    """The reverse-offload command ring executing the host forms of fence, P, broadcast, reduce, fcollect and
+    alltoall (each rank submits the command to its own proxy thread, like a device kernel would)."""
+    from rocshmem_b200 import runtime as rt
+    init("16M")
+    C = rt._C()
+    me, npes = shm.my_pe(), shm.n_pes()
+    FENCE, BROADCAST, REDUCE, FCOLLECT, ALLTOALL, P = 8, 9, 10, 11, 12, 13
+    I64 = 6  # ROCSHMEM_I64
+    p = C.proxy_start()
+    try:
+        n = 64
+        src = shm.zeros(n * npes, torch.int64)
+        dst = shm.zeros(n * npes, torch.int64)
+        src.copy_((torch.arange(n * npes) + 1000 * me).to(dev()))
+        shm.barrier_all()
+        sub = lambda *a: C.proxy_submit(p, *a, True, 20000)
+        assert sub(FENCE, 0, 0, 0, 0, 0, 0, 0)[0] == 0
+        # reduce: sum over ranks of (i + 1000 r)
+        rc, status = sub(REDUCE, 0, dst.data_ptr(), src.data_ptr(), n, I64, shm.OP_SUM, 8)
+        assert rc == 0 and status == 0
+        want = torch.arange(n) * npes + 1000 * sum(range(npes))
+        assert torch.equal(dst.cpu()[:n], want)
+        shm.barrier_all()
+        # broadcast from the last rank: everybody else receives its src
+        dst.zero_()
+        shm.barrier_all()
+        root = npes - 1
+        assert sub(BROADCAST, root, dst.data_ptr(), src.data_ptr(), n * 8, 0, 0, 1)[0] == 0
+        got = dst.cpu()[:n]
+        assert torch.equal(got, torch.zeros(n, dtype=torch.int64) if me == root else torch.arange(n) + 1000 * root)
+        shm.barrier_all()
+        # fcollect: block r of dst is rank r's first n elements
+        assert sub(FCOLLECT, 0, dst.data_ptr(), src.data_ptr(), n * 8, 0, 0, 1)[0] == 0
+        got = dst.cpu().view(npes, n)
+        assert all(torch.equal(got[r], torch.arange(n) + 1000 * r) for r in range(npes))
+        shm.barrier_all()
+        # alltoall: block r of dst is rank r's block `me`
+        assert sub(ALLTOALL, 0, dst.data_ptr(), src.data_ptr(), n * 8, 0, 0, 1)[0] == 0
+        got = dst.cpu().view(npes, n)
+        assert all(torch.equal(got[r], torch.arange(n) + me * n + 1000 * r) for r in range(npes))
+        shm.barrier_all()
+        # P: one element by value to the right-hand neighbour
+        cell = shm.zeros(1, torch.int64)
+        shm.barrier_all()
+        assert sub(P, (me + 1) % npes, cell.data_ptr(), 0, 4242 + me, 0, 0, 8)[0] == 0
+        shm.barrier_all()
+        assert int(cell.cpu()[0]) == 4242 + (me - 1) % npes
+    finally:
+        C.proxy_stop(p)
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

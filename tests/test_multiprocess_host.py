@@ -25,3 +25,9 @@ def test_host_collectives(world):
 
 def test_wait_family_between_processes():
     assert_all_ok(run_ranks("wait_and_signal", 3))
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_proxy_ring_runs_host_collectives(world):
+    """Reverse-offload command set beyond RMA: fence, P, broadcast, reduce, fcollect, alltoall."""
+    assert_all_ok(run_ranks("proxy_collectives", world))
