@@ -24,6 +24,12 @@ void bind_gemm(py::module_ &m) {
   m.def("gemm_bf16", [](uintptr_t a, uintptr_t b, uintptr_t c, int M, int N, int K, uintptr_t stream) {
     check(gemm_bf16(P<void>(a), P<void>(b), P<void>(c), M, N, K, P<void>(stream)), "gemm_bf16");
   });
+  m.def("gemm_bf16_one_cta", [](uintptr_t a, uintptr_t b, uintptr_t c, int M, int N, int K, uintptr_t stream) {
+    check(gemm_bf16_one_cta(P<void>(a), P<void>(b), P<void>(c), M, N, K, P<void>(stream)), "gemm_bf16_one_cta");
+  });
+  m.def("gemm_bf16_pair", [](uintptr_t a, uintptr_t b, uintptr_t c, int M, int N, int K, uintptr_t stream) {
+    check(gemm_bf16_pair(P<void>(a), P<void>(b), P<void>(c), M, N, K, P<void>(stream)), "gemm_bf16_pair");
+  });
   m.def("grouped_gemm_bf16", [](uintptr_t a, uintptr_t b, uintptr_t c, uintptr_t offsets, int groups, int max_rows,
                                 int N, int K, int swiglu, uintptr_t stream) {
     check(grouped_gemm_bf16(P<void>(a), P<void>(b), P<void>(c), P<int>(offsets), groups, max_rows, N, K, swiglu,

@@ -17,9 +17,12 @@
 // Nothing here has a counterpart in the reference; the ingredients it offers are fcollect, reduction
 // and put-with-signal (src/ipc/context_ipc_tmpl_device.hpp:166-531).
 #include <cuda.h>
+
+#include <cstdlib>
 #include <cuda_bf16.h>
 
 #include "gemm_core.cuh"
+#include "gemm2_core.cuh"
 #include "gemm_fp8_core.cuh"
 #include "gemm_kernels.hpp"
 #include "gemm_tmap.hpp"
@@ -202,6 +205,85 @@ ag_gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   gemm::run<false, SWIGLU>(&map_a, &map_b, a.k * 2, sched, epi, smem_raw, sh);
 }
 
+// Two-CTA form: a pair of CTAs computes 256 x 256 tiles, i.e. two 128-row blocks of the gathered matrix at
+// a time (m_shard must be a multiple of 256); the producer waits for both blocks' counters.
+template <bool SWIGLU>
+struct AgPairScheduler {
+  int me, n_ranks, tiles_per_shard, tiles_n, tiles, m_shard, n;   // tiles_per_shard counts 256-row blocks
+  const unsigned int *ready_count;
+  unsigned target;
+  AgPush push;
+  __device__ bool get(int iter, gemm::Tile &t) const {
+    const int id = blockIdx.x / 2 + iter * (gridDim.x / 2);
+    if (id >= tiles) return false;
+    int oi, nt;
+    gemm::raster(id, tiles / tiles_n, tiles_n, min(gemm::RASTER_GROUP / 2, tiles_per_shard), oi, nt);
+    const int src = (me + oi / tiles_per_shard) % n_ranks;
+    const int mt = oi % tiles_per_shard;
+    t.a_row = src * m_shard + mt * 2 * gemm2::BM;
+    t.rows = 2 * gemm2::BM;
+    if (SWIGLU) {
+      const int j0 = nt * (gemm2::BN / 2);
+      t.b_row[0] = j0;
+      t.b_row[1] = n / 2 + j0;
+      t.cols = min(gemm2::BN / 2, n / 2 - j0);
+      t.c_col = j0;
+    } else {
+      t.b_row[0] = nt * gemm2::BN;
+      t.b_row[1] = nt * gemm2::BN + gemm2::BN / 2;
+      t.cols = min(gemm2::BN, n - nt * gemm2::BN);
+      t.c_col = nt * gemm2::BN;
+    }
+    t.c_row = t.a_row;
+    t.tag = 2 * oi;   // first of the two 128-row blocks, in arrival order
+    return true;
+  }
+  __device__ bool wait_block(const unsigned int *p) const {
+    if (detail::ld_acquire_sys_u32(p) < target) {
+      detail::SpinBudget budget(gemm::WAIT_BUDGET_NS);
+      while (detail::ld_acquire_sys_u32(p) < target) {
+        if (!budget.keep_going()) {
+          detail::record_error(ROCSHMEM_ERR_KERNEL, -1, 81, p, target, *reinterpret_cast<const volatile unsigned int *>(p));
+          return false;
+        }
+      }
+    }
+    return true;
+  }
+  __device__ bool ready(const gemm::Tile &t) const {
+    // Each CTA of the pair loads one of the two row blocks; waiting for both keeps the logic symmetric.
+    if (!wait_block(ready_count + t.tag) || !wait_block(ready_count + t.tag + 1)) return false;
+    sm100::fence_proxy_async();
+    return true;
+  }
+  __device__ void side_role() const { ag_push_role(push); }
+};
+
+template <bool SWIGLU>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS + 32, 1)
+ag_gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, AgArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ gemm2::Shared sh;
+  const rocshmem_team_dev *t = detail::team_of(a.team);
+  if (t->my_pe < 0) return;
+  if (!block_pair_barrier(t, blockIdx.x, false)) return;
+  AgPairScheduler<SWIGLU> sched;
+  sched.me = t->my_pe;
+  sched.n_ranks = t->size;
+  sched.tiles_per_shard = a.m_shard / (2 * gemm2::BM);
+  sched.tiles_n = SWIGLU ? (a.n / 2 + gemm2::BN / 2 - 1) / (gemm2::BN / 2) : (a.n + gemm2::BN - 1) / gemm2::BN;
+  sched.tiles = t->size * sched.tiles_per_shard * sched.tiles_n;
+  sched.m_shard = a.m_shard;
+  sched.n = a.n;
+  sched.ready_count = a.ready;
+  const size_t tile_bytes = size_t(gemm::BM) * a.k * 2;
+  sched.target = a.epoch * static_cast<unsigned>(ag_slices_per_tile(tile_bytes));
+  sched.push = AgPush{t, reinterpret_cast<const char *>(a.x_shard), reinterpret_cast<char *>(a.gathered), tile_bytes,
+                      nullptr, nullptr, 0, a.m_shard / gemm::BM, a.ready};
+  PlainEpilogue epi{a.c, static_cast<size_t>(SWIGLU ? a.n / 2 : a.n)};
+  gemm2::run<SWIGLU>(&map_a, &map_b, a.k * 2, sched, epi, smem_raw, sh);
+}
+
 // ---- GEMM -> reduce-scatter ----------------------------------------------------------------------------------
 
 struct RsArgs {
@@ -312,6 +394,58 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   rs_reduce(a, t);
 }
 
+struct RsPairScheduler {
+  int me, n_ranks, tiles_per_shard, tiles_n, tiles, m_shard, n;   // tiles_per_shard counts 256-row blocks
+  __device__ bool get(int iter, gemm::Tile &t) const {
+    const int id = blockIdx.x / 2 + iter * (gridDim.x / 2);
+    if (id >= tiles) return false;
+    int oi, nt;
+    gemm::raster(id, tiles / tiles_n, tiles_n, min(gemm::RASTER_GROUP / 2, tiles_per_shard), oi, nt);
+    const int owner = (me + 1 + oi / tiles_per_shard) % n_ranks;
+    const int mt = oi % tiles_per_shard;
+    t.a_row = owner * m_shard + mt * 2 * gemm2::BM;
+    t.rows = 2 * gemm2::BM;
+    t.b_row[0] = nt * gemm2::BN;
+    t.b_row[1] = nt * gemm2::BN + gemm2::BN / 2;
+    t.cols = min(gemm2::BN, n - nt * gemm2::BN);
+    t.c_row = mt * 2 * gemm2::BM;
+    t.c_col = nt * gemm2::BN;
+    t.tag = owner;
+    return true;
+  }
+  __device__ bool ready(const gemm::Tile &) const { return true; }
+  __device__ void side_role() const {}
+};
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(gemm2::THREADS, 1)
+gemm_rs_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, RsArgs a) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ gemm2::Shared sh;
+  const rocshmem_team_dev *t = detail::team_of(a.team);
+  if (t->my_pe < 0) return;
+  RsPairScheduler sched;
+  sched.me = t->my_pe;
+  sched.n_ranks = t->size;
+  sched.tiles_per_shard = a.m_shard / (2 * gemm2::BM);
+  sched.tiles_n = (a.n + gemm2::BN - 1) / gemm2::BN;
+  sched.tiles = t->size * sched.tiles_per_shard * sched.tiles_n;
+  sched.m_shard = a.m_shard;
+  sched.n = a.n;
+  RsEpilogue epi{t, a.staging, t->my_pe, a.m_shard, a.n};
+  gemm2::run<false>(&map_a, &map_b, a.k * 2, sched, epi, smem_raw, sh);
+  rs_reduce(a, t);
+}
+
+// Kernels with two CTAs per tile are used where the shapes allow; ROCSHMEM_GEMM_TWO_CTA=0 selects the
+// one-CTA kernels everywhere (for comparison).
+bool use_two_cta() {
+  static const bool on = [] {
+    const char *e = std::getenv("ROCSHMEM_GEMM_TWO_CTA");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
 // ---- block-scaled e4m3 variants -------------------------------------------------------------------------------
 // Same structure with the fp8 core: the comm CTAs gather the e4m3 rows and, as a second array, their
 // 1 x 128 scales (half the NVLink bytes of the bf16 kernel); the weights carry 128 x 128 scales.
@@ -402,12 +536,18 @@ int ag_gemm_bf16(rocshmem_team_t team, const void *x_shard, void *gathered, unsi
       !encode_tmap_2d(&map_b, b, n, k, 2, gemm::BN / 2)) {
     return -1;
   }
-  if (int rc = swiglu ? prepare_smem(ag_gemm_kernel<true>) : prepare_smem(ag_gemm_kernel<false>)) return rc;
   AgArgs a{team, static_cast<const __nv_bfloat16 *>(x_shard), static_cast<__nv_bfloat16 *>(gathered),
            reinterpret_cast<unsigned int *>(flags), static_cast<__nv_bfloat16 *>(c), m_shard, n, k, epoch};
   // The GEMM roles wait for rows that other ranks' CTAs push: all CTAs of all ranks must be resident.
   const int sms = device_sm_count();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (use_two_cta() && m_shard % (2 * gemm2::BM) == 0 && sms % 2 == 0) {
+    auto kp = swiglu ? ag_gemm_pair_kernel<true> : ag_gemm_pair_kernel<false>;
+    cudaError_t e = cudaFuncSetAttribute(kp, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return launch_pes(kp, sms, gemm2::THREADS + 32, gemm2::SMEM_BYTES, s, true, map_a, map_b, a);
+  }
+  if (int rc = swiglu ? prepare_smem(ag_gemm_kernel<true>) : prepare_smem(ag_gemm_kernel<false>)) return rc;
   if (swiglu) return launch_pes(ag_gemm_kernel<true>, sms, gemm::THREADS + 32, gemm::SMEM_BYTES, s, true, map_a, map_b, a);
   return launch_pes(ag_gemm_kernel<false>, sms, gemm::THREADS + 32, gemm::SMEM_BYTES, s, true, map_a, map_b, a);
 }
@@ -424,9 +564,15 @@ int gemm_rs_bf16(rocshmem_team_t team, const void *a_mat, const void *b, void *s
       !encode_tmap_2d(&map_b, b, n, k, 2, gemm::BN / 2)) {
     return -1;
   }
-  if (int rc = prepare_smem(gemm_rs_kernel)) return rc;
   RsArgs a{team, static_cast<__nv_bfloat16 *>(staging), static_cast<__nv_bfloat16 *>(out), m_shard, n, k,
            grid_counter, epoch};
+  if (use_two_cta() && m_shard % (2 * gemm2::BM) == 0 && device_sm_count() % 2 == 0) {
+    cudaError_t e = cudaFuncSetAttribute(gemm_rs_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm2::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return launch_pes(gemm_rs_pair_kernel, device_sm_count(), gemm2::THREADS, gemm2::SMEM_BYTES,
+                      static_cast<cudaStream_t>(stream), true, map_a, map_b, a);
+  }
+  if (int rc = prepare_smem(gemm_rs_kernel)) return rc;
   return launch_pes(gemm_rs_kernel, device_sm_count(), gemm::THREADS, gemm::SMEM_BYTES,
                     static_cast<cudaStream_t>(stream), true, map_a, map_b, a);
 }

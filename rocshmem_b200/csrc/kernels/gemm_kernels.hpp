@@ -25,6 +25,9 @@ int gemm_bf16(const void *a, const void *b, void *c, int m, int n, int k, void *
 // be known on the host (they come out of the MoE dispatch). `max_rows` bounds offsets[groups].
 // With swiglu != 0, N must be even and the output is [rows, N / 2]:
 // out[:, j] = silu(acc[:, j]) * acc[:, j + N/2]  (gate and up projections stacked in B).
+// The same product with two CTAs per 256 x 256 tile (tcgen05 cta_group::2, clusters of two).
+int gemm_bf16_pair(const void *a, const void *b, void *c, int m, int n, int k, void *stream);
+int gemm_bf16_one_cta(const void *a, const void *b, void *c, int m, int n, int k, void *stream);
 int grouped_gemm_bf16(const void *a, const void *b, void *c, const int *offsets, int groups, int max_rows,
                       int n, int k, int swiglu, void *stream);
 

@@ -26,8 +26,11 @@ def _check(t: torch.Tensor, name: str) -> None:
         raise ValueError(f"{name} must be 16-byte aligned")
 
 
-def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
-    """``a [M, K] @ b [N, K].T -> [M, N]`` (bf16 in, fp32 accumulate in TMEM, bf16 out)."""
+def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None,
+              two_cta: Optional[bool] = None) -> torch.Tensor:
+    """``a [M, K] @ b [N, K].T -> [M, N]`` (bf16 in, fp32 accumulate in TMEM, bf16 out). By default the
+    library picks the kernel (a pair of CTAs per 256 x 256 tile, ``tcgen05`` ``cta_group::2``, when M > 128);
+    ``two_cta`` forces one or the other."""
     _check(a, "a")
     _check(b, "b")
     M, K = a.shape
@@ -36,7 +39,9 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
         raise ValueError("inner dimensions must match and be a multiple of 8")
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
-    rt._C().gemm_bf16(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, _stream(stream))
+    C = rt._C()
+    fn = C.gemm_bf16 if two_cta is None else (C.gemm_bf16_pair if two_cta else C.gemm_bf16_one_cta)
+    fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, _stream(stream))
     return out
 
 

@@ -158,3 +158,19 @@ def test_grouped_gemm_fp8_swiglu():
         ok, err = close(out[lo:lo + sz], want, k)
         assert ok, (gi, err)
         lo += sz
+
+
+@pytest.mark.parametrize("two_cta", [True, False])
+@pytest.mark.parametrize("m,n,k", [(256, 256, 64), (300, 520, 1024), (1000, 3584, 512), (129, 8, 256)])
+def test_gemm_bf16_kernel_variants(m, n, k, two_cta):
+    """The one-CTA and the two-CTA (cta_group::2) kernels, forced explicitly."""
+    from rocshmem_b200.ops import gemm
+    g = torch.Generator(device="cuda").manual_seed(m + k)
+    a = (torch.randn(m, k, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    b = (torch.randn(n, k, generator=g, device="cuda") * 0.5).to(torch.bfloat16)
+    before = gemm.gemm_error_count()
+    c = gemm.gemm_bf16(a, b, two_cta=two_cta)
+    torch.cuda.synchronize()
+    assert gemm.gemm_error_count() == before
+    ok, err = close(c, ref_gemm(a, b), k)
+    assert ok, f"max abs error {err}"
