@@ -39,7 +39,7 @@ def reference_arm(args) -> None:
     if rank == 0:
         print(json.dumps({"impl": "reference", "unavailable":
                           "reference is HIP-only (hipcc/ROCm/MPI, no setup.py or pyproject.toml): pip install of "
-                          "/root/reference fails and it cannot target sm_100a; it also has no dispatch/combine"}))
+                          "the reference tree fails and it cannot target sm_100a; it also has no dispatch/combine"}))
 
 
 class ClockSampler:

@@ -2,7 +2,7 @@
 """Collective and RMA micro-benchmarks on the symmetric heap, with NCCL on the same GPUs as baseline.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-        --master-port 29544 benchmarks/coll_bench.py --out gpurun_out/coll_n8.json
+        --master-port 29544 benchmarks/coll_bench.py --out bench_out/coll_n8.json
 
 For every message size: device time (CUDA events, maximum over ranks, L2 not flushed because the
 payloads above 128 MiB exceed it and the small ones are latency-bound) of
@@ -51,7 +51,7 @@ def timed(fn, iters, warmup=3):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/coll_bench.json")
+    ap.add_argument("--out", default="bench_out/coll_bench.json")
     ap.add_argument("--max-bytes", type=int, default=512 << 20)
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     ap.add_argument("--only", default="allreduce,copies,rma", help="comma list of: allreduce, copies, rma")

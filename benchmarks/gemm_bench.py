@@ -1,10 +1,10 @@
 #!/usr/bin/env python
 """tcgen05 GEMM kernels of this package against cuBLAS (``torch.matmul``) on one GPU.
 
-    python benchmarks/gemm_bench.py --out gpurun_out/gemm_bench.json          # the table
+    python benchmarks/gemm_bench.py --out bench_out/gemm_bench.json          # the table
     python benchmarks/gemm_bench.py --profile                                   # one small shape, few launches
     python benchmarks/gemm_bench.py --profile-fp8                               # the same for the e4m3 kernel
-    ncu --set full --clock-control none -k regex:gemm_bf16_kernel -c 2 -o gpurun_out/gemm \
+    ncu --set full --clock-control none -k regex:gemm_bf16_kernel -c 2 -o bench_out/gemm \
         python benchmarks/gemm_bench.py --profile
 
 Shapes are the per-rank GEMMs of the tensor-parallel MLP (8192 tokens, d_model 8192, d_ff 28672 over 8 or

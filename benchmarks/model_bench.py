@@ -2,7 +2,7 @@
 """Fused model blocks against their library baselines on the same GPUs.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
-        --master-port 29545 benchmarks/model_bench.py --out gpurun_out/model_n8.json
+        --master-port 29545 benchmarks/model_bench.py --out bench_out/model_n8.json
 
 * TP MLP (default: 8192 tokens in total, d_model 8192, d_ff 28672, bf16): this package's two fused kernels
   (all-gather -> GEMM -> SwiGLU, GEMM -> reduce-scatter) against NCCL all-gather + cuBLAS + NCCL
@@ -141,7 +141,7 @@ def bench_moe(args, world, rank, res):
 
 def main():
     ap = argparse.ArgumentParser()
-    ap.add_argument("--out", default="gpurun_out/model_bench.json")
+    ap.add_argument("--out", default="bench_out/model_bench.json")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--d-model", type=int, default=8192)
     ap.add_argument("--d-ff", type=int, default=28672)

@@ -5,7 +5,7 @@ Sized so that a capture ends by itself: one PE, a 2 GiB heap, 8192 tokens of hid
 outputs together exceed the 126 MB L2, so DRAM counters mean something), a handful of launches.
 
     python benchmarks/profile_ep.py --steps 3
-    ncu --set full --clock-control none -k regex:ep_dispatch -c 2 -o gpurun_out/ep_dispatch \
+    ncu --set full --clock-control none -k regex:ep_dispatch -c 2 -o bench_out/ep_dispatch \
         python benchmarks/profile_ep.py --steps 3
 """
 from __future__ import annotations

@@ -447,7 +447,7 @@ bool use_two_cta() {
 }
 
 // ---- block-scaled e4m3 variants -------------------------------------------------------------------------------
-// Same structure with the fp8 core: the comm CTAs gather the e4m3 rows and, as a second array, their
+// Same structure with the fp8 core: the push warps send the e4m3 rows and, as a second array, their
 // 1 x 128 scales (half the NVLink bytes of the bf16 kernel); the weights carry 128 x 128 scales.
 
 struct Ag8Args {

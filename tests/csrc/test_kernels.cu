@@ -1,6 +1,6 @@
 // Kernels of the functional test-suite: user-style __global__ code that calls the device API, in
 // the way the reference's functional tester classes do (tests/functional_tests/*_tester.cpp), plus
-// the pybind11 glue that launches them. Oracles follow SURVEY of those testers: patterns written
+// the pybind11 glue that launches them. Oracles follow those testers: patterns written
 // by the initiator, exact signal counts, max fetched values of atomics, collectives against a host
 // reference.
 //
