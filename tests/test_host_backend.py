@@ -165,3 +165,37 @@ def test_reinit_with_other_shape(fresh_runtime):
     x = shm.zeros(4, torch.int64)
     assert shm.atomic_fetch_add(x, 1, 0) == 0
     shm.finalize()
+
+
+def test_threads_share_the_host_api(shm4):
+    """THREAD_MULTIPLE: several host threads issue atomics and puts at once, each with its own context and
+    acting for its own local PE (the reference's SOS tests `threading` and `mt_contention`)."""
+    import threading
+    shm = shm4
+    n_threads, iters = 8, 200
+    counter = shm.zeros(1, torch.int64)
+    slots = shm.zeros(n_threads * 16, torch.int32)
+    errors = []
+
+    def work(tid):
+        try:
+            shm.set_local_pe(tid % 4)
+            ctx = shm.Context()
+            fetched = [shm.atomic_fetch_add(counter, 1, 2, ctx=ctx) for _ in range(iters)]
+            assert all(b > a for a, b in zip(fetched, fetched[1:])), "fetched values of one thread must grow"
+            shm.putmem(shm.local_view(slots, tid % 4)[tid * 16:(tid + 1) * 16],
+                       torch.full((16,), tid + 1, dtype=torch.int32), 3, ctx=ctx)
+            ctx.quiet()
+            ctx.destroy()
+        except Exception as e:  # noqa: BLE001 - reported by the main thread
+            errors.append((tid, repr(e)))
+
+    threads = [threading.Thread(target=work, args=(t,)) for t in range(n_threads)]
+    [t.start() for t in threads]
+    [t.join(60) for t in threads]
+    assert not errors, errors
+    assert int(shm.local_view(counter, 2)[0]) == n_threads * iters
+    got = shm.local_view(slots, 3).view(n_threads, 16)
+    assert all(torch.all(got[t] == t + 1) for t in range(n_threads))
+    shm.free(slots)
+    shm.free(counter)
