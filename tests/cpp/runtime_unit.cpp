@@ -1,0 +1,180 @@
+// Native unit tests of the host-side runtime pieces that need no GPU: allocator, team arithmetic,
+// configuration parsing and the bootstrap store. The program is built twice by the Python test that drives it,
+// with AddressSanitizer + UBSan and with ThreadSanitizer, so that memory errors, undefined behaviour and data
+// races in these components surface without any device. (The reference's unit tests are gtest programs over the
+// same kind of pieces: tests/unit_tests/*.)
+#include <atomic>
+#include <cstdio>
+#include <cstdlib>
+#include <random>
+#include <set>
+#include <stdexcept>
+#include <string>
+#include <thread>
+#include <vector>
+
+#include "allocator.hpp"
+#include "bootstrap.hpp"
+#include "config.hpp"
+#include "team.hpp"
+
+using namespace rocshmem;
+
+static int g_failures = 0;
+#define EXPECT(cond)                                                                  \
+  do {                                                                                \
+    if (!(cond)) {                                                                    \
+      std::fprintf(stderr, "%s:%d: EXPECT(%s) failed\n", __FILE__, __LINE__, #cond);  \
+      ++g_failures;                                                                   \
+    }                                                                                 \
+  } while (0)
+
+static void test_allocator_basic() {
+  Pow2Allocator a(1 << 20, 128);
+  EXPECT(a.alloc(0) == Pow2Allocator::kNull);
+  const size_t x = a.alloc(100), y = a.alloc(129);
+  EXPECT(x == 0 && a.block_size(x) == 128);
+  EXPECT(y == 256 && a.block_size(y) == 256);   // a 256-byte block is 256-aligned
+  EXPECT(a.used() == 384);
+  EXPECT(!a.free(64));                          // not a live allocation
+  EXPECT(a.free(x) && a.free(y));
+  EXPECT(a.used() == 0 && a.largest_free_block() == (1u << 20));   // buddies merged back
+  EXPECT(a.alloc((1 << 20) + 1) == Pow2Allocator::kNull);
+}
+
+static void test_allocator_random_walk() {
+  // Random alloc / free sequence: live blocks never overlap, stay aligned, and everything merges back.
+  Pow2Allocator a((3u << 20) + 4096, 128);      // not a power of two: several top-level chunks
+  std::mt19937 rng(7);
+  std::vector<std::pair<size_t, size_t>> live;  // offset, size
+  for (int step = 0; step < 20000; ++step) {
+    if (live.empty() || rng() % 3 != 0) {
+      const size_t want = 1 + rng() % 70000;
+      const size_t off = a.alloc(want);
+      if (off == Pow2Allocator::kNull) continue;
+      const size_t sz = a.block_size(off);
+      EXPECT(sz >= want && (sz & (sz - 1)) == 0 && off % 128 == 0 && off + sz <= a.size());
+      for (const auto &l : live) EXPECT(off + sz <= l.first || l.first + l.second <= off);
+      live.emplace_back(off, sz);
+    } else {
+      const size_t i = rng() % live.size();
+      EXPECT(a.free(live[i].first));
+      live[i] = live.back();
+      live.pop_back();
+    }
+  }
+  for (const auto &l : live) EXPECT(a.free(l.first));
+  EXPECT(a.used() == 0 && a.live_allocations() == 0);
+  EXPECT(a.largest_free_block() == (2u << 20));
+}
+
+static void test_allocator_is_deterministic() {
+  // Two instances fed the same call sequence return the same offsets: what makes the heap symmetric.
+  Pow2Allocator a(1 << 22), b(1 << 22);
+  std::mt19937 rng(11);
+  std::vector<size_t> held;
+  for (int step = 0; step < 5000; ++step) {
+    if (held.empty() || rng() % 2) {
+      const size_t want = 1 + rng() % 9000;
+      const size_t oa = a.alloc(want), ob = b.alloc(want);
+      EXPECT(oa == ob);
+      if (oa != Pow2Allocator::kNull) held.push_back(oa);
+    } else {
+      const size_t i = rng() % held.size();
+      EXPECT(a.free(held[i]) == b.free(held[i]));
+      held[i] = held.back();
+      held.pop_back();
+    }
+  }
+}
+
+static void test_team_math() {
+  const TeamTriplet world{0, 1, 8};
+  SplitPlan p = plan_split(world, 8, 8, 1, 2, 4);   // {1, 3, 5, 7}
+  EXPECT(p.ok && p.world.pe_start == 1 && p.world.stride == 2 && p.world.size == 4);
+  EXPECT(p.world.pe_in_team(5) == 2 && p.world.pe_in_team(4) == -1 && p.world.pe_in_world(3) == 7);
+  EXPECT(translate_pe(p.world, 3, world) == 7 && translate_pe(world, 6, p.world) == -1);
+  SplitPlan q = plan_split(p.world, 4, 8, 1, 2, 2);  // members 1 and 3 of the parent: world {3, 7}
+  EXPECT(q.ok && q.world.pe_start == 3 && q.world.stride == 4 && q.world.size == 2);
+  EXPECT(!plan_split(world, 8, 8, 0, 0, 2).ok);      // stride < 1
+  EXPECT(!plan_split(world, 8, 8, 6, 2, 3).ok);      // runs past the parent
+  EXPECT(!plan_split(world, 8, 8, -1, 1, 2).ok);
+  TeamSlots s(40);
+  EXPECT(s.in_use() == 0 && s.capacity() == 40);
+  EXPECT(s.take(0));                                 // the runtime reserves slot 0 for the world team
+  std::vector<uint64_t> masks = {s.mask(), s.mask() & ~uint64_t(2)};
+  EXPECT(TeamSlots::lowest_common(masks) == 2);      // slot 0 is taken everywhere, slot 1 on one member
+  EXPECT(s.take(2) && !s.take(2) && s.in_use() == 2);
+  s.release(2);
+  EXPECT(s.take(2));
+  EXPECT(!s.take(40) && !s.take(-1));
+  EXPECT(TeamSlots::lowest_common({0x4, 0x8}) == -1);
+}
+
+static void test_config() {
+  EXPECT(parse_size("64M") == (size_t(64) << 20) && parse_size("0x100") == 256 && parse_size("2G") == (size_t(2) << 30));
+  bool threw = false;
+  try { parse_size("12Q"); } catch (const std::invalid_argument &) { threw = true; }
+  EXPECT(threw);
+  Config c = Config::from_env({{"ROCSHMEM_HEAP_SIZE", "8M"}, {"ROCSHMEM_MAX_NUM_TEAMS", "12"}});
+  EXPECT(c.heap_size == (size_t(8) << 20) && c.max_teams == 12);
+  c.validate();
+  threw = false;
+  try { Config::from_env({{"ROCSHMEM_WAIT_TIMEOUT_MS", "0"}}).validate(); } catch (const std::invalid_argument &) { threw = true; }
+  EXPECT(threw);
+}
+
+static void test_file_bootstrap_between_threads(const std::string &dir) {
+  // Four "ranks" as threads of this process, each with its own FileBootstrap over one directory: allgather,
+  // barrier and a group allgather, repeated so that the per-tag sequence numbers are exercised.
+  constexpr int kRanks = 4;
+  std::atomic<int> bad{0};
+  std::vector<std::thread> threads;
+  for (int r = 0; r < kRanks; ++r) {
+    threads.emplace_back([&, r] {
+      try {
+        FileBootstrap bs(dir, r, kRanks);
+        bs.set_timeout_ms(20000);
+        for (int round = 0; round < 5; ++round) {
+          int mine = 100 * round + r, all[kRanks] = {};
+          bs.allgather("ag", &mine, all, sizeof(int));
+          for (int i = 0; i < kRanks; ++i) bad += all[i] != 100 * round + i;
+          bs.barrier("bar");
+          if (r % 2 == 1) {   // group of the odd ranks
+            int pair[2] = {};
+            bs.allgather_group("odd", {1, 3}, r / 2, &mine, pair, sizeof(int));
+            bad += pair[0] != 100 * round + 1 || pair[1] != 100 * round + 3;
+          }
+        }
+        // a key nobody writes: the bounded get reports instead of hanging
+        bool threw = false;
+        try { bs.get("never-" + std::to_string(r), 50); } catch (const BootstrapError &) { threw = true; }
+        bad += !threw;
+      } catch (const std::exception &e) {
+        std::fprintf(stderr, "rank %d: %s\n", r, e.what());
+        ++bad;
+      }
+    });
+  }
+  for (auto &t : threads) t.join();
+  EXPECT(bad.load() == 0);
+}
+
+int main(int argc, char **argv) {
+  if (argc < 2) {
+    std::fprintf(stderr, "usage: %s <scratch directory>\n", argv[0]);
+    return 2;
+  }
+  test_allocator_basic();
+  test_allocator_random_walk();
+  test_allocator_is_deterministic();
+  test_team_math();
+  test_config();
+  test_file_bootstrap_between_threads(argv[1]);
+  if (g_failures) {
+    std::fprintf(stderr, "%d check(s) failed\n", g_failures);
+    return 1;
+  }
+  std::printf("runtime unit tests: all passed\n");
+  return 0;
+}
