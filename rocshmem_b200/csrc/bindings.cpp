@@ -101,6 +101,8 @@ PYBIND11_MODULE(_C, m) {
   m.def("backend_name", [] { return std::string(Runtime::instance().mem().name()); });
   m.def("cuda_device_count", [] { return cuda_device_count(); });
   m.def("nvls_available", [] { return Runtime::instance().mc_base() != nullptr; });
+  m.def("check_canaries", [] { return Runtime::instance().check_canaries(); });
+  m.def("internal_guard_offsets", [] { return Runtime::instance().layout().guards; });
   m.def("dump_stats", [] { host::dump_stats(); });
   m.def("reset_stats", [] { host::reset_stats(); });
   m.def("device_stats", [](int local) { return Runtime::instance().read_stats(local); }, py::arg("local") = -1);

@@ -31,9 +31,11 @@ std::mutex &module_mutex() {
 InternalLayout InternalLayout::build(const Config &cfg) {
   InternalLayout l;
   size_t off = 0;
-  auto take = [&off](size_t bytes) {
+  auto take = [&off, &l](size_t bytes) {
     size_t at = off;
     off = align_up(off + bytes, 256);
+    l.guards.push_back(off);
+    off += kGuardBytes;
     return at;
   };
   l.error = take(sizeof(rocshmem_error_record));
@@ -138,6 +140,9 @@ void Runtime::init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local
     handles_[pe] = mem_->create(stride_, multi_process);
     mem_->map(heap_base(pe), handles_[pe]);
     mem_->zero(internal_base(pe), layout_.total);
+    std::vector<unsigned long long> pattern(InternalLayout::kGuardBytes / sizeof(unsigned long long),
+                                            InternalLayout::kGuardWord);
+    for (size_t g : layout_.guards) mem_->write(internal_base(pe) + g, pattern.data(), InternalLayout::kGuardBytes);
   }
   if (multi_process) {
     for (int l = 0; l < n_local_; ++l) {
@@ -308,9 +313,32 @@ void Runtime::set_wait_timeout_ms(uint64_t ms) {
   upload_states();
 }
 
+int Runtime::check_canaries() {
+  std::lock_guard<std::recursive_mutex> g(mu_);
+  if (!inited_) return 0;
+  int bad = 0;
+  std::vector<unsigned long long> got(InternalLayout::kGuardBytes / sizeof(unsigned long long));
+  for (int l = 0; l < n_local_; ++l) {
+    for (size_t off : layout_.guards) {
+      mem_->read(got.data(), internal_base(first_pe_ + l) + off, InternalLayout::kGuardBytes);
+      for (unsigned long long w : got) {
+        if (w != InternalLayout::kGuardWord) {
+          ++bad;
+          break;
+        }
+      }
+    }
+  }
+  return bad;
+}
+
 void Runtime::finalize() {
   std::lock_guard<std::recursive_mutex> g(mu_);
   if (!inited_) return;
+  if (int bad = check_canaries()) {
+    std::fprintf(stderr, "[rocshmem pe %d] finalize: %d guard region(s) of the internal heap area were overwritten\n",
+                 first_pe_, bad);
+  }
   // Everybody stops using peers' memory before anything is unmapped.
   try {
     ops_->quiet(default_ctx_);

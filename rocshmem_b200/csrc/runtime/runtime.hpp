@@ -58,6 +58,11 @@ struct InternalLayout {
   size_t error = 0, stats = 0, teams = 0, ctxs = 0, ctx_free_mask = 0, barrier_flags = 0,
          coll_flags = 0, lib_flags = 0, lib_state = 0, proxy = 0, host_slots = 0, scratch = 0;
   size_t total = 0;
+  // A 256-byte guard filled with a fixed pattern follows every sub-region; a write that runs past the end of a
+  // flag or descriptor array lands there and is reported by Runtime::check_canaries().
+  std::vector<size_t> guards;
+  static constexpr size_t kGuardBytes = 256;
+  static constexpr unsigned long long kGuardWord = 0xC0DEC0DEC0DEC0DEull;
   static InternalLayout build(const Config &cfg);
 };
 
@@ -71,6 +76,8 @@ class Runtime {
   // Collective over all processes of the bootstrap. n_local PEs are hosted by each process.
   void init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local, int device);
   void finalize();
+  // Number of guard regions (over all local PEs) whose pattern has been overwritten; 0 in a healthy run.
+  int check_canaries();
 
   // Identity. In multi-PE-per-process mode the "current" local PE is a thread-local selector.
   int n_pes() const { return n_pes_; }

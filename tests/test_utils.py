@@ -69,3 +69,25 @@ def test_trace_range_is_a_no_op_without_nvtx(monkeypatch):
     assert trace.nvtx_enabled()
     with trace.trace_range("still fine without a GPU"):
         pass
+
+
+def test_guard_regions_detect_an_overrun(shm_cpu):
+    """Every internal sub-region (flags, descriptors, ...) is followed by a guard pattern; a write past the end
+    of a region is reported by check_canaries() and at finalize."""
+    from rocshmem_b200 import runtime as rt
+    shm = shm_cpu
+    C = rt._C()
+    assert C.check_canaries() == 0
+    guards = C.internal_guard_offsets()
+    assert len(guards) >= 10 and all(g % 256 == 0 for g in guards)
+    a = shm.zeros(1024, torch.int32)       # ordinary use leaves the guards alone
+    shm.barrier_all()
+    assert C.check_canaries() == 0
+    internal = C.heap_base(1) + shm.heap_info()["size"]          # PE 1's internal area
+    word = rt.tensor_from_address(internal + guards[3] + 8, (1,), torch.int64)
+    saved = int(word[0])
+    word[0] = 12345
+    assert C.check_canaries() == 1
+    word[0] = saved
+    assert C.check_canaries() == 0
+    shm.free(a)
