@@ -217,3 +217,16 @@ struct Group {
 
 }  // namespace detail
 }  // namespace rocshmem
+
+// Debug print from device code, prefixed with the PE and the block; compiled in with -DROCSHMEM_DEBUG_PRINT and
+// a no-op otherwise. Device printf emits each call atomically, so no print lock is needed (the reference
+// serialises GPU_DPRINTF with a device-wide lock, src/util.hpp:51-71,145-168).
+#ifdef ROCSHMEM_DEBUG_PRINT
+#include <cstdio>
+#define ROCSHMEM_GPU_DPRINTF(fmt, ...) \
+  printf("[rocshmem pe %d block %u] " fmt, ::rocshmem::detail::st().my_pe, blockIdx.x, ##__VA_ARGS__)
+#else
+#define ROCSHMEM_GPU_DPRINTF(fmt, ...) \
+  do {                                 \
+  } while (0)
+#endif
