@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 EX = os.path.join(ROOT, "examples")
-PROGS = ["getmem", "put_signal", "broadcast", "alltoall", "allreduce"]
+PROGS = ["getmem", "put_signal", "broadcast", "alltoall", "allreduce", "team_reduce"]
 
 
 @pytest.fixture(scope="module")
@@ -48,7 +48,7 @@ def test_cuda_example_two_pes(built, prog, tmp_path):
     run(["--no-python", os.path.join(built, prog)], 2, tmp_path)
 
 
-@pytest.mark.parametrize("script", ["allreduce.py", "moe_layer.py"])
+@pytest.mark.parametrize("script", ["allreduce.py", "moe_layer.py", "tp_mlp.py"])
 def test_python_example(script, tmp_path):
     world = 2 if torch.cuda.device_count() >= 2 else 1
     cmd = [os.path.join(EX, "python", script)]
