@@ -66,6 +66,10 @@ class CudaHostOps final : public HostOps {
     check(cudaHostAlloc(reinterpret_cast<void **>(&slots_), 4096, cudaHostAllocMapped | cudaHostAllocPortable),
           "pinned result slots");
     check(cudaStreamCreateWithFlags(&poll_stream_, cudaStreamNonBlocking), "poll stream");
+    // Load the helper kernel now. With lazy module loading its first launch could otherwise have to wait for
+    // running kernels, and the proxy thread launches it precisely while a kernel waits for its result.
+    cudaFuncAttributes attr;
+    check(cudaFuncGetAttributes(&attr, host_amo_kernel), "helper kernel load");
   }
   ~CudaHostOps() override {
     if (slots_) cudaFreeHost(slots_);

@@ -47,13 +47,15 @@ void Proxy::start() {
   ring_.read_index = w;
   ring_.status = w + 8;
   ring_.fetched = w + 8 + cap;
-  // The reservation counter is bumped with device atomics, so it lives in device memory next to
-  // the device-visible copy of the ring header.
+  // The reservation counter is bumped with device atomics, so it lives in device memory next to the
+  // device-visible copy of the ring header. All PEs of this process produce into the one ring, so they
+  // share one counter (the first local PE's); a counter per PE would hand the same slots out twice.
+  char *counter = rt_->internal_base(rt_->first_pe()) + rt_->layout().proxy + 128;
+  rt_->mem().zero(counter, 8);
   for (int l = 0; l < rt_->n_local(); ++l) {
     char *ib = rt_->internal_base(rt_->first_pe() + l) + rt_->layout().proxy;
     rocshmem_proxy_ring dev = ring_;
-    dev.write_index = reinterpret_cast<unsigned long long *>(ib + 128);
-    rt_->mem().zero(ib + 128, 8);
+    dev.write_index = reinterpret_cast<unsigned long long *>(counter);
     rt_->mem().write(ib, &dev, sizeof(dev));
   }
   ring_.write_index = nullptr;

@@ -1,0 +1,89 @@
+"""Reverse-offload path on the GPU (ROCSHMEM_USE_PROXY=1): thread-scope puts, gets and atomics issued by device
+code are written as commands into the pinned-host ring and executed by the host proxy thread, which completes
+them while the kernel waits (reference: src/reverse_offload/context_ro_device.cpp:457-664, backend_ro.cpp:281-294)."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+NPES = 2
+RMA_PUT, RMA_GET = 0, 2
+SC_THREAD = 0
+A_FADD = 0
+PROXY_CMD = 28  # ROCSHMEM_STAT_PROXY_CMD
+
+
+@pytest.fixture(scope="module")
+def env():
+    import rocshmem_b200 as shm
+    from rocshmem_b200 import _native
+    if shm.is_initialized():
+        shm.finalize()
+    shm.init(n_local=NPES, heap_size="64M", ROCSHMEM_WAIT_TIMEOUT_MS=5000, ROCSHMEM_USE_PROXY=1)
+    yield shm, _native.load_test_kernels()
+    torch.cuda.synchronize()
+    shm.finalize()
+
+
+def test_device_rma_and_atomics_through_the_ring(env):
+    from rocshmem_b200 import runtime as rt
+    shm, k = env
+    C = rt._C()
+    assert C.proxy_running()
+    side = torch.cuda.Stream()   # the kernel waits for the host thread, which works on streams of its own
+    nbytes, threads = 2048, 8
+    src = shm.zeros(nbytes, torch.uint8)
+    dst = shm.zeros(nbytes, torch.uint8)
+    pats = []
+    for l in range(NPES):
+        p = torch.randint(0, 256, (nbytes,), generator=torch.Generator().manual_seed(5 + l), dtype=torch.uint8)
+        pats.append(p)
+        shm.local_view(src, l).copy_(p.cuda())
+    torch.cuda.synchronize()
+    shm.barrier_all()
+    C.reset_stats()
+    for op, origin in ((RMA_PUT, lambda l: (l - 1) % NPES), (RMA_GET, lambda l: (l + 1) % NPES)):
+        for l in range(NPES):
+            shm.local_view(dst, l).zero_()
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            k.rma(op, SC_THREAD, dst.data_ptr(), src.data_ptr(), nbytes, 1, 0, threads, side.cuda_stream)
+        torch.cuda.synchronize()
+        err = shm.get_error()
+        assert err["count"] == 0, err
+        for l in range(NPES):
+            assert torch.equal(shm.local_view(dst, l).cpu(), pats[origin(l)]), (op, l)
+    executed = C.host_stats()[PROXY_CMD]
+    assert executed >= 2 * NPES * threads, executed     # every thread's put and get went through the host
+    for t in (dst, src):
+        shm.free(t)
+
+
+def test_device_atomics_through_the_ring_single_pe():
+    """Fetching atomics executed by the host thread while the kernel waits for the fetched value. One PE per
+    process here: the host's helper kernel has to run next to the waiting kernel, which a cooperative launch
+    (several PEs per process) does not allow."""
+    import rocshmem_b200 as shm
+    from rocshmem_b200 import _native, runtime as rt
+    if shm.is_initialized():
+        shm.finalize()
+    shm.init(n_local=1, heap_size="64M", ROCSHMEM_WAIT_TIMEOUT_MS=5000, ROCSHMEM_USE_PROXY=1)
+    try:
+        k = _native.load_test_kernels()
+        assert rt._C().proxy_running()
+        side = torch.cuda.Stream()
+        threads, iters = 8, 3
+        target = shm.zeros(1, torch.int64)
+        ret = shm.zeros(threads, torch.int64)
+        torch.cuda.synchronize()
+        with torch.cuda.stream(side):
+            k.amo(A_FADD, target.data_ptr(), ret.data_ptr(), iters, 1, threads, side.cuda_stream)
+        torch.cuda.synchronize()
+        err = shm.get_error()
+        assert err["count"] == 0, err
+        msgs = threads * iters
+        assert int(target.cpu()[0]) == 2 * msgs
+        assert int(ret.max().cpu()) == 2 * (msgs - 1)
+    finally:
+        torch.cuda.synchronize()
+        shm.finalize()
