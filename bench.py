@@ -109,8 +109,8 @@ class ClockSampler:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=TOKENS)
     ap.add_argument("--layout", default="compact", choices=["compact", "slotted"])
@@ -200,7 +200,6 @@ def main() -> None:
         ev[i][2].record(stream)
     torch.cuda.synchronize()
     shm.barrier_all()
-    clocks = sampler.stop() if rank == 0 else None
     phases = d.phase_times_us()
     launches = d.kernel_launches - launches_before
     disp_ms = sum(e[0].elapsed_time(e[1]) for e in ev)
@@ -250,6 +249,8 @@ def main() -> None:
     torch.cuda.synchronize()
     shm.barrier_all()
     e2e_s = max_over_ranks([time.perf_counter() - t0])[0]
+    # The sampler has been running since before the warm-up: it covers both timed regions.
+    clocks = sampler.stop() if rank == 0 else None
 
     # traffic accounting for GB/s (per rank, remote destinations only)
     ranks_of = torch.where(idx_cpu >= 0, idx_cpu // epr, torch.full_like(idx_cpu, -1))
