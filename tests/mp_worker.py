@@ -361,7 +361,60 @@ def proxy_collectives():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def ep_host():
+    """Expert-parallel dispatch / combine through the host API: layout and records against the reference routing,
+    then a round trip (identity experts) against the de-quantised input."""
+    from rocshmem_b200.ops import moe, moe_host
+    init("64M")
+    me, P = shm.my_pe(), shm.n_pes()
+    E, K, H, T = 4 * P, 3, 256, 37 + me
+    d = moe_host.HostEpDispatcher(E, K, H, max_tokens=64)
+    for rep in range(2):
+        routing = [moe.make_routing(37 + r, E, K, seed=10 * rep + r) for r in range(P)]
+        if rep == 1:
+            for idx, _ in routing:
+                idx[::4, -1] = -1
+        xs = [torch.randn(37 + r, H, generator=torch.Generator().manual_seed(100 * rep + r)).to(torch.bfloat16)
+              for r in range(P)]
+        idx, w = routing[me]
+        res = d.dispatch(xs[me].to(dev()), idx, w)
+        want_rows = moe.ref_dispatch([r[0] for r in routing], P, E)[me]
+        info = res.recv_info.cpu().tolist()
+        assert info[0] == len(want_rows)
+        pos = 0
+        for s in range(P):
+            mine = [t for ss, t in want_rows if ss == s]
+            assert info[1 + s] == pos and info[1 + P + s] == len(mine)
+            rows = slice(pos, pos + len(mine))
+            pos += len(mine)
+            if not mine:
+                continue
+            assert res.src_token()[rows].cpu().tolist() == mine and set(res.src_rank()[rows].cpu().tolist()) == {s}
+            q, sc = moe.ref_quantize_1x128(xs[s][mine])
+            assert torch.equal(res.recv_x[rows].cpu().view(torch.uint8), q.view(torch.uint8))
+            assert torch.allclose(res.recv_scales[rows].cpu(), sc)
+            src_idx, src_w = routing[s]
+            epr = E // P
+            want_local = torch.where(src_idx[mine] // epr == me, src_idx[mine] % epr, torch.full_like(src_idx[mine], -1))
+            want_local = torch.where(src_idx[mine] >= 0, want_local, torch.full_like(want_local, -1))
+            assert torch.equal(res.local_expert_idx()[rows].cpu(), want_local.to(torch.int32))
+            assert torch.equal(res.gate_weights()[rows].cpu(), src_w[mine])
+        per_expert = res.rows_per_expert().cpu().tolist()
+        assert sum(per_expert) == int((res.local_expert_idx()[:info[0]].cpu() >= 0).sum())
+        # identity experts: every rank returns the de-quantised rows it received
+        y = d.result_buffer()
+        n_rows = info[0]
+        y[:n_rows].copy_(moe.ref_dequantize_1x128(res.recv_x[:n_rows].cpu(), res.recv_scales[:n_rows].cpu()).to(torch.bfloat16).to(dev()))
+        out = d.combine(y, idx, w, xs[me].shape[0])
+        q, sc = moe.ref_quantize_1x128(xs[me])
+        xd = moe.ref_dequantize_1x128(q, sc).to(torch.bfloat16).float()
+        gate = torch.where(idx >= 0, w, torch.zeros_like(w)).sum(dim=1, keepdim=True)
+        assert torch.allclose(out.float(), xd * gate, rtol=2e-2, atol=2e-2), rep
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

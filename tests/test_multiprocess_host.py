@@ -31,3 +31,8 @@ def test_wait_family_between_processes():
 def test_proxy_ring_runs_host_collectives(world):
     """Reverse-offload command set beyond RMA: fence, P, broadcast, reduce, fcollect, alltoall."""
     assert_all_ok(run_ranks("proxy_collectives", world))
+
+
+@pytest.mark.parametrize("world", [2, 3])
+def test_expert_parallel_dispatch_combine_through_the_host_api(world):
+    assert_all_ok(run_ranks("ep_host", world))
