@@ -165,3 +165,39 @@ def reference_forward(x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: tor
         y = (h @ w2.t()).to(torch.bfloat16).float()
         out.index_add_(0, tok, y * w[tok, k].unsqueeze(1))
     return out
+
+
+class HostMoEFeedForward:
+    """The same layer over :class:`rocshmem_b200.ops.moe_host.HostEpDispatcher` with the experts evaluated by
+    ``torch.matmul``: host-API data movement, any backend (CPU shared memory included). The structure is that of
+    :class:`MoEFeedForward` (dispatch, per-expert rows, per-row gate-weighted reduction, unweighted combine), so
+    multi-process CPU tests cover the layer's logic; it is not a fast path."""
+
+    def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, max_tokens: int, seed: int = 0):
+        from ..ops import moe_host
+        self.d = moe_host.HostEpDispatcher(num_experts, top_k, hidden, max_tokens)
+        self.hidden, self.inter, self.top_k = hidden, inter, top_k
+        self.e_local = self.d.experts_per_rank
+        first = rt.my_pe() * self.e_local
+        self.weights = [expert_weights(first + e, hidden, inter, seed) for e in range(self.e_local)]
+
+    def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        res = self.d.dispatch(x, topk_idx, topk_weights)
+        rows = res.num_rows()
+        xin = moe.ref_dequantize_1x128(res.recv_x[:rows].cpu(), res.recv_scales[:rows].cpu()).to(torch.bfloat16).float()
+        local = res.local_expert_idx()[:rows].cpu()
+        gates = res.gate_weights()[:rows].cpu()
+        y_rows = torch.zeros((rows, self.hidden))
+        for e, (w13, w2) in enumerate(self.weights):
+            r, k = (local == e).nonzero(as_tuple=True)
+            if r.numel() == 0:
+                continue
+            hc = xin[r] @ w13.float().t()
+            h = (torch.nn.functional.silu(hc[:, :self.inter]) * hc[:, self.inter:]).to(torch.bfloat16).float()
+            y = (h @ w2.float().t()).to(torch.bfloat16).float()
+            y_rows.index_add_(0, r, y * gates[r, k].unsqueeze(1))
+        buf = self.d.result_buffer()
+        buf[:rows].copy_(y_rows.to(torch.bfloat16).to(buf.device))
+        return self.d.combine(buf, topk_idx, topk_weights, x.shape[0], weighted=False)
+
+    __call__ = forward

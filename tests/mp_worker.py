@@ -414,7 +414,28 @@ def ep_host():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def moe_layer_host():
+    """The MoE feed-forward layer over the host-API dispatcher against the single-process fp32 evaluation."""
+    from rocshmem_b200.models import moe_ffn
+    from rocshmem_b200.ops import moe
+    init("64M")
+    me, P = shm.my_pe(), shm.n_pes()
+    E, K, H, I, T = 2 * P, 2, 256, 128, 29 + 2 * me
+    layer = moe_ffn.HostMoEFeedForward(E, K, H, I, max_tokens=64, seed=9)
+    for rep in range(2):
+        x = torch.randn(T, H, generator=torch.Generator().manual_seed(50 * rep + me)).to(torch.bfloat16)
+        idx, w = moe.make_routing(T, E, K, seed=7 * rep + me)
+        if rep:
+            idx[::5, -1] = -1
+        out = layer(x.to(dev()), idx, w)
+        want = moe_ffn.reference_forward(x, idx, w, H, I, seed=9)
+        err = (out.float().cpu() - want).abs().max().item()
+        assert err <= 3e-2 * want.abs().max().item() + 0.02, (rep, err)
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

@@ -36,3 +36,7 @@ def test_proxy_ring_runs_host_collectives(world):
 @pytest.mark.parametrize("world", [2, 3])
 def test_expert_parallel_dispatch_combine_through_the_host_api(world):
     assert_all_ok(run_ranks("ep_host", world))
+
+
+def test_moe_layer_over_the_host_api():
+    assert_all_ok(run_ranks("moe_layer_host", 3))
