@@ -435,7 +435,44 @@ def moe_layer_host():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def parallel_layout():
+    """A 2 x 2 process grid: row teams (tensor / expert parallel), column teams (data parallel), a reduction over
+    each, and a pipeline channel between the first and the last PE."""
+    from rocshmem_b200.parallel import layout as pl, pipeline
+    init("16M")
+    me, n = shm.my_pe(), shm.n_pes()
+    assert n == 4
+    lay = pl.ParallelLayout(inner=2)
+    assert (lay.row, lay.col, lay.dp, lay.inner) == (me // 2, me % 2, 2, 2)
+    assert lay.inner_team.n_pes() == 2 and lay.inner_team.my_pe() == me % 2
+    assert lay.dp_team.n_pes() == 2 and lay.dp_team.my_pe() == me // 2
+    assert lay.inner_team.translate_pe(1, shm.team_world()) == (me // 2) * 2 + 1
+    assert lay.dp_team.translate_pe(1, shm.team_world()) == 2 + me % 2
+    src = shm.zeros(8, torch.int64)
+    dst = shm.zeros(8, torch.int64)
+    src.fill_(1 << me)
+    shm.barrier_all()
+    assert coll.reduce(dst, src, shm.OP_SUM, lay.inner_team) == 0
+    row = me // 2
+    assert int(dst.cpu()[0]) == (1 << (2 * row)) + (1 << (2 * row + 1))
+    assert coll.reduce(dst, src, shm.OP_SUM, lay.dp_team) == 0
+    assert int(dst.cpu()[0]) == (1 << (me % 2)) + (1 << (2 + me % 2))
+    shm.barrier_all()
+    # pipeline: PE 0 -> PE 3, three messages in order, back-pressure through the acknowledgement counter
+    ch = pipeline.P2PChannel((16,), torch.float32, src_pe=0, dst_pe=3)
+    shm.barrier_all()
+    for i in range(3):
+        if me == 0:
+            ch.send(torch.full((16,), float(i + 1)).to(dev()))
+        elif me == 3:
+            got = ch.recv()
+            assert torch.all(got.cpu() == float(i + 1)), (i, got)
+    shm.barrier_all()
+    lay.destroy()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

@@ -40,3 +40,7 @@ def test_expert_parallel_dispatch_combine_through_the_host_api(world):
 
 def test_moe_layer_over_the_host_api():
     assert_all_ok(run_ranks("moe_layer_host", 3))
+
+
+def test_process_grid_teams_and_pipeline_channel():
+    assert_all_ok(run_ranks("parallel_layout", 4))
