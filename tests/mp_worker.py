@@ -472,7 +472,51 @@ def parallel_layout():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def stress_host():
+    """Back-to-back collectives without barriers in between, repeated team creation and destruction, and many
+    context create / destroy cycles (the reference's SOS tests shmem_team_b2b_collectives, shmem_team_reuse_teams,
+    many-ctx)."""
+    init("16M")
+    me, n = shm.my_pe(), shm.n_pes()
+    world = shm.team_world()
+    src = shm.zeros(64 * n, torch.int64)
+    dst = shm.zeros(64 * n, torch.int64)
+    for it in range(30):
+        src.copy_((torch.arange(64 * n) + it + 100 * me).to(dev()))
+        if shm.is_cuda():
+            torch.cuda.synchronize()
+        assert coll.reduce(dst[:64], src[:64], shm.OP_SUM, world) == 0
+        assert torch.equal(dst.cpu()[:64], (torch.arange(64) + it) * n + 100 * sum(range(n)))
+        assert coll.fcollect(dst, src[:64], world) == 0
+        got = dst.cpu().view(n, 64)
+        assert all(int(got[r][5]) == 5 + it + 100 * r for r in range(n))
+        assert coll.broadcast(dst[:64], src[:64], it % n, world) == 0
+        if me != it % n:
+            assert int(dst.cpu()[7]) == 7 + it + 100 * (it % n)
+    before = shm.runtime._C().num_user_teams()
+    for it in range(25):
+        half = world.split_strided(0, 1, max(1, n // 2))
+        rest = world.split_strided(max(1, n // 2), 1, n - max(1, n // 2)) if n > 1 else None
+        mine = half if half.valid else rest
+        if mine is not None and mine.valid:
+            assert coll.reduce(dst[:8], src[:8], shm.OP_MAX, mine) == 0
+        for t in (half, rest):
+            if t is not None and t.valid:
+                t.destroy()
+    assert shm.runtime._C().num_user_teams() == before
+    shm.barrier_all()   # the team reductions above write dst too
+    for it in range(100):
+        c = shm.Context()
+        shm.putmem(dst[:8], torch.full((8,), it, dtype=torch.int64).to(dev()), (me + 1) % n, ctx=c)
+        c.quiet()
+        c.destroy()
+    shm.barrier_all()
+    assert int(dst.cpu()[0]) == 99
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

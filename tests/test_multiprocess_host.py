@@ -44,3 +44,7 @@ def test_moe_layer_over_the_host_api():
 
 def test_process_grid_teams_and_pipeline_channel():
     assert_all_ok(run_ranks("parallel_layout", 4))
+
+
+def test_back_to_back_collectives_team_reuse_and_many_contexts():
+    assert_all_ok(run_ranks("stress_host", 3, timeout=240))
