@@ -9,6 +9,7 @@
 #include "kernels/kernels.hpp"
 // Bindings of the MoE and GEMM kernels live beside those kernels' launchers.
 namespace rocshmem { namespace kernels { void bind_ep(pybind11::module_ &m); void bind_gemm(pybind11::module_ &m); } }
+#include "rocshmem/coalesce.h"
 #include "rocshmem/rocshmem_host.h"
 #include "runtime/allocator.hpp"
 #include "runtime/bootstrap.hpp"
@@ -312,6 +313,33 @@ PYBIND11_MODULE(_C, m) {
   m.def("proxy_counts", [](uintptr_t p) {
     return py::make_tuple(ptr_of<Proxy>(p)->executed(), ptr_of<Proxy>(p)->dropped());
   });
+  m.def("proxy_set_coalesce", [](uintptr_t p, bool on) { ptr_of<Proxy>(p)->set_coalesce(on); });
+  m.def("proxy_merged", [](uintptr_t p) { return ptr_of<Proxy>(p)->merged(); });
+  // The lane-mask arithmetic of the warp coalescer, evaluated for every lane of one warp.
+  m.def("coalesce_warp_plan", [](unsigned active, std::vector<std::tuple<int, uint64_t, uint64_t, uint64_t>> msgs) {
+    if (msgs.size() != 32) throw std::invalid_argument("coalesce_warp_plan wants 32 lane messages");
+    unsigned cont = 0;
+    auto at = [&](int l) {
+      coalesce::Msg m{std::get<0>(msgs[l]), std::get<1>(msgs[l]), std::get<2>(msgs[l]), std::get<3>(msgs[l])};
+      return m;
+    };
+    for (int l = 0; l < 32; ++l) {
+      if (!(active & (1u << l))) continue;
+      int p = coalesce::previous_active(active, l);
+      if (p >= 0 && coalesce::continues(at(p), at(l))) cont |= 1u << l;
+    }
+    std::vector<int> runs(32);
+    for (int l = 0; l < 32; ++l) runs[l] = coalesce::run_length(active, cont, l);
+    return runs;
+  });
+  m.def("coalesce_merge_runs", [](std::vector<std::tuple<int, uint64_t, uint64_t, uint64_t>> msgs) {
+    std::vector<coalesce::Msg> m;
+    for (auto &t : msgs) m.push_back({std::get<0>(t), std::get<1>(t), std::get<2>(t), std::get<3>(t)});
+    size_t n = coalesce::merge_runs(m.data(), m.size());
+    std::vector<std::tuple<int, uint64_t, uint64_t, uint64_t>> out;
+    for (size_t i = 0; i < n; ++i) out.emplace_back(m[i].pe, m[i].dst, m[i].src, m[i].size);
+    return out;
+  });
 
   // ---- pieces exposed for unit tests ----------------------------------------------------------------------
   m.def("parse_size", [](const std::string &s) { return parse_size(s); });
@@ -327,6 +355,7 @@ PYBIND11_MODULE(_C, m) {
     d["debug"] = c.debug;
     d["use_proxy"] = c.use_proxy;
     d["proxy_queue_size"] = c.proxy_queue_size;
+    d["proxy_coalesce"] = c.proxy_coalesce;
     d["enable_nvls"] = c.enable_nvls;
     d["backend"] = c.backend;
     return d;

@@ -17,6 +17,7 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include "../coalesce.h"
 #include "state.cuh"
 
 namespace rocshmem {
@@ -141,6 +142,26 @@ __device__ inline unsigned long long proxy_submit(unsigned type, int pe, const v
   return fetched;
 }
 
+// A thread-level put or get through the proxy. With coalescing on, lanes whose messages form one
+// contiguous run to one PE send a single command from the first lane of the run; the others wait for it
+// at the warp barrier, so a blocking call still returns only after its bytes have been moved.
+__device__ inline void proxy_rma(unsigned type, int pe, void *dest, const void *source, size_t bytes,
+                                 bool blocking) {
+  bool ok;
+  if (!(st().use_proxy & 2)) {
+    proxy_submit(type, pe, dest, source, bytes, 0, 0, 1, blocking, &ok);
+    return;
+  }
+  const unsigned active = __activemask();
+  coalesce::Msg m{pe, reinterpret_cast<unsigned long long>(dest),
+                  reinterpret_cast<unsigned long long>(source), static_cast<unsigned long long>(bytes)};
+  if (coalesce::warp_coalesce(m, active)) {
+    proxy_submit(type, m.pe, reinterpret_cast<void *>(m.dst), reinterpret_cast<const void *>(m.src), m.size, 0,
+                 0, 1, blocking, &ok);
+  }
+  __syncwarp(active);
+}
+
 // ---- put / get ----------------------------------------------------------------------------------------
 
 template <Scope S>
@@ -151,8 +172,7 @@ __device__ __forceinline__ void putmem(void *dest, const void *source, size_t by
   Group<S> g;
   if (g.leader()) stat_add(ROCSHMEM_STAT_BYTES_PUT, bytes);
   if (S == Scope::THREAD && st().use_proxy) {
-    bool ok;
-    proxy_submit(ROCSHMEM_PROXY_PUT, pe, dest, source, bytes, 0, 0, 1, blocking, &ok);
+    proxy_rma(ROCSHMEM_PROXY_PUT, pe, dest, const_cast<void *>(source), bytes, blocking);
     return;
   }
   copy_bytes<S>(remote_ptr(static_cast<char *>(dest), pe), source, bytes, g);
@@ -172,8 +192,7 @@ __device__ __forceinline__ void getmem(void *dest, const void *source, size_t by
   Group<S> g;
   if (g.leader()) stat_add(ROCSHMEM_STAT_BYTES_GET, bytes);
   if (S == Scope::THREAD && st().use_proxy) {
-    bool ok;
-    proxy_submit(ROCSHMEM_PROXY_GET, pe, dest, source, bytes, 0, 0, 1, true, &ok);
+    proxy_rma(ROCSHMEM_PROXY_GET, pe, dest, source, bytes, true);
     return;
   }
   copy_bytes<S>(dest, remote_ptr(static_cast<const char *>(source), pe), bytes, g);

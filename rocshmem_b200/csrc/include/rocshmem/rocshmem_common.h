@@ -250,7 +250,8 @@ struct rocshmem_device_state {
   int max_ctxs;
   unsigned long long wait_timeout_ns;  // budget of every device-side wait
   int debug_checks;                    // 1: validate pe / symmetric addresses on the device
-  int use_proxy;                       // 1: route thread-level RMA/AMO through the host proxy
+  int use_proxy;                       // bit 0: route thread-level RMA/AMO through the host proxy;
+                                       // bit 1: coalesce contiguous messages of neighbouring lanes first
   int device_ordinal;                  // CUDA device that hosts this PE
 };
 

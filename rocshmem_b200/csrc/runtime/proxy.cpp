@@ -8,6 +8,7 @@
 #include <stdexcept>
 
 #include "host_ops.hpp"
+#include "rocshmem/coalesce.h"
 #include "runtime.hpp"
 
 namespace rocshmem {
@@ -62,6 +63,7 @@ void Proxy::start() {
   read_ = 0;
   host_write_.store(0);
   stop_.store(false);
+  coalesce_.store(rt_->config().proxy_coalesce != 0);
   running_.store(true);
   thread_ = std::thread([this] { run(); });
 }
@@ -121,18 +123,45 @@ void Proxy::run() {
       dropped_count_.fetch_add(1);
       if (cmd.status_slot < 0) __atomic_store_n(&slot.valid, 0u, __ATOMIC_RELEASE);
     } else {
+      // Commands behind this one that continue it (published already, same kind and PE, equal sizes, both
+      // addresses following on) are executed as part of it and then acknowledged one by one.
+      unsigned extra = 0;
+      if (coalesce_.load(std::memory_order_relaxed) &&
+          (cmd.type == ROCSHMEM_PROXY_PUT || cmd.type == ROCSHMEM_PROXY_GET)) {
+        coalesce::Msg last{cmd.pe, cmd.dst, cmd.src, cmd.size};
+        while (extra + 1 < ring_.capacity && extra < 63) {
+          rocshmem_proxy_cmd &next = ring_.cmds[(read_ + extra + 1) % ring_.capacity];
+          if (__atomic_load_n(&next.valid, __ATOMIC_ACQUIRE) != 1 || next.type != cmd.type) break;
+          coalesce::Msg m{next.pe, next.dst, next.src, next.size};
+          if (!coalesce::continues(last, m)) break;
+          __atomic_store_n(&next.valid, 2u, __ATOMIC_RELAXED);
+          cmd.size += m.size;
+          last = m;
+          ++extra;
+        }
+      }
       execute(cmd, seq);
-      if (cmd.status_slot < 0) {
-        __atomic_store_n(&slot.valid, 0u, __ATOMIC_RELEASE);
-      } else {
-        __atomic_store_n(const_cast<unsigned long long *>(&ring_.status[cmd.status_slot]),
-                         static_cast<unsigned long long>(seq), __ATOMIC_RELEASE);
+      retire(slot, cmd.status_slot, seq);
+      for (unsigned e = 1; e <= extra; ++e) {
+        rocshmem_proxy_cmd &next = ring_.cmds[(read_ + e) % ring_.capacity];
+        retire(next, next.status_slot, seq + e);
       }
       executed_.fetch_add(1);
+      merged_.fetch_add(extra);
+      read_ += extra;
     }
     ++read_;
     __atomic_store_n(const_cast<unsigned long long *>(ring_.read_index),
                      static_cast<unsigned long long>(read_), __ATOMIC_RELEASE);
+  }
+}
+
+void Proxy::retire(volatile rocshmem_proxy_cmd &slot, int status_slot, uint64_t seq) {
+  if (status_slot < 0) {
+    __atomic_store_n(const_cast<unsigned int *>(&slot.valid), 0u, __ATOMIC_RELEASE);
+  } else {
+    __atomic_store_n(const_cast<unsigned long long *>(&ring_.status[status_slot]),
+                     static_cast<unsigned long long>(seq), __ATOMIC_RELEASE);
   }
 }
 

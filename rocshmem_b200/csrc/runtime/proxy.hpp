@@ -42,6 +42,11 @@ class Proxy {
   void inject_drop(int n) { drop_.store(n); }
   void inject_delay_ms(int ms) { delay_ms_.store(ms); }
 
+  // Merging of consecutive commands that continue one another (same type and PE, equal sizes, both
+  // addresses following on): the consumer executes the run as one transfer. On by ROCSHMEM_USE_WF_COAL.
+  void set_coalesce(bool on) { coalesce_.store(on); }
+  uint64_t merged() const { return merged_.load(); }
+
   uint64_t executed() const { return executed_.load(); }
   uint64_t dropped() const { return dropped_count_.load(); }
   const rocshmem_proxy_ring &ring() const { return ring_; }
@@ -49,6 +54,7 @@ class Proxy {
  private:
   void run();
   void execute(rocshmem_proxy_cmd &cmd, uint64_t seq);
+  void retire(volatile rocshmem_proxy_cmd &slot, int status_slot, uint64_t seq);
 
   Runtime *rt_;
   rocshmem_proxy_ring ring_{};
@@ -62,6 +68,8 @@ class Proxy {
   std::atomic<int> delay_ms_{0};
   std::atomic<uint64_t> executed_{0};
   std::atomic<uint64_t> dropped_count_{0};
+  std::atomic<bool> coalesce_{false};
+  std::atomic<uint64_t> merged_{0};       // commands that travelled inside an earlier command
   uint64_t read_ = 0;
   std::atomic<uint64_t> host_write_{0};  // reservation counter of the host-side producer
 };

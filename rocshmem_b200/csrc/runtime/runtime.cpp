@@ -301,7 +301,8 @@ void Runtime::build_states() {
     s.wait_timeout_ns = cfg_.wait_timeout_ms * 1000000ull;
     s.device_ordinal = device_;
     s.debug_checks = cfg_.debug_checks;
-    s.use_proxy = (proxy_ && proxy_->running()) ? cfg_.use_proxy : 0;
+    // Bit 0: thread-level RMA / atomics go through the proxy; bit 1: lanes coalesce their messages first.
+    s.use_proxy = (proxy_ && proxy_->running() && cfg_.use_proxy) ? (1 | (cfg_.proxy_coalesce ? 2 : 0)) : 0;
   }
 }
 
