@@ -11,6 +11,7 @@
 namespace rocshmem { namespace kernels { void bind_ep(pybind11::module_ &m); void bind_gemm(pybind11::module_ &m); } }
 #include "rocshmem/coalesce.h"
 #include "rocshmem/rocshmem_host.h"
+#include "rocshmem/slab.h"
 #include "runtime/allocator.hpp"
 #include "runtime/bootstrap.hpp"
 #include "runtime/config.hpp"
@@ -313,6 +314,22 @@ PYBIND11_MODULE(_C, m) {
   m.def("proxy_counts", [](uintptr_t p) {
     return py::make_tuple(ptr_of<Proxy>(p)->executed(), ptr_of<Proxy>(p)->dropped());
   });
+  // ---- slab ---------------------------------------------------------------------------------------------------
+  auto slab_of = [](uintptr_t base, uint64_t size) {
+    rocshmemx_slab_t s{reinterpret_cast<char *>(base), size,
+                       reinterpret_cast<unsigned long long *>(base + size)};
+    return s;
+  };
+  m.def("slab_create", [](size_t bytes) {
+    rocshmemx_slab_t s = rocshmemx_slab_create(bytes);
+    return py::make_tuple(reinterpret_cast<uintptr_t>(s.base), static_cast<uint64_t>(s.size));
+  });
+  m.def("slab_destroy", [slab_of](uintptr_t base, uint64_t size) { rocshmemx_slab_destroy(slab_of(base, size)); });
+  m.def("slab_reset", [slab_of](uintptr_t base, uint64_t size) { rocshmemx_slab_reset(slab_of(base, size)); });
+  m.def("slab_used", [slab_of](uintptr_t base, uint64_t size) { return rocshmemx_slab_used(slab_of(base, size)); });
+  m.def("slab_alloc_host", [slab_of](uintptr_t base, uint64_t size, size_t bytes, size_t align) {
+    return reinterpret_cast<uintptr_t>(rocshmemx_slab_alloc_host(slab_of(base, size), bytes, align));
+  });
   m.def("proxy_set_coalesce", [](uintptr_t p, bool on) { ptr_of<Proxy>(p)->set_coalesce(on); });
   m.def("proxy_merged", [](uintptr_t p) { return ptr_of<Proxy>(p)->merged(); });
   // The lane-mask arithmetic of the warp coalescer, evaluated for every lane of one warp.
@@ -348,6 +365,7 @@ PYBIND11_MODULE(_C, m) {
     py::dict d;
     d["heap_size"] = c.heap_size;
     d["scratch_size"] = c.scratch_size;
+    d["slab_size"] = c.slab_size;
     d["max_contexts"] = c.max_contexts;
     d["max_host_contexts"] = c.max_host_contexts;
     d["max_teams"] = c.max_teams;

@@ -25,6 +25,7 @@
 
 #include "rocshmem_common.h"
 #include "rocshmem_host.h"
+#include "slab.h"
 
 #if defined(__CUDACC__)
 #include "device/collectives.cuh"

@@ -75,6 +75,7 @@ Config Config::from_env(const std::map<std::string, std::string> &ov) {
   try {
     if (lookup(ov, "ROCSHMEM_HEAP_SIZE", &v)) c.heap_size = parse_size(v);
     if (lookup(ov, "ROCSHMEM_SCRATCH_SIZE", &v)) c.scratch_size = parse_size(v);
+    if (lookup(ov, "ROCSHMEM_SLAB_SIZE", &v)) c.slab_size = parse_size(v);
     if (lookup(ov, "ROCSHMEM_MAX_NUM_CONTEXTS", &v)) c.max_contexts = static_cast<int>(parse_int(v));
     if (lookup(ov, "ROCSHMEM_MAX_NUM_HOST_CONTEXTS", &v))
       c.max_host_contexts = static_cast<int>(parse_int(v));
@@ -102,6 +103,7 @@ void Config::validate() const {
   if (heap_size < ROCSHMEM_ALIGNMENT) fail("ROCSHMEM_HEAP_SIZE must be at least 128 bytes");
   if (heap_size > (size_t(1) << 40)) fail("ROCSHMEM_HEAP_SIZE above 1 TiB");
   if (scratch_size < (size_t(1) << 16)) fail("ROCSHMEM_SCRATCH_SIZE must be at least 64 KiB");
+  if (slab_size < 256) fail("ROCSHMEM_SLAB_SIZE must be at least 256 bytes");
   if (max_contexts < 1 || max_contexts > ROCSHMEM_CTX_SLOTS)
     fail("ROCSHMEM_MAX_NUM_CONTEXTS must be in [1, 4096]");
   if (max_host_contexts < 1 || max_host_contexts > 4096)

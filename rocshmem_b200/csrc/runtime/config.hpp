@@ -19,6 +19,7 @@ namespace rocshmem {
 struct Config {
   size_t heap_size = size_t(1) << 30;        // ROCSHMEM_HEAP_SIZE
   size_t scratch_size = size_t(64) << 20;    // ROCSHMEM_SCRATCH_SIZE (library-collective staging)
+  size_t slab_size = size_t(1) << 20;        // ROCSHMEM_SLAB_SIZE (default size of rocshmemx_slab_create)
   int max_contexts = 1024;                   // ROCSHMEM_MAX_NUM_CONTEXTS
   int max_host_contexts = 40;                // ROCSHMEM_MAX_NUM_HOST_CONTEXTS
   int max_teams = 40;                        // ROCSHMEM_MAX_NUM_TEAMS

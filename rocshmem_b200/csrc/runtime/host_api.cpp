@@ -12,6 +12,7 @@
 
 #include "host_ops.hpp"
 #include "rocshmem/rocshmem_host.h"
+#include "rocshmem/slab.h"
 #include "runtime.hpp"
 
 namespace rocshmem {
@@ -517,6 +518,55 @@ void rocshmemx_heap_read(void *host_dst, const void *heap_src, size_t bytes) {
   rt().mem().read(host_dst, heap_src, bytes);
 }
 void *rocshmemx_default_stream() { return rt().default_ctx()->stream; }
+
+// ---- slab (device-side bump allocation) ----------------------------------------------------------------
+
+namespace {
+unsigned long long slab_cursor_read(const rocshmemx_slab_t &s) {
+  unsigned long long v = 0;
+  rt().mem().read(&v, s.cursor, sizeof(v));
+  return v;
+}
+}  // namespace
+
+rocshmemx_slab_t rocshmemx_slab_create(size_t bytes) {
+  Runtime &r = rt();
+  if (bytes == 0) bytes = r.config().slab_size;
+  bytes = static_cast<size_t>(detail::slab_round_up(bytes, 256));
+  rocshmemx_slab_t s{nullptr, 0, nullptr};
+  // One heap object: the slab, then a 256-byte line that holds the cursor.
+  char *p = static_cast<char *>(r.malloc(bytes + 256));
+  if (!p) return s;
+  for (int l = 0; l < r.n_local(); ++l) {
+    r.mem().zero(static_cast<char *>(r.translate(p, r.first_pe() + l)) + bytes, 256);
+  }
+  s.base = p;
+  s.size = bytes;
+  s.cursor = reinterpret_cast<unsigned long long *>(p + bytes);
+  return s;
+}
+
+void rocshmemx_slab_destroy(rocshmemx_slab_t slab) {
+  if (slab.base) rt().free(slab.base);
+}
+
+void rocshmemx_slab_reset(rocshmemx_slab_t slab) {
+  if (slab.cursor) rt().mem().zero(slab.cursor, sizeof(unsigned long long));
+}
+
+size_t rocshmemx_slab_used(rocshmemx_slab_t slab) {
+  return slab.cursor ? static_cast<size_t>(slab_cursor_read(slab)) : 0;
+}
+
+void *rocshmemx_slab_alloc_host(rocshmemx_slab_t slab, size_t bytes, size_t align) {
+  if (!slab.base || align == 0 || (align & (align - 1)) != 0 || align > 256) return nullptr;
+  const unsigned long long cur = slab_cursor_read(slab);
+  const unsigned long long start = detail::slab_place(slab, cur, bytes, align);
+  if (start == ~0ull) return nullptr;
+  const unsigned long long next = start + bytes;
+  rt().mem().write(slab.cursor, &next, sizeof(next));
+  return slab.base + start;
+}
 
 }  // namespace rocshmem
 
