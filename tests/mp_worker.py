@@ -516,7 +516,37 @@ def stress_host():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def host_algorithms():
+    """Bruck and clustered schedules of alltoall / fcollect against the expected layout, for block sizes below and
+    at the plan's capacity."""
+    from rocshmem_b200.ops.host_algorithms import HostCollectivePlan, choose_algorithm, cluster_size
+    init("16M")
+    me, n = shm.my_pe(), shm.n_pes()
+    plan = HostCollectivePlan(max_block_bytes=96)
+    assert plan.cluster == cluster_size(n) and n % plan.cluster == 0
+    for elems in (1, 5, 12):                     # int64 blocks of 8, 40 and 96 bytes
+        src = shm.zeros(n * elems, torch.int64)
+        dst = shm.zeros(n * elems, torch.int64)
+        one = shm.zeros(elems, torch.int64)
+        src.copy_((1000 * me + torch.arange(n * elems)).to(dev()))
+        one.copy_((7000 * me + torch.arange(elems)).to(dev()))
+        want_a2a = torch.cat([1000 * p + me * elems + torch.arange(elems) for p in range(n)])
+        want_fc = torch.cat([7000 * p + torch.arange(elems) for p in range(n)])
+        for algo in ("linear", "bruck", "clustered", "auto"):
+            dst.zero_()
+            used = plan.alltoall(dst, src, algo)
+            assert torch.equal(dst.cpu(), want_a2a), (algo, used, elems, dst.cpu(), want_a2a)
+            dst.zero_()
+            used = plan.fcollect(dst, one, algo)
+            assert torch.equal(dst.cpu(), want_fc), (algo, used, elems, dst.cpu(), want_fc)
+    plan.destroy()
+    assert choose_algorithm(2, 8) == "linear" and choose_algorithm(8, 1 << 20) == "linear"
+    assert choose_algorithm(64, 8) in ("bruck", "clustered")
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

@@ -48,3 +48,8 @@ def test_process_grid_teams_and_pipeline_channel():
 
 def test_back_to_back_collectives_team_reuse_and_many_contexts():
     assert_all_ok(run_ranks("stress_host", 3, timeout=240))
+
+
+@pytest.mark.parametrize("world", [4, 6])
+def test_bruck_and_clustered_schedules_match_the_linear_ones(world):
+    assert_all_ok(run_ranks("host_algorithms", world, timeout=240))
