@@ -546,7 +546,60 @@ def host_algorithms():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def threads_host():
+    """Several host threads per process, each with its own context: an all-to-all of puts from every thread
+    (the reference's SOS test mt_a2a), a chain of waits where a thread of PE p waits for the matching thread of
+    PE p - 1 (thread_wait), and one large put / get pair (bigput / bigget)."""
+    import threading
+    init("160M")
+    me, n = shm.my_pe(), shm.n_pes()
+    T, W = 4, 32
+    dst = shm.zeros(n * T * W, torch.int64)      # [source pe][thread][W]
+    flags = shm.zeros(T, torch.int64)
+    errors = []
+    shm.barrier_all()
+
+    def work(t):
+        try:
+            ctx = shm.Context()
+            for j in range(n):
+                pe = (me + j) % n
+                val = torch.full((W,), 100 * me + t, dtype=torch.int64).to(dev())
+                shm.putmem(dst[(me * T + t) * W:(me * T + t + 1) * W], val, pe, ctx=ctx)
+            ctx.quiet()
+            # chain: PE 0 starts, everyone else waits for its predecessor's thread t, then passes on
+            if me > 0:
+                assert shm.wait_until(flags, shm.CMP_EQ, 1 + t, index=t) == 0
+            if me + 1 < n:
+                shm.atomic_swap(flags, 1 + t, me + 1, index=t, ctx=ctx)
+            ctx.destroy()
+        except Exception as e:  # noqa: BLE001 - reported below
+            errors.append((t, repr(e)))
+
+    threads = [threading.Thread(target=work, args=(t,)) for t in range(T)]
+    [t.start() for t in threads]
+    [t.join(120) for t in threads]
+    assert not errors, errors
+    shm.barrier_all()
+    got = dst.cpu().view(n, T, W)
+    for p in range(n):
+        for t in range(T):
+            assert torch.all(got[p, t] == 100 * p + t), (p, t, got[p, t][:4])
+    # one large transfer each way (32 MiB)
+    big = shm.zeros(4 << 20, torch.int64)
+    back = shm.zeros(4 << 20, torch.int64)
+    pattern = (torch.arange(4 << 20, dtype=torch.int64) * 3 + me).to(dev())
+    shm.putmem(big, pattern, (me + 1) % n)
+    shm.barrier_all()
+    left = (me - 1) % n
+    assert torch.equal(big.cpu(), torch.arange(4 << 20, dtype=torch.int64) * 3 + left)
+    shm.getmem(back, big, (me + 1) % n)
+    assert torch.equal(back.cpu(), torch.arange(4 << 20, dtype=torch.int64) * 3 + me)
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

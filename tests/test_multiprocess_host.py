@@ -53,3 +53,7 @@ def test_back_to_back_collectives_team_reuse_and_many_contexts():
 @pytest.mark.parametrize("world", [4, 6])
 def test_bruck_and_clustered_schedules_match_the_linear_ones(world):
     assert_all_ok(run_ranks("host_algorithms", world, timeout=240))
+
+
+def test_threads_per_process_all_to_all_wait_chain_and_large_transfers():
+    assert_all_ok(run_ranks("threads_host", 3, timeout=240))
