@@ -88,6 +88,7 @@ __device__ inline unsigned long long proxy_submit(unsigned type, int pe, const v
   SpinBudget budget(s.wait_timeout_ns);
   unsigned long long idx;
   unsigned slot;
+  const unsigned long long t_start = prof_now();
   // Reserve an index only once its slot is free (see Proxy::submit for the protocol).
   for (;;) {
     idx = ld_relaxed_sys(ring->write_index);
@@ -102,6 +103,8 @@ __device__ inline unsigned long long proxy_submit(unsigned type, int pe, const v
       return 0;
     }
   }
+  const unsigned long long t_slot = prof_now();
+  stat_add(ROCSHMEM_STAT_PROXY_SLOT_NS, t_slot - t_start);
   rocshmem_proxy_cmd *c = &ring->cmds[slot];
   c->type = type;
   c->pe = pe;
@@ -115,6 +118,8 @@ __device__ inline unsigned long long proxy_submit(unsigned type, int pe, const v
   __threadfence_system();
   c->valid = 1;
   __threadfence_system();
+  const unsigned long long t_packed = prof_now();
+  stat_add(ROCSHMEM_STAT_PROXY_PACK_NS, t_packed - t_slot);
   if (!blocking) {
     *ok = true;
     return 0;
@@ -128,6 +133,7 @@ __device__ inline unsigned long long proxy_submit(unsigned type, int pe, const v
       break;
     }
   }
+  stat_add(ROCSHMEM_STAT_PROXY_HOST_NS, prof_now() - t_packed);
   if (done) {
     __threadfence_system();
     fetched = ring->fetched[slot];
@@ -378,6 +384,7 @@ __device__ __forceinline__ int wait_until(T *ivar, int cmp, T value) {
   T seen = *p;
   if (!compare(seen, cmp, value)) {
     SpinBudget budget(st().wait_timeout_ns);
+    const unsigned long long t_start = prof_now();
     while (!compare(seen = *p, cmp, value)) {
       if (!budget.keep_going()) {
         unsigned long long e = 0, o = 0;
@@ -388,6 +395,7 @@ __device__ __forceinline__ int wait_until(T *ivar, int cmp, T value) {
         return ROCSHMEM_ERROR;
       }
     }
+    stat_add(ROCSHMEM_STAT_WAIT_NS, prof_now() - t_start);
   }
   __threadfence_system();
   return ROCSHMEM_SUCCESS;

@@ -93,6 +93,15 @@ __device__ __forceinline__ void stat_add(int id, unsigned long long n = 1) {
 #endif
 }
 
+// Time stamp for the *_NS counters: the global timer in profiling builds, 0 (and no timer read) otherwise.
+__device__ __forceinline__ unsigned long long prof_now() {
+#ifdef ROCSHMEM_PROFILE
+  return now_ns();
+#else
+  return 0;
+#endif
+}
+
 // ---- system-scope flag accesses -----------------------------------------------------------------
 
 __device__ __forceinline__ void st_release_sys(unsigned long long *p, unsigned long long v) {

@@ -170,6 +170,11 @@ enum rocshmem_stat_id {
   ROCSHMEM_STAT_FCOLLECT, ROCSHMEM_STAT_ALLTOALL, ROCSHMEM_STAT_CTX_CREATE,
   ROCSHMEM_STAT_CTX_DESTROY, ROCSHMEM_STAT_BYTES_PUT, ROCSHMEM_STAT_BYTES_GET,
   ROCSHMEM_STAT_PROXY_CMD, ROCSHMEM_STAT_TIMEOUTS,
+  // Nanoseconds spent by device threads, summed over threads (reference: the reverse-offload profiler's
+  // WAITING_ON_SLOT / PACK_QUEUE + THREAD_FENCE / WAITING_ON_HOST / SHMEM_WAIT buckets,
+  // src/reverse_offload/profiler.hpp:36-50).
+  ROCSHMEM_STAT_PROXY_SLOT_NS, ROCSHMEM_STAT_PROXY_PACK_NS, ROCSHMEM_STAT_PROXY_HOST_NS,
+  ROCSHMEM_STAT_WAIT_NS,
   ROCSHMEM_NUM_STATS
 };
 

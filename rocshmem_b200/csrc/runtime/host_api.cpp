@@ -124,7 +124,8 @@ static const char *stat_name(int i) {
       "put", "put_nbi", "p", "get", "get_nbi", "g", "put_warp", "put_block", "get_warp", "get_block",
       "put_signal", "signal_fetch", "amo_fetch", "amo_nofetch", "fence", "quiet", "wait", "test",
       "barrier", "sync", "broadcast", "reduce", "fcollect", "alltoall", "ctx_create", "ctx_destroy",
-      "bytes_put", "bytes_get", "proxy_cmd", "timeouts"};
+      "bytes_put", "bytes_get", "proxy_cmd", "timeouts", "proxy_slot_ns", "proxy_pack_ns", "proxy_host_ns",
+      "wait_ns"};
   return names[i];
 }
 
