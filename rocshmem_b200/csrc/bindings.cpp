@@ -290,7 +290,8 @@ PYBIND11_MODULE(_C, m) {
   });
   m.def("proxy_stop", [](uintptr_t p) { ptr_of<Proxy>(p)->stop(); });
   m.def("proxy_submit", [](uintptr_t p, unsigned type, int pe, uintptr_t dst, uintptr_t src, uint64_t size,
-                           uint64_t cond, unsigned op, unsigned dtype_size, bool blocking, uint64_t timeout_ms) {
+                           uint64_t cond, unsigned op, unsigned dtype_size, bool blocking, uint64_t timeout_ms,
+                           uint64_t team_slot) {
     rocshmem_proxy_cmd c;
     std::memset(&c, 0, sizeof(c));
     c.type = type;
@@ -301,6 +302,7 @@ PYBIND11_MODULE(_C, m) {
     c.cond = cond;
     c.op = op;
     c.dtype_size = dtype_size;
+    c.team_slot = team_slot;
     uint64_t fetched = 0;
     int rc;
     {
@@ -308,6 +310,12 @@ PYBIND11_MODULE(_C, m) {
       rc = ptr_of<Proxy>(p)->submit(c, blocking, &fetched, timeout_ms);
     }
     return py::make_tuple(rc, fetched);
+  }, py::arg("proxy"), py::arg("type"), py::arg("pe"), py::arg("dst"), py::arg("src"), py::arg("size"),
+     py::arg("cond"), py::arg("op"), py::arg("dtype_size"), py::arg("blocking"), py::arg("timeout_ms"),
+     py::arg("team_slot") = 0);
+  m.def("team_slot", [](uintptr_t t) {
+    HostTeam *ht = Runtime::instance().team_from_handle(team_of(t));
+    return ht ? ht->slot : -1;
   });
   m.def("proxy_inject_drop", [](uintptr_t p, int n) { ptr_of<Proxy>(p)->inject_drop(n); });
   m.def("proxy_inject_delay_ms", [](uintptr_t p, int ms) { ptr_of<Proxy>(p)->inject_delay_ms(ms); });
@@ -374,6 +382,7 @@ PYBIND11_MODULE(_C, m) {
     d["use_proxy"] = c.use_proxy;
     d["proxy_queue_size"] = c.proxy_queue_size;
     d["proxy_coalesce"] = c.proxy_coalesce;
+    d["proxy_collectives"] = c.proxy_collectives;
     d["enable_nvls"] = c.enable_nvls;
     d["backend"] = c.backend;
     return d;

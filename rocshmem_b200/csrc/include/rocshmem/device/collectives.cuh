@@ -123,6 +123,48 @@ __device__ inline void ctx_destroy(rocshmem_ctx_t *ctx) {
   __syncthreads();
 }
 
+// ---- collectives through the host proxy ------------------------------------------------------------------
+
+// With bit 2 of use_proxy set, a block-level collective is one blocking command: thread 0 submits it, the host
+// thread runs the host form of the collective for the team, the block waits (reference: ROContext's
+// collectives, src/reverse_offload/context_ro_tmpl_device.hpp:111-374). Needs one PE per process: the host
+// form acts for all PEs of its process at once.
+__device__ __forceinline__ bool proxy_collectives_on() { return (st().use_proxy & 4) != 0; }
+
+// Element type codes of the host engine (rocshmem_dtype in rocshmem_host.h).
+template <typename T> struct ProxyDtype;
+template <> struct ProxyDtype<signed char> { static constexpr int code = 0; };
+template <> struct ProxyDtype<char> { static constexpr int code = 0; };
+template <> struct ProxyDtype<unsigned char> { static constexpr int code = 1; };
+template <> struct ProxyDtype<short> { static constexpr int code = 2; };
+template <> struct ProxyDtype<unsigned short> { static constexpr int code = 3; };
+template <> struct ProxyDtype<int> { static constexpr int code = 4; };
+template <> struct ProxyDtype<unsigned int> { static constexpr int code = 5; };
+template <> struct ProxyDtype<long> { static constexpr int code = 6; };
+template <> struct ProxyDtype<long long> { static constexpr int code = 6; };
+template <> struct ProxyDtype<unsigned long> { static constexpr int code = 7; };
+template <> struct ProxyDtype<unsigned long long> { static constexpr int code = 7; };
+template <> struct ProxyDtype<float> { static constexpr int code = 8; };
+template <> struct ProxyDtype<double> { static constexpr int code = 9; };
+template <> struct ProxyDtype<__half> { static constexpr int code = 10; };
+template <> struct ProxyDtype<__nv_bfloat16> { static constexpr int code = 11; };
+
+// Block-collective. `pe` carries the root of a broadcast, `cond` the element type of a reduction.
+__device__ inline int proxy_collective(unsigned type, const rocshmem_team_dev *t, void *dest, const void *source,
+                                       unsigned long long size, int pe, unsigned long long cond, unsigned op) {
+  __shared__ int proxy_collective_rc;
+  __syncthreads();   // the block's earlier writes (and a previous call's result) are settled
+  if (block_tid() == 0) {
+    bool ok = false;
+    __threadfence_system();
+    unsigned long long status = proxy_submit(type, pe, dest, source, size, cond, op, 1, true, &ok,
+                                             static_cast<unsigned long long>(t->slot));
+    proxy_collective_rc = (ok && status == 0) ? ROCSHMEM_SUCCESS : ROCSHMEM_ERROR;
+  }
+  __syncthreads();
+  return proxy_collective_rc;
+}
+
 // ---- barrier ------------------------------------------------------------------------------------------
 
 // Block-collective. Returns ROCSHMEM_SUCCESS or ROCSHMEM_ERROR (a peer did not arrive in time).
@@ -130,6 +172,7 @@ __device__ inline int team_barrier(rocshmem_team_dev *t) {
   const rocshmem_device_state &s = st();
   const unsigned tid = block_tid(), nthr = block_threads();
   if (t->my_pe < 0) return ROCSHMEM_ERROR;
+  if (proxy_collectives_on()) return proxy_collective(ROCSHMEM_PROXY_BARRIER, t, nullptr, nullptr, 0, 0, 0, 0);
   __syncthreads();  // everything the block did before the barrier is ordered before the signals
   if (tid == 0) t->barrier_epoch = t->barrier_epoch + 1;
   __syncthreads();
@@ -242,6 +285,9 @@ __device__ inline int team_reduce(rocshmem_team_dev *t, T *dest, const T *source
   if (nreduce == 0) return ROCSHMEM_SUCCESS;
   if (t->my_pe < 0) return ROCSHMEM_ERROR;
   stat_add(ROCSHMEM_STAT_REDUCE);
+  if (proxy_collectives_on()) {
+    return proxy_collective(ROCSHMEM_PROXY_REDUCE, t, dest, source, nreduce, 0, ProxyDtype<T>::code, OP);
+  }
   // Sources of all members are complete.
   if (team_barrier(t) != ROCSHMEM_SUCCESS) return ROCSHMEM_ERROR;
   constexpr size_t VEC = 16 / sizeof(T);
@@ -265,6 +311,10 @@ __device__ inline void team_broadcast(rocshmem_team_dev *t, void *dest, const vo
                                       size_t bytes, int pe_root) {
   if (bytes == 0 || t->my_pe < 0) return;
   stat_add(ROCSHMEM_STAT_BROADCAST);
+  if (proxy_collectives_on()) {
+    proxy_collective(ROCSHMEM_PROXY_BROADCAST, t, dest, source, bytes, pe_root, 0, 0);
+    return;
+  }
   if (t->my_pe == pe_root) {
     Group<Scope::BLOCK> g;
     for (int j = 0; j < t->size; ++j) {
@@ -280,6 +330,10 @@ __device__ inline void team_broadcast(rocshmem_team_dev *t, void *dest, const vo
 __device__ inline void team_fcollect(rocshmem_team_dev *t, void *dest, const void *source, size_t bytes) {
   if (bytes == 0 || t->my_pe < 0) return;
   stat_add(ROCSHMEM_STAT_FCOLLECT);
+  if (proxy_collectives_on()) {
+    proxy_collective(ROCSHMEM_PROXY_FCOLLECT, t, dest, const_cast<void *>(source), bytes, 0, 0, 0);
+    return;
+  }
   Group<Scope::BLOCK> g;
   char *slot = static_cast<char *>(dest) + size_t(t->my_pe) * bytes;
   for (int d = 0; d < t->size; ++d) {
@@ -293,6 +347,10 @@ __device__ inline void team_fcollect(rocshmem_team_dev *t, void *dest, const voi
 __device__ inline void team_alltoall(rocshmem_team_dev *t, void *dest, const void *source, size_t bytes) {
   if (bytes == 0 || t->my_pe < 0) return;
   stat_add(ROCSHMEM_STAT_ALLTOALL);
+  if (proxy_collectives_on()) {
+    proxy_collective(ROCSHMEM_PROXY_ALLTOALL, t, dest, const_cast<void *>(source), bytes, 0, 0, 0);
+    return;
+  }
   Group<Scope::BLOCK> g;
   char *slot = static_cast<char *>(dest) + size_t(t->my_pe) * bytes;
   for (int d = 0; d < t->size; ++d) {

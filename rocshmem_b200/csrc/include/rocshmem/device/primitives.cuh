@@ -80,7 +80,8 @@ __device__ __forceinline__ void copy_bytes(void *dst_v, const void *src_v, size_
 __device__ inline unsigned long long proxy_submit(unsigned type, int pe, const void *dst,
                                                   const void *src, unsigned long long size,
                                                   unsigned long long cond, unsigned op,
-                                                  unsigned dtype_size, bool blocking, bool *ok) {
+                                                  unsigned dtype_size, bool blocking, bool *ok,
+                                                  unsigned long long team_slot = 0) {
   const rocshmem_device_state &s = st();
   rocshmem_proxy_ring *ring = s.proxy;
   *ok = false;
@@ -115,6 +116,7 @@ __device__ inline unsigned long long proxy_submit(unsigned type, int pe, const v
   c->cond = cond;
   c->op = op;
   c->dtype_size = dtype_size;
+  c->team_slot = team_slot;
   __threadfence_system();
   c->valid = 1;
   __threadfence_system();

@@ -191,7 +191,7 @@ struct rocshmem_proxy_cmd {
   unsigned long long cond;       // compare value for CAS
   unsigned int op;               // amo sub-operation / signal op
   unsigned int dtype_size;
-  unsigned long long pad[1];
+  unsigned long long team_slot;  // collectives: sync-pool slot of the team (0: world)
 };
 static_assert(sizeof(rocshmem_proxy_cmd) == 64, "one command per 64-byte line");
 
@@ -256,7 +256,8 @@ struct rocshmem_device_state {
   unsigned long long wait_timeout_ns;  // budget of every device-side wait
   int debug_checks;                    // 1: validate pe / symmetric addresses on the device
   int use_proxy;                       // bit 0: route thread-level RMA/AMO through the host proxy;
-                                       // bit 1: coalesce contiguous messages of neighbouring lanes first
+                                       // bit 1: coalesce contiguous messages of neighbouring lanes first;
+                                       // bit 2: block-level collectives are executed by the proxy
   int device_ordinal;                  // CUDA device that hosts this PE
 };
 

@@ -87,6 +87,7 @@ Config Config::from_env(const std::map<std::string, std::string> &ov) {
     if (lookup(ov, "ROCSHMEM_USE_PROXY", &v)) c.use_proxy = static_cast<int>(parse_int(v));
     if (lookup(ov, "RO_NET_QUEUE_SIZE", &v)) c.proxy_queue_size = static_cast<int>(parse_int(v));
     if (lookup(ov, "RO_NET_CPU_QUEUE", &v)) c.proxy_on_cpu = static_cast<int>(parse_int(v));
+    if (lookup(ov, "ROCSHMEM_PROXY_COLLECTIVES", &v)) c.proxy_collectives = static_cast<int>(parse_int(v)) != 0;
     if (lookup(ov, "ROCSHMEM_USE_WF_COAL", &v)) c.proxy_coalesce = static_cast<int>(parse_int(v)) != 0;
     if (lookup(ov, "ROCSHMEM_ENABLE_NVLS", &v)) c.enable_nvls = static_cast<int>(parse_int(v));
     if (lookup(ov, "ROCSHMEM_BACKEND", &v)) c.backend = v;

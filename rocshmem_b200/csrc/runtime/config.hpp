@@ -29,6 +29,7 @@ struct Config {
   int use_proxy = 0;                         // ROCSHMEM_USE_PROXY (host-thread reverse offload)
   int proxy_queue_size = 512;                // RO_NET_QUEUE_SIZE (entries, power of two)
   int proxy_on_cpu = 1;                      // RO_NET_CPU_QUEUE (ring in pinned host memory)
+  int proxy_collectives = 0;                 // ROCSHMEM_PROXY_COLLECTIVES (device collectives run by the proxy)
   int proxy_coalesce = 0;                    // ROCSHMEM_USE_WF_COAL (merge contiguous proxied messages)
   int enable_nvls = 1;                       // ROCSHMEM_ENABLE_NVLS (try multicast mapping)
   std::string backend = "auto";              // ROCSHMEM_BACKEND: auto | cuda | host

@@ -171,6 +171,19 @@ void Proxy::execute(rocshmem_proxy_cmd &cmd, uint64_t) {
   rt_->count(ROCSHMEM_STAT_PROXY_CMD);
   unsigned long long fetched = 0;
   try {
+    // Collective commands name their team by its slot; an unknown slot fails the command.
+    HostTeam *team = rt_->team_from_slot(static_cast<int>(cmd.team_slot));
+    const bool collective = cmd.type == ROCSHMEM_PROXY_BARRIER || cmd.type == ROCSHMEM_PROXY_BROADCAST ||
+                            cmd.type == ROCSHMEM_PROXY_REDUCE || cmd.type == ROCSHMEM_PROXY_FCOLLECT ||
+                            cmd.type == ROCSHMEM_PROXY_ALLTOALL;
+    if (collective && team == nullptr) {
+      fetched = static_cast<unsigned long long>(ROCSHMEM_ERROR);
+      if (cmd.status_slot >= 0) {
+        __atomic_store_n(const_cast<unsigned long long *>(&ring_.fetched[cmd.status_slot]), fetched,
+                         __ATOMIC_RELAXED);
+      }
+      return;
+    }
     switch (cmd.type) {
       case ROCSHMEM_PROXY_PUT:
         ops.put(ctx, reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src),
@@ -196,7 +209,7 @@ void Proxy::execute(rocshmem_proxy_cmd &cmd, uint64_t) {
         ops.quiet(ctx);
         break;
       case ROCSHMEM_PROXY_BARRIER:
-        ops.barrier(ctx, rt_->team_world(), false);
+        fetched = static_cast<unsigned long long>(ops.barrier(ctx, team, false));
         break;
       case ROCSHMEM_PROXY_FENCE:
         ops.fence(ctx);
@@ -209,21 +222,21 @@ void Proxy::execute(rocshmem_proxy_cmd &cmd, uint64_t) {
       }
       case ROCSHMEM_PROXY_BROADCAST:
         fetched = static_cast<unsigned long long>(ops.broadcast(
-            ctx, rt_->team_world(), reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src),
+            ctx, team, reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src),
             cmd.size, cmd.pe));
         break;
       case ROCSHMEM_PROXY_REDUCE:
         fetched = static_cast<unsigned long long>(ops.reduce(
-            ctx, rt_->team_world(), reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src),
+            ctx, team, reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src),
             cmd.size, static_cast<DType>(cmd.cond), static_cast<ROCSHMEM_OP>(cmd.op)));
         break;
       case ROCSHMEM_PROXY_FCOLLECT:
         fetched = static_cast<unsigned long long>(ops.fcollect(
-            ctx, rt_->team_world(), reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src), cmd.size));
+            ctx, team, reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src), cmd.size));
         break;
       case ROCSHMEM_PROXY_ALLTOALL:
         fetched = static_cast<unsigned long long>(ops.alltoall(
-            ctx, rt_->team_world(), reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src), cmd.size));
+            ctx, team, reinterpret_cast<void *>(cmd.dst), reinterpret_cast<const void *>(cmd.src), cmd.size));
         break;
       default:
         break;

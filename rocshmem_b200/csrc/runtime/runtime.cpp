@@ -177,6 +177,7 @@ void Runtime::init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local
   world->id = 0;
   world_team_ = world.get();
   teams_.push_back(std::move(world));
+  team_by_slot_[0].store(teams_.back().get(), std::memory_order_release);
   write_team_descriptor(world_team_);
 
   // Device context pool: all free.
@@ -301,8 +302,11 @@ void Runtime::build_states() {
     s.wait_timeout_ns = cfg_.wait_timeout_ms * 1000000ull;
     s.device_ordinal = device_;
     s.debug_checks = cfg_.debug_checks;
-    // Bit 0: thread-level RMA / atomics go through the proxy; bit 1: lanes coalesce their messages first.
-    s.use_proxy = (proxy_ && proxy_->running() && cfg_.use_proxy) ? (1 | (cfg_.proxy_coalesce ? 2 : 0)) : 0;
+    // Bit 0: thread-level RMA / atomics go through the proxy; bit 1: lanes coalesce their messages first;
+    // bit 2: block-level collectives are executed by the proxy too.
+    s.use_proxy = (proxy_ && proxy_->running() && cfg_.use_proxy)
+                      ? (1 | (cfg_.proxy_coalesce ? 2 : 0) | (cfg_.proxy_collectives ? 4 : 0))
+                      : 0;
   }
 }
 
@@ -363,6 +367,7 @@ void Runtime::finalize() {
   for (auto &c : ctxs_) ops_->ctx_fini(c.get());
   ctxs_.clear();
   default_ctx_ = nullptr;
+  for (auto &slot : team_by_slot_) slot.store(nullptr, std::memory_order_release);
   teams_.clear();
   world_team_ = nullptr;
   ops_.reset();
@@ -533,6 +538,7 @@ int Runtime::team_split_strided(HostTeam *parent, int start, int stride, int siz
   HostTeam *raw = team.get();
   teams_.push_back(std::move(team));
   write_team_descriptor(raw);
+  team_by_slot_[raw->slot].store(raw, std::memory_order_release);
   // Descriptors and cleared flags are in place on every member before the handle is used.
   std::vector<char> tokens(procs.size());
   char one = 1;
@@ -551,6 +557,7 @@ void Runtime::team_destroy(HostTeam *t) {
     auto *dst = reinterpret_cast<rocshmem_team_dev *>(internal_base(first_pe_ + l) + layout_.teams) + t->slot;
     mem_->write(dst, &d, sizeof(d));
   }
+  team_by_slot_[t->slot].store(nullptr, std::memory_order_release);
   slots_->release(t->slot);
   teams_.erase(std::remove_if(teams_.begin(), teams_.end(),
                               [t](const std::unique_ptr<HostTeam> &p) { return p.get() == t; }),

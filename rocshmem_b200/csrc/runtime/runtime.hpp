@@ -116,6 +116,10 @@ class Runtime {
   // Teams.
   HostTeam *team_world() { return world_team_; }
   HostTeam *team_from_handle(rocshmem_team_t h);
+  // Lock-free lookup for the proxy thread (nullptr: no team owns the slot).
+  HostTeam *team_from_slot(int slot) const {
+    return slot >= 0 && slot < ROCSHMEM_TEAM_SLOTS ? team_by_slot_[slot].load(std::memory_order_acquire) : nullptr;
+  }
   int team_split_strided(HostTeam *parent, int start, int stride, int size, rocshmem_team_t *out);
   void team_destroy(HostTeam *t);
   int num_user_teams() const { return static_cast<int>(teams_.size()) - 1; }
@@ -170,6 +174,7 @@ class Runtime {
   std::unique_ptr<TeamSlots> slots_;
   std::vector<std::unique_ptr<HostTeam>> teams_;
   HostTeam *world_team_ = nullptr;
+  std::atomic<HostTeam *> team_by_slot_[ROCSHMEM_TEAM_SLOTS] = {};
   std::vector<std::unique_ptr<HostCtx>> ctxs_;
   HostCtx *default_ctx_ = nullptr;
   uint64_t next_team_id_ = 1;

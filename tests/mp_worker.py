@@ -355,6 +355,28 @@ def proxy_collectives():
         assert sub(P, (me + 1) % npes, cell.data_ptr(), 0, 4242 + me, 0, 0, 8)[0] == 0
         shm.barrier_all()
         assert int(cell.cpu()[0]) == 4242 + (me - 1) % npes
+        # collectives of a sub-team: the command names the team by its sync-pool slot
+        BARRIER = 6
+        half = max(1, npes // 2)
+        lower = shm.team_world().split_strided(0, 1, half)
+        upper = shm.team_world().split_strided(half, 1, npes - half) if npes > half else None
+        mine = lower if lower.valid else upper
+        slot = C.team_slot(mine.handle)
+        assert slot >= 1
+        members = list(range(half)) if lower.valid else list(range(half, npes))
+        subt = lambda *a: C.proxy_submit(p, *a, True, 20000, slot)
+        rc, status = subt(REDUCE, 0, dst.data_ptr(), src.data_ptr(), n, I64, shm.OP_SUM, 8)
+        assert rc == 0 and status == 0
+        assert torch.equal(dst.cpu()[:n], torch.arange(n) * len(members) + 1000 * sum(members))
+        rc, status = subt(BARRIER, 0, 0, 0, 0, 0, 0, 0)
+        assert rc == 0 and status == 0
+        # a slot that no team owns fails the command instead of running it on the wrong team
+        rc, status = C.proxy_submit(p, REDUCE, 0, dst.data_ptr(), src.data_ptr(), n, I64, shm.OP_SUM, 8, True, 20000, 37)
+        assert rc == 0 and status == 1
+        shm.barrier_all()
+        for t in (lower, upper):
+            if t is not None and t.valid:
+                t.destroy()
     finally:
         C.proxy_stop(p)
     shm.barrier_all()
