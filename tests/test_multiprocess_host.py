@@ -50,7 +50,7 @@ def test_back_to_back_collectives_team_reuse_and_many_contexts():
     assert_all_ok(run_ranks("stress_host", 3, timeout=240))
 
 
-@pytest.mark.parametrize("world", [4, 6])
+@pytest.mark.parametrize("world", [4, 6, 8])
 def test_bruck_and_clustered_schedules_match_the_linear_ones(world):
     assert_all_ok(run_ranks("host_algorithms", world, timeout=240))
 
