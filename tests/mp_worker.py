@@ -621,7 +621,57 @@ def threads_host():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def ep_collective_baseline():
+    """The all-to-all (torch.distributed) baseline of dispatch / combine against the reference routing, and a
+    round trip with identity experts against the de-quantised input."""
+    import torch.distributed as dist
+    from rocshmem_b200.baselines.ep import NcclEpDispatcher
+    from rocshmem_b200.ops import moe
+    dist.init_process_group("gloo", rank=RANK, world_size=WORLD)
+    me, P = RANK, WORLD
+    E, K, H = 4 * P, 3, 256
+    d = NcclEpDispatcher(E, K, H)
+    for rep in range(2):
+        routing = [moe.make_routing(37 + r, E, K, seed=10 * rep + r) for r in range(P)]
+        if rep == 1:
+            for idx, _ in routing:
+                idx[::4, -1] = -1
+        xs = [torch.randn(37 + r, H, generator=torch.Generator().manual_seed(100 * rep + r)).to(torch.bfloat16)
+              for r in range(P)]
+        idx, w = routing[me]
+        res = d.dispatch(xs[me], idx, w)
+        want_rows = moe.ref_dispatch([r[0] for r in routing], P, E)[me]
+        assert sum(res.recv_counts) == len(want_rows) == res.recv_x.shape[0]
+        pos = 0
+        epr = E // P
+        for s in range(P):
+            mine = [t for ss, t in want_rows if ss == s]
+            assert res.recv_counts[s] == len(mine)
+            rows = slice(pos, pos + len(mine))
+            pos += len(mine)
+            if not mine:
+                continue
+            assert res.src_token[rows].tolist() == mine
+            q, sc = moe.ref_quantize_1x128(xs[s][mine])
+            assert torch.equal(res.recv_x[rows].view(torch.uint8), q.view(torch.uint8))
+            assert torch.allclose(res.recv_scales[rows], sc)
+            src_idx, src_w = routing[s]
+            want_local = torch.where(src_idx[mine] // epr == me, src_idx[mine] % epr, torch.full_like(src_idx[mine], -1))
+            want_local = torch.where(src_idx[mine] >= 0, want_local, torch.full_like(want_local, -1))
+            assert torch.equal(res.local_expert_idx[rows], want_local.to(torch.int32))
+            assert torch.equal(res.gate_weights[rows], src_w[mine])
+        y = moe.ref_dequantize_1x128(res.recv_x, res.recv_scales).to(torch.bfloat16)
+        out = d.combine(y, idx, w, xs[me].shape[0])
+        q, sc = moe.ref_quantize_1x128(xs[me])
+        deq = moe.ref_dequantize_1x128(q, sc).to(torch.bfloat16).float()
+        gates = torch.where(idx >= 0, w, torch.zeros_like(w)).sum(dim=1, keepdim=True)
+        assert torch.allclose(out.float(), deq * gates, rtol=2e-2, atol=2e-2)
+    assert d.collectives == 2 * 5
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+SCENARIOS = {f.__name__: f for f in (ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":
