@@ -29,6 +29,8 @@ class NcclDispatchResult:
 
 
 class NcclEpDispatcher:
+    """Dispatch / combine with the traffic of ``EpDispatcher`` over ``all_to_all_single``."""
+
     def __init__(self, num_experts: int, top_k: int, hidden: int, group=None, quantize: bool = True):
         self.group = group
         self.P, self.rank = dist.get_world_size(group), dist.get_rank(group)
@@ -48,6 +50,7 @@ class NcclEpDispatcher:
         self.collectives += 1
 
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> NcclDispatchResult:
+        """Count exchange, then rows, scales and routing records in three all-to-all calls."""
         P, K, epr, dev = self.P, self.K, self.epr, x.device
         idx = topk_idx.long()
         rank_of = torch.where(idx >= 0, idx // epr, torch.full_like(idx, -1))                  # [T, K]

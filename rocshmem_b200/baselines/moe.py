@@ -10,6 +10,8 @@ from ..models.moe_ffn import expert_weights
 
 
 class NcclMoEFeedForward:
+    """The MoE feed-forward layer over NCCL all-to-all and per-expert cuBLAS GEMMs (same weights)."""
+
     def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, seed: int = 0, group=None):
         self.group = group
         self.P, self.rank = dist.get_world_size(group), dist.get_rank(group)
@@ -21,6 +23,7 @@ class NcclMoEFeedForward:
         self.w2 = [w[1].to(dev) for w in ws]
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        """Replicate tokens per expert, exchange, per-expert SwiGLU feed-forward, exchange back, weighted sum."""
         T = x.shape[0]
         flat_e = topk_idx.reshape(-1).long()
         valid = flat_e >= 0

@@ -182,6 +182,7 @@ class HostMoEFeedForward:
         self.weights = [expert_weights(first + e, hidden, inter, seed) for e in range(self.e_local)]
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
+        """Dispatch, per-expert SwiGLU feed-forward in PyTorch, combine; collective."""
         res = self.d.dispatch(x, topk_idx, topk_weights)
         rows = res.num_rows()
         xin = moe.ref_dequantize_1x128(res.recv_x[:rows].cpu(), res.recv_scales[:rows].cpu()).to(torch.bfloat16).float()

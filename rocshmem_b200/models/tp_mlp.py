@@ -33,6 +33,8 @@ def mlp_weights(rank: int, n_ranks: int, d_model: int, d_ff: int, seed: int = 0,
 
 
 class TensorParallelMLP:
+    """SwiGLU MLP with weights sharded over the team: all-gather -> up projection, down projection -> reduce-scatter, two fused kernels."""
+
     def __init__(self, d_model: int, d_ff: int, m_shard: int, team: Optional[rt.Team] = None, seed: int = 0):
         self.tp = TensorParallelLinear(m_shard, team=team)
         P = self.tp.n_ranks
@@ -62,6 +64,7 @@ class TensorParallelMLP:
 
     @property
     def kernel_launches(self) -> int:
+        """Kernels launched by this object so far."""
         return self.tp.kernel_launches
 
 
@@ -87,6 +90,7 @@ class TensorParallelMLPFp8:
 
     @traced("rocshmem_b200.tp_mlp_fp8")
     def forward(self, x_shard: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """Quantise the shard, all-gather -> up projection with SwiGLU, quantise, down projection -> reduce-scatter."""
         self.tp.set_input(x_shard, stream)
         self.tp.ag_gemm(self.w1_q, self.w1_s, out=self.h, swiglu=True, stream=stream)
         gemm.quantize_1x128_into(self.h, self.h_q, self.h_s, stream)
@@ -97,6 +101,7 @@ class TensorParallelMLPFp8:
 
     @property
     def kernel_launches(self) -> int:
+        """Kernels launched by this object so far."""
         return self.tp.kernel_launches
 
 

@@ -57,29 +57,34 @@ def alltoall(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] =
 # ---- stream-ordered ---------------------------------------------------------------------------------------
 
 def barrier_async(team: Optional[rt.Team] = None, stream=None) -> None:
+    """Team barrier as one kernel on ``stream`` (the current stream by default)."""
     rt._C().k_barrier(_team(team), _stream(stream))
 
 
 def allreduce_async(dest: torch.Tensor, source: torch.Tensor, op: int = rt.OP_SUM,
                     team: Optional[rt.Team] = None, algo: int = rt.ALLREDUCE_AUTO, stream=None) -> None:
+    """Allreduce as one kernel on ``stream``; ``algo`` picks one-shot, two-shot or NVLS (``ALLREDUCE_AUTO`` by size)."""
     rt._C().k_allreduce(_team(team), dest.data_ptr(), source.data_ptr(), source.numel(),
                         rt.dtype_code(source.dtype), op, algo, _stream(stream))
 
 
 def broadcast_async(dest: torch.Tensor, source: torch.Tensor, root: int, team: Optional[rt.Team] = None,
                     stream=None, pre_sync: bool = True) -> None:
+    """Broadcast from ``root`` as one kernel on ``stream``; the root's ``dest`` is left untouched."""
     rt._C().k_broadcast(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source), root,
                         _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)
 
 
 def fcollect_async(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None, stream=None,
                    pre_sync: bool = True) -> None:
+    """All-gather as one kernel on ``stream``: block ``i`` of ``dest`` receives PE ``i``'s ``source``."""
     rt._C().k_fcollect(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source),
                        _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)
 
 
 def alltoall_async(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None, stream=None,
                    pre_sync: bool = True) -> None:
+    """All-to-all as one kernel on ``stream``: block ``j`` of ``source`` goes to PE ``j``, stored at block ``my_pe``."""
     n = (team or rt.team_world()).n_pes()
     rt._C().k_alltoall(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source) // n,
                        _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)

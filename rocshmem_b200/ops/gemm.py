@@ -161,6 +161,7 @@ def quantize_weight_128x128(w: torch.Tensor):
 
 
 def dequantize_weight_128x128(q: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """fp32 weight from e4m3 values and one scale per 128 x 128 block (reference for tests)."""
     *lead, N, K = q.shape
     blocks = q.float().reshape(*lead, N // 128, 128, K // 128, 128)
     return (blocks * scale.reshape(*lead, N // 128, 1, K // 128, 1)).reshape(*lead, N, K)
@@ -256,6 +257,7 @@ class TensorParallelLinearFp8:
 
     def ag_gemm(self, w_q: torch.Tensor, w_s: torch.Tensor, out: Optional[torch.Tensor] = None, swiglu: bool = False,
                 stream=None) -> torch.Tensor:
+        """All-gather of the quantised activations fused with ``gathered @ w.T`` (block-scaled e4m3), optionally with SwiGLU."""
         N, K = w_q.shape
         x_q, x_s, g_q, g_s, flags, _ = buf = self._ag_buffers(K)
         buf[5] += 1
@@ -270,6 +272,7 @@ class TensorParallelLinearFp8:
 
     def gemm_rs(self, a_q: torch.Tensor, a_s: torch.Tensor, w_q: torch.Tensor, w_s: torch.Tensor,
                 out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+        """``a @ w.T`` (block-scaled e4m3) fused with the reduce-scatter of the bf16 result over the team."""
         N, K = w_q.shape
         if a_q.shape[0] != self.n_ranks * self.m_shard or a_q.shape[1] != K:
             raise ValueError("gemm_rs: a must be [n_ranks * m_shard, K_local]")

@@ -48,6 +48,7 @@ class HostCollectivePlan:
         self.cluster = cluster_size(n)
 
     def destroy(self) -> None:
+        """Free the staging buffers (collective)."""
         rt.free(self.stage)
         rt.free(self.tmp)
 
@@ -58,6 +59,7 @@ class HostCollectivePlan:
     # ---- alltoall ---------------------------------------------------------------------------------------
 
     def alltoall_linear(self, dest: torch.Tensor, source: torch.Tensor) -> None:
+        """n - 1 puts of one block each."""
         n, me = self.n, self.me
         d, s = _blocks(dest, n), _blocks(source, n)
         rt.barrier_all()
@@ -124,6 +126,7 @@ class HostCollectivePlan:
     # ---- fcollect ---------------------------------------------------------------------------------------
 
     def fcollect_linear(self, dest: torch.Tensor, source: torch.Tensor) -> None:
+        """My block to every PE with one put each."""
         n, me = self.n, self.me
         d = _blocks(dest, n)
         src = source.view(torch.uint8).view(-1)
@@ -182,6 +185,7 @@ class HostCollectivePlan:
     # ---- selection ----------------------------------------------------------------------------------------
 
     def alltoall(self, dest: torch.Tensor, source: torch.Tensor, algorithm: str = "auto") -> str:
+        """Run the named schedule (``linear``, ``bruck``, ``clustered`` or ``auto``); returns the one used."""
         nb = _blocks(source, self.n).shape[1]
         if algorithm == "auto":
             algorithm = choose_algorithm(self.n, nb)
@@ -189,6 +193,7 @@ class HostCollectivePlan:
         return algorithm
 
     def fcollect(self, dest: torch.Tensor, source: torch.Tensor, algorithm: str = "auto") -> str:
+        """Run the named schedule (``linear``, ``bruck``, ``clustered`` or ``auto``); returns the one used."""
         nb = source.numel() * source.element_size()
         if algorithm == "auto":
             algorithm = choose_algorithm(self.n, nb)

@@ -49,15 +49,19 @@ class DispatchResult:
         return int(self.recv_info[0].item())
 
     def local_expert_idx(self) -> torch.Tensor:
+        """[rows, top_k] local expert index of every choice that lives on this rank, -1 otherwise."""
         return self.recv_meta[:, 0:self.top_k]
 
     def gate_weights(self) -> torch.Tensor:
+        """[rows, top_k] fp32 gate weights as sent by the source."""
         return self.recv_meta[:, 8:8 + self.top_k].view(torch.float32)
 
     def src_token(self) -> torch.Tensor:
+        """Token index on the source rank, per row."""
         return self.recv_meta[:, 16]
 
     def src_rank(self) -> torch.Tensor:
+        """Source rank, per row."""
         return self.recv_meta[:, 17]
 
     def row_ranges(self):
@@ -67,11 +71,14 @@ class DispatchResult:
         return [(info[1 + s], info[1 + P + s]) for s in range(P)]
 
     def rows_per_expert(self) -> torch.Tensor:
+        """Number of (row, choice) pairs per local expert."""
         P = self.n_ranks
         return self.recv_info[1 + 2 * P:]
 
 
 class EpDispatcher:
+    """Symmetric receive buffers and launch state of dispatch / combine for one (team, shape) combination."""
+
     def __init__(self, num_experts: int, top_k: int, hidden: int, max_tokens: int,
                  team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact",
                  blocks: Optional[int] = None):
@@ -198,6 +205,7 @@ def fp8_quantize_1x128(x: torch.Tensor, stream=None):
 
 
 def fp8_dequantize_1x128(q: torch.Tensor, scales: torch.Tensor, stream=None) -> torch.Tensor:
+    """CUDA kernel: e4m3 rows with one fp32 scale per 128 elements back to bf16."""
     rows, hidden = q.shape
     out = torch.empty((rows, hidden), dtype=torch.bfloat16, device=q.device)
     rt._C().fp8_dequantize_1x128(q.data_ptr(), scales.data_ptr(), out.data_ptr(), rows, hidden, _stream(stream))
@@ -207,6 +215,7 @@ def fp8_dequantize_1x128(q: torch.Tensor, scales: torch.Tensor, stream=None) -> 
 # ---- fp32 references (plain PyTorch, any device) -------------------------------------------------------------------------
 
 def ref_quantize_1x128(x: torch.Tensor):
+    """PyTorch reference of the 1 x 128 e4m3 quantisation; returns (float8_e4m3fn rows, fp32 scales)."""
     rows, hidden = x.shape
     xf = x.float().view(rows, hidden // 128, 128)
     amax = xf.abs().amax(dim=-1, keepdim=True)
@@ -217,6 +226,7 @@ def ref_quantize_1x128(x: torch.Tensor):
 
 
 def ref_dequantize_1x128(q: torch.Tensor, scales: torch.Tensor) -> torch.Tensor:
+    """PyTorch reference of the de-quantisation, in fp32."""
     rows, hidden = q.shape
     return (q.float().view(rows, hidden // 128, 128) * scales.view(rows, hidden // 128, 1)).view(rows, hidden)
 

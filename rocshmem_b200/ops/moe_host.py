@@ -28,6 +28,8 @@ META_WORDS = 32
 
 
 class HostEpDispatcher:
+    """Dispatch / combine with the buffers of ``EpDispatcher`` (compact layout), moved by host-API puts and gets."""
+
     def __init__(self, num_experts: int, top_k: int, hidden: int, max_tokens: int, quantize: bool = True):
         P = rt.n_pes()
         if num_experts % P or hidden % 128 or not (1 <= top_k <= 8):
@@ -46,6 +48,7 @@ class HostEpDispatcher:
         self._sent_slot: Optional[torch.Tensor] = None
 
     def result_buffer(self) -> torch.Tensor:
+        """Symmetric bf16 buffer the experts write their result rows to (row ``i`` answers received row ``i``)."""
         if self._y is None:
             self._y = rt.zeros((self.n_ranks * self.max_tokens, self.hidden), torch.bfloat16)
         return self._y
@@ -54,6 +57,7 @@ class HostEpDispatcher:
         return t.to(self.recv_x.device)
 
     def dispatch(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> moe.DispatchResult:
+        """Send every token once to each rank that owns one of its experts; collective."""
         P, me, K, epr = self.n_ranks, rt.my_pe(), self.top_k, self.experts_per_rank
         T = x.shape[0]
         if T > self.max_tokens:

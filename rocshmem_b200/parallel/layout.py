@@ -17,6 +17,8 @@ from .. import runtime as rt
 
 
 class ParallelLayout:
+    """The row (inner) and column (data-parallel) teams of this rank on a ``dp x inner`` grid; collective to create."""
+
     def __init__(self, inner: int, world: Optional[rt.Team] = None):
         self.world = world or rt.team_world()
         n, me = self.world.n_pes(), self.world.my_pe()
@@ -37,12 +39,15 @@ class ParallelLayout:
                 self.dp_team = t
 
     def inner_rank(self) -> int:
+        """My index inside the inner (tensor- or expert-parallel) team."""
         return self.col
 
     def dp_rank(self) -> int:
+        """My index inside the data-parallel team."""
         return self.row
 
     def destroy(self) -> None:
+        """Destroy both teams (collective)."""
         for t in (self.inner_team, self.dp_team):
             if t is not None and t.valid:
                 t.destroy()

@@ -25,6 +25,8 @@ import torch.distributed as dist
 
 
 class Membership:
+    """Heartbeats and departure notes of the ranks of a job in a key-value store, for failure detection between steps."""
+
     def __init__(self, store, rank: int, world_size: int, prefix: str = "membership"):
         self.store = store
         self.rank = rank
@@ -46,12 +48,15 @@ class Membership:
 
     # ---- liveness ----------------------------------------------------------------------------------
     def heartbeat(self) -> None:
+        """Record that this rank is alive now."""
         self.store.set(self._key("hb", self.rank), repr(time.time()))
 
     def announce_leave(self) -> None:
+        """Record that this rank leaves the job (call between steps, with nothing in flight)."""
         self.store.set(self._key("left", self.rank), "1")
 
     def has_left(self, rank: int) -> bool:
+        """True once ``rank`` has announced its departure."""
         return bool(self.store.check([self._key("left", rank)]))
 
     def alive(self) -> List[int]:
@@ -87,7 +92,9 @@ class Membership:
 
     # ---- simple rendezvous -----------------------------------------------------------------------------
     def post(self, name: str) -> None:
+        """Set a named one-shot flag."""
         self.store.set(f"{self.prefix}/post/{name}", "1")
 
     def wait_for(self, name: str, timeout_s: float = 60.0) -> None:
+        """Block until the named flag has been posted (raises on time-out)."""
         self.store.wait([f"{self.prefix}/post/{name}"], datetime.timedelta(seconds=timeout_s))

@@ -25,6 +25,7 @@ class P2PChannel:
         self.count = 0
 
     def send(self, t: torch.Tensor) -> None:
+        """Put the tensor into the receiver's buffer once the previous message has been taken, then signal."""
         if rt.my_pe() != self.src_pe:
             raise RuntimeError("send on a PE that is not the channel's source")
         if self.count and rt.wait_until(self.consumed, rt.CMP_GE, self.count) != rt.SUCCESS:
@@ -35,6 +36,7 @@ class P2PChannel:
         self.count += 1
 
     def recv(self) -> torch.Tensor:
+        """Wait for the next message, return a copy and tell the sender the buffer is free."""
         if rt.my_pe() != self.dst_pe:
             raise RuntimeError("recv on a PE that is not the channel's destination")
         self.count += 1

@@ -41,6 +41,7 @@ for _name, _code in (("uint16", 3), ("uint32", 5), ("uint64", 7)):
 
 
 def dtype_code(dtype: torch.dtype) -> int:
+    """Element type code of the untyped host engine (``rocshmem_dtype``) for a torch dtype."""
     try:
         return _DTYPE_CODE[dtype]
     except KeyError:
@@ -131,6 +132,7 @@ def init(store=None, rank: Optional[int] = None, world_size: Optional[int] = Non
 
 
 def finalize() -> None:
+    """Collective tear-down: frees the heap mappings, stops the proxy, checks the guard regions."""
     C = _C()
     if C.is_initialized():
         if C.is_cuda():
@@ -141,18 +143,22 @@ def finalize() -> None:
 
 
 def is_initialized() -> bool:
+    """True between ``init`` and ``finalize``."""
     return _C().is_initialized()
 
 
 def my_pe() -> int:
+    """This process's PE number (the current local PE when several are hosted)."""
     return _C().my_pe()
 
 
 def n_pes() -> int:
+    """Total number of PEs."""
     return _C().n_pes()
 
 
 def n_local_pes() -> int:
+    """PEs hosted by this process (1 unless ``init(n_local=...)``)."""
     return _C().n_local()
 
 
@@ -162,14 +168,17 @@ def set_local_pe(index: int) -> None:
 
 
 def is_cuda() -> bool:
+    """True when the heap is GPU memory (CUDA backend), False on the CPU shared-memory backend."""
     return _C().is_cuda()
 
 
 def device() -> torch.device:
+    """The torch device that holds this PE's heap."""
     return _state.device
 
 
 def nvls_available() -> bool:
+    """True when the heap is also mapped through an NVLink multicast object (``multimem`` collectives)."""
     return _C().nvls_available()
 
 
@@ -217,6 +226,7 @@ def empty(shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
 
 
 def zeros(shape, dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Collective: a zero-filled symmetric tensor (same heap offset on every PE)."""
     t = empty(shape, dtype)
     for l in range(n_local_pes()):
         local_view(t, l).zero_()
@@ -250,6 +260,7 @@ def peer_address(t: torch.Tensor, pe: int) -> int:
 
 
 def heap_info() -> dict:
+    """Heap size, stride between PEs, bytes used and available, backend name, NVLS availability."""
     C = _C()
     return {"size": C.heap_size(), "stride": C.heap_stride(), "used": C.heap_used(),
             "avail": C.heap_avail(), "backend": C.backend_name(), "nvls": C.nvls_available()}
@@ -265,15 +276,19 @@ class Team:
 
     @property
     def valid(self) -> bool:
+        """False for the invalid team (returned by a split to PEs that are not members)."""
         return self.handle != 0
 
     def n_pes(self) -> int:
+        """Number of members."""
         return _C().team_n_pes(self.handle)
 
     def my_pe(self) -> int:
+        """My index in the team, -1 when I am not a member."""
         return _C().team_my_pe(self.handle)
 
     def translate_pe(self, pe: int, dst: "Team") -> int:
+        """Index in ``dst`` of the PE that has index ``pe`` in this team, -1 when it is not a member of ``dst``."""
         return _C().team_translate_pe(self.handle, pe, dst.handle)
 
     def split_strided(self, start: int, stride: int, size: int) -> "Team":
@@ -287,9 +302,11 @@ class Team:
         return Team(h)
 
     def sync(self) -> int:
+        """Host-side team barrier without the completion of outstanding operations; 0 on success."""
         return _C().team_sync(self.handle)
 
     def destroy(self) -> None:
+        """Release the team's slot (collective over its members)."""
         if self.handle:
             _C().team_destroy(self.handle)
             self.handle = 0
@@ -299,10 +316,12 @@ class Team:
 
 
 def team_world() -> Team:
+    """The team of all PEs."""
     return Team(_C().team_world())
 
 
 def team_capacity() -> int:
+    """Number of team slots (``ROCSHMEM_MAX_NUM_TEAMS``), the world team included."""
     return _C().config_from_env({})["max_teams"]
 
 
@@ -319,9 +338,11 @@ class Context:
         self.handle, self.team_handle = c, t
 
     def quiet(self) -> None:
+        """Wait until every operation issued on this context has completed."""
         _C().quiet(self.handle, self.team_handle)
 
     def destroy(self) -> None:
+        """Complete outstanding operations and release the context."""
         if self.handle:
             _C().ctx_destroy(self.handle, self.team_handle)
             self.handle = 0
@@ -391,18 +412,22 @@ def atomic(op: int, target: torch.Tensor, value=0, pe: int = 0, cond=0, index: i
 
 
 def atomic_fetch_add(target, value, pe, index=0, ctx=None):
+    """Add ``value`` to element ``index`` of ``target`` on ``pe``; returns the previous value."""
     return atomic(AMO_ADD, target, value, pe, index=index, ctx=ctx)
 
 
 def atomic_compare_swap(target, cond, value, pe, index=0, ctx=None):
+    """Store ``value`` if the element equals ``cond``; returns the previous value."""
     return atomic(AMO_CAS, target, value, pe, cond=cond, index=index, ctx=ctx)
 
 
 def atomic_swap(target, value, pe, index=0, ctx=None):
+    """Store ``value``; returns the previous value."""
     return atomic(AMO_SWAP, target, value, pe, index=index, ctx=ctx)
 
 
 def atomic_fetch(target, pe, index=0, ctx=None):
+    """Atomic read of element ``index`` of ``target`` on ``pe``."""
     return atomic(AMO_FETCH, target, 0, pe, index=index, ctx=ctx)
 
 
@@ -412,16 +437,19 @@ def wait_until(ivar: torch.Tensor, cmp: int, value, index: int = 0) -> int:
 
 
 def test(ivar: torch.Tensor, cmp: int, value, index: int = 0) -> bool:
+    """One non-blocking evaluation of the comparison ``wait_until`` would wait for."""
     return bool(_C().test(_element_ptr(ivar, index), dtype_code(ivar.dtype), cmp, _bits(value, ivar.dtype)))
 
 
 def wait_until_all(ivars: torch.Tensor, cmp: int, values, status: Sequence[int] = ()) -> None:
+    """Wait until every element (whose ``status`` entry is 0) satisfies the comparison."""
     vec = isinstance(values, (list, tuple))
     vals = [_bits(v, ivars.dtype) for v in (values if vec else [values])]
     _C().wait_until_all(ivars.data_ptr(), ivars.numel(), list(status), dtype_code(ivars.dtype), cmp, vals, vec)
 
 
 def wait_until_any(ivars: torch.Tensor, cmp: int, values, status: Sequence[int] = ()) -> int:
+    """Wait until one element satisfies the comparison; returns its index (``SIZE_MAX`` for an empty set)."""
     vec = isinstance(values, (list, tuple))
     vals = [_bits(v, ivars.dtype) for v in (values if vec else [values])]
     r = _C().wait_until_any(ivars.data_ptr(), ivars.numel(), list(status), dtype_code(ivars.dtype), cmp, vals, vec)
@@ -429,24 +457,29 @@ def wait_until_any(ivars: torch.Tensor, cmp: int, values, status: Sequence[int] 
 
 
 def wait_until_some(ivars: torch.Tensor, cmp: int, values, status: Sequence[int] = ()):
+    """Wait until at least one element satisfies the comparison; returns the indices of all that do."""
     vec = isinstance(values, (list, tuple))
     vals = [_bits(v, ivars.dtype) for v in (values if vec else [values])]
     return _C().wait_until_some(ivars.data_ptr(), ivars.numel(), list(status), dtype_code(ivars.dtype), cmp, vals, vec)
 
 
 def fence() -> None:
+    """Order this PE's earlier puts before its later ones, per destination."""
     _C().fence()
 
 
 def quiet(ctx: Optional[Context] = None) -> None:
+    """Wait until every operation issued on the context (default context if none) has completed."""
     _C().quiet(*_ctx_args(ctx))
 
 
 def barrier_all() -> None:
+    """Complete outstanding operations, then synchronise all PEs."""
     _C().barrier_all()
 
 
 def sync_all() -> None:
+    """Synchronise all PEs without completing outstanding operations."""
     _C().sync_all()
 
 
@@ -456,8 +489,10 @@ def get_error(local: int = -1) -> dict:
 
 
 def clear_error() -> None:
+    """Reset the first-error record of this PE."""
     _C().clear_error()
 
 
 def set_wait_timeout_ms(ms: int) -> None:
+    """Change the budget of host- and device-side waits (must be positive)."""
     _C().set_wait_timeout_ms(ms)

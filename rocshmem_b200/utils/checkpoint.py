@@ -42,4 +42,5 @@ def save(path: str, tensors: Dict[str, torch.Tensor]) -> None:
 
 
 def load(path: str, tensors: Dict[str, torch.Tensor], barrier: bool = True) -> None:
+    """Read a file written by ``save`` and ``restore`` it into the given symmetric tensors."""
     restore(tensors, torch.load(path, map_location="cpu"), barrier=barrier)

@@ -25,11 +25,13 @@ def measured_peaks(root: Optional[str] = None) -> dict:
 
 
 def memory_fraction(bytes_moved: float, seconds: float, peaks: Optional[dict] = None) -> float:
+    """Achieved bytes per second as a fraction of the measured copy bandwidth."""
     peaks = peaks or measured_peaks()
     return bytes_moved / seconds / 1e9 / peaks["hbm_gbs"]
 
 
 def compute_fraction(flops: float, seconds: float, sustained: bool = False, peaks: Optional[dict] = None) -> float:
+    """Achieved FLOP/s as a fraction of the measured cuBLAS bf16 throughput (burst or sustained)."""
     peaks = peaks or measured_peaks()
     return flops / seconds / 1e12 / peaks["bf16_tflops_sustained" if sustained else "bf16_tflops"]
 

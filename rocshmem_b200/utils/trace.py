@@ -21,6 +21,7 @@ log.setLevel({0: logging.WARNING, 1: logging.INFO}.get(int(os.environ.get("ROCSH
 
 
 def nvtx_enabled() -> bool:
+    """True when ``ROCSHMEM_NVTX`` asks for NVTX ranges."""
     return os.environ.get("ROCSHMEM_NVTX", "0") not in ("", "0")
 
 

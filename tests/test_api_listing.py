@@ -51,3 +51,13 @@ def test_name_coverage_translation_unit_compiles(tmp_path):
     out = subprocess.run(["nvcc", "-std=c++17", "-I", INC, "-gencode", "arch=compute_100a,code=sm_100a", "-c", str(src),
                           "-o", str(tmp_path / "names.o")], capture_output=True, text=True, timeout=900)
     assert out.returncode == 0, out.stderr[-3000:]
+
+
+def test_every_public_python_name_has_a_docstring():
+    """The Python listing (rocshmem_b200.utils.gen_pydoc) has a description for every public function, class and
+    method of the package's modules."""
+    from rocshmem_b200.utils import gen_pydoc
+    text = gen_pydoc.markdown()
+    missing = [line for line in text.splitlines() if line.rstrip().endswith("—")]
+    assert not missing, missing
+    assert "## `rocshmem_b200.ops.moe`" in text and "EpDispatcher" in text
