@@ -72,6 +72,10 @@ class MoEFeedForward:
             self.h_q = torch.zeros((cap, inter), dtype=torch.uint8, device=dev)
             self.h_s = torch.zeros((cap, inter // 128), dtype=torch.float32, device=dev)
 
+    def destroy(self) -> None:
+        """Collective: free the dispatcher's symmetric buffers (the weights and work buffers are ordinary tensors)."""
+        self.d.destroy()
+
     @traced("rocshmem_b200.moe_feed_forward")
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor,
                 out: Optional[torch.Tensor] = None, stream=None, stage_us: Optional[dict] = None) -> torch.Tensor:
@@ -180,6 +184,10 @@ class HostMoEFeedForward:
         self.e_local = self.d.experts_per_rank
         first = rt.my_pe() * self.e_local
         self.weights = [expert_weights(first + e, hidden, inter, seed) for e in range(self.e_local)]
+
+    def destroy(self) -> None:
+        """Collective: free the dispatcher's symmetric buffers."""
+        self.d.destroy()
 
     def forward(self, x: torch.Tensor, topk_idx: torch.Tensor, topk_weights: torch.Tensor) -> torch.Tensor:
         """Dispatch, per-expert SwiGLU feed-forward in PyTorch, combine; collective."""

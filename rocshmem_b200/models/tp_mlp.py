@@ -50,6 +50,10 @@ class TensorParallelMLP:
         :meth:`forward`."""
         return self.tp.ag_input(self.d_model)
 
+    def destroy(self) -> None:
+        """Collective: free the symmetric gather / staging buffers (the weights are ordinary tensors)."""
+        self.tp.destroy()
+
     @traced("rocshmem_b200.tp_mlp")
     def forward(self, x_shard: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None,
                 stream=None) -> torch.Tensor:
@@ -87,6 +91,10 @@ class TensorParallelMLPFp8:
         self.h = torch.empty((M, self.ff_local), dtype=torch.bfloat16, device=dev)
         self.h_q = torch.empty((M, self.ff_local), dtype=torch.uint8, device=dev)
         self.h_s = torch.empty((M, self.ff_local // 128), dtype=torch.float32, device=dev)
+
+    def destroy(self) -> None:
+        """Collective: free the symmetric gather / staging buffers (the weights are ordinary tensors)."""
+        self.tp.destroy()
 
     @traced("rocshmem_b200.tp_mlp_fp8")
     def forward(self, x_shard: torch.Tensor, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:

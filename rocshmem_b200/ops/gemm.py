@@ -73,6 +73,16 @@ def gemm_error_count() -> int:
     return rt._C().gemm_error_count()
 
 
+def _free_buffer_tables(*tables) -> None:
+    """Collective: free every symmetric tensor held in the per-shape buffer tables, then clear them."""
+    tensors = [v for table in tables for entry in table.values() for v in entry if isinstance(v, torch.Tensor)]
+    if tensors and rt.is_cuda():
+        torch.cuda.synchronize()
+    rt.free_all(tensors)
+    for table in tables:
+        table.clear()
+
+
 class TensorParallelLinear:
     """Buffers and calls of the fused tensor-parallel kernels for one (m_shard, K, N) shape.
 
@@ -91,6 +101,10 @@ class TensorParallelLinear:
         self._ag = {}
         self._rs = {}
         self.kernel_launches = 0
+
+    def destroy(self) -> None:
+        """Collective: give the gather, staging and flag buffers of every shape used so far back to the heap."""
+        _free_buffer_tables(self._ag, self._rs)
 
     def ag_input(self, k: int) -> torch.Tensor:
         """The symmetric ``[m_shard, k]`` buffer that holds this rank's activation shard."""
@@ -234,6 +248,10 @@ class TensorParallelLinearFp8:
         self._ag = {}
         self._rs = {}
         self.kernel_launches = 0
+
+    def destroy(self) -> None:
+        """Collective: give the gather, staging and flag buffers of every shape used so far back to the heap."""
+        _free_buffer_tables(self._ag, self._rs)
 
     def _ag_buffers(self, k: int):
         if k not in self._ag:

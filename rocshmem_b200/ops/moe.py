@@ -123,6 +123,22 @@ class EpDispatcher:
                              self.layout, self.blocks, ptrs)
         self.kernel_launches = 0
 
+    def destroy(self) -> None:
+        """Collective: give the symmetric buffers back to the heap. The object must not be used afterwards and no
+        kernel that uses the buffers may be in flight on any member."""
+        if self._h is None:
+            return
+        if rt.is_cuda():
+            torch.cuda.synchronize()
+        lay = list(getattr(self, "_lay", ()))
+        rt.free_all([self.recv_x, self.recv_scales, self.recv_meta, self.cnt_in, self.exp_in, self.sent_slot,
+                     self.tok_mask, self.blk_cnt, self.exp_cnt, self.grid_counter, self.phase_ns, self.recv_info,
+                     self._y] + lay)
+        self._h = None
+        self._y = None
+        if lay:
+            del self._lay
+
     # -- buffers -------------------------------------------------------------------------------------------
     def result_buffer(self) -> torch.Tensor:
         """Symmetric [P * max_tokens, hidden] bf16 buffer for the experts' output rows (input of

@@ -47,6 +47,11 @@ class HostEpDispatcher:
         self._y: Optional[torch.Tensor] = None
         self._sent_slot: Optional[torch.Tensor] = None
 
+    def destroy(self) -> None:
+        """Collective: give the symmetric buffers back to the heap."""
+        rt.free_all([self.recv_x, self.recv_scales, self.recv_meta, self.recv_info, self.counts, self._y])
+        self.recv_x = self.recv_scales = self.recv_meta = self.recv_info = self.counts = self._y = None
+
     def result_buffer(self) -> torch.Tensor:
         """Symmetric bf16 buffer the experts write their result rows to (row ``i`` answers received row ``i``)."""
         if self._y is None:

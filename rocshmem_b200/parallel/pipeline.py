@@ -24,6 +24,11 @@ class P2PChannel:
         self.consumed = rt.zeros(1, torch.int64)    # on the sender: messages the receiver has taken
         self.count = 0
 
+    def destroy(self) -> None:
+        """Collective: free the buffer and the two counters."""
+        rt.free_all([self.buf, self.arrived, self.consumed])
+        self.buf = self.arrived = self.consumed = None
+
     def send(self, t: torch.Tensor) -> None:
         """Put the tensor into the receiver's buffer once the previous message has been taken, then signal."""
         if rt.my_pe() != self.src_pe:

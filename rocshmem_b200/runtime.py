@@ -245,6 +245,12 @@ def free(t: torch.Tensor) -> None:
     _C().free(ptr)
 
 
+def free_all(tensors) -> None:
+    """Collective: :func:`free` every tensor of an iterable (``None`` entries are skipped), last allocated first."""
+    for t in reversed([t for t in tensors if t is not None]):
+        free(t)
+
+
 def local_view(t: torch.Tensor, local_index: int) -> torch.Tensor:
     """The copy of symmetric tensor ``t`` that belongs to local PE ``local_index`` of this process."""
     if local_index == 0:

@@ -390,6 +390,7 @@ def ep_host():
     init("64M")
     me, P = shm.my_pe(), shm.n_pes()
     E, K, H, T = 4 * P, 3, 256, 37 + me
+    used_before = shm.heap_info()["used"]
     d = moe_host.HostEpDispatcher(E, K, H, max_tokens=64)
     for rep in range(2):
         routing = [moe.make_routing(37 + r, E, K, seed=10 * rep + r) for r in range(P)]
@@ -433,6 +434,9 @@ def ep_host():
         gate = torch.where(idx >= 0, w, torch.zeros_like(w)).sum(dim=1, keepdim=True)
         assert torch.allclose(out.float(), xd * gate, rtol=2e-2, atol=2e-2), rep
     shm.barrier_all()
+    assert shm.heap_info()["used"] > used_before
+    d.destroy()                                  # every symmetric buffer goes back to the heap
+    assert shm.heap_info()["used"] == used_before
     shm.finalize()
 
 
@@ -443,6 +447,7 @@ def moe_layer_host():
     init("64M")
     me, P = shm.my_pe(), shm.n_pes()
     E, K, H, I, T = 2 * P, 2, 256, 128, 29 + 2 * me
+    used_before = shm.heap_info()["used"]
     layer = moe_ffn.HostMoEFeedForward(E, K, H, I, max_tokens=64, seed=9)
     for rep in range(2):
         x = torch.randn(T, H, generator=torch.Generator().manual_seed(50 * rep + me)).to(torch.bfloat16)
@@ -454,6 +459,8 @@ def moe_layer_host():
         err = (out.float().cpu() - want).abs().max().item()
         assert err <= 3e-2 * want.abs().max().item() + 0.02, (rep, err)
     shm.barrier_all()
+    layer.destroy()
+    assert shm.heap_info()["used"] == used_before
     shm.finalize()
 
 
@@ -481,6 +488,7 @@ def parallel_layout():
     assert int(dst.cpu()[0]) == (1 << (me % 2)) + (1 << (2 + me % 2))
     shm.barrier_all()
     # pipeline: PE 0 -> PE 3, three messages in order, back-pressure through the acknowledgement counter
+    used_before = shm.heap_info()["used"]
     ch = pipeline.P2PChannel((16,), torch.float32, src_pe=0, dst_pe=3)
     shm.barrier_all()
     for i in range(3):
@@ -490,6 +498,8 @@ def parallel_layout():
             got = ch.recv()
             assert torch.all(got.cpu() == float(i + 1)), (i, got)
     shm.barrier_all()
+    ch.destroy()
+    assert shm.heap_info()["used"] == used_before
     lay.destroy()
     shm.finalize()
 
