@@ -23,6 +23,15 @@ def _team(team: Optional[rt.Team]) -> int:
     return (team or rt.team_world()).handle
 
 
+def _check(dest: torch.Tensor, source: torch.Tensor, dest_elems: int, what: str) -> None:
+    """Both buffers symmetric and contiguous, same element type, ``dest`` large enough."""
+    rt.require_symmetric(dest=dest, source=source)
+    if dest.dtype != source.dtype:
+        raise ValueError(f"{what}: dest is {dest.dtype}, source is {source.dtype}")
+    if dest.numel() < dest_elems:
+        raise ValueError(f"{what}: dest holds {dest.numel()} elements, {dest_elems} are needed")
+
+
 def _stream(stream) -> int:
     if stream is None:
         stream = torch.cuda.current_stream()
@@ -64,6 +73,7 @@ def barrier_async(team: Optional[rt.Team] = None, stream=None) -> None:
 def allreduce_async(dest: torch.Tensor, source: torch.Tensor, op: int = rt.OP_SUM,
                     team: Optional[rt.Team] = None, algo: int = rt.ALLREDUCE_AUTO, stream=None) -> None:
     """Allreduce as one kernel on ``stream``; ``algo`` picks one-shot, two-shot or NVLS (``ALLREDUCE_AUTO`` by size)."""
+    _check(dest, source, source.numel(), "allreduce_async")
     rt._C().k_allreduce(_team(team), dest.data_ptr(), source.data_ptr(), source.numel(),
                         rt.dtype_code(source.dtype), op, algo, _stream(stream))
 
@@ -71,6 +81,7 @@ def allreduce_async(dest: torch.Tensor, source: torch.Tensor, op: int = rt.OP_SU
 def broadcast_async(dest: torch.Tensor, source: torch.Tensor, root: int, team: Optional[rt.Team] = None,
                     stream=None, pre_sync: bool = True) -> None:
     """Broadcast from ``root`` as one kernel on ``stream``; the root's ``dest`` is left untouched."""
+    _check(dest, source, source.numel(), "broadcast_async")
     rt._C().k_broadcast(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source), root,
                         _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)
 
@@ -78,6 +89,7 @@ def broadcast_async(dest: torch.Tensor, source: torch.Tensor, root: int, team: O
 def fcollect_async(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None, stream=None,
                    pre_sync: bool = True) -> None:
     """All-gather as one kernel on ``stream``: block ``i`` of ``dest`` receives PE ``i``'s ``source``."""
+    _check(dest, source, source.numel() * (team or rt.team_world()).n_pes(), "fcollect_async")
     rt._C().k_fcollect(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source),
                        _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)
 
@@ -86,5 +98,8 @@ def alltoall_async(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.T
                    pre_sync: bool = True) -> None:
     """All-to-all as one kernel on ``stream``: block ``j`` of ``source`` goes to PE ``j``, stored at block ``my_pe``."""
     n = (team or rt.team_world()).n_pes()
+    if source.numel() % n:
+        raise ValueError(f"alltoall_async: source has {source.numel()} elements, not a multiple of {n} members")
+    _check(dest, source, source.numel(), "alltoall_async")
     rt._C().k_alltoall(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source) // n,
                        _stream(stream), rt.COLL_PRE_SYNC if pre_sync else 0)

@@ -55,6 +55,8 @@ class _State:
     store: object = None
     prefix: str = ""
     allocations: Dict[int, int] = None  # data_ptr -> bytes
+    heap_lo: int = 0                    # address range of the heaps of this process's PEs
+    heap_hi: int = 0
 
 
 _state = _State(allocations={})
@@ -129,6 +131,9 @@ def init(store=None, rank: Optional[int] = None, world_size: Optional[int] = Non
         C.init_file(0, 1, "", ov, n_local, device, timeout_ms)
     _state.initialised = True
     _state.allocations = {}
+    first = C.my_pe()                   # local PE 0 is current right after init
+    _state.heap_lo = C.heap_base(first)
+    _state.heap_hi = C.heap_base(first + n_local - 1) + C.heap_size()
 
 
 def finalize() -> None:
@@ -140,6 +145,7 @@ def finalize() -> None:
         C.finalize()
     _state.initialised = False
     _state.allocations = {}
+    _state.heap_lo = _state.heap_hi = 0
 
 
 def is_initialized() -> bool:
@@ -368,6 +374,24 @@ def _check_contig(*ts: torch.Tensor) -> None:
     for t in ts:
         if not t.is_contiguous():
             raise ValueError("rocshmem_b200: tensors must be contiguous")
+
+
+def is_symmetric(t: torch.Tensor) -> bool:
+    """True when the tensor's memory lies inside the symmetric heap of one of this process's PEs."""
+    ptr = t.data_ptr()
+    return _state.heap_lo <= ptr and ptr + t.numel() * t.element_size() <= _state.heap_hi and _state.heap_hi > 0
+
+
+def require_symmetric(**tensors: torch.Tensor) -> None:
+    """Raise ``ValueError`` naming the first argument that is not a contiguous tensor on the symmetric heap.
+    Kernels derive peer addresses from these pointers, so anything else would make them touch foreign memory."""
+    for name, t in tensors.items():
+        if t.numel() == 0:
+            continue                    # nothing is read or written; the collectives treat it as a no-op
+        if not t.is_contiguous():
+            raise ValueError(f"rocshmem_b200: `{name}` must be contiguous")
+        if not is_symmetric(t):
+            raise ValueError(f"rocshmem_b200: `{name}` must live on the symmetric heap (rocshmem_b200.empty / zeros)")
 
 
 def putmem(dest: torch.Tensor, source: torch.Tensor, pe: int, ctx: Optional[Context] = None,

@@ -199,3 +199,30 @@ def test_threads_share_the_host_api(shm4):
     assert all(torch.all(got[t] == t + 1) for t in range(n_threads))
     shm.free(slots)
     shm.free(counter)
+
+
+def test_stream_ordered_collectives_reject_buffers_that_are_not_symmetric(shm4):
+    """The kernels derive peer addresses from the tensors' pointers, so the Python layer refuses anything that is
+    not a contiguous tensor on the symmetric heap (and mismatched types or sizes) before a kernel is launched."""
+    from rocshmem_b200.ops import collectives as coll
+    shm = shm4
+    a = shm.zeros(64, torch.float32)
+    b = shm.zeros(64, torch.float32)
+    small = shm.zeros(8, torch.float32)
+    other = shm.zeros(64, torch.int32)
+    local = torch.zeros(64)
+    assert shm.is_symmetric(a) and shm.is_symmetric(a[8:16]) and not shm.is_symmetric(local)
+    with pytest.raises(ValueError, match="`dest` must live on the symmetric heap"):
+        coll.allreduce_async(local, a, stream=0)
+    with pytest.raises(ValueError, match="`source` must live on the symmetric heap"):
+        coll.fcollect_async(a, local, stream=0)
+    with pytest.raises(ValueError, match="contiguous"):
+        coll.broadcast_async(a[::2], b[::2], 0, stream=0)
+    with pytest.raises(ValueError, match="torch.int32"):
+        coll.allreduce_async(other, a, stream=0)
+    with pytest.raises(ValueError, match="64 are needed"):
+        coll.allreduce_async(small, a, stream=0)
+    with pytest.raises(ValueError, match="256 are needed"):
+        coll.fcollect_async(a, b, stream=0)               # 4 PEs x 64 elements
+    with pytest.raises(ValueError, match="not a multiple"):
+        coll.alltoall_async(a, shm.zeros(6, torch.float32), stream=0)
