@@ -39,6 +39,10 @@ def gemm_bf16(a: torch.Tensor, b: torch.Tensor, out: Optional[torch.Tensor] = No
         raise ValueError("inner dimensions must match and be a multiple of 8")
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=a.device)
+    else:
+        _check(out, "out")
+        if tuple(out.shape) != (M, N):
+            raise ValueError(f"out must be [{M}, {N}]")
     C = rt._C()
     fn = C.gemm_bf16 if two_cta is None else (C.gemm_bf16_pair if two_cta else C.gemm_bf16_one_cta)
     fn(a.data_ptr(), b.data_ptr(), out.data_ptr(), M, N, K, _stream(stream))

@@ -178,8 +178,18 @@ class EpDispatcher:
         token, the (weighted) sum of its rows over the ranks it was dispatched to."""
         if y.data_ptr() != self.result_buffer().data_ptr():
             raise ValueError("combine: y must be this dispatcher's result_buffer()")
+        if not 0 <= num_tokens <= self.max_tokens:
+            raise ValueError("combine: num_tokens must be in [0, max_tokens]")
+        if topk_idx.dtype != torch.int32 or topk_weights.dtype != torch.float32:
+            raise TypeError("combine: topk_idx must be int32 and topk_weights fp32")
+        for t in (topk_idx, topk_weights):
+            if not t.is_contiguous() or t.shape[0] < num_tokens or t.shape[1] != self.top_k:
+                raise ValueError("combine: topk tensors must be contiguous [>= num_tokens, top_k]")
         if out is None:
             out = torch.empty((num_tokens, self.hidden), dtype=torch.bfloat16, device=y.device)
+        elif (out.dtype != torch.bfloat16 or not out.is_contiguous() or out.shape[0] < num_tokens
+              or out.shape[1] != self.hidden):
+            raise ValueError("combine: out must be a contiguous [>= num_tokens, hidden] bf16 tensor")
         with trace_range("rocshmem_b200.ep_combine"):
             self._h.combine(y.data_ptr(), out.data_ptr(), topk_idx.data_ptr(), topk_weights.data_ptr(), num_tokens,
                             int(weighted), _stream(stream))
