@@ -518,6 +518,27 @@ __global__ void mutex_kernel(rocshmemx_ticket_mutex_t *ticket, rocshmemx_spin_mu
   }
 }
 
+// Slab allocation from device code. Every thread allocates `bytes` (16-byte aligned) and records its pointer; then
+// every warp allocates once for its lanes and every block once for its threads, and each thread checks that it saw
+// the same pointer as lane 0 / thread 0 (differences are counted in `errors`).
+__global__ void slab_kernel(rocshmemx_slab_t slab, size_t bytes, unsigned long long *thread_ptrs,
+                            unsigned long long *warp_ptrs, unsigned long long *block_ptrs, int *errors) {
+  const unsigned g = blockIdx.x * blockDim.x + threadIdx.x;
+  void *p = rocshmemx_slab_alloc(slab, bytes, 16);
+  thread_ptrs[g] = reinterpret_cast<unsigned long long>(p);
+  if (p != nullptr) *static_cast<unsigned int *>(p) = g;   // the block is usable memory
+  void *w = rocshmemx_slab_alloc_wave(slab, 64, 64);
+  const unsigned long long w0 = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(w), 0);
+  if (w0 != reinterpret_cast<unsigned long long>(w)) atomicAdd(errors, 1);
+  if ((threadIdx.x & 31) == 0) warp_ptrs[g / 32] = reinterpret_cast<unsigned long long>(w);
+  void *b = rocshmemx_slab_alloc_wg(slab, 256, 256);
+  __shared__ unsigned long long first;
+  if (threadIdx.x == 0) first = reinterpret_cast<unsigned long long>(b);
+  __syncthreads();
+  if (first != reinterpret_cast<unsigned long long>(b)) atomicAdd(errors, 1);
+  if (threadIdx.x == 0) block_ptrs[blockIdx.x] = first;
+}
+
 // ---- launch glue ---------------------------------------------------------------------------------------------------------------------
 
 template <typename T> T *P(uintptr_t v) { return reinterpret_cast<T *>(v); }
@@ -613,6 +634,14 @@ PYBIND11_MODULE(_testk, m) {
                                                     P<unsigned long long>(counters), P<unsigned long long>(grid_counter),
                                                     rounds, P<int>(phase_errors));
     ok(cudaGetLastError(), "mutex_kernel");
+  });
+  m.def("slab_test", [](uintptr_t base, uint64_t size, size_t bytes, uintptr_t thread_ptrs, uintptr_t warp_ptrs,
+                        uintptr_t block_ptrs, uintptr_t errors, int blocks, int threads, uintptr_t stream) {
+    rocshmemx_slab_t slab{reinterpret_cast<char *>(base), size, reinterpret_cast<unsigned long long *>(base + size)};
+    slab_kernel<<<blocks, threads, 0, S(stream)>>>(slab, bytes, P<unsigned long long>(thread_ptrs),
+                                                   P<unsigned long long>(warp_ptrs), P<unsigned long long>(block_ptrs),
+                                                   P<int>(errors));
+    ok(cudaGetLastError(), "slab_kernel");
   });
   m.def("api_surface", [](uintptr_t p, uintptr_t team, uintptr_t stream) {
     ok(kernels::launch_pes(api_surface_kernel, 1, 32, 0, S(stream), false, 0, P<void>(p),

@@ -1,0 +1,154 @@
+"""GPU checks of device code that has been compiled for sm_100a but has not run on a GPU yet: the slab allocator's
+device half, warp coalescing of proxied puts and gets, the time buckets of profiling builds, and block-level
+collectives executed by the proxy.
+
+The file name does not match pytest's ``test_*.py`` pattern on purpose, so the default GPU run does not collect it;
+run it explicitly, and move each case into the regular test files once it has passed on a B200:
+
+    python -m pytest tests/pending_gpu_checks.py -m gpu -x -q
+    python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 tests/pending_gpu_checks.py
+"""
+import os
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+RMA_PUT, RMA_GET = 0, 2
+SC_THREAD = 0
+C_BCAST, C_FCOLLECT, C_ALLTOALL, C_SUM = 0, 1, 2, 3
+STAT_PROXY_SLOT_NS, STAT_PROXY_PACK_NS, STAT_PROXY_HOST_NS, STAT_WAIT_NS = 30, 31, 32, 33
+
+
+def _fresh(**kw):
+    import rocshmem_b200 as shm
+    from rocshmem_b200 import _native
+    if shm.is_initialized():
+        shm.finalize()
+    shm.init(heap_size="64M", ROCSHMEM_WAIT_TIMEOUT_MS=5000, **kw)
+    return shm, _native.load_test_kernels()
+
+
+def test_slab_allocation_from_kernels():
+    from rocshmem_b200 import runtime as rt
+    shm, k = _fresh()
+    try:
+        C = rt._C()
+        blocks, threads, each = 4, 128, 48
+        base, size = C.slab_create(1 << 20)
+        n = blocks * threads
+        tp = torch.zeros(n, dtype=torch.int64, device="cuda")
+        wp = torch.zeros(n // 32, dtype=torch.int64, device="cuda")
+        bp = torch.zeros(blocks, dtype=torch.int64, device="cuda")
+        errors = torch.zeros(1, dtype=torch.int32, device="cuda")
+        k.slab_test(base, size, each, tp.data_ptr(), wp.data_ptr(), bp.data_ptr(), errors.data_ptr(), blocks, threads,
+                    torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        assert int(errors.item()) == 0
+        spans = [(p, each) for p in tp.tolist()] + [(p, 64) for p in wp.tolist()] + [(p, 256) for p in bp.tolist()]
+        assert all(base <= p and p + s <= base + size for p, s in spans)
+        assert all(p % 16 == 0 for p in tp.tolist()) and all(p % 64 == 0 for p in wp.tolist())
+        assert all(p % 256 == 0 for p in bp.tolist())
+        spans.sort()
+        assert all(a + s <= b for (a, s), (b, _) in zip(spans, spans[1:])), "allocations overlap"
+        assert C.slab_used(base, size) >= n * each + (n // 32) * 64 + blocks * 256
+        # exhaustion: requests that do not fit return null and leave the cursor alone
+        C.slab_reset(base, size)
+        used0 = C.slab_used(base, size)
+        k.slab_test(base, size, size, tp.data_ptr(), wp.data_ptr(), bp.data_ptr(), errors.data_ptr(), 1, 32,
+                    torch.cuda.current_stream().cuda_stream)
+        torch.cuda.synchronize()
+        got = tp[:32].tolist()
+        assert sum(1 for p in got if p != 0) == 1 and used0 == 0      # exactly one thread gets the whole slab
+        C.slab_destroy(base, size)
+    finally:
+        torch.cuda.synchronize()
+        shm.finalize()
+
+
+def test_warp_coalescing_merges_proxied_puts_and_gets_and_time_buckets_fill():
+    from rocshmem_b200 import runtime as rt
+    shm, k = _fresh(n_local=2, ROCSHMEM_USE_PROXY=1, ROCSHMEM_USE_WF_COAL=1)
+    try:
+        C = rt._C()
+        side = torch.cuda.Stream()
+        nbytes, threads = 4096, 32
+        src = shm.zeros(nbytes, torch.uint8)
+        dst = shm.zeros(nbytes, torch.uint8)
+        pats = []
+        for l in range(2):
+            p = torch.randint(0, 256, (nbytes,), generator=torch.Generator().manual_seed(5 + l), dtype=torch.uint8)
+            pats.append(p)
+            shm.local_view(src, l).copy_(p.cuda())
+        torch.cuda.synchronize()
+        shm.barrier_all()
+        C.reset_stats()
+        before = C.host_stats()[28]
+        for op, origin in ((RMA_PUT, lambda l: (l - 1) % 2), (RMA_GET, lambda l: (l + 1) % 2)):
+            for l in range(2):
+                shm.local_view(dst, l).zero_()
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                k.rma(op, SC_THREAD, dst.data_ptr(), src.data_ptr(), nbytes, 1, 0, threads, side.cuda_stream)
+            torch.cuda.synchronize()
+            assert shm.get_error()["count"] == 0
+            for l in range(2):
+                assert torch.equal(shm.local_view(dst, l).cpu(), pats[origin(l)]), (op, l)
+        executed = C.host_stats()[28] - before
+        # 32 lanes with adjacent equal shares: one command per warp and operation instead of 32
+        assert executed <= 2 * 2 * 2, executed
+        for l in range(2):
+            st = C.device_stats(l)
+            assert st[STAT_PROXY_PACK_NS] > 0 and st[STAT_PROXY_HOST_NS] > 0, st[28:34]
+    finally:
+        torch.cuda.synchronize()
+        shm.finalize()
+
+
+def proxied_collectives_scenario():
+    """Two processes, one GPU each: block-level reduce, fcollect and broadcast of a kernel run through the proxy."""
+    import rocshmem_b200 as shm
+    from rocshmem_b200 import _native
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
+    shm.init(heap_size="64M", backend="cuda", ROCSHMEM_WAIT_TIMEOUT_MS=5000, ROCSHMEM_USE_PROXY=1,
+             ROCSHMEM_PROXY_COLLECTIVES=1, ROCSHMEM_ENABLE_NVLS=0)
+    k = _native.load_test_kernels()
+    n = 1024
+    src = shm.zeros(n * world, torch.float32)
+    dst = shm.zeros(n * world, torch.float32)
+    rc = shm.zeros(4, torch.int32)
+    src.copy_((torch.arange(n * world) + 1000 * rank).float().cuda())
+    torch.cuda.synchronize()
+    shm.barrier_all()
+    side = torch.cuda.Stream()
+    team = shm.team_world().handle
+
+    def run(op, count, root=0):
+        with torch.cuda.stream(side):
+            k.coll(op, "float32", team, dst.data_ptr(), src.data_ptr(), count, root, 1, rc.data_ptr(), 128, side.cuda_stream)
+        torch.cuda.synchronize()
+        assert shm.get_error()["count"] == 0, shm.get_error()
+
+    run(C_SUM, n)
+    want = torch.arange(n).float() * world + 1000.0 * sum(range(world))
+    assert torch.equal(dst.cpu()[:n], want)
+    run(C_FCOLLECT, n)
+    got = dst.cpu().view(world, n)
+    assert all(torch.equal(got[r], torch.arange(n).float() + 1000 * r) for r in range(world))
+    dst.zero_()
+    torch.cuda.synchronize()
+    shm.barrier_all()
+    run(C_BCAST, n, root=world - 1)
+    if rank != world - 1:
+        assert torch.equal(dst.cpu()[:n], torch.arange(n).float() + 1000 * (world - 1))
+    shm.barrier_all()
+    shm.finalize()
+    print(f"rank {rank}: proxied collectives ok")
+
+
+if __name__ == "__main__":
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    proxied_collectives_scenario()
