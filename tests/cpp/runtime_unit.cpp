@@ -16,6 +16,8 @@
 #include "allocator.hpp"
 #include "bootstrap.hpp"
 #include "config.hpp"
+#include "rocshmem/coalesce.h"
+#include "rocshmem/slab.h"
 #include "team.hpp"
 
 using namespace rocshmem;
@@ -160,6 +162,76 @@ static void test_file_bootstrap_between_threads(const std::string &dir) {
   EXPECT(bad.load() == 0);
 }
 
+// Lane arithmetic of the warp coalescer against a lane-by-lane walk, on random warps (every shift and mask in
+// it runs under UBSan here), and the list form.
+static void test_coalesce() {
+  std::mt19937_64 rng(11);
+  for (int round = 0; round < 2000; ++round) {
+    unsigned active = static_cast<unsigned>(rng()) | (1u << (rng() % 32));
+    if (round == 0) active = 0xffffffffu;
+    if (round == 1) active = 0x80000001u;
+    coalesce::Msg m[32];
+    unsigned long long dst = 0x10000, src = 0x80000;
+    for (int l = 0; l < 32; ++l) {
+      unsigned long long size = (rng() % 4) ? 8 : 16;
+      if (rng() % 5 == 0) dst += 64;
+      m[l] = coalesce::Msg{(rng() % 10) ? 1 : 2, dst, src, size};
+      if (active & (1u << l)) {
+        dst += size;
+        src += size;
+      }
+    }
+    unsigned cont = 0;
+    for (int l = 0; l < 32; ++l) {
+      if (!(active & (1u << l))) continue;
+      int p = coalesce::previous_active(active, l);
+      EXPECT(p < l);
+      if (p >= 0 && coalesce::continues(m[p], m[l])) cont |= 1u << l;
+    }
+    int covered = 0, lanes = 0;
+    for (int l = 0; l < 32; ++l) {
+      int n = coalesce::run_length(active, cont, l);
+      covered += n;
+      if (active & (1u << l)) ++lanes;
+      if (n > 0) {
+        // the run is n consecutive active lanes starting here, all but the first continuing their predecessor
+        int seen = 1, q = l + 1;
+        for (; q < 32 && seen < n; ++q) {
+          if (!(active & (1u << q))) continue;
+          EXPECT(cont & (1u << q));
+          ++seen;
+        }
+        EXPECT(seen == n);
+        for (; q < 32; ++q) {
+          if (active & (1u << q)) {
+            EXPECT(!(cont & (1u << q)));   // the next active lane starts a new run
+            break;
+          }
+        }
+      }
+    }
+    EXPECT(covered == lanes);
+  }
+  coalesce::Msg list[5] = {{1, 100, 500, 10}, {1, 110, 510, 10}, {2, 120, 520, 10}, {2, 130, 530, 10}, {2, 150, 550, 10}};
+  EXPECT(coalesce::merge_runs(list, 5) == 3);
+  EXPECT(list[0].size == 20 && list[1].size == 20 && list[1].pe == 2 && list[2].dst == 150);
+  EXPECT(coalesce::merge_runs(list, 0) == 0);
+}
+
+// Placement arithmetic shared by the host and device halves of the slab allocator.
+static void test_slab_place() {
+  rocshmemx_slab_t s{nullptr, 4096, nullptr};
+  EXPECT(detail::slab_place(s, 0, 100, 16) == 0);
+  EXPECT(detail::slab_place(s, 100, 1, 1) == 100);
+  EXPECT(detail::slab_place(s, 101, 64, 256) == 256);
+  EXPECT(detail::slab_place(s, 0, 4096, 16) == 0);
+  EXPECT(detail::slab_place(s, 0, 4097, 16) == ~0ull);
+  EXPECT(detail::slab_place(s, 4090, 8, 16) == ~0ull);     // rounding up leaves the slab
+  EXPECT(detail::slab_place(s, 4096, 1, 1) == ~0ull);
+  EXPECT(detail::slab_place(s, 0, 0, 16) == ~0ull);
+  EXPECT(detail::slab_place(s, 0, ~0ull, 16) == ~0ull);    // no overflow in the fit test
+}
+
 int main(int argc, char **argv) {
   if (argc < 2) {
     std::fprintf(stderr, "usage: %s <scratch directory>\n", argv[0]);
@@ -170,6 +242,8 @@ int main(int argc, char **argv) {
   test_allocator_is_deterministic();
   test_team_math();
   test_config();
+  test_coalesce();
+  test_slab_place();
   test_file_bootstrap_between_threads(argv[1]);
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);
