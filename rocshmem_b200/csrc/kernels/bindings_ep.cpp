@@ -49,6 +49,11 @@ void bind_ep(py::module_ &m) {
         h.buf.grid_counter = P<unsigned long long>(get("grid_counter"));
         h.buf.phase_ns = P<unsigned long long>(get("phase_ns"));
         h.buf.recv_info = P<int>(get("recv_info"));
+        // Optional: with a work counter the dispatch kernel hands tokens out dynamically.
+        if (ptrs.contains("work_counter")) {
+          h.buf.work_counter = P<unsigned long long>(get("work_counter"));
+          h.cfg.dynamic = 1;
+        }
         return h;
       }))
       .def_readonly("epoch", &EpHandle::epoch)

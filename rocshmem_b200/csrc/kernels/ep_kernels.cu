@@ -111,6 +111,10 @@ __device__ __forceinline__ int4 quantize16(const int4 &a, const int4 &b, float *
   return q;
 }
 
+// DYNAMIC: after the offsets are known every block publishes the destination rows of its own tokens, a second
+// grid barrier follows, and warps then take tokens one at a time from a device-wide counter. Blocks whose share
+// happens to carry fewer bytes no longer idle while the heaviest block finishes.
+template <bool DYNAMIC>
 __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs a) {
   extern __shared__ __align__(16) unsigned char s_dyn[];  // masks [tpb] u64, then ranks [tpb][P] int
   __shared__ int s_rank_cnt[ROCSHMEM_MAX_PES];
@@ -153,6 +157,8 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   unsigned long long *phase_ns = rebase(a.buf.phase_ns);
   const bool stamp = (b == 0 && tid == 0);
   if (stamp) phase_ns[0] = detail::now_ns();
+  unsigned long long *work = DYNAMIC ? rebase(a.buf.work_counter) : nullptr;
+  if (DYNAMIC && stamp) work[parity ^ 1] = 0;  // cleared for the next call
 
   // ---- A: routing scan ------------------------------------------------------------------------------
   for (unsigned i = tid; i < ROCSHMEM_MAX_PES; i += nthr) s_rank_cnt[i] = 0;
@@ -189,7 +195,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
     s_total[d] = 0;
   }
   if (stamp) phase_ns[1] = detail::now_ns();
-  if (!grid_barrier(grid_counter, epoch, B)) return;
+  if (!grid_barrier(grid_counter, DYNAMIC ? 2ull * epoch - 1 : epoch, B)) return;
   if (stamp) phase_ns[2] = detail::now_ns();
 
   // ---- B: offsets and count exchange -------------------------------------------------------------------
@@ -229,6 +235,18 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
     if (!ok) atomicExch(&s_ok, 0);
   }
   __syncthreads();
+  if (DYNAMIC) {
+    // A failed count wait must not leave the other blocks waiting at the second barrier for ever: every block
+    // reaches it (its waits are bounded), and gives up afterwards.
+    if (s_ok) {
+      for (int i = tid; i < (t1 - t0) * P; i += nthr) {
+        const int tk = i / P, d = i % P;
+        const bool goes = (s_mask[tk] >> d) & 1ull;
+        sent_slot[size_t(t0 + tk) * P + d] = goes ? s_base[d] + s_blk_base[d] + s_rank_in_block[tk * P + d] : -1;
+      }
+    }
+    if (!grid_barrier(grid_counter, 2ull * epoch, B)) return;
+  }
   if (!s_ok) return;
   if (stamp) phase_ns[3] = detail::now_ns();
 
@@ -237,14 +255,31 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   const int iters = H / 512;
   const int nscale = H / 128;
   constexpr int kBatch = 8;  // iterations (of 512 elements) whose loads are issued together
-  for (int tok = t0 + warp; tok < t1; tok += nwarps) {
-    const unsigned long long mask = s_mask[tok - t0];
+  for (int tok_static = t0 + warp;; tok_static += nwarps) {
+    int tok;
+    if (DYNAMIC) {
+      unsigned long long next = 0;
+      if (lane == 0) next = atomicAdd(work + parity, 1ull);
+      next = __shfl_sync(0xffffffffu, next, 0);
+      if (next >= static_cast<unsigned long long>(T)) break;
+      tok = static_cast<int>(next);
+    } else {
+      if (tok_static >= t1) break;
+      tok = tok_static;
+    }
+    // In dynamic mode mask and rows were written by the token's owner block before the second barrier: read
+    // them through L2.
+    const unsigned long long mask = DYNAMIC ? __ldcg(tok_mask + tok) : s_mask[tok - t0];
     // Lane d keeps the row index on destination d; everybody reads it with a shuffle.
     int my_slot = -1;
-    if (lane < unsigned(P) && ((mask >> lane) & 1ull)) {
-      my_slot = s_base[lane] + s_blk_base[lane] + s_rank_in_block[(tok - t0) * P + lane];
+    if (DYNAMIC) {
+      if (lane < unsigned(P)) my_slot = __ldcg(sent_slot + size_t(tok) * P + lane);
+    } else {
+      if (lane < unsigned(P) && ((mask >> lane) & 1ull)) {
+        my_slot = s_base[lane] + s_blk_base[lane] + s_rank_in_block[(tok - t0) * P + lane];
+      }
+      if (lane < unsigned(P)) sent_slot[size_t(tok) * P + lane] = my_slot;
     }
-    if (lane < unsigned(P)) sent_slot[size_t(tok) * P + lane] = my_slot;
     if (mask == 0) continue;
     const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
     int k_idx = -1;
@@ -583,7 +618,13 @@ int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf,
   const int tpb = (cfg.max_tokens + cfg.blocks - 1) / cfg.blocks;
   const size_t smem = size_t(tpb) * (ht->world.size * sizeof(int) + sizeof(unsigned long long));
   if (smem > 40 * 1024) return cudaErrorInvalidValue;  // use more blocks for this many tokens
-  return launch_pes(ep_dispatch_kernel, cfg.blocks, kEpThreads, smem, static_cast<cudaStream_t>(stream), true, a);
+  if (cfg.dynamic) {
+    if (buf.work_counter == nullptr) return cudaErrorInvalidValue;
+    return launch_pes(ep_dispatch_kernel<true>, cfg.blocks, kEpThreads, smem, static_cast<cudaStream_t>(stream), true,
+                      a);
+  }
+  return launch_pes(ep_dispatch_kernel<false>, cfg.blocks, kEpThreads, smem, static_cast<cudaStream_t>(stream), true,
+                    a);
 }
 
 int ep_combine(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *y, void *out,

@@ -36,6 +36,8 @@ struct EpConfig {
   int quantize;        // 1: dispatch carries e4m3 rows + one fp32 scale per 128 elements; 0: bf16 rows
   int layout;          // EpLayout
   int blocks;          // blocks per PE (the same on every member)
+  int dynamic;         // 1: dispatch hands tokens to warps through a device-wide counter instead of fixed
+                       //    per-block shares (needs EpBuffers::work_counter; fixed for the buffers' life)
 };
 
 // Symmetric buffers of one dispatcher (all allocated by the caller on the symmetric heap).
@@ -57,6 +59,7 @@ struct EpBuffers {
   // outputs, local
   int *recv_info;           // [0] total rows, [1 + s] first row of source s (P + 1 entries), then
                             // [2 + P + e] rows whose top-k contains local expert e
+  unsigned long long *work_counter;  // [2] next token to hand out, double-buffered by call parity (dynamic mode)
 };
 
 // x [T, hidden] bf16, topk_idx [T, top_k] int32 (global expert ids, -1 = unused), topk_w [T, top_k] fp32.

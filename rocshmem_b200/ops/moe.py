@@ -16,6 +16,7 @@ every source a fixed window of ``max_tokens`` rows so that sending needs no coun
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 from typing import Optional
 
@@ -81,7 +82,10 @@ class EpDispatcher:
 
     def __init__(self, num_experts: int, top_k: int, hidden: int, max_tokens: int,
                  team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact",
-                 blocks: Optional[int] = None):
+                 blocks: Optional[int] = None, dynamic: Optional[bool] = None):
+        """``dynamic``: dispatch hands tokens to warps through a device-wide counter instead of fixed per-block
+        shares (levels the tail when blocks carry unequal numbers of bytes, costs a second grid barrier). ``None``
+        takes ``ROCSHMEM_EP_DYNAMIC`` (default off). Every member must choose the same."""
         C = rt._C()
         if not C.is_cuda():
             raise RuntimeError("EpDispatcher needs the CUDA backend")
@@ -115,10 +119,16 @@ class EpDispatcher:
         self.grid_counter = z(1, torch.int64)
         self.phase_ns = z(16, torch.int64)
         self.recv_info = z(1 + 2 * P + self.experts_per_rank, torch.int32)
+        if dynamic is None:
+            dynamic = os.environ.get("ROCSHMEM_EP_DYNAMIC", "0") not in ("", "0")
+        self.dynamic = bool(dynamic)
+        self.work_counter = z(2, torch.int64) if self.dynamic else None
         self._y = None
         ptrs = {name: getattr(self, name).data_ptr() for name in (
             "recv_x", "recv_scales", "recv_meta", "cnt_in", "exp_in", "sent_slot", "tok_mask", "blk_cnt",
             "exp_cnt", "grid_counter", "phase_ns", "recv_info")}
+        if self.dynamic:
+            ptrs["work_counter"] = self.work_counter.data_ptr()
         self._h = C.EpHandle(self.team.handle, num_experts, top_k, hidden, max_tokens, int(quantize),
                              self.layout, self.blocks, ptrs)
         self.kernel_launches = 0
@@ -133,7 +143,7 @@ class EpDispatcher:
         lay = list(getattr(self, "_lay", ()))
         rt.free_all([self.recv_x, self.recv_scales, self.recv_meta, self.cnt_in, self.exp_in, self.sent_slot,
                      self.tok_mask, self.blk_cnt, self.exp_cnt, self.grid_counter, self.phase_ns, self.recv_info,
-                     self._y] + lay)
+                     self.work_counter, self._y] + lay)
         self._h = None
         self._y = None
         if lay:

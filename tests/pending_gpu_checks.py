@@ -6,6 +6,8 @@ The file name does not match pytest's ``test_*.py`` pattern on purpose, so the d
 run it explicitly, and move each case into the regular test files once it has passed on a B200:
 
     python -m pytest tests/pending_gpu_checks.py -m gpu -x -q
+    ROCSHMEM_EP_DYNAMIC=1 python -m pytest tests/test_gpu_moe.py -m gpu -x -q     # dynamic token hand-out in dispatch
+    ROCSHMEM_EP_DYNAMIC=1 python bench.py --steps 50                              # ... and its timing against the default
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 tests/pending_gpu_checks.py
 """
 import os
