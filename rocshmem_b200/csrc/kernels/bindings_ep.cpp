@@ -26,6 +26,7 @@ struct EpHandle {
   EpBuffers buf{};
   uintptr_t team = 0;
   unsigned epoch = 0;
+  unsigned long long combine_base = 0;  // dynamic mode: counter increments of all earlier combine calls
 };
 }  // namespace
 
@@ -66,7 +67,9 @@ void bind_ep(py::module_ &m) {
       .def("combine", [](EpHandle &h, uintptr_t y, uintptr_t out, uintptr_t topk_idx, uintptr_t topk_w,
                          int num_tokens, int weighted, uintptr_t stream) {
         check(ep_combine(reinterpret_cast<rocshmem_team_t>(h.team), h.cfg, h.buf, P<void>(y), P<void>(out),
-                         P<int>(topk_idx), P<float>(topk_w), num_tokens, weighted, P<void>(stream)), "ep_combine");
+                         P<int>(topk_idx), P<float>(topk_w), num_tokens, weighted, P<void>(stream), h.combine_base),
+              "ep_combine");
+        if (h.cfg.dynamic) h.combine_base += ep_combine_fetches(h.cfg, num_tokens);
       })
       .def("expert_layout", [](EpHandle &h, int n_ranks, uintptr_t offsets, uintptr_t row_index, uintptr_t pair_k,
                                uintptr_t cursor, uintptr_t stream) {

@@ -394,6 +394,7 @@ struct CombineArgs {
   int num_tokens;
   int weighted;
   rocshmem_team_t team;
+  unsigned long long work_base;  // dynamic mode: counter value at which this call's tokens start
 };
 
 // Sums `n_src` rows (scaled by wgt) into dst. U vectors per source are loaded before any is used, so
@@ -438,6 +439,9 @@ __device__ __forceinline__ void combine_row(int4 *dst, const int4 **src, const f
   }
 }
 
+// DYNAMIC: warps take tokens from a device-wide counter (a token costs as many remote rows as it has sources, one
+// to eight, so fixed shares differ a lot); the counter only grows, the host tells every call where it starts.
+template <bool DYNAMIC>
 __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_kernel(CombineArgs a) {
   __shared__ const int4 *s_src[kCombineThreads / 32][EP_MAX_TOPK];
   __shared__ float s_wgt[kCombineThreads / 32][EP_MAX_TOPK];
@@ -462,7 +466,19 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_kernel(CombineA
   const unsigned gwarp = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
   const unsigned nwarps = gridDim.x * (blockDim.x / 32);
   const int nvec = H / 8;  // int4 vectors of 8 bf16 per row
-  for (int tok = gwarp; tok < a.num_tokens; tok += nwarps) {
+  unsigned long long *work = DYNAMIC ? rebase(a.buf.work_counter) + 2 : nullptr;
+  for (int tok_static = gwarp;; tok_static += nwarps) {
+    int tok;
+    if (DYNAMIC) {
+      unsigned long long next = 0;
+      if (lane == 0) next = atomicAdd(work, 1ull) - a.work_base;
+      next = __shfl_sync(0xffffffffu, next, 0);
+      if (next >= static_cast<unsigned long long>(a.num_tokens)) break;
+      tok = static_cast<int>(next);
+    } else {
+      if (tok_static >= a.num_tokens) break;
+      tok = tok_static;
+    }
     // Lane d owns destination rank d: its row index there and the gate weight of that rank.
     // Lanes < K fetch one (expert, weight) pair each, so all small loads are issued at once.
     int my_slot = -1;
@@ -608,6 +624,10 @@ int ep_default_blocks() {
   return std::max(1, per_pe);
 }
 
+unsigned long long ep_combine_fetches(const EpConfig &cfg, int num_tokens) {
+  return static_cast<unsigned long long>(num_tokens) + static_cast<unsigned long long>(cfg.blocks) * (kCombineThreads / 32);
+}
+
 int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *x,
                 const int *topk_idx, const float *topk_w, int num_tokens, unsigned epoch, void *stream) {
   Runtime &rt = Runtime::instance();
@@ -628,14 +648,21 @@ int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf,
 }
 
 int ep_combine(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *y, void *out,
-               const int *topk_idx, const float *topk_w, int num_tokens, int weighted, void *stream) {
+               const int *topk_idx, const float *topk_w, int num_tokens, int weighted, void *stream,
+               unsigned long long combine_calls_base) {
   Runtime &rt = Runtime::instance();
   HostTeam *ht = rt.team_from_handle(team);
   if (!ht) return cudaErrorInvalidValue;
   if (int rc = validate(cfg, ht->world.size, num_tokens)) return rc;
   CombineArgs a{cfg, buf, static_cast<const __nv_bfloat16 *>(y), static_cast<__nv_bfloat16 *>(out), topk_idx,
-                topk_w, num_tokens, weighted, team};
-  return launch_pes(ep_combine_kernel, cfg.blocks, kCombineThreads, 0, static_cast<cudaStream_t>(stream), false, a);
+                topk_w, num_tokens, weighted, team, combine_calls_base};
+  if (cfg.dynamic) {
+    if (buf.work_counter == nullptr) return cudaErrorInvalidValue;
+    return launch_pes(ep_combine_kernel<true>, cfg.blocks, kCombineThreads, 0, static_cast<cudaStream_t>(stream), false,
+                      a);
+  }
+  return launch_pes(ep_combine_kernel<false>, cfg.blocks, kCombineThreads, 0, static_cast<cudaStream_t>(stream), false,
+                    a);
 }
 
 int fp8_quantize_1x128(const void *x, void *q, float *scales, size_t rows, int hidden, void *stream) {

@@ -59,7 +59,9 @@ struct EpBuffers {
   // outputs, local
   int *recv_info;           // [0] total rows, [1 + s] first row of source s (P + 1 entries), then
                             // [2 + P + e] rows whose top-k contains local expert e
-  unsigned long long *work_counter;  // [2] next token to hand out, double-buffered by call parity (dynamic mode)
+  // Dynamic mode: [0], [1] next token of a dispatch, double-buffered by call parity; [2] tokens handed out by
+  // all combine calls so far (never reset: every call knows where its range starts).
+  unsigned long long *work_counter;
 };
 
 // x [T, hidden] bf16, topk_idx [T, top_k] int32 (global expert ids, -1 = unused), topk_w [T, top_k] fp32.
@@ -70,8 +72,13 @@ int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf,
 // y: symmetric [P * max_tokens, hidden] bf16 in the row layout produced by dispatch. out [T, hidden]
 // bf16 (local). Every token receives the sum over the ranks it was sent to of that rank's row,
 // scaled (weighted != 0) by the sum of the token's gate weights of the experts living on that rank.
+// `combine_calls_base` (dynamic mode only): value of work_counter[2] when this call starts, i.e. the sum over the
+// earlier combine calls on these buffers of ep_combine_fetches(cfg, their num_tokens).
 int ep_combine(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *y, void *out,
-               const int *topk_idx, const float *topk_w, int num_tokens, int weighted, void *stream);
+               const int *topk_idx, const float *topk_w, int num_tokens, int weighted, void *stream,
+               unsigned long long combine_calls_base = 0);
+// Counter increments of one dynamic combine call: one per token plus one failing fetch per warp.
+unsigned long long ep_combine_fetches(const EpConfig &cfg, int num_tokens);
 
 // Stand-alone 1x128 block-scaled e4m3 quantisation of [rows, hidden] bf16 and its inverse.
 int fp8_quantize_1x128(const void *x_bf16, void *q_u8, float *scales, size_t rows, int hidden, void *stream);

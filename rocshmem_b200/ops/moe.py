@@ -122,7 +122,7 @@ class EpDispatcher:
         if dynamic is None:
             dynamic = os.environ.get("ROCSHMEM_EP_DYNAMIC", "0") not in ("", "0")
         self.dynamic = bool(dynamic)
-        self.work_counter = z(2, torch.int64) if self.dynamic else None
+        self.work_counter = z(4, torch.int64) if self.dynamic else None
         self._y = None
         ptrs = {name: getattr(self, name).data_ptr() for name in (
             "recv_x", "recv_scales", "recv_meta", "cnt_in", "exp_in", "sent_slot", "tok_mask", "blk_cnt",
