@@ -83,9 +83,9 @@ class EpDispatcher:
     def __init__(self, num_experts: int, top_k: int, hidden: int, max_tokens: int,
                  team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact",
                  blocks: Optional[int] = None, dynamic: Optional[bool] = None):
-        """``dynamic``: dispatch hands tokens to warps through a device-wide counter instead of fixed per-block
-        shares (levels the tail when blocks carry unequal numbers of bytes, costs a second grid barrier). ``None``
-        takes ``ROCSHMEM_EP_DYNAMIC`` (default off). Every member must choose the same."""
+        """``dynamic``: dispatch and combine hand tokens to warps through a device-wide counter instead of fixed
+        shares (levels the tail when shares carry unequal numbers of bytes; dispatch pays a second grid barrier for
+        it). ``None`` takes ``ROCSHMEM_EP_DYNAMIC`` (default off). Every member must choose the same."""
         C = rt._C()
         if not C.is_cuda():
             raise RuntimeError("EpDispatcher needs the CUDA backend")
