@@ -1,0 +1,50 @@
+"""Builds the host-only C++ program tests/cpp/host_api_sos.cpp with g++ against the runtime library and runs it as
+several processes on the CPU shared-memory backend: the typed C++ host API (put / get / p / g, atomics, waits,
+collectives, teams, contexts, rocshmem_ptr) end to end, as the reference's SOS programs do for its host API."""
+import os
+import shutil
+import subprocess
+
+import pytest
+
+from rocshmem_b200 import _build
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+INC = os.path.join(ROOT, "rocshmem_b200", "csrc", "include")
+LIB = os.path.join(ROOT, "rocshmem_b200", "lib")
+
+
+@pytest.fixture(scope="module")
+def program(tmp_path_factory):
+    if shutil.which("g++") is None:
+        pytest.skip("needs g++")
+    if not _build.is_built():
+        _build.build(with_tests=False)
+    exe = str(tmp_path_factory.mktemp("sos") / "host_api_sos")
+    cmd = ["g++", "-std=c++17", "-O1", "-g", f"-I{INC}", os.path.join(ROOT, "tests", "cpp", "host_api_sos.cpp"), "-o", exe,
+           f"-L{LIB}", "-lrocshmem_b200", f"-Wl,-rpath,{LIB}"]
+    build = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert build.returncode == 0, build.stderr[-3000:]
+    return exe
+
+
+@pytest.mark.parametrize("world", [2, 5])
+def test_typed_host_api_program_on_the_cpu_backend(program, world, tmp_path):
+    kv = tmp_path / "kv"
+    kv.mkdir()
+    procs = []
+    for r in range(world):
+        env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), ROCSHMEM_BACKEND="host",
+                   ROCSHMEM_HEAP_SIZE="16M", ROCSHMEM_BOOTSTRAP_DIR=str(kv), ROCSHMEM_WAIT_TIMEOUT_MS="30000")
+        procs.append(subprocess.Popen([program], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = []
+    try:
+        for p in procs:
+            out, _ = p.communicate(timeout=180)
+            outs.append((p.returncode, out))
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
+    for r, (rc, out) in enumerate(outs):
+        assert rc == 0 and f"[pe {r}] PASS" in out, (r, rc, out[-2000:])
