@@ -1,6 +1,7 @@
-"""Builds the host-only C++ program tests/cpp/host_api_sos.cpp with g++ against the runtime library and runs it as
-several processes on the CPU shared-memory backend: the typed C++ host API (put / get / p / g, atomics, waits,
-collectives, teams, contexts, rocshmem_ptr) end to end, as the reference's SOS programs do for its host API."""
+"""Builds the host-only C++ programs tests/cpp/host_api_sos.cpp and host_threads_sos.cpp with g++ against the
+runtime library and runs them as several processes on the CPU shared-memory backend: the typed C++ host API (put /
+get / p / g, atomics, waits, collectives, teams, contexts, rocshmem_ptr; then several threads per process, each
+with its own context) end to end, as the reference's SOS programs do for its host API."""
 import os
 import shutil
 import subprocess
@@ -15,21 +16,25 @@ LIB = os.path.join(ROOT, "rocshmem_b200", "lib")
 
 
 @pytest.fixture(scope="module")
-def program(tmp_path_factory):
+def programs(tmp_path_factory):
     if shutil.which("g++") is None:
         pytest.skip("needs g++")
     if not _build.is_built():
         _build.build(with_tests=False)
-    exe = str(tmp_path_factory.mktemp("sos") / "host_api_sos")
-    cmd = ["g++", "-std=c++17", "-O1", "-g", f"-I{INC}", os.path.join(ROOT, "tests", "cpp", "host_api_sos.cpp"), "-o", exe,
-           f"-L{LIB}", "-lrocshmem_b200", f"-Wl,-rpath,{LIB}"]
-    build = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
-    assert build.returncode == 0, build.stderr[-3000:]
-    return exe
+    out = {}
+    for name in ("host_api_sos", "host_threads_sos"):
+        exe = str(tmp_path_factory.mktemp("sos") / name)
+        cmd = ["g++", "-std=c++17", "-O1", "-g", f"-I{INC}", os.path.join(ROOT, "tests", "cpp", name + ".cpp"), "-o", exe,
+               f"-L{LIB}", "-lrocshmem_b200", f"-Wl,-rpath,{LIB}", "-lpthread"]
+        build = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+        assert build.returncode == 0, build.stderr[-3000:]
+        out[name] = exe
+    return out
 
 
-@pytest.mark.parametrize("world", [2, 5])
-def test_typed_host_api_program_on_the_cpu_backend(program, world, tmp_path):
+@pytest.mark.parametrize("name,world", [("host_api_sos", 2), ("host_api_sos", 5), ("host_threads_sos", 3)])
+def test_cpp_host_programs_on_the_cpu_backend(programs, name, world, tmp_path):
+    program = programs[name]
     kv = tmp_path / "kv"
     kv.mkdir()
     procs = []
