@@ -681,7 +681,66 @@ def ep_collective_baseline():
     dist.destroy_process_group()
 
 
-SCENARIOS = {f.__name__: f for f in (ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def data_parallel():
+    """Gradient buckets over the world team: averaged gradients of a small model against the gradient of the mean
+    loss over all ranks' batches, with buckets small enough to need several, mixed dtypes and an unused parameter."""
+    from rocshmem_b200.parallel.data_parallel import GradientBuckets
+    init("32M")
+    me, n = shm.my_pe(), shm.n_pes()
+
+    def make_model():
+        torch.manual_seed(5)
+        m = torch.nn.Sequential(torch.nn.Linear(24, 40), torch.nn.Tanh(), torch.nn.Linear(40, 17), torch.nn.Tanh(),
+                                torch.nn.Linear(17, 3))
+        m.extra = torch.nn.Parameter(torch.ones(5))                          # never used: no gradient
+        m.scale = torch.nn.Parameter(torch.ones(3, dtype=torch.bfloat16))    # another dtype: its own bucket
+        return m
+
+    def batch(r, step):
+        g = torch.Generator().manual_seed(1000 * step + r)
+        return torch.randn(8, 24, generator=g), torch.randn(8, 3, generator=g)
+
+    def loss_of(m, x, y):
+        return ((m(x) * m.scale.float() - y) ** 2).mean()
+
+    used_before = shm.heap_info()["used"]
+    model = make_model()
+    dp = GradientBuckets(list(model.parameters()), bucket_bytes=2048)
+    assert len(dp.buckets) >= 3
+    for step in range(3):
+        model.zero_grad(set_to_none=True)
+        x, y = batch(me, step)
+        loss_of(model, x, y).backward()
+        dp.finish()
+        ref = make_model()
+        for r in range(n):
+            xr, yr = batch(r, step)
+            (loss_of(ref, xr, yr) / n).backward()
+        for (name, p), q in zip(model.named_parameters(), ref.parameters()):
+            want = q.grad if q.grad is not None else torch.zeros_like(q)
+            tol = 2e-2 if p.dtype == torch.bfloat16 else 1e-5
+            assert torch.allclose(p.grad.float(), want.float(), rtol=tol, atol=tol), (step, name)
+    # without hooks: everything is packed and reduced in finish()
+    dp.destroy()
+    dp = GradientBuckets(list(model.parameters()), bucket_bytes=1 << 20, average=False, register_hooks=False)
+    model.zero_grad(set_to_none=True)
+    x, y = batch(me, 9)
+    loss_of(model, x, y).backward()
+    mine = model[0].weight.grad.clone()
+    dp.finish()
+    total = shm.zeros(mine.numel(), torch.float32)
+    part = shm.zeros(mine.numel(), torch.float32)
+    part.copy_(mine.reshape(-1))
+    assert coll.reduce(total, part, shm.OP_SUM) == 0
+    assert torch.allclose(model[0].weight.grad.reshape(-1), total.cpu(), rtol=1e-5, atol=1e-6)
+    shm.free(part)
+    shm.free(total)
+    dp.destroy()
+    assert shm.heap_info()["used"] == used_before
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

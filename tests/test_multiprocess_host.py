@@ -61,3 +61,7 @@ def test_threads_per_process_all_to_all_wait_chain_and_large_transfers():
 
 def test_all_to_all_baseline_of_dispatch_and_combine():
     assert_all_ok(run_ranks("ep_collective_baseline", 3, timeout=240))
+
+
+def test_data_parallel_gradient_buckets():
+    assert_all_ok(run_ranks("data_parallel", 3, timeout=240))
