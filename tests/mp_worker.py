@@ -740,7 +740,44 @@ def data_parallel():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def ulysses():
+    """Sequence-parallel attention through the all-to-all re-sharding: every rank holds a slice of the sequence,
+    attention runs per head on whole sequences, the result comes back as sequence slices and must equal the
+    single-process computation."""
+    from rocshmem_b200.parallel.ulysses import UlyssesResharder
+    init("32M")
+    me, n = shm.my_pe(), shm.n_pes()
+    S, H, D = 8 * n, 2 * n, 16
+    g = torch.Generator().manual_seed(3)
+    q, k, v = (torch.randn(S, H, D, generator=g) for _ in range(3))
+    used_before = shm.heap_info()["used"]
+    sp = UlyssesResharder(S, H, D, torch.float32)
+    sl, hl = S // n, H // n
+    mine = slice(me * sl, (me + 1) * sl)
+    qh, kh, vh = (sp.seq_to_heads(t[mine].contiguous().to(dev())) for t in (q, k, v))
+    heads = slice(me * hl, (me + 1) * hl)
+    assert torch.equal(qh.cpu(), q[:, heads]) and torch.equal(kh.cpu(), k[:, heads]) and torch.equal(vh.cpu(), v[:, heads])
+
+    def attention(q_, k_, v_):                   # [S, h, D] per head, causal
+        scores = torch.einsum("shd,thd->hst", q_, k_) / D ** 0.5
+        scores = scores.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), float("-inf"))
+        return torch.einsum("hst,thd->shd", torch.softmax(scores, dim=-1), v_)
+
+    o_heads = attention(qh.cpu(), kh.cpu(), vh.cpu())
+    o_seq = sp.heads_to_seq(o_heads.contiguous().to(dev()))
+    want = attention(q, k, v)[mine]
+    assert torch.allclose(o_seq.cpu(), want, rtol=1e-5, atol=1e-6)
+    try:
+        sp.seq_to_heads(torch.zeros(sl + 1, H, D).to(dev()))
+        raise AssertionError("a wrong shape must be refused")
+    except ValueError:
+        pass
+    sp.destroy()
+    assert shm.heap_info()["used"] == used_before
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

@@ -65,3 +65,7 @@ def test_all_to_all_baseline_of_dispatch_and_combine():
 
 def test_data_parallel_gradient_buckets():
     assert_all_ok(run_ranks("data_parallel", 3, timeout=240))
+
+
+def test_sequence_parallel_attention_through_all_to_all_resharding():
+    assert_all_ok(run_ranks("ulysses", 4, timeout=240))
