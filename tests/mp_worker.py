@@ -777,7 +777,44 @@ def ulysses():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def ring_attention():
+    """Context parallelism: keys and values travel around the ring (put, counter, wait), every rank accumulates its
+    queries' attention online; the result equals single-process attention, causal and not."""
+    from rocshmem_b200.parallel.ring import RingExchange, ring_attention as ring_attn
+    init("32M")
+    me, n = shm.my_pe(), shm.n_pes()
+    S, H, D = 6 * n, 3, 8
+    sl = S // n
+    g = torch.Generator().manual_seed(17)
+    q, k, v = (torch.randn(S, H, D, generator=g) for _ in range(3))
+    mine = slice(me * sl, (me + 1) * sl)
+    used_before = shm.heap_info()["used"]
+    rk, rv = RingExchange((sl, H, D), torch.float32), RingExchange((sl, H, D), torch.float32)
+    # the exchange by itself: after j shifts everybody holds the block of the rank j to its left
+    blk = torch.full((sl, H, D), float(me)).to(dev())
+    for j in range(1, 2 * n + 1):
+        blk = rk.shift(blk)
+        assert torch.all(blk.cpu() == float((me - j) % n)), (j, blk.flatten()[:2])
+    rk.destroy()
+    rk = RingExchange((sl, H, D), torch.float32)
+
+    def full(causal):
+        scores = torch.einsum("shd,thd->hst", q, k) / D ** 0.5
+        if causal:
+            scores = scores.masked_fill(torch.triu(torch.ones(S, S, dtype=torch.bool), 1), float("-inf"))
+        return torch.einsum("hst,thd->shd", torch.softmax(scores, dim=-1), v)
+
+    for causal in (False, True):
+        out = ring_attn(q[mine].to(dev()), k[mine].to(dev()), v[mine].to(dev()), rk, rv, causal=causal)
+        assert torch.allclose(out.cpu(), full(causal)[mine], rtol=1e-5, atol=1e-5), causal
+        shm.barrier_all()
+    rk.destroy()
+    rv.destroy()
+    assert shm.heap_info()["used"] == used_before
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

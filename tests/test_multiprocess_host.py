@@ -69,3 +69,7 @@ def test_data_parallel_gradient_buckets():
 
 def test_sequence_parallel_attention_through_all_to_all_resharding():
     assert_all_ok(run_ranks("ulysses", 4, timeout=240))
+
+
+def test_ring_exchange_and_ring_attention():
+    assert_all_ok(run_ranks("ring_attention", 4, timeout=240))
