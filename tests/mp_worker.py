@@ -814,7 +814,52 @@ def ring_attention():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def pipeline_stages():
+    """Three pipeline stages with the all-forward, all-backward schedule: losses and parameter gradients equal
+    those of the whole model run in one process over the same micro-batches."""
+    from rocshmem_b200.parallel.pipeline import PipelineStage
+    init("32M")
+    me, n = shm.my_pe(), shm.n_pes()
+    d, mb, micro = 12, 4, 5
+
+    def make_layers():
+        torch.manual_seed(21)
+        return [torch.nn.Sequential(torch.nn.Linear(d, d), torch.nn.Tanh()) for _ in range(n)]
+
+    g = torch.Generator().manual_seed(4)
+    xs = [torch.randn(mb, d, generator=g) for _ in range(micro)]
+    ys = [torch.randn(mb, d, generator=g) for _ in range(micro)]
+    loss_fn = lambda out, tgt: ((out - tgt) ** 2).mean()
+    used_before = shm.heap_info()["used"]
+    mine = make_layers()[me]
+    stage = PipelineStage(mine, num_stages=n, act_shape=(mb, d))
+    assert stage.active and stage.stage == me
+    for rep in range(2):
+        mine.zero_grad(set_to_none=True)
+        losses = stage.run(micro_batches=xs if me == 0 else None, loss_fn=loss_fn if me == n - 1 else None,
+                           targets=ys if me == n - 1 else None, num_micro=micro)
+        ref = make_layers()
+        ref_losses = []
+        for x, y in zip(xs, ys):
+            h = x
+            for layer in ref:
+                h = layer(h)
+            l = loss_fn(h, y)
+            l.backward()
+            ref_losses.append(l.detach())
+        for p, q in zip(mine.parameters(), ref[me].parameters()):
+            assert torch.allclose(p.grad, q.grad, rtol=1e-5, atol=1e-6), rep
+        if me == n - 1:
+            assert torch.allclose(torch.stack(losses).cpu(), torch.stack(ref_losses), rtol=1e-5, atol=1e-6)
+        else:
+            assert losses is None
+        shm.barrier_all()
+    stage.destroy()
+    assert shm.heap_info()["used"] == used_before
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

@@ -73,3 +73,7 @@ def test_sequence_parallel_attention_through_all_to_all_resharding():
 
 def test_ring_exchange_and_ring_attention():
     assert_all_ok(run_ranks("ring_attention", 4, timeout=240))
+
+
+def test_pipeline_stages_match_the_whole_model():
+    assert_all_ok(run_ranks("pipeline_stages", 3, timeout=240))
