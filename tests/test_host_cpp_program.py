@@ -53,3 +53,28 @@ def test_cpp_host_programs_on_the_cpu_backend(programs, name, world, tmp_path):
                 p.kill()
     for r, (rc, out) in enumerate(outs):
         assert rc == 0 and f"[pe {r}] PASS" in out, (r, rc, out[-2000:])
+
+
+def test_launcher_runs_ranks_tags_output_and_propagates_failures(programs):
+    """python -m rocshmem_b200.launch: the mpirun of this runtime."""
+    import io
+    import sys
+    import time
+
+    from rocshmem_b200 import launch
+    out = io.StringIO()
+    rc = launch.launch([programs["host_api_sos"]], 3, backend="host", timeout_s=120, out=out,
+                       extra_env={"ROCSHMEM_HEAP_SIZE": "16M"})
+    text = out.getvalue()
+    assert rc == 0, text[-2000:]
+    assert all(f"[{r}] [pe {r}] PASS" in text for r in range(3))
+    # one rank fails: its exit code comes back and the ranks that would run on are terminated
+    script = "import os, sys, time\nif os.environ['RANK'] == '1': sys.exit(7)\ntime.sleep(60)"
+    t0 = time.time()
+    rc = launch.launch([sys.executable, "-c", script], 3, timeout_s=50, out=io.StringIO())
+    assert rc == 7 and time.time() - t0 < 30
+    # time-out
+    rc = launch.launch([sys.executable, "-c", "import time; time.sleep(60)"], 2, timeout_s=1.0, out=io.StringIO())
+    assert rc == 124
+    # command line form
+    assert launch.main(["-n", "2", "--no-tag", "--", sys.executable, "-c", "import os; assert os.environ['WORLD_SIZE'] == '2'"]) == 0
