@@ -5,7 +5,8 @@
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 \
         benchmarks/functional_driver.py -a allreduce -s 67108864                    # one PE per GPU
 
-``-a`` selects the test (the reference numbers them, tests/functional_tests/tester.hpp; names are used here):
+``-a`` selects the test by name, or by the reference's number (tests/functional_tests/tester.hpp:36-96) where
+the test has a timed form here:
 put, get (block-scope RMA from PE 0 to PE 1, timed on the device), amo_fadd / amo_finc / amo_fcswap / amo_add
 (int64 atomics on PE 0 from every PE), pingpong (signal round trips), barrier (device barrier_all), and the
 library collectives allreduce, broadcast, fcollect, alltoall (timed with CUDA events on the host, maximum over
@@ -28,6 +29,37 @@ from rocshmem_b200 import _native  # noqa: E402
 from rocshmem_b200.ops import collectives as coll  # noqa: E402
 
 AMO = {"amo_fadd": 0, "amo_finc": 1, "amo_add": 2, "amo_fcswap": 4}
+
+# The reference selects tests by number (enum TestType, tests/functional_tests/tester.hpp:36-96). Numbers whose test
+# has a timed form here map to its name; the functional content of all of them is covered by the pytest suite
+# (tests/test_gpu_device_api.py), which is where the others point.
+REFERENCE_NUMBERS = {
+    0: "get", 1: "get", 2: "put", 3: "put", 5: "amo_fadd", 6: "amo_finc", 8: "amo_fcswap", 9: "amo_add",
+    13: "pingpong", 15: "barrier", 16: "barrier", 19: "fcollect", 20: "alltoall", 25: "get", 26: "get", 27: "put",
+    28: "put", 33: "broadcast", 34: "allreduce",
+}
+REFERENCE_NAMES = [
+    "Get", "GetNBI", "Put", "PutNBI", "GetSwarm", "AMO_FAdd", "AMO_FInc", "AMO_Fetch", "AMO_FCswap", "AMO_Add", "AMO_Inc",
+    "AMO_Cswap", "Init", "PingPong", "RandomAccess", "BarrierAll", "SyncAll", "Sync", "Collect", "TeamFCollect",
+    "TeamAllToAll", "AllToAlls", "ShmemPtr", "P", "G", "WGGet", "WGGetNBI", "WGPut", "WGPutNBI", "WAVEGet", "WAVEGetNBI",
+    "WAVEPut", "WAVEPutNBI", "TeamBroadcast", "TeamReduction", "TeamCtxGet", "TeamCtxGetNBI", "TeamCtxPut",
+    "TeamCtxPutNBI", "TeamCtxInfra", "PutNBIMR", "AMO_Set", "AMO_Swap", "AMO_FetchAnd", "AMO_FetchOr", "AMO_FetchXor",
+    "AMO_And", "AMO_Or", "AMO_Xor", "PingAll", "PutSignal", "WGPutSignal", "WAVEPutSignal", "PutSignalNBI",
+    "WGPutSignalNBI", "WAVEPutSignalNBI", "SignalFetch", "WGSignalFetch", "WAVESignalFetch",
+]
+
+
+def resolve_test(selector: str) -> str:
+    """A test name as it is, or the name for one of the reference's test numbers (0 .. 58)."""
+    if not selector.lstrip("-").isdigit():
+        return selector
+    number = int(selector)
+    if not 0 <= number < len(REFERENCE_NAMES):
+        raise SystemExit(f"test numbers run from 0 to {len(REFERENCE_NAMES) - 1}")
+    if number not in REFERENCE_NUMBERS:
+        raise SystemExit(f"test {number} ({REFERENCE_NAMES[number]}TestType) has no timed form in this driver; its "
+                         "checks are part of the pytest suite: python -m pytest tests/test_gpu_device_api.py -m gpu")
+    return REFERENCE_NUMBERS[number]
 
 
 def header():
@@ -64,6 +96,7 @@ def main() -> int:
     ap.add_argument("--skip", type=int, default=10)
     ap.add_argument("--local-pes", type=int, default=0, help="PEs hosted by this process on one GPU (0: one per process)")
     args = ap.parse_args()
+    args.test = resolve_test(args.test)
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
     kw = {"n_local": args.local_pes} if args.local_pes else {}

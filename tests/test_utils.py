@@ -91,3 +91,19 @@ def test_guard_regions_detect_an_overrun(shm_cpu):
     word[0] = saved
     assert C.check_canaries() == 0
     shm.free(a)
+
+
+def test_functional_driver_accepts_the_reference_test_numbers():
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "functional_driver.py")
+    spec = importlib.util.spec_from_file_location("functional_driver", path)
+    fd = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(fd)
+    assert len(fd.REFERENCE_NAMES) == 59 and fd.REFERENCE_NAMES[58] == "WAVESignalFetch"
+    assert fd.resolve_test("put") == "put" and fd.resolve_test("2") == "put" and fd.resolve_test("34") == "allreduce"
+    assert fd.resolve_test("13") == "pingpong" and fd.resolve_test("0") == "get"
+    with pytest.raises(SystemExit, match="RandomAccessTestType"):
+        fd.resolve_test("14")
+    with pytest.raises(SystemExit, match="0 to 58"):
+        fd.resolve_test("59")
