@@ -9,6 +9,9 @@ run it explicitly, and move each case into the regular test files once it has pa
     ROCSHMEM_EP_DYNAMIC=1 python -m pytest tests/test_gpu_moe.py -m gpu -x -q     # dynamic token hand-out in dispatch
     ROCSHMEM_EP_DYNAMIC=1 python bench.py --steps 50                              # ... and its timing against the default
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 tests/pending_gpu_checks.py
+    python -m rocshmem_b200.launch -n 2 python examples/python/data_parallel.py    # gradient buckets on the allreduce kernel
+    python -m rocshmem_b200.launch -n 2 python examples/python/ring_attention.py   # host-API ring between GPUs
+    python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/ep_baseline_bench.py
 """
 import os
 import sys
