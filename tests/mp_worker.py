@@ -296,15 +296,13 @@ def rank_leaves():
         return
     alive = mem.wait_for_change(expected_alive=npes - 1, timeout_s=30)
     assert alive == list(range(npes - 1)), alive
-    team = shm.team_world().split_strided(0, 1, npes - 1) if False else None
-    # Survivors use a team that excludes the leaver; the split involves the survivors only
-    # (an active-set style collective), so the absent rank is not needed.
+    # Survivors reduce over an active set that excludes the leaver: only its members take part in setting it up,
+    # so the absent rank is not needed.
     rc = shm.runtime._C().reduce_active_set(y.data_ptr(), x.data_ptr(), 8, shm.runtime.dtype_code(torch.int64),
                                             shm.OP_SUM, 0, 0, npes - 1)
     assert rc == 0 and int(y.cpu()[0]) == sum(range(1, npes))
     if me == 0:
         mem.post("survivors-done")
-    del team
 
 
 def proxy_collectives():
