@@ -14,7 +14,7 @@ values travel around the ring while every member accumulates its queries' output
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional
 
 import torch
 

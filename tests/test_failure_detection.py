@@ -3,7 +3,6 @@ joins, a rank that leaves between steps, a dropped proxy command) and must surfa
 status, never as a hang."""
 import time
 
-import pytest
 import torch
 
 from mp_util import assert_all_ok, run_ranks
