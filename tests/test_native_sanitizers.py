@@ -1,6 +1,7 @@
 """Builds the native unit-test program of the host-side runtime (allocator, teams, configuration, bootstrap)
 with sanitizers and runs it: AddressSanitizer + UBSan for memory errors and undefined behaviour, ThreadSanitizer
-for data races between the threads that play the ranks of the bootstrap test."""
+for data races between the threads that play the ranks of the bootstrap test. A second test instruments the whole
+host side of the runtime library and runs multi-threaded programs (host API, reverse-offload ring) against it."""
 import os
 import shutil
 import subprocess
@@ -30,3 +31,68 @@ def test_runtime_unit_program_under_sanitizers(flags, tmp_path):
     run = subprocess.run([exe, str(scratch)], capture_output=True, text=True, timeout=600, env=env)
     assert run.returncode == 0, run.stdout[-2000:] + run.stderr[-4000:]
     assert "all passed" in run.stdout
+
+
+@pytest.mark.skipif(shutil.which("g++") is None or shutil.which("nvcc") is None, reason="needs g++ and nvcc")
+def test_whole_runtime_with_threads_and_proxy_under_thread_sanitizer(tmp_path):
+    """The host side of the runtime library (all .cpp files, instrumented) linked with the device objects of the
+    regular build, then two programs on the CPU backend: several host threads per process on the typed host API
+    (two processes), and several producer threads on the reverse-offload ring with command merging on. A data race
+    anywhere between user threads, the runtime and the proxy's consumer thread fails the test."""
+    from rocshmem_b200 import _build
+    if not _build.is_built():
+        _build.build(with_tests=False)
+    objdir = os.path.join(ROOT, "rocshmem_b200", "build")
+    cu_objs = sorted(os.path.join(objdir, f) for f in os.listdir(objdir)
+                     if f.endswith(".cu.o") and (f.startswith("kernels_") or f == "runtime_host_ops_cuda.cu.o"))
+    assert cu_objs, "device objects of the regular build are missing"
+    inc = [f"-I{os.path.join(ROOT, 'rocshmem_b200', 'csrc', 'include')}", f"-I{os.path.join(ROOT, 'rocshmem_b200', 'csrc')}"]
+    cuda_home = os.path.dirname(os.path.dirname(os.path.realpath(shutil.which("nvcc"))))
+    inc.append(f"-I{os.path.join(cuda_home, 'include')}")
+    objs = []
+    for name in ("config", "allocator", "team", "bootstrap", "host_shm_provider", "runtime", "host_ops_cpu", "host_api",
+                 "proxy", "cuda_vmm_provider"):
+        obj = str(tmp_path / f"{name}.o")
+        cc = subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fPIC", "-fsanitize=thread", "-Wno-tsan", *inc, "-c",
+                             os.path.join(RT, name + ".cpp"), "-o", obj], capture_output=True, text=True, timeout=600)
+        if cc.returncode != 0 and "sanitize" in cc.stderr and "cannot find" in cc.stderr:
+            pytest.skip("sanitizer runtime libraries are not installed")
+        assert cc.returncode == 0, cc.stderr[-3000:]
+        objs.append(obj)
+    lib = str(tmp_path / "librocshmem_b200_tsan.so")
+    link = subprocess.run(["nvcc", "-shared", "-o", lib, *objs, *cu_objs, "-Xcompiler", "-fsanitize=thread", "-lpthread",
+                           "-ldl", "-lrt"], capture_output=True, text=True, timeout=600)
+    if link.returncode != 0 and "tsan" in link.stderr and "cannot find" in link.stderr:
+        pytest.skip("sanitizer runtime libraries are not installed")
+    assert link.returncode == 0, link.stderr[-3000:]
+    exes = {}
+    for prog in ("host_threads_sos", "proxy_threads"):
+        exe = str(tmp_path / prog)
+        cc = subprocess.run(["g++", "-std=c++17", "-O1", "-g", "-fsanitize=thread", *inc,
+                             os.path.join(ROOT, "tests", "cpp", prog + ".cpp"), "-o", exe, f"-L{tmp_path}",
+                             "-lrocshmem_b200_tsan", f"-Wl,-rpath,{tmp_path}", "-lpthread"],
+                            capture_output=True, text=True, timeout=600)
+        assert cc.returncode == 0, cc.stderr[-3000:]
+        exes[prog] = exe
+    base = dict(os.environ, ROCSHMEM_BACKEND="host", ROCSHMEM_HEAP_SIZE="16M", ROCSHMEM_WAIT_TIMEOUT_MS="60000",
+                TSAN_OPTIONS="halt_on_error=1 exitcode=66")
+    # the ring, one process with two PEs
+    run = subprocess.run([exes["proxy_threads"]], env=dict(base, RANK="0", WORLD_SIZE="1", ROCSHMEM_LOCAL_PES="2"),
+                         capture_output=True, text=True, timeout=600)
+    assert run.returncode == 0 and "PASS" in run.stdout, run.stdout[-2000:] + run.stderr[-4000:]
+    assert "ThreadSanitizer" not in run.stderr
+    # threads on the host API, two processes
+    kv = tmp_path / "kv"
+    kv.mkdir()
+    procs = [subprocess.Popen([exes["host_threads_sos"]],
+                              env=dict(base, RANK=str(r), WORLD_SIZE="2", LOCAL_RANK=str(r), ROCSHMEM_BOOTSTRAP_DIR=str(kv)),
+                              stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(2)]
+    try:
+        for r, p in enumerate(procs):
+            out, err = p.communicate(timeout=600)
+            assert p.returncode == 0 and f"[pe {r}] PASS" in out, out[-2000:] + err[-4000:]
+            assert "ThreadSanitizer" not in err
+    finally:
+        for p in procs:
+            if p.poll() is None:
+                p.kill()
