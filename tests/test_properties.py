@@ -67,3 +67,75 @@ def test_split_matches_a_set_model(world, p_start, p_stride, p_size, start, stri
     outside = [w for w in range(world) if w not in members(got)]
     for w in outside[:5]:
         assert C.translate_pe((0, 1, world), w, got) == -1
+
+
+# ---- host RMA and atomics against a model -----------------------------------------------------------------------------
+
+_RMA_OP = st.one_of(
+    st.tuples(st.just("put"), st.integers(0, 3), st.integers(0, 3), st.integers(0, 63), st.integers(0, 63),
+              st.integers(1, 64)),                                   # origin PE, target PE, source offset, dest offset, n
+    st.tuples(st.just("get"), st.integers(0, 3), st.integers(0, 3), st.integers(0, 63), st.integers(0, 63),
+              st.integers(1, 64)),
+    st.tuples(st.just("fadd"), st.integers(0, 3), st.integers(0, 3), st.integers(0, 127), st.integers(-50, 50),
+              st.just(0)),                                           # origin, target, index, value
+    st.tuples(st.just("swap"), st.integers(0, 3), st.integers(0, 3), st.integers(0, 127), st.integers(-50, 50),
+              st.just(0)),
+    st.tuples(st.just("cas"), st.integers(0, 3), st.integers(0, 3), st.integers(0, 127), st.integers(-3, 3),
+              st.integers(-3, 3)),                                   # origin, target, index, compare, value
+)
+
+
+@settings(max_examples=25, deadline=None)
+@given(st.lists(_RMA_OP, min_size=1, max_size=60))
+def test_host_rma_and_atomics_match_a_model(ops):
+    """Random sequences of puts, gets and atomics between four PEs of one process (CPU backend) against plain
+    Python lists: every returned value and the final content of every PE's array."""
+    import torch
+
+    import rocshmem_b200 as shm
+    if shm.is_initialized():
+        shm.finalize()
+    shm.init(n_local=4, heap_size="4M", backend="host")
+    try:
+        N = 128
+        arr = shm.zeros(N, torch.int64)
+        model = [[0] * N for _ in range(4)]
+        for pe in range(4):
+            init = [(pe + 1) * 1000 + i for i in range(N)]
+            shm.local_view(arr, pe).copy_(torch.tensor(init))
+            model[pe] = init
+        for op, origin, target, a, b, c in ops:
+            shm.set_local_pe(origin)
+            mine = shm.local_view(arr, origin)
+            if op == "put":
+                n = min(c, N - a, N - b)
+                shm.putmem(mine[b:b + n], mine[a:a + n].clone(), target)     # dest offset b on the target
+                model[target][b:b + n] = model[origin][a:a + n]
+            elif op == "get":
+                n = min(c, N - a, N - b)
+                tmp = torch.zeros(n, dtype=torch.int64)
+                shm.getmem(tmp, mine[a:a + n], target)                       # source offset a on the target
+                assert tmp.tolist() == model[target][a:a + n]
+                shm.local_view(arr, origin)[b:b + n] = tmp
+                model[origin][b:b + n] = model[target][a:a + n]
+            elif op == "fadd":
+                old = shm.atomic_fetch_add(mine, b, target, index=a)
+                assert old == model[target][a]
+                model[target][a] += b
+            elif op == "swap":
+                old = shm.atomic_swap(mine, b, target, index=a)
+                assert old == model[target][a]
+                model[target][a] = b
+            else:
+                # make the comparison hit now and then: values near zero only occur after swaps
+                old = shm.atomic_compare_swap(mine, b, c, target, index=a)
+                assert old == model[target][a]
+                if model[target][a] == b:
+                    model[target][a] = c
+        shm.set_local_pe(0)
+        shm.quiet()
+        for pe in range(4):
+            assert shm.local_view(arr, pe).tolist() == model[pe], pe
+    finally:
+        shm.set_local_pe(0)
+        shm.finalize()
