@@ -139,3 +139,82 @@ def test_host_rma_and_atomics_match_a_model(ops):
     finally:
         shm.set_local_pe(0)
         shm.finalize()
+
+
+# ---- host collectives on random strided teams against torch ---------------------------------------------------------------
+
+@settings(max_examples=20, deadline=None)
+@given(st.integers(0, 7), st.integers(1, 4), st.integers(1, 8), st.integers(1, 70),
+       st.sampled_from(["int32", "int64", "float32", "float64", "bfloat16", "int16"]),
+       st.sampled_from(["sum", "min", "max", "prod", "and", "or", "xor"]), st.integers(0, 10 ** 6))
+def test_host_collectives_on_random_teams_match_torch(start, stride, size, nelems, dtype_name, op_name, seed):
+    """Eight PEs in one process (CPU backend): a random strided team, then reduce, broadcast, fcollect and alltoall
+    on it against the same operations computed with torch; PEs outside the team keep their buffers."""
+    import torch
+
+    import rocshmem_b200 as shm
+    from rocshmem_b200.ops import collectives as coll
+    P = 8
+    if start + (size - 1) * stride >= P:
+        size = (P - 1 - start) // stride + 1
+    dtype = getattr(torch, dtype_name)
+    if op_name in ("and", "or", "xor") and dtype.is_floating_point:
+        op_name = "max"
+    op = {"sum": shm.OP_SUM, "min": shm.OP_MIN, "max": shm.OP_MAX, "prod": shm.OP_PROD, "and": shm.OP_AND,
+          "or": shm.OP_OR, "xor": shm.OP_XOR}[op_name]
+    if shm.is_initialized():
+        shm.finalize()
+    shm.init(n_local=P, heap_size="4M", backend="host")
+    try:
+        members = [start + i * stride for i in range(size)]
+        team = shm.team_world().split_strided(start, stride, size)
+        g = torch.Generator().manual_seed(seed)
+        src = shm.zeros(nelems * size, dtype)
+        dst = shm.zeros(nelems * size, dtype)
+        data = []
+        for pe in range(P):
+            # small integers: products of up to eight of them stay exact in every type, bf16 included
+            v = torch.randint(-2, 3, (nelems * size,), generator=g).to(dtype)
+            data.append(v)
+            shm.local_view(src, pe).copy_(v)
+            shm.local_view(dst, pe).fill_(7)
+        # reduce
+        assert coll.reduce(dst[:nelems], src[:nelems], op, team) == 0
+        stack = torch.stack([data[m][:nelems] for m in members])
+        wide = stack.double() if dtype.is_floating_point else stack.long()
+        want = {"sum": lambda: wide.sum(0), "min": lambda: wide.min(0).values, "max": lambda: wide.max(0).values,
+                "prod": lambda: wide.prod(0)}.get(op_name)
+        if want is None:
+            acc = wide[0].clone()
+            for row in wide[1:]:
+                acc = {"and": acc & row, "or": acc | row, "xor": acc ^ row}[op_name]
+            expect = acc
+        else:
+            expect = want()
+        for pe in range(P):
+            got = shm.local_view(dst, pe)[:nelems]
+            if pe in members:
+                assert torch.equal(got.double() if dtype.is_floating_point else got.long(), expect.to(got.device)), (pe, op_name)
+            else:
+                assert torch.all(got == 7)
+        # broadcast from the last member: everybody but the root receives
+        root = size - 1
+        for pe in range(P):
+            shm.local_view(dst, pe).fill_(7)
+        assert coll.broadcast(dst[:nelems], src[:nelems], root, team) == 0
+        for i, m in enumerate(members):
+            got = shm.local_view(dst, m)[:nelems]
+            assert torch.equal(got, data[members[root]][:nelems]) if i != root else torch.all(got == 7)
+        # fcollect and alltoall
+        assert coll.fcollect(dst, src[:nelems], team) == 0
+        for m in members:
+            got = shm.local_view(dst, m).view(size, nelems)
+            assert all(torch.equal(got[i], data[members[i]][:nelems]) for i in range(size))
+        assert coll.alltoall(dst, src, team) == 0
+        for j, m in enumerate(members):
+            got = shm.local_view(dst, m).view(size, nelems)
+            assert all(torch.equal(got[i], data[members[i]].view(size, nelems)[j]) for i in range(size))
+        team.destroy()
+    finally:
+        shm.set_local_pe(0)
+        shm.finalize()
