@@ -229,3 +229,51 @@ def choose_algorithm(n: int, block_bytes: int, per_message_us: float = 6.0, gbyt
     if c > 1:
         cost["clustered"] = (n + n // c) * per_message_us + 2 * n * block_bytes * per_byte_us
     return min(cost, key=cost.get)
+
+
+class HostAllToAllV:
+    """Variable-count all-to-all over the host API (the reference's ``alltoall`` is fixed-size only).
+
+    Every PE sends ``send_counts[j]`` rows of ``source`` to PE ``j`` (rows for PE 0 first, then PE 1, ...); the rows a
+    PE receives land in ``dest`` ordered by source PE. Counts travel first (one row of a symmetric count matrix per
+    PE), then every PE knows where each source's rows start in every destination and puts its rows there directly -
+    the protocol of the MoE dispatch without the routing. Collective over all PEs; ``dest`` and ``source`` are
+    symmetric tensors whose first dimension is the row index.
+    """
+
+    def __init__(self):
+        self.n, self.me = rt.n_pes(), rt.my_pe()
+        self.counts = rt.zeros((self.n, self.n), torch.int64)       # counts[s, d]: rows PE s sends to PE d
+
+    def destroy(self) -> None:
+        """Collective: free the count matrix."""
+        rt.free(self.counts)
+        self.counts = None
+
+    def __call__(self, dest: torch.Tensor, source: torch.Tensor, send_counts) -> torch.Tensor:
+        """Returns the int64 tensor of rows received from every PE (``recv_counts``); the rows are in
+        ``dest[:recv_counts.sum()]``. Raises ``ValueError`` on every PE alike when ``dest`` is too small for some PE."""
+        n, me = self.n, self.me
+        send = torch.as_tensor(list(send_counts), dtype=torch.int64)
+        if send.numel() != n or int(send.min()) < 0 or int(send.sum()) > source.shape[0]:
+            raise ValueError("send_counts needs one non-negative entry per PE and may not exceed the rows of source")
+        row = send.to(self.counts.device)
+        for d in range(n):
+            rt.putmem(self.counts[me], row, d, nbi=True)
+        rt.barrier_all()                       # completes the puts: the whole matrix is everywhere
+        matrix = self.counts.cpu()
+        recv = matrix[:, me].clone()
+        # dest is symmetric, so it has the same number of rows everywhere: every PE can check every destination
+        # and all of them agree on whether the exchange takes place.
+        need = matrix.sum(dim=0)
+        if int(need.max()) > dest.shape[0]:
+            raise ValueError(f"dest holds {dest.shape[0]} rows, up to {int(need.max())} arrive")
+        for dd in range(n):
+            d = (me + dd) % n
+            cnt = int(send[d])
+            start = int(send[:d].sum())
+            if cnt:
+                base = int(matrix[:me, d].sum())       # rows that PEs before me send to d
+                rt.putmem(dest[base:base + cnt], source[start:start + cnt], d, nbi=True)
+        rt.barrier_all()
+        return recv

@@ -857,7 +857,49 @@ def pipeline_stages():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def alltoallv_host():
+    """Variable-count all-to-all: random counts (zeros included), rows tagged with source, destination and index."""
+    from rocshmem_b200.ops.host_algorithms import HostAllToAllV
+    init("32M")
+    me, n = shm.my_pe(), shm.n_pes()
+    a2av = HostAllToAllV()
+    W = 6
+    for rep in range(3):
+        gen = torch.Generator().manual_seed(77 + rep)
+        counts = torch.randint(0, 9, (n, n), generator=gen)          # counts[s, d], known to everybody for the check
+        if rep == 1:
+            counts[:, 0] = 0                                         # nobody sends to PE 0
+        send = counts[me]
+        src = shm.zeros((int(counts.sum(dim=1).max()), W), torch.int32)
+        dst = shm.zeros((int(counts.sum(dim=0).max()), W), torch.int32)
+        rows = []
+        for d in range(n):
+            for i in range(int(send[d])):
+                rows.append([me, d, i, rep, 0, 0])
+        if rows:
+            src[:len(rows)] = torch.tensor(rows, dtype=torch.int32).to(dev())
+        recv = a2av(dst, src, send.tolist())
+        assert recv.tolist() == counts[:, me].tolist()
+        got = dst.cpu()[:int(recv.sum())].tolist()
+        want = [[s, me, i, rep, 0, 0] for s in range(n) for i in range(int(counts[s, me]))]
+        assert got == want, (rep, got[:3], want[:3])
+        shm.barrier_all()
+        shm.free(dst)
+        shm.free(src)
+    # a destination that is too small is refused on every PE alike
+    src = shm.zeros((8, W), torch.int32)
+    dst = shm.zeros((3, W), torch.int32)
+    try:
+        a2av(dst, src, [1] * n)
+        raise AssertionError("an overflowing exchange must be refused")
+    except ValueError:
+        pass
+    shm.barrier_all()
+    a2av.destroy()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

@@ -77,3 +77,7 @@ def test_ring_exchange_and_ring_attention():
 
 def test_pipeline_stages_match_the_whole_model():
     assert_all_ok(run_ranks("pipeline_stages", 3, timeout=240))
+
+
+def test_variable_count_all_to_all():
+    assert_all_ok(run_ranks("alltoallv_host", 4, timeout=240))
