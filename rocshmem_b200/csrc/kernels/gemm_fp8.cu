@@ -3,6 +3,7 @@
 #include <cuda_bf16.h>
 
 #include <algorithm>
+#include <cstdlib>
 
 #include "gemm_fp8_core.cuh"
 #include "gemm_kernels.hpp"
@@ -42,6 +43,8 @@ struct RowMajorEpilogue8 {
   }
 };
 
+// PIPE selects the accumulate warps' variant with two TMEM loads in flight (see gemm_fp8_core.cuh).
+template <bool PIPE>
 __global__ void __launch_bounds__(gemm8::THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const float *a_scale, const float *b_scale, __nv_bfloat16 *c, int m, int n, int k) {
@@ -53,7 +56,16 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   sched.tiles_n = (n + gemm8::BN - 1) / gemm8::BN;
   sched.tiles = ((m + gemm8::BM - 1) / gemm8::BM) * sched.tiles_n;
   RowMajorEpilogue8 epi{c, static_cast<size_t>(n)};
-  gemm8::run<false>(&map_a, &map_b, a_scale, b_scale, k / gemm8::KB, sched, epi, smem_raw, sh);
+  gemm8::run<false, false, PIPE>(&map_a, &map_b, a_scale, b_scale, k / gemm8::KB, sched, epi, smem_raw, sh);
+}
+
+// ROCSHMEM_FP8_PIPE=1 switches the block-scaled kernels of this file to the pipelined accumulate warps.
+bool fp8_pipe() {
+  static const bool on = [] {
+    const char *e = std::getenv("ROCSHMEM_FP8_PIPE");
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
+  }();
+  return on;
 }
 
 constexpr int kMaxGroups8 = 256;
@@ -96,7 +108,7 @@ struct GroupedScheduler8 {
   __device__ void side_role() const {}
 };
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool PIPE>
 __global__ void __launch_bounds__(gemm8::THREADS, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const float *a_scale, const float *b_scale, __nv_bfloat16 *c, const int *offsets,
@@ -112,7 +124,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   sched.n = n;
   sched.tiles_n = SWIGLU ? (n / 2 + gemm8::BN / 2 - 1) / (gemm8::BN / 2) : (n + gemm8::BN - 1) / gemm8::BN;
   RowMajorEpilogue8 epi{c, static_cast<size_t>(SWIGLU ? n / 2 : n)};
-  gemm8::run<SWIGLU>(&map_a, &map_b, a_scale, b_scale, k / gemm8::KB, sched, epi, smem_raw, sh);
+  gemm8::run<SWIGLU, false, PIPE>(&map_a, &map_b, a_scale, b_scale, k / gemm8::KB, sched, epi, smem_raw, sh);
 }
 
 template <typename K>
@@ -135,11 +147,17 @@ int gemm_fp8_blockscaled(const void *a_q, const float *a_scale, const void *b_q,
   if (m <= 0 || n <= 0 || k <= 0 || (k % 512) != 0 || (n % 128) != 0) return cudaErrorInvalidValue;
   CUtensorMap map_a, map_b;
   if (!encode_tmap_2d(&map_a, a_q, m, k, 1, gemm8::BM) || !encode_tmap_2d(&map_b, b_q, n, k, 1, gemm8::BN / 2)) return -1;
-  if (int rc = prepare8(gemm_fp8_kernel)) return rc;
   const int tiles = ((m + gemm8::BM - 1) / gemm8::BM) * ((n + gemm8::BN - 1) / gemm8::BN);
   const int grid = std::min(tiles, device_sm_count());
-  gemm_fp8_kernel<<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-      map_a, map_b, a_scale, b_scale, static_cast<__nv_bfloat16 *>(c), m, n, k);
+  if (fp8_pipe()) {
+    if (int rc = prepare8(gemm_fp8_kernel<true>)) return rc;
+    gemm_fp8_kernel<true><<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+        map_a, map_b, a_scale, b_scale, static_cast<__nv_bfloat16 *>(c), m, n, k);
+  } else {
+    if (int rc = prepare8(gemm_fp8_kernel<false>)) return rc;
+    gemm_fp8_kernel<false><<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+        map_a, map_b, a_scale, b_scale, static_cast<__nv_bfloat16 *>(c), m, n, k);
+  }
   return cudaGetLastError();
 }
 
@@ -157,16 +175,16 @@ int grouped_gemm_fp8_blockscaled(const void *a_q, const float *a_scale, const vo
   }
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = device_sm_count();
-  if (swiglu) {
-    if (int rc = prepare8(grouped_gemm_fp8_kernel<true>)) return rc;
-    grouped_gemm_fp8_kernel<true><<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, s>>>(
-        map_a, map_b, a_scale, b_scale, static_cast<__nv_bfloat16 *>(c), offsets, groups, n, k);
-  } else {
-    if (int rc = prepare8(grouped_gemm_fp8_kernel<false>)) return rc;
-    grouped_gemm_fp8_kernel<false><<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, s>>>(
-        map_a, map_b, a_scale, b_scale, static_cast<__nv_bfloat16 *>(c), offsets, groups, n, k);
+  auto launch = [&](auto kernel) -> int {
+    if (int rc = prepare8(kernel)) return rc;
+    kernel<<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, s>>>(map_a, map_b, a_scale, b_scale,
+                                                           static_cast<__nv_bfloat16 *>(c), offsets, groups, n, k);
+    return cudaGetLastError();
+  };
+  if (fp8_pipe()) {
+    return swiglu ? launch(grouped_gemm_fp8_kernel<true, true>) : launch(grouped_gemm_fp8_kernel<false, true>);
   }
-  return cudaGetLastError();
+  return swiglu ? launch(grouped_gemm_fp8_kernel<true, false>) : launch(grouped_gemm_fp8_kernel<false, false>);
 }
 
 }  // namespace kernels

@@ -8,6 +8,8 @@ run it explicitly, and move each case into the regular test files once it has pa
     python -m pytest tests/pending_gpu_checks.py -m gpu -x -q
     ROCSHMEM_EP_DYNAMIC=1 python -m pytest tests/test_gpu_moe.py -m gpu -x -q     # dynamic token hand-out in dispatch
     ROCSHMEM_EP_DYNAMIC=1 python bench.py --steps 50                              # ... and its timing against the default
+    ROCSHMEM_FP8_PIPE=1 python -m pytest tests/test_gpu_gemm.py -m gpu -x -q -k fp8   # two TMEM loads in flight
+    ROCSHMEM_FP8_PIPE=1 python benchmarks/gemm_bench.py                           # ... and its rate against the default
     python -m torch.distributed.run --nproc-per-node 2 --master-addr 127.0.0.1 tests/pending_gpu_checks.py
     python -m rocshmem_b200.launch -n 2 python examples/python/data_parallel.py    # gradient buckets on the allreduce kernel
     python -m rocshmem_b200.launch -n 2 python examples/python/ring_attention.py   # host-API ring between GPUs
