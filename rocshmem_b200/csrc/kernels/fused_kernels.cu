@@ -446,6 +446,15 @@ bool use_two_cta() {
   return on;
 }
 
+// ROCSHMEM_FP8_PIPE=1 selects the accumulate warps with two TMEM loads in flight (see gemm_fp8_core.cuh).
+bool use_fp8_pipe() {
+  static const bool on = [] {
+    const char *e = std::getenv("ROCSHMEM_FP8_PIPE");
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
+  }();
+  return on;
+}
+
 // ---- block-scaled e4m3 variants -------------------------------------------------------------------------------
 // Same structure with the fp8 core: the push warps send the e4m3 rows and, as a second array, their
 // 1 x 128 scales (half the NVLink bytes of the bf16 kernel); the weights carry 128 x 128 scales.
@@ -463,7 +472,7 @@ struct Ag8Args {
   unsigned epoch;
 };
 
-template <bool SWIGLU>
+template <bool SWIGLU, bool PIPE>
 __global__ void __launch_bounds__(gemm8::THREADS + 32, 1)
 ag_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, Ag8Args a) {
   extern __shared__ unsigned char smem_raw[];
@@ -486,9 +495,10 @@ ag_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                       reinterpret_cast<const char *>(a.x_s), reinterpret_cast<char *>(a.gathered_s),
                       size_t(gemm8::BM) * (a.k / 128) * sizeof(float), a.m_shard / gemm8::BM, a.ready};
   PlainEpilogue epi{a.c, static_cast<size_t>(SWIGLU ? a.n / 2 : a.n)};
-  gemm8::run<SWIGLU, true>(&map_a, &map_b, a.gathered_s, a.b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
+  gemm8::run<SWIGLU, true, PIPE>(&map_a, &map_b, a.gathered_s, a.b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
 }
 
+template <bool PIPE>
 __global__ void __launch_bounds__(gemm8::THREADS, 1)
 gemm_rs_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const float *a_scale, const float *b_scale, RsArgs a) {
@@ -505,7 +515,7 @@ gemm_rs_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   sched.m_shard = a.m_shard;
   sched.n = a.n;
   RsEpilogue epi{t, a.staging, t->my_pe, a.m_shard, a.n};
-  gemm8::run<false>(&map_a, &map_b, a_scale, b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
+  gemm8::run<false, false, PIPE>(&map_a, &map_b, a_scale, b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
   rs_reduce(a, t);
 }
 
@@ -595,14 +605,13 @@ int ag_gemm_fp8(rocshmem_team_t team, const void *x_q, const float *x_s, void *g
             reinterpret_cast<unsigned int *>(flags), b_scale, static_cast<__nv_bfloat16 *>(c), m_shard, n, k, epoch};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int sms = device_sm_count();
-  if (swiglu) {
-    cudaError_t e = cudaFuncSetAttribute(ag_gemm_fp8_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm8::SMEM_BYTES);
+  auto launch = [&](auto kernel) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm8::SMEM_BYTES);
     if (e != cudaSuccess) return static_cast<int>(e);
-    return launch_pes(ag_gemm_fp8_kernel<true>, sms, gemm8::THREADS + 32, gemm8::SMEM_BYTES, s, true, map_a, map_b, a);
-  }
-  cudaError_t e = cudaFuncSetAttribute(ag_gemm_fp8_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm8::SMEM_BYTES);
-  if (e != cudaSuccess) return static_cast<int>(e);
-  return launch_pes(ag_gemm_fp8_kernel<false>, sms, gemm8::THREADS + 32, gemm8::SMEM_BYTES, s, true, map_a, map_b, a);
+    return launch_pes(kernel, sms, gemm8::THREADS + 32, gemm8::SMEM_BYTES, s, true, map_a, map_b, a);
+  };
+  if (use_fp8_pipe()) return swiglu ? launch(ag_gemm_fp8_kernel<true, true>) : launch(ag_gemm_fp8_kernel<false, true>);
+  return swiglu ? launch(ag_gemm_fp8_kernel<true, false>) : launch(ag_gemm_fp8_kernel<false, false>);
 }
 
 int gemm_rs_fp8(rocshmem_team_t team, const void *a_q, const float *a_scale, const void *b_q, const float *b_scale,
@@ -618,12 +627,15 @@ int gemm_rs_fp8(rocshmem_team_t team, const void *a_q, const float *a_scale, con
       !encode_tmap_2d(&map_b, b_q, n, k, 1, gemm8::BN / 2)) {
     return -1;
   }
-  cudaError_t e = cudaFuncSetAttribute(gemm_rs_fp8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm8::SMEM_BYTES);
-  if (e != cudaSuccess) return static_cast<int>(e);
   RsArgs a{team, static_cast<__nv_bfloat16 *>(staging), static_cast<__nv_bfloat16 *>(out), m_shard, n, k, grid_counter,
            epoch};
-  return launch_pes(gemm_rs_fp8_kernel, device_sm_count(), gemm8::THREADS, gemm8::SMEM_BYTES,
-                    static_cast<cudaStream_t>(stream), true, map_a, map_b, a_scale, b_scale, a);
+  auto launch = [&](auto kernel) -> int {
+    cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, gemm8::SMEM_BYTES);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    return launch_pes(kernel, device_sm_count(), gemm8::THREADS, gemm8::SMEM_BYTES, static_cast<cudaStream_t>(stream),
+                      true, map_a, map_b, a_scale, b_scale, a);
+  };
+  return use_fp8_pipe() ? launch(gemm_rs_fp8_kernel<true>) : launch(gemm_rs_fp8_kernel<false>);
 }
 
 }  // namespace kernels
