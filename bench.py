@@ -277,7 +277,8 @@ def main() -> None:
             "config": {"model": "DeepEP-style MoE dispatch+combine (DeepSeek-V3-like)", "experts": EXPERTS,
                        "experts_per_rank": epr, "top_k": TOPK, "hidden": HIDDEN, "tokens_per_rank": T,
                        "global_batch": world * T, "seq_len": 1, "parallelism": f"ep{world}",
-                       "layout": args.layout, "l2": "flushed between steps (512 MiB write)",
+                       "layout": args.layout, "dynamic_handout": bool(d.dynamic),
+                       "l2": "flushed between steps (512 MiB write)",
                        "dispatch": "fp8 e4m3 + fp32 scale per 128", "combine": "bf16 weighted sum"},
             "clocks": clocks,
             "e2e": {"value": world * T * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
