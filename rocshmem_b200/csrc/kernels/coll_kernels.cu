@@ -19,6 +19,8 @@
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
+#include <cstdlib>
+
 #include "kernels.hpp"
 #include "launch.cuh"
 #include "lib_common.cuh"
@@ -359,6 +361,78 @@ broadcast_relay_kernel(rocshmem_team_t team, char *dest_arg, const char *source_
   block_pair_barrier(t, blockIdx.x);
 }
 
+// Large broadcast through the NVLink multicast mapping (world team, one PE per process). The root stores every
+// 16-byte vector once to the multicast address of the staging area and the switch delivers it to every member: one
+// hop, the root sends the payload once, nobody forwards. The multicast object spans all members, the root included,
+// whose own dest must stay as it is, so the payload does not go to dest directly: it lands in the staging area and
+// every other member copies it from its local staging into dest (a local copy at HBM speed). Sub-chunks alternate
+// between the two halves of the staging area with one cross-PE barrier each, so the members' copy of sub-chunk c
+// overlaps the root's stores of sub-chunk c + 1. Block b of every member handles share b of every sub-chunk, which
+// is why the pairwise barrier between equal block indices suffices.
+__global__ void __launch_bounds__(kThreads)
+broadcast_nvls_kernel(rocshmem_team_t team, char *dest_arg, const char *source_arg, size_t bytes, int root,
+                      size_t sub_bytes, int pre_sync) {
+  const rocshmem_device_state &s = st();
+  const rocshmem_team_dev *t = detail::team_of(team);
+  if (t->my_pe < 0 || s.mc_base == nullptr) return;
+  char *dest = detail::local_ptr(dest_arg);
+  const char *source = detail::local_ptr(const_cast<char *>(source_arg));
+  if (pre_sync && !block_pair_barrier(t, blockIdx.x)) return;
+  const bool is_root = t->my_pe == root;
+  char *stage = s.scratch;
+  char *stage_mc = s.mc_base + (s.scratch - s.heap_base);  // the same bytes on every member
+  int half = 0;
+  for (size_t base = 0; base < bytes; base += sub_bytes, half ^= 1) {
+    const size_t len = bytes - base < sub_bytes ? bytes - base : sub_bytes;  // a multiple of 16 (launcher)
+    const size_t nvec = len / 16, per = (nvec + gridDim.x - 1) / gridDim.x;
+    size_t lo = per * blockIdx.x, hi = lo + per;
+    if (lo > nvec) lo = nvec;
+    if (hi > nvec) hi = nvec;
+    const size_t stage_off = size_t(half) * sub_bytes;
+    if (is_root) {
+      const int4 *src = reinterpret_cast<const int4 *>(source + base);
+      size_t v = lo + threadIdx.x;
+      for (; v + 3 * blockDim.x < hi; v += 4 * blockDim.x) {
+        const int4 a = src[v], b = src[v + blockDim.x], c = src[v + 2 * blockDim.x], d = src[v + 3 * blockDim.x];
+        multimem_st(stage_mc + stage_off + v * 16, a);
+        multimem_st(stage_mc + stage_off + (v + blockDim.x) * 16, b);
+        multimem_st(stage_mc + stage_off + (v + 2 * blockDim.x) * 16, c);
+        multimem_st(stage_mc + stage_off + (v + 3 * blockDim.x) * 16, d);
+      }
+      for (; v < hi; v += blockDim.x) multimem_st(stage_mc + stage_off + v * 16, src[v]);
+    }
+    // Share b of this sub-chunk has landed in every member's staging half. The half is reused two sub-chunks
+    // later, after the barrier of the next one, which a member reaches only when its copy below is done.
+    if (!block_pair_barrier(t, blockIdx.x)) return;
+    if (!is_root) {
+      // Written by another GPU: read past L1, which may still hold the lines of an earlier sub-chunk.
+      const int4 *from = reinterpret_cast<const int4 *>(stage + stage_off);
+      int4 *to = reinterpret_cast<int4 *>(dest + base);
+      size_t v = lo + threadIdx.x;
+      for (; v + 3 * blockDim.x < hi; v += 4 * blockDim.x) {
+        const int4 a = __ldcg(from + v), b = __ldcg(from + v + blockDim.x), c = __ldcg(from + v + 2 * blockDim.x),
+                   d = __ldcg(from + v + 3 * blockDim.x);
+        to[v] = a;
+        to[v + blockDim.x] = b;
+        to[v + 2 * blockDim.x] = c;
+        to[v + 3 * blockDim.x] = d;
+      }
+      for (; v < hi; v += blockDim.x) to[v] = __ldcg(from + v);
+    }
+  }
+  // The staging area belongs to this call until every member has copied its last sub-chunk.
+  block_pair_barrier(t, blockIdx.x, false);
+}
+
+// ROCSHMEM_BCAST_NVLS=1 lets large broadcasts on the world team use the multicast kernel where the mapping exists.
+bool use_bcast_nvls() {
+  static const bool on = [] {
+    const char *e = std::getenv("ROCSHMEM_BCAST_NVLS");
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
+  }();
+  return on;
+}
+
 template <typename K>
 unsigned clamp_blocks(K kernel, unsigned want) {
   Runtime &rt = Runtime::instance();
@@ -460,6 +534,21 @@ int coll_broadcast(rocshmem_team_t team, void *dest, const void *source, size_t 
   Runtime &rt = Runtime::instance();
   HostTeam *ht = rt.team_from_handle(team);
   const int n = ht ? ht->world.size : 0;
+  if (use_bcast_nvls() && ht != nullptr && ht == rt.team_world() && rt.n_local() == 1 && rt.mc_base() != nullptr &&
+      n >= 2 && bytes >= (size_t(1) << 20) && bytes % 16 == 0 && reinterpret_cast<uintptr_t>(dest) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(source) % 16 == 0) {
+    // Two staging halves of one sub-chunk each; sub-chunks as for the relay (a transfer that dwarfs its barrier).
+    size_t sub = std::max<size_t>(size_t(4) << 20, bytes / 8);
+    sub = std::min<size_t>(sub, size_t(16) << 20);
+    sub = std::min<size_t>(sub, rt.config().scratch_size / 2);
+    sub = sub / 4096 * 4096;
+    if (sub >= (size_t(1) << 20)) {
+      unsigned blocks = clamp_blocks(broadcast_nvls_kernel, static_cast<unsigned>(coll_blocks_for(sub)));
+      return launch_pes(broadcast_nvls_kernel, blocks, kThreads, 0, static_cast<cudaStream_t>(stream), false, team,
+                        static_cast<char *>(dest), static_cast<const char *>(source), bytes, root, sub,
+                        (flags & COLL_PRE_SYNC) ? 1 : 0);
+    }
+  }
   if (n >= 3 && bytes >= (size_t(512) << 10)) {
     // Sub-chunks large enough that a sub-chunk's transfer time dwarfs the barrier that ends it.
     size_t sub = bytes;
