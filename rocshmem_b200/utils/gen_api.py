@@ -111,6 +111,20 @@ def untyped_names() -> List[str]:
     ]
 
 
+def extension_names() -> List[str]:
+    """``rocshmemx_*``: additions of this library (host side unless noted)."""
+    return [
+        "rocshmemx_set_local_pe", "rocshmemx_n_local_pes", "rocshmemx_get_error", "rocshmemx_clear_error",
+        "rocshmemx_set_wait_timeout_ms", "rocshmemx_heap_write", "rocshmemx_heap_read", "rocshmemx_default_stream",
+        "rocshmemx_slab_create", "rocshmemx_slab_destroy", "rocshmemx_slab_reset", "rocshmemx_slab_used",
+        "rocshmemx_slab_alloc_host",
+        # device side
+        "rocshmemx_slab_alloc", "rocshmemx_slab_alloc_wave", "rocshmemx_slab_alloc_wg", "rocshmemx_team_my_pe",
+        "rocshmemx_team_n_pes", "rocshmemx_local", "rocshmemx_block_team_sync_status", "rocshmemx_grid_sync",
+        "rocshmemx_ticket_lock_block", "rocshmemx_ticket_unlock_block", "rocshmemx_spin_lock", "rocshmemx_spin_unlock",
+    ]
+
+
 def families() -> Dict[str, List[str]]:
     return {"lifecycle, identity, heap, teams, contexts, ordering, barriers": untyped_names(), "RMA": rma_names(),
             "signalling": signal_names(), "atomics": amo_names(), "point-to-point synchronisation": sync_names(),
@@ -135,6 +149,10 @@ def markdown() -> str:
         lines += [f"## {fam} ({len(names)} functions)", "", "```"]
         lines += sorted(names)
         lines += ["```", ""]
+    ext = extension_names()
+    lines += [f"## extensions ({len(ext)} functions, not part of the count above; described in `GUIDE.md`)", "", "```"]
+    lines += sorted(ext)
+    lines += ["```", ""]
     return "\n".join(lines)
 
 

@@ -29,8 +29,8 @@ def test_every_generated_name_is_declared(tmp_path):
     out = subprocess.run(["nvcc", "-E", "-std=c++17", "-I", INC, "-gencode", "arch=compute_100a,code=sm_100a", str(src)],
                          capture_output=True, text=True, timeout=300)
     assert out.returncode == 0, out.stderr[-2000:]
-    declared = set(re.findall(r"\brocshmem_[a-z0-9_]+\b", out.stdout))
-    missing = [n for n in gen_api.all_names() if n not in declared]
+    declared = set(re.findall(r"\brocshmemx?_[a-z0-9_]+\b", out.stdout))
+    missing = [n for n in gen_api.all_names() + gen_api.extension_names() if n not in declared]
     assert not missing, f"{len(missing)} names are not declared, e.g. {missing[:10]}"
 
 
