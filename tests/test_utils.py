@@ -107,3 +107,22 @@ def test_functional_driver_accepts_the_reference_test_numbers():
         fd.resolve_test("14")
     with pytest.raises(SystemExit, match="0 to 58"):
         fd.resolve_test("59")
+
+
+def test_info_command_reports_configuration_and_runtime(capsys, monkeypatch):
+    import json
+
+    import rocshmem_b200 as shm
+    from rocshmem_b200 import info
+    if shm.is_initialized():
+        shm.finalize()
+    monkeypatch.setenv("ROCSHMEM_HEAP_SIZE", "8M")
+    monkeypatch.setenv("ROCSHMEM_BACKEND", "host")
+    assert info.main(["--init", "--json"]) == 0
+    data = json.loads(capsys.readouterr().out)
+    assert data["built"] and data["config"]["heap_size"] == 8 << 20
+    assert data["runtime"]["n_pes"] == 1 and data["runtime"]["backend"] == "host-shm" and data["runtime"]["size"] == 8 << 20
+    assert not shm.is_initialized()
+    monkeypatch.setenv("ROCSHMEM_MAX_NUM_TEAMS", "0")
+    assert info.main([]) == 0
+    assert "ROCSHMEM_MAX_NUM_TEAMS" in capsys.readouterr().out
