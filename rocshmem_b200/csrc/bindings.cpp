@@ -379,12 +379,14 @@ PYBIND11_MODULE(_C, m) {
     d["max_teams"] = c.max_teams;
     d["wait_timeout_ms"] = c.wait_timeout_ms;
     d["debug"] = c.debug;
+    d["debug_checks"] = c.debug_checks;
     d["use_proxy"] = c.use_proxy;
     d["proxy_queue_size"] = c.proxy_queue_size;
     d["proxy_coalesce"] = c.proxy_coalesce;
     d["proxy_collectives"] = c.proxy_collectives;
     d["enable_nvls"] = c.enable_nvls;
     d["backend"] = c.backend;
+    d["bootstrap_dir"] = c.bootstrap_dir;
     return d;
   });
   py::class_<Pow2Allocator>(m, "Pow2Allocator")
