@@ -10,10 +10,16 @@ import pytest
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 CONSUMER = """cmake_minimum_required(VERSION 3.24)
-project(consumer LANGUAGES CXX)
+project(consumer LANGUAGES CXX CUDA)
+set(CMAKE_CUDA_ARCHITECTURES "100a")
+set(CMAKE_CUDA_STANDARD 17)
 find_package(rocshmem_b200 REQUIRED)
+find_package(CUDAToolkit REQUIRED)
 add_executable(sos {src})
 target_link_libraries(sos PRIVATE roc::rocshmem)
+# a program that uses the device API from its own kernels (compiled and linked here, run by the GPU tests)
+add_executable(allreduce {cu})
+target_link_libraries(allreduce PRIVATE roc::rocshmem CUDA::cudart CUDA::cuda_driver)
 """
 
 
@@ -31,10 +37,12 @@ def test_installed_package_is_usable_from_another_cmake_project(tmp_path):
     assert (prefix / "include" / "rocshmem" / "rocshmem.h").exists()
     consumer = tmp_path / "consumer"
     consumer.mkdir()
-    (consumer / "CMakeLists.txt").write_text(CONSUMER.format(src=os.path.join(ROOT, "tests", "cpp", "host_api_sos.cpp")))
+    (consumer / "CMakeLists.txt").write_text(CONSUMER.format(src=os.path.join(ROOT, "tests", "cpp", "host_api_sos.cpp"),
+                                                              cu=os.path.join(ROOT, "examples", "allreduce.cu")))
     cbuild = tmp_path / "cbuild"
     _run(["cmake", "-S", str(consumer), "-B", str(cbuild), f"-DCMAKE_PREFIX_PATH={prefix}"])
-    _run(["cmake", "--build", str(cbuild)])
+    _run(["cmake", "--build", str(cbuild), "-j", "4"])
+    assert (cbuild / "allreduce").exists()
     kv = tmp_path / "kv"
     kv.mkdir()
     procs = [subprocess.Popen([str(cbuild / "sos")],
