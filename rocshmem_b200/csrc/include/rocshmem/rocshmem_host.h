@@ -30,7 +30,9 @@ namespace host {
 
 // ---- lifecycle ------------------------------------------------------------------------------
 // Bootstraps from the environment: RANK / WORLD_SIZE / LOCAL_RANK as set by torchrun (a single
-// process when unset), rendezvous through files under ROCSHMEM_BOOTSTRAP_DIR, ROCSHMEM_LOCAL_PES
+// process when unset), rendezvous through files under ROCSHMEM_BOOTSTRAP_DIR (by default a directory in
+// /dev/shm named after the user, MASTER_PORT, the run id and the launching process, so that every launch
+// gets its own; ranks started by different parent processes must set the variable), ROCSHMEM_LOCAL_PES
 // PEs per process. Python programs initialise through rocshmem_b200.init() instead, which hands a
 // torch.distributed store to the runtime.
 void init();

@@ -1,4 +1,5 @@
 // Host-side API: argument checking, handle unwrapping, statistics, then the host-operation engine.
+#include <dirent.h>
 #include <unistd.h>
 
 #include <chrono>
@@ -58,6 +59,80 @@ HostTeam *host_team(rocshmem_team_t team) {
 
 }  // namespace
 
+namespace {
+
+// Start time of a process in clock ticks since boot (field 22 of /proc/<pid>/stat), 0 when it does not exist.
+unsigned long long process_start_time(long pid) {
+  std::FILE *f = std::fopen(("/proc/" + std::to_string(pid) + "/stat").c_str(), "r");
+  if (!f) return 0;
+  char buf[1024];
+  size_t n = std::fread(buf, 1, sizeof(buf) - 1, f);
+  std::fclose(f);
+  buf[n] = '\0';
+  const char *p = std::strrchr(buf, ')');   // the command name may contain spaces and parentheses
+  if (!p) return 0;
+  unsigned long long value = 0;
+  int field = 2;
+  for (++p; *p; ++p) {
+    if (*p != ' ') continue;
+    if (++field == 22) {
+      value = std::strtoull(p + 1, nullptr, 10);
+      break;
+    }
+  }
+  return value;
+}
+
+constexpr const char *kRendezvousRoot = "/dev/shm";
+std::string rendezvous_prefix() { return "rocshmem_b200." + std::to_string(::getuid()) + "."; }
+
+// The default rendezvous directory of a job. All ranks of one launch share their parent process (torchrun's
+// agent, the launcher of this package, mpirun), so its pid and start time make the name unique per launch: files
+// that an earlier job on the same port left behind are never read. Ranks started by different parents (by hand,
+// in separate shells) have to agree on ROCSHMEM_BOOTSTRAP_DIR instead.
+std::string default_rendezvous_dir() {
+  const char *port = std::getenv("MASTER_PORT");
+  const char *run = std::getenv("TORCHELASTIC_RUN_ID");
+  const long parent = static_cast<long>(::getppid());
+  return std::string(kRendezvousRoot) + "/" + rendezvous_prefix() + (port ? port : "0") + "." + (run ? run : "job") +
+         "." + std::to_string(parent) + "." + std::to_string(process_start_time(parent));
+}
+
+// Best effort, rank 0 only: remove rendezvous directories of this user whose launching process is gone.
+void purge_stale_rendezvous_dirs() {
+  DIR *d = ::opendir(kRendezvousRoot);
+  if (!d) return;
+  const std::string prefix = rendezvous_prefix();
+  std::vector<std::string> stale;
+  while (dirent *e = ::readdir(d)) {
+    const std::string name = e->d_name;
+    if (name.compare(0, prefix.size(), prefix) != 0) continue;
+    // ... .<parent pid>.<parent start time>
+    const size_t dot2 = name.rfind('.');
+    const size_t dot1 = dot2 == std::string::npos || dot2 == 0 ? std::string::npos : name.rfind('.', dot2 - 1);
+    if (dot1 == std::string::npos) continue;
+    char *end = nullptr;
+    const long pid = std::strtol(name.c_str() + dot1 + 1, &end, 10);
+    if (end != name.c_str() + dot2 || pid <= 0) continue;      // not a name of the current scheme: leave it alone
+    const unsigned long long start = std::strtoull(name.c_str() + dot2 + 1, &end, 10);
+    if (*end != '\0') continue;
+    if (process_start_time(pid) != start) stale.push_back(name);
+  }
+  ::closedir(d);
+  for (const std::string &name : stale) {
+    const std::string path = std::string(kRendezvousRoot) + "/" + name;
+    if (DIR *sub = ::opendir(path.c_str())) {
+      while (dirent *e = ::readdir(sub)) {
+        if (std::strcmp(e->d_name, ".") != 0 && std::strcmp(e->d_name, "..") != 0) ::unlink((path + "/" + e->d_name).c_str());
+      }
+      ::closedir(sub);
+    }
+    ::rmdir(path.c_str());
+  }
+}
+
+}  // namespace
+
 namespace host {
 
 void init() {
@@ -73,10 +148,8 @@ void init() {
   } else {
     std::string dir = cfg.bootstrap_dir;
     if (dir.empty()) {
-      const char *port = std::getenv("MASTER_PORT");
-      const char *run = std::getenv("TORCHELASTIC_RUN_ID");
-      dir = std::string("/dev/shm/rocshmem_b200.") + std::to_string(::getuid()) + "." +
-            (port ? port : "0") + "." + (run ? run : "job");
+      if (rank == 0) purge_stale_rendezvous_dirs();
+      dir = default_rendezvous_dir();
     }
     bs = std::make_unique<FileBootstrap>(dir, rank, size);
   }

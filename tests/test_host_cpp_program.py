@@ -78,3 +78,22 @@ def test_launcher_runs_ranks_tags_output_and_propagates_failures(programs):
     assert rc == 124
     # command line form
     assert launch.main(["-n", "2", "--no-tag", "--", sys.executable, "-c", "import os; assert os.environ['WORLD_SIZE'] == '2'"]) == 0
+
+
+def test_repeated_launches_on_one_port_do_not_see_each_others_rendezvous_files(programs):
+    """Without ROCSHMEM_BOOTSTRAP_DIR the rendezvous directory is derived from the port, the run id and the
+    launching process, so a second job on the same port starts clean, and directories whose launcher is gone are
+    removed by the next job."""
+    import glob
+    import sys
+    env = {k: v for k, v in os.environ.items() if k != "ROCSHMEM_BOOTSTRAP_DIR"}
+    env.update(ROCSHMEM_BACKEND="host", ROCSHMEM_HEAP_SIZE="16M")
+    pattern = f"/dev/shm/rocshmem_b200.{os.getuid()}.29677.*"
+    for attempt in range(2):
+        out = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--no-python", "--nnodes=1",
+                              "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port", "29677",
+                              programs["host_api_sos"]], env=env, capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0 and out.stdout.count("PASS") == 2, (attempt, out.stdout[-2000:] + out.stderr[-3000:])
+        assert len(glob.glob(pattern)) == 1          # the first job's directory was purged by the second
+    for d in glob.glob(pattern):
+        shutil.rmtree(d, ignore_errors=True)
