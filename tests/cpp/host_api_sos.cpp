@@ -8,6 +8,7 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <stdexcept>
 #include <vector>
 
 using namespace rocshmem;
@@ -183,6 +184,41 @@ int main() {
   }
   rocshmem_barrier_all();
   CHECK(rocshmem_long_g(a + 1, me) == 1099L);
+
+  // the pool of host contexts is finite: creation reports it with -1, and destroying makes room again
+  {
+    std::vector<rocshmem_ctx_t> pool;
+    for (;;) {
+      rocshmem_ctx_t ctx;
+      if (rocshmem_ctx_create(0, &ctx) != 0) break;
+      pool.push_back(ctx);
+      CHECK(pool.size() <= 4096);
+    }
+    CHECK(pool.size() == 39);                     // ROCSHMEM_MAX_NUM_HOST_CONTEXTS = 40, one is the default context
+    for (rocshmem_ctx_t &ctx : pool) rocshmem_ctx_destroy(ctx);
+    rocshmem_ctx_t again;
+    CHECK(rocshmem_ctx_create(0, &again) == 0);
+    rocshmem_ctx_destroy(again);
+  }
+  // misuse is reported, not fatal: freeing nothing is a no-op, freeing a foreign pointer and naming a PE that does
+  // not exist raise exceptions, queries on the invalid team answer -1
+  rocshmem_free(nullptr);
+  bool threw = false;
+  try {
+    rocshmem_free(&threw);
+  } catch (const std::exception &) {
+    threw = true;
+  }
+  CHECK(threw);
+  threw = false;
+  try {
+    rocshmem_long_p(a, 1L, n + 3);
+  } catch (const std::exception &) {
+    threw = true;
+  }
+  CHECK(threw);
+  CHECK(rocshmem_team_n_pes(ROCSHMEM_TEAM_INVALID) == -1 && rocshmem_team_my_pe(ROCSHMEM_TEAM_INVALID) == -1);
+  rocshmem_team_destroy(ROCSHMEM_TEAM_INVALID);
 
   // rocshmem_ptr: the peer's address of a symmetric object, nullptr for a bad PE or a foreign pointer
   CHECK(rocshmem_ptr(a, right) != nullptr && rocshmem_ptr(a, n) == nullptr);
