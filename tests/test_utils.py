@@ -126,3 +126,23 @@ def test_info_command_reports_configuration_and_runtime(capsys, monkeypatch):
     monkeypatch.setenv("ROCSHMEM_MAX_NUM_TEAMS", "0")
     assert info.main([]) == 0
     assert "ROCSHMEM_MAX_NUM_TEAMS" in capsys.readouterr().out
+
+
+def test_matrix_runner_lists_its_cases_and_parses_driver_tables(capsys):
+    import importlib.util
+    import os
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "benchmarks", "run_matrix.py")
+    spec = importlib.util.spec_from_file_location("run_matrix", path)
+    rm = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rm)
+    assert rm.main(["--dry-run", "--only", "put,allreduce"]) == 0
+    lines = [l for l in capsys.readouterr().out.splitlines() if l]
+    assert len(lines) == 7 and all("functional_driver.py -a " in l and "--local-pes 2" in l for l in lines)
+    assert rm.main(["--dry-run", "--gpus", "4"]) == 0
+    lines = [l for l in capsys.readouterr().out.splitlines() if l]
+    assert len(lines) == len(rm.MATRIX) and all("launch -n 4" in l and "--local-pes" not in l for l in lines)
+    table = "\n".join(["# test put, 2 PEs", "    Size (B)     # msgs   Latency (us)   Bandwidth (GB/s)   Msg rate (msg/s)",
+                       "[0]            8         10          0.310              0.026            3225806",
+                       "        1048576         10          2.005            523.000             498753", "noise 1 2 3 4"])
+    rows = list(rm.parse_rows(table))
+    assert rows == [(8, 10, 0.31, 0.026, 3225806.0), (1048576, 10, 2.005, 523.0, 498753.0)]
