@@ -518,6 +518,35 @@ def get_error(local: int = -1) -> dict:
     return _C().get_error(local)
 
 
+ERROR_KINDS = {0: "none", 1: "wait_until timed out", 2: "barrier / collective flag wait timed out", 3: "PE out of range",
+               4: "address outside the symmetric heap", 5: "device context pool exhausted",
+               6: "reverse-offload ring timed out", 7: "grid barrier timed out", 8: "library kernel gave up on an internal wait"}
+
+# The `where` field of an error record: which operation recorded it.
+ERROR_SITES = {
+    0: "a host API call", 1: "reverse-offload ring: no free slot", 2: "reverse-offload ring: no completion",
+    10: "putmem", 11: "getmem", 12: "p", 13: "g", 20: "atomic add / fetch_add", 21: "atomic swap / set",
+    22: "atomic compare_swap", 23: "atomic fetch", 24: "atomic and", 25: "atomic or", 26: "atomic xor",
+    30: "put with signal", 40: "wait_until", 41: "wait_until_any", 42: "wait_until_some",
+    50: "team barrier / sync", 60: "library collective: peer block did not arrive", 61: "library kernel: grid barrier",
+    70: "MoE dispatch: count exchange", 80: "all-gather -> GEMM: rows of a peer did not arrive",
+    81: "all-gather -> GEMM (two CTAs per tile): rows of a peer did not arrive",
+    90: "ticket lock", 91: "spin lock", 92: "rocshmemx_grid_sync",
+}
+
+
+def describe_error(err: Optional[dict] = None) -> str:
+    """One line of plain words for an error record (the current one of this PE by default)."""
+    err = get_error() if err is None else err
+    if not err.get("count"):
+        return "no error recorded"
+    kind = ERROR_KINDS.get(err.get("kind"), f"kind {err.get('kind')}")
+    site = ERROR_SITES.get(err.get("where"), f"site {err.get('where')}")
+    peer = f", peer PE {err['pe']}" if err.get("pe", -1) >= 0 else ""
+    return (f"{kind} in {site}{peer}: expected {err.get('expected')}, observed {err.get('observed')} at address "
+            f"0x{err.get('addr', 0):x} ({err['count']} error(s) since the record was cleared)")
+
+
 def clear_error() -> None:
     """Reset the first-error record of this PE."""
     _C().clear_error()

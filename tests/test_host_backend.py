@@ -226,3 +226,21 @@ def test_stream_ordered_collectives_reject_buffers_that_are_not_symmetric(shm4):
         coll.fcollect_async(a, b, stream=0)               # 4 PEs x 64 elements
     with pytest.raises(ValueError, match="not a multiple"):
         coll.alltoall_async(a, shm.zeros(6, torch.float32), stream=0)
+
+
+def test_error_records_are_described_in_words(fresh_runtime):
+    shm = fresh_runtime
+    shm.init(n_local=2, heap_size="4M", backend="host", ROCSHMEM_WAIT_TIMEOUT_MS=50)
+    try:
+        assert shm.describe_error() == "no error recorded"
+        flag = shm.zeros(1, torch.int64)
+        assert shm.wait_until(flag, shm.CMP_EQ, 5) == shm.ERROR
+        text = shm.describe_error()
+        assert text.startswith("wait_until timed out in a host API call") and "expected 5, observed 0" in text
+        made_up = {"count": 2, "kind": 2, "pe": 3, "where": 70, "addr": 0x10, "expected": 9, "observed": 8}
+        assert shm.describe_error(made_up).startswith("barrier / collective flag wait timed out in MoE dispatch: count "
+                                                      "exchange, peer PE 3")
+        shm.clear_error()
+        assert shm.describe_error() == "no error recorded"
+    finally:
+        shm.finalize()
