@@ -14,6 +14,7 @@ run it explicitly, and move each case into the regular test files once it has pa
     python -m rocshmem_b200.launch -n 2 python examples/python/data_parallel.py    # gradient buckets on the allreduce kernel
     python -m rocshmem_b200.launch -n 2 python examples/python/ring_attention.py   # host-API ring between GPUs
     python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/ep_baseline_bench.py
+    python benchmarks/profile_moe_layer.py --steps 2 [--fp8]                      # per-stage times; the ncu capture target
     ROCSHMEM_BCAST_NVLS=1 python -m pytest tests/test_multi_gpu.py -m gpu -x -q -k library   # multicast broadcast (>= 2 GPUs)
     ROCSHMEM_BCAST_NVLS=1 python -m torch.distributed.run --nproc-per-node 8 --master-addr 127.0.0.1 benchmarks/coll_bench.py
 """
