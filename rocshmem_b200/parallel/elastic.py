@@ -1,0 +1,47 @@
+"""Shrinking a running job: ranks leave between steps, the survivors re-initialise a smaller world and carry on.
+
+The reference has no recovery of any kind (an error aborts the job, ``src/ipc/backend_ipc.cpp:28-34``). Teams
+cannot express an arbitrary set of survivors either: OpenSHMEM teams are strided, and the survivors of a job that
+lost rank 2 of 4 are not. So the world itself is rebuilt: every rank of the old world calls :func:`shrink` at the same
+point between two steps, with nothing in flight; those that leave say so; everybody finalises the runtime (the last
+collective the old world performs); the survivors initialise a new runtime over the same store with dense PE
+numbers in the old order. Heap contents do not survive a re-initialisation: take a
+``rocshmem_b200.utils.checkpoint.snapshot`` before and ``restore`` it into the tensors allocated afterwards.
+
+This is the planned, host-side half of failure handling - a rank that decides to go (draining a node, a failed
+health check seen between steps). A rank that dies in the middle of a step is a different matter: its peers' waits
+run out, their error records say which PE did not answer (``describe_error``), and the job decides on the host what
+to do next; no kernel waits for ever in either case.
+"""
+from __future__ import annotations
+
+from typing import Optional, Tuple
+
+from .. import runtime as rt
+from .membership import Membership
+
+
+def shrink(membership: Membership, leaving: bool = False) -> Optional[Tuple[int, int]]:
+    """Collective over the current world. Returns ``(new_pe, new_n_pes)`` on survivors, ``None`` on ranks that left
+    (their runtime is finalised; they may exit). Requires a multi-process runtime initialised over a store that
+    survives the departure (under torchrun the agent serves it; otherwise the rank that hosts it must stay)."""
+    store = rt.bootstrap_store()
+    if store is None or not rt.is_initialized():
+        raise RuntimeError("shrink needs a runtime that was initialised over a store")
+    args = rt.last_init_arguments()
+    old_pe = membership.rank
+    if leaving:
+        membership.announce_leave()
+    # finalize synchronises the old world: every leave record is in the store before anybody goes on
+    rt.finalize()
+    if leaving:
+        return None
+    alive = membership.alive()
+    if old_pe not in alive:
+        raise RuntimeError("this rank was declared gone by its own record")
+    new_pe, new_n = alive.index(old_pe), len(alive)
+    timeout_s = args.pop("timeout_s", 120.0)
+    n_local = args.pop("n_local", 1)
+    device = args.pop("device", None)
+    rt.init(store, new_pe, new_n, n_local=n_local, device=device, timeout_s=timeout_s, **args)
+    return new_pe, new_n

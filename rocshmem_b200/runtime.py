@@ -56,6 +56,7 @@ class _State:
     prefix: str = ""
     allocations: Dict[int, int] = None  # data_ptr -> bytes
     heap_lo: int = 0                    # address range of the heaps of this process's PEs
+    init_args: Dict[str, object] = None # keyword arguments of the last init (for a re-initialisation)
     heap_hi: int = 0
 
 
@@ -131,9 +132,22 @@ def init(store=None, rank: Optional[int] = None, world_size: Optional[int] = Non
         C.init_file(0, 1, "", ov, n_local, device, timeout_ms)
     _state.initialised = True
     _state.allocations = {}
+    _state.init_args = dict(n_local=n_local, device=device if _state.device.type == "cuda" else None,
+                            timeout_s=timeout_s, **ov)
     first = C.my_pe()                   # local PE 0 is current right after init
     _state.heap_lo = C.heap_base(first)
     _state.heap_hi = C.heap_base(first + n_local - 1) + C.heap_size()
+
+
+def bootstrap_store():
+    """The ``torch.distributed`` store the last multi-process ``init`` exchanged its descriptors through (``None``
+    for a single process). It outlives ``finalize``, so a smaller or larger world can be initialised over it."""
+    return _state.store
+
+
+def last_init_arguments() -> dict:
+    """Keyword arguments of the last ``init`` (PEs per process, device, time-out, configuration overrides)."""
+    return dict(_state.init_args or {})
 
 
 def finalize() -> None:

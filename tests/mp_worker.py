@@ -899,7 +899,46 @@ def alltoallv_host():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def elastic_shrink():
+    """Rank 2 of 4 leaves between two steps; the others rebuild a world of three (not a strided subset of the old
+    one), restore their heap tensors from a snapshot and go on with collectives."""
+    from rocshmem_b200.parallel.elastic import shrink
+    from rocshmem_b200.parallel.membership import Membership
+    from rocshmem_b200.utils import checkpoint
+    init("16M")
+    me, n = shm.my_pe(), shm.n_pes()
+    assert n == 4
+    mem = Membership(shm.runtime.bootstrap_store(), me, n, prefix="elastic")
+    weights = shm.zeros(32, torch.float64)
+    total = shm.zeros(32, torch.float64)
+    weights.copy_((torch.arange(32, dtype=torch.float64) + 100 * me).to(dev()))
+    assert coll.reduce(total, weights, shm.OP_SUM) == 0
+    assert torch.equal(total.cpu(), torch.arange(32, dtype=torch.float64) * 4 + 100 * 6)
+    saved = checkpoint.snapshot({"weights": weights})
+    result = shrink(mem, leaving=(me == 2))
+    if me == 2:
+        assert result is None and not shm.is_initialized()
+        print("rank 2 left", flush=True)
+        return
+    new_pe, new_n = result
+    assert new_n == 3 and new_pe == {0: 0, 1: 1, 3: 2}[me]
+    assert shm.my_pe() == new_pe and shm.n_pes() == 3
+    weights = shm.zeros(32, torch.float64)
+    total = shm.zeros(32, torch.float64)
+    checkpoint.restore({"weights": weights}, saved)
+    assert coll.reduce(total, weights, shm.OP_SUM) == 0
+    assert torch.equal(total.cpu(), torch.arange(32, dtype=torch.float64) * 3 + 100 * (0 + 1 + 3))
+    # point-to-point with the new numbering: old rank 3 is now PE 2
+    probe = shm.zeros(1, torch.int64)
+    shm.barrier_all()
+    shm.putmem(probe, torch.tensor([me + 10]).to(dev()), (new_pe + 1) % 3)
+    shm.barrier_all()
+    assert int(probe.cpu()[0]) == {0: 3, 1: 0, 2: 1}[new_pe] + 10
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

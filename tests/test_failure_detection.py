@@ -62,3 +62,9 @@ def test_proxy_ring_executes_and_reports_dropped_commands(fresh_runtime):
     finally:
         C.proxy_stop(p)
         shm.finalize()
+
+
+def test_world_shrinks_when_a_middle_rank_leaves_and_survivors_restore_their_heap():
+    results = run_ranks("elastic_shrink", 4, timeout=180)
+    assert_all_ok(results)
+    assert "rank 2 left" in results[2][1]
