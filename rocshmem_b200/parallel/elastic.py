@@ -15,16 +15,21 @@ to do next; no kernel waits for ever in either case.
 """
 from __future__ import annotations
 
-from typing import Optional, Tuple
+from typing import Optional, Sequence, Tuple
 
 from .. import runtime as rt
 from .membership import Membership
 
 
-def shrink(membership: Membership, leaving: bool = False) -> Optional[Tuple[int, int]]:
+def shrink(membership: Membership, leaving: bool = False, dead: Sequence[int] = ()) -> Optional[Tuple[int, int]]:
     """Collective over the current world. Returns ``(new_pe, new_n_pes)`` on survivors, ``None`` on ranks that left
     (their runtime is finalised; they may exit). Requires a multi-process runtime initialised over a store that
-    survives the departure (under torchrun the agent serves it; otherwise the rank that hosts it must stay)."""
+    survives the departure (under torchrun the agent serves it; otherwise the rank that hosts it must stay).
+
+    ``dead``: ranks that went away without saying so (every survivor passes the same list, e.g. from
+    ``membership.stale(age)`` with an age that all agree on). They are recorded as gone on their behalf; the old
+    world's last synchronisation then runs into its time-out (the bootstrap time-out given to ``init``) instead of
+    completing, which is reported on stderr and otherwise harmless."""
     store = rt.bootstrap_store()
     if store is None or not rt.is_initialized():
         raise RuntimeError("shrink needs a runtime that was initialised over a store")
@@ -32,6 +37,8 @@ def shrink(membership: Membership, leaving: bool = False) -> Optional[Tuple[int,
     old_pe = membership.rank
     if leaving:
         membership.announce_leave()
+    for r in dead:
+        membership.declare_left(int(r))
     # finalize synchronises the old world: every leave record is in the store before anybody goes on
     rt.finalize()
     if leaving:

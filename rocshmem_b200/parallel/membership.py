@@ -55,6 +55,10 @@ class Membership:
         """Record that this rank leaves the job (call between steps, with nothing in flight)."""
         self.store.set(self._key("left", self.rank), "1")
 
+    def declare_left(self, rank: int) -> None:
+        """Record on behalf of ``rank`` that it is gone (a peer that stopped sending heartbeats). Idempotent."""
+        self.store.set(self._key("left", rank), "1")
+
     def has_left(self, rank: int) -> bool:
         """True once ``rank`` has announced its departure."""
         return bool(self.store.check([self._key("left", rank)]))

@@ -938,7 +938,43 @@ def elastic_shrink():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def elastic_unplanned():
+    """A rank disappears between two steps without a word; the others notice that its heartbeat went stale, record
+    it as gone, rebuild a world of two and go on."""
+    import time
+    from rocshmem_b200.parallel.elastic import shrink
+    from rocshmem_b200.parallel.membership import Membership
+    init("16M")
+    me, n = shm.my_pe(), shm.n_pes()
+    assert n == 3
+    mem = Membership(shm.runtime.bootstrap_store(), me, n, prefix="unplanned")
+    x = shm.zeros(4, torch.int64)
+    y = shm.zeros(4, torch.int64)
+    x.fill_(me + 1)
+    assert coll.reduce(y, x) == 0 and int(y.cpu()[0]) == 6
+    shm.barrier_all()
+    if me == 1:
+        os._exit(0)                                # gone: no leave record, no finalize
+    deadline = time.time() + 30
+    stale = []
+    while time.time() < deadline:
+        mem.heartbeat()
+        stale = mem.stale(1.5)
+        if stale:
+            break
+        time.sleep(0.2)
+    assert stale == [1], stale
+    new_pe, new_n = shrink(mem, dead=stale)
+    assert (new_pe, new_n) == ({0: 0, 2: 1}[me], 2)
+    x = shm.zeros(4, torch.int64)
+    y = shm.zeros(4, torch.int64)
+    x.fill_(me + 1)
+    assert coll.reduce(y, x) == 0 and int(y.cpu()[0]) == 1 + 3
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

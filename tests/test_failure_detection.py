@@ -68,3 +68,10 @@ def test_world_shrinks_when_a_middle_rank_leaves_and_survivors_restore_their_hea
     results = run_ranks("elastic_shrink", 4, timeout=180)
     assert_all_ok(results)
     assert "rank 2 left" in results[2][1]
+
+
+def test_survivors_notice_a_silent_departure_and_rebuild_the_world():
+    t0 = time.time()
+    results = run_ranks("elastic_unplanned", 3, timeout=150, env_extra={"ROCSHMEM_TEST_TIMEOUT": 6})
+    assert_all_ok(results)
+    assert time.time() - t0 < 120
