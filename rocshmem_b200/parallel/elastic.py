@@ -8,8 +8,9 @@ collective the old world performs); the survivors initialise a new runtime over 
 numbers in the old order. Heap contents do not survive a re-initialisation: take a
 ``rocshmem_b200.utils.checkpoint.snapshot`` before and ``restore`` it into the tensors allocated afterwards.
 
-This is the planned, host-side half of failure handling - a rank that decides to go (draining a node, a failed
-health check seen between steps). A rank that dies in the middle of a step is a different matter: its peers' waits
+This is the host-side half of failure handling: a rank that decides to go (draining a node, a failed health check
+seen between steps), or one that vanished between steps and whose heartbeat went stale (``dead=``). A rank that dies
+in the middle of a step is a different matter: its peers' waits
 run out, their error records say which PE did not answer (``describe_error``), and the job decides on the host what
 to do next; no kernel waits for ever in either case.
 """
