@@ -63,6 +63,43 @@ def alltoall(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] =
     return rt._C().alltoall(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source) // n)
 
 
+def reduce_scatter(dest: torch.Tensor, source: torch.Tensor, op: int = rt.OP_SUM,
+                   team: Optional[rt.Team] = None) -> int:
+    """Member *i*'s ``dest`` (``source.numel() / n`` elements) receives block *i* of the element-wise reduction of
+    all members' ``source``. Host-blocking; built from the host API (every member pulls block *i* of each peer and
+    reduces it locally), so it runs on every backend. The fused GEMM -> reduce-scatter kernel is the fast path for
+    tensor parallelism; this is the general-purpose form (sharded optimiser states and the like)."""
+    t = team or rt.team_world()
+    n, me = t.n_pes(), t.my_pe()
+    if me < 0:
+        return rt.ERROR
+    if source.numel() % n or dest.numel() < source.numel() // n or dest.dtype != source.dtype:
+        raise ValueError("reduce_scatter: source must hold n equal blocks of dest's type, dest one block")
+    rt.require_symmetric(dest=dest, source=source)
+    if op not in (rt.OP_SUM, rt.OP_MIN, rt.OP_MAX, rt.OP_PROD):
+        raise ValueError("reduce_scatter supports sum, min, max and prod")
+    blk = source.numel() // n
+    world = rt.team_world()
+    if t.sync() != rt.SUCCESS:                         # every member's source is complete
+        return rt.ERROR
+    mine = source.view(-1)[me * blk:(me + 1) * blk]
+    wide = torch.float64 if source.dtype.is_floating_point else torch.int64
+    acc = mine.to(wide).clone()
+    tmp = torch.empty(blk, dtype=source.dtype, device=source.device)
+    for d in range(1, n):
+        peer = (me + d) % n
+        rt.getmem(tmp, mine, t.translate_pe(peer, world))
+        v = tmp.to(wide)
+        acc = {rt.OP_SUM: torch.add, rt.OP_PROD: torch.mul, rt.OP_MIN: torch.minimum, rt.OP_MAX: torch.maximum}[op](acc, v)
+    dest.view(-1)[:blk].copy_(acc.to(dest.dtype))
+    return t.sync()                                    # nobody overwrites its source while a peer still reads it
+
+
+def allgather(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None) -> int:
+    """Alias of :func:`fcollect` under its usual name."""
+    return fcollect(dest, source, team)
+
+
 # ---- stream-ordered ---------------------------------------------------------------------------------------
 
 def barrier_async(team: Optional[rt.Team] = None, stream=None) -> None:

@@ -974,7 +974,43 @@ def elastic_unplanned():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def reduce_scatter_host():
+    """Reduce-scatter over the world and over a strided team, every operation and three element types, against
+    torch."""
+    init("16M")
+    me, n = shm.my_pe(), shm.n_pes()
+    blk = 6
+    world = shm.team_world()
+    evens = world.split_strided(0, 2, (n + 1) // 2)
+    types = (torch.float32, torch.int64, torch.bfloat16)
+    src_w = {dt: shm.zeros(n * blk, dt) for dt in types}
+    dst_w = {dt: shm.zeros(blk, dt) for dt in types}
+    ops = ((shm.OP_SUM, lambda a: a.sum(0)), (shm.OP_MAX, lambda a: a.max(0).values),
+           (shm.OP_MIN, lambda a: a.min(0).values), (shm.OP_PROD, lambda a: a.prod(0)))
+    for team, members in ((world, list(range(n))), (evens, list(range(0, n, 2)))):
+        m = len(members)
+        for dtype in types:
+            # small integers: sums and products of up to n of them are exact in every type
+            data = {r: ((torch.arange(m * blk) % 5) - 2 + (r % 2)).to(dtype) for r in range(n)}
+            src, dst = src_w[dtype], dst_w[dtype]
+            src[:m * blk].copy_(data[me].to(dev()))
+            shm.barrier_all()
+            if me in members:
+                i = members.index(me)
+                stack = torch.stack([data[r] for r in members])
+                wide = stack.double() if dtype.is_floating_point else stack.long()
+                for op, fn in ops:
+                    assert coll.reduce_scatter(dst, src[:m * blk], op, team) == 0
+                    want = fn(wide)[i * blk:(i + 1) * blk].to(dtype)
+                    assert torch.equal(dst.cpu(), want), (dtype, op, dst.cpu(), want)
+            shm.barrier_all()
+    if evens.valid:
+        evens.destroy()
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (reduce_scatter_host, elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

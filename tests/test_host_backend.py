@@ -244,3 +244,22 @@ def test_error_records_are_described_in_words(fresh_runtime):
         assert shm.describe_error() == "no error recorded"
     finally:
         shm.finalize()
+
+
+def test_reduce_scatter_argument_checks_and_allgather_alias(shm4):
+    shm = shm4
+    n = 4
+    src = shm.zeros(n * 5, torch.float32)
+    dst = shm.zeros(5, torch.float32)
+    data = [torch.arange(n * 5, dtype=torch.float32) * (l + 1) - 3 * l for l in range(n)]
+    for l in range(n):
+        shm.local_view(src, l).copy_(data[l])
+    with pytest.raises(ValueError, match="equal blocks"):
+        coll.reduce_scatter(dst, shm.zeros(7, torch.float32))
+    with pytest.raises(ValueError, match="sum, min, max and prod"):
+        coll.reduce_scatter(dst, src, shm.OP_XOR)
+    with pytest.raises(ValueError, match="symmetric heap"):
+        coll.reduce_scatter(torch.zeros(5), src)
+    gat = shm.zeros(n * 5, torch.float32)
+    assert coll.allgather(gat, src[:5]) == 0
+    assert torch.equal(shm.local_view(gat, 2).view(n, 5)[3], data[3][:5])

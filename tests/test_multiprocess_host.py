@@ -81,3 +81,8 @@ def test_pipeline_stages_match_the_whole_model():
 
 def test_variable_count_all_to_all():
     assert_all_ok(run_ranks("alltoallv_host", 4, timeout=240))
+
+
+@pytest.mark.parametrize("world", [3, 4])
+def test_reduce_scatter_over_the_host_api(world):
+    assert_all_ok(run_ranks("reduce_scatter_host", world, timeout=240))
