@@ -103,7 +103,12 @@ void Proxy::run() {
       continue;
     }
     idle = 0;
-    __atomic_store_n(&slot.valid, 2u, __ATOMIC_RELAXED);
+    // Claim the command with a compare-and-swap: a producer whose wait ran out may be cancelling it (1 -> 3) at
+    // this very moment, and a plain store would overwrite the cancellation and leave the slot claimed for ever.
+    unsigned expect_published = 1;
+    if (!__atomic_compare_exchange_n(&slot.valid, &expect_published, 2u, false, __ATOMIC_ACQ_REL, __ATOMIC_ACQUIRE)) {
+      continue;   // cancelled in the meantime: the next iteration retires it
+    }
     rocshmem_proxy_cmd cmd;
     std::memcpy(&cmd, const_cast<rocshmem_proxy_cmd *>(&slot), sizeof(cmd));
     uint64_t seq = read_ + 1;
@@ -134,7 +139,10 @@ void Proxy::run() {
           if (__atomic_load_n(&next.valid, __ATOMIC_ACQUIRE) != 1 || next.type != cmd.type) break;
           coalesce::Msg m{next.pe, next.dst, next.src, next.size};
           if (!coalesce::continues(last, m)) break;
-          __atomic_store_n(&next.valid, 2u, __ATOMIC_RELAXED);
+          unsigned expect_next = 1;
+          if (!__atomic_compare_exchange_n(&next.valid, &expect_next, 2u, false, __ATOMIC_ACQ_REL, __ATOMIC_ACQUIRE)) {
+            break;   // being cancelled by its producer
+          }
           cmd.size += m.size;
           last = m;
           ++extra;
