@@ -1,4 +1,5 @@
-"""Shrinking a running job: ranks leave between steps, the survivors re-initialise a smaller world and carry on.
+"""Shrinking and growing a running job: ranks leave or join between steps, the others re-initialise a world of the new
+size and carry on.
 
 The reference has no recovery of any kind (an error aborts the job, ``src/ipc/backend_ipc.cpp:28-34``). Teams
 cannot express an arbitrary set of survivors either: OpenSHMEM teams are strided, and the survivors of a job that
@@ -7,6 +8,8 @@ point between two steps, with nothing in flight; those that leave say so; everyb
 collective the old world performs); the survivors initialise a new runtime over the same store with dense PE
 numbers in the old order. Heap contents do not survive a re-initialisation: take a
 ``rocshmem_b200.utils.checkpoint.snapshot`` before and ``restore`` it into the tensors allocated afterwards.
+:func:`grow` and :func:`join` are the opposite direction: the members re-initialise with a larger world and new
+processes take the additional PE numbers.
 
 This is the host-side half of failure handling: a rank that decides to go (draining a node, a failed health check
 seen between steps), or one that vanished between steps and whose heartbeat went stale (``dead=``). A rank that dies
@@ -53,3 +56,39 @@ def shrink(membership: Membership, leaving: bool = False, dead: Sequence[int] = 
     device = args.pop("device", None)
     rt.init(store, new_pe, new_n, n_local=n_local, device=device, timeout_s=timeout_s, **args)
     return new_pe, new_n
+
+
+_GROW_KEY = "rocshmem_b200/grow"
+
+
+def grow(new_world_size: int) -> Tuple[int, int]:
+    """Collective over the current world (one PE per process): finalise and re-initialise with ``new_world_size``
+    PEs. The current members keep their PE numbers; the additional ones are processes that call :func:`join` with
+    PE numbers from the old size upwards. Returns ``(pe, new_world_size)``. Heap contents do not survive (snapshot
+    and restore, as for :func:`shrink`)."""
+    store = rt.bootstrap_store()
+    if store is None or not rt.is_initialized():
+        raise RuntimeError("grow needs a runtime that was initialised over a store")
+    if rt.n_local_pes() != 1 or new_world_size <= rt.n_pes():
+        raise ValueError("grow needs one PE per process and a larger world")
+    args = rt.last_init_arguments()
+    pe, gen = rt.my_pe(), rt.generation() + 1
+    if pe == 0:
+        store.set(_GROW_KEY, f"{gen}:{new_world_size}")
+    rt.finalize()
+    rt.init(store, pe, new_world_size, n_local=args.pop("n_local", 1), device=args.pop("device", None),
+            timeout_s=args.pop("timeout_s", 120.0), generation=gen, **args)
+    return pe, new_world_size
+
+
+def join(store, pe: int, timeout_s: float = 120.0, **init_arguments) -> Tuple[int, int]:
+    """Called by a new process: wait until the running job announces that it grows, then initialise as PE ``pe`` of
+    the new world over ``store`` (a client connection to the job's store). ``init_arguments`` are those of
+    ``rocshmem_b200.init`` (heap size, backend, device ...) and must match the running job's."""
+    import datetime
+    store.wait([_GROW_KEY], datetime.timedelta(seconds=timeout_s))
+    gen, n = (int(v) for v in bytes(store.get(_GROW_KEY)).decode().split(":"))
+    if not gen > 0 or not 0 <= pe < n:
+        raise ValueError(f"cannot join as PE {pe} of {n}")
+    rt.init(store, pe, n, timeout_s=timeout_s, generation=gen, **init_arguments)
+    return pe, n

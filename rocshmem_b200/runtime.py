@@ -72,14 +72,17 @@ def _C():
 
 def init(store=None, rank: Optional[int] = None, world_size: Optional[int] = None, *,
          n_local: int = 1, device: Optional[int] = None, heap_size=None, backend: Optional[str] = None,
-         timeout_s: float = 120.0, **overrides) -> None:
+         timeout_s: float = 120.0, generation: Optional[int] = None, **overrides) -> None:
     """Collective initialisation.
 
     ``store`` is any ``torch.distributed`` store; when omitted, the store of the default process group
     is used if there is one, else a ``TCPStore`` is created from ``MASTER_ADDR`` / ``MASTER_PORT``
     (``RANK`` / ``WORLD_SIZE`` as set by torchrun), else the process runs alone. ``n_local > 1`` hosts
     several PEs in this process on one GPU. Keyword overrides use the names of the environment
-    variables (``ROCSHMEM_HEAP_SIZE='64M'`` ...); ``heap_size`` and ``backend`` are shorthands.
+    variables (``ROCSHMEM_HEAP_SIZE='64M'`` ...); ``heap_size`` and ``backend`` are shorthands. ``generation``
+    names the key space inside the store; by default it counts the initialisations of this process, which agrees
+    between processes that have lived through the same ones (a process that joins a running job passes the value it
+    was told, see ``parallel.elastic``).
     """
     global _init_count
     C = _C()
@@ -114,7 +117,7 @@ def init(store=None, rank: Optional[int] = None, world_size: Optional[int] = Non
                                       int(os.environ.get("MASTER_PORT", "29500")), world_size,
                                       rank == 0 and not agent_store,
                                       timeout=datetime.timedelta(seconds=timeout_s))
-        _init_count += 1
+        _init_count = _init_count + 1 if generation is None else int(generation)
         prefix = f"rocshmem_b200/{_init_count}/"
         wait = datetime.timedelta(milliseconds=timeout_ms)
 
@@ -143,6 +146,11 @@ def bootstrap_store():
     """The ``torch.distributed`` store the last multi-process ``init`` exchanged its descriptors through (``None``
     for a single process). It outlives ``finalize``, so a smaller or larger world can be initialised over it."""
     return _state.store
+
+
+def generation() -> int:
+    """The key-space number of the last multi-process ``init`` (see its ``generation`` argument)."""
+    return _init_count
 
 
 def last_init_arguments() -> dict:

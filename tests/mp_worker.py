@@ -1010,7 +1010,37 @@ def reduce_scatter_host():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (reduce_scatter_host, elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+def elastic_grow():
+    """Two ranks run; a third process joins between two steps and the world becomes three."""
+    import datetime
+    import torch.distributed as dist
+    from rocshmem_b200.parallel import elastic
+    timeout = float(os.environ.get("ROCSHMEM_TEST_TIMEOUT", "60"))
+    if RANK < 2:
+        shm.init(rank=RANK, world_size=2, heap_size="16M", backend=BACKEND, timeout_s=timeout)
+        x, y = shm.zeros(4, torch.int64), shm.zeros(4, torch.int64)
+        x.fill_(RANK + 1)
+        assert coll.reduce(y, x) == 0 and int(y.cpu()[0]) == 3
+        shm.barrier_all()
+        pe, n = elastic.grow(3)
+        assert (pe, n) == (RANK, 3)
+    else:
+        store = dist.TCPStore(os.environ["MASTER_ADDR"], int(os.environ["MASTER_PORT"]), 3, False,
+                              timeout=datetime.timedelta(seconds=timeout))
+        pe, n = elastic.join(store, 2, timeout_s=timeout, heap_size="16M", backend=BACKEND)
+        assert (pe, n) == (2, 3)
+    assert shm.my_pe() == RANK and shm.n_pes() == 3
+    x, y = shm.zeros(4, torch.int64), shm.zeros(4, torch.int64)
+    x.fill_(RANK + 1)
+    assert coll.reduce(y, x) == 0 and int(y.cpu()[0]) == 6
+    shm.putmem(x, torch.full((4,), 40 + RANK, dtype=torch.int64).to(dev()), (RANK + 1) % 3)
+    shm.barrier_all()
+    assert int(x.cpu()[0]) == 40 + (RANK - 1) % 3
+    shm.barrier_all()
+    shm.finalize()
+
+
+SCENARIOS = {f.__name__: f for f in (elastic_grow, reduce_scatter_host, elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

@@ -75,3 +75,7 @@ def test_survivors_notice_a_silent_departure_and_rebuild_the_world():
     results = run_ranks("elastic_unplanned", 3, timeout=150, env_extra={"ROCSHMEM_TEST_TIMEOUT": 6})
     assert_all_ok(results)
     assert time.time() - t0 < 120
+
+
+def test_world_grows_when_a_process_joins_between_steps():
+    assert_all_ok(run_ranks("elastic_grow", 3, timeout=180))
