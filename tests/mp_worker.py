@@ -959,10 +959,10 @@ def elastic_unplanned():
     stale = []
     while time.time() < deadline:
         mem.heartbeat()
-        stale = mem.stale(1.5)
+        stale = mem.stale(3.0)
         if stale:
             break
-        time.sleep(0.2)
+        time.sleep(0.1)
     assert stale == [1], stale
     new_pe, new_n = shrink(mem, dead=stale)
     assert (new_pe, new_n) == ({0: 0, 2: 1}[me], 2)
