@@ -1,11 +1,11 @@
-"""Editable / in-place install: ``pip install --no-build-isolation -e .`` compiles the native parts in the source
-tree (nvcc for sm_100a through ``rocshmem_b200/_build.py``, the same step as ``python -m rocshmem_b200._build``)
-and then installs the package; nothing is copied into site-packages, so the built ``.so`` files stay next to
-their sources."""
+"""``pip install --no-build-isolation [-e] .`` compiles the native parts in the source tree (nvcc for sm_100a through
+``rocshmem_b200/_build.py``, the same step as ``python -m rocshmem_b200._build``) and then installs the package.
+An editable install copies nothing, so the built ``.so`` files stay next to their sources; a regular install
+packages them (the bindings find the runtime library through ``$ORIGIN/lib``)."""
 import importlib.util
 import os
 
-from setuptools import setup
+from setuptools import Distribution, setup
 from setuptools.command.build_py import build_py
 from setuptools.command.develop import develop
 
@@ -32,4 +32,11 @@ class Develop(develop):
         super().run()
 
 
-setup(cmdclass={"build_py": BuildPy, "develop": Develop})
+class BinaryDistribution(Distribution):
+    """The package carries compiled libraries: wheels get a platform tag instead of "any"."""
+
+    def has_ext_modules(self):
+        return True
+
+
+setup(cmdclass={"build_py": BuildPy, "develop": Develop}, distclass=BinaryDistribution)
