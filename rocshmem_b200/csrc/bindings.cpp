@@ -29,6 +29,12 @@ template <typename T>
 T *ptr_of(uintptr_t v) { return reinterpret_cast<T *>(v); }
 uintptr_t addr_of(const void *p) { return reinterpret_cast<uintptr_t>(p); }
 rocshmem_team_t team_of(uintptr_t h) { return reinterpret_cast<rocshmem_team_t>(h); }
+
+// The runtime, for calls that make no sense before init: an exception instead of a null dereference.
+Runtime &live() {
+  if (!Runtime::initialized()) throw std::runtime_error("rocshmem: library is not initialised");
+  return Runtime::instance();
+}
 rocshmem_ctx_t ctx_of(uintptr_t c, uintptr_t t) { return rocshmem_ctx_t{ptr_of<void>(c), ptr_of<void>(t)}; }
 
 void check_launch(int rc, const char *what) {
@@ -96,20 +102,20 @@ PYBIND11_MODULE(_C, m) {
   m.def("is_initialized", [] { return Runtime::initialized(); });
   m.def("my_pe", [] { return host::my_pe(); });
   m.def("n_pes", [] { return host::n_pes(); });
-  m.def("n_local", [] { return Runtime::instance().n_local(); });
-  m.def("first_pe", [] { return Runtime::instance().first_pe(); });
+  m.def("n_local", [] { return live().n_local(); });
+  m.def("first_pe", [] { return live().first_pe(); });
   m.def("set_local_pe", [](int l) { rocshmemx_set_local_pe(l); });
-  m.def("is_cuda", [] { return Runtime::instance().is_cuda(); });
-  m.def("backend_name", [] { return std::string(Runtime::instance().mem().name()); });
+  m.def("is_cuda", [] { return live().is_cuda(); });
+  m.def("backend_name", [] { return std::string(live().mem().name()); });
   m.def("cuda_device_count", [] { return cuda_device_count(); });
-  m.def("nvls_available", [] { return Runtime::instance().mc_base() != nullptr; });
-  m.def("check_canaries", [] { return Runtime::instance().check_canaries(); });
-  m.def("internal_guard_offsets", [] { return Runtime::instance().layout().guards; });
+  m.def("nvls_available", [] { return live().mc_base() != nullptr; });
+  m.def("check_canaries", [] { return live().check_canaries(); });
+  m.def("internal_guard_offsets", [] { return live().layout().guards; });
   m.def("dump_stats", [] { host::dump_stats(); });
   m.def("reset_stats", [] { host::reset_stats(); });
-  m.def("device_stats", [](int local) { return Runtime::instance().read_stats(local); }, py::arg("local") = -1);
-  m.def("host_stats", [] { return Runtime::instance().host_stats(); });
-  m.def("get_error", [](int local) { return error_to_dict(Runtime::instance().read_error(local)); },
+  m.def("device_stats", [](int local) { return live().read_stats(local); }, py::arg("local") = -1);
+  m.def("host_stats", [] { return live().host_stats(); });
+  m.def("get_error", [](int local) { return error_to_dict(live().read_error(local)); },
         py::arg("local") = -1);
   m.def("clear_error", [] { rocshmemx_clear_error(); });
   m.def("set_wait_timeout_ms", [](uint64_t ms) { rocshmemx_set_wait_timeout_ms(ms); });
@@ -119,12 +125,12 @@ PYBIND11_MODULE(_C, m) {
   m.def("malloc", [](size_t bytes) { return addr_of(host::malloc(bytes)); });
   m.def("free", [](uintptr_t p) { host::free(ptr_of<void>(p)); });
   m.def("ptr", [](uintptr_t p, int pe) { return addr_of(host::ptr(ptr_of<void>(p), pe)); });
-  m.def("heap_base", [](int pe) { return addr_of(Runtime::instance().heap_base(pe)); });
-  m.def("heap_size", [] { return Runtime::instance().heap_size(); });
-  m.def("heap_stride", [] { return Runtime::instance().stride(); });
-  m.def("heap_used", [] { return Runtime::instance().heap_used(); });
-  m.def("heap_avail", [] { return Runtime::instance().heap_avail(); });
-  m.def("mc_base", [] { return addr_of(Runtime::instance().mc_base()); });
+  m.def("heap_base", [](int pe) { return addr_of(live().heap_base(pe)); });
+  m.def("heap_size", [] { return live().heap_size(); });
+  m.def("heap_stride", [] { return live().stride(); });
+  m.def("heap_used", [] { return live().heap_used(); });
+  m.def("heap_avail", [] { return live().heap_avail(); });
+  m.def("mc_base", [] { return addr_of(live().mc_base()); });
   m.def("heap_write", [](uintptr_t dst, py::bytes data) {
     std::string s = data;
     rocshmemx_heap_write(ptr_of<void>(dst), s.data(), s.size());
@@ -149,7 +155,7 @@ PYBIND11_MODULE(_C, m) {
     return host::team_translate_pe(team_of(s), pe, team_of(d));
   });
   m.def("team_sync", [](uintptr_t t) { return host::team_sync(team_of(t)); });
-  m.def("num_user_teams", [] { return Runtime::instance().num_user_teams(); });
+  m.def("num_user_teams", [] { return live().num_user_teams(); });
   m.def("ctx_create", [](int64_t options) {
     rocshmem_ctx_t c{nullptr, nullptr};
     int rc = host::ctx_create(options, &c);
@@ -275,18 +281,18 @@ PYBIND11_MODULE(_C, m) {
 
   // ---- proxy -----------------------------------------------------------------------------------------------
   m.def("proxy_running", [] {
-    Proxy *p = Runtime::instance().proxy();
+    Proxy *p = live().proxy();
     return p && p->running();
   });
   m.def("proxy_start", [] {
     // Test hook: start a proxy on any backend (the CPU backend exercises the ring protocol).
     static std::unique_ptr<Proxy> extra;
-    if (!Runtime::instance().proxy()) {
-      extra = std::make_unique<Proxy>(&Runtime::instance());
+    if (!live().proxy()) {
+      extra = std::make_unique<Proxy>(&live());
       extra->start();
       return addr_of(extra.get());
     }
-    return addr_of(Runtime::instance().proxy());
+    return addr_of(live().proxy());
   });
   m.def("proxy_stop", [](uintptr_t p) { ptr_of<Proxy>(p)->stop(); });
   m.def("proxy_submit", [](uintptr_t p, unsigned type, int pe, uintptr_t dst, uintptr_t src, uint64_t size,
@@ -314,7 +320,7 @@ PYBIND11_MODULE(_C, m) {
      py::arg("cond"), py::arg("op"), py::arg("dtype_size"), py::arg("blocking"), py::arg("timeout_ms"),
      py::arg("team_slot") = 0);
   m.def("team_slot", [](uintptr_t t) {
-    HostTeam *ht = Runtime::instance().team_from_handle(team_of(t));
+    HostTeam *ht = live().team_from_handle(team_of(t));
     return ht ? ht->slot : -1;
   });
   m.def("proxy_inject_drop", [](uintptr_t p, int n) { ptr_of<Proxy>(p)->inject_drop(n); });

@@ -263,3 +263,14 @@ def test_reduce_scatter_argument_checks_and_allgather_alias(shm4):
     gat = shm.zeros(n * 5, torch.float32)
     assert coll.allgather(gat, src[:5]) == 0
     assert torch.equal(shm.local_view(gat, 2).view(n, 5)[3], data[3][:5])
+
+
+def test_calls_before_init_raise_instead_of_crashing(fresh_runtime):
+    shm = fresh_runtime
+    C = shm.runtime._C()
+    for call in (shm.get_error, shm.heap_info, shm.is_cuda, shm.describe_error, shm.barrier_all, lambda: shm.zeros(4),
+                 lambda: C.device_stats(0), C.check_canaries, C.num_user_teams, C.proxy_start):
+        with pytest.raises(RuntimeError, match="not initialised"):
+            call()
+    assert shm.my_pe() == 0 and shm.n_pes() >= 1          # identity works before init, as in the reference
+    shm.finalize()                                        # a no-op
