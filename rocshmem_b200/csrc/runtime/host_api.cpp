@@ -400,12 +400,19 @@ int team_sync(rocshmem_team_t team) {
   return r.ops().barrier(r.default_ctx(), host_team(team), true);
 }
 
+// An unknown comparison would never be satisfied: refuse it instead of waiting for the time-out.
+static void check_cmp(int cmp) {
+  if (cmp < ROCSHMEM_CMP_EQ || cmp > ROCSHMEM_CMP_LE) throw std::invalid_argument("rocshmem: unknown comparison operator");
+}
+
 int wait_until(void *ivar, int dtype, int cmp, uint64_t value) {
+  check_cmp(cmp);
   rt().count(ROCSHMEM_STAT_WAIT);
   return rt().ops().wait_until(ivar, static_cast<DType>(dtype), cmp, value);
 }
 
 int test(void *ivar, int dtype, int cmp, uint64_t value) {
+  check_cmp(cmp);
   rt().count(ROCSHMEM_STAT_TEST);
   return rt().ops().test(ivar, static_cast<DType>(dtype), cmp, value);
 }
@@ -424,7 +431,9 @@ struct Poller {
       : r(rt()), base(static_cast<char *>(ivars)), esz(dtype_size(static_cast<DType>(dtype))),
         t(static_cast<DType>(dtype)), cmp(cmp_), values(v), vector(vec),
         deadline(std::chrono::steady_clock::now() +
-                 std::chrono::milliseconds(rt().config().wait_timeout_ms)) {}
+                 std::chrono::milliseconds(rt().config().wait_timeout_ms)) {
+    check_cmp(cmp_);
+  }
   bool ready(size_t i) { return r.ops().test(base + i * esz, t, cmp, vector ? values[i] : values[0]) != 0; }
   bool expired() const { return std::chrono::steady_clock::now() > deadline; }
 };

@@ -274,3 +274,15 @@ def test_calls_before_init_raise_instead_of_crashing(fresh_runtime):
             call()
     assert shm.my_pe() == 0 and shm.n_pes() >= 1          # identity works before init, as in the reference
     shm.finalize()                                        # a no-op
+
+
+def test_unknown_comparison_is_refused_at_once(shm4):
+    shm = shm4
+    flags = shm.zeros(4, torch.int64)
+    import time
+    t0 = time.time()
+    for call in (lambda: shm.wait_until(flags, 99, 1), lambda: shm.test(flags, -1, 1),
+                 lambda: shm.wait_until_any(flags, 7, [1, 1, 1, 1]), lambda: shm.wait_until_all(flags, 6, [0, 0, 0, 0])):
+        with pytest.raises(ValueError, match="comparison"):
+            call()
+    assert time.time() - t0 < 2          # not after a time-out
