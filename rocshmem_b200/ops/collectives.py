@@ -42,24 +42,30 @@ def _stream(stream) -> int:
 
 def broadcast(dest: torch.Tensor, source: torch.Tensor, root: int, team: Optional[rt.Team] = None) -> int:
     """``dest`` on every member except the root receives the root's ``source``."""
+    _check(dest, source, source.numel(), "broadcast")
     return rt._C().broadcast(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source), root)
 
 
 def reduce(dest: torch.Tensor, source: torch.Tensor, op: int = rt.OP_SUM,
            team: Optional[rt.Team] = None) -> int:
     """All-reduce: every member's ``dest`` receives the element-wise reduction of all ``source``s."""
+    _check(dest, source, source.numel(), "reduce")
     return rt._C().reduce(_team(team), dest.data_ptr(), source.data_ptr(), source.numel(),
                           rt.dtype_code(source.dtype), op)
 
 
 def fcollect(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None) -> int:
     """All-gather: member *i*'s ``source`` lands at ``dest[i * source.numel():]`` on every member."""
+    _check(dest, source, source.numel() * (team or rt.team_world()).n_pes(), "fcollect")
     return rt._C().fcollect(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source))
 
 
 def alltoall(dest: torch.Tensor, source: torch.Tensor, team: Optional[rt.Team] = None) -> int:
     """Member *i* sends chunk *j* of ``source`` to member *j*, which stores it as chunk *i* of ``dest``."""
     n = (team or rt.team_world()).n_pes()
+    if source.numel() % n:
+        raise ValueError(f"alltoall: source has {source.numel()} elements, not a multiple of {n} members")
+    _check(dest, source, source.numel(), "alltoall")
     return rt._C().alltoall(_team(team), dest.data_ptr(), source.data_ptr(), rt._nbytes(source) // n)
 
 
