@@ -215,9 +215,29 @@ void dump_stats() {
 
 void reset_stats() { rt().reset_stats(); }
 
-void *malloc(size_t bytes) { return rt().malloc(bytes); }
+// ROCSHMEM_DEBUG=2: one line on stderr per collective management call (heap, teams, contexts), in the spirit of
+// the reference's DPRINTF tracing (src/util.hpp:51-71). Data-path calls are not traced.
+#define ROCSHMEM_TRACE(r, ...)                                        \
+  do {                                                                \
+    if ((r).config().debug >= 2) {                                    \
+      std::fprintf(stderr, "[rocshmem pe %d] ", (r).my_pe());         \
+      std::fprintf(stderr, __VA_ARGS__);                              \
+      std::fputc('\n', stderr);                                       \
+    }                                                                 \
+  } while (0)
 
-void free(void *p) { rt().free(p); }
+void *malloc(size_t bytes) {
+  Runtime &r = rt();
+  void *p = r.malloc(bytes);
+  ROCSHMEM_TRACE(r, "malloc(%zu) = %p, %zu bytes of the heap in use", bytes, p, r.heap_used());
+  return p;
+}
+
+void free(void *p) {
+  Runtime &r = rt();
+  r.free(p);
+  ROCSHMEM_TRACE(r, "free(%p), %zu bytes of the heap in use", p, r.heap_used());
+}
 
 void *ptr(const void *p, int pe) {
   Runtime &r = rt();
@@ -227,6 +247,7 @@ void *ptr(const void *p, int pe) {
 
 int ctx_create(int64_t options, rocshmem_ctx_t *ctx) {
   HostCtx *c = rt().ctx_create(options, rt().team_world());
+  ROCSHMEM_TRACE(rt(), "ctx_create(options %lld) = %p", static_cast<long long>(options), static_cast<void *>(c));
   if (!c) return -1;
   ctx->ctx_opaque = c;
   ctx->team_opaque = c->team->dev;
@@ -276,12 +297,16 @@ int team_split_strided(rocshmem_team_t parent, int start, int stride, int size,
     *new_team = nullptr;
     return -1;
   }
-  return rt().team_split_strided(p, start, stride, size, new_team);
+  int rc = rt().team_split_strided(p, start, stride, size, new_team);
+  ROCSHMEM_TRACE(rt(), "team_split_strided(start %d, stride %d, size %d) = %d, team %p", start, stride, size, rc,
+                 static_cast<void *>(*new_team));
+  return rc;
 }
 
 void team_destroy(rocshmem_team_t team) {
   if (team == nullptr) return;
   HostTeam *t = rt().team_from_handle(team);
+  ROCSHMEM_TRACE(rt(), "team_destroy(%p)%s", static_cast<void *>(team), t ? "" : ": unknown handle");
   if (t) rt().team_destroy(t);
 }
 

@@ -146,3 +146,21 @@ def test_matrix_runner_lists_its_cases_and_parses_driver_tables(capsys):
                        "        1048576         10          2.005            523.000             498753", "noise 1 2 3 4"])
     rows = list(rm.parse_rows(table))
     assert rows == [(8, 10, 0.31, 0.026, 3225806.0), (1048576, 10, 2.005, 523.0, 498753.0)]
+
+
+def test_debug_level_two_traces_management_calls():
+    import os
+    import subprocess
+    import sys
+    code = ("import rocshmem_b200 as shm, torch\n"
+            "shm.init(n_local=2, heap_size='4M', backend='host')\n"
+            "x = shm.zeros(100, torch.float32)\n"
+            "t = shm.team_world().split_strided(0, 1, 1)\n"
+            "t.destroy(); shm.free(x); shm.finalize()\n")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    for level, expect in (("2", True), ("0", False)):
+        out = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, ROCSHMEM_DEBUG=level, PYTHONPATH=root),
+                             capture_output=True, text=True, timeout=120)
+        assert out.returncode == 0, out.stderr[-2000:]
+        traced = "malloc(400)" in out.stderr and "team_split_strided(start 0, stride 1, size 1) = 0" in out.stderr
+        assert traced == expect, out.stderr[-2000:]
