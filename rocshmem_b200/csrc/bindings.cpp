@@ -10,6 +10,7 @@
 // Bindings of the MoE and GEMM kernels live beside those kernels' launchers.
 namespace rocshmem { namespace kernels { void bind_ep(pybind11::module_ &m); void bind_gemm(pybind11::module_ &m); } }
 #include "rocshmem/coalesce.h"
+#include "rocshmem/rocshmem_debug.hpp"
 #include "rocshmem/rocshmem_host.h"
 #include "rocshmem/slab.h"
 #include "runtime/allocator.hpp"
@@ -346,6 +347,9 @@ PYBIND11_MODULE(_C, m) {
   });
   m.def("proxy_set_coalesce", [](uintptr_t p, bool on) { ptr_of<Proxy>(p)->set_coalesce(on); });
   m.def("proxy_merged", [](uintptr_t p) { return ptr_of<Proxy>(p)->merged(); });
+  m.def("proxy_describe_command", [](uintptr_t p, unsigned i) { return ptr_of<Proxy>(p)->describe_command(i); });
+  m.def("proxy_describe_completion", [](uintptr_t p, unsigned i) { return ptr_of<Proxy>(p)->describe_completion(i); });
+  m.def("debug_print_ring", [](int first, int count) { live(); debug_print_ring(first, count); });
   // The lane-mask arithmetic of the warp coalescer, evaluated for every lane of one warp.
   m.def("coalesce_warp_plan", [](unsigned active, std::vector<std::tuple<int, uint64_t, uint64_t, uint64_t>> msgs) {
     if (msgs.size() != 32) throw std::invalid_argument("coalesce_warp_plan wants 32 lane messages");

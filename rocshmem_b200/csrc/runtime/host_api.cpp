@@ -12,6 +12,8 @@
 #include <vector>
 
 #include "host_ops.hpp"
+#include "proxy.hpp"
+#include "rocshmem/rocshmem_debug.hpp"
 #include "rocshmem/rocshmem_host.h"
 #include "rocshmem/slab.h"
 #include "runtime.hpp"
@@ -616,6 +618,34 @@ int reduce_active_set(rocshmem_ctx_t ctx, void *dest, const void *source, size_t
 
 void rocshmemx_set_local_pe(int local_index) { rt().set_current_local(local_index); }
 int rocshmemx_n_local_pes() { return rt().n_local(); }
+
+void debug_print_ring(int first, int count) {
+  Runtime &r = rt();
+  Proxy *p = r.proxy();
+  if (p == nullptr || !p->running()) {
+    std::fprintf(stderr, "[rocshmem pe %d] no reverse-offload ring in this process (ROCSHMEM_USE_PROXY is off)\n", r.my_pe());
+    return;
+  }
+  for (int i = 0; i < count; ++i) {
+    std::fprintf(stderr, "[rocshmem pe %d] %s\n", r.my_pe(), p->describe_command(static_cast<unsigned>(first + i)).c_str());
+  }
+}
+
+void debug_print_sq(int dest_pe, int src_wg, int index_wqe) {
+  std::fprintf(stderr, "[rocshmem pe %d] command queue entry (asked for pe %d, block %d):\n", rt().my_pe(), dest_pe, src_wg);
+  debug_print_ring(index_wqe, 1);
+}
+
+void debug_print_cq(int dest_pe, int src_wg, int cqe_index) {
+  Runtime &r = rt();
+  Proxy *p = r.proxy();
+  std::fprintf(stderr, "[rocshmem pe %d] completion queue entry (asked for pe %d, block %d):\n", r.my_pe(), dest_pe, src_wg);
+  if (p == nullptr || !p->running()) {
+    std::fprintf(stderr, "[rocshmem pe %d] no reverse-offload ring in this process (ROCSHMEM_USE_PROXY is off)\n", r.my_pe());
+    return;
+  }
+  std::fprintf(stderr, "[rocshmem pe %d] %s\n", r.my_pe(), p->describe_completion(static_cast<unsigned>(cqe_index)).c_str());
+}
 rocshmem_error_record rocshmemx_get_error() { return rt().read_error(); }
 void rocshmemx_clear_error() { rt().clear_error(); }
 void rocshmemx_set_wait_timeout_ms(uint64_t ms) { rt().set_wait_timeout_ms(ms); }

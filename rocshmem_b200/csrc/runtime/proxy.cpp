@@ -3,6 +3,7 @@
 #include <cuda_runtime_api.h>
 
 #include <chrono>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <stdexcept>
@@ -257,6 +258,36 @@ void Proxy::execute(rocshmem_proxy_cmd &cmd, uint64_t) {
     __atomic_store_n(const_cast<unsigned long long *>(&ring_.fetched[cmd.status_slot]), fetched,
                      __ATOMIC_RELAXED);
   }
+}
+
+std::string Proxy::describe_command(unsigned index) const {
+  static const char *const states[] = {"free", "published", "claimed", "cancelled"};
+  static const char *const ops[] = {"nop", "put", "get", "amo_fadd", "amo_cas", "quiet", "barrier", "signal",
+                                    "fence", "broadcast", "reduce", "fcollect", "alltoall", "p"};
+  if (ring_.cmds == nullptr || ring_.capacity == 0) return "no ring";
+  const unsigned i = index & (ring_.capacity - 1);
+  const volatile rocshmem_proxy_cmd &c = ring_.cmds[i];
+  const unsigned valid = c.valid, type = c.type;
+  char line[320];
+  std::snprintf(line, sizeof(line),
+                "slot %u of %u: %s, op %s (%u), pe %d, dst 0x%llx, src 0x%llx, size %llu, cond %llu, sub-op %u, "
+                "element %u bytes, team slot %llu, completion slot %d",
+                i, ring_.capacity, valid < 4 ? states[valid] : "corrupt", type < 14 ? ops[type] : "unknown", type, c.pe,
+                c.dst, c.src, c.size, c.cond, c.op, c.dtype_size, c.team_slot, c.status_slot);
+  return line;
+}
+
+std::string Proxy::describe_completion(unsigned index) const {
+  if (ring_.status == nullptr || ring_.n_status == 0) return "no ring";
+  const unsigned i = index % ring_.n_status;
+  char line[200];
+  std::snprintf(line, sizeof(line),
+                "completion %u of %u: last acknowledged command %llu (0: none yet), fetched value %llu (0x%llx); "
+                "consumer has retired %llu commands",
+                i, ring_.n_status, static_cast<unsigned long long>(ring_.status[i]),
+                static_cast<unsigned long long>(ring_.fetched[i]), static_cast<unsigned long long>(ring_.fetched[i]),
+                static_cast<unsigned long long>(ring_.read_index ? *ring_.read_index : 0));
+  return line;
 }
 
 int Proxy::submit(const rocshmem_proxy_cmd &in, bool blocking, uint64_t *fetched, uint64_t timeout_ms) {

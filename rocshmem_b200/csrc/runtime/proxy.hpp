@@ -17,6 +17,7 @@
 
 #include <atomic>
 #include <cstdint>
+#include <string>
 #include <thread>
 
 #include "rocshmem/rocshmem_common.h"
@@ -50,6 +51,11 @@ class Proxy {
   uint64_t executed() const { return executed_.load(); }
   uint64_t dropped() const { return dropped_count_.load(); }
   const rocshmem_proxy_ring &ring() const { return ring_; }
+
+  // One line of text about a command slot / a completion slot (index taken modulo the array's size), for the
+  // debug dump. Reads the ring without taking part in its protocol.
+  std::string describe_command(unsigned index) const;
+  std::string describe_completion(unsigned index) const;
 
  private:
   void run();

@@ -3,7 +3,16 @@
 // many-ctx). Compiled with g++ against the runtime library and run as several processes on the CPU
 // shared-memory backend (ROCSHMEM_BACKEND=host, rendezvous through ROCSHMEM_BOOTSTRAP_DIR), so the C++ surface of
 // the host API is exercised end to end without a GPU. Prints "PASS" on every PE; any failed check exits with 1.
-#include <rocshmem/rocshmem.h>
+// The reference's header names: every one of them must be enough on its own and they must combine.
+#include <rocshmem/rocshmem.hpp>
+#include <rocshmem/rocshmem_AMO.hpp>
+#include <rocshmem/rocshmem_COLL.hpp>
+#include <rocshmem/rocshmem_P2P_SYNC.hpp>
+#include <rocshmem/rocshmem_RMA.hpp>
+#include <rocshmem/rocshmem_RMA_X.hpp>
+#include <rocshmem/rocshmem_SIG_OP.hpp>
+#include <rocshmem/rocshmem_common.hpp>
+#include <rocshmem/rocshmem_debug.hpp>
 
 #include <cstdio>
 #include <cstdlib>
@@ -229,6 +238,12 @@ int main() {
   for (void *p : {static_cast<void *>(dst), static_cast<void *>(src), static_cast<void *>(flag), static_cast<void *>(bits),
                   static_cast<void *>(ctr), static_cast<void *>(scratch), static_cast<void *>(b), static_cast<void *>(a)}) {
     rocshmem_free(p);
+  }
+  // No proxy thread on this backend: the queue dump says so instead of failing.
+  if (rocshmem_my_pe() == 0) {
+    debug_print_ring(0, 2);
+    debug_print_sq(1, 0, 0);
+    debug_print_cq(1, 0, 0);
   }
   rocshmem_finalize();
   std::printf("[pe %d] PASS\n", me);

@@ -127,6 +127,10 @@ def test_ring_consumer_executes_a_run_of_puts_as_one_transfer(fresh_runtime):
             t.join()
         assert rcs == [0, 0]
         assert torch.equal(shm.local_view(back, 0)[:128], torch.arange(128) + 1000)
+        # the debug dump of a slot names its state and operation; blocking commands leave their completion behind
+        text = C.proxy_describe_command(p, 0)
+        assert text.startswith("slot 0 of ") and ("op put" in text or "op get" in text or "op amo_fadd" in text), text
+        assert "completion 0 of" in C.proxy_describe_completion(p, 0)
         # with merging off nothing is merged
         C.proxy_set_coalesce(p, False)
         before = C.proxy_merged(p)
