@@ -384,7 +384,9 @@ broadcast_nvls_kernel(rocshmem_team_t team, char *dest_arg, const char *source_a
   int half = 0;
   for (size_t base = 0; base < bytes; base += sub_bytes, half ^= 1) {
     const size_t len = bytes - base < sub_bytes ? bytes - base : sub_bytes;  // a multiple of 16 (launcher)
-    const size_t nvec = len / 16, per = (nvec + gridDim.x - 1) / gridDim.x;
+    // Shares are cut from the full sub-chunk size, also for a shorter last sub-chunk: block b then only ever touches
+    // bytes of a staging half that the blocks b of the other members touch, the blocks it synchronises with.
+    const size_t nvec = len / 16, per = (sub_bytes / 16 + gridDim.x - 1) / gridDim.x;
     size_t lo = per * blockIdx.x, hi = lo + per;
     if (lo > nvec) lo = nvec;
     if (hi > nvec) hi = nvec;
