@@ -12,6 +12,7 @@
 #include <rocshmem/rocshmem_RMA_X.hpp>
 #include <rocshmem/rocshmem_SIG_OP.hpp>
 #include <rocshmem/rocshmem_common.hpp>
+#include <rocshmem/rocshmem_config.h>
 #include <rocshmem/rocshmem_debug.hpp>
 
 #include <cstdio>
@@ -45,6 +46,12 @@ static std::vector<T> fetch(const T *sym, size_t n) {
   rocshmemx_heap_read(h.data(), sym, n * sizeof(T));
   return h;
 }
+
+static_assert(ROCSHMEM_HAS_PEER_MAPPING && ROCSHMEM_HAS_REVERSE_OFFLOAD && !ROCSHMEM_HAS_NIC_BACKEND,
+              "the configuration header describes the one build there is");
+#ifdef USE_IPC
+#error "the reference's bare option names are opt-in"
+#endif
 
 int main() {
   // identity before init (the reference's programs pick their GPU this way)

@@ -164,3 +164,14 @@ def test_debug_level_two_traces_management_calls():
         assert out.returncode == 0, out.stderr[-2000:]
         traced = "malloc(400)" in out.stderr and "team_split_strided(start 0, stride 1, size 1) = 0" in out.stderr
         assert traced == expect, out.stderr[-2000:]
+
+
+def test_configuration_header_carries_the_package_version():
+    import os
+    import re
+    import rocshmem_b200
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    text = open(os.path.join(root, "rocshmem_b200", "csrc", "include", "rocshmem", "rocshmem_config.h")).read()
+    parts = [re.search(rf"#define ROCSHMEM_B200_VERSION_{k} (\d+)", text).group(1) for k in ("MAJOR", "MINOR", "PATCH")]
+    assert ".".join(parts) == rocshmem_b200.__version__
+    assert f'"{rocshmem_b200.__version__}"' in text
