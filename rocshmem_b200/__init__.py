@@ -9,7 +9,7 @@ from .runtime import (  # noqa: F401
     AMO_FETCH, AMO_OR, AMO_SWAP, AMO_XOR, CMP_EQ, CMP_GE, CMP_GT, CMP_LE, CMP_LT, CMP_NE, CTX_NOSTORE,
     ERROR, OP_AND, OP_MAX, OP_MIN, OP_OR, OP_PROD, OP_SUM, OP_XOR, SIGNAL_ADD, SIGNAL_SET, SUCCESS,
     Context, Team, atomic, atomic_compare_swap, atomic_fetch, atomic_fetch_add, atomic_swap,
-    barrier_all, clear_error, describe_error, device, empty, fence, finalize, free, free_all, get_error, getmem, heap_info, init,
+    barrier_all, clear_error, debug_print_ring, describe_error, device, empty, fence, finalize, free, free_all, get_error, getmem, heap_info, init,
     is_cuda, is_initialized, is_symmetric, require_symmetric, local_view, my_pe, n_local_pes, n_pes, nvls_available, peer_address,
     putmem, quiet, set_local_pe, set_wait_timeout_ms, sync_all, team_world, tensor_from_address, test,
     wait_until, wait_until_all, wait_until_any, wait_until_some, zeros,

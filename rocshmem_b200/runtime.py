@@ -557,6 +557,13 @@ ERROR_SITES = {
 }
 
 
+def debug_print_ring(first: int = 0, count: int = 8) -> None:
+    """Print ``count`` command slots of the reverse-offload ring, starting at ``first``, to standard error: state,
+    operation, PE, addresses, size. Says so in one line when the process runs no proxy thread
+    (``ROCSHMEM_USE_PROXY`` off). Counterpart of ``debug_print_sq`` (include/rocshmem/rocshmem_debug.hpp:28-30)."""
+    _C().debug_print_ring(int(first), int(count))
+
+
 def describe_error(err: Optional[dict] = None) -> str:
     """One line of plain words for an error record (the current one of this PE by default)."""
     err = get_error() if err is None else err

@@ -175,3 +175,13 @@ def test_configuration_header_carries_the_package_version():
     parts = [re.search(rf"#define ROCSHMEM_B200_VERSION_{k} (\d+)", text).group(1) for k in ("MAJOR", "MINOR", "PATCH")]
     assert ".".join(parts) == rocshmem_b200.__version__
     assert f'"{rocshmem_b200.__version__}"' in text
+
+
+def test_ring_dump_without_a_proxy_says_so(fresh_runtime, capfd):
+    shm = fresh_runtime
+    shm.init(n_local=1, heap_size="1M", backend="host")
+    try:
+        shm.debug_print_ring(0, 2)
+    finally:
+        shm.finalize()
+    assert "no reverse-offload ring in this process" in capfd.readouterr().err
