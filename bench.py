@@ -10,11 +10,13 @@ synthetic. The reported value is tokens per second for the whole job (sum over r
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29511 bench.py --gpus 8 --steps 20 --warmup 5
 
-Timing: CUDA events on the launching stream around each step (dispatch + combine), L2 flushed
-between steps by writing a 512 MiB buffer (outside the timed events), barrier + synchronise on both
-sides of the measurement, maximum over ranks. The "e2e" figure repeats the measurement through the
-public API with the step's inputs copied from pinned host memory and a result checksum read back
-every step.
+A step is R dispatch+combine pairs (R is chosen so that a step lasts about 3 ms and is reported as
+``pairs_per_step``). Timing: CUDA events on the launching stream around each pair, L2 flushed before every
+pair by writing a 512 MiB buffer (outside the timed events), barrier + synchronise on both sides of the
+measurement, maximum over ranks. One pair is checked on every rank before anything is timed (``verified``).
+The same workload is then run over NCCL all-to-all (``baseline``; ``vs_baseline`` is ours / NCCL). The
+"e2e" figure repeats the measurement through the public API with the step's inputs copied from pinned
+host memory and a result checksum read back every step.
 """
 from __future__ import annotations
 
@@ -106,14 +108,33 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def h2d_ceiling_gbs(torch, host, dev, reps: int = 5) -> float:
+    """Plain pinned-host -> device copy rate of this rank (GB/s), the ceiling of the end-to-end figure."""
+    dst = torch.empty_like(host, device=dev)
+    for _ in range(2):
+        dst.copy_(host, non_blocking=True)
+    torch.cuda.synchronize()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for _ in range(reps):
+        dst.copy_(host, non_blocking=True)
+    b.record()
+    torch.cuda.synchronize()
+    return host.numel() * host.element_size() * reps / (a.elapsed_time(b) * 1e-3) / 1e9
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=200)
-    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=TOKENS)
     ap.add_argument("--layout", default="compact", choices=["compact", "slotted"])
+    ap.add_argument("--low-latency", action="store_true", help="low-latency kernels (use with --tokens 128)")
+    ap.add_argument("--repeats", type=int, default=0,
+                    help="dispatch+combine pairs per step (0: as many as make a step last about 3 ms)")
+    ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL all-to-all form of the workload")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -126,6 +147,7 @@ def main() -> None:
     import rocshmem_b200 as shm
     from rocshmem_b200.ops import collectives as coll
     from rocshmem_b200.ops import moe
+    from rocshmem_b200.utils import numa
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -133,19 +155,29 @@ def main() -> None:
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
     torch.cuda.set_device(local_rank)
-    if world > 1:
-        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        dist.init_process_group("gloo")  # control plane only; the data plane is the symmetric heap
+    # Pinned input buffers on the GPU's own NUMA node: otherwise the ranks' host-to-device copies share one
+    # socket's memory and the inter-socket link.
+    numa_info = numa.bind_to_device_node(local_rank)
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    if "MASTER_PORT" not in os.environ:
+        import socket
+        with socket.socket() as sock:                # single process: any free port will do
+            sock.bind(("127.0.0.1", 0))
+            os.environ["MASTER_PORT"] = str(sock.getsockname()[1])
+    # gloo is the control plane of the symmetric heap's bootstrap; NCCL carries only the baseline's all-to-all.
+    dist.init_process_group("cpu:gloo,cuda:nccl", rank=rank, world_size=world,
+                            device_id=torch.device("cuda", local_rank))
     T = args.tokens
     heap = 6 << 30
     shm.init(heap_size=heap, device=local_rank)
     dev = shm.device()
-    d = moe.EpDispatcher(EXPERTS, TOPK, HIDDEN, T, layout=args.layout)
+    d = moe.EpDispatcher(EXPERTS, TOPK, HIDDEN, T, layout=args.layout, low_latency=args.low_latency)
     epr = EXPERTS // world
 
     g = torch.Generator().manual_seed(1234 + rank)
     x_host = torch.randn(T, HIDDEN, generator=g).to(torch.bfloat16).pin_memory()
-    idx_cpu, w_cpu = moe.make_routing(T, EXPERTS, TOPK, 99 + rank)
+    routes = [moe.make_routing(T, EXPERTS, TOPK, 99 + r) for r in range(world)]
+    idx_cpu, w_cpu = routes[rank]
     idx_host, w_host = idx_cpu.pin_memory(), w_cpu.pin_memory()
     x = x_host.to(dev)
     idx = idx_host.to(dev)
@@ -164,51 +196,127 @@ def main() -> None:
 
     stream = torch.cuda.current_stream()
 
-    def step():
-        res = d.dispatch(x, idx, w)
-        # "Experts": the combine input has to exist as bf16 rows; the benchmark measures the two
-        # collectives, so the rows that arrived are reused as-is (any bf16 content has the same cost).
-        d.combine(y, idx, w, T, weighted=True, out=out)
-        return res
-
     # y gets deterministic content once (dequantised rows of a first dispatch) so combine sums real data.
     res = d.dispatch(x, idx, w)
     torch.cuda.synchronize()
-    n_rows = res.num_rows()
-    y[:n_rows].copy_(moe.fp8_dequantize_1x128(res.recv_x[:n_rows], res.recv_scales[:n_rows]))
+    info = res.recv_info.cpu().tolist()
+    n_rows = info[0]
+    for s in range(world):
+        first, count = info[1 + s], info[1 + world + s]
+        if count:
+            y[first:first + count].copy_(moe.fp8_dequantize_1x128(res.recv_x[first:first + count],
+                                                                  res.recv_scales[first:first + count]))
     torch.cuda.synchronize()
     shm.barrier_all()
+
+    # ---- correctness of one step, on every rank, before anything is timed ---------------------------------------
+    # Bookkeeping against the reference routing of all ranks (their gating is rebuilt from the seeds), and the
+    # combine output against the fp32 weighted sum of the de-quantised rows (the gate weights sum to one, so
+    # that sum is the de-quantised token itself).
+    want_rows = moe.ref_dispatch([r[0] for r in routes], world, EXPERTS)[rank]
+    bad = 0.0
+    if n_rows != len(want_rows):
+        bad = 1.0
+    meta = res.recv_meta.cpu()
+    for s in range(world):
+        first, count = info[1 + s], info[1 + world + s]
+        toks = sorted(meta[first:first + count, 16].tolist())
+        if toks != [t for ss, t in want_rows if ss == s]:
+            bad = 1.0
+    d.combine(y, idx, w, T, weighted=True, out=out)
+    torch.cuda.synchronize()
+    xf = x.float()
+    if (out.float() - xf).abs().max().item() > 0.08 * xf.abs().max().item() + 2e-2:
+        bad = 1.0
+    del xf
+    verified = max_over_ranks([bad])[0] == 0.0
+    shm.barrier_all()
+
+    def pair(events=None):
+        if events:
+            events[0].record(stream)
+        d.dispatch(x, idx, w)
+        if events:
+            events[1].record(stream)
+        d.combine(y, idx, w, T, weighted=True, out=out)
+        if events:
+            events[2].record(stream)
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
     for _ in range(args.warmup):
         flush.fill_(1)
-        step()
+        pair()
     torch.cuda.synchronize()
+    # Pairs per step: enough for a step of about 3 ms, so that the timed region is long enough for the clock
+    # samples to mean something. Every rank derives the same number from the maximum over ranks.
+    if args.repeats > 0:
+        R = args.repeats
+    else:
+        probe = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+        flush.fill_(2)
+        pair(probe)
+        torch.cuda.synchronize()
+        pair_ms = max_over_ranks([probe[0].elapsed_time(probe[2])])[0]
+        R = int(max(1, min(64, round(3.0 / max(pair_ms, 1e-3)))))
     shm.barrier_all()
-    ev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    ev = [[[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(R)] for _ in range(args.steps)]
     launches_before = d.kernel_launches
     torch.cuda.synchronize()
     shm.barrier_all()
     for i in range(args.steps):
-        flush.fill_(i & 0xff)            # L2 flush, outside the timed events
-        ev[i][0].record(stream)
-        d.dispatch(x, idx, w)
-        ev[i][1].record(stream)
-        d.combine(y, idx, w, T, weighted=True, out=out)
-        ev[i][2].record(stream)
+        for r in range(R):
+            flush.fill_((i + r) & 0xff)      # L2 flush, outside the timed events
+            pair(ev[i][r])
     torch.cuda.synchronize()
     shm.barrier_all()
     phases = d.phase_times_us()
     launches = d.kernel_launches - launches_before
-    disp_ms = sum(e[0].elapsed_time(e[1]) for e in ev)
-    comb_ms = sum(e[1].elapsed_time(e[2]) for e in ev)
+    disp_ms = sum(e[0].elapsed_time(e[1]) for step in ev for e in step)
+    comb_ms = sum(e[1].elapsed_time(e[2]) for step in ev for e in step)
     total_ms, disp_ms, comb_ms = max_over_ranks([disp_ms + comb_ms, disp_ms, comb_ms])
     ms_per_step = total_ms / args.steps
+    pairs = args.steps * R
 
-    # ---- end to end through the public API: pinned-host inputs in, checksum out, every step -------------
+    # ---- the same workload over NCCL all-to-all (the library baseline), same tensors, same timing rules -----------
+    base = None
+    if not args.no_baseline:
+        from rocshmem_b200.baselines.ep import NcclEpDispatcher
+        nd = NcclEpDispatcher(EXPERTS, TOPK, HIDDEN)
+        nres = nd.dispatch(x, idx, w)
+        ny = moe.fp8_dequantize_1x128(nres.recv_x, nres.recv_scales) if nres.recv_x.shape[0] else \
+            torch.empty((0, HIDDEN), dtype=torch.bfloat16, device=dev)
+        nout = nd.combine(ny, idx, w, T)
+        base_ok = (nout.float() - x.float()).abs().max().item() <= 0.08 * x.float().abs().max().item() + 2e-2
+        for _ in range(3):
+            flush.fill_(3)
+            nd.dispatch(x, idx, w)
+            nd.combine(ny, idx, w, T)
+        torch.cuda.synchronize()
+        dist.barrier()
+        nsteps = max(3, min(pairs, 40))
+        nev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(nsteps)]
+        for i in range(nsteps):
+            flush.fill_(i & 0xff)
+            nev[i][0].record(stream)
+            nd.dispatch(x, idx, w)
+            nev[i][1].record(stream)
+            nd.combine(ny, idx, w, T)
+            nev[i][2].record(stream)
+        torch.cuda.synchronize()
+        dist.barrier()
+        bd = sum(e[0].elapsed_time(e[1]) for e in nev)
+        bc = sum(e[1].elapsed_time(e[2]) for e in nev)
+        btot, bd, bc = max_over_ranks([bd + bc, bd, bc])
+        base = {"impl": "NCCL all_to_all_single (torch.distributed) + torch kernels", "pairs_timed": nsteps,
+                "ms_per_pair": btot / nsteps, "dispatch_us": bd / nsteps * 1e3, "combine_us": bc / nsteps * 1e3,
+                "value": world * T / (btot / nsteps * 1e-3), "verified": bool(base_ok)}
+        del nd, nres, ny, nout
+
+    # ---- end to end through the public API: pinned-host inputs in, result checksum out, every step ----------------
     h2d_bytes = x_host.numel() * 2 + idx_host.numel() * 4 + w_host.numel() * 4
+    h2d_gbs = max_over_ranks([-h2d_ceiling_gbs(torch, x_host, dev)])[0] * -1.0   # slowest rank
     checksum_host = torch.zeros(1, dtype=torch.float32).pin_memory()
     # Two sets of device-side inputs: the copy of step i + 1 (on its own stream) overlaps the kernels of step i,
     # as an input pipeline would; every step's copy and every step's result read are inside the timed region.
@@ -241,11 +349,12 @@ def main() -> None:
 
     for e in consumed:
         e.record(stream)
+    e2e_steps = max(args.steps, min(200, pairs))
     e2e_loop(max(3, args.warmup))                     # warm-up covers every kernel of the loop, checksum included
     torch.cuda.synchronize()
     shm.barrier_all()
     t0 = time.perf_counter()
-    e2e_loop(args.steps)
+    e2e_loop(e2e_steps)
     torch.cuda.synchronize()
     shm.barrier_all()
     e2e_s = max_over_ranks([time.perf_counter() - t0])[0]
@@ -260,42 +369,55 @@ def main() -> None:
             remote_rows += int((ranks_of == r).any(dim=1).sum())
     disp_bytes = remote_rows * (HIDDEN + HIDDEN // 128 * 4 + 128)
     comb_bytes = remote_rows * HIDDEN * 2
-    disp_us = disp_ms / args.steps * 1e3
-    comb_us = comb_ms / args.steps * 1e3
+    disp_us = disp_ms / pairs * 1e3
+    comb_us = comb_ms / pairs * 1e3
 
     err = shm.get_error()
     if err["count"]:
         raise SystemExit(f"bench: a device-side wait timed out: {err}")
 
     if rank == 0:
-        value = world * T / (ms_per_step * 1e-3)
+        value = world * T * R / (ms_per_step * 1e-3)
+
+        def frac(nbytes, us, gbs):
+            return (nbytes / (gbs * 1e9)) / (us * 1e-6) if remote_rows else None
+
         line = {
             "metric": "ep_dispatch_combine_tokens_per_s", "value": value, "unit": "tokens/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_per_step,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp8-e4m3 dispatch / bf16 combine",
-            "data": "synthetic", "impl": "ours",
+            "higher_is_better": True, "scaling": "weak",
+            # No published number exists for the reference; the ratio is against the NCCL form measured above.
+            "vs_baseline": (value / base["value"]) if base else None,
+            "dtype": "fp8-e4m3 dispatch / bf16 combine",
+            "data": "synthetic", "impl": "ours", "verified": bool(verified),
             "config": {"model": "DeepEP-style MoE dispatch+combine (DeepSeek-V3-like)", "experts": EXPERTS,
                        "experts_per_rank": epr, "top_k": TOPK, "hidden": HIDDEN, "tokens_per_rank": T,
-                       "global_batch": world * T, "seq_len": 1, "parallelism": f"ep{world}",
-                       "layout": args.layout, "dynamic_handout": bool(d.dynamic),
-                       "l2": "flushed between steps (512 MiB write)",
+                       "pairs_per_step": R, "global_batch": world * T * R, "seq_len": 1, "parallelism": f"ep{world}",
+                       "layout": "slotted" if args.low_latency else args.layout, "low_latency": bool(args.low_latency),
+                       "dynamic_handout": bool(d.dynamic),
+                       "l2": "flushed before every dispatch+combine pair (512 MiB write, outside the timed events)",
                        "dispatch": "fp8 e4m3 + fp32 scale per 128", "combine": "bf16 weighted sum"},
             "clocks": clocks,
-            "e2e": {"value": world * T * args.steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
-                    "d2h_bytes_per_step": 4},
+            "e2e": {"value": world * T * e2e_steps / e2e_s, "unit": "tokens/s", "h2d_bytes_per_step": h2d_bytes,
+                    "d2h_bytes_per_step": 4, "d2h": "fp32 checksum of the step's output (one scalar, like a loss)",
+                    "steps": e2e_steps, "pairs_per_step": 1,
+                    "h2d_ceiling_gbs_slowest_rank": h2d_gbs,
+                    "h2d_ceiling_tokens_per_s": world * T * (h2d_gbs * 1e9 / h2d_bytes), "numa": numa_info},
             "gpu_launches": launches,
+            "baseline": base,
             "extra": {"dispatch_us": disp_us, "combine_us": comb_us,
                       "dispatch_remote_gbs_per_rank": disp_bytes / (disp_us * 1e-6) / 1e9 if remote_rows else 0.0,
                       "combine_remote_gbs_per_rank": comb_bytes / (comb_us * 1e-6) / 1e9 if remote_rows else 0.0,
                       "remote_rows_rank0": remote_rows, "recv_rows_rank0": n_rows,
                       "device_phase_us_last_step": phases,
-                      "nvlink_roofline_frac_dispatch": (disp_bytes / 770e9) / (disp_us * 1e-6) if remote_rows else None,
-                      "nvlink_roofline_frac_combine": (comb_bytes / 770e9) / (comb_us * 1e-6) if remote_rows else None},
+                      "nvlink_roofline_frac_dispatch": {"of_measured_770": frac(disp_bytes, disp_us, 770),
+                                                        "of_link_rate_900": frac(disp_bytes, disp_us, 900)},
+                      "nvlink_roofline_frac_combine": {"of_measured_770": frac(comb_bytes, comb_us, 770),
+                                                       "of_link_rate_900": frac(comb_bytes, comb_us, 900)}},
         }
         print(json.dumps(line))
     shm.finalize()
-    if world > 1:
-        dist.destroy_process_group()
+    dist.destroy_process_group()
 
 
 if __name__ == "__main__":

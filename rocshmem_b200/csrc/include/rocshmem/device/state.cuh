@@ -25,9 +25,13 @@ static __constant__ int g_n_local = 1;
 static void upload_state(const rocshmem_device_state *states, int n_local) {
   // Each shared object may carry its own copy of the CUDA runtime; make sure this one works on the
   // device that hosts the PEs before touching the module's symbols.
+  // The caller's current device is put back afterwards.
+  int previous = -1;
+  if (cudaGetDevice(&previous) != cudaSuccess) previous = -1;
   cudaSetDevice(states[0].device_ordinal);
   cudaMemcpyToSymbol(g_state, states, sizeof(rocshmem_device_state) * n_local);
   cudaMemcpyToSymbol(g_n_local, &n_local, sizeof(int));
+  if (previous >= 0 && previous != states[0].device_ordinal) cudaSetDevice(previous);
 }
 
 struct ModuleRegistration {

@@ -139,7 +139,6 @@ struct rocshmem_team_dev {
   // collectives, so the counters agree without communication. Flags are never reset: a waiter
   // compares against the epoch it expects (>=), which removes the reset phase and its races.
   unsigned long long barrier_epoch;
-  unsigned long long coll_epoch;
 };
 
 // Context descriptor (device pool entry).
@@ -242,7 +241,6 @@ struct rocshmem_device_state {
   rocshmem_ctx_dev *ctxs;              // [max_ctxs]
   unsigned long long *ctx_free_mask;   // bitmask over ctxs, 1 = free
   unsigned long long *barrier_flags;   // [max_teams][ROCSHMEM_MAX_PES] arrival epochs
-  unsigned long long *coll_flags;      // [max_teams][ROCSHMEM_MAX_PES] data-ready epochs
   unsigned long long *lib_flags;       // [ROCSHMEM_LIB_FLAG_WORDS] flags of library kernels
   unsigned long long *lib_state;       // [ROCSHMEM_LIB_STATE_WORDS] local epochs of library kernels
   char *scratch;                       // staging for library collectives

@@ -33,11 +33,14 @@ struct EpHandle {
 void bind_ep(py::module_ &m) {
   py::class_<EpHandle>(m, "EpHandle")
       .def(py::init([](uintptr_t team, int num_experts, int top_k, int hidden, int max_tokens, int quantize,
-                       int layout, int blocks, py::dict ptrs) {
+                       int layout, int blocks, int dynamic, int expert_layout, int low_latency, py::dict ptrs) {
         EpHandle h;
         h.team = team;
-        h.cfg = EpConfig{num_experts, top_k, hidden, max_tokens, quantize, layout, blocks};
-        auto get = [&ptrs](const char *k) { return ptrs[k].cast<uintptr_t>(); };
+        h.cfg = EpConfig{num_experts, top_k, hidden, max_tokens, quantize, layout, blocks, dynamic, expert_layout,
+                         low_latency};
+        auto get = [&ptrs](const char *k) -> uintptr_t {
+          return ptrs.contains(k) ? ptrs[k].cast<uintptr_t>() : uintptr_t(0);
+        };
         h.buf.recv_x = P<void>(get("recv_x"));
         h.buf.recv_scales = P<float>(get("recv_scales"));
         h.buf.recv_meta = P<int>(get("recv_meta"));
@@ -50,11 +53,15 @@ void bind_ep(py::module_ &m) {
         h.buf.grid_counter = P<unsigned long long>(get("grid_counter"));
         h.buf.phase_ns = P<unsigned long long>(get("phase_ns"));
         h.buf.recv_info = P<int>(get("recv_info"));
-        // Optional: with a work counter the dispatch kernel hands tokens out dynamically.
-        if (ptrs.contains("work_counter")) {
-          h.buf.work_counter = P<unsigned long long>(get("work_counter"));
-          h.cfg.dynamic = 1;
-        }
+        h.buf.work_counter = P<unsigned long long>(get("work_counter"));
+        h.buf.stage_x = P<void>(get("stage_x"));
+        h.buf.stage_scales = P<float>(get("stage_scales"));
+        h.buf.stage_meta = P<int>(get("stage_meta"));
+        h.buf.item_tok = P<int>(get("item_tok"));
+        h.buf.lay_offsets = P<int>(get("lay_offsets"));
+        h.buf.lay_row = P<int>(get("lay_row"));
+        h.buf.lay_k = P<int>(get("lay_k"));
+        h.buf.lay_w = P<float>(get("lay_w"));
         return h;
       }))
       .def_readonly("epoch", &EpHandle::epoch)
@@ -100,6 +107,8 @@ void bind_ep(py::module_ &m) {
                            hidden, weighted, P<void>(y), P<void>(stream)), "moe_reduce_pairs");
   });
   m.attr("EP_META_WORDS") = EP_META_WORDS;
+  m.attr("EP_WORK_WORDS") = EP_WORK_WORDS;
+  m.attr("EP_MAX_RANKS") = EP_MAX_RANKS;
 }
 
 }  // namespace kernels

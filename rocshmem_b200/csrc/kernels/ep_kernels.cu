@@ -1,26 +1,37 @@
-// Expert-parallel MoE dispatch and combine as two fused kernels over NVLink peer memory.
+// Expert-parallel MoE dispatch and combine as fused kernels over NVLink peer memory.
 //
-// Dispatch (one cooperative kernel per rank):
+// Dispatch, normal mode (one cooperative kernel per rank):
 //   A. every block scans its share of the tokens: destination-rank bitmask per token (a token that
 //      selects several experts of one rank is sent to that rank once), per-block per-rank counts,
-//      per-expert counts;
+//      per-expert counts and the position of every (token, k) pair among this rank's pairs for its expert;
 //   B. after one grid barrier each block derives its write offsets; block 0 publishes this rank's row
 //      of the rank-to-rank count matrix, and the per-expert counts, to every peer as single 64-bit
 //      words that carry the call's epoch in their upper half (data and "ready" flag in one store, so
 //      no fence and no separate flag);
-//   C. one warp per token: the bf16 row is loaded once, quantised to e4m3 with one fp32 scale per 128
-//      elements in registers (amax by shuffles inside 8-lane groups), and stored with 16-byte peer
-//      stores straight into its final row of every destination's receive buffer, together with the
-//      scales and a 128-byte metadata record. There is no staging buffer and no receiver-side copy;
+//   C. rows are quantised to e4m3 with one fp32 scale per 128 elements in registers (amax by shuffles
+//      inside 8-lane groups) and stored with 16-byte peer stores straight into their final rows of the
+//      destinations' receive buffers, together with the scales and a 128-byte metadata record. There is
+//      no receiver-side copy. Two ways of sharing the work:
+//        fixed shares   a warp owns whole tokens of its block and sends each to all its destinations;
+//        staged pairs   every token is quantised once into a local staging buffer (while the count exchange is
+//                       in flight), then warps take (token, destination) pairs from per-destination counters
+//                       and copy staged rows, so that no warp is left with eight destinations while another
+//                       has one;
 //   D. blocks pair up with the same block of every peer (release/acquire flags), so when the kernel
-//      has finished on a rank, everything sent to that rank is visible to its next kernel.
-// With the SLOTTED layout the write offset does not depend on other ranks' counts, so step C starts
-// right after the local count and the count exchange overlaps the payload (low-latency mode).
+//      has finished on a rank, everything sent to that rank is visible to its next kernel;
+//   E. on request, after one more grid barrier, all blocks turn the received metadata into the expert-grouped
+//      pair lists a grouped GEMM consumes (no atomics: a pair's position is its expert's offset + the pairs of
+//      earlier sources + the position its source gave it).
+//
+// Dispatch, low-latency mode (one ordinary launch, a block of four warps per token, slotted layout): rows go out as
+// soon as they are quantised, the last block to finish sends one signal word per destination that carries the row
+// count (release), then waits for the signals of all sources. No grid barrier, no count round-trip.
 //
 // Combine (one kernel per rank) is a pull: for each of its tokens a warp reads the result rows from
 // the (up to top_k) ranks the token went to, 16 bytes per lane with the loads of all sources in
 // flight together, accumulates in fp32 with the per-rank gate weight, and writes the bf16 row once.
-// Pulling needs no staging memory and no receive-side reduction pass.
+// Pulling needs no staging memory and no receive-side reduction pass. In low-latency mode four warps share a
+// token.
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
 
@@ -44,14 +55,17 @@ __device__ __forceinline__ unsigned long long pack(unsigned epoch, unsigned valu
   return (static_cast<unsigned long long>(epoch) << 32) | value;
 }
 
-// Spin (bounded) until the word carries `epoch`; returns its payload, or 0 with *ok = false.
+// Spin (bounded) until the word carries `epoch`; returns its payload, or 0 with *ok = false. A tag that is newer
+// than `epoch` can never turn into `epoch` again (the sender is a call ahead of what the buffers allow), so it is
+// reported at once instead of after the whole budget.
 __device__ __forceinline__ unsigned wait_packed(const unsigned long long *p, unsigned epoch, int peer, bool *ok) {
   unsigned long long v = detail::ld_relaxed_sys(p);
   if (static_cast<unsigned>(v >> 32) != epoch) {
     detail::SpinBudget budget(st().wait_timeout_ns);
     while (static_cast<unsigned>((v = detail::ld_relaxed_sys(p)) >> 32) != epoch) {
-      if (!budget.keep_going()) {
-        detail::record_error(ROCSHMEM_ERR_BARRIER_TIMEOUT, peer, 70, p, epoch, v);
+      const bool newer = static_cast<int>(static_cast<unsigned>(v >> 32) - epoch) > 0;
+      if (newer || !budget.keep_going()) {
+        detail::record_error(ROCSHMEM_ERR_BARRIER_TIMEOUT, peer, newer ? 71 : 70, p, epoch, v);
         *ok = false;
         return 0;
       }
@@ -111,20 +125,138 @@ __device__ __forceinline__ int4 quantize16(const int4 &a, const int4 &b, float *
   return q;
 }
 
-// DYNAMIC: after the offsets are known every block publishes the destination rows of its own tokens, a second
-// grid barrier follows, and warps then take tokens one at a time from a device-wide counter. Blocks whose share
-// happens to carry fewer bytes no longer idle while the heaviest block finishes.
-template <bool DYNAMIC>
+// Copies `nvec` 16-byte vectors with all loads of a batch (N per lane) in flight before the first store.
+template <int N>
+__device__ __forceinline__ void copy_row_vec(int4 *dst, const int4 *src, int nvec, unsigned lane) {
+  for (int v0 = 0; v0 < nvec; v0 += 32 * N) {
+    int4 r[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int v = v0 + i * 32 + int(lane);
+      if (v < nvec) r[i] = __ldcg(src + v);
+    }
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const int v = v0 + i * 32 + int(lane);
+      if (v < nvec) dst[v] = r[i];
+    }
+  }
+}
+
+// Exclusive prefix sum of data[0 .. n) in place (n <= 1024), done by the first warp of the block; returns the
+// total through *total. Callers synchronise the block before and after.
+__device__ __forceinline__ void warp0_exclusive_scan(int *data, int n, int *total) {
+  if (threadIdx.x >= 32) return;
+  const int lane = threadIdx.x;
+  const int chunk = (n + 31) / 32;
+  const int lo = min(n, lane * chunk), hi = min(n, lo + chunk);
+  int sum = 0;
+  for (int i = lo; i < hi; ++i) sum += data[i];
+  int incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int v = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += v;
+  }
+  int run = incl - sum;
+  for (int i = lo; i < hi; ++i) {
+    const int c = data[i];
+    data[i] = run;
+    run += c;
+  }
+  if (lane == 31) *total = incl;
+}
+
+// Receive-side bookkeeping shared by the dispatch kernels: rows per source, first row per source, rows per local
+// expert. Called by one whole block once every source's counts are known to have been sent.
+__device__ __forceinline__ void write_recv_info(const DispatchArgs &a, const rocshmem_team_dev *t, int *recv_info,
+                                                const unsigned long long *cnt_in, const unsigned long long *exp_in) {
+  const int P = t->size, me = t->my_pe, epr = a.cfg.num_experts / P;
+  const unsigned tid = threadIdx.x, nthr = blockDim.x;
+  for (unsigned s = tid; s < unsigned(P); s += nthr) {
+    bool good = true;
+    int start = 0, mine = 0;
+    for (int s2 = 0; s2 <= int(s); ++s2) {
+      const int c = static_cast<int>(wait_packed(cnt_in + s2 * P + me, a.epoch, s2, &good));
+      if (s2 < int(s)) start += c; else mine = c;
+    }
+    recv_info[1 + s] = a.cfg.layout == EP_LAYOUT_SLOTTED ? int(s) * a.cfg.max_tokens : start;
+    recv_info[1 + P + s] = mine;
+    if (s == unsigned(P - 1)) recv_info[0] = start + mine;
+  }
+  for (unsigned e = tid; e < unsigned(epr); e += nthr) {
+    bool good = true;
+    int sum = 0;
+    for (int s = 0; s < P; ++s) sum += static_cast<int>(wait_packed(exp_in + s * epr + e, a.epoch, s, &good));
+    recv_info[1 + 2 * P + e] = sum;
+  }
+}
+
+// Expert-grouped pair lists from the metadata of the received rows. s_off / s_src are shared-memory tables of
+// experts_per_rank + 1 and P * experts_per_rank ints. Every thread of every calling block takes part; `part` of
+// `parts` selects the share of the rows this block scans. All rows must be visible to the caller.
+__device__ __forceinline__ bool build_expert_layout(const DispatchArgs &a, const rocshmem_team_dev *t,
+                                                    const unsigned long long *cnt_in,
+                                                    const unsigned long long *exp_in, const int *recv_meta,
+                                                    int *s_off, int *s_src, int *s_total, unsigned part,
+                                                    unsigned parts) {
+  const int P = t->size, me = t->my_pe, epr = a.cfg.num_experts / P, K = a.cfg.top_k;
+  const unsigned tid = threadIdx.x, nthr = blockDim.x;
+  int *lay_offsets = rebase(a.buf.lay_offsets), *lay_row = rebase(a.buf.lay_row), *lay_k = rebase(a.buf.lay_k);
+  float *lay_w = rebase(a.buf.lay_w);
+  const int cap = P * a.cfg.max_tokens * K;
+  bool ok = true;
+  for (unsigned e = tid; e < unsigned(epr); e += nthr) {
+    int run = 0;
+    for (int s = 0; s < P; ++s) {
+      s_src[s * epr + e] = run;  // pairs of expert e that come from sources before s
+      run += static_cast<int>(wait_packed(exp_in + s * epr + e, a.epoch, s, &ok));
+    }
+    s_off[e] = run;
+  }
+  __syncthreads();
+  warp0_exclusive_scan(s_off, epr, s_total);
+  __syncthreads();
+  if (part == 0) {
+    for (unsigned e = tid; e < unsigned(epr); e += nthr) lay_offsets[e] = s_off[e];
+    if (tid == 0) lay_offsets[epr] = *s_total;
+  }
+  int start = 0;
+  for (int s = 0; s < P; ++s) {
+    const int count = static_cast<int>(wait_packed(cnt_in + s * P + me, a.epoch, s, &ok));
+    const int first = a.cfg.layout == EP_LAYOUT_SLOTTED ? s * a.cfg.max_tokens : start;
+    start += count;
+    for (int i = part * nthr + tid; i < count * K; i += parts * nthr) {
+      const int row = first + i / K, k = i % K;
+      const int *meta = recv_meta + size_t(row) * EP_META_WORDS;
+      const int e = meta[EP_META_IDX + k];
+      if (e >= 0 && e < epr) {
+        const int pos = s_off[e] + s_src[s * epr + e] + meta[EP_META_RANK + k];
+        if (pos < 0 || pos >= cap) continue;  // inconsistent record: never write outside the lists
+        lay_row[pos] = row;
+        lay_k[pos] = k;
+        lay_w[pos] = __int_as_float(meta[EP_META_WEIGHT + k]);
+      }
+    }
+  }
+  return ok;
+}
+
+// STAGED: see "staged pairs" at the top of the file; otherwise fixed shares of whole tokens.
+template <bool STAGED>
 __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs a) {
-  extern __shared__ __align__(16) unsigned char s_dyn[];  // masks [tpb] u64, then ranks [tpb][P] int
-  __shared__ int s_rank_cnt[ROCSHMEM_MAX_PES];
-  __shared__ int s_blk_base[ROCSHMEM_MAX_PES];
-  __shared__ int s_total[ROCSHMEM_MAX_PES];
-  __shared__ int s_base[ROCSHMEM_MAX_PES];
-  __shared__ int s_exp_cnt[1024];
+  // masks [tpb] u64, ranks among the block's tokens per destination [tpb][P] int, pair ranks [tpb][K] int
+  extern __shared__ __align__(16) unsigned char s_dyn[];
+  __shared__ int s_rank_cnt[EP_MAX_RANKS];
+  __shared__ int s_blk_base[EP_MAX_RANKS];
+  __shared__ int s_total[EP_MAX_RANKS];
+  __shared__ int s_base[EP_MAX_RANKS];
+  __shared__ int s_exp_cnt[1024];   // phase A: pairs per expert in this block; phase E: offsets per local expert
+  __shared__ int s_exp_base[1024];  // phase A: first position of the block's pairs; phase E: pairs of earlier sources
   // Read back as float4 vectors, so the array needs 16-byte alignment (float alone guarantees 4).
   __shared__ __align__(16) float s_scales[kEpThreads / 32][EP_MAX_HIDDEN / 128];
   __shared__ int s_ok;
+  __shared__ int s_lay_total;
 
   const rocshmem_team_dev *t = detail::team_of(a.team);
   if (t->my_pe < 0) return;
@@ -141,27 +273,35 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   char *recv_x = static_cast<char *>(rebase(a.buf.recv_x));
   float *recv_scales = rebase(a.buf.recv_scales);
   int *recv_meta = rebase(a.buf.recv_meta);
-  unsigned long long *cnt_in = rebase(a.buf.cnt_in);
-  unsigned long long *exp_in = rebase(a.buf.exp_in);
+  unsigned long long *cnt_in = rebase(a.buf.cnt_in) + size_t(parity) * P * P;
+  unsigned long long *exp_in = rebase(a.buf.exp_in) + size_t(parity) * P * epr;
   int *sent_slot = rebase(a.buf.sent_slot);
   unsigned long long *tok_mask = rebase(a.buf.tok_mask);
   int *blk_cnt = rebase(a.buf.blk_cnt);
   int *exp_cnt = rebase(a.buf.exp_cnt);
   unsigned long long *grid_counter = rebase(a.buf.grid_counter);
   int *recv_info = rebase(a.buf.recv_info);
+  char *stage_x = STAGED ? static_cast<char *>(rebase(a.buf.stage_x)) : nullptr;
+  float *stage_scales = STAGED ? rebase(a.buf.stage_scales) : nullptr;
+  int *stage_meta = STAGED ? rebase(a.buf.stage_meta) : nullptr;
+  int *item_tok = STAGED ? rebase(a.buf.item_tok) : nullptr;
 
   const int tpb = (a.cfg.max_tokens + B - 1) / B;  // tokens per block, fixed for the buffer's life
   const int t0 = min(T, int(b) * tpb), t1 = min(T, t0 + tpb);
   unsigned long long *s_mask = reinterpret_cast<unsigned long long *>(s_dyn);
   int *s_rank_in_block = reinterpret_cast<int *>(s_dyn + size_t(tpb) * sizeof(unsigned long long));
+  int *s_pair_rank = s_rank_in_block + size_t(tpb) * P;
   unsigned long long *phase_ns = rebase(a.buf.phase_ns);
   const bool stamp = (b == 0 && tid == 0);
   if (stamp) phase_ns[0] = detail::now_ns();
-  unsigned long long *work = DYNAMIC ? rebase(a.buf.work_counter) : nullptr;
-  if (DYNAMIC && stamp) work[parity ^ 1] = 0;  // cleared for the next call
+  // Grid barriers of one call: 1 (fixed shares), 2 (staged pairs), + 1 with the expert layout.
+  const unsigned long long rounds = (STAGED ? 2ull : 1ull) + (a.cfg.expert_layout ? 1ull : 0ull);
+  unsigned long long round = rounds * (epoch - 1);
+  unsigned long long *work = STAGED ? rebase(a.buf.work_counter) + EP_WORK_DISPATCH : nullptr;
+  if (STAGED && b == 0 && tid < EP_MAX_RANKS) work[(parity ^ 1) * EP_MAX_RANKS + tid] = 0;  // for the next call
 
   // ---- A: routing scan ------------------------------------------------------------------------------
-  for (unsigned i = tid; i < ROCSHMEM_MAX_PES; i += nthr) s_rank_cnt[i] = 0;
+  for (unsigned i = tid; i < EP_MAX_RANKS; i += nthr) s_rank_cnt[i] = 0;
   for (unsigned i = tid; i < unsigned(E); i += nthr) s_exp_cnt[i] = 0;
   if (tid == 0) s_ok = 1;
   __syncthreads();
@@ -169,10 +309,12 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
     unsigned long long mask = 0;
     for (int k = 0; k < K; ++k) {
       const int e = topk_idx[size_t(tok) * K + k];
+      int rank = 0;
       if (e >= 0 && e < E) {
         mask |= 1ull << (e / epr);
-        atomicAdd(&s_exp_cnt[e], 1);
+        rank = atomicAdd(&s_exp_cnt[e], 1);
       }
+      s_pair_rank[(tok - t0) * K + k] = rank;
     }
     tok_mask[tok] = mask;
     s_mask[tok - t0] = mask;
@@ -181,7 +323,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   __syncthreads();
   for (unsigned d = tid; d < unsigned(P); d += nthr) blk_cnt[b * P + d] = s_rank_cnt[d];
   for (unsigned e = tid; e < unsigned(E); e += nthr) {
-    if (s_exp_cnt[e]) atomicAdd(&exp_cnt[parity * E + e], s_exp_cnt[e]);
+    s_exp_base[e] = s_exp_cnt[e] ? atomicAdd(&exp_cnt[parity * E + e], s_exp_cnt[e]) : 0;
   }
   // Position of every token of the block among the block's tokens that go to the same rank (does not
   // depend on other blocks, so it is done before the grid barrier).
@@ -195,7 +337,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
     s_total[d] = 0;
   }
   if (stamp) phase_ns[1] = detail::now_ns();
-  if (!grid_barrier(grid_counter, DYNAMIC ? 2ull * epoch - 1 : epoch, B)) return;
+  if (!grid_barrier(grid_counter, ++round, B)) return;
   if (stamp) phase_ns[2] = detail::now_ns();
 
   // ---- B: offsets and count exchange -------------------------------------------------------------------
@@ -222,6 +364,54 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
       exp_cnt[(parity ^ 1) * E + e] = 0;  // cleared for the next call
     }
   }
+  const unsigned warp = tid / 32, lane = tid % 32, nwarps = nthr / 32;
+  const int iters = H / 512;
+  const int nscale = H / 128;
+  constexpr int kBatch = 8;  // iterations (of 512 elements) whose loads are issued together
+  if (STAGED) {
+    // ---- quantise the block's tokens once, locally, while the counts travel -----------------------------------
+    for (int tok = t0 + warp; tok < t1; tok += nwarps) {
+      if (s_mask[tok - t0] == 0) continue;
+      int *rec = stage_meta + size_t(tok) * EP_META_WORDS;
+      int word = 0;
+      if (lane < unsigned(K)) {
+        word = topk_idx[size_t(tok) * K + lane];
+      } else if (lane >= unsigned(EP_META_WEIGHT) && lane < unsigned(EP_META_WEIGHT + K)) {
+        word = __float_as_int(topk_w[size_t(tok) * K + lane - EP_META_WEIGHT]);
+      } else if (lane == unsigned(EP_META_SRC_TOKEN)) {
+        word = tok;
+      } else if (lane == unsigned(EP_META_SRC_RANK)) {
+        word = me;
+      } else if (lane >= unsigned(EP_META_RANK) && lane < unsigned(EP_META_RANK + K)) {
+        const int k = lane - EP_META_RANK;
+        const int e = topk_idx[size_t(tok) * K + k];
+        word = (e >= 0 && e < E) ? s_exp_base[e] + s_pair_rank[(tok - t0) * K + k] : 0;
+      }
+      rec[lane] = word;
+      if (a.cfg.quantize) {
+        const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
+        int4 *dst = reinterpret_cast<int4 *>(stage_x + size_t(tok) * H);
+        for (int i0 = 0; i0 < iters; i0 += kBatch) {
+          int4 raw[2 * kBatch];
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i) {
+            if (i0 + i < iters) {
+              raw[2 * i] = row[((i0 + i) * 512 + lane * 16) / 8];
+              raw[2 * i + 1] = row[((i0 + i) * 512 + lane * 16) / 8 + 1];
+            }
+          }
+#pragma unroll
+          for (int i = 0; i < kBatch; ++i) {
+            if (i0 + i < iters) {
+              float scale;
+              dst[(i0 + i) * 32 + lane] = quantize16(raw[2 * i], raw[2 * i + 1], &scale);
+              if ((lane & 7) == 0) stage_scales[size_t(tok) * nscale + (i0 + i) * 4 + lane / 8] = scale;
+            }
+          }
+        }
+      }
+    }
+  }
   if (a.cfg.layout == EP_LAYOUT_SLOTTED) {
     for (unsigned d = tid; d < unsigned(P); d += nthr) s_base[d] = me * a.cfg.max_tokens;
   } else {
@@ -235,58 +425,73 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
     if (!ok) atomicExch(&s_ok, 0);
   }
   __syncthreads();
-  if (DYNAMIC) {
+  if (STAGED) {
     // A failed count wait must not leave the other blocks waiting at the second barrier for ever: every block
     // reaches it (its waits are bounded), and gives up afterwards.
     if (s_ok) {
       for (int i = tid; i < (t1 - t0) * P; i += nthr) {
         const int tk = i / P, d = i % P;
         const bool goes = (s_mask[tk] >> d) & 1ull;
-        sent_slot[size_t(t0 + tk) * P + d] = goes ? s_base[d] + s_blk_base[d] + s_rank_in_block[tk * P + d] : -1;
+        const int item = s_blk_base[d] + s_rank_in_block[tk * P + d];  // index among my rows for d
+        sent_slot[size_t(t0 + tk) * P + d] = goes ? s_base[d] + item : -1;
+        if (goes) item_tok[size_t(d) * a.cfg.max_tokens + item] = t0 + tk;
       }
     }
-    if (!grid_barrier(grid_counter, 2ull * epoch, B)) return;
+    if (!grid_barrier(grid_counter, ++round, B)) return;
   }
   if (!s_ok) return;
   if (stamp) phase_ns[3] = detail::now_ns();
 
-  // ---- C: quantise and send, one warp per token ----------------------------------------------------------
-  const unsigned warp = tid / 32, lane = tid % 32, nwarps = nthr / 32;
-  const int iters = H / 512;
-  const int nscale = H / 128;
-  constexpr int kBatch = 8;  // iterations (of 512 elements) whose loads are issued together
-  for (int tok_static = t0 + warp;; tok_static += nwarps) {
-    int tok;
-    if (DYNAMIC) {
-      unsigned long long next = 0;
-      if (lane == 0) next = atomicAdd(work + parity, 1ull);
-      next = __shfl_sync(0xffffffffu, next, 0);
-      if (next >= static_cast<unsigned long long>(T)) break;
-      tok = static_cast<int>(next);
-    } else {
-      if (tok_static >= t1) break;
-      tok = tok_static;
+  if (STAGED) {
+    // ---- C (staged pairs): warps take (token, destination) pairs from per-destination counters -----------------
+    // Warps start on different destinations and move on when a destination's rows are all taken.
+    const unsigned gwarp = b * nwarps + warp;
+    const size_t row_bytes = a.cfg.quantize ? size_t(H) : size_t(H) * 2;
+    const int nvec = static_cast<int>(row_bytes / 16);
+    for (int dd = 0; dd < P; ++dd) {
+      const int d = (me + 1 + gwarp + dd) % P;
+      const int w = team_pe_to_world(t, d);
+      const int total = s_total[d];
+      if (total == 0) continue;
+      for (;;) {
+        unsigned long long next = 0;
+        if (lane == 0) next = atomicAdd(work + parity * EP_MAX_RANKS + d, 1ull);
+        next = __shfl_sync(0xffffffffu, next, 0);
+        if (next >= static_cast<unsigned long long>(total)) break;
+        const int item = static_cast<int>(next);
+        const int tok = __ldcg(item_tok + size_t(d) * a.cfg.max_tokens + item);
+        const int slot = s_base[d] + item;
+        const int rec = __ldcg(stage_meta + size_t(tok) * EP_META_WORDS + lane);
+        const int4 *src = a.cfg.quantize ? reinterpret_cast<const int4 *>(stage_x + size_t(tok) * H)
+                                         : reinterpret_cast<const int4 *>(x + size_t(tok) * H);
+        copy_row_vec<16>(reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * row_bytes, w)), src, nvec, lane);
+        if (a.cfg.quantize && lane < unsigned(nscale / 4)) {
+          const float4 sc = __ldcg(reinterpret_cast<const float4 *>(stage_scales + size_t(tok) * nscale) + lane);
+          reinterpret_cast<float4 *>(remote_ptr(recv_scales + size_t(slot) * nscale, w))[lane] = sc;
+        }
+        int word = rec;
+        if (lane < unsigned(EP_MAX_TOPK)) word = (lane < unsigned(K) && rec >= 0 && rec / epr == d) ? rec % epr : -1;
+        remote_ptr(recv_meta + size_t(slot) * EP_META_WORDS, w)[lane] = word;
+      }
     }
-    // In dynamic mode mask and rows were written by the token's owner block before the second barrier: read
-    // them through L2.
-    const unsigned long long mask = DYNAMIC ? __ldcg(tok_mask + tok) : s_mask[tok - t0];
+  } else {
+  // ---- C (fixed shares): quantise and send, one warp per token ---------------------------------------------
+  for (int tok = t0 + warp; tok < t1; tok += nwarps) {
+    const unsigned long long mask = s_mask[tok - t0];
     // Lane d keeps the row index on destination d; everybody reads it with a shuffle.
     int my_slot = -1;
-    if (DYNAMIC) {
-      if (lane < unsigned(P)) my_slot = __ldcg(sent_slot + size_t(tok) * P + lane);
-    } else {
-      if (lane < unsigned(P) && ((mask >> lane) & 1ull)) {
-        my_slot = s_base[lane] + s_blk_base[lane] + s_rank_in_block[(tok - t0) * P + lane];
-      }
-      if (lane < unsigned(P)) sent_slot[size_t(tok) * P + lane] = my_slot;
+    if (lane < unsigned(P) && ((mask >> lane) & 1ull)) {
+      my_slot = s_base[lane] + s_blk_base[lane] + s_rank_in_block[(tok - t0) * P + lane];
     }
+    if (lane < unsigned(P)) sent_slot[size_t(tok) * P + lane] = my_slot;
     if (mask == 0) continue;
     const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
-    int k_idx = -1;
+    int k_idx = -1, k_rank = 0;
     float k_w = 0.f;
     if (lane < unsigned(K)) {
       k_idx = topk_idx[size_t(tok) * K + lane];
       k_w = topk_w[size_t(tok) * K + lane];
+      if (k_idx >= 0 && k_idx < E) k_rank = s_exp_base[k_idx] + s_pair_rank[(tok - t0) * K + lane];
     }
     if (a.cfg.quantize) {
       for (int i0 = 0; i0 < iters; i0 += kBatch) {
@@ -334,19 +539,13 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
           reinterpret_cast<float4 *>(remote_ptr(recv_scales + size_t(slot) * nscale, w))[lane] = sc;
         }
       } else {
-        int4 *dst = reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H * 2, w));
-        const int nvec = H / 8;
-        int v = lane;
-        for (; v + 96 < nvec; v += 128) {
-          const int4 r0 = row[v], r1 = row[v + 32], r2 = row[v + 64], r3 = row[v + 96];
-          dst[v] = r0; dst[v + 32] = r1; dst[v + 64] = r2; dst[v + 96] = r3;
-        }
-        for (; v < nvec; v += 32) dst[v] = row[v];
+        copy_row_vec<4>(reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H * 2, w)), row, H / 8, lane);
       }
       int *meta = remote_ptr(recv_meta + size_t(slot) * EP_META_WORDS, w);
       if (lane < unsigned(K)) {
         meta[EP_META_IDX + lane] = (k_idx >= 0 && k_idx / epr == d) ? k_idx % epr : -1;
         meta[EP_META_WEIGHT + lane] = __float_as_int(k_w);
+        meta[EP_META_RANK + lane] = k_rank;
       } else if (lane == 16) {
         meta[EP_META_SRC_TOKEN] = tok;
       } else if (lane == 17) {
@@ -355,33 +554,187 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
     }
     __syncwarp();
   }
+  }
 
   // ---- D: completion ------------------------------------------------------------------------------------------
   if (stamp) phase_ns[4] = detail::now_ns();
   bool ok = block_pair_barrier(t, b);
   if (stamp) phase_ns[5] = detail::now_ns();
-  if (b == 0 && ok) {
-    // Receive-side bookkeeping: rows per source, first row per source, rows per local expert.
-    for (unsigned s = tid; s < unsigned(P); s += nthr) {
-      bool good = true;
-      int start = 0, mine = 0;
-      for (int s2 = 0; s2 <= int(s); ++s2) {
-        const int c = static_cast<int>(wait_packed(cnt_in + s2 * P + me, epoch, s2, &good));
-        if (s2 < int(s)) start += c; else mine = c;
-      }
-      recv_info[1 + s] = a.cfg.layout == EP_LAYOUT_SLOTTED ? int(s) * a.cfg.max_tokens : start;
-      recv_info[1 + P + s] = mine;
-      if (s == unsigned(P - 1)) recv_info[0] = start + mine;
-    }
-    for (unsigned e = tid; e < unsigned(epr); e += nthr) {
-      bool good = true;
-      int sum = 0;
-      for (int s = 0; s < P; ++s) sum += static_cast<int>(wait_packed(exp_in + s * epr + e, epoch, s, &good));
-      recv_info[1 + 2 * P + e] = sum;
+  if (b == 0 && ok) write_recv_info(a, t, recv_info, cnt_in, exp_in);
+  if (a.cfg.expert_layout) {
+    // ---- E: expert-grouped pair lists. Rows written by any block of a peer must be visible: every block of this
+    // PE has passed its pair barrier once the grid barrier completes.
+    if (!grid_barrier(grid_counter, ++round, B)) return;
+    if (ok) build_expert_layout(a, t, cnt_in, exp_in, recv_meta, s_exp_cnt, s_exp_base, &s_lay_total, b, B);
+  }
+  __syncthreads();
+  if (stamp) phase_ns[6] = detail::now_ns();
+}
+
+// ---- low-latency dispatch ------------------------------------------------------------------------------------------
+
+constexpr unsigned kLlThreads = 128;
+
+__global__ void __launch_bounds__(kLlThreads) ep_ll_dispatch_kernel(DispatchArgs a) {
+  __shared__ int s_e[EP_MAX_TOPK];
+  __shared__ int s_rank[EP_MAX_TOPK];
+  __shared__ float s_w[EP_MAX_TOPK];
+  __shared__ int s_slot[EP_MAX_RANKS];
+  __shared__ __align__(16) float s_scales[EP_MAX_HIDDEN / 128];
+  __shared__ int s_last;
+  __shared__ int s_off[1024];
+  __shared__ int s_src[1024];
+  __shared__ int s_lay_total;
+
+  const rocshmem_team_dev *t = detail::team_of(a.team);
+  if (t->my_pe < 0) return;
+  const int P = t->size, me = t->my_pe;
+  const int E = a.cfg.num_experts, epr = E / P, K = a.cfg.top_k, H = a.cfg.hidden;
+  const int T = a.num_tokens;
+  const unsigned tid = threadIdx.x, nthr = blockDim.x;
+  const unsigned warp = tid / 32, lane = tid % 32, nwarps = nthr / 32;
+  const unsigned epoch = a.epoch;
+  const int parity = epoch & 1;
+
+  const __nv_bfloat16 *x = rebase(a.x);
+  const int *topk_idx = rebase(a.topk_idx);
+  const float *topk_w = rebase(a.topk_w);
+  char *recv_x = static_cast<char *>(rebase(a.buf.recv_x));
+  float *recv_scales = rebase(a.buf.recv_scales);
+  int *recv_meta = rebase(a.buf.recv_meta);
+  unsigned long long *cnt_in = rebase(a.buf.cnt_in) + size_t(parity) * P * P;
+  unsigned long long *exp_in = rebase(a.buf.exp_in) + size_t(parity) * P * epr;
+  int *sent_slot = rebase(a.buf.sent_slot);
+  int *exp_cnt = rebase(a.buf.exp_cnt);  // [E] pairs per expert so far (first half of the array)
+  int *recv_info = rebase(a.buf.recv_info);
+  unsigned long long *work = rebase(a.buf.work_counter);
+  unsigned long long *phase_ns = rebase(a.buf.phase_ns);
+  if (blockIdx.x == 0 && tid == 0) phase_ns[0] = detail::now_ns();
+
+  // Normally one token per block; the loop serves launches whose grid had to be capped.
+  for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
+    if (tid < unsigned(K)) {
+      const int e = topk_idx[size_t(tok) * K + tid];
+      const bool valid = e >= 0 && e < E;
+      s_e[tid] = valid ? e : -1;
+      s_w[tid] = topk_w[size_t(tok) * K + tid];
+      s_rank[tid] = valid ? atomicAdd(&exp_cnt[e], 1) : 0;
     }
     __syncthreads();
-    if (stamp) phase_ns[6] = detail::now_ns();
+    if (tid < unsigned(P)) {
+      bool goes = false;
+      for (int k = 0; k < K; ++k) goes = goes || (s_e[k] >= 0 && s_e[k] / epr == int(tid));
+      int slot = -1;
+      if (goes) {
+        slot = me * a.cfg.max_tokens + static_cast<int>(atomicAdd(work + EP_WORK_LL_ROWS + tid, 1ull));
+      }
+      s_slot[tid] = slot;
+      sent_slot[size_t(tok) * P + tid] = slot;
+    }
+    __syncthreads();
+    const int iters = H / 512, nscale = H / 128;
+    const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
+    if (a.cfg.quantize) {
+      // The warps share the row: warp w takes the 512-element pieces w, w + 4, ... (all loads first).
+      constexpr int kWarps = kLlThreads / 32, kMine = (EP_MAX_HIDDEN / 512 + kWarps - 1) / kWarps;
+      int4 raw[2 * kMine];
+#pragma unroll
+      for (int m = 0; m < kMine; ++m) {
+        const int i = warp + m * kWarps;
+        if (i < iters) {
+          raw[2 * m] = row[(i * 512 + lane * 16) / 8];
+          raw[2 * m + 1] = row[(i * 512 + lane * 16) / 8 + 1];
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < kMine; ++m) {
+        const int i = warp + m * kWarps;
+        if (i < iters) {
+          float scale;
+          const int4 q = quantize16(raw[2 * m], raw[2 * m + 1], &scale);
+          if ((lane & 7) == 0) s_scales[i * 4 + lane / 8] = scale;
+          for (int dd = 0; dd < P; ++dd) {
+            const int d = (me + dd) % P;
+            const int slot = s_slot[d];
+            if (slot < 0) continue;
+            reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H, team_pe_to_world(t, d)))[i * 32 + lane] = q;
+          }
+        }
+      }
+      __syncthreads();
+    }
+    // Scales, record (and the bf16 row without quantisation): one destination per warp and step.
+    for (int dd = warp; dd < P; dd += nwarps) {
+      const int d = (me + dd) % P;
+      const int slot = s_slot[d];
+      if (slot < 0) continue;
+      const int w = team_pe_to_world(t, d);
+      if (a.cfg.quantize) {
+        if (lane < unsigned(nscale / 4)) {
+          reinterpret_cast<float4 *>(remote_ptr(recv_scales + size_t(slot) * nscale, w))[lane] =
+              reinterpret_cast<const float4 *>(s_scales)[lane];
+        }
+      } else {
+        copy_row_vec<8>(reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H * 2, w)), row, H / 8, lane);
+      }
+      int word = 0;
+      if (lane < unsigned(EP_MAX_TOPK)) {
+        word = (lane < unsigned(K) && s_e[lane] >= 0 && s_e[lane] / epr == d) ? s_e[lane] % epr : -1;
+      } else if (lane >= unsigned(EP_META_WEIGHT) && lane < unsigned(EP_META_WEIGHT + K)) {
+        word = __float_as_int(s_w[lane - EP_META_WEIGHT]);
+      } else if (lane == unsigned(EP_META_SRC_TOKEN)) {
+        word = tok;
+      } else if (lane == unsigned(EP_META_SRC_RANK)) {
+        word = me;
+      } else if (lane >= unsigned(EP_META_RANK) && lane < unsigned(EP_META_RANK + K)) {
+        word = s_rank[lane - EP_META_RANK];
+      }
+      remote_ptr(recv_meta + size_t(slot) * EP_META_WORDS, w)[lane] = word;
+    }
+    __syncthreads();  // the shared tables are reused by the next token
   }
+
+  // ---- completion: the last block to finish signals every destination, then collects the sources' signals ------
+  __syncthreads();
+  if (tid == 0) {
+    __threadfence_system();  // this block's rows, before the count
+    const unsigned long long prev = atomicAdd(work + EP_WORK_LL_DONE, 1ull);
+    s_last = (prev == gridDim.x - 1) ? 1 : 0;
+    if (s_last) __threadfence_system();
+  }
+  __syncthreads();
+  if (!s_last) return;
+  if (tid == 0) phase_ns[4] = detail::now_ns();
+  for (unsigned e = tid; e < unsigned(E); e += nthr) {
+    const int owner = e / epr;
+    const int c = __ldcg(exp_cnt + e);
+    detail::st_relaxed_sys(remote_ptr(exp_in + me * epr + (e % epr), team_pe_to_world(t, owner)),
+                           pack(epoch, static_cast<unsigned>(c)));
+    exp_cnt[e] = 0;  // this block is the only one left: cleared for the next call
+  }
+  __syncthreads();
+  if (tid < unsigned(P)) {
+    const unsigned long long c = __ldcg(work + EP_WORK_LL_ROWS + tid);
+    // Release: the rows of all blocks (ordered before this store through the done counter and the fences around
+    // it) and the expert counts above are visible to whoever acquires the word.
+    detail::st_release_sys(remote_ptr(cnt_in + me * P + tid, team_pe_to_world(t, tid)),
+                           pack(epoch, static_cast<unsigned>(c)));
+    work[EP_WORK_LL_ROWS + tid] = 0;
+  }
+  if (tid == 0) work[EP_WORK_LL_DONE] = 0;
+  // Receive side: the signal of source s says how many rows it sent and that they have landed.
+  bool ok = true;
+  if (tid < unsigned(P)) {
+    wait_packed(cnt_in + tid * P + me, epoch, tid, &ok);
+    detail::fence_sys();  // acquire side of the sources' release stores
+  }
+  ok = __syncthreads_and(ok ? 1 : 0) != 0;
+  if (tid == 0) phase_ns[5] = detail::now_ns();
+  if (!ok) return;
+  write_recv_info(a, t, recv_info, cnt_in, exp_in);
+  if (a.cfg.expert_layout) build_expert_layout(a, t, cnt_in, exp_in, recv_meta, s_off, s_src, &s_lay_total, 0, 1);
+  __syncthreads();
+  if (tid == 0) phase_ns[6] = detail::now_ns();
 }
 
 struct CombineArgs {
@@ -395,14 +748,16 @@ struct CombineArgs {
   int weighted;
   rocshmem_team_t team;
   unsigned long long work_base;  // dynamic mode: counter value at which this call's tokens start
+  int split;                     // warps that share one token (1, 2 or 4), each taking a slice of the row
+  int closing;                   // 0: no "done reading" barrier at the end (low-latency mode)
 };
 
 // Sums `n_src` rows (scaled by wgt) into dst. U vectors per source are loaded before any is used, so
 // up to S * U 16-byte loads are in flight per lane.
 template <int S, int U>
 __device__ __forceinline__ void combine_row(int4 *dst, const int4 **src, const float *wgt, int n_src,
-                                            int nvec, unsigned lane) {
-  for (int v0 = lane; v0 < nvec; v0 += 32 * U) {
+                                            int vbegin, int nvec, unsigned lane) {
+  for (int v0 = vbegin + lane; v0 < nvec; v0 += 32 * U) {
     int4 raw[S][U];
 #pragma unroll
     for (int s = 0; s < S; ++s) {
@@ -466,8 +821,11 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_kernel(CombineA
   const unsigned gwarp = blockIdx.x * (blockDim.x / 32) + threadIdx.x / 32;
   const unsigned nwarps = gridDim.x * (blockDim.x / 32);
   const int nvec = H / 8;  // int4 vectors of 8 bf16 per row
-  unsigned long long *work = DYNAMIC ? rebase(a.buf.work_counter) + 2 : nullptr;
-  for (int tok_static = gwarp;; tok_static += nwarps) {
+  unsigned long long *work = DYNAMIC ? rebase(a.buf.work_counter) + EP_WORK_COMBINE : nullptr;
+  const int split = DYNAMIC ? 1 : a.split;
+  const int part = gwarp % split;
+  const int vbegin = nvec / split * part, vend = nvec / split * (part + 1);
+  for (int tok_static = gwarp / split;; tok_static += nwarps / split) {
     int tok;
     if (DYNAMIC) {
       unsigned long long next = 0;
@@ -514,16 +872,16 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_kernel(CombineA
     __syncwarp();
     int4 *dst = reinterpret_cast<int4 *>(out + size_t(tok) * H);
     if (n_src <= 4) {
-      combine_row<4, 4>(dst, src, wgt, n_src, nvec, lane);
+      combine_row<4, 4>(dst, src, wgt, n_src, vbegin, vend, lane);
     } else {
-      combine_row<8, 2>(dst, src, wgt, n_src, nvec, lane);
+      combine_row<8, 2>(dst, src, wgt, n_src, vbegin, vend, lane);
     }
     __syncwarp();
   }
   if (stamp) phase_ns[10] = detail::now_ns();
   // Nobody reuses its result rows while a peer may still be reading them. Nothing is handed over
   // here (the output rows are local), so the relaxed form suffices.
-  block_pair_barrier(t, blockIdx.x, false);
+  if (a.closing) block_pair_barrier(t, blockIdx.x, false);
   if (stamp) phase_ns[11] = detail::now_ns();
 }
 
@@ -605,13 +963,23 @@ __global__ void ep_expert_layout_kernel(const int *recv_meta_a, const int *recv_
 }
 
 int validate(const EpConfig &cfg, int team_size, int num_tokens) {
-  if (team_size < 1 || team_size > ROCSHMEM_MAX_PES) return cudaErrorInvalidValue;
+  // Destinations live in the lanes of a warp (slot shuffles, per-lane weights), hence at most 32 ranks.
+  if (team_size < 1 || team_size > EP_MAX_RANKS) return cudaErrorInvalidValue;
   if (cfg.num_experts < team_size || cfg.num_experts % team_size || cfg.num_experts > 1024) return cudaErrorInvalidValue;
   if (cfg.top_k < 1 || cfg.top_k > EP_MAX_TOPK) return cudaErrorInvalidValue;
   if (cfg.hidden < 512 || cfg.hidden % 512 || cfg.hidden > EP_MAX_HIDDEN) return cudaErrorInvalidValue;
   if (num_tokens < 0 || num_tokens > cfg.max_tokens) return cudaErrorInvalidValue;
-  if (cfg.blocks < 1) return cudaErrorInvalidValue;
+  // block_pair_barrier keeps one flag row per block.
+  if (cfg.blocks < 1 || cfg.blocks > ROCSHMEM_LIB_MAX_BLOCKS) return cudaErrorInvalidValue;
+  if (cfg.low_latency && cfg.layout != EP_LAYOUT_SLOTTED) return cudaErrorInvalidValue;
   return 0;
+}
+
+// Blocks of a low-latency combine: a function of the configuration only, because every member must launch the
+// same number (block b pairs with block b of the peers) while their token counts may differ.
+int ll_combine_blocks(const EpConfig &cfg) {
+  const int warps = cfg.max_tokens * 4;
+  return std::max(1, std::min<int>(ROCSHMEM_LIB_MAX_BLOCKS, (warps + 3) / 4));
 }
 
 }  // namespace
@@ -621,7 +989,7 @@ int ep_default_blocks() {
   // One block per SM (the kernels are written for one resident block of 512 threads per SM), shared
   // between the PEs of the process when it hosts several.
   int per_pe = device_sm_count() / std::max(1, rt.n_local());
-  return std::max(1, per_pe);
+  return std::max(1, std::min<int>(per_pe, ROCSHMEM_LIB_MAX_BLOCKS));
 }
 
 unsigned long long ep_combine_fetches(const EpConfig &cfg, int num_tokens) {
@@ -634,12 +1002,24 @@ int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf,
   HostTeam *ht = rt.team_from_handle(team);
   if (!ht) return cudaErrorInvalidValue;
   if (int rc = validate(cfg, ht->world.size, num_tokens)) return rc;
+  if (cfg.expert_layout && (!buf.lay_offsets || !buf.lay_row || !buf.lay_k || !buf.lay_w)) return cudaErrorInvalidValue;
   DispatchArgs a{cfg, buf, static_cast<const __nv_bfloat16 *>(x), topk_idx, topk_w, num_tokens, epoch, team};
+  if (cfg.low_latency) {
+    if (buf.work_counter == nullptr) return cudaErrorInvalidValue;
+    // A block per token; with several PEs per process the launch is cooperative and must fit the GPU at once.
+    unsigned blocks = static_cast<unsigned>(std::max(1, std::min(num_tokens, 4096)));
+    if (rt.n_local() > 1) {
+      blocks = std::min(blocks, coresident_blocks_per_pe(ep_ll_dispatch_kernel, kLlThreads, 0, rt.n_local()));
+    }
+    return launch_pes(ep_ll_dispatch_kernel, blocks, kLlThreads, 0, static_cast<cudaStream_t>(stream), false, a);
+  }
   const int tpb = (cfg.max_tokens + cfg.blocks - 1) / cfg.blocks;
-  const size_t smem = size_t(tpb) * (ht->world.size * sizeof(int) + sizeof(unsigned long long));
+  const size_t smem = size_t(tpb) * ((ht->world.size + cfg.top_k) * sizeof(int) + sizeof(unsigned long long));
   if (smem > 40 * 1024) return cudaErrorInvalidValue;  // use more blocks for this many tokens
   if (cfg.dynamic) {
-    if (buf.work_counter == nullptr) return cudaErrorInvalidValue;
+    if (!buf.work_counter || !buf.stage_meta || !buf.item_tok || (cfg.quantize && (!buf.stage_x || !buf.stage_scales))) {
+      return cudaErrorInvalidValue;
+    }
     return launch_pes(ep_dispatch_kernel<true>, cfg.blocks, kEpThreads, smem, static_cast<cudaStream_t>(stream), true,
                       a);
   }
@@ -655,7 +1035,17 @@ int ep_combine(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, 
   if (!ht) return cudaErrorInvalidValue;
   if (int rc = validate(cfg, ht->world.size, num_tokens)) return rc;
   CombineArgs a{cfg, buf, static_cast<const __nv_bfloat16 *>(y), static_cast<__nv_bfloat16 *>(out), topk_idx,
-                topk_w, num_tokens, weighted, team, combine_calls_base};
+                topk_w, num_tokens, weighted, team, combine_calls_base, 1, 1};
+  if (cfg.low_latency) {
+    // Four warps per token, one token per block of 128 threads, no closing barrier.
+    a.split = (cfg.hidden / 8) % 4 == 0 ? 4 : 1;
+    a.closing = 0;
+    unsigned blocks = static_cast<unsigned>(ll_combine_blocks(cfg));
+    if (rt.n_local() > 1) {
+      blocks = std::min(blocks, coresident_blocks_per_pe(ep_combine_kernel<false>, kLlThreads, 0, rt.n_local()));
+    }
+    return launch_pes(ep_combine_kernel<false>, blocks, kLlThreads, 0, static_cast<cudaStream_t>(stream), false, a);
+  }
   if (cfg.dynamic) {
     if (buf.work_counter == nullptr) return cudaErrorInvalidValue;
     return launch_pes(ep_combine_kernel<true>, cfg.blocks, kCombineThreads, 0, static_cast<cudaStream_t>(stream), false,

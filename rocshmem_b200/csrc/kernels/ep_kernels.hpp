@@ -19,8 +19,11 @@ constexpr int EP_META_IDX = 0;         // [0, top_k): expert index local to the 
 constexpr int EP_META_WEIGHT = 8;      // [8, 8 + top_k): gate weights (float bits)
 constexpr int EP_META_SRC_TOKEN = 16;  // token index on the source rank
 constexpr int EP_META_SRC_RANK = 17;   // source rank (team numbering)
+constexpr int EP_META_RANK = 24;       // [24, 24 + top_k): position of this (token, k) pair among the source's
+                                       // pairs for the same expert (staged hand-out and low-latency kernels)
 constexpr int EP_MAX_TOPK = 8;
 constexpr int EP_MAX_HIDDEN = 8192;
+constexpr int EP_MAX_RANKS = 32;       // destinations live in the lanes of a warp
 
 enum EpLayout : int {
   EP_LAYOUT_COMPACT = 0,  // rows of source s start at the sum of the counts of sources < s
@@ -31,22 +34,34 @@ enum EpLayout : int {
 struct EpConfig {
   int num_experts;     // global, divisible by the team size
   int top_k;           // <= 8
-  int hidden;          // multiple of 128, <= 8192
+  int hidden;          // multiple of 512, <= 8192
   int max_tokens;      // per rank and call
   int quantize;        // 1: dispatch carries e4m3 rows + one fp32 scale per 128 elements; 0: bf16 rows
   int layout;          // EpLayout
   int blocks;          // blocks per PE (the same on every member)
-  int dynamic;         // 1: dispatch hands tokens to warps through a device-wide counter instead of fixed
-                       //    per-block shares (needs EpBuffers::work_counter; fixed for the buffers' life)
+  int dynamic;         // 1: dispatch quantises every token once into a local staging buffer and hands (token,
+                       //    destination) pairs to warps through per-destination counters; combine hands tokens out
+                       //    through a counter. 0: fixed per-block shares of whole tokens.
+  int expert_layout;   // 1: the dispatch kernel also writes the expert-grouped pair lists (EpBuffers::lay_*)
+  int low_latency;     // 1: one non-cooperative launch, a block per token, slotted layout, per-source signals
 };
+
+// Words of EpBuffers::work_counter.
+constexpr int EP_WORK_DISPATCH = 0;    // [2][EP_MAX_RANKS]: next item per destination, by call parity
+constexpr int EP_WORK_COMBINE = 64;    // tokens handed out by all combine calls so far (never reset)
+constexpr int EP_WORK_LL_DONE = 65;    // low-latency dispatch: blocks that have finished sending
+constexpr int EP_WORK_LL_ROWS = 66;    // [EP_MAX_RANKS]: rows sent to each destination by the running call
+constexpr int EP_WORK_WORDS = 128;
 
 // Symmetric buffers of one dispatcher (all allocated by the caller on the symmetric heap).
 struct EpBuffers {
   void *recv_x;             // [P * max_tokens, hidden] uint8 (quantize) or bf16
   float *recv_scales;       // [P * max_tokens, hidden / 128]
   int *recv_meta;           // [P * max_tokens, EP_META_WORDS]
-  unsigned long long *cnt_in;   // [P][P] packed (epoch << 32 | tokens source s sends to rank d), full matrix
-  unsigned long long *exp_in;   // [P][experts_per_rank] packed (epoch << 32 | rows for local expert e from s)
+  // Both double-buffered by call parity: a peer that is one call ahead does not overwrite words that
+  // this PE still reads.
+  unsigned long long *cnt_in;   // [2][P][P] packed (epoch << 32 | tokens source s sends to rank d), full matrix
+  unsigned long long *exp_in;   // [2][P][experts_per_rank] packed (epoch << 32 | rows for local expert e from s)
   // local scratch (symmetric allocation for simplicity, only ever accessed by its owner)
   int *sent_slot;           // [max_tokens][P] row index at destination d, -1 if not sent
   unsigned long long *tok_mask;  // [max_tokens] bit d set: token goes to rank d
@@ -57,11 +72,21 @@ struct EpBuffers {
   // Always on: eight 8-byte stores per kernel.
   unsigned long long *phase_ns;
   // outputs, local
-  int *recv_info;           // [0] total rows, [1 + s] first row of source s (P + 1 entries), then
-                            // [2 + P + e] rows whose top-k contains local expert e
-  // Dynamic mode: [0], [1] next token of a dispatch, double-buffered by call parity; [2] tokens handed out by
-  // all combine calls so far (never reset: every call knows where its range starts).
-  unsigned long long *work_counter;
+  int *recv_info;           // [0] total rows, [1 + s] first row of source s, [1 + P + s] rows of source s,
+                            // [1 + 2 P + e] (row, k) pairs of local expert e
+  unsigned long long *work_counter;  // [EP_WORK_WORDS], see EP_WORK_*
+  // Staged hand-out (dynamic == 1): this rank's tokens, quantised once; local.
+  void *stage_x;            // [max_tokens, hidden] uint8 (unused without quantisation: rows are read from x)
+  float *stage_scales;      // [max_tokens, hidden / 128]
+  int *stage_meta;          // [max_tokens, EP_META_WORDS] record with global expert ids
+  int *item_tok;            // [P][max_tokens] token of this rank's i-th row for destination d
+  // Expert-grouped pair lists (expert_layout == 1), local outputs: positions lay_offsets[e] .. lay_offsets[e + 1]
+  // belong to local expert e; lay_row / lay_k / lay_w give the received row, the top-k position and the gate
+  // weight of the pair at a position.
+  int *lay_offsets;         // [experts_per_rank + 1]
+  int *lay_row;             // [P * max_tokens * top_k]
+  int *lay_k;
+  float *lay_w;
 };
 
 // x [T, hidden] bf16, topk_idx [T, top_k] int32 (global expert ids, -1 = unused), topk_w [T, top_k] fp32.
@@ -72,8 +97,11 @@ int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf,
 // y: symmetric [P * max_tokens, hidden] bf16 in the row layout produced by dispatch. out [T, hidden]
 // bf16 (local). Every token receives the sum over the ranks it was sent to of that rank's row,
 // scaled (weighted != 0) by the sum of the token's gate weights of the experts living on that rank.
-// `combine_calls_base` (dynamic mode only): value of work_counter[2] when this call starts, i.e. the sum over the
-// earlier combine calls on these buffers of ep_combine_fetches(cfg, their num_tokens).
+// `combine_calls_base` (dynamic mode only): value of work_counter[EP_WORK_COMBINE] when this call starts, i.e. the
+// sum over the earlier combine calls on these buffers of ep_combine_fetches(cfg, their num_tokens).
+// In low-latency mode a token is shared by four warps and the closing "done reading" barrier is left out: `y` may
+// be rewritten only after the next dispatch on these buffers has completed on this rank (every peer finishes its
+// combine before it starts that dispatch, and the dispatch waits for every peer's signal).
 int ep_combine(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf, const void *y, void *out,
                const int *topk_idx, const float *topk_w, int num_tokens, int weighted, void *stream,
                unsigned long long combine_calls_base = 0);

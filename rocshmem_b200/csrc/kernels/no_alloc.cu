@@ -35,8 +35,10 @@ __global__ void noalloc_offsets_kernel(const int *recv_info, int n_ranks, int ex
 }
 
 // Second pass: every (row, k) pair that selects a local expert takes the next position of that expert.
-__global__ void noalloc_layout_kernel(const int *recv_meta, const int *recv_info, int n_ranks, int top_k,
-                                      const int *offsets, int *row_index, int *pair_k, int *cursor) {
+// An expert index outside [0, experts_per_rank) (a caller whose experts_per_rank is smaller than the
+// dispatcher's) is skipped: its cursor was not cleared by this call and may lie outside the array.
+__global__ void noalloc_layout_kernel(const int *recv_meta, const int *recv_info, int n_ranks, int experts_per_rank,
+                                      int top_k, const int *offsets, int *row_index, int *pair_k, int *cursor) {
   using rocshmem::kernels::EP_META_IDX;
   using rocshmem::kernels::EP_META_WORDS;
   for (int s = 0; s < n_ranks; ++s) {
@@ -44,7 +46,7 @@ __global__ void noalloc_layout_kernel(const int *recv_meta, const int *recv_info
     for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < count * top_k; i += gridDim.x * blockDim.x) {
       const int row = start + i / top_k, k = i % top_k;
       const int e = recv_meta[size_t(row) * EP_META_WORDS + EP_META_IDX + k];
-      if (e >= 0) {
+      if (e >= 0 && e < experts_per_rank) {
         const int pos = offsets[e] + atomicAdd(&cursor[e], 1);
         row_index[pos] = row;
         pair_k[pos] = k;
@@ -97,8 +99,8 @@ extern "C" int rocshmem_b200_expert_layout_noalloc(const int *recv_meta, const i
   cudaGetDevice(&dev);
   cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
   const unsigned blocks = sms > 0 ? static_cast<unsigned>(sms) : 1u;
-  noalloc_layout_kernel<<<blocks, 256, 0, stream>>>(recv_meta, recv_info, n_ranks, top_k, offsets, row_index, pair_k,
-                                                    cursor);
+  noalloc_layout_kernel<<<blocks, 256, 0, stream>>>(recv_meta, recv_info, n_ranks, experts_per_rank, top_k, offsets,
+                                                    row_index, pair_k, cursor);
   e = cudaGetLastError();
   return e == cudaSuccess ? 0 : static_cast<int>(e);
 }

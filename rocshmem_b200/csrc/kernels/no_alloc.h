@@ -21,7 +21,10 @@
  *
  * Rules of use:
  *   - The first call on each device looks up the device address of the scratch array (with that
- *     device current) and caches it. Make that first call outside any stream capture.
+ *     device current) and caches it. Make that first call outside any stream capture. The cached
+ *     address does not survive cudaDeviceReset(): do not reset a device after its first call.
+ *   - experts_per_rank must be the value the dispatch was configured with. Pairs whose expert index is
+ *     not below experts_per_rank are left out of the layout.
  *   - All calls on a device share the one scratch array. The kernels clear what they need at the
  *     start of every call, so calls that follow each other on one stream are fine; calls that may
  *     overlap on the GPU (different streams, no dependency) race on the scratch and must be avoided.

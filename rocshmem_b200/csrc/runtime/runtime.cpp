@@ -44,7 +44,6 @@ InternalLayout InternalLayout::build(const Config &cfg) {
   l.ctxs = take(sizeof(rocshmem_ctx_dev) * size_t(cfg.max_contexts));
   l.ctx_free_mask = take(sizeof(unsigned long long) * (ROCSHMEM_CTX_SLOTS / 64));
   l.barrier_flags = take(sizeof(unsigned long long) * ROCSHMEM_TEAM_SLOTS * ROCSHMEM_MAX_PES);
-  l.coll_flags = take(sizeof(unsigned long long) * ROCSHMEM_TEAM_SLOTS * ROCSHMEM_MAX_PES);
   l.lib_flags = take(sizeof(unsigned long long) * ROCSHMEM_LIB_FLAG_WORDS);
   l.lib_state = take(sizeof(unsigned long long) * ROCSHMEM_LIB_STATE_WORDS);
   l.proxy = take(sizeof(rocshmem_proxy_ring) + 256);
@@ -287,7 +286,6 @@ void Runtime::build_states() {
     s.ctxs = reinterpret_cast<rocshmem_ctx_dev *>(ib + layout_.ctxs);
     s.ctx_free_mask = reinterpret_cast<unsigned long long *>(ib + layout_.ctx_free_mask);
     s.barrier_flags = reinterpret_cast<unsigned long long *>(ib + layout_.barrier_flags);
-    s.coll_flags = reinterpret_cast<unsigned long long *>(ib + layout_.coll_flags);
     s.lib_flags = reinterpret_cast<unsigned long long *>(ib + layout_.lib_flags);
     s.lib_state = reinterpret_cast<unsigned long long *>(ib + layout_.lib_state);
     s.scratch = ib + layout_.scratch;
@@ -358,7 +356,12 @@ void Runtime::finalize() {
   // Kernels launched after finalize (plain GEMMs, layout helpers on ordinary tensors) must not see
   // the window of a heap that no longer exists: every module gets an all-zero state back.
   if (is_cuda()) {
-    for (auto &s : states_) s = rocshmem_device_state{};
+    // The zeroed state keeps the device ordinal: the modules' upload functions select that device before they
+    // write their symbols, and ordinal 0 would create a context on (and write to) the wrong GPU.
+    for (auto &s : states_) {
+      s = rocshmem_device_state{};
+      s.device_ordinal = device_;
+    }
     try {
       upload_states();
     } catch (...) {
@@ -467,17 +470,20 @@ void Runtime::write_team_descriptor(HostTeam *t) {
     d.world_size = n_pes_;
     d.my_pe_world = pe;
     d.barrier_epoch = 0;
-    d.coll_epoch = 0;
     auto *dst = reinterpret_cast<rocshmem_team_dev *>(internal_base(pe) + layout_.teams) + t->slot;
     mem_->write(dst, &d, sizeof(d));
-    // A reused slot starts from epoch 0 again, so its arrival flags are cleared as well. All
-    // members do this before the collective that ends the split, and nobody signals on the new
-    // team before that collective has completed.
-    std::vector<unsigned long long> zeros(ROCSHMEM_MAX_PES, 0ull);
-    mem_->write(internal_base(pe) + layout_.barrier_flags + size_t(t->slot) * ROCSHMEM_MAX_PES * 8,
-                zeros.data(), zeros.size() * 8);
-    mem_->write(internal_base(pe) + layout_.coll_flags + size_t(t->slot) * ROCSHMEM_MAX_PES * 8,
-                zeros.data(), zeros.size() * 8);
+    // A reused slot starts from epoch 0 again, so the arrival flags of the device barrier and the
+    // per-(slot, block) epochs and flags of the library kernels are cleared as well: the slot's earlier
+    // occupants may have had other members and may have run another number of kernels. All members do
+    // this before the collective that ends the split, and nobody signals on the new team before that
+    // collective has completed.
+    mem_->zero(internal_base(pe) + layout_.barrier_flags + size_t(t->slot) * ROCSHMEM_MAX_PES * 8,
+               size_t(ROCSHMEM_MAX_PES) * 8);
+    mem_->zero(internal_base(pe) + layout_.lib_state + size_t(t->slot) * ROCSHMEM_LIB_MAX_BLOCKS * 8,
+               size_t(ROCSHMEM_LIB_MAX_BLOCKS) * 8);
+    mem_->zero(internal_base(pe) + layout_.lib_flags +
+                   size_t(t->slot) * ROCSHMEM_LIB_MAX_BLOCKS * ROCSHMEM_MAX_PES * 8,
+               size_t(ROCSHMEM_LIB_MAX_BLOCKS) * ROCSHMEM_MAX_PES * 8);
   }
   t->dev = reinterpret_cast<rocshmem_team_dev *>(internal_base(first_pe_) + layout_.teams) + t->slot;
 }

@@ -56,7 +56,7 @@ struct HostCtx {
 // Layout of the internal region (offsets from internal_base, identical on every PE).
 struct InternalLayout {
   size_t error = 0, stats = 0, teams = 0, ctxs = 0, ctx_free_mask = 0, barrier_flags = 0,
-         coll_flags = 0, lib_flags = 0, lib_state = 0, proxy = 0, host_slots = 0, scratch = 0;
+         lib_flags = 0, lib_state = 0, proxy = 0, host_slots = 0, scratch = 0;
   size_t total = 0;
   // A 256-byte guard filled with a fixed pattern follows every sub-region; a write that runs past the end of a
   // flag or descriptor array lands there and is reported by Runtime::check_canaries().

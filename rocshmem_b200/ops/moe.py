@@ -82,15 +82,27 @@ class EpDispatcher:
 
     def __init__(self, num_experts: int, top_k: int, hidden: int, max_tokens: int,
                  team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact",
-                 blocks: Optional[int] = None, dynamic: Optional[bool] = None):
-        """``dynamic``: dispatch and combine hand tokens to warps through a device-wide counter instead of fixed
-        shares (levels the tail when shares carry unequal numbers of bytes; dispatch pays a second grid barrier for
-        it). ``None`` takes ``ROCSHMEM_EP_DYNAMIC`` (default off). Every member must choose the same."""
+                 blocks: Optional[int] = None, dynamic: Optional[bool] = None, expert_layout: bool = False,
+                 low_latency: bool = False):
+        """``dynamic``: dispatch quantises every token once into a local staging buffer and hands (token,
+        destination) pairs to warps through per-destination counters, combine hands tokens out through a counter
+        (levels the tail when fixed shares carry unequal numbers of bytes; dispatch pays a second grid barrier for
+        it). ``None`` takes ``ROCSHMEM_EP_DYNAMIC`` (default on).
+
+        ``expert_layout``: the dispatch kernel also groups the received (row, k) pairs by local expert
+        (:meth:`expert_pairs`), which a grouped GEMM consumes directly.
+
+        ``low_latency``: for small batches (decode): one ordinary launch with a block per token, the slotted
+        layout (implied), one signal word per source instead of a count round-trip, and a combine without the
+        closing barrier: the result buffer may be rewritten only after the next dispatch on this object has
+        completed. Every member must choose the same options."""
         C = rt._C()
         if not C.is_cuda():
             raise RuntimeError("EpDispatcher needs the CUDA backend")
         self.team = team or rt.team_world()
         P = self.team.n_pes()
+        if P > C.EP_MAX_RANKS:
+            raise ValueError(f"EpDispatcher supports teams of at most {C.EP_MAX_RANKS} ranks")
         if num_experts % P:
             raise ValueError("num_experts must be divisible by the team size")
         if hidden % 512 or not (512 <= hidden <= 8192):
@@ -100,18 +112,25 @@ class EpDispatcher:
         self.num_experts, self.top_k, self.hidden, self.max_tokens = num_experts, top_k, hidden, max_tokens
         self.n_ranks, self.experts_per_rank = P, num_experts // P
         self.quantize = bool(quantize)
+        self.low_latency = bool(low_latency)
+        if self.low_latency:
+            layout = "slotted"
         self.layout = {"compact": 0, "slotted": 1}[layout]
         self.blocks = int(blocks or C.ep_default_blocks())
-        # tokens handled per block must fit the kernel's shared-memory table
-        while (max_tokens + self.blocks - 1) // self.blocks * P * 4 > 40 * 1024:
+        # tokens handled per block must fit the kernel's shared-memory tables
+        while (max_tokens + self.blocks - 1) // self.blocks * ((P + top_k) * 4 + 8) > 40 * 1024:
             self.blocks *= 2
+        if dynamic is None:
+            dynamic = os.environ.get("ROCSHMEM_EP_DYNAMIC", "1") not in ("", "0")
+        self.dynamic = bool(dynamic) and not self.low_latency
+        self.with_expert_layout = bool(expert_layout)
         rows = P * max_tokens
         z = rt.zeros
         self.recv_x = z((rows, hidden), torch.uint8 if quantize else torch.bfloat16)
         self.recv_scales = z((rows, hidden // 128), torch.float32)
         self.recv_meta = z((rows, C.EP_META_WORDS), torch.int32)
-        self.cnt_in = z(P * P, torch.int64)
-        self.exp_in = z(P * self.experts_per_rank, torch.int64)
+        self.cnt_in = z(2 * P * P, torch.int64)
+        self.exp_in = z(2 * P * self.experts_per_rank, torch.int64)
         self.sent_slot = z((max_tokens, P), torch.int32)
         self.tok_mask = z(max_tokens, torch.int64)
         self.blk_cnt = z(self.blocks * P, torch.int32)
@@ -119,18 +138,29 @@ class EpDispatcher:
         self.grid_counter = z(1, torch.int64)
         self.phase_ns = z(16, torch.int64)
         self.recv_info = z(1 + 2 * P + self.experts_per_rank, torch.int32)
-        if dynamic is None:
-            dynamic = os.environ.get("ROCSHMEM_EP_DYNAMIC", "0") not in ("", "0")
-        self.dynamic = bool(dynamic)
-        self.work_counter = z(4, torch.int64) if self.dynamic else None
-        self._y = None
-        ptrs = {name: getattr(self, name).data_ptr() for name in (
-            "recv_x", "recv_scales", "recv_meta", "cnt_in", "exp_in", "sent_slot", "tok_mask", "blk_cnt",
-            "exp_cnt", "grid_counter", "phase_ns", "recv_info")}
+        self.work_counter = z(C.EP_WORK_WORDS, torch.int64)
+        self._buffers = ["recv_x", "recv_scales", "recv_meta", "cnt_in", "exp_in", "sent_slot", "tok_mask", "blk_cnt",
+                         "exp_cnt", "grid_counter", "phase_ns", "recv_info", "work_counter"]
         if self.dynamic:
-            ptrs["work_counter"] = self.work_counter.data_ptr()
+            if quantize:
+                self.stage_x = z((max_tokens, hidden), torch.uint8)
+                self.stage_scales = z((max_tokens, hidden // 128), torch.float32)
+                self._buffers += ["stage_x", "stage_scales"]
+            self.stage_meta = z((max_tokens, C.EP_META_WORDS), torch.int32)
+            self.item_tok = z((P, max_tokens), torch.int32)
+            self._buffers += ["stage_meta", "item_tok"]
+        if self.with_expert_layout:
+            cap = rows * top_k
+            self.lay_offsets = z(self.experts_per_rank + 1, torch.int32)
+            self.lay_row = z(cap, torch.int32)
+            self.lay_k = z(cap, torch.int32)
+            self.lay_w = z(cap, torch.float32)
+            self._buffers += ["lay_offsets", "lay_row", "lay_k", "lay_w"]
+        self._y = None
+        ptrs = {name: getattr(self, name).data_ptr() for name in self._buffers}
         self._h = C.EpHandle(self.team.handle, num_experts, top_k, hidden, max_tokens, int(quantize),
-                             self.layout, self.blocks, ptrs)
+                             self.layout, self.blocks, int(self.dynamic), int(self.with_expert_layout),
+                             int(self.low_latency), ptrs)
         self.kernel_launches = 0
 
     def destroy(self) -> None:
@@ -141,9 +171,7 @@ class EpDispatcher:
         if rt.is_cuda():
             torch.cuda.synchronize()
         lay = list(getattr(self, "_lay", ()))
-        rt.free_all([self.recv_x, self.recv_scales, self.recv_meta, self.cnt_in, self.exp_in, self.sent_slot,
-                     self.tok_mask, self.blk_cnt, self.exp_cnt, self.grid_counter, self.phase_ns, self.recv_info,
-                     self.work_counter, self._y] + lay)
+        rt.free_all([getattr(self, name) for name in self._buffers] + [self._y] + lay)
         self._h = None
         self._y = None
         if lay:
@@ -210,10 +238,22 @@ class EpDispatcher:
         """Device timestamps of the last dispatch and combine (block 0), as microseconds since the
         kernel's first timestamp. Synchronises."""
         ns = self.phase_ns.cpu().tolist()
-        names_d = ["start", "scan", "grid_barrier", "offsets_counts", "sent", "peers_done", "outputs"]
+        if self.low_latency:
+            names_d = {0: "start", 4: "sent", 5: "peers_done", 6: "outputs"}
+        else:
+            names_d = dict(enumerate(["start", "scan", "grid_barrier", "offsets_counts", "sent", "peers_done",
+                                      "outputs"]))
         names_c = ["start", "peers_ready", "summed", "peers_done"]
-        return {"dispatch": {n: (ns[i] - ns[0]) / 1e3 for i, n in enumerate(names_d)},
+        return {"dispatch": {n: (ns[i] - ns[0]) / 1e3 for i, n in names_d.items()},
                 "combine": {n: (ns[8 + i] - ns[8]) / 1e3 for i, n in enumerate(names_c)}}
+
+    def expert_pairs(self):
+        """Expert-grouped pair lists written by the last dispatch (``expert_layout=True``): ``offsets``
+        [E_local + 1], and per position the received row, the top-k position and the gate weight. Only the first
+        ``offsets[-1]`` entries are meaningful; the order inside one expert's range is unspecified."""
+        if not self.with_expert_layout:
+            raise RuntimeError("the dispatcher was created without expert_layout=True")
+        return self.lay_offsets, self.lay_row, self.lay_k, self.lay_w
 
     def expert_layout(self, stream=None):
         """Row lists grouped by local expert for a grouped GEMM: ``offsets`` [E_local + 1], ``row_index``

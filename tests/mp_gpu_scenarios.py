@@ -162,6 +162,46 @@ def gpu_library_collectives():
     shm.finalize()
 
 
+C_BCAST, C_FCOLLECT, C_ALLTOALL, C_SUM = 0, 1, 2, 3
+
+
+def gpu_proxied_collectives():
+    """Two processes, one GPU each: block-level reduce, fcollect and broadcast of a kernel run through the proxy."""
+    k = _init("64M", ROCSHMEM_USE_PROXY=1, ROCSHMEM_PROXY_COLLECTIVES=1, ROCSHMEM_ENABLE_NVLS=0)
+    rank, world = RANK, WORLD
+    n = 1024
+    src = shm.zeros(n * world, torch.float32)
+    dst = shm.zeros(n * world, torch.float32)
+    rc = shm.zeros(4, torch.int32)
+    src.copy_((torch.arange(n * world) + 1000 * rank).float().cuda())
+    torch.cuda.synchronize()
+    shm.barrier_all()
+    side = torch.cuda.Stream()
+    team = shm.team_world().handle
+
+    def run(op, count, root=0):
+        with torch.cuda.stream(side):
+            k.coll(op, "float32", team, dst.data_ptr(), src.data_ptr(), count, root, 1, rc.data_ptr(), 128, side.cuda_stream)
+        torch.cuda.synchronize()
+        assert shm.get_error()["count"] == 0, shm.get_error()
+
+    run(C_SUM, n)
+    want = torch.arange(n).float() * world + 1000.0 * sum(range(world))
+    assert torch.equal(dst.cpu()[:n], want)
+    run(C_FCOLLECT, n)
+    got = dst.cpu().view(world, n)
+    assert all(torch.equal(got[r], torch.arange(n).float() + 1000 * r) for r in range(world))
+    dst.zero_()
+    torch.cuda.synchronize()
+    shm.barrier_all()
+    run(C_BCAST, n, root=world - 1)
+    if rank != world - 1:
+        assert torch.equal(dst.cpu()[:n], torch.arange(n).float() + 1000 * (world - 1))
+    shm.barrier_all()
+    shm.finalize()
+    print(f"rank {rank}: proxied collectives ok")
+
+
 def gpu_moe():
     """Dispatch + combine across real GPUs: identity experts return the token, rank-constant rows
     give exact sums, routing bookkeeping matches a CPU reference."""
@@ -314,4 +354,5 @@ def gpu_models():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_moe, gpu_tp_fused, gpu_models)}
+SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_proxied_collectives, gpu_moe,
+                                     gpu_tp_fused, gpu_models)}

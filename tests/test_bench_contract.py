@@ -1,9 +1,11 @@
-"""The parts of the benchmark entry point that need no GPU: the reference arm's answer and the JSON keys the
-single-line report carries (checked against the source, the GPU run itself is exercised on a B200)."""
+"""The benchmark entry point: the reference arm's answer (no GPU needed) and, on a GPU, the single-line report of
+a short run."""
 import json
 import os
 import subprocess
 import sys
+
+import pytest
 
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
@@ -16,9 +18,17 @@ def test_reference_arm_reports_unavailable_and_exits_zero():
     assert line["impl"] == "reference" and isinstance(line["unavailable"], str) and "\n" not in line["unavailable"]
 
 
-def test_report_carries_the_contract_keys():
-    src = open(os.path.join(ROOT, "bench.py")).read()
+@pytest.mark.gpu
+def test_a_short_run_prints_one_json_line_with_the_contract_keys():
+    """A real (small) run on one GPU: the last line of stdout is the report."""
+    out = subprocess.run([sys.executable, os.path.join(ROOT, "bench.py"), "--gpus", "1", "--steps", "2", "--warmup", "3",
+                          "--tokens", "256", "--repeats", "2"], capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, (out.stdout[-2000:], out.stderr[-2000:])
+    line = json.loads(out.stdout.strip().splitlines()[-1])
     for key in ("metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
-                "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "h2d_bytes_per_step", "d2h_bytes_per_step",
-                "gpu_launches"):
-        assert f'"{key}"' in src, key
+                "vs_baseline", "dtype", "data", "config", "clocks", "e2e", "gpu_launches", "verified", "baseline"):
+        assert key in line, key
+    assert line["n_gpus"] == 1 and line["steps"] == 2 and line["warmup"] == 3 and line["verified"] is True
+    assert line["value"] > 0 and line["gpu_launches"] == 2 * 2 * 2          # steps x pairs x (dispatch + combine)
+    assert line["e2e"]["h2d_bytes_per_step"] == 256 * 7168 * 2 + 2 * 256 * 8 * 4 and line["e2e"]["value"] > 0
+    assert line["baseline"]["value"] > 0 and abs(line["vs_baseline"] - line["value"] / line["baseline"]["value"]) < 1e-6

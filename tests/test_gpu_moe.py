@@ -48,11 +48,34 @@ def make_inputs(shm, T, H, E, K, seed, drop_some=False):
     return x, idx, w, host
 
 
-@pytest.mark.parametrize("layout", ["compact", "slotted"])
+def check_expert_pairs(shm, d, res, K, epr):
+    """The pair lists written by the dispatch kernel against a brute-force grouping of the metadata."""
+    offsets, lay_row, lay_k, lay_w = d.expert_pairs()
+    for l in range(NPES):
+        off = shm.local_view(offsets, l).cpu().tolist()
+        rows = shm.local_view(lay_row, l).cpu()
+        ks = shm.local_view(lay_k, l).cpu()
+        ws = shm.local_view(lay_w, l).cpu()
+        meta = shm.local_view(res.recv_meta, l).cpu()
+        info = shm.local_view(res.recv_info, l).cpu().tolist()
+        live = [r for s in range(NPES) for r in range(info[1 + s], info[1 + s] + info[1 + NPES + s])]
+        assert off[0] == 0 and off[-1] == sum(int((meta[r, 0:K] >= 0).sum()) for r in live)
+        for e in range(epr):
+            got = sorted(zip(rows[off[e]:off[e + 1]].tolist(), ks[off[e]:off[e + 1]].tolist()))
+            want = sorted((r, k) for r in live for k in range(K) if meta[r, k] == e)
+            assert got == want, (l, e)
+            for p in range(off[e], off[e + 1]):
+                assert ws[p].item() == meta[rows[p], 8 + ks[p]].view(torch.float32).item()
+
+
+@pytest.mark.parametrize("mode", ["fixed-compact", "fixed-slotted", "staged-compact", "staged-slotted", "low-latency"])
 @pytest.mark.parametrize("T,H,E,K", [(96, 1024, 16, 4), (257, 7168, 32, 8), (8, 512, 4, 2)])
-def test_dispatch_fp8_and_combine(shm, layout, T, H, E, K):
+def test_dispatch_fp8_and_combine(shm, mode, T, H, E, K):
     from rocshmem_b200.ops import moe
-    d = moe.EpDispatcher(E, K, H, T + 3, layout=layout)
+    low_latency = mode == "low-latency"
+    layout = "slotted" if low_latency else mode.split("-")[1]
+    d = moe.EpDispatcher(E, K, H, T + 3, layout=layout, dynamic=mode.startswith("staged"), low_latency=low_latency,
+                         expert_layout=True)
     epr = E // NPES
     for rep in range(3):  # repeated use exercises the epoch / double-buffer logic
         x, idx, w, host = make_inputs(shm, T, H, E, K, seed=rep + 1, drop_some=(rep == 1))
@@ -77,6 +100,9 @@ def test_dispatch_fp8_and_combine(shm, layout, T, H, E, K):
                 if count == 0:
                     continue
                 rows = slice(first, first + count)
+                if low_latency:
+                    # Rows of one source arrive in the order its blocks took their slots: sort by token.
+                    rows = first + torch.argsort(meta[rows, 16])
                 assert meta[rows, 16].tolist() == [t for _, t in src_list]
                 assert meta[rows, 17].tolist() == [s] * count
                 xs, is_, ws = host[s]
@@ -96,6 +122,7 @@ def test_dispatch_fp8_and_combine(shm, layout, T, H, E, K):
                     if e >= 0:
                         pairs_per_expert[e] += 1
             assert info[1 + 2 * NPES:1 + 2 * NPES + epr] == pairs_per_expert
+        check_expert_pairs(shm, d, res, K, epr)
         # combine with "identity experts": y = dequantised input, weighted sum returns the token
         y = d.result_buffer()
         for l in range(NPES):
@@ -126,12 +153,14 @@ def test_dispatch_fp8_and_combine(shm, layout, T, H, E, K):
             assert torch.equal(got[:, 0], want) and torch.equal(got[:, -1], want)
         for t in (out, w, idx, x):
             shm.free(t)
+    d.destroy()
 
 
-def test_dispatch_bf16_rows_are_exact(shm):
+@pytest.mark.parametrize("dynamic", [False, True])
+def test_dispatch_bf16_rows_are_exact(shm, dynamic):
     from rocshmem_b200.ops import moe
     T, H, E, K = 130, 2048, 8, 3
-    d = moe.EpDispatcher(E, K, H, T, quantize=False)
+    d = moe.EpDispatcher(E, K, H, T, quantize=False, dynamic=dynamic)
     x, idx, w, host = make_inputs(shm, T, H, E, K, seed=9)
     res = d.dispatch(x, idx, w)
     check_clean(shm)

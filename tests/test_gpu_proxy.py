@@ -87,3 +87,54 @@ def test_device_atomics_through_the_ring_single_pe():
     finally:
         torch.cuda.synchronize()
         shm.finalize()
+
+
+STAT_PROXY_SLOT_NS, STAT_PROXY_PACK_NS, STAT_PROXY_HOST_NS, STAT_WAIT_NS = 30, 31, 32, 33
+
+
+def _fresh(**kw):
+    import rocshmem_b200 as shm
+    from rocshmem_b200 import _native
+    if shm.is_initialized():
+        shm.finalize()
+    shm.init(heap_size="64M", ROCSHMEM_WAIT_TIMEOUT_MS=5000, **kw)
+    return shm, _native.load_test_kernels()
+
+
+def test_warp_coalescing_merges_proxied_puts_and_gets_and_time_buckets_fill():
+    from rocshmem_b200 import runtime as rt
+    shm, k = _fresh(n_local=2, ROCSHMEM_USE_PROXY=1, ROCSHMEM_USE_WF_COAL=1)
+    try:
+        C = rt._C()
+        side = torch.cuda.Stream()
+        nbytes, threads = 4096, 32
+        src = shm.zeros(nbytes, torch.uint8)
+        dst = shm.zeros(nbytes, torch.uint8)
+        pats = []
+        for l in range(2):
+            p = torch.randint(0, 256, (nbytes,), generator=torch.Generator().manual_seed(5 + l), dtype=torch.uint8)
+            pats.append(p)
+            shm.local_view(src, l).copy_(p.cuda())
+        torch.cuda.synchronize()
+        shm.barrier_all()
+        C.reset_stats()
+        before = C.host_stats()[28]
+        for op, origin in ((RMA_PUT, lambda l: (l - 1) % 2), (RMA_GET, lambda l: (l + 1) % 2)):
+            for l in range(2):
+                shm.local_view(dst, l).zero_()
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                k.rma(op, SC_THREAD, dst.data_ptr(), src.data_ptr(), nbytes, 1, 0, threads, side.cuda_stream)
+            torch.cuda.synchronize()
+            assert shm.get_error()["count"] == 0
+            for l in range(2):
+                assert torch.equal(shm.local_view(dst, l).cpu(), pats[origin(l)]), (op, l)
+        executed = C.host_stats()[28] - before
+        # 32 lanes with adjacent equal shares: one command per warp and operation instead of 32
+        assert executed <= 2 * 2 * 2, executed
+        for l in range(2):
+            st = C.device_stats(l)
+            assert st[STAT_PROXY_PACK_NS] > 0 and st[STAT_PROXY_HOST_NS] > 0, st[28:34]
+    finally:
+        torch.cuda.synchronize()
+        shm.finalize()

@@ -23,7 +23,8 @@ CUDA_ENV = {"ROCSHMEM_TEST_BACKEND": "cuda", "NCCL_NVLS_ENABLE": "0"}
 
 @pytest.mark.parametrize("world", world_sizes())
 @pytest.mark.parametrize("scenario", ["host_plumbing", "store_bootstrap", "teams", "collectives_host",
-                                      "wait_and_signal", "gpu_device_suite", "gpu_library_collectives", "gpu_moe", "gpu_tp_fused", "gpu_models"])
+                                      "wait_and_signal", "gpu_device_suite", "gpu_library_collectives",
+                                      "gpu_proxied_collectives", "gpu_moe", "gpu_tp_fused", "gpu_models"])
 def test_scenario(scenario, world):
     if world == 0:
         pytest.skip("needs at least two GPUs")

@@ -55,7 +55,7 @@ def grouped(offsets, row_index, pair_k):
     return off, [sorted(zip(rows[a:b], ks[a:b])) for a, b in zip(off[:-1], off[1:])]
 
 
-def run_both(shm, entry, d, T, H, E, K, seed, out):
+def run_both(shm, entry, d, T, H, E, K, seed, out, side_stream=False):
     from rocshmem_b200.ops import moe
     dev = shm.device()
     x = shm.zeros((T, H), torch.bfloat16)
@@ -69,7 +69,11 @@ def run_both(shm, entry, d, T, H, E, K, seed, out):
     d.dispatch(x, idx, w)
     want = grouped(*d.expert_layout())
     offsets, row_index, pair_k = out
-    stream = torch.cuda.current_stream().cuda_stream
+    # A stream of the caller's own: the work is ordered after the dispatch, which ran on the current stream.
+    side = torch.cuda.Stream() if side_stream else None
+    if side is not None:
+        side.wait_stream(torch.cuda.current_stream())
+    stream = (side or torch.cuda.current_stream()).cuda_stream
     rc = entry(d.recv_meta.data_ptr(), d.recv_info.data_ptr(), 1, E, K, offsets.data_ptr(), row_index.data_ptr(),
                pair_k.data_ptr(), stream)
     assert rc == 0, f"rocshmem_b200_expert_layout_noalloc returned {rc}"
@@ -100,6 +104,7 @@ def test_noalloc_matches_regular_entry_point_twice(shm, entry):
     run_both(shm, entry, d_big, T, H, big, K, seed=12, out=out)
     run_both(shm, entry, d_small, T, H, small, K, seed=13, out=out)
     run_both(shm, entry, d_big, T, H, big, K, seed=14, out=out)
+    run_both(shm, entry, d_big, T, H, big, K, seed=15, out=out, side_stream=True)
 
 
 def test_noalloc_rejects_sizes_beyond_its_scratch(shm, entry):
