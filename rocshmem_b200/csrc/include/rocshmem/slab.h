@@ -73,7 +73,9 @@ __device__ inline void *rocshmemx_slab_alloc_wg(rocshmemx_slab_t slab, size_t by
   return shared_result;
 }
 
-// One allocation for the calling warp's active lanes: the lowest active lane allocates.
+// One allocation for the calling warp's active lanes: the lowest active lane allocates. Lanes that reach the call
+// separately (after divergent code) form separate groups with an allocation each; call __syncwarp() first when the
+// whole warp is meant to share one.
 __device__ inline void *rocshmemx_slab_alloc_wave(rocshmemx_slab_t slab, size_t bytes, size_t align = 16) {
   const unsigned active = __activemask();
   const int leader = __ffs(active) - 1;

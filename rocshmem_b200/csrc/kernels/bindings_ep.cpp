@@ -54,8 +54,6 @@ void bind_ep(py::module_ &m) {
         h.buf.phase_ns = P<unsigned long long>(get("phase_ns"));
         h.buf.recv_info = P<int>(get("recv_info"));
         h.buf.work_counter = P<unsigned long long>(get("work_counter"));
-        h.buf.stage_x = P<void>(get("stage_x"));
-        h.buf.stage_scales = P<float>(get("stage_scales"));
         h.buf.stage_meta = P<int>(get("stage_meta"));
         h.buf.item_tok = P<int>(get("item_tok"));
         h.buf.lay_offsets = P<int>(get("lay_offsets"));

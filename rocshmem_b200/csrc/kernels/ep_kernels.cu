@@ -13,10 +13,9 @@
 //      destinations' receive buffers, together with the scales and a 128-byte metadata record. There is
 //      no receiver-side copy. Two ways of sharing the work:
 //        fixed shares   a warp owns whole tokens of its block and sends each to all its destinations;
-//        staged pairs   every token is quantised once into a local staging buffer (while the count exchange is
-//                       in flight), then warps take (token, destination) pairs from per-destination counters
-//                       and copy staged rows, so that no warp is left with eight destinations while another
-//                       has one;
+//        pairs          warps take (token, destination) pairs from per-destination counters, so that no warp is
+//                       left with eight destinations while another has one; a row is quantised again for every
+//                       destination (re-reading it from L2 costs less than a staging pass that idles the links);
 //   D. blocks pair up with the same block of every peer (release/acquire flags), so when the kernel
 //      has finished on a rank, everything sent to that rank is visible to its next kernel;
 //   E. on request, after one more grid barrier, all blocks turn the received metadata into the expert-grouped
@@ -242,7 +241,8 @@ __device__ __forceinline__ bool build_expert_layout(const DispatchArgs &a, const
   return ok;
 }
 
-// STAGED: see "staged pairs" at the top of the file; otherwise fixed shares of whole tokens.
+// STAGED: (token, destination) pairs handed out through counters (see the top of the file); otherwise fixed shares
+// of whole tokens.
 template <bool STAGED>
 __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs a) {
   // masks [tpb] u64, ranks among the block's tokens per destination [tpb][P] int, pair ranks [tpb][K] int
@@ -281,8 +281,6 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   int *exp_cnt = rebase(a.buf.exp_cnt);
   unsigned long long *grid_counter = rebase(a.buf.grid_counter);
   int *recv_info = rebase(a.buf.recv_info);
-  char *stage_x = STAGED ? static_cast<char *>(rebase(a.buf.stage_x)) : nullptr;
-  float *stage_scales = STAGED ? rebase(a.buf.stage_scales) : nullptr;
   int *stage_meta = STAGED ? rebase(a.buf.stage_meta) : nullptr;
   int *item_tok = STAGED ? rebase(a.buf.item_tok) : nullptr;
 
@@ -369,10 +367,9 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   const int nscale = H / 128;
   constexpr int kBatch = 8;  // iterations (of 512 elements) whose loads are issued together
   if (STAGED) {
-    // ---- quantise the block's tokens once, locally, while the counts travel -----------------------------------
+    // ---- one record per token (global expert ids, weights, pair positions) for whichever warp sends its rows ------
     for (int tok = t0 + warp; tok < t1; tok += nwarps) {
       if (s_mask[tok - t0] == 0) continue;
-      int *rec = stage_meta + size_t(tok) * EP_META_WORDS;
       int word = 0;
       if (lane < unsigned(K)) {
         word = topk_idx[size_t(tok) * K + lane];
@@ -387,29 +384,7 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
         const int e = topk_idx[size_t(tok) * K + k];
         word = (e >= 0 && e < E) ? s_exp_base[e] + s_pair_rank[(tok - t0) * K + k] : 0;
       }
-      rec[lane] = word;
-      if (a.cfg.quantize) {
-        const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
-        int4 *dst = reinterpret_cast<int4 *>(stage_x + size_t(tok) * H);
-        for (int i0 = 0; i0 < iters; i0 += kBatch) {
-          int4 raw[2 * kBatch];
-#pragma unroll
-          for (int i = 0; i < kBatch; ++i) {
-            if (i0 + i < iters) {
-              raw[2 * i] = row[((i0 + i) * 512 + lane * 16) / 8];
-              raw[2 * i + 1] = row[((i0 + i) * 512 + lane * 16) / 8 + 1];
-            }
-          }
-#pragma unroll
-          for (int i = 0; i < kBatch; ++i) {
-            if (i0 + i < iters) {
-              float scale;
-              dst[(i0 + i) * 32 + lane] = quantize16(raw[2 * i], raw[2 * i + 1], &scale);
-              if ((lane & 7) == 0) stage_scales[size_t(tok) * nscale + (i0 + i) * 4 + lane / 8] = scale;
-            }
-          }
-        }
-      }
+      stage_meta[size_t(tok) * EP_META_WORDS + lane] = word;
     }
   }
   if (a.cfg.layout == EP_LAYOUT_SLOTTED) {
@@ -443,35 +418,62 @@ __global__ void __launch_bounds__(kEpThreads, 1) ep_dispatch_kernel(DispatchArgs
   if (stamp) phase_ns[3] = detail::now_ns();
 
   if (STAGED) {
-    // ---- C (staged pairs): warps take (token, destination) pairs from per-destination counters -----------------
-    // Warps start on different destinations and move on when a destination's rows are all taken.
+    // ---- C (pairs): warps take (token, destination) pairs from per-destination counters ------------------------
+    // Warps start on different destinations and move on when a destination's rows are all taken. A row is
+    // quantised again for every destination it goes to (it comes from L2 after the first time): cheaper than a
+    // staging pass during which the links would idle.
     const unsigned gwarp = b * nwarps + warp;
-    const size_t row_bytes = a.cfg.quantize ? size_t(H) : size_t(H) * 2;
-    const int nvec = static_cast<int>(row_bytes / 16);
     for (int dd = 0; dd < P; ++dd) {
       const int d = (me + 1 + gwarp + dd) % P;
       const int w = team_pe_to_world(t, d);
-      const int total = s_total[d];
+      const unsigned long long total = static_cast<unsigned long long>(s_total[d]);
       if (total == 0) continue;
-      for (;;) {
-        unsigned long long next = 0;
-        if (lane == 0) next = atomicAdd(work + parity * EP_MAX_RANKS + d, 1ull);
-        next = __shfl_sync(0xffffffffu, next, 0);
-        if (next >= static_cast<unsigned long long>(total)) break;
+      unsigned long long *queue = work + parity * EP_MAX_RANKS + d;
+      unsigned long long next = 0;
+      if (lane == 0) next = atomicAdd(queue, 1ull);
+      next = __shfl_sync(0xffffffffu, next, 0);
+      while (next < total) {
         const int item = static_cast<int>(next);
+        // The next item is claimed now, so that the counter's round trip overlaps this item's copies.
+        unsigned long long after = 0;
+        if (lane == 0) after = atomicAdd(queue, 1ull);
         const int tok = __ldcg(item_tok + size_t(d) * a.cfg.max_tokens + item);
         const int slot = s_base[d] + item;
         const int rec = __ldcg(stage_meta + size_t(tok) * EP_META_WORDS + lane);
-        const int4 *src = a.cfg.quantize ? reinterpret_cast<const int4 *>(stage_x + size_t(tok) * H)
-                                         : reinterpret_cast<const int4 *>(x + size_t(tok) * H);
-        copy_row_vec<16>(reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * row_bytes, w)), src, nvec, lane);
-        if (a.cfg.quantize && lane < unsigned(nscale / 4)) {
-          const float4 sc = __ldcg(reinterpret_cast<const float4 *>(stage_scales + size_t(tok) * nscale) + lane);
-          reinterpret_cast<float4 *>(remote_ptr(recv_scales + size_t(slot) * nscale, w))[lane] = sc;
+        const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
+        if (a.cfg.quantize) {
+          int4 *dst = reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H, w));
+          for (int i0 = 0; i0 < iters; i0 += kBatch) {
+            int4 raw[2 * kBatch];
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+              if (i0 + i < iters) {
+                raw[2 * i] = row[((i0 + i) * 512 + lane * 16) / 8];
+                raw[2 * i + 1] = row[((i0 + i) * 512 + lane * 16) / 8 + 1];
+              }
+            }
+#pragma unroll
+            for (int i = 0; i < kBatch; ++i) {
+              if (i0 + i < iters) {
+                float scale;
+                dst[(i0 + i) * 32 + lane] = quantize16(raw[2 * i], raw[2 * i + 1], &scale);
+                if ((lane & 7) == 0) s_scales[warp][(i0 + i) * 4 + lane / 8] = scale;
+              }
+            }
+          }
+          __syncwarp();
+          if (lane < unsigned(nscale / 4)) {
+            reinterpret_cast<float4 *>(remote_ptr(recv_scales + size_t(slot) * nscale, w))[lane] =
+                reinterpret_cast<const float4 *>(s_scales[warp])[lane];
+          }
+          __syncwarp();
+        } else {
+          copy_row_vec<8>(reinterpret_cast<int4 *>(remote_ptr(recv_x + size_t(slot) * H * 2, w)), row, H / 8, lane);
         }
         int word = rec;
         if (lane < unsigned(EP_MAX_TOPK)) word = (lane < unsigned(K) && rec >= 0 && rec / epr == d) ? rec % epr : -1;
         remote_ptr(recv_meta + size_t(slot) * EP_META_WORDS, w)[lane] = word;
+        next = __shfl_sync(0xffffffffu, after, 0);
       }
     }
   } else {
@@ -825,14 +827,16 @@ __global__ void __launch_bounds__(kCombineThreads, 1) ep_combine_kernel(CombineA
   const int split = DYNAMIC ? 1 : a.split;
   const int part = gwarp % split;
   const int vbegin = nvec / split * part, vend = nvec / split * (part + 1);
+  // Dynamic: the counter is fetched one token ahead, so that its round trip overlaps the current token's loads.
+  unsigned long long pending = 0;
+  if (DYNAMIC && lane == 0) pending = atomicAdd(work, 1ull) - a.work_base;
   for (int tok_static = gwarp / split;; tok_static += nwarps / split) {
     int tok;
     if (DYNAMIC) {
-      unsigned long long next = 0;
-      if (lane == 0) next = atomicAdd(work, 1ull) - a.work_base;
-      next = __shfl_sync(0xffffffffu, next, 0);
+      const unsigned long long next = __shfl_sync(0xffffffffu, pending, 0);
       if (next >= static_cast<unsigned long long>(a.num_tokens)) break;
       tok = static_cast<int>(next);
+      if (lane == 0) pending = atomicAdd(work, 1ull) - a.work_base;
     } else {
       if (tok_static >= a.num_tokens) break;
       tok = tok_static;
@@ -1017,9 +1021,7 @@ int ep_dispatch(rocshmem_team_t team, const EpConfig &cfg, const EpBuffers &buf,
   const size_t smem = size_t(tpb) * ((ht->world.size + cfg.top_k) * sizeof(int) + sizeof(unsigned long long));
   if (smem > 40 * 1024) return cudaErrorInvalidValue;  // use more blocks for this many tokens
   if (cfg.dynamic) {
-    if (!buf.work_counter || !buf.stage_meta || !buf.item_tok || (cfg.quantize && (!buf.stage_x || !buf.stage_scales))) {
-      return cudaErrorInvalidValue;
-    }
+    if (!buf.work_counter || !buf.stage_meta || !buf.item_tok) return cudaErrorInvalidValue;
     return launch_pes(ep_dispatch_kernel<true>, cfg.blocks, kEpThreads, smem, static_cast<cudaStream_t>(stream), true,
                       a);
   }

@@ -39,9 +39,8 @@ struct EpConfig {
   int quantize;        // 1: dispatch carries e4m3 rows + one fp32 scale per 128 elements; 0: bf16 rows
   int layout;          // EpLayout
   int blocks;          // blocks per PE (the same on every member)
-  int dynamic;         // 1: dispatch quantises every token once into a local staging buffer and hands (token,
-                       //    destination) pairs to warps through per-destination counters; combine hands tokens out
-                       //    through a counter. 0: fixed per-block shares of whole tokens.
+  int dynamic;         // 1: dispatch hands (token, destination) pairs to warps through per-destination counters;
+                       //    combine hands tokens out through a counter. 0: fixed per-block shares of whole tokens.
   int expert_layout;   // 1: the dispatch kernel also writes the expert-grouped pair lists (EpBuffers::lay_*)
   int low_latency;     // 1: one non-cooperative launch, a block per token, slotted layout, per-source signals
 };
@@ -75,10 +74,8 @@ struct EpBuffers {
   int *recv_info;           // [0] total rows, [1 + s] first row of source s, [1 + P + s] rows of source s,
                             // [1 + 2 P + e] (row, k) pairs of local expert e
   unsigned long long *work_counter;  // [EP_WORK_WORDS], see EP_WORK_*
-  // Staged hand-out (dynamic == 1): this rank's tokens, quantised once; local.
-  void *stage_x;            // [max_tokens, hidden] uint8 (unused without quantisation: rows are read from x)
-  float *stage_scales;      // [max_tokens, hidden / 128]
-  int *stage_meta;          // [max_tokens, EP_META_WORDS] record with global expert ids
+  // Pair hand-out (dynamic == 1), local.
+  int *stage_meta;          // [max_tokens, EP_META_WORDS] record of every token with global expert ids
   int *item_tok;            // [P][max_tokens] token of this rank's i-th row for destination d
   // Expert-grouped pair lists (expert_layout == 1), local outputs: positions lay_offsets[e] .. lay_offsets[e + 1]
   // belong to local expert e; lay_row / lay_k / lay_w give the received row, the top-k position and the gate

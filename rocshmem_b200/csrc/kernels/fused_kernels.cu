@@ -446,14 +446,6 @@ bool use_two_cta() {
   return on;
 }
 
-// ROCSHMEM_FP8_PIPE=1 selects the accumulate warps with two TMEM loads in flight (see gemm_fp8_core.cuh).
-bool use_fp8_pipe() {
-  static const bool on = [] {
-    const char *e = std::getenv("ROCSHMEM_FP8_PIPE");
-    return e != nullptr && e[0] != '\0' && e[0] != '0';
-  }();
-  return on;
-}
 
 // ---- block-scaled e4m3 variants -------------------------------------------------------------------------------
 // Same structure with the fp8 core: the push warps send the e4m3 rows and, as a second array, their
@@ -472,7 +464,7 @@ struct Ag8Args {
   unsigned epoch;
 };
 
-template <bool SWIGLU, bool PIPE>
+template <bool SWIGLU>
 __global__ void __launch_bounds__(gemm8::THREADS + 32, 1)
 ag_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, Ag8Args a) {
   extern __shared__ unsigned char smem_raw[];
@@ -495,10 +487,9 @@ ag_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                       reinterpret_cast<const char *>(a.x_s), reinterpret_cast<char *>(a.gathered_s),
                       size_t(gemm8::BM) * (a.k / 128) * sizeof(float), a.m_shard / gemm8::BM, a.ready};
   PlainEpilogue epi{a.c, static_cast<size_t>(SWIGLU ? a.n / 2 : a.n)};
-  gemm8::run<SWIGLU, true, PIPE>(&map_a, &map_b, a.gathered_s, a.b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
+  gemm8::run<SWIGLU, true>(&map_a, &map_b, a.gathered_s, a.b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
 }
 
-template <bool PIPE>
 __global__ void __launch_bounds__(gemm8::THREADS, 1)
 gemm_rs_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const float *a_scale, const float *b_scale, RsArgs a) {
@@ -515,7 +506,7 @@ gemm_rs_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   sched.m_shard = a.m_shard;
   sched.n = a.n;
   RsEpilogue epi{t, a.staging, t->my_pe, a.m_shard, a.n};
-  gemm8::run<false, false, PIPE>(&map_a, &map_b, a_scale, b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
+  gemm8::run<false, false>(&map_a, &map_b, a_scale, b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
   rs_reduce(a, t);
 }
 
@@ -610,8 +601,7 @@ int ag_gemm_fp8(rocshmem_team_t team, const void *x_q, const float *x_s, void *g
     if (e != cudaSuccess) return static_cast<int>(e);
     return launch_pes(kernel, sms, gemm8::THREADS + 32, gemm8::SMEM_BYTES, s, true, map_a, map_b, a);
   };
-  if (use_fp8_pipe()) return swiglu ? launch(ag_gemm_fp8_kernel<true, true>) : launch(ag_gemm_fp8_kernel<false, true>);
-  return swiglu ? launch(ag_gemm_fp8_kernel<true, false>) : launch(ag_gemm_fp8_kernel<false, false>);
+  return swiglu ? launch(ag_gemm_fp8_kernel<true>) : launch(ag_gemm_fp8_kernel<false>);
 }
 
 int gemm_rs_fp8(rocshmem_team_t team, const void *a_q, const float *a_scale, const void *b_q, const float *b_scale,
@@ -635,7 +625,7 @@ int gemm_rs_fp8(rocshmem_team_t team, const void *a_q, const float *a_scale, con
     return launch_pes(kernel, device_sm_count(), gemm8::THREADS, gemm8::SMEM_BYTES, static_cast<cudaStream_t>(stream),
                       true, map_a, map_b, a_scale, b_scale, a);
   };
-  return use_fp8_pipe() ? launch(gemm_rs_fp8_kernel<true>) : launch(gemm_rs_fp8_kernel<false>);
+  return launch(gemm_rs_fp8_kernel);
 }
 
 }  // namespace kernels

@@ -43,8 +43,6 @@ struct RowMajorEpilogue8 {
   }
 };
 
-// PIPE selects the accumulate warps' variant with two TMEM loads in flight (see gemm_fp8_core.cuh).
-template <bool PIPE>
 __global__ void __launch_bounds__(gemm8::THREADS, 1)
 gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 const float *a_scale, const float *b_scale, __nv_bfloat16 *c, int m, int n, int k) {
@@ -56,16 +54,7 @@ gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   sched.tiles_n = (n + gemm8::BN - 1) / gemm8::BN;
   sched.tiles = ((m + gemm8::BM - 1) / gemm8::BM) * sched.tiles_n;
   RowMajorEpilogue8 epi{c, static_cast<size_t>(n)};
-  gemm8::run<false, false, PIPE>(&map_a, &map_b, a_scale, b_scale, k / gemm8::KB, sched, epi, smem_raw, sh);
-}
-
-// ROCSHMEM_FP8_PIPE=1 switches the block-scaled kernels of this file to the pipelined accumulate warps.
-bool fp8_pipe() {
-  static const bool on = [] {
-    const char *e = std::getenv("ROCSHMEM_FP8_PIPE");
-    return e != nullptr && e[0] != '\0' && e[0] != '0';
-  }();
-  return on;
+  gemm8::run<false, false>(&map_a, &map_b, a_scale, b_scale, k / gemm8::KB, sched, epi, smem_raw, sh);
 }
 
 constexpr int kMaxGroups8 = 256;
@@ -108,7 +97,7 @@ struct GroupedScheduler8 {
   __device__ void side_role() const {}
 };
 
-template <bool SWIGLU, bool PIPE>
+template <bool SWIGLU>
 __global__ void __launch_bounds__(gemm8::THREADS, 1)
 grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                         const float *a_scale, const float *b_scale, __nv_bfloat16 *c, const int *offsets,
@@ -124,7 +113,7 @@ grouped_gemm_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_
   sched.n = n;
   sched.tiles_n = SWIGLU ? (n / 2 + gemm8::BN / 2 - 1) / (gemm8::BN / 2) : (n + gemm8::BN - 1) / gemm8::BN;
   RowMajorEpilogue8 epi{c, static_cast<size_t>(SWIGLU ? n / 2 : n)};
-  gemm8::run<SWIGLU, false, PIPE>(&map_a, &map_b, a_scale, b_scale, k / gemm8::KB, sched, epi, smem_raw, sh);
+  gemm8::run<SWIGLU, false>(&map_a, &map_b, a_scale, b_scale, k / gemm8::KB, sched, epi, smem_raw, sh);
 }
 
 template <typename K>
@@ -149,15 +138,9 @@ int gemm_fp8_blockscaled(const void *a_q, const float *a_scale, const void *b_q,
   if (!encode_tmap_2d(&map_a, a_q, m, k, 1, gemm8::BM) || !encode_tmap_2d(&map_b, b_q, n, k, 1, gemm8::BN / 2)) return -1;
   const int tiles = ((m + gemm8::BM - 1) / gemm8::BM) * ((n + gemm8::BN - 1) / gemm8::BN);
   const int grid = std::min(tiles, device_sm_count());
-  if (fp8_pipe()) {
-    if (int rc = prepare8(gemm_fp8_kernel<true>)) return rc;
-    gemm_fp8_kernel<true><<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-        map_a, map_b, a_scale, b_scale, static_cast<__nv_bfloat16 *>(c), m, n, k);
-  } else {
-    if (int rc = prepare8(gemm_fp8_kernel<false>)) return rc;
-    gemm_fp8_kernel<false><<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
-        map_a, map_b, a_scale, b_scale, static_cast<__nv_bfloat16 *>(c), m, n, k);
-  }
+  if (int rc = prepare8(gemm_fp8_kernel)) return rc;
+  gemm_fp8_kernel<<<grid, gemm8::THREADS, gemm8::SMEM_BYTES, static_cast<cudaStream_t>(stream)>>>(
+      map_a, map_b, a_scale, b_scale, static_cast<__nv_bfloat16 *>(c), m, n, k);
   return cudaGetLastError();
 }
 
@@ -181,10 +164,7 @@ int grouped_gemm_fp8_blockscaled(const void *a_q, const float *a_scale, const vo
                                                            static_cast<__nv_bfloat16 *>(c), offsets, groups, n, k);
     return cudaGetLastError();
   };
-  if (fp8_pipe()) {
-    return swiglu ? launch(grouped_gemm_fp8_kernel<true, true>) : launch(grouped_gemm_fp8_kernel<false, true>);
-  }
-  return swiglu ? launch(grouped_gemm_fp8_kernel<true, false>) : launch(grouped_gemm_fp8_kernel<false, false>);
+  return swiglu ? launch(grouped_gemm_fp8_kernel<true>) : launch(grouped_gemm_fp8_kernel<false>);
 }
 
 }  // namespace kernels

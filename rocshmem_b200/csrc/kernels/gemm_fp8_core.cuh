@@ -51,10 +51,7 @@ struct Shared {
 // and k_blocks must be a multiple of 4 (the scales are fetched four K blocks at a time). With SWIGLU
 // the tile's b_row[0] / b_row[1] are the gate and up rows of 128 output columns and the result is
 // silu(gate) * up (t.cols <= 128).
-// PIPE: the accumulate warps keep two TMEM loads in flight (the load of the next 16 columns is issued before the
-// FMAs of the current ones) and fetch the scales one K block ahead as scalars instead of four K blocks ahead as
-// vectors, which pays for the second register set.
-template <bool SWIGLU, bool LATE_A = false, bool PIPE = false, class Scheduler, class Epilogue>
+template <bool SWIGLU, bool LATE_A = false, class Scheduler, class Epilogue>
 __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap *map_b, const float *a_scale,
                                     const float *b_scale, int k_blocks, Scheduler &sched, Epilogue &epi,
                                     unsigned char *smem_raw, Shared &sh) {
@@ -153,52 +150,9 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
       // LATE_A: the A scales of a tile may still be on their way from another GPU until the producer has
       // seen the tile's rows arrive; the first finished K block proves it has. Read past L1 (__ldcg).
       if (LATE_A && !sm100::mbar_wait(&sh.tmem_full[buf], buf_phase, &sh.abort_flag, WAIT_BUDGET_NS)) break;
-      if (PIPE) {
-        const float *sa = reinterpret_cast<const float *>(sa4), *sb = reinterpret_cast<const float *>(sb4);
-        const float *su = reinterpret_cast<const float *>(su4);
-        float a_s = __ldcg(sa), b_s = sb[0], u_s = SWIGLU ? su[0] : 0.f;
-        for (int kb = 0; kb < k_blocks && !sh.abort_flag; ++kb) {
-          const float s_gate = a_s * b_s, s_up = a_s * u_s;
-          if (kb + 1 < k_blocks) {  // fetched one K block ahead of its use
-            a_s = __ldcg(sa + kb + 1);
-            b_s = sb[kb + 1];
-            if (SWIGLU) u_s = su[kb + 1];
-          }
-          if (!sm100::mbar_wait(&sh.tmem_full[buf], buf_phase, &sh.abort_flag, WAIT_BUDGET_NS)) break;
-          sm100::tcgen05_fence_after();
-          const uint32_t tbuf = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + buf * BN;
-          auto column = [&](int c) -> uint32_t {
-            return SWIGLU ? (c < 4 ? half * 64 + c * 16 : 128 + half * 64 + (c - 4) * 16) : half * 128 + c * 16;
-          };
-          uint32_t va[16], vb[16];
-          sm100::tmem_ld_32x16(tbuf + column(0), va);
-#pragma unroll
-          for (int c = 0; c < 8; c += 2) {
-            sm100::tmem_ld_wait_for(va);
-            sm100::tmem_ld_32x16(tbuf + column(c + 1), vb);   // in flight during the FMAs below
-            const float s0 = (SWIGLU && c >= 4) ? s_up : s_gate;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[c * 16 + i] = fmaf(s0, __uint_as_float(va[i]), acc[c * 16 + i]);
-            sm100::tmem_ld_wait_for(vb);
-            if (c + 2 < 8) sm100::tmem_ld_32x16(tbuf + column(c + 2), va);
-            const float s1 = (SWIGLU && c + 1 >= 4) ? s_up : s_gate;
-#pragma unroll
-            for (int i = 0; i < 16; ++i) acc[(c + 1) * 16 + i] = fmaf(s1, __uint_as_float(vb[i]), acc[(c + 1) * 16 + i]);
-          }
-          sm100::tcgen05_fence_before();
-          __syncwarp();
-          if (lane == 0) sm100::mbar_arrive(&sh.tmem_empty[buf]);
-          buf ^= 1u;
-          if (buf == 0) buf_phase ^= 1u;
-        }
-      }
-      float4 a_next = make_float4(0.f, 0.f, 0.f, 0.f), b_next = a_next, u_next = a_next;
-      if (!PIPE) {
-        a_next = __ldcg(sa4);
-        b_next = sb4[0];
-        if (SWIGLU) u_next = su4[0];
-      }
-      for (int kb4 = 0; !PIPE && kb4 < k_blocks / 4 && !sh.abort_flag; ++kb4) {
+      float4 a_next = __ldcg(sa4), b_next = sb4[0], u_next = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (SWIGLU) u_next = su4[0];
+      for (int kb4 = 0; kb4 < k_blocks / 4 && !sh.abort_flag; ++kb4) {
         const float4 a_cur = a_next, b_cur = b_next, u_cur = u_next;
         if (kb4 + 1 < k_blocks / 4) {  // fetched one group ahead of its use
           a_next = __ldcg(sa4 + kb4 + 1);

@@ -84,10 +84,9 @@ class EpDispatcher:
                  team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact",
                  blocks: Optional[int] = None, dynamic: Optional[bool] = None, expert_layout: bool = False,
                  low_latency: bool = False):
-        """``dynamic``: dispatch quantises every token once into a local staging buffer and hands (token,
-        destination) pairs to warps through per-destination counters, combine hands tokens out through a counter
-        (levels the tail when fixed shares carry unequal numbers of bytes; dispatch pays a second grid barrier for
-        it). ``None`` takes ``ROCSHMEM_EP_DYNAMIC`` (default on).
+        """``dynamic``: dispatch hands (token, destination) pairs to warps through per-destination counters and
+        combine hands tokens out through a counter (levels the tail when fixed shares carry unequal numbers of
+        bytes; dispatch pays a second grid barrier for it). ``None`` takes ``ROCSHMEM_EP_DYNAMIC`` (default on).
 
         ``expert_layout``: the dispatch kernel also groups the received (row, k) pairs by local expert
         (:meth:`expert_pairs`), which a grouped GEMM consumes directly.
@@ -142,10 +141,6 @@ class EpDispatcher:
         self._buffers = ["recv_x", "recv_scales", "recv_meta", "cnt_in", "exp_in", "sent_slot", "tok_mask", "blk_cnt",
                          "exp_cnt", "grid_counter", "phase_ns", "recv_info", "work_counter"]
         if self.dynamic:
-            if quantize:
-                self.stage_x = z((max_tokens, hidden), torch.uint8)
-                self.stage_scales = z((max_tokens, hidden // 128), torch.float32)
-                self._buffers += ["stage_x", "stage_scales"]
             self.stage_meta = z((max_tokens, C.EP_META_WORDS), torch.int32)
             self.item_tok = z((P, max_tokens), torch.int32)
             self._buffers += ["stage_meta", "item_tok"]

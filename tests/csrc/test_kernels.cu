@@ -527,6 +527,7 @@ __global__ void slab_kernel(rocshmemx_slab_t slab, size_t bytes, unsigned long l
   void *p = rocshmemx_slab_alloc(slab, bytes, 16);
   thread_ptrs[g] = reinterpret_cast<unsigned long long>(p);
   if (p != nullptr) *static_cast<unsigned int *>(p) = g;   // the block is usable memory
+  __syncwarp();  // the lanes left the compare-and-swap loop above at different times: converge before a warp-level call
   void *w = rocshmemx_slab_alloc_wave(slab, 64, 64);
   const unsigned long long w0 = __shfl_sync(0xffffffffu, reinterpret_cast<unsigned long long>(w), 0);
   if (w0 != reinterpret_cast<unsigned long long>(w)) atomicAdd(errors, 1);
