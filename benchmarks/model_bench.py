@@ -3,6 +3,8 @@
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
         --master-port 29545 benchmarks/model_bench.py --out bench_out/model_n8.json
+    python benchmarks/model_bench.py --skip tp_mlp --experts 32 --no-moe-baseline   # one rank's share of the MoE layer
+                                                                                 # on one GPU (also the ncu target)
 
 * TP MLP (default: 8192 tokens in total, d_model 8192, d_ff 28672, bf16): this package's two fused kernels
   (all-gather -> GEMM -> SwiGLU, GEMM -> reduce-scatter) against NCCL all-gather + cuBLAS + NCCL
@@ -107,11 +109,22 @@ def bench_moe(args, world, rank, res):
     idx, w = moe.make_routing(T, E, K, seed=100 + rank, device="cuda")
     out = layer(x, idx, w)
     torch.cuda.synchronize()
-    pairs = int(layer.d.expert_layout()[0][-1].item())
+    pairs = int(layer.d.recv_info[1 + 2 * world:].sum().item())
     assert pairs <= cap, (pairs, cap)
     t_layer = timed(lambda: layer(x, idx, w), args.iters)
     row = {"experts": E, "top_k": K, "hidden": H, "inter": I, "tokens_per_rank": T, "layer_us": t_layer,
-           "pairs_this_rank": pairs, "tokens_per_s_all_ranks": world * T / t_layer * 1e6}
+           "fused": bool(layer.fused), "pairs_this_rank": pairs, "tokens_per_s_all_ranks": world * T / t_layer * 1e6}
+    if args.moe_unfused:
+        # The same layer with separate gather and per-row reduction kernels, for comparison.
+        plain = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=2, pair_capacity=cap, fused=False)
+        out_plain = plain(x, idx, w)
+        torch.cuda.synchronize()
+        row["unfused_max_abs_diff"] = (out_plain.float() - out.float()).abs().max().item()
+        row["unfused_layer_us"] = timed(lambda: plain(x, idx, w), args.iters)
+        stages_plain = {}
+        plain(x, idx, w, stage_us=stages_plain)
+        row["unfused_stage_us_rank0"] = stages_plain
+        plain.destroy()
     flops = 2.0 * pairs * H * (2 * I) + 2.0 * pairs * I * H
     row["expert_tflops_this_rank"] = flops / t_layer / 1e6
     if args.moe_baseline:
@@ -154,11 +167,14 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--skip", default="", help="comma list of: tp_mlp, moe")
     ap.add_argument("--no-moe-baseline", dest="moe_baseline", action="store_false")
+    ap.add_argument("--moe-unfused", action="store_true", help="also time the layer with separate gather / reduction kernels")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+    os.environ.setdefault("MASTER_PORT", "29547")
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", local))
     shm.init(heap_size=24 << 30, device=local)
     res = {"n_gpus": world}
     skip = set(args.skip.split(","))

@@ -260,6 +260,17 @@ __device__ __forceinline__ double amo_fetch_add(double *target, double value, in
   return atomicAdd_system(remote_ptr(target, pe), value);
 }
 
+// Any atomic through the reverse-offload ring: `op` is the host's operation code (fetch 0, swap 1, cas 2, add 3,
+// and 4, or 5, xor 6). The reference routes every atomic of its reverse-offload backend through the host
+// (src/reverse_offload/context_ro_tmpl_device.hpp:210-275).
+template <typename T>
+__device__ __forceinline__ T amo_via_proxy(unsigned op, T *target, T value, T cond, int pe) {
+  using U = typename UIntOf<sizeof(T)>::type;
+  bool ok;
+  return from_bits<T>(static_cast<U>(proxy_submit(ROCSHMEM_PROXY_AMO, pe, target, nullptr, to_bits(value),
+                                                  to_bits(cond), op, sizeof(T), true, &ok)));
+}
+
 template <typename T>
 __device__ __forceinline__ void amo_add(T *target, T value, int pe) {
   // The result is unused, so the compiler emits the non-returning reduction form.
@@ -270,6 +281,7 @@ template <typename T>
 __device__ __forceinline__ T amo_swap(T *target, T value, int pe) {
   using U = typename UIntOf<sizeof(T)>::type;
   if (!check_pe(pe, 21) || !check_symmetric(target, sizeof(T), 21)) return T();
+  if (st().use_proxy) return amo_via_proxy<T>(1, target, value, T(), pe);
   return from_bits<T>(atomicExch_system(reinterpret_cast<U *>(remote_ptr(target, pe)), to_bits(value)));
 }
 
@@ -291,6 +303,7 @@ template <typename T>
 __device__ __forceinline__ T amo_fetch(T *target, int pe) {
   using U = typename UIntOf<sizeof(T)>::type;
   if (!check_pe(pe, 23) || !check_symmetric(target, sizeof(T), 23)) return T();
+  if (st().use_proxy) return amo_via_proxy<T>(0, target, T(), T(), pe);
   // An atomic read: OR with zero leaves the value unchanged for every type, including floats.
   return from_bits<T>(atomicOr_system(reinterpret_cast<U *>(remote_ptr(target, pe)), U(0)));
 }
@@ -299,18 +312,21 @@ template <typename T>
 __device__ __forceinline__ T amo_fetch_and(T *target, T value, int pe) {
   using U = typename UIntOf<sizeof(T)>::type;
   if (!check_pe(pe, 24) || !check_symmetric(target, sizeof(T), 24)) return T();
+  if (st().use_proxy) return amo_via_proxy<T>(4, target, value, T(), pe);
   return from_bits<T>(atomicAnd_system(reinterpret_cast<U *>(remote_ptr(target, pe)), to_bits(value)));
 }
 template <typename T>
 __device__ __forceinline__ T amo_fetch_or(T *target, T value, int pe) {
   using U = typename UIntOf<sizeof(T)>::type;
   if (!check_pe(pe, 25) || !check_symmetric(target, sizeof(T), 25)) return T();
+  if (st().use_proxy) return amo_via_proxy<T>(5, target, value, T(), pe);
   return from_bits<T>(atomicOr_system(reinterpret_cast<U *>(remote_ptr(target, pe)), to_bits(value)));
 }
 template <typename T>
 __device__ __forceinline__ T amo_fetch_xor(T *target, T value, int pe) {
   using U = typename UIntOf<sizeof(T)>::type;
   if (!check_pe(pe, 26) || !check_symmetric(target, sizeof(T), 26)) return T();
+  if (st().use_proxy) return amo_via_proxy<T>(6, target, value, T(), pe);
   return from_bits<T>(atomicXor_system(reinterpret_cast<U *>(remote_ptr(target, pe)), to_bits(value)));
 }
 
@@ -325,6 +341,13 @@ __device__ __forceinline__ void quiet() { __threadfence_system(); }
 // ---- signals ----------------------------------------------------------------------------------------------
 
 __device__ __forceinline__ void signal_op(uint64_t *sig_addr, uint64_t signal, int sig_op, int pe) {
+  if (st().use_proxy) {
+    // The ring is consumed in order by one host thread, so the signal follows the proxied payload; a payload that
+    // this thread (or its group) stored directly is ordered before the command by the fences of the submission.
+    bool ok;
+    proxy_submit(ROCSHMEM_PROXY_SIGNAL, pe, sig_addr, nullptr, signal, 0, static_cast<unsigned>(sig_op), 8, true, &ok);
+    return;
+  }
   unsigned long long *r = reinterpret_cast<unsigned long long *>(remote_ptr(sig_addr, pe));
   if (sig_op == ROCSHMEM_SIGNAL_ADD) {
     __threadfence_system();

@@ -211,6 +211,8 @@ enum rocshmem_proxy_op : unsigned int {
   ROCSHMEM_PROXY_FCOLLECT = 11,
   ROCSHMEM_PROXY_ALLTOALL = 12,
   ROCSHMEM_PROXY_P = 13,          // single element put by value: `size` holds the bits, dtype_size its width
+  ROCSHMEM_PROXY_AMO = 14,        // any other atomic: `op` is the host's operation code (fetch 0, swap 1, cas 2,
+                                  // add 3, and 4, or 5, xor 6), `size` the operand, `cond` the compare value
 };
 
 struct rocshmem_proxy_ring {

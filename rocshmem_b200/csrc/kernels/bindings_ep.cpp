@@ -104,6 +104,9 @@ void bind_ep(py::module_ &m) {
     check(moe_reduce_pairs(P<void>(pairs), P<int>(inverse), P<int>(recv_meta), P<int>(recv_info), n_ranks, top_k,
                            hidden, weighted, P<void>(y), P<void>(stream)), "moe_reduce_pairs");
   });
+  m.def("moe_zero_rows", [](uintptr_t recv_info, int n_ranks, int hidden, uintptr_t y, uintptr_t stream) {
+    check(moe_zero_rows(P<int>(recv_info), n_ranks, hidden, P<void>(y), P<void>(stream)), "moe_zero_rows");
+  });
   m.attr("EP_META_WORDS") = EP_META_WORDS;
   m.attr("EP_WORK_WORDS") = EP_WORK_WORDS;
   m.attr("EP_MAX_RANKS") = EP_MAX_RANKS;

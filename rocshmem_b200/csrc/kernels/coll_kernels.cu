@@ -500,6 +500,46 @@ int coll_blocks_for(size_t bytes) {
 
 bool nvls_available() { return Runtime::initialized() && Runtime::instance().mc_base() != nullptr; }
 
+namespace {
+template <typename K>
+void load_now(K kernel, int *rc) {
+  cudaFuncAttributes attr;
+  cudaError_t e = cudaFuncGetAttributes(&attr, kernel);
+  if (e != cudaSuccess && *rc == 0) *rc = static_cast<int>(e);
+}
+template <typename T>
+void load_allreduce_now(int *rc) {
+  load_now(allreduce_one_shot_kernel<T, ROCSHMEM_SUM>, rc);
+  load_now(allreduce_one_shot_kernel<T, OP_RUNTIME>, rc);
+  load_now(allreduce_two_shot_kernel<T, ROCSHMEM_SUM>, rc);
+  load_now(allreduce_two_shot_kernel<T, OP_RUNTIME>, rc);
+}
+}  // namespace
+
+// With lazy module loading the first launch of a kernel may have to wait for the kernels that are running. The
+// proxy thread launches these collectives precisely while a user kernel waits for their completion, so a process
+// that runs device collectives through the proxy loads all of them up front.
+int coll_preload() {
+  int rc = 0;
+  load_now(barrier_kernel, &rc);
+  load_now(push_kernel, &rc);
+  load_now(broadcast_relay_kernel, &rc);
+  load_now(broadcast_nvls_kernel, &rc);
+  load_allreduce_now<short>(&rc);
+  load_allreduce_now<int>(&rc);
+  load_allreduce_now<long long>(&rc);
+  load_allreduce_now<unsigned int>(&rc);
+  load_allreduce_now<unsigned long long>(&rc);
+  load_allreduce_now<float>(&rc);
+  load_allreduce_now<double>(&rc);
+  load_allreduce_now<__half>(&rc);
+  load_allreduce_now<__nv_bfloat16>(&rc);
+  load_now(allreduce_nvls_kernel<float>, &rc);
+  load_now(allreduce_nvls_kernel<__half>, &rc);
+  load_now(allreduce_nvls_kernel<__nv_bfloat16>, &rc);
+  return rc;
+}
+
 int coll_barrier(rocshmem_team_t team, void *stream) {
   return launch_pes(barrier_kernel, 1, 64, 0, static_cast<cudaStream_t>(stream), false, team);
 }

@@ -614,7 +614,23 @@ __global__ void __launch_bounds__(kLlThreads) ep_ll_dispatch_kernel(DispatchArgs
   if (blockIdx.x == 0 && tid == 0) phase_ns[0] = detail::now_ns();
 
   // Normally one token per block; the loop serves launches whose grid had to be capped.
+  const int iters = H / 512, nscale = H / 128;
+  constexpr int kWarps = kLlThreads / 32, kMine = (EP_MAX_HIDDEN / 512 + kWarps - 1) / kWarps;
   for (int tok = blockIdx.x; tok < T; tok += gridDim.x) {
+    // The row does not depend on the routing: its loads are issued first and travel while the slots are taken.
+    // The warps share the row: warp w takes the 512-element pieces w, w + 4, ...
+    const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
+    int4 raw[2 * kMine];
+    if (a.cfg.quantize) {
+#pragma unroll
+      for (int m = 0; m < kMine; ++m) {
+        const int i = warp + m * kWarps;
+        if (i < iters) {
+          raw[2 * m] = row[(i * 512 + lane * 16) / 8];
+          raw[2 * m + 1] = row[(i * 512 + lane * 16) / 8 + 1];
+        }
+      }
+    }
     if (tid < unsigned(K)) {
       const int e = topk_idx[size_t(tok) * K + tid];
       const bool valid = e >= 0 && e < E;
@@ -634,20 +650,7 @@ __global__ void __launch_bounds__(kLlThreads) ep_ll_dispatch_kernel(DispatchArgs
       sent_slot[size_t(tok) * P + tid] = slot;
     }
     __syncthreads();
-    const int iters = H / 512, nscale = H / 128;
-    const int4 *row = reinterpret_cast<const int4 *>(x + size_t(tok) * H);
     if (a.cfg.quantize) {
-      // The warps share the row: warp w takes the 512-element pieces w, w + 4, ... (all loads first).
-      constexpr int kWarps = kLlThreads / 32, kMine = (EP_MAX_HIDDEN / 512 + kWarps - 1) / kWarps;
-      int4 raw[2 * kMine];
-#pragma unroll
-      for (int m = 0; m < kMine; ++m) {
-        const int i = warp + m * kWarps;
-        if (i < iters) {
-          raw[2 * m] = row[(i * 512 + lane * 16) / 8];
-          raw[2 * m + 1] = row[(i * 512 + lane * 16) / 8 + 1];
-        }
-      }
 #pragma unroll
       for (int m = 0; m < kMine; ++m) {
         const int i = warp + m * kWarps;

@@ -10,11 +10,15 @@
 //               accumulator the MMA warp already fills the other one.
 // Policies supply the tile order (Scheduler), a hook the producer calls before it loads a tile's A
 // rows (used to wait for rows that another GPU is still sending) and the epilogue's destination.
+// A rows can also be gathered by index (warps 6..9 instead of TMA: one thread per tile row loads its row's 128
+// bytes of the K slab, optionally de-quantises e4m3 to bf16, and stores them with the 128-byte swizzle), and the
+// epilogue can scale rows and add them into the destination instead of storing them.
 // Every wait is bounded; on expiry the CTA sets its abort flag, all roles leave their loops, TMEM is
 // freed and a global error counter is bumped.
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "sm100_ptx.cuh"
 
@@ -34,6 +38,8 @@ constexpr int EPI_ROW_BYTES = EPI_COLS * 2 + 16;        // padded: conflict-free
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;      // one staging area per epilogue warp
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 4 * EPI_WARP_BYTES + 1024;  // + slack for 1024-byte alignment
 constexpr int THREADS = 192;
+constexpr int GATHER_WARPS = 4;                    // extra warps of kernels whose A rows are gathered by index
+constexpr int GATHER_THREADS = THREADS + GATHER_WARPS * 32;
 constexpr int TMEM_COLS = 512;     // two accumulators of 256 fp32 columns
 constexpr unsigned long long WAIT_BUDGET_NS = 2000000000ull;  // 2 s per wait
 
@@ -63,6 +69,18 @@ __device__ __forceinline__ void raster(int id, int row_blocks, int tiles_n, int 
 // One counter per translation unit (the kernels are not built as relocatable device code).
 static __device__ unsigned int g_gemm_errors = 0;
 
+// Where the A rows come from when they are gathered: tile row r of a tile reads source row
+// row_index[t.a_row + r]. A_GATHER 1: rows hold the MMA's element type (row_bytes = K * element size).
+// A_GATHER 2 (bf16 MMA only): rows are e4m3 with one fp32 scale per 128 elements (`scales` [rows, nscale]) and
+// are de-quantised to bf16 on the way into shared memory.
+struct GatherSrc {
+  const int *row_index;
+  const unsigned char *base;
+  size_t row_bytes;
+  const float *scales;
+  int nscale;
+};
+
 struct Shared {
   uint64_t full[STAGES];
   uint64_t empty[STAGES];
@@ -79,10 +97,13 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x));
 //            and          __device__ void side_role()             (run by warps beyond the six of the GEMM,
 //                                                                  if the kernel is launched with any).
 // Epilogue:  struct with  __device__ __nv_bfloat16 *row_ptr(const Tile &t, int row_in_tile)
-//            returning the address of output element (row, t.c_col), or nullptr to skip the row.
-template <bool IS_FP8, bool SWIGLU, class Scheduler, class Epilogue>
+//            returning the address of output element (row, t.c_col), or nullptr to skip the row; with EPI_ADD
+//            also  __device__ float row_scale(const Tile &t, int row_in_tile)  and the rows are multiplied by it
+//            and added to the destination (red.global.add on packed bf16) instead of stored.
+template <bool IS_FP8, bool SWIGLU, int A_GATHER = 0, bool EPI_ADD = false, class Scheduler, class Epilogue>
 __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap *map_b, int k_bytes,
-                                    Scheduler &sched, Epilogue &epi, unsigned char *smem_raw, Shared &sh) {
+                                    Scheduler &sched, Epilogue &epi, unsigned char *smem_raw, Shared &sh,
+                                    const GatherSrc *gather = nullptr) {
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   const int k_slabs = (k_bytes + SLAB_BYTES - 1) / SLAB_BYTES;
@@ -92,7 +113,8 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      sm100::mbar_init(&sh.full[s], 1);
+      // Gathered A: the stage is full when the B bytes have landed and every gather thread has stored its row.
+      sm100::mbar_init(&sh.full[s], A_GATHER ? 1 + GATHER_WARPS * 32 : 1);
       sm100::mbar_init(&sh.empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -101,7 +123,7 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
     }
     sh.abort_flag = 0;
     sm100::mbar_fence_init();
-    sm100::tma_prefetch_desc(map_a);
+    if (!A_GATHER) sm100::tma_prefetch_desc(map_a);
     sm100::tma_prefetch_desc(map_b);
   }
   if (warp == 1) sm100::tmem_alloc(&sh.tmem_base, TMEM_COLS);
@@ -124,8 +146,8 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
           if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) break;
           unsigned char *sa = smem + stage * STAGE_BYTES;
           unsigned char *sb = sa + A_STAGE_BYTES;
-          sm100::mbar_arrive_expect_tx(&sh.full[stage], STAGE_BYTES);
-          sm100::tma_load_2d(sa, map_a, &sh.full[stage], ks * SLAB_ELEMS, t.a_row);
+          sm100::mbar_arrive_expect_tx(&sh.full[stage], A_GATHER ? B_STAGE_BYTES : STAGE_BYTES);
+          if (!A_GATHER) sm100::tma_load_2d(sa, map_a, &sh.full[stage], ks * SLAB_ELEMS, t.a_row);
           sm100::tma_load_2d(sb, map_b, &sh.full[stage], ks * SLAB_ELEMS, t.b_row[0]);
           sm100::tma_load_2d(sb + B_STAGE_BYTES / 2, map_b, &sh.full[stage], ks * SLAB_ELEMS, t.b_row[1]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -164,6 +186,76 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         sm100::mma_commit(&sh.tmem_full[acc]);  // accumulator complete
       }
     }
+  } else if (A_GATHER != 0 && warp >= 6 && warp < 6 + GATHER_WARPS) {
+    // ---- gather producer: thread r owns tile row r -----------------------------------------------------------------
+    // Two K slabs are kept in flight in registers (loads of slab ks + 2 are issued right after slab ks has been
+    // stored), so that the L2 latency of a row's 128 bytes is covered by two stages of MMAs.
+    static_assert(A_GATHER == 0 || A_GATHER == 1 || (A_GATHER == 2 && !IS_FP8), "de-quantising gather feeds bf16");
+    constexpr int NV = A_GATHER == 2 ? 4 : 8;   // 16-byte source vectors per row and slab
+    const int r = (warp - 6) * 32 + lane;
+    const uint32_t row_off = static_cast<uint32_t>(r) * SLAB_BYTES;
+    const uint32_t sw = static_cast<uint32_t>(r & 7);
+    uint32_t stage = 0, phase = 0;
+    Tile t;
+    for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
+      const bool live = r < t.rows;
+      const long long src_row = live ? gather->row_index[t.a_row + r] : 0;
+      const int4 *src = reinterpret_cast<const int4 *>(gather->base + static_cast<size_t>(src_row) * gather->row_bytes);
+      const float *sc = A_GATHER == 2 ? gather->scales + static_cast<size_t>(src_row) * gather->nscale : nullptr;
+      int4 buf0[NV], buf1[NV];
+      auto fetch = [&](int4 (&b)[NV], int ks) {
+        if (live && ks < k_slabs) {
+#pragma unroll
+          for (int c = 0; c < NV; ++c) b[c] = __ldg(src + ks * NV + c);
+        } else {
+#pragma unroll
+          for (int c = 0; c < NV; ++c) b[c] = make_int4(0, 0, 0, 0);
+        }
+      };
+      auto put = [&](const int4 (&b)[NV], int ks) -> bool {
+        if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) return false;
+        unsigned char *sa = smem + stage * STAGE_BYTES + row_off;
+        if (A_GATHER == 2) {
+          // 64 e4m3 values of this slab -> 64 bf16 (eight 16-byte chunks); one scale covers two slabs.
+          const float scale = live ? __ldg(sc + ks / 2) : 0.f;
+#pragma unroll
+          for (int c = 0; c < NV; ++c) {
+            const unsigned short *p = reinterpret_cast<const unsigned short *>(&b[c]);
+            int4 o[2];
+            __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(o);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p[i], __NV_E4M3);
+              const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&h));
+              o2[i] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+            }
+            *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(2 * c) ^ sw) << 4)) = o[0];
+            *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(2 * c + 1) ^ sw) << 4)) = o[1];
+          }
+        } else {
+#pragma unroll
+          for (int c = 0; c < NV; ++c) *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(c) ^ sw) << 4)) = b[c];
+        }
+        sm100::fence_proxy_async_smem();
+        sm100::mbar_arrive(&sh.full[stage]);
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        return true;
+      };
+      fetch(buf0, 0);
+      fetch(buf1, 1);
+      bool ok = true;
+      for (int ks = 0; ks < k_slabs && ok; ks += 2) {
+        ok = put(buf0, ks);
+        if (!ok) break;
+        fetch(buf0, ks + 2);
+        if (ks + 1 < k_slabs) {
+          ok = put(buf1, ks + 1);
+          if (!ok) break;
+          fetch(buf1, ks + 3);
+        }
+      }
+      if (!ok || sh.abort_flag) break;
+    }
   } else if (warp >= 6) {
     // ---- optional extra warps (kernels launched with more than THREADS threads) ------------------------------
     sched.side_role();
@@ -183,6 +275,8 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
       sm100::tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       constexpr int OUT_CHUNKS = (SWIGLU ? BN / 2 : BN) / EPI_COLS;
+      float row_scale = 1.f;
+      if constexpr (EPI_ADD) row_scale = (quarter * 32 + lane) < t.rows ? epi.row_scale(t, quarter * 32 + lane) : 0.f;
 #pragma unroll 1
       for (int c = 0; c < OUT_CHUNKS; ++c) {
         if (c * EPI_COLS >= t.cols) break;
@@ -201,6 +295,10 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
             sm100::tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) f[i] = __uint_as_float(v[i]);
+          }
+          if (EPI_ADD) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) f[i] *= row_scale;
           }
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
@@ -223,10 +321,14 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
               const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
               __nv_bfloat16 *dst = out + col;
               if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(src);
+                if (EPI_ADD) sm100::red_add_bf16x8(dst, *reinterpret_cast<const int4 *>(src));
+                else *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(src);
               } else {
                 const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
-                for (int i = 0; i < 8 && col + i < t.cols; ++i) dst[i] = s16[i];
+                for (int i = 0; i < 8 && col + i < t.cols; ++i) {
+                  if (EPI_ADD) atomicAdd(dst + i, s16[i]);
+                  else dst[i] = s16[i];
+                }
               }
             }
           }

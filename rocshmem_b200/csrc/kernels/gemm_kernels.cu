@@ -172,6 +172,59 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   gemm::run<false, SWIGLU>(&map_a, &map_b, k * 2, sched, epi, smem_raw, sh);
 }
 
+// Grouped GEMM whose A rows are gathered by index from the buffers an expert-parallel dispatch filled (bf16 rows,
+// or e4m3 rows with 1 x 128 scales that are de-quantised on the way into shared memory): position p of the grouped
+// order reads source row row_index[p]. Replaces a separate gather / de-quantise pass over the activations.
+template <bool SWIGLU, int A_GATHER>
+__global__ void __launch_bounds__(gemm::GATHER_THREADS, 1)
+grouped_gemm_bf16_gather_kernel(const __grid_constant__ CUtensorMap map_b, gemm::GatherSrc src, __nv_bfloat16 *c,
+                                const int *offsets, int groups, int n, int k) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ gemm::Shared sh;
+  __shared__ int s_offsets[kMaxGroups + 1];
+  for (int i = threadIdx.x; i <= groups; i += blockDim.x) s_offsets[i] = offsets[i];
+  __syncthreads();
+  GroupedScheduler<SWIGLU> sched;
+  sched.offsets = s_offsets;
+  sched.groups = groups;
+  sched.n = n;
+  sched.tiles_n = SWIGLU ? (n / 2 + gemm::BN / 2 - 1) / (gemm::BN / 2) : (n + gemm::BN - 1) / gemm::BN;
+  RowMajorEpilogue epi{c, static_cast<size_t>(SWIGLU ? n / 2 : n)};
+  gemm::run<false, SWIGLU, A_GATHER>(&map_b, &map_b, k * 2, sched, epi, smem_raw, sh, &src);
+}
+
+// Rows of the grouped product are multiplied by a per-position weight and added to row row_index[p] of the
+// destination: the gate-weighted sum over a token's local experts happens in the epilogue (packed bf16
+// reductions in L2) instead of in a separate pass. The destination rows must be zero beforehand.
+struct ScatterAddEpilogue {
+  __nv_bfloat16 *y;
+  size_t ldc;
+  const int *row_index;
+  const float *weight;
+  __device__ __nv_bfloat16 *row_ptr(const gemm::Tile &t, int row) const {
+    return y + static_cast<size_t>(row_index[t.c_row + row]) * ldc + t.c_col;
+  }
+  __device__ float row_scale(const gemm::Tile &t, int row) const { return weight ? weight[t.c_row + row] : 1.0f; }
+};
+
+__global__ void __launch_bounds__(gemm::THREADS, 1)
+grouped_gemm_bf16_scatter_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                                 __nv_bfloat16 *y, const int *offsets, const int *row_index, const float *weight,
+                                 int groups, int n, int k) {
+  extern __shared__ unsigned char smem_raw[];
+  __shared__ gemm::Shared sh;
+  __shared__ int s_offsets[kMaxGroups + 1];
+  for (int i = threadIdx.x; i <= groups; i += blockDim.x) s_offsets[i] = offsets[i];
+  __syncthreads();
+  GroupedScheduler<false> sched;
+  sched.offsets = s_offsets;
+  sched.groups = groups;
+  sched.n = n;
+  sched.tiles_n = (n + gemm::BN - 1) / gemm::BN;
+  ScatterAddEpilogue epi{y, static_cast<size_t>(n), row_index, weight};
+  gemm::run<false, false, 0, true>(&map_a, &map_b, k * 2, sched, epi, smem_raw, sh);
+}
+
 template <typename K>
 int prepare(K kernel) {
   // Kernels of different instantiations share one function-pointer type, so the attribute is set
@@ -252,6 +305,48 @@ int grouped_gemm_bf16(const void *a, const void *b, void *c, const int *offsets,
     grouped_gemm_bf16_kernel<false><<<grid, gemm::THREADS, gemm::SMEM_BYTES, s>>>(
         map_a, map_b, static_cast<__nv_bfloat16 *>(c), offsets, groups, n, k);
   }
+  return cudaGetLastError();
+}
+
+int grouped_gemm_bf16_gathered(const void *a_rows, int a_is_fp8, const float *a_scales, const int *row_index,
+                               const void *b, void *c, const int *offsets, int groups, int n, int k, int swiglu,
+                               void *stream) {
+  if (groups <= 0 || groups > kMaxGroups || n <= 0 || k <= 0 || (k % 128) != 0) return cudaErrorInvalidValue;
+  if (swiglu && (n % 2) != 0) return cudaErrorInvalidValue;
+  if (a_rows == nullptr || row_index == nullptr || (a_is_fp8 && a_scales == nullptr)) return cudaErrorInvalidValue;
+  CUtensorMap map_b;
+  if (!encode_tmap_2d(&map_b, b, static_cast<uint64_t>(groups) * n, k, 2, gemm::BN / 2)) return -1;
+  gemm::GatherSrc src{row_index, static_cast<const unsigned char *>(a_rows),
+                      a_is_fp8 ? static_cast<size_t>(k) : static_cast<size_t>(k) * 2, a_scales, k / 128};
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = device_sm_count();
+  auto launch = [&](auto kernel) -> int {
+    if (int rc = prepare(kernel)) return rc;
+    kernel<<<grid, gemm::GATHER_THREADS, gemm::SMEM_BYTES, s>>>(map_b, src, static_cast<__nv_bfloat16 *>(c), offsets,
+                                                                groups, n, k);
+    return cudaGetLastError();
+  };
+  if (a_is_fp8) {
+    return swiglu ? launch(grouped_gemm_bf16_gather_kernel<true, 2>) : launch(grouped_gemm_bf16_gather_kernel<false, 2>);
+  }
+  return swiglu ? launch(grouped_gemm_bf16_gather_kernel<true, 1>) : launch(grouped_gemm_bf16_gather_kernel<false, 1>);
+}
+
+int grouped_gemm_bf16_scatter_add(const void *a, const void *b, void *y, const int *offsets, const int *row_index,
+                                  const float *weights, int groups, int max_rows, int n, int k, void *stream) {
+  if (groups <= 0 || groups > kMaxGroups || max_rows <= 0 || n <= 0 || k <= 0 || (k % 8) != 0 || (n % 8) != 0) {
+    return cudaErrorInvalidValue;
+  }
+  if (row_index == nullptr || (reinterpret_cast<uintptr_t>(y) & 15u) != 0) return cudaErrorInvalidValue;
+  CUtensorMap map_a, map_b;
+  if (!encode_tmap_2d(&map_a, a, max_rows, k, 2, gemm::BM) ||
+      !encode_tmap_2d(&map_b, b, static_cast<uint64_t>(groups) * n, k, 2, gemm::BN / 2)) {
+    return -1;
+  }
+  if (int rc = prepare(grouped_gemm_bf16_scatter_kernel)) return rc;
+  grouped_gemm_bf16_scatter_kernel<<<device_sm_count(), gemm::THREADS, gemm::SMEM_BYTES,
+                                     static_cast<cudaStream_t>(stream)>>>(
+      map_a, map_b, static_cast<__nv_bfloat16 *>(y), offsets, row_index, weights, groups, n, k);
   return cudaGetLastError();
 }
 

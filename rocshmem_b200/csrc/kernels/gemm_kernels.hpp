@@ -31,6 +31,20 @@ int gemm_bf16_one_cta(const void *a, const void *b, void *c, int m, int n, int k
 int grouped_gemm_bf16(const void *a, const void *b, void *c, const int *offsets, int groups, int max_rows,
                       int n, int k, int swiglu, void *stream);
 
+// The grouped GEMM fed directly by the buffers of an expert-parallel dispatch: position p of the grouped order
+// (offsets as above) reads row row_index[p] of `a_rows`, which holds bf16 rows [*, K] or, with a_is_fp8 != 0, e4m3
+// rows [*, K] with one fp32 scale per 128 elements in `a_scales` [*, K / 128] (de-quantised to bf16 on the way
+// into shared memory). K must be a multiple of 128. Output as for grouped_gemm_bf16, in grouped order.
+int grouped_gemm_bf16_gathered(const void *a_rows, int a_is_fp8, const float *a_scales, const int *row_index,
+                               const void *b, void *c, const int *offsets, int groups, int n, int k, int swiglu,
+                               void *stream);
+// The grouped GEMM whose result rows are scaled and summed where they belong: y[row_index[p], :] += weights[p] *
+// (A[p, :] * B[g]^T) for every position p of group g (weights == nullptr: 1). y [*, N] bf16 must hold zeros (or the
+// values to add to) beforehand; sums of several positions into one row are packed bf16 reductions in L2, so the
+// order of additions, and with it the last bit of the result, may differ between runs. N must be a multiple of 8.
+int grouped_gemm_bf16_scatter_add(const void *a, const void *b, void *y, const int *offsets, const int *row_index,
+                                  const float *weights, int groups, int max_rows, int n, int k, void *stream);
+
 // Device-side status of the last GEMM launched by this process: 0 ok, otherwise the number of
 // CTAs whose bounded wait expired (they released their TMEM and returned early).
 int gemm_error_count();

@@ -21,6 +21,8 @@ enum AllreduceAlgo : int {
 };
 
 // ---- collectives on the symmetric heap (coll_kernels.cu) -----------------------------------------------
+// Loads every collective kernel of the library now (see coll_kernels.cu); 0 or the first CUDA error.
+int coll_preload();
 int coll_barrier(rocshmem_team_t team, void *stream);
 int coll_allreduce(rocshmem_team_t team, void *dest, const void *source, size_t nelems, int dtype,
                    int op, int algo, void *stream);

@@ -134,7 +134,27 @@ __global__ void reduce_pairs_kernel(const __nv_bfloat16 *pairs, const int *inver
   }
 }
 
+// Zeroes the received rows listed in recv_info (16 bytes per thread and step).
+__global__ void zero_rows_kernel(const int *recv_info, int n_ranks, int hidden, __nv_bfloat16 *y) {
+  const size_t vec_per_row = size_t(hidden) / 8;
+  for (int s = 0; s < n_ranks; ++s) {
+    const size_t first = recv_info[1 + s], count = recv_info[1 + n_ranks + s];
+    int4 *base = reinterpret_cast<int4 *>(y + first * hidden);
+    const size_t total = count * vec_per_row;
+    for (size_t i = size_t(blockIdx.x) * blockDim.x + threadIdx.x; i < total; i += size_t(gridDim.x) * blockDim.x) {
+      base[i] = make_int4(0, 0, 0, 0);
+    }
+  }
+}
+
 }  // namespace
+
+int moe_zero_rows(const int *recv_info, int n_ranks, int hidden, void *y_bf16, void *stream) {
+  if (hidden <= 0 || hidden % 8 || n_ranks < 1) return cudaErrorInvalidValue;
+  zero_rows_kernel<<<static_cast<unsigned>(device_sm_count() * 4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      recv_info, n_ranks, hidden, static_cast<__nv_bfloat16 *>(y_bf16));
+  return cudaGetLastError();
+}
 
 int moe_gather_rows(const void *recv_x, const float *recv_scales, int fp8, const int *offsets, int experts,
                     const int *row_index, int hidden, void *out_bf16, void *stream) {

@@ -19,5 +19,9 @@ int moe_inverse_map(const int *offsets, int experts, const int *row_index, const
 int moe_reduce_pairs(const void *pairs_bf16, const int *inverse, const int *recv_meta, const int *recv_info,
                      int n_ranks, int top_k, int hidden, int weighted, void *y_bf16, void *stream);
 
+// Zeroes the rows of y [*, hidden] (bf16) that recv_info lists as received (the destination of a scatter-add
+// grouped GEMM must start from zero).
+int moe_zero_rows(const int *recv_info, int n_ranks, int hidden, void *y_bf16, void *stream);
+
 }  // namespace kernels
 }  // namespace rocshmem

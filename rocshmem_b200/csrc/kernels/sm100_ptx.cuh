@@ -101,6 +101,16 @@ __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.comm
 __device__ __forceinline__ void bulk_wait_read_all() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void bulk_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async;" ::: "memory"); }
+// Makes this thread's earlier shared-memory writes (generic proxy) visible to the async proxy (TMA, tcgen05.mma):
+// the writer executes it after its stores and before it signals the reader.
+__device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// Adds eight bf16 values (four packed pairs) to 16 bytes of global memory, no return value. The address must be
+// 16-byte aligned.
+__device__ __forceinline__ void red_add_bf16x8(void *gmem, const int4 &v) {
+  asm volatile("red.global.add.noftz.v4.bf16x2 [%0], {%1, %2, %3, %4};"
+               ::"l"(gmem), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w)
+               : "memory");
+}
 
 // ---- tcgen05 / TMEM --------------------------------------------------------------------------------------------
 // One full warp allocates `cols` (power of two, 32..512) TMEM columns; the base address is written to smem.

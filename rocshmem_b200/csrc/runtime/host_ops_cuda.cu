@@ -70,6 +70,9 @@ class CudaHostOps final : public HostOps {
     // running kernels, and the proxy thread launches it precisely while a kernel waits for its result.
     cudaFuncAttributes attr;
     check(cudaFuncGetAttributes(&attr, host_amo_kernel), "helper kernel load");
+    if (rt->config().use_proxy && rt->config().proxy_collectives) {
+      check(static_cast<cudaError_t>(kernels::coll_preload()), "collective kernel load");
+    }
   }
   ~CudaHostOps() override {
     if (slots_) cudaFreeHost(slots_);

@@ -210,6 +210,11 @@ void Proxy::execute(rocshmem_proxy_cmd &cmd, uint64_t) {
         fetched = ops.amo(ctx, AmoOp::CAS, dtype_for_size(cmd.dtype_size),
                           reinterpret_cast<void *>(cmd.dst), cmd.size, cmd.cond, cmd.pe);
         break;
+      case ROCSHMEM_PROXY_AMO:
+        if (cmd.op > static_cast<unsigned>(AmoOp::XOR)) throw std::invalid_argument("atomic operation code");
+        fetched = ops.amo(ctx, static_cast<AmoOp>(cmd.op), dtype_for_size(cmd.dtype_size),
+                          reinterpret_cast<void *>(cmd.dst), cmd.size, cmd.cond, cmd.pe);
+        break;
       case ROCSHMEM_PROXY_SIGNAL:
         fetched = ops.amo(ctx, cmd.op == ROCSHMEM_SIGNAL_ADD ? AmoOp::ADD : AmoOp::SWAP, DType::U64,
                           reinterpret_cast<void *>(cmd.dst), cmd.size, 0, cmd.pe);

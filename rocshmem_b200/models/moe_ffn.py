@@ -1,10 +1,17 @@
 """Expert-parallel MoE feed-forward layer (SwiGLU experts) built from this package's kernels.
 
-One call runs, stream-ordered and without a host synchronisation::
+One call runs, stream-ordered and without a host synchronisation, as four kernels (plus a memset-like one on a
+side stream)::
 
-    dispatch (fp8 1x128 rows over NVLink)  ->  expert layout  ->  gather + de-quantise into expert order
-      ->  grouped GEMM [gate | up] with SwiGLU epilogue (tcgen05)  ->  grouped GEMM down (tcgen05)
-      ->  per-row sum over the row's local experts, gate-weighted  ->  combine (pull over NVLink)
+    dispatch       fp8 1x128 rows over NVLink; its tail groups the received (row, k) pairs by local expert
+    gate/up GEMM   grouped tcgen05 GEMM whose producer warps gather the received rows by index (de-quantising
+                   e4m3 to bf16 on the way into shared memory), SwiGLU in the epilogue
+    down GEMM      grouped tcgen05 GEMM whose epilogue multiplies every row by its gate weight and adds it into
+                   the row's slot of the result buffer (the sum over a token's local experts)
+    combine        pull over NVLink, sum over the ranks a token went to
+
+``fused=False`` keeps the separate gather and per-row reduction kernels (the block-scaled e4m3 experts still use
+them).
 
 Experts are sharded over the team: rank r owns global experts ``[r * E_local, (r + 1) * E_local)``.
 The reference has no model code; its nearest building block is the fixed-size alltoall
@@ -40,10 +47,15 @@ class MoEFeedForward:
 
     def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, max_tokens: int,
                  team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact", seed: int = 0,
-                 pair_capacity: Optional[int] = None, fp8_experts: bool = False):
+                 pair_capacity: Optional[int] = None, fp8_experts: bool = False, fused: Optional[bool] = None,
+                 low_latency: bool = False):
         if rt.n_local_pes() != 1:
             raise RuntimeError("MoEFeedForward needs one PE per process")
-        self.d = moe.EpDispatcher(num_experts, top_k, hidden, max_tokens, team=team, quantize=quantize, layout=layout)
+        self.fused = (not fp8_experts and hidden % 128 == 0) if fused is None else bool(fused)
+        if self.fused and (fp8_experts or hidden % 128):
+            raise ValueError("the fused path needs bf16 experts and hidden % 128 == 0")
+        self.d = moe.EpDispatcher(num_experts, top_k, hidden, max_tokens, team=team, quantize=quantize, layout=layout,
+                                  expert_layout=self.fused, low_latency=low_latency)
         self.hidden, self.inter, self.top_k = hidden, inter, top_k
         self.n_ranks, self.e_local = self.d.n_ranks, self.d.experts_per_rank
         dev = rt.device()
@@ -54,10 +66,14 @@ class MoEFeedForward:
         cap = pair_capacity or self.n_ranks * max_tokens * top_k
         self.pair_capacity = cap
         bf = dict(dtype=torch.bfloat16, device=dev)
-        self.xs = torch.zeros((cap, hidden), **bf)      # rows in expert order
         self.h = torch.zeros((cap, inter), **bf)        # silu(gate) * up
-        self.yp = torch.zeros((cap, hidden), **bf)      # expert outputs per pair
-        self.inverse = torch.zeros(self.n_ranks * max_tokens * top_k, dtype=torch.int32, device=dev)
+        if self.fused:
+            self.side = torch.cuda.Stream()
+            self.ev_dispatched, self.ev_zeroed = torch.cuda.Event(), torch.cuda.Event()
+        else:
+            self.xs = torch.zeros((cap, hidden), **bf)      # rows in expert order
+            self.yp = torch.zeros((cap, hidden), **bf)      # expert outputs per pair
+            self.inverse = torch.zeros(self.n_ranks * max_tokens * top_k, dtype=torch.int32, device=dev)
         self.kernel_launches = 0
         # Block-scaled e4m3 experts: the received e4m3 rows feed the first grouped GEMM as they are (no
         # de-quantisation), the hidden activation is re-quantised for the second one.
@@ -99,6 +115,30 @@ class MoEFeedForward:
         mark("start")
         d.dispatch(x, topk_idx, topk_weights, stream=stream)
         mark("dispatch")
+        if self.fused:
+            cur = torch.cuda.ExternalStream(stream) if isinstance(stream, int) else (stream or torch.cuda.current_stream())
+            offsets, lay_row, _, lay_w = d.expert_pairs()
+            y = d.result_buffer()
+            # The result rows start from zero; clearing them runs beside the first GEMM.
+            self.ev_dispatched.record(cur)
+            self.side.wait_event(self.ev_dispatched)
+            C.moe_zero_rows(d.recv_info.data_ptr(), self.n_ranks, self.hidden, y.data_ptr(), self.side.cuda_stream)
+            self.ev_zeroed.record(self.side)
+            gemm.grouped_gemm_bf16_gathered(d.recv_x, lay_row, self.w13, offsets,
+                                            a_scales=d.recv_scales if d.quantize else None, swiglu=True, out=self.h,
+                                            stream=stream)
+            mark("gemm_gate_up")
+            cur.wait_event(self.ev_zeroed)
+            gemm.grouped_gemm_bf16_scatter_add(self.h, self.w2, offsets, lay_row, y, weights=lay_w, stream=stream)
+            mark("gemm_down")
+            out = d.combine(y, topk_idx, topk_weights, x.shape[0], weighted=False, out=out, stream=stream)
+            mark("combine")
+            self.kernel_launches += (d.kernel_launches - before) + 3
+            if stage_us is not None:
+                torch.cuda.synchronize()
+                for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
+                    stage_us[name] = a.elapsed_time(b) * 1e3
+            return out
         offsets, row_index, pair_k = d.expert_layout(stream=stream)
         C.moe_inverse_map(offsets.data_ptr(), self.e_local, row_index.data_ptr(), pair_k.data_ptr(), self.top_k,
                           self.inverse.data_ptr(), s)

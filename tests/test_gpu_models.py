@@ -23,12 +23,13 @@ def clean(shm):
     assert err["count"] == 0, err
 
 
+@pytest.mark.parametrize("fused", [True, False])
 @pytest.mark.parametrize("quantize", [True, False])
 @pytest.mark.parametrize("E,K,H,I,T", [(8, 2, 1024, 512, 200), (16, 8, 2048, 256, 333)])
-def test_moe_feed_forward(shm, quantize, E, K, H, I, T):
+def test_moe_feed_forward(shm, quantize, fused, E, K, H, I, T):
     from rocshmem_b200.models import moe_ffn
     from rocshmem_b200.ops import gemm, moe
-    layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T + 5, quantize=quantize, seed=2)
+    layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T + 5, quantize=quantize, seed=2, fused=fused)
     for rep in range(2):
         x = torch.randn(T, H, generator=torch.Generator().manual_seed(rep + 1)).to(torch.bfloat16)
         idx, w = moe.make_routing(T, E, K, seed=50 + rep)
@@ -41,6 +42,7 @@ def test_moe_feed_forward(shm, quantize, E, K, H, I, T):
         want = moe_ffn.reference_forward(x, idx, w, H, I, seed=2, quantize=quantize)
         err = (out.float().cpu() - want).abs().max().item()
         assert err <= 3e-2 * want.abs().max().item() + 0.02, (rep, err, want.abs().max().item())
+    layer.destroy()
 
 
 @pytest.mark.parametrize("d_model,d_ff,m", [(1024, 512, 256), (2048, 1280, 384)])

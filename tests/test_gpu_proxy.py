@@ -9,7 +9,7 @@ pytestmark = pytest.mark.gpu
 NPES = 2
 RMA_PUT, RMA_GET = 0, 2
 SC_THREAD = 0
-A_FADD = 0
+A_FADD, A_FINC, A_ADD, A_INC, A_FCSWAP, A_FETCH, A_SET, A_SWAP, A_FAND, A_AND, A_FOR, A_OR, A_FXOR, A_XOR = range(14)
 PROXY_CMD = 28  # ROCSHMEM_STAT_PROXY_CMD
 
 
@@ -73,17 +73,45 @@ def test_device_atomics_through_the_ring_single_pe():
         assert rt._C().proxy_running()
         side = torch.cuda.Stream()
         threads, iters = 8, 3
+        msgs = threads * iters
         target = shm.zeros(1, torch.int64)
         ret = shm.zeros(threads, torch.int64)
-        torch.cuda.synchronize()
-        with torch.cuda.stream(side):
-            k.amo(A_FADD, target.data_ptr(), ret.data_ptr(), iters, 1, threads, side.cuda_stream)
-        torch.cuda.synchronize()
-        err = shm.get_error()
-        assert err["count"] == 0, err
-        msgs = threads * iters
-        assert int(target.cpu()[0]) == 2 * msgs
-        assert int(ret.max().cpu()) == 2 * (msgs - 1)
+        before = rt._C().host_stats()[PROXY_CMD]
+        # Every atomic family goes through the ring (the reference's reverse-offload backend routes all of them
+        # through the host, src/reverse_offload/context_ro_tmpl_device.hpp:210-275); oracles as in the direct test.
+        for test in range(14):
+            target.zero_()
+            ret.zero_()
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                k.amo(test, target.data_ptr(), ret.data_ptr(), iters, 1, threads, side.cuda_stream)
+            torch.cuda.synchronize()
+            err = shm.get_error()
+            assert err["count"] == 0, (test, err)
+            final, best = int(target.cpu()[0]), int(ret.max().cpu())
+            want = {A_FADD: (2 * msgs, 2 * (msgs - 1)), A_FINC: (msgs, msgs - 1), A_ADD: (2 * msgs, 0),
+                    A_INC: (msgs, 0), A_FCSWAP: (msgs, msgs - 1), A_FETCH: (0, 0), A_SET: (44, 0), A_SWAP: (1, 1),
+                    A_FAND: (0, 0), A_AND: (0, 0), A_FOR: (0xFFFF, 0xFFFF), A_OR: (0xFFFF, 0),
+                    A_FXOR: (0xFFFF if msgs % 2 else 0, 0xFFFF), A_XOR: (0xFFFF if msgs % 2 else 0, 0)}[test]
+            assert (final, best) == want, (test, final, best, want)
+        assert rt._C().host_stats()[PROXY_CMD] - before >= 14 * msgs, "the atomics did not go through the ring"
+        # put with signal: the payload is stored directly (the one PE is its own neighbour), the signal is a command.
+        nbytes = 64 * 128
+        src, dst = shm.zeros(nbytes, torch.uint8), shm.zeros(nbytes, torch.uint8)
+        sig, fetched = shm.zeros(1, torch.int64), shm.zeros(2, torch.int64)
+        src.fill_(ord("7"))
+        for sig_op, start, expect in ((0, 123, 1), (1, 123, 123 + 64)):
+            sig.fill_(start)
+            dst.zero_()
+            torch.cuda.synchronize()
+            with torch.cuda.stream(side):
+                k.signal(SC_THREAD, sig_op, dst.data_ptr(), src.data_ptr(), nbytes, sig.data_ptr(), 1, expect,
+                         fetched.data_ptr(), 64, side.cuda_stream)
+            torch.cuda.synchronize()
+            err = shm.get_error()
+            assert err["count"] == 0, (sig_op, err)
+            assert int(sig.cpu()[0]) == expect and fetched.cpu().tolist() == [expect, 0]
+            assert torch.all(dst.cpu() == ord("7"))
     finally:
         torch.cuda.synchronize()
         shm.finalize()
