@@ -5,7 +5,7 @@ this package adds symmetric tensors, teams, host-side OpenSHMEM calls and stream
 MoE and tensor-parallel operations on top of the same runtime.
 """
 from .runtime import (  # noqa: F401
-    ALLREDUCE_AUTO, ALLREDUCE_NVLS, ALLREDUCE_ONE_SHOT, ALLREDUCE_TWO_SHOT, AMO_ADD, AMO_AND, AMO_CAS,
+    ALLREDUCE_AUTO, ALLREDUCE_LL, ALLREDUCE_NVLS, ALLREDUCE_ONE_SHOT, ALLREDUCE_TWO_SHOT, AMO_ADD, AMO_AND, AMO_CAS,
     AMO_FETCH, AMO_OR, AMO_SWAP, AMO_XOR, CMP_EQ, CMP_GE, CMP_GT, CMP_LE, CMP_LT, CMP_NE, CTX_NOSTORE,
     ERROR, OP_AND, OP_MAX, OP_MIN, OP_OR, OP_PROD, OP_SUM, OP_XOR, SIGNAL_ADD, SIGNAL_SET, SUCCESS,
     Context, Team, atomic, atomic_compare_swap, atomic_fetch, atomic_fetch_add, atomic_swap,

@@ -139,6 +139,8 @@ struct rocshmem_team_dev {
   // collectives, so the counters agree without communication. Flags are never reset: a waiter
   // compares against the epoch it expects (>=), which removes the reset phase and its races.
   unsigned long long barrier_epoch;
+  // Calls of the flag-in-word small allreduce on this team so far (its words carry the call's number).
+  unsigned long long ll_epoch;
 };
 
 // Context descriptor (device pool entry).
@@ -245,6 +247,7 @@ struct rocshmem_device_state {
   unsigned long long *barrier_flags;   // [max_teams][ROCSHMEM_MAX_PES] arrival epochs
   unsigned long long *lib_flags;       // [ROCSHMEM_LIB_FLAG_WORDS] flags of library kernels
   unsigned long long *lib_state;       // [ROCSHMEM_LIB_STATE_WORDS] local epochs of library kernels
+  unsigned long long *ll_buf;          // [ROCSHMEM_TEAM_SLOTS][2][n_pes][ROCSHMEM_LL_WORDS] small-allreduce mailboxes
   char *scratch;                       // staging for library collectives
   size_t scratch_size;
   rocshmem_error_record *error;        // first-error record
@@ -267,5 +270,8 @@ constexpr int ROCSHMEM_LIB_MAX_BLOCKS = 256;
 constexpr int ROCSHMEM_LIB_FLAG_WORDS = ROCSHMEM_TEAM_SLOTS * ROCSHMEM_LIB_MAX_BLOCKS * ROCSHMEM_MAX_PES;
 constexpr int ROCSHMEM_LIB_STATE_WORDS = ROCSHMEM_TEAM_SLOTS * ROCSHMEM_LIB_MAX_BLOCKS;
 constexpr int ROCSHMEM_MAX_LOCAL_PES = 8;
+// Small allreduce: every member owns a mailbox of this many 8-byte words (4 bytes of data + the call's number) in
+// every other member's heap, two per team slot (calls alternate between them).
+constexpr int ROCSHMEM_LL_WORDS = 512;
 
 }  // namespace rocshmem

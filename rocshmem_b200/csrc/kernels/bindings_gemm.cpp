@@ -49,6 +49,20 @@ void bind_gemm(py::module_ &m) {
                                         P<float>(weights), groups, max_rows, N, K, P<void>(stream)),
           "grouped_gemm_bf16_scatter_add");
   });
+  m.def("grouped_gemm_fp8_swiglu_quant", [](uintptr_t a, uintptr_t a_s, uintptr_t row_index, uintptr_t b, uintptr_t b_s,
+                                            uintptr_t out_q, uintptr_t out_s, uintptr_t offsets, int groups,
+                                            int max_rows, int N, int K, uintptr_t stream) {
+    check(grouped_gemm_fp8_swiglu_quant(P<void>(a), P<float>(a_s), P<int>(row_index), P<void>(b), P<float>(b_s),
+                                        P<void>(out_q), P<float>(out_s), P<int>(offsets), groups, max_rows, N, K,
+                                        P<void>(stream)), "grouped_gemm_fp8_swiglu_quant");
+  });
+  m.def("grouped_gemm_fp8_scatter_add", [](uintptr_t a, uintptr_t a_s, uintptr_t b, uintptr_t b_s, uintptr_t y,
+                                           uintptr_t offsets, uintptr_t row_index, uintptr_t weights, int groups,
+                                           int max_rows, int N, int K, uintptr_t stream) {
+    check(grouped_gemm_fp8_scatter_add(P<void>(a), P<float>(a_s), P<void>(b), P<float>(b_s), P<void>(y),
+                                       P<int>(offsets), P<int>(row_index), P<float>(weights), groups, max_rows, N, K,
+                                       P<void>(stream)), "grouped_gemm_fp8_scatter_add");
+  });
   m.def("gemm_error_count", [] { return gemm_error_count(); });
   m.def("gemm_fp8_blockscaled", [](uintptr_t a, uintptr_t a_s, uintptr_t b, uintptr_t b_s, uintptr_t c, int M, int N,
                                    int K, uintptr_t stream) {

@@ -11,7 +11,8 @@
 //     block of its own GPU and the kernels need no grid-wide synchronisation;
 //   * data moves as 16-byte NVLink peer loads / stores, with one load per team member in flight per
 //     thread (allreduce) or four independent vectors per thread (copies);
-//   * allreduce: ONE_SHOT = every PE pulls every source and reduces locally (3 hops, small payloads);
+//   * allreduce: LL = payloads up to 2 KiB travel as 8-byte words of data + call number, no barrier at all;
+//     ONE_SHOT = every PE pulls every source and reduces locally (3 hops, small payloads);
 //     TWO_SHOT = PE i reduces slice i from all sources and pushes the result to every dest, which
 //     moves (n-1)/n of the payload per direction per GPU, the minimum over point-to-point links;
 //     NVLS = multimem.ld_reduce on slice i (the NVSwitch adds the n copies) followed by multimem.st
@@ -270,6 +271,104 @@ allreduce_nvls_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg, si
   block_pair_barrier(t, blockIdx.x);
 }
 
+// ---- small allreduce without any barrier ---------------------------------------------------------------------------
+// Every member stores its payload into its mailbox on every member (itself included) as 8-byte words that carry
+// 4 bytes of data and the number of this call: data and "ready" flag arrive in one store, so the receiver needs no
+// fence and no flag round trip, and nobody has to wait for anybody before sending. The result is reduced locally in
+// member order, hence bit-identical on all members. Two mailboxes per team alternate between calls: a member can be
+// at most one call ahead of another (it needs everybody's words of call k to finish call k), so the words of call
+// k + 2 never overwrite words of call k that are still being read. One NVLink crossing in total, against the three
+// of the one-shot kernel with its two pair barriers. Payloads up to ROCSHMEM_LL_WORDS * 4 bytes, a multiple of 4;
+// element types of 2 or 4 bytes.
+template <typename T, int OP>
+__global__ void __launch_bounds__(kThreads)
+allreduce_ll_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg, size_t nelems, int op) {
+  using A = typename Acc<T>::type;
+  constexpr int PER = 4 / sizeof(T);  // elements per word
+  static_assert(sizeof(T) == 2 || sizeof(T) == 4, "mailbox words carry 4 bytes of data");
+  __shared__ unsigned s_epoch;
+  const rocshmem_device_state &s = st();
+  rocshmem_team_dev *t = const_cast<rocshmem_team_dev *>(detail::team_of(team));
+  if (t->my_pe < 0) return;
+  unsigned *dest = reinterpret_cast<unsigned *>(detail::local_ptr(dest_arg));
+  const unsigned *source = reinterpret_cast<const unsigned *>(detail::local_ptr(const_cast<T *>(source_arg)));
+  const int n = t->size, me = t->my_pe;
+  const unsigned words = static_cast<unsigned>(nelems / PER);
+  if (threadIdx.x == 0) {
+    unsigned long long e = t->ll_epoch + 1;
+    if ((e & 0xffffffffull) == 0) ++e;   // the flag value 0 means "empty"
+    t->ll_epoch = e;
+    s_epoch = static_cast<unsigned>(e);
+  }
+  __syncthreads();
+  const unsigned epoch = s_epoch;
+  const size_t slot_words = size_t(2) * s.n_pes * ROCSHMEM_LL_WORDS;
+  unsigned long long *box = s.ll_buf + size_t(t->slot) * slot_words + size_t(epoch & 1u) * s.n_pes * ROCSHMEM_LL_WORDS;
+  for (unsigned w = threadIdx.x; w < words; w += blockDim.x) {
+    const unsigned long long word = (static_cast<unsigned long long>(epoch) << 32) | source[w];
+    for (int d = 0; d < n; ++d) {
+      const int j = (me + d) % n;
+      detail::st_relaxed_sys(remote_ptr(box + size_t(me) * ROCSHMEM_LL_WORDS + w, team_pe_to_world(t, j)), word);
+    }
+  }
+  for (unsigned w = threadIdx.x; w < words; w += blockDim.x) {
+    A acc[PER];
+    bool ok = true;
+    for (int j = 0; j < n && ok; ++j) {
+      const unsigned long long *p = box + size_t(j) * ROCSHMEM_LL_WORDS + w;
+      unsigned long long v = detail::ld_relaxed_sys(p);
+      if (static_cast<unsigned>(v >> 32) != epoch) {
+        detail::SpinBudget budget(s.wait_timeout_ns);
+        while (static_cast<unsigned>((v = detail::ld_relaxed_sys(p)) >> 32) != epoch) {
+          if (!budget.keep_going()) {
+            detail::record_error(ROCSHMEM_ERR_BARRIER_TIMEOUT, team_pe_to_world(t, j), 63, p, epoch, v);
+            ok = false;
+            break;
+          }
+        }
+      }
+      const unsigned data = static_cast<unsigned>(v);
+      const T *x = reinterpret_cast<const T *>(&data);
+#pragma unroll
+      for (int q = 0; q < PER; ++q) acc[q] = j == 0 ? to_acc<T>(x[q]) : combine<T, OP>(acc[q], to_acc<T>(x[q]), op);
+    }
+    if (!ok) break;
+    unsigned out;
+    T *o = reinterpret_cast<T *>(&out);
+#pragma unroll
+    for (int q = 0; q < PER; ++q) o[q] = from_acc<T>(acc[q]);
+    dest[w] = out;
+  }
+}
+
+// All-gather through the NVLink multicast mapping (world team, one PE per process): every 16-byte vector of my
+// block is stored once to the multicast address of dest[my_pe * bytes] and the switch delivers it to every member,
+// myself included. A member puts `bytes` on its links instead of (n - 1) x bytes.
+__global__ void __launch_bounds__(kThreads)
+fcollect_nvls_kernel(rocshmem_team_t team, char *dest_arg, const char *source_arg, size_t bytes, int pre_sync) {
+  const rocshmem_device_state &s = st();
+  const rocshmem_team_dev *t = detail::team_of(team);
+  if (t->my_pe < 0 || s.mc_base == nullptr) return;
+  char *dest = detail::local_ptr(dest_arg);
+  const int4 *src = reinterpret_cast<const int4 *>(detail::local_ptr(const_cast<char *>(source_arg)));
+  if (pre_sync && !block_pair_barrier(t, blockIdx.x)) return;
+  char *dst_mc = s.mc_base + (dest - s.heap_base) + size_t(t->my_pe) * bytes;
+  const size_t nvec = bytes / 16, per = (nvec + gridDim.x - 1) / gridDim.x;
+  size_t lo = per * blockIdx.x, hi = lo + per;
+  if (lo > nvec) lo = nvec;
+  if (hi > nvec) hi = nvec;
+  size_t v = lo + threadIdx.x;
+  for (; v + 3 * blockDim.x < hi; v += 4 * blockDim.x) {
+    const int4 a = src[v], b = src[v + blockDim.x], c = src[v + 2 * blockDim.x], d = src[v + 3 * blockDim.x];
+    multimem_st(dst_mc + v * 16, a);
+    multimem_st(dst_mc + (v + blockDim.x) * 16, b);
+    multimem_st(dst_mc + (v + 2 * blockDim.x) * 16, c);
+    multimem_st(dst_mc + (v + 3 * blockDim.x) * 16, d);
+  }
+  for (; v < hi; v += blockDim.x) multimem_st(dst_mc + v * 16, src[v]);
+  block_pair_barrier(t, blockIdx.x);
+}
+
 // ---- copies -----------------------------------------------------------------------------------------------
 
 // mode 0: broadcast (root pushes source to every other member's dest)
@@ -435,6 +534,15 @@ bool use_bcast_nvls() {
   return on;
 }
 
+// ROCSHMEM_FCOLLECT_NVLS=0 keeps all-gathers on the point-to-point push kernel even where the multicast mapping exists.
+bool use_fcollect_nvls() {
+  static const bool on = [] {
+    const char *e = std::getenv("ROCSHMEM_FCOLLECT_NVLS");
+    return e == nullptr || e[0] != '0';
+  }();
+  return on;
+}
+
 template <typename K>
 unsigned clamp_blocks(K kernel, unsigned want) {
   Runtime &rt = Runtime::instance();
@@ -454,8 +562,25 @@ int launch_allreduce_typed(rocshmem_team_t team, void *dest, const void *source,
     const bool nvls_ok = rt.mc_base() != nullptr && ht == rt.team_world() && op == ROCSHMEM_SUM &&
                          (std::is_same<T, float>::value || std::is_same<T, __half>::value ||
                           std::is_same<T, __nv_bfloat16>::value);
-    if (bytes <= (size_t(256) << 10) && dest != source) algo = ALLREDUCE_ONE_SHOT;
+    const bool ll_ok = (sizeof(T) == 2 || sizeof(T) == 4) && bytes % 4 == 0 && bytes <= size_t(ROCSHMEM_LL_WORDS) * 4 &&
+                       ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 3u) == 0;
+    if (ll_ok) algo = ALLREDUCE_LL;
+    else if (bytes <= (size_t(256) << 10) && dest != source) algo = ALLREDUCE_ONE_SHOT;
     else algo = nvls_ok ? ALLREDUCE_NVLS : ALLREDUCE_TWO_SHOT;
+  }
+  if (algo == ALLREDUCE_LL) {
+    if constexpr (sizeof(T) == 2 || sizeof(T) == 4) {
+      const bool fits = bytes % 4 == 0 && bytes <= size_t(ROCSHMEM_LL_WORDS) * 4 &&
+                        ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 3u) == 0;
+      if (fits) {
+        const unsigned words = static_cast<unsigned>(bytes / 4);
+        const unsigned threads = std::min(kThreads, std::max(32u, (words + 31) / 32 * 32));
+        auto k = op == ROCSHMEM_SUM ? allreduce_ll_kernel<T, ROCSHMEM_SUM> : allreduce_ll_kernel<T, OP_RUNTIME>;
+        return launch_pes(k, 1, threads, 0, stream, false, team, static_cast<T *>(dest), static_cast<const T *>(source),
+                          nelems, op);
+      }
+    }
+    algo = dest != source ? ALLREDUCE_ONE_SHOT : ALLREDUCE_TWO_SHOT;
   }
   if (algo == ALLREDUCE_ONE_SHOT && dest == source) algo = ALLREDUCE_TWO_SHOT;
   if (algo == ALLREDUCE_NVLS) {
@@ -509,6 +634,10 @@ void load_now(K kernel, int *rc) {
 }
 template <typename T>
 void load_allreduce_now(int *rc) {
+  if constexpr (sizeof(T) == 2 || sizeof(T) == 4) {
+    load_now(allreduce_ll_kernel<T, ROCSHMEM_SUM>, rc);
+    load_now(allreduce_ll_kernel<T, OP_RUNTIME>, rc);
+  }
   load_now(allreduce_one_shot_kernel<T, ROCSHMEM_SUM>, rc);
   load_now(allreduce_one_shot_kernel<T, OP_RUNTIME>, rc);
   load_now(allreduce_two_shot_kernel<T, ROCSHMEM_SUM>, rc);
@@ -525,6 +654,7 @@ int coll_preload() {
   load_now(push_kernel, &rc);
   load_now(broadcast_relay_kernel, &rc);
   load_now(broadcast_nvls_kernel, &rc);
+  load_now(fcollect_nvls_kernel, &rc);
   load_allreduce_now<short>(&rc);
   load_allreduce_now<int>(&rc);
   load_allreduce_now<long long>(&rc);
@@ -608,6 +738,16 @@ int coll_broadcast(rocshmem_team_t team, void *dest, const void *source, size_t 
 }
 int coll_fcollect(rocshmem_team_t team, void *dest, const void *source, size_t bytes, void *stream,
                   int flags) {
+  Runtime &rt = Runtime::instance();
+  HostTeam *ht = rt.team_from_handle(team);
+  if (use_fcollect_nvls() && ht != nullptr && ht == rt.team_world() && rt.n_local() == 1 && rt.mc_base() != nullptr &&
+      ht->world.size >= 2 && bytes >= 4096 && bytes % 16 == 0 && reinterpret_cast<uintptr_t>(dest) % 16 == 0 &&
+      reinterpret_cast<uintptr_t>(source) % 16 == 0) {
+    unsigned blocks = clamp_blocks(fcollect_nvls_kernel, static_cast<unsigned>(coll_blocks_for(bytes)));
+    return launch_pes(fcollect_nvls_kernel, blocks, kThreads, 0, static_cast<cudaStream_t>(stream), false, team,
+                      static_cast<char *>(dest), static_cast<const char *>(source), bytes,
+                      (flags & COLL_PRE_SYNC) ? 1 : 0);
+  }
   return launch_push(team, dest, source, bytes, 0, 1, stream, flags);
 }
 int coll_alltoall(rocshmem_team_t team, void *dest, const void *source, size_t bytes, void *stream,

@@ -14,6 +14,7 @@
 #pragma once
 
 #include <cuda_bf16.h>
+#include <cuda_fp8.h>
 
 #include "gemm_core.cuh"
 #include "sm100_ptx.cuh"
@@ -34,6 +35,8 @@ constexpr int EPI_ROW_BYTES = 32 * 2 + 16;              // 32 staged bf16 column
 constexpr int EPI_WARP_BYTES = 32 * EPI_ROW_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + ACC_WARPS * EPI_WARP_BYTES + 1024;
 constexpr int THREADS = 64 + ACC_WARPS * 32;
+constexpr int GATHER_WARPS = 2;                     // registers are granted per four warps: 10 or 12 warps cost the same
+constexpr int GATHER_THREADS = THREADS + GATHER_WARPS * 32;
 constexpr int TMEM_COLS = 512;
 constexpr unsigned long long WAIT_BUDGET_NS = gemm::WAIT_BUDGET_NS;
 
@@ -44,6 +47,8 @@ struct Shared {
   uint64_t tmem_empty[2];
   uint32_t tmem_base;
   volatile int abort_flag;
+  // QUANT_OUT: [tile parity][column half][row], (tile number + 1) << 32 | bits of the half's largest magnitude
+  unsigned long long amax[2][2][BM];
 };
 
 // Scales: a_scale [rows of A][k_blocks] fp32 (row-major), b_scale [rows of B / 128][k_blocks] fp32.
@@ -51,17 +56,25 @@ struct Shared {
 // and k_blocks must be a multiple of 4 (the scales are fetched four K blocks at a time). With SWIGLU
 // the tile's b_row[0] / b_row[1] are the gate and up rows of 128 output columns and the result is
 // silu(gate) * up (t.cols <= 128).
-template <bool SWIGLU, bool LATE_A = false, class Scheduler, class Epilogue>
+// EPI_ADD: rows are multiplied by epi.row_scale(t, row) and added to the destination (packed bf16 reductions) instead
+// of stored. QUANT_OUT (with SWIGLU): the 128 output columns of a tile are one 1 x 128 block of the next GEMM's A
+// operand; they are quantised to e4m3 here (the two threads that hold a row's halves exchange their maxima through
+// shared memory) and written to epi.q_row_ptr(t, row) with the block's scale at epi.scale_ptr(t, row).
+// A_GATHER: the A rows (and their scales) are picked by index: tile row r reads row gather->row_index[t.a_row + r]
+// of gather->base / gather->scales. Two extra warps (threads THREADS .. GATHER_THREADS) store the rows into the
+// stage with the 128-byte swizzle instead of a TMA load; the kernel must then be launched with GATHER_THREADS.
+template <bool SWIGLU, bool LATE_A = false, bool EPI_ADD = false, bool QUANT_OUT = false, bool A_GATHER = false,
+          class Scheduler, class Epilogue>
 __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap *map_b, const float *a_scale,
                                     const float *b_scale, int k_blocks, Scheduler &sched, Epilogue &epi,
-                                    unsigned char *smem_raw, Shared &sh) {
+                                    unsigned char *smem_raw, Shared &sh, const gemm::GatherSrc *gather = nullptr) {
   const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
   unsigned char *smem = reinterpret_cast<unsigned char *>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   constexpr uint32_t IDESC = sm100::make_idesc(BM, BN, sm100::kFormatE4M3);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      sm100::mbar_init(&sh.full[s], 1);
+      sm100::mbar_init(&sh.full[s], A_GATHER ? 1 + GATHER_WARPS * 32 : 1);
       sm100::mbar_init(&sh.empty[s], 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -70,8 +83,11 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
     }
     sh.abort_flag = 0;
     sm100::mbar_fence_init();
-    sm100::tma_prefetch_desc(map_a);
+    if (!A_GATHER) sm100::tma_prefetch_desc(map_a);
     sm100::tma_prefetch_desc(map_b);
+  }
+  if (QUANT_OUT) {
+    for (int i = threadIdx.x; i < 2 * 2 * BM; i += blockDim.x) (&sh.amax[0][0][0])[i] = 0ull;   // tag 0: no tile yet
   }
   if (warp == 1) sm100::tmem_alloc(&sh.tmem_base, TMEM_COLS);
   sm100::tcgen05_fence_before();
@@ -92,8 +108,8 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
           if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) break;
           unsigned char *sa = smem + stage * STAGE_BYTES;
           unsigned char *sb = sa + A_STAGE_BYTES;
-          sm100::mbar_arrive_expect_tx(&sh.full[stage], STAGE_BYTES);
-          sm100::tma_load_2d(sa, map_a, &sh.full[stage], kb * KB, t.a_row);
+          sm100::mbar_arrive_expect_tx(&sh.full[stage], A_GATHER ? B_STAGE_BYTES : STAGE_BYTES);
+          if (!A_GATHER) sm100::tma_load_2d(sa, map_a, &sh.full[stage], kb * KB, t.a_row);
           sm100::tma_load_2d(sb, map_b, &sh.full[stage], kb * KB, t.b_row[0]);
           sm100::tma_load_2d(sb + B_STAGE_BYTES / 2, map_b, &sh.full[stage], kb * KB, t.b_row[1]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
@@ -126,6 +142,64 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         if (sh.abort_flag) break;
       }
     }
+  } else if (A_GATHER && warp >= 2 + ACC_WARPS) {
+    // ---- gather producer: a thread owns two tile rows and keeps two K blocks of both in flight in registers ----
+    const int g = (warp - 2 - ACC_WARPS) * 32 + lane;   // 0 .. 63
+    uint32_t stage = 0, phase = 0;
+    gemm::Tile t;
+    for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
+      const int4 *src[2];
+      bool live[2];
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const int r = g + 64 * h;
+        live[h] = r < t.rows;
+        const long long src_row = live[h] ? gather->row_index[t.a_row + r] : 0;
+        src[h] = reinterpret_cast<const int4 *>(gather->base + static_cast<size_t>(src_row) * gather->row_bytes);
+      }
+      int4 buf0[2][8], buf1[2][8];
+      auto fetch = [&](int4 (&b)[2][8], int kb) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          if (live[h] && kb < k_blocks) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) b[h][c] = __ldg(src[h] + kb * 8 + c);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) b[h][c] = make_int4(0, 0, 0, 0);
+          }
+        }
+      };
+      auto put = [&](const int4 (&b)[2][8]) -> bool {
+        if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) return false;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const int r = g + 64 * h;
+          unsigned char *sa = smem + stage * STAGE_BYTES + r * KB;
+          const uint32_t sw = static_cast<uint32_t>(r & 7);
+#pragma unroll
+          for (int c = 0; c < 8; ++c) *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(c) ^ sw) << 4)) = b[h][c];
+        }
+        sm100::fence_proxy_async_smem();
+        sm100::mbar_arrive(&sh.full[stage]);
+        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        return true;
+      };
+      fetch(buf0, 0);
+      fetch(buf1, 1);
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks && ok; kb += 2) {
+        ok = put(buf0);
+        if (!ok) break;
+        fetch(buf0, kb + 2);
+        if (kb + 1 < k_blocks) {
+          ok = put(buf1);
+          if (!ok) break;
+          fetch(buf1, kb + 3);
+        }
+      }
+      if (!ok || sh.abort_flag) break;
+    }
   } else if (warp >= 2 + ACC_WARPS) {
     sched.side_role();  // optional extra warps (kernels launched with more than THREADS threads)
   } else {
@@ -144,7 +218,10 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
 #pragma unroll
       for (int i = 0; i < 128; ++i) acc[i] = 0.f;
       const bool row_ok = row < t.rows;
-      const float4 *sa4 = reinterpret_cast<const float4 *>(a_scale + static_cast<size_t>(t.a_row + (row_ok ? row : 0)) * k_blocks);
+      // Gathered A: the row's scales sit with its source row.
+      const size_t a_scale_row = A_GATHER ? static_cast<size_t>(gather->row_index[t.a_row + (row_ok ? row : 0)])
+                                          : static_cast<size_t>(t.a_row + (row_ok ? row : 0));
+      const float4 *sa4 = reinterpret_cast<const float4 *>((A_GATHER ? gather->scales : a_scale) + a_scale_row * k_blocks);
       const float4 *sb4 = reinterpret_cast<const float4 *>(b_scale + static_cast<size_t>(t.b_row[SWIGLU ? 0 : half] / 128) * k_blocks);
       const float4 *su4 = reinterpret_cast<const float4 *>(b_scale + static_cast<size_t>(t.b_row[1] / 128) * k_blocks);
       // LATE_A: the A scales of a tile may still be on their way from another GPU until the producer has
@@ -190,10 +267,65 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
 #pragma unroll
         for (int i = 0; i < 64; ++i) acc[i] = gemm::silu(acc[i]) * acc[64 + i];
       }
-      // Write-out through the warp's padded staging rows, 32 columns at a time: 4 lanes per row write 64
-      // contiguous bytes, 8 rows per instruction (instead of one row per thread in 16-byte pieces).
+      if constexpr (EPI_ADD) {
+        const float rs = row_ok ? epi.row_scale(t, row) : 0.f;
+#pragma unroll
+        for (int i = 0; i < OUT; ++i) acc[i] *= rs;
+      }
       const int col0 = half * OUT;
       unsigned char *stg = smem + STAGES * STAGE_BYTES + aw * EPI_WARP_BYTES;
+      if constexpr (QUANT_OUT) {
+        static_assert(!QUANT_OUT || SWIGLU, "the quantising epilogue belongs to the SwiGLU tile");
+        // This thread holds 64 of the row's 128 columns; its partner (same row, other half) sits in another warp.
+        float amax = 0.f;
+#pragma unroll
+        for (int i = 0; i < 64; ++i) amax = fmaxf(amax, fabsf(acc[i]));
+        // Value and "this is tile `iter`" travel in one 8-byte shared-memory store; the partner polls for the tag
+        // (bounded, and released by the abort flag: no block-wide barrier that a role that gave up could miss).
+        // Two slots alternate: a thread can only be at tile i + 2 once its partner has written tile i + 1, i.e.
+        // after the partner has read tile i.
+        const int par = iter & 1;
+        const unsigned long long tag = static_cast<unsigned long long>(iter + 1) << 32;
+        *reinterpret_cast<volatile unsigned long long *>(&sh.amax[par][half][row]) = tag | __float_as_uint(amax);
+        volatile unsigned long long *theirs = &sh.amax[par][half ^ 1][row];
+        unsigned long long seen = *theirs;
+        for (unsigned spins = 0; (seen >> 32) != static_cast<unsigned long long>(iter + 1); seen = *theirs) {
+          if ((++spins & 1023u) == 0 && sh.abort_flag) break;
+          if (spins > (1u << 28)) { sh.abort_flag = 1; break; }
+        }
+        if (sh.abort_flag) break;
+        amax = fmaxf(amax, __uint_as_float(static_cast<unsigned>(seen)));
+        const float scale = amax > 0.f ? amax * (1.0f / 448.0f) : 1.0f;
+        const float inv = amax > 0.f ? 448.0f / amax : 1.0f;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          int4 pk;
+          unsigned *w = reinterpret_cast<unsigned *>(&pk);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float *v = acc + q * 16 + i * 4;
+            const unsigned lo = __nv_cvt_float2_to_fp8x2(make_float2(v[0] * inv, v[1] * inv), __NV_SATFINITE, __NV_E4M3);
+            const unsigned hi = __nv_cvt_float2_to_fp8x2(make_float2(v[2] * inv, v[3] * inv), __NV_SATFINITE, __NV_E4M3);
+            w[i] = lo | (hi << 16);
+          }
+          *reinterpret_cast<int4 *>(stg + lane * EPI_ROW_BYTES + q * 16) = pk;
+        }
+        if (half == 0 && row_ok) *epi.scale_ptr(t, row) = scale;
+        __syncwarp();
+        // 64 bytes per row: 4 lanes per row, 8 rows per instruction.
+#pragma unroll
+        for (int it = 0; it < 4; ++it) {
+          const int r = it * 8 + lane / 4, seg = lane % 4;
+          const int orow = quarter * 32 + r;
+          if (orow < t.rows) {
+            unsigned char *dst = epi.q_row_ptr(t, orow) + col0 + seg * 16;
+            *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(stg + r * EPI_ROW_BYTES + seg * 16);
+          }
+        }
+        __syncwarp();
+      } else {
+      // Write-out through the warp's padded staging rows, 32 columns at a time: 4 lanes per row write 64
+      // contiguous bytes, 8 rows per instruction (instead of one row per thread in 16-byte pieces).
 #pragma unroll
       for (int c = 0; c < OUT / 32; ++c) {
 #pragma unroll
@@ -216,15 +348,20 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
               const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
               __nv_bfloat16 *dst = out + col;
               if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(src);
+                if (EPI_ADD) sm100::red_add_bf16x8(dst, *reinterpret_cast<const int4 *>(src));
+                else *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(src);
               } else {
                 const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
-                for (int i = 0; i < 8 && col + i < t.cols; ++i) dst[i] = s16[i];
+                for (int i = 0; i < 8 && col + i < t.cols; ++i) {
+                  if (EPI_ADD) atomicAdd(dst + i, s16[i]);
+                  else dst[i] = s16[i];
+                }
               }
             }
           }
         }
         __syncwarp();
+      }
       }
     }
   }

@@ -59,6 +59,19 @@ int grouped_gemm_fp8_blockscaled(const void *a_q, const float *a_scale, const vo
                                  const int *offsets, int groups, int max_rows, int n, int k, int swiglu,
                                  void *stream);
 
+// Block-scaled forms of the two MoE-specific grouped GEMMs. The first is the gate/up projection with SwiGLU whose
+// result is quantised in the epilogue to the next GEMM's operand format: out_q [rows, n / 2] e4m3 with out_s
+// [rows, n / 256] fp32 (one scale per 128 columns); n must be a multiple of 256. The second is the block-scaled
+// grouped_gemm_bf16_scatter_add. With row_index != nullptr the first one gathers its A rows and their scales by
+// index (position p reads row row_index[p] of a_q / a_scale, which then need not be in grouped order; max_rows
+// bounds the source rows).
+int grouped_gemm_fp8_swiglu_quant(const void *a_q, const float *a_scale, const int *row_index, const void *b_q,
+                                   const float *b_scale, void *out_q, float *out_s, const int *offsets, int groups,
+                                   int max_rows, int n, int k, void *stream);
+int grouped_gemm_fp8_scatter_add(const void *a_q, const float *a_scale, const void *b_q, const float *b_scale, void *y,
+                                 const int *offsets, const int *row_index, const float *weights, int groups,
+                                 int max_rows, int n, int k, void *stream);
+
 // Tensor-parallel fused kernels on the symmetric heap (fused_kernels.cu).
 // All-gather -> GEMM: every rank holds x_shard [m_shard, K] (symmetric); computes
 // C[n_ranks * m_shard, N] = concat_ranks(x_shard) * B^T with its local B [N, K]. `gathered` is a

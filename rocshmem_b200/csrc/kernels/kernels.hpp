@@ -18,6 +18,7 @@ enum AllreduceAlgo : int {
   ALLREDUCE_ONE_SHOT = 1,  // every PE reads every source; lowest latency for small payloads
   ALLREDUCE_TWO_SHOT = 2,  // reduce-scatter by pull + all-gather by push; bandwidth-optimal over P2P
   ALLREDUCE_NVLS = 3,      // multimem.ld_reduce + multimem.st through the NVSwitch (TEAM_WORLD only)
+  ALLREDUCE_LL = 4,        // up to 2 KiB: data and call number in one 8-byte word, no barrier, one NVLink crossing
 };
 
 // ---- collectives on the symmetric heap (coll_kernels.cu) -----------------------------------------------

@@ -28,7 +28,7 @@ std::mutex &module_mutex() {
 }
 }  // namespace
 
-InternalLayout InternalLayout::build(const Config &cfg) {
+InternalLayout InternalLayout::build(const Config &cfg, int n_pes) {
   InternalLayout l;
   size_t off = 0;
   auto take = [&off, &l](size_t bytes) {
@@ -46,6 +46,8 @@ InternalLayout InternalLayout::build(const Config &cfg) {
   l.barrier_flags = take(sizeof(unsigned long long) * ROCSHMEM_TEAM_SLOTS * ROCSHMEM_MAX_PES);
   l.lib_flags = take(sizeof(unsigned long long) * ROCSHMEM_LIB_FLAG_WORDS);
   l.lib_state = take(sizeof(unsigned long long) * ROCSHMEM_LIB_STATE_WORDS);
+  l.ll_slot_bytes = sizeof(unsigned long long) * 2 * size_t(n_pes) * ROCSHMEM_LL_WORDS;
+  l.ll_buf = take(l.ll_slot_bytes * ROCSHMEM_TEAM_SLOTS);
   l.proxy = take(sizeof(rocshmem_proxy_ring) + 256);
   l.host_slots = take(4096);
   off = align_up(off, 4096);
@@ -112,7 +114,7 @@ void Runtime::init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local
                  first_pe_, mem_->name(), n_pes_, n_local_, cfg_.heap_size);
   }
 
-  layout_ = InternalLayout::build(cfg_);
+  layout_ = InternalLayout::build(cfg_, n_pes_);
   size_t gran = mem_->granularity();
   if (mem_->is_cuda() && cfg_.enable_nvls && bs_->size() > 1 && n_local_ == 1) {
     // A heap that is to be bound to an NVLink multicast object must be a multiple of the multicast
@@ -288,6 +290,7 @@ void Runtime::build_states() {
     s.barrier_flags = reinterpret_cast<unsigned long long *>(ib + layout_.barrier_flags);
     s.lib_flags = reinterpret_cast<unsigned long long *>(ib + layout_.lib_flags);
     s.lib_state = reinterpret_cast<unsigned long long *>(ib + layout_.lib_state);
+    s.ll_buf = reinterpret_cast<unsigned long long *>(ib + layout_.ll_buf);
     s.scratch = ib + layout_.scratch;
     s.scratch_size = cfg_.scratch_size;
     s.error = reinterpret_cast<rocshmem_error_record *>(ib + layout_.error);
@@ -470,10 +473,11 @@ void Runtime::write_team_descriptor(HostTeam *t) {
     d.world_size = n_pes_;
     d.my_pe_world = pe;
     d.barrier_epoch = 0;
+    d.ll_epoch = 0;
     auto *dst = reinterpret_cast<rocshmem_team_dev *>(internal_base(pe) + layout_.teams) + t->slot;
     mem_->write(dst, &d, sizeof(d));
     // A reused slot starts from epoch 0 again, so the arrival flags of the device barrier and the
-    // per-(slot, block) epochs and flags of the library kernels are cleared as well: the slot's earlier
+    // per-(slot, block) epochs and flags of the library kernels and the small-allreduce mailboxes are cleared as well: the slot's earlier
     // occupants may have had other members and may have run another number of kernels. All members do
     // this before the collective that ends the split, and nobody signals on the new team before that
     // collective has completed.
@@ -481,6 +485,7 @@ void Runtime::write_team_descriptor(HostTeam *t) {
                size_t(ROCSHMEM_MAX_PES) * 8);
     mem_->zero(internal_base(pe) + layout_.lib_state + size_t(t->slot) * ROCSHMEM_LIB_MAX_BLOCKS * 8,
                size_t(ROCSHMEM_LIB_MAX_BLOCKS) * 8);
+    mem_->zero(internal_base(pe) + layout_.ll_buf + size_t(t->slot) * layout_.ll_slot_bytes, layout_.ll_slot_bytes);
     mem_->zero(internal_base(pe) + layout_.lib_flags +
                    size_t(t->slot) * ROCSHMEM_LIB_MAX_BLOCKS * ROCSHMEM_MAX_PES * 8,
                size_t(ROCSHMEM_LIB_MAX_BLOCKS) * ROCSHMEM_MAX_PES * 8);

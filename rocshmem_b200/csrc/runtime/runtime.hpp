@@ -56,14 +56,15 @@ struct HostCtx {
 // Layout of the internal region (offsets from internal_base, identical on every PE).
 struct InternalLayout {
   size_t error = 0, stats = 0, teams = 0, ctxs = 0, ctx_free_mask = 0, barrier_flags = 0,
-         lib_flags = 0, lib_state = 0, proxy = 0, host_slots = 0, scratch = 0;
+         lib_flags = 0, lib_state = 0, ll_buf = 0, proxy = 0, host_slots = 0, scratch = 0;
+  size_t ll_slot_bytes = 0;   // mailboxes of one team slot: 2 x n_pes x ROCSHMEM_LL_WORDS words
   size_t total = 0;
   // A 256-byte guard filled with a fixed pattern follows every sub-region; a write that runs past the end of a
   // flag or descriptor array lands there and is reported by Runtime::check_canaries().
   std::vector<size_t> guards;
   static constexpr size_t kGuardBytes = 256;
   static constexpr unsigned long long kGuardWord = 0xC0DEC0DEC0DEC0DEull;
-  static InternalLayout build(const Config &cfg);
+  static InternalLayout build(const Config &cfg, int n_pes);
 };
 
 using ModuleUploadFn = void (*)(const rocshmem_device_state *states, int n_local);

@@ -10,8 +10,9 @@ side stream)::
                    the row's slot of the result buffer (the sum over a token's local experts)
     combine        pull over NVLink, sum over the ranks a token went to
 
-``fused=False`` keeps the separate gather and per-row reduction kernels (the block-scaled e4m3 experts still use
-them).
+With ``fp8_experts`` both GEMMs are block-scaled e4m3: the received e4m3 rows and their scales are gathered as they
+are, and the first GEMM's epilogue quantises the hidden activation for the second. ``fused=False`` keeps the
+separate gather, quantise and per-row reduction kernels.
 
 Experts are sharded over the team: rank r owns global experts ``[r * E_local, (r + 1) * E_local)``.
 The reference has no model code; its nearest building block is the fixed-size alltoall
@@ -51,9 +52,9 @@ class MoEFeedForward:
                  low_latency: bool = False):
         if rt.n_local_pes() != 1:
             raise RuntimeError("MoEFeedForward needs one PE per process")
-        self.fused = (not fp8_experts and hidden % 128 == 0) if fused is None else bool(fused)
-        if self.fused and (fp8_experts or hidden % 128):
-            raise ValueError("the fused path needs bf16 experts and hidden % 128 == 0")
+        self.fused = (hidden % 128 == 0) if fused is None else bool(fused)
+        if self.fused and hidden % 128:
+            raise ValueError("the fused path needs hidden % 128 == 0")
         self.d = moe.EpDispatcher(num_experts, top_k, hidden, max_tokens, team=team, quantize=quantize, layout=layout,
                                   expert_layout=self.fused, low_latency=low_latency)
         self.hidden, self.inter, self.top_k = hidden, inter, top_k
@@ -83,8 +84,9 @@ class MoEFeedForward:
                 raise ValueError("fp8 experts need an fp8 dispatch, hidden % 1024 == 0 and inter % 512 == 0")
             self.w13_q, self.w13_s = gemm.quantize_weight_128x128(self.w13)
             self.w2_q, self.w2_s = gemm.quantize_weight_128x128(self.w2)
-            self.xs_q = torch.zeros((cap, hidden), dtype=torch.uint8, device=dev)
-            self.xs_s = torch.zeros((cap, hidden // 128), dtype=torch.float32, device=dev)
+            if not self.fused:
+                self.xs_q = torch.zeros((cap, hidden), dtype=torch.uint8, device=dev)
+                self.xs_s = torch.zeros((cap, hidden // 128), dtype=torch.float32, device=dev)
             self.h_q = torch.zeros((cap, inter), dtype=torch.uint8, device=dev)
             self.h_s = torch.zeros((cap, inter // 128), dtype=torch.float32, device=dev)
 
@@ -124,12 +126,22 @@ class MoEFeedForward:
             self.side.wait_event(self.ev_dispatched)
             C.moe_zero_rows(d.recv_info.data_ptr(), self.n_ranks, self.hidden, y.data_ptr(), self.side.cuda_stream)
             self.ev_zeroed.record(self.side)
-            gemm.grouped_gemm_bf16_gathered(d.recv_x, lay_row, self.w13, offsets,
-                                            a_scales=d.recv_scales if d.quantize else None, swiglu=True, out=self.h,
-                                            stream=stream)
-            mark("gemm_gate_up")
-            cur.wait_event(self.ev_zeroed)
-            gemm.grouped_gemm_bf16_scatter_add(self.h, self.w2, offsets, lay_row, y, weights=lay_w, stream=stream)
+            if self.fp8_experts:
+                # Received e4m3 rows and their scales feed the first GEMM as they are; its epilogue quantises the
+                # hidden activation for the second one.
+                gemm.grouped_gemm_fp8_swiglu_quant(d.recv_x, d.recv_scales, self.w13_q, self.w13_s, offsets, self.h_q,
+                                                   self.h_s, row_index=lay_row, stream=stream)
+                mark("gemm_gate_up")
+                cur.wait_event(self.ev_zeroed)
+                gemm.grouped_gemm_fp8_scatter_add(self.h_q, self.h_s, self.w2_q, self.w2_s, offsets, lay_row, y,
+                                                  weights=lay_w, stream=stream)
+            else:
+                gemm.grouped_gemm_bf16_gathered(d.recv_x, lay_row, self.w13, offsets,
+                                                a_scales=d.recv_scales if d.quantize else None, swiglu=True,
+                                                out=self.h, stream=stream)
+                mark("gemm_gate_up")
+                cur.wait_event(self.ev_zeroed)
+                gemm.grouped_gemm_bf16_scatter_add(self.h, self.w2, offsets, lay_row, y, weights=lay_w, stream=stream)
             mark("gemm_down")
             out = d.combine(y, topk_idx, topk_weights, x.shape[0], weighted=False, out=out, stream=stream)
             mark("combine")

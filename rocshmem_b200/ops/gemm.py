@@ -120,6 +120,44 @@ def grouped_gemm_bf16_scatter_add(a: torch.Tensor, b: torch.Tensor, offsets: tor
     return y
 
 
+def grouped_gemm_fp8_swiglu_quant(a_q: torch.Tensor, a_scale: torch.Tensor, b_q: torch.Tensor, b_scale: torch.Tensor,
+                                  offsets: torch.Tensor, out_q: torch.Tensor, out_s: torch.Tensor,
+                                  row_index: Optional[torch.Tensor] = None, stream=None):
+    """Block-scaled gate/up projection with SwiGLU whose result leaves the kernel as the next GEMM's operand:
+    ``out_q [rows, N / 2]`` e4m3 with one fp32 scale per 128 columns in ``out_s [rows, N / 256]``. With
+    ``row_index`` the A rows (``a_q [*, K]`` e4m3, ``a_scale [*, K / 128]``) are gathered inside the kernel:
+    position ``p`` of the grouped order reads row ``row_index[p]``."""
+    K = a_q.shape[1]
+    G, N, K2 = b_q.shape
+    if K != K2 or K % 512 or N % 256 or offsets.numel() != G + 1 or out_q.shape[1] != N // 2:
+        raise ValueError("grouped_gemm_fp8_swiglu_quant: shape mismatch (K % 512, N % 256)")
+    if tuple(a_scale.shape) != (a_q.shape[0], K // 128) or tuple(out_s.shape) != (out_q.shape[0], N // 256):
+        raise ValueError("grouped_gemm_fp8_swiglu_quant: scale shapes")
+    for t in (a_q, a_scale, b_q, b_scale, out_q, out_s):
+        if not t.is_contiguous():
+            raise ValueError("grouped_gemm_fp8_swiglu_quant: tensors must be contiguous")
+    rt._C().grouped_gemm_fp8_swiglu_quant(a_q.data_ptr(), a_scale.data_ptr(),
+                                          row_index.data_ptr() if row_index is not None else 0, b_q.data_ptr(),
+                                          b_scale.data_ptr(), out_q.data_ptr(), out_s.data_ptr(), offsets.data_ptr(), G,
+                                          a_q.shape[0], N, K, _stream(stream))
+    return out_q, out_s
+
+
+def grouped_gemm_fp8_scatter_add(a_q: torch.Tensor, a_scale: torch.Tensor, b_q: torch.Tensor, b_scale: torch.Tensor,
+                                 offsets: torch.Tensor, row_index: torch.Tensor, y: torch.Tensor,
+                                 weights: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+    """Block-scaled form of :func:`grouped_gemm_bf16_scatter_add`."""
+    rows, K = a_q.shape
+    G, N, K2 = b_q.shape
+    if K != K2 or K % 512 or N % 128 or y.shape[1] != N or offsets.numel() != G + 1:
+        raise ValueError("grouped_gemm_fp8_scatter_add: shape mismatch (K % 512, N % 128)")
+    rt._C().grouped_gemm_fp8_scatter_add(a_q.data_ptr(), a_scale.data_ptr(), b_q.data_ptr(), b_scale.data_ptr(),
+                                         y.data_ptr(), offsets.data_ptr(), row_index.data_ptr(),
+                                         weights.data_ptr() if weights is not None else 0, G, rows, N, K,
+                                         _stream(stream))
+    return y
+
+
 def gemm_error_count() -> int:
     """Number of GEMM CTAs (since process start) whose bounded wait expired; 0 in a healthy run."""
     return rt._C().gemm_error_count()

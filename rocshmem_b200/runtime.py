@@ -27,7 +27,7 @@ OP_SUM, OP_MAX, OP_MIN, OP_PROD, OP_AND, OP_OR, OP_XOR = range(7)
 SIGNAL_SET, SIGNAL_ADD = 0, 1
 AMO_FETCH, AMO_SWAP, AMO_CAS, AMO_ADD, AMO_AND, AMO_OR, AMO_XOR = range(7)
 CTX_NOSTORE, CTX_SERIALIZED, CTX_WG_PRIVATE, CTX_SHARED = 1, 2, 4, 8
-ALLREDUCE_AUTO, ALLREDUCE_ONE_SHOT, ALLREDUCE_TWO_SHOT, ALLREDUCE_NVLS = range(4)
+ALLREDUCE_AUTO, ALLREDUCE_ONE_SHOT, ALLREDUCE_TWO_SHOT, ALLREDUCE_NVLS, ALLREDUCE_LL = range(5)
 COLL_PRE_SYNC = 1
 SUCCESS, ERROR = 0, 1
 

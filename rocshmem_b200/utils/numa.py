@@ -14,6 +14,7 @@ import os
 from typing import Optional
 
 MPOL_PREFERRED = 1
+MPOL_INTERLEAVE = 3
 _SYS_set_mempolicy = 238  # x86_64
 
 
@@ -49,6 +50,27 @@ def node_cpus(node: int, sysfs: str = "/sys") -> set:
         return set()
 
 
+def online_nodes(sysfs: str = "/sys") -> list:
+    """NUMA nodes of the host (empty when unknown)."""
+    try:
+        with open(os.path.join(sysfs, "devices/system/node/online")) as f:
+            return sorted(_parse_cpulist(f.read()))
+    except (OSError, ValueError):
+        return []
+
+
+def _set_mempolicy(mode: int, nodes) -> bool:
+    try:
+        libc = ctypes.CDLL(None, use_errno=True)
+        nbits = max(64, max(nodes) + 1)
+        mask = (ctypes.c_ulong * ((nbits + 63) // 64))()
+        for n in nodes:
+            mask[n // 64] |= 1 << (n % 64)
+        return libc.syscall(_SYS_set_mempolicy, mode, mask, nbits + 1) == 0
+    except (OSError, AttributeError, ValueError):
+        return False
+
+
 def bind_to_device_node(device_index: int, sysfs: str = "/sys") -> dict:
     """Restrict this process to the CPUs of the GPU's NUMA node and prefer that node for new pages.
 
@@ -56,7 +78,13 @@ def bind_to_device_node(device_index: int, sysfs: str = "/sys") -> dict:
     out = {"node": None, "cpus": 0, "mempolicy": False, "note": ""}
     node = device_numa_node(device_index, sysfs)
     if node is None:
+        # The host does not say where the GPU sits (common in containers). Spreading new pages over all nodes at
+        # least keeps eight ranks from filling, and copying out of, one socket's memory.
+        nodes = online_nodes(sysfs)
         out["note"] = "no NUMA node reported for the device"
+        if len(nodes) > 1:
+            out["mempolicy"] = _set_mempolicy(MPOL_INTERLEAVE, nodes)
+            out["note"] += f"; pages interleaved over nodes {nodes}" if out["mempolicy"] else ""
         return out
     out["node"] = node
     cpus = node_cpus(node, sysfs)
@@ -70,13 +98,5 @@ def bind_to_device_node(device_index: int, sysfs: str = "/sys") -> dict:
             out["note"] = "none of the node's CPUs is available to this process"
     except (OSError, AttributeError) as e:
         out["note"] = f"affinity not changed: {e}"
-    try:
-        libc = ctypes.CDLL(None, use_errno=True)
-        nbits = max(64, node + 1)
-        mask = (ctypes.c_ulong * ((nbits + 63) // 64))()
-        mask[node // 64] = 1 << (node % 64)
-        rc = libc.syscall(_SYS_set_mempolicy, MPOL_PREFERRED, mask, nbits + 1)
-        out["mempolicy"] = rc == 0
-    except (OSError, AttributeError, ValueError):
-        pass
+    out["mempolicy"] = _set_mempolicy(MPOL_PREFERRED, [node])
     return out

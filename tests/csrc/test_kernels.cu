@@ -439,6 +439,97 @@ __global__ void bw_kernel(int mode, char *dst_a, const char *src_a, size_t bytes
   if (threadIdx.x == 0) ns[blockIdx.x] = detail::now_ns() - t0;
 }
 
+// Micro-benchmark of the device API (the reference's primitive / message-rate / atomic testers:
+// tests/functional_tests/primitive_tester.cpp, primitive_mr_tester.cpp:41-52, amo_standard_tester.cpp:82-100).
+// Every active PE runs `iters` rounds; in round i it talks to PE (me + 1 + i % (n - 1)) % n when `all_pairs` is set
+// (every PE targets every other in turn) and to its successor otherwise; with all_pairs == 0 only PE 0 is active
+// (a pair of PEs), except for the put-with-signal ring, which needs every PE.
+//   op 0 put (blocking)   1 get   2 window of 64 put_nbi + quiet (message rate)   3 put_signal to the successor,
+//   then wait_until on my own signal (one hop of a ring per round)   4 int64 fetch_add   5 int64 compare_swap
+// `groups` thread / warp / block groups of the grid take part, each moving its own slice of `bytes` (atomics: one
+// operation per participating thread). Elapsed nanoseconds of every block go to ns[blockIdx.x].
+enum BenchOp { B_PUT = 0, B_GET, B_PUT_NBI_WINDOW, B_PUT_SIGNAL_RING, B_FETCH_ADD, B_COMPARE_SWAP };
+
+__global__ void rma_bench_kernel(int op, int scope, char *dst_a, const char *src_a, size_t bytes, int groups,
+                                 int iters, int all_pairs, uint64_t *sig_a, long long *counter_a,
+                                 unsigned long long *ns_a, uint64_t sig_base) {
+  char *dst = rocshmemx_local(dst_a);
+  const char *src = rocshmemx_local(const_cast<char *>(src_a));
+  uint64_t *sig = rocshmemx_local(sig_a);
+  long long *counter = rocshmemx_local(counter_a);
+  unsigned long long *ns = rocshmemx_local(ns_a);
+  const int me = rocshmem_my_pe(), n = rocshmem_n_pes();
+  const bool ring = op == B_PUT_SIGNAL_RING;
+  if (n < 2 || (!all_pairs && !ring && me != 0)) return;
+  // Which group am I, and does it take part?
+  int gid, per_block;
+  if (scope == SC_THREAD) { per_block = blockDim.x; gid = blockIdx.x * per_block + threadIdx.x; }
+  else if (scope == SC_WARP) { per_block = blockDim.x / 32; gid = blockIdx.x * per_block + threadIdx.x / 32; }
+  else { per_block = 1; gid = blockIdx.x; }
+  const bool active = gid < groups;
+  size_t share = ((bytes + groups - 1) / groups + 15) / 16 * 16;
+  if (bytes < 16) share = bytes;
+  size_t lo = share * size_t(gid), hi = lo + share;
+  if (lo > bytes) lo = bytes;
+  if (hi > bytes) hi = bytes;
+  const size_t len = active ? hi - lo : 0;
+  __shared__ int s_fail;
+  if (threadIdx.x == 0) s_fail = 0;
+  __syncthreads();
+  const unsigned long long t0 = detail::now_ns();
+  for (int i = 0; i < iters; ++i) {
+    const int pe = all_pairs ? (me + 1 + i % (n - 1)) % n : (me + 1) % n;
+    if (op == B_PUT || op == B_GET) {
+      if (active) {
+        if (scope == SC_THREAD) {
+          if (op == B_PUT) rocshmem_putmem(dst + lo, src + lo, len, pe); else rocshmem_getmem(dst + lo, src + lo, len, pe);
+        } else if (scope == SC_WARP) {
+          if (op == B_PUT) rocshmem_putmem_wave(dst + lo, src + lo, len, pe); else rocshmem_getmem_wave(dst + lo, src + lo, len, pe);
+        } else {
+          if (op == B_PUT) rocshmem_putmem_wg(dst + lo, src + lo, len, pe); else rocshmem_getmem_wg(dst + lo, src + lo, len, pe);
+        }
+      }
+    } else if (op == B_PUT_NBI_WINDOW) {
+      if (active) {
+        for (int m = 0; m < 64; ++m) {
+          if (scope == SC_THREAD) rocshmem_putmem_nbi(dst + lo, src + lo, len, pe);
+          else if (scope == SC_WARP) rocshmem_putmem_nbi_wave(dst + lo, src + lo, len, pe);
+          else rocshmem_putmem_nbi_wg(dst + lo, src + lo, len, pe);
+        }
+        rocshmem_quiet();
+      }
+    } else if (ring) {
+      // One group only (the host passes groups == 1): group 0 of block 0.
+      if (blockIdx.x == 0 && gid == 0) {
+        const uint64_t value = sig_base + uint64_t(i) + 1;
+        const int next = (me + 1) % n;
+        if (scope == SC_THREAD) {
+          if (threadIdx.x == 0) rocshmem_putmem_signal(dst, src, bytes, sig, value, ROCSHMEM_SIGNAL_SET, next);
+        } else if (scope == SC_WARP) {
+          rocshmem_putmem_signal_wave(dst, src, bytes, sig, value, ROCSHMEM_SIGNAL_SET, next);
+        } else {
+          rocshmem_putmem_signal_wg(dst, src, bytes, sig, value, ROCSHMEM_SIGNAL_SET, next);
+        }
+        // A wait that ran out ends the loop for the whole group at once (the calls above are collective).
+        if (threadIdx.x == 0 && rocshmemx_uint64_wait_until_status(sig, ROCSHMEM_CMP_GE, value) != ROCSHMEM_SUCCESS) {
+          s_fail = 1;
+        }
+        if (scope == SC_BLOCK) __syncthreads();
+        else if (scope == SC_WARP) __syncwarp();
+        if (*reinterpret_cast<volatile int *>(&s_fail)) break;
+      }
+    } else if (active) {
+      if (op == B_FETCH_ADD) {
+        (void)rocshmem_longlong_atomic_fetch_add(counter, 1, pe);
+      } else {
+        (void)rocshmem_longlong_atomic_compare_swap(counter, (long long)i, (long long)i + 1, pe);
+      }
+    }
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) ns[blockIdx.x] = detail::now_ns() - t0;
+}
+
 // Compile-time coverage of the typed API surface: references one member of every generated family
 // for every type table entry. It is launched with run == 0, so nothing executes.
 __global__ void api_surface_kernel(int run, void *p, rocshmem_team_t team) {
@@ -628,6 +719,13 @@ PYBIND11_MODULE(_testk, m) {
                  int threads, uintptr_t stream) {
     ok(kernels::launch_pes(bw_kernel, blocks, threads, 0, S(stream), false, mode, P<char>(dst), P<char>(src),
                            bytes, pe, iters, P<unsigned long long>(ns)), "bw_kernel");
+  });
+  m.def("rma_bench", [](int op, int scope, uintptr_t dst, uintptr_t src, size_t bytes, int groups, int iters,
+                        int all_pairs, uintptr_t sig, uintptr_t counter, uintptr_t ns, uint64_t sig_base, int blocks,
+                        int threads, uintptr_t stream) {
+    ok(kernels::launch_pes(rma_bench_kernel, blocks, threads, 0, S(stream), false, op, scope, P<char>(dst),
+                           P<char>(src), bytes, groups, iters, all_pairs, P<uint64_t>(sig), P<long long>(counter),
+                           P<unsigned long long>(ns), sig_base), "rma_bench_kernel");
   });
   m.def("mutex_test", [](uintptr_t ticket, uintptr_t spin, uintptr_t counters, uintptr_t grid_counter, int rounds,
                          uintptr_t phase_errors, int blocks, int threads, uintptr_t stream) {

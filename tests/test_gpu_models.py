@@ -61,12 +61,13 @@ def test_tp_mlp_single_rank(shm, d_model, d_ff, m):
         assert err <= 2e-2 * want.abs().max().item() + 0.05, (rep, err)
 
 
-def test_moe_feed_forward_fp8_experts(shm):
+@pytest.mark.parametrize("fused", [True, False])
+def test_moe_feed_forward_fp8_experts(shm, fused):
     """e4m3 rows from the dispatch feed block-scaled fp8 grouped GEMMs directly."""
     from rocshmem_b200.models import moe_ffn
     from rocshmem_b200.ops import gemm, moe
     E, K, H, I, T = 8, 2, 1024, 512, 300
-    layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=6, fp8_experts=True)
+    layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=6, fp8_experts=True, fused=fused)
     for rep in range(2):
         x = torch.randn(T, H, generator=torch.Generator().manual_seed(rep + 20)).to(torch.bfloat16)
         idx, w = moe.make_routing(T, E, K, seed=70 + rep)
