@@ -196,6 +196,19 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
       sm100::tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       const int row_base = int(rank) * BM;   // my rows inside the pair's tile
+      bool final_tile = false;
+      if constexpr (gemm::has_final_reduce<Epilogue>::value) {
+        final_tile = epi.is_final(t);
+        if (final_tile) {
+          int ok = 1;
+          if (lane == 0) ok = epi.wait_partials(t) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) {
+            sh.abort_flag = 1;
+            break;
+          }
+        }
+      }
       constexpr int OUT_CHUNKS = (SWIGLU ? BN / 2 : BN) / EPI_COLS;
 #pragma unroll 1
       for (int c = 0; c < OUT_CHUNKS; ++c) {
@@ -226,26 +239,16 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
           }
         }
         __syncwarp();
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int r = it * 4 + lane / 8, seg = lane % 8;
-          const int row = row_base + quarter * 32 + r;
-          const int col = c * EPI_COLS + seg * 8;
-          if (row < t.rows && col < t.cols) {
-            __nv_bfloat16 *out = epi.row_ptr(t, row);
-            if (out != nullptr) {
-              const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
-              __nv_bfloat16 *dst = out + col;
-              if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(src);
-              } else {
-                const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
-                for (int i = 0; i < 8 && col + i < t.cols; ++i) dst[i] = s16[i];
-              }
-            }
-          }
+        if constexpr (gemm::has_final_reduce<Epilogue>::value) {
+          if (final_tile) gemm::write_out_block<false, true>(t, epi, stg, row_base + quarter * 32, c * EPI_COLS, lane);
+          else gemm::write_out_block<false, false>(t, epi, stg, row_base + quarter * 32, c * EPI_COLS, lane);
+        } else {
+          gemm::write_out_block<false, false>(t, epi, stg, row_base + quarter * 32, c * EPI_COLS, lane);
         }
         __syncwarp();
+      }
+      if constexpr (gemm::has_final_reduce<Epilogue>::value) {
+        if (!final_tile) epi.tile_done(t, lane);
       }
       sm100::tcgen05_fence_before();
       __syncwarp();

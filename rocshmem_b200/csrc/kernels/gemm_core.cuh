@@ -10,15 +10,18 @@
 //               accumulator the MMA warp already fills the other one.
 // Policies supply the tile order (Scheduler), a hook the producer calls before it loads a tile's A
 // rows (used to wait for rows that another GPU is still sending) and the epilogue's destination.
-// A rows can also be gathered by index (warps 6..9 instead of TMA: one thread per tile row loads its row's 128
-// bytes of the K slab, optionally de-quantises e4m3 to bf16, and stores them with the 128-byte swizzle), and the
-// epilogue can scale rows and add them into the destination instead of storing them.
+// A rows can also be gathered by index (warps 6..9 instead of TMA: one thread per tile row moves its row's 128
+// bytes of the K slab into the stage with the 128-byte swizzle, either with cp.async or, when e4m3 rows are
+// de-quantised to bf16 on the way, through registers), and the epilogue can scale rows and add them into the
+// destination instead of storing them.
 // Every wait is bounded; on expiry the CTA sets its abort flag, all roles leave their loops, TMEM is
 // freed and a global error counter is bumped.
 #pragma once
 
 #include <cuda_bf16.h>
 #include <cuda_fp8.h>
+
+#include <type_traits>
 
 #include "sm100_ptx.cuh"
 
@@ -80,6 +83,102 @@ struct GatherSrc {
   const float *scales;
   int nscale;
 };
+
+// An epilogue policy may declare `static constexpr bool kFinalReduce = true` to take part in a reduction across
+// GPUs: tiles for which is_final(t) holds are not stored as they are but summed (fp32) with n_partials(t) staged
+// partial tiles (partial(t, s, row) points at element (row, t.c_col) of partial s) once wait_partials(t) has seen
+// them arrive, and every other tile is announced to its owner with tile_done(t) after its stores.
+template <class E, class = void>
+struct has_final_reduce : std::false_type {};
+template <class E>
+struct has_final_reduce<E, std::void_t<decltype(E::kFinalReduce)>> : std::true_type {};
+
+// Write-out of one warp's staged 32 x 64 bf16 block (padded rows in shared memory), 8 lanes per row, shared by the
+// one-CTA and the two-CTA cores. FINAL: add the staged partials of the other GPUs before storing (two row groups
+// with all their partials' loads in flight at a time).
+template <bool EPI_ADD, bool FINAL, class Epilogue>
+__device__ __forceinline__ void write_out_block(const Tile &t, Epilogue &epi, const unsigned char *stg, int row0,
+                                                int col0, int lane) {
+  constexpr int MAXP = 7;
+#pragma unroll 1
+  for (int it0 = 0; it0 < 8; it0 += 2) {
+    int4 part[2][MAXP];
+    int np = 0;
+    if constexpr (FINAL) np = epi.n_partials(t);
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int r = (it0 + u) * 4 + lane / 8, seg = lane % 8;
+      const int row = row0 + r, col = col0 + seg * 8;
+      const bool full = row < t.rows && col + 8 <= t.cols;
+      if constexpr (FINAL) {
+#pragma unroll
+        for (int s = 0; s < MAXP; ++s) {
+          if (s < np && full) part[u][s] = __ldcg(reinterpret_cast<const int4 *>(epi.partial(t, s, row) + col));
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int r = (it0 + u) * 4 + lane / 8, seg = lane % 8;
+      const int row = row0 + r, col = col0 + seg * 8;
+      if (row >= t.rows || col >= t.cols) continue;
+      __nv_bfloat16 *out = epi.row_ptr(t, row);
+      if (out == nullptr) continue;
+      const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
+      __nv_bfloat16 *dst = out + col;
+      if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+        int4 val = *reinterpret_cast<const int4 *>(src);
+        if constexpr (FINAL) {
+          float acc[8];
+          const __nv_bfloat162 *v2 = reinterpret_cast<const __nv_bfloat162 *>(&val);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const float2 f = __bfloat1622float2(v2[i]);
+            acc[2 * i] = f.x;
+            acc[2 * i + 1] = f.y;
+          }
+#pragma unroll
+          for (int s = 0; s < MAXP; ++s) {
+            if (s < np) {
+              const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&part[u][s]);
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const float2 f = __bfloat1622float2(p2[i]);
+                acc[2 * i] += f.x;
+                acc[2 * i + 1] += f.y;
+              }
+            }
+          }
+          for (int s = MAXP; s < np; ++s) {   // teams of more than eight: the rest one by one
+            const int4 extra = __ldcg(reinterpret_cast<const int4 *>(epi.partial(t, s, row) + col));
+            const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&extra);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const float2 f = __bfloat1622float2(p2[i]);
+              acc[2 * i] += f.x;
+              acc[2 * i + 1] += f.y;
+            }
+          }
+          __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&val);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
+        }
+        if (EPI_ADD) sm100::red_add_bf16x8(dst, val);
+        else *reinterpret_cast<int4 *>(dst) = val;
+      } else {
+        const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
+        for (int i = 0; i < 8 && col + i < t.cols; ++i) {
+          float v = __bfloat162float(s16[i]);
+          if constexpr (FINAL) {
+            for (int s = 0; s < np; ++s) v += __bfloat162float(epi.partial(t, s, row)[col + i]);
+          }
+          if (EPI_ADD) atomicAdd(dst + i, __float2bfloat16_rn(v));
+          else dst[i] = __float2bfloat16_rn(v);
+        }
+      }
+    }
+  }
+}
 
 struct Shared {
   uint64_t full[STAGES];
@@ -169,6 +268,9 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         for (int ks = 0; ks < k_slabs; ++ks) {
           if (!sm100::mbar_wait(&sh.full[stage], phase, &sh.abort_flag, WAIT_BUDGET_NS)) break;
           sm100::tcgen05_fence_after();
+          // Gathered rows were written through the generic proxy (cp.async, st.shared); the MMA reads them through
+          // the async proxy.
+          if (A_GATHER) sm100::fence_proxy_async_smem();
           const uint32_t sa = sm100::smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
           const uint64_t da = sm100::make_sw128_desc(sa), db = sm100::make_sw128_desc(sb);
@@ -188,10 +290,7 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
     }
   } else if (A_GATHER != 0 && warp >= 6 && warp < 6 + GATHER_WARPS) {
     // ---- gather producer: thread r owns tile row r -----------------------------------------------------------------
-    // Two K slabs are kept in flight in registers (loads of slab ks + 2 are issued right after slab ks has been
-    // stored), so that the L2 latency of a row's 128 bytes is covered by two stages of MMAs.
     static_assert(A_GATHER == 0 || A_GATHER == 1 || (A_GATHER == 2 && !IS_FP8), "de-quantising gather feeds bf16");
-    constexpr int NV = A_GATHER == 2 ? 4 : 8;   // 16-byte source vectors per row and slab
     const int r = (warp - 6) * 32 + lane;
     const uint32_t row_off = static_cast<uint32_t>(r) * SLAB_BYTES;
     const uint32_t sw = static_cast<uint32_t>(r & 7);
@@ -200,58 +299,74 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
     for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
       const bool live = r < t.rows;
       const long long src_row = live ? gather->row_index[t.a_row + r] : 0;
-      const int4 *src = reinterpret_cast<const int4 *>(gather->base + static_cast<size_t>(src_row) * gather->row_bytes);
-      const float *sc = A_GATHER == 2 ? gather->scales + static_cast<size_t>(src_row) * gather->nscale : nullptr;
-      int4 buf0[NV], buf1[NV];
-      auto fetch = [&](int4 (&b)[NV], int ks) {
-        if (live && ks < k_slabs) {
-#pragma unroll
-          for (int c = 0; c < NV; ++c) b[c] = __ldg(src + ks * NV + c);
-        } else {
-#pragma unroll
-          for (int c = 0; c < NV; ++c) b[c] = make_int4(0, 0, 0, 0);
-        }
-      };
-      auto put = [&](const int4 (&b)[NV], int ks) -> bool {
-        if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) return false;
-        unsigned char *sa = smem + stage * STAGE_BYTES + row_off;
-        if (A_GATHER == 2) {
-          // 64 e4m3 values of this slab -> 64 bf16 (eight 16-byte chunks); one scale covers two slabs.
-          const float scale = live ? __ldg(sc + ks / 2) : 0.f;
-#pragma unroll
-          for (int c = 0; c < NV; ++c) {
-            const unsigned short *p = reinterpret_cast<const unsigned short *>(&b[c]);
-            int4 o[2];
-            __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(o);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p[i], __NV_E4M3);
-              const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&h));
-              o2[i] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
-            }
-            *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(2 * c) ^ sw) << 4)) = o[0];
-            *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(2 * c + 1) ^ sw) << 4)) = o[1];
-          }
-        } else {
-#pragma unroll
-          for (int c = 0; c < NV; ++c) *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(c) ^ sw) << 4)) = b[c];
-        }
-        sm100::fence_proxy_async_smem();
-        sm100::mbar_arrive(&sh.full[stage]);
-        if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-        return true;
-      };
-      fetch(buf0, 0);
-      fetch(buf1, 1);
+      const unsigned char *src = gather->base + static_cast<size_t>(src_row) * gather->row_bytes;
       bool ok = true;
-      for (int ks = 0; ks < k_slabs && ok; ks += 2) {
-        ok = put(buf0, ks);
-        if (!ok) break;
-        fetch(buf0, ks + 2);
-        if (ks + 1 < k_slabs) {
-          ok = put(buf1, ks + 1);
+      if constexpr (A_GATHER == 1) {
+        // Rows already have the MMA's element type: asynchronous 16-byte copies straight into the stage. The thread
+        // never waits for data, so it runs as far ahead as the ring has free stages; the stage's barrier gets this
+        // thread's arrival when its copies have landed. (The MMA thread crosses to the async proxy after its wait.)
+        for (int ks = 0; ks < k_slabs; ++ks) {
+          if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+          unsigned char *sa = smem + stage * STAGE_BYTES + row_off;
+          const unsigned char *g = src + static_cast<size_t>(ks) * SLAB_BYTES;
+#pragma unroll
+          for (uint32_t c = 0; c < 8; ++c) sm100::cp_async_16(sa + ((c ^ sw) << 4), g + c * 16, live ? 16u : 0u);
+          sm100::cp_async_arrive_noinc(&sh.full[stage]);
+          if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+        }
+      } else {
+        // e4m3 source: one 128-byte line of the row feeds two K slabs of bf16. Two lines (four slabs) are kept in
+        // flight in registers: a line's loads are issued right after the line before it has been converted.
+        const float *sc = gather->scales + static_cast<size_t>(src_row) * gather->nscale;
+        const int lines = (k_slabs + 1) / 2;
+        int4 buf0[8], buf1[8];
+        auto fetch = [&](int4 (&b)[8], int line) {
+          if (live && line < lines) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) b[c] = __ldg(reinterpret_cast<const int4 *>(src) + line * 8 + c);
+          } else {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) b[c] = make_int4(0, 0, 0, 0);
+          }
+        };
+        auto put = [&](const int4 (&b)[8], int line) -> bool {
+          const float scale = (live && line < lines) ? __ldg(sc + line) : 0.f;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            if (2 * line + half >= k_slabs) break;
+            if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) return false;
+            unsigned char *sa = smem + stage * STAGE_BYTES + row_off;
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const unsigned short *p = reinterpret_cast<const unsigned short *>(&b[half * 4 + c]);
+              int4 o[2];
+              __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(o);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) {
+                const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p[i], __NV_E4M3);
+                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&h));
+                o2[i] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+              }
+              *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(2 * c) ^ sw) << 4)) = o[0];
+              *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(2 * c + 1) ^ sw) << 4)) = o[1];
+            }
+            sm100::fence_proxy_async_smem();
+            sm100::mbar_arrive(&sh.full[stage]);
+            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+          }
+          return true;
+        };
+        fetch(buf0, 0);
+        fetch(buf1, 1);
+        for (int line = 0; line < lines && ok; line += 2) {
+          ok = put(buf0, line);
           if (!ok) break;
-          fetch(buf1, ks + 3);
+          fetch(buf0, line + 2);
+          if (line + 1 < lines) {
+            ok = put(buf1, line + 1);
+            if (!ok) break;
+            fetch(buf1, line + 3);
+          }
         }
       }
       if (!ok || sh.abort_flag) break;
@@ -275,6 +390,19 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
       sm100::tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       constexpr int OUT_CHUNKS = (SWIGLU ? BN / 2 : BN) / EPI_COLS;
+      bool final_tile = false;
+      if constexpr (has_final_reduce<Epilogue>::value) {
+        final_tile = epi.is_final(t);
+        if (final_tile) {
+          int ok = 1;
+          if (lane == 0) ok = epi.wait_partials(t) ? 1 : 0;
+          ok = __shfl_sync(0xffffffffu, ok, 0);
+          if (!ok) {
+            sh.abort_flag = 1;
+            break;
+          }
+        }
+      }
       float row_scale = 1.f;
       if constexpr (EPI_ADD) row_scale = (quarter * 32 + lane) < t.rows ? epi.row_scale(t, quarter * 32 + lane) : 0.f;
 #pragma unroll 1
@@ -310,30 +438,16 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
           }
         }
         __syncwarp();
-#pragma unroll
-        for (int it = 0; it < 8; ++it) {
-          const int r = it * 4 + lane / 8, seg = lane % 8;
-          const int row = quarter * 32 + r;
-          const int col = c * EPI_COLS + seg * 8;
-          if (row < t.rows && col < t.cols) {
-            __nv_bfloat16 *out = epi.row_ptr(t, row);
-            if (out != nullptr) {
-              const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
-              __nv_bfloat16 *dst = out + col;
-              if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-                if (EPI_ADD) sm100::red_add_bf16x8(dst, *reinterpret_cast<const int4 *>(src));
-                else *reinterpret_cast<int4 *>(dst) = *reinterpret_cast<const int4 *>(src);
-              } else {
-                const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
-                for (int i = 0; i < 8 && col + i < t.cols; ++i) {
-                  if (EPI_ADD) atomicAdd(dst + i, s16[i]);
-                  else dst[i] = s16[i];
-                }
-              }
-            }
-          }
+        if constexpr (has_final_reduce<Epilogue>::value) {
+          if (final_tile) write_out_block<EPI_ADD, true>(t, epi, stg, quarter * 32, c * EPI_COLS, lane);
+          else write_out_block<EPI_ADD, false>(t, epi, stg, quarter * 32, c * EPI_COLS, lane);
+        } else {
+          write_out_block<EPI_ADD, false>(t, epi, stg, quarter * 32, c * EPI_COLS, lane);
         }
         __syncwarp();
+      }
+      if constexpr (has_final_reduce<Epilogue>::value) {
+        if (!final_tile) epi.tile_done(t, lane);
       }
       sm100::tcgen05_fence_before();
       __syncwarp();

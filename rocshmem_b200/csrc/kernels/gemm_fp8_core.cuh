@@ -61,8 +61,8 @@ struct Shared {
 // operand; they are quantised to e4m3 here (the two threads that hold a row's halves exchange their maxima through
 // shared memory) and written to epi.q_row_ptr(t, row) with the block's scale at epi.scale_ptr(t, row).
 // A_GATHER: the A rows (and their scales) are picked by index: tile row r reads row gather->row_index[t.a_row + r]
-// of gather->base / gather->scales. Two extra warps (threads THREADS .. GATHER_THREADS) store the rows into the
-// stage with the 128-byte swizzle instead of a TMA load; the kernel must then be launched with GATHER_THREADS.
+// of gather->base / gather->scales. Two extra warps (threads THREADS .. GATHER_THREADS) copy the rows into the
+// stage with the 128-byte swizzle (cp.async) instead of a TMA load; the kernel must then be launched with GATHER_THREADS.
 template <bool SWIGLU, bool LATE_A = false, bool EPI_ADD = false, bool QUANT_OUT = false, bool A_GATHER = false,
           class Scheduler, class Epilogue>
 __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap *map_b, const float *a_scale,
@@ -127,6 +127,7 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
           if (!sm100::mbar_wait(&sh.tmem_empty[buf], buf_phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) break;
           if (!sm100::mbar_wait(&sh.full[stage], phase, &sh.abort_flag, WAIT_BUDGET_NS)) break;
           sm100::tcgen05_fence_after();
+          if (A_GATHER) sm100::fence_proxy_async_smem();   // rows written by cp.async, read by the async proxy
           const uint32_t tmem_d = tmem_base + buf * BN;
           const uint32_t sa = sm100::smem_u32(smem + stage * STAGE_BYTES);
           const uint32_t sb = sa + A_STAGE_BYTES;
@@ -143,60 +144,35 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
       }
     }
   } else if (A_GATHER && warp >= 2 + ACC_WARPS) {
-    // ---- gather producer: a thread owns two tile rows and keeps two K blocks of both in flight in registers ----
+    // ---- gather producer: a thread owns two tile rows and copies their 128 bytes of every K block into the stage
+    // with asynchronous 16-byte copies (no registers, so it runs as far ahead as the ring has free stages) ----------
     const int g = (warp - 2 - ACC_WARPS) * 32 + lane;   // 0 .. 63
     uint32_t stage = 0, phase = 0;
     gemm::Tile t;
     for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
-      const int4 *src[2];
+      const unsigned char *src[2];
       bool live[2];
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         const int r = g + 64 * h;
         live[h] = r < t.rows;
         const long long src_row = live[h] ? gather->row_index[t.a_row + r] : 0;
-        src[h] = reinterpret_cast<const int4 *>(gather->base + static_cast<size_t>(src_row) * gather->row_bytes);
+        src[h] = gather->base + static_cast<size_t>(src_row) * gather->row_bytes;
       }
-      int4 buf0[2][8], buf1[2][8];
-      auto fetch = [&](int4 (&b)[2][8], int kb) {
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          if (live[h] && kb < k_blocks) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) b[h][c] = __ldg(src[h] + kb * 8 + c);
-          } else {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) b[h][c] = make_int4(0, 0, 0, 0);
-          }
-        }
-      };
-      auto put = [&](const int4 (&b)[2][8]) -> bool {
-        if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) return false;
+      bool ok = true;
+      for (int kb = 0; kb < k_blocks; ++kb) {
+        if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
           const int r = g + 64 * h;
           unsigned char *sa = smem + stage * STAGE_BYTES + r * KB;
           const uint32_t sw = static_cast<uint32_t>(r & 7);
+          const unsigned char *gp = src[h] + static_cast<size_t>(kb) * KB;
 #pragma unroll
-          for (int c = 0; c < 8; ++c) *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(c) ^ sw) << 4)) = b[h][c];
+          for (uint32_t c = 0; c < 8; ++c) sm100::cp_async_16(sa + ((c ^ sw) << 4), gp + c * 16, live[h] ? 16u : 0u);
         }
-        sm100::fence_proxy_async_smem();
-        sm100::mbar_arrive(&sh.full[stage]);
+        sm100::cp_async_arrive_noinc(&sh.full[stage]);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-        return true;
-      };
-      fetch(buf0, 0);
-      fetch(buf1, 1);
-      bool ok = true;
-      for (int kb = 0; kb < k_blocks && ok; kb += 2) {
-        ok = put(buf0);
-        if (!ok) break;
-        fetch(buf0, kb + 2);
-        if (kb + 1 < k_blocks) {
-          ok = put(buf1);
-          if (!ok) break;
-          fetch(buf1, kb + 3);
-        }
       }
       if (!ok || sh.abort_flag) break;
     }

@@ -104,6 +104,16 @@ __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.
 // Makes this thread's earlier shared-memory writes (generic proxy) visible to the async proxy (TMA, tcgen05.mma):
 // the writer executes it after its stores and before it signals the reader.
 __device__ __forceinline__ void fence_proxy_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+// 16-byte asynchronous copy global -> shared (LDGSTS, no registers); src_bytes == 0 writes zeros instead.
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src, uint32_t src_bytes) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(smem_dst)), "l"(gmem_src), "r"(src_bytes)
+               : "memory");
+}
+// The mbarrier receives one arrival (already counted in its expected count) once all cp.async operations that this
+// thread has issued so far have completed.
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t *bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
 // Adds eight bf16 values (four packed pairs) to 16 bytes of global memory, no return value. The address must be
 // 16-byte aligned.
 __device__ __forceinline__ void red_add_bf16x8(void *gmem, const int4 &v) {
