@@ -11,8 +11,8 @@ Families:
   collectives  two PEs on the one GPU (one cooperative launch per call, so the peer paths run over the local
                mapping): allreduce (flag-in-word, one-shot, two-shot), fcollect / alltoall / broadcast push kernels
   ep           dispatch and combine, fixed shares and pair hand-out, and the low-latency pair (one PE)
-  moe          the grouped GEMMs of the MoE layer: gathered e4m3 -> bf16 with SwiGLU, scatter-add, and their
-               block-scaled forms (32 experts x ~1024 rows, hidden 7168, intermediate 2048)
+  moe          the grouped GEMMs of the MoE layer: gathered bf16 rows with SwiGLU, scatter-add, and their
+               block-scaled forms (gathered e4m3 rows, quantising epilogue) (32 experts x ~1024 rows, hidden 7168, intermediate 2048)
   tp           all-gather -> GEMM and GEMM -> reduce-scatter on a team of one (the tensor-core side of the fused
                kernels; the NVLink side needs several GPUs and is timed by benchmarks/model_bench.py)
 """
@@ -114,7 +114,9 @@ def tour_moe(reps, flush, rows):
     def add(name, us, flops):
         rows.append({"family": "moe", "kernel": name, "us": us, "tflops": flops / us / 1e6})
 
-    add("grouped gate/up, gathered e4m3 -> bf16, SwiGLU", timed(lambda: gemm.grouped_gemm_bf16_gathered(xq, row_index, w13, offsets, a_scales=xs, swiglu=True, out=h), reps, flush), f1)
+    xb = moe.fp8_dequantize_1x128(xq, xs)
+    add("grouped gate/up, gathered bf16 rows, SwiGLU", timed(lambda: gemm.grouped_gemm_bf16_gathered(xb, row_index, w13, offsets, swiglu=True, out=h), reps, flush), f1)
+    del xb
     add("grouped down, scatter-add epilogue", timed(lambda: gemm.grouped_gemm_bf16_scatter_add(h, w2, offsets, row_index, y, weights=weights), reps, flush), f2)
     w13q, w13s = gemm.quantize_weight_128x128(w13)
     w2q, w2s = gemm.quantize_weight_128x128(w2)

@@ -104,7 +104,7 @@ def bench_tp_mlp(args, world, rank, res):
 def bench_moe(args, world, rank, res):
     E, K, H, I, T = args.experts, args.top_k, args.hidden, args.inter, args.moe_tokens
     cap = int(T * K * args.capacity_factor)
-    layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=2, pair_capacity=cap)
+    layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=2, pair_capacity=cap, fp8_experts=False)
     x = torch.randn(T, H, device="cuda").to(torch.bfloat16)
     idx, w = moe.make_routing(T, E, K, seed=100 + rank, device="cuda")
     out = layer(x, idx, w)
@@ -113,18 +113,7 @@ def bench_moe(args, world, rank, res):
     assert pairs <= cap, (pairs, cap)
     t_layer = timed(lambda: layer(x, idx, w), args.iters)
     row = {"experts": E, "top_k": K, "hidden": H, "inter": I, "tokens_per_rank": T, "layer_us": t_layer,
-           "fused": bool(layer.fused), "pairs_this_rank": pairs, "tokens_per_s_all_ranks": world * T / t_layer * 1e6}
-    if args.moe_unfused:
-        # The same layer with separate gather and per-row reduction kernels, for comparison.
-        plain = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=2, pair_capacity=cap, fused=False)
-        out_plain = plain(x, idx, w)
-        torch.cuda.synchronize()
-        row["unfused_max_abs_diff"] = (out_plain.float() - out.float()).abs().max().item()
-        row["unfused_layer_us"] = timed(lambda: plain(x, idx, w), args.iters)
-        stages_plain = {}
-        plain(x, idx, w, stage_us=stages_plain)
-        row["unfused_stage_us_rank0"] = stages_plain
-        plain.destroy()
+           "experts_dtype": "bf16", "pairs_this_rank": pairs, "tokens_per_s_all_ranks": world * T / t_layer * 1e6}
     flops = 2.0 * pairs * H * (2 * I) + 2.0 * pairs * I * H
     row["expert_tflops_this_rank"] = flops / t_layer / 1e6
     if args.moe_baseline:
@@ -138,7 +127,8 @@ def bench_moe(args, world, rank, res):
     stages = {}
     layer(x, idx, w, stage_us=stages)
     row["stage_us_rank0"] = stages
-    if H % 1024 == 0 and I % 512 == 0:
+    layer.destroy()
+    if H % 512 == 0 and I % 512 == 0:
         layer8 = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=T, seed=2, pair_capacity=cap, fp8_experts=True)
         out8 = layer8(x, idx, w)
         torch.cuda.synchronize()
@@ -148,6 +138,10 @@ def bench_moe(args, world, rank, res):
         row["fp8_experts_max_abs_diff_vs_bf16_experts"] = (out8.float() - out.float()).abs().max().item()
         row["fp8_experts_layer_us"] = timed(lambda: layer8(x, idx, w), args.iters)
         row["fp8_experts_tokens_per_s_all_ranks"] = world * T / row["fp8_experts_layer_us"] * 1e6
+        row["fp8_experts_tflops_this_rank"] = flops / row["fp8_experts_layer_us"] / 1e6
+        if args.moe_baseline:
+            row["fp8_experts_speedup"] = row["nccl_cublas_us"] / row["fp8_experts_layer_us"]
+        layer8.destroy()
     row["gemm_errors"] = gemm.gemm_error_count()
     res["moe_ffn"] = row
 
@@ -167,7 +161,6 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--skip", default="", help="comma list of: tp_mlp, moe")
     ap.add_argument("--no-moe-baseline", dest="moe_baseline", action="store_false")
-    ap.add_argument("--moe-unfused", action="store_true", help="also time the layer with separate gather / reduction kernels")
     args = ap.parse_args()
     rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))

@@ -94,16 +94,6 @@ void bind_ep(py::module_ &m) {
     check(moe_gather_rows(P<void>(recv_x), P<float>(scales), fp8, P<int>(offsets), experts, P<int>(row_index), hidden,
                           P<void>(out), P<void>(stream)), "moe_gather_rows");
   });
-  m.def("moe_inverse_map", [](uintptr_t offsets, int experts, uintptr_t row_index, uintptr_t pair_k, int top_k,
-                              uintptr_t inverse, uintptr_t stream) {
-    check(moe_inverse_map(P<int>(offsets), experts, P<int>(row_index), P<int>(pair_k), top_k, P<int>(inverse),
-                          P<void>(stream)), "moe_inverse_map");
-  });
-  m.def("moe_reduce_pairs", [](uintptr_t pairs, uintptr_t inverse, uintptr_t recv_meta, uintptr_t recv_info,
-                               int n_ranks, int top_k, int hidden, int weighted, uintptr_t y, uintptr_t stream) {
-    check(moe_reduce_pairs(P<void>(pairs), P<int>(inverse), P<int>(recv_meta), P<int>(recv_info), n_ranks, top_k,
-                           hidden, weighted, P<void>(y), P<void>(stream)), "moe_reduce_pairs");
-  });
   m.def("moe_zero_rows", [](uintptr_t recv_info, int n_ranks, int hidden, uintptr_t y, uintptr_t stream) {
     check(moe_zero_rows(P<int>(recv_info), n_ranks, hidden, P<void>(y), P<void>(stream)), "moe_zero_rows");
   });

@@ -35,12 +35,10 @@ void bind_gemm(py::module_ &m) {
     check(grouped_gemm_bf16(P<void>(a), P<void>(b), P<void>(c), P<int>(offsets), groups, max_rows, N, K, swiglu,
                             P<void>(stream)), "grouped_gemm_bf16");
   });
-  m.def("grouped_gemm_bf16_gathered", [](uintptr_t a_rows, int a_is_fp8, uintptr_t a_scales, uintptr_t row_index,
-                                         uintptr_t b, uintptr_t c, uintptr_t offsets, int groups, int N, int K,
-                                         int swiglu, uintptr_t stream) {
-    check(grouped_gemm_bf16_gathered(P<void>(a_rows), a_is_fp8, P<float>(a_scales), P<int>(row_index), P<void>(b),
-                                     P<void>(c), P<int>(offsets), groups, N, K, swiglu, P<void>(stream)),
-          "grouped_gemm_bf16_gathered");
+  m.def("grouped_gemm_bf16_gathered", [](uintptr_t a_rows, uintptr_t row_index, uintptr_t b, uintptr_t c,
+                                         uintptr_t offsets, int groups, int N, int K, int swiglu, uintptr_t stream) {
+    check(grouped_gemm_bf16_gathered(P<void>(a_rows), P<int>(row_index), P<void>(b), P<void>(c), P<int>(offsets), groups,
+                                     N, K, swiglu, P<void>(stream)), "grouped_gemm_bf16_gathered");
   });
   m.def("grouped_gemm_bf16_scatter_add", [](uintptr_t a, uintptr_t b, uintptr_t y, uintptr_t offsets,
                                             uintptr_t row_index, uintptr_t weights, int groups, int max_rows, int N,

@@ -10,10 +10,9 @@
 //               accumulator the MMA warp already fills the other one.
 // Policies supply the tile order (Scheduler), a hook the producer calls before it loads a tile's A
 // rows (used to wait for rows that another GPU is still sending) and the epilogue's destination.
-// A rows can also be gathered by index (warps 6..9 instead of TMA: one thread per tile row moves its row's 128
-// bytes of the K slab into the stage with the 128-byte swizzle, either with cp.async or, when e4m3 rows are
-// de-quantised to bf16 on the way, through registers), and the epilogue can scale rows and add them into the
-// destination instead of storing them.
+// A rows can also be gathered by index (warps 6..9 instead of TMA: cp.async copies of each row's 128 bytes of the K
+// slab into the stage with the 128-byte swizzle, eight lanes per row), and the epilogue can scale rows and add
+// them into the destination instead of storing them.
 // Every wait is bounded; on expiry the CTA sets its abort flag, all roles leave their loops, TMEM is
 // freed and a global error counter is bumped.
 #pragma once
@@ -73,9 +72,8 @@ __device__ __forceinline__ void raster(int id, int row_blocks, int tiles_n, int 
 static __device__ unsigned int g_gemm_errors = 0;
 
 // Where the A rows come from when they are gathered: tile row r of a tile reads source row
-// row_index[t.a_row + r]. A_GATHER 1: rows hold the MMA's element type (row_bytes = K * element size).
-// A_GATHER 2 (bf16 MMA only): rows are e4m3 with one fp32 scale per 128 elements (`scales` [rows, nscale]) and
-// are de-quantised to bf16 on the way into shared memory.
+// row_index[t.a_row + r], which holds the MMA's element type (row_bytes = K * element size). The block-scaled core
+// also reads the rows' scales through the index (`scales` [rows, nscale]).
 struct GatherSrc {
   const int *row_index;
   const unsigned char *base;
@@ -199,7 +197,7 @@ __device__ __forceinline__ float silu(float x) { return x / (1.0f + __expf(-x));
 //            returning the address of output element (row, t.c_col), or nullptr to skip the row; with EPI_ADD
 //            also  __device__ float row_scale(const Tile &t, int row_in_tile)  and the rows are multiplied by it
 //            and added to the destination (red.global.add on packed bf16) instead of stored.
-template <bool IS_FP8, bool SWIGLU, int A_GATHER = 0, bool EPI_ADD = false, class Scheduler, class Epilogue>
+template <bool IS_FP8, bool SWIGLU, bool A_GATHER = false, bool EPI_ADD = false, class Scheduler, class Epilogue>
 __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap *map_b, int k_bytes,
                                     Scheduler &sched, Epilogue &epi, unsigned char *smem_raw, Shared &sh,
                                     const GatherSrc *gather = nullptr) {
@@ -288,85 +286,43 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         sm100::mma_commit(&sh.tmem_full[acc]);  // accumulator complete
       }
     }
-  } else if (A_GATHER != 0 && warp >= 6 && warp < 6 + GATHER_WARPS) {
-    // ---- gather producer: thread r owns tile row r -----------------------------------------------------------------
-    static_assert(A_GATHER == 0 || A_GATHER == 1 || (A_GATHER == 2 && !IS_FP8), "de-quantising gather feeds bf16");
-    const int r = (warp - 6) * 32 + lane;
-    const uint32_t row_off = static_cast<uint32_t>(r) * SLAB_BYTES;
-    const uint32_t sw = static_cast<uint32_t>(r & 7);
+  } else if (A_GATHER && warp >= 6 && warp < 6 + GATHER_WARPS) {
+    // ---- gather producers -----------------------------------------------------------------------------------------
+    // Lanes are laid out so that neighbouring lanes read neighbouring 16-byte pieces of one row (a warp instruction
+    // then touches 4 or 8 lines, not 32): warp w serves tile rows [32 w, 32 w + 32).
+    const int gw = warp - 6;
     uint32_t stage = 0, phase = 0;
     Tile t;
     for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
-      const bool live = r < t.rows;
-      const long long src_row = live ? gather->row_index[t.a_row + r] : 0;
-      const unsigned char *src = gather->base + static_cast<size_t>(src_row) * gather->row_bytes;
       bool ok = true;
-      if constexpr (A_GATHER == 1) {
-        // Rows already have the MMA's element type: asynchronous 16-byte copies straight into the stage. The thread
-        // never waits for data, so it runs as far ahead as the ring has free stages; the stage's barrier gets this
-        // thread's arrival when its copies have landed. (The MMA thread crosses to the async proxy after its wait.)
+      {
+        // Rows have the MMA's element type: asynchronous 16-byte copies straight into the stage, eight
+        // lanes per row (128 contiguous bytes), four rows per instruction, eight instructions per stage and warp.
+        // The thread never waits for data, so it runs as far ahead as the ring has free stages; the stage's barrier
+        // gets this thread's arrival when its copies have landed. (The MMA thread crosses to the async proxy after
+        // its wait.)
+        const uint32_t c = static_cast<uint32_t>(lane & 7);
+        const unsigned char *src[8];
+        uint32_t dst_off[8];
+        uint32_t live_bytes[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const int r = gw * 32 + j * 4 + lane / 8;
+          const bool live = r < t.rows;
+          const long long src_row = live ? gather->row_index[t.a_row + r] : 0;
+          src[j] = gather->base + static_cast<size_t>(src_row) * gather->row_bytes + c * 16;
+          dst_off[j] = static_cast<uint32_t>(r) * SLAB_BYTES + ((c ^ static_cast<uint32_t>(r & 7)) << 4);
+          live_bytes[j] = live ? 16u : 0u;
+        }
         for (int ks = 0; ks < k_slabs; ++ks) {
           if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
-          unsigned char *sa = smem + stage * STAGE_BYTES + row_off;
-          const unsigned char *g = src + static_cast<size_t>(ks) * SLAB_BYTES;
+          unsigned char *sa = smem + stage * STAGE_BYTES;
 #pragma unroll
-          for (uint32_t c = 0; c < 8; ++c) sm100::cp_async_16(sa + ((c ^ sw) << 4), g + c * 16, live ? 16u : 0u);
+          for (int j = 0; j < 8; ++j) {
+            sm100::cp_async_16(sa + dst_off[j], src[j] + static_cast<size_t>(ks) * SLAB_BYTES, live_bytes[j]);
+          }
           sm100::cp_async_arrive_noinc(&sh.full[stage]);
           if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-        }
-      } else {
-        // e4m3 source: one 128-byte line of the row feeds two K slabs of bf16. Two lines (four slabs) are kept in
-        // flight in registers: a line's loads are issued right after the line before it has been converted.
-        const float *sc = gather->scales + static_cast<size_t>(src_row) * gather->nscale;
-        const int lines = (k_slabs + 1) / 2;
-        int4 buf0[8], buf1[8];
-        auto fetch = [&](int4 (&b)[8], int line) {
-          if (live && line < lines) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) b[c] = __ldg(reinterpret_cast<const int4 *>(src) + line * 8 + c);
-          } else {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) b[c] = make_int4(0, 0, 0, 0);
-          }
-        };
-        auto put = [&](const int4 (&b)[8], int line) -> bool {
-          const float scale = (live && line < lines) ? __ldg(sc + line) : 0.f;
-#pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            if (2 * line + half >= k_slabs) break;
-            if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) return false;
-            unsigned char *sa = smem + stage * STAGE_BYTES + row_off;
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-              const unsigned short *p = reinterpret_cast<const unsigned short *>(&b[half * 4 + c]);
-              int4 o[2];
-              __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(o);
-#pragma unroll
-              for (int i = 0; i < 8; ++i) {
-                const __half2_raw h = __nv_cvt_fp8x2_to_halfraw2(p[i], __NV_E4M3);
-                const float2 f = __half22float2(*reinterpret_cast<const __half2 *>(&h));
-                o2[i] = __floats2bfloat162_rn(f.x * scale, f.y * scale);
-              }
-              *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(2 * c) ^ sw) << 4)) = o[0];
-              *reinterpret_cast<int4 *>(sa + ((static_cast<uint32_t>(2 * c + 1) ^ sw) << 4)) = o[1];
-            }
-            sm100::fence_proxy_async_smem();
-            sm100::mbar_arrive(&sh.full[stage]);
-            if (++stage == STAGES) { stage = 0; phase ^= 1u; }
-          }
-          return true;
-        };
-        fetch(buf0, 0);
-        fetch(buf1, 1);
-        for (int line = 0; line < lines && ok; line += 2) {
-          ok = put(buf0, line);
-          if (!ok) break;
-          fetch(buf0, line + 2);
-          if (line + 1 < lines) {
-            ok = put(buf1, line + 1);
-            if (!ok) break;
-            fetch(buf1, line + 3);
-          }
         }
       }
       if (!ok || sh.abort_flag) break;

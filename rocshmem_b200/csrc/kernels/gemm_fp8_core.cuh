@@ -144,32 +144,31 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
       }
     }
   } else if (A_GATHER && warp >= 2 + ACC_WARPS) {
-    // ---- gather producer: a thread owns two tile rows and copies their 128 bytes of every K block into the stage
-    // with asynchronous 16-byte copies (no registers, so it runs as far ahead as the ring has free stages) ----------
-    const int g = (warp - 2 - ACC_WARPS) * 32 + lane;   // 0 .. 63
+    // ---- gather producers: asynchronous 16-byte copies straight into the stage, eight lanes per row (128 contiguous
+    // bytes), four rows per instruction, sixteen instructions per stage and warp (warp w serves rows [64 w, 64 w + 64)).
+    // No registers hold data, so the warps run as far ahead as the ring has free stages.
+    const int gw = warp - 2 - ACC_WARPS;
+    const uint32_t c = static_cast<uint32_t>(lane & 7);
     uint32_t stage = 0, phase = 0;
     gemm::Tile t;
     for (int iter = 0; sched.get(iter, t) && !sh.abort_flag; ++iter) {
-      const unsigned char *src[2];
-      bool live[2];
+      int rows[16];
 #pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        const int r = g + 64 * h;
-        live[h] = r < t.rows;
-        const long long src_row = live[h] ? gather->row_index[t.a_row + r] : 0;
-        src[h] = gather->base + static_cast<size_t>(src_row) * gather->row_bytes;
+      for (int j = 0; j < 16; ++j) {
+        const int r = gw * 64 + j * 4 + lane / 8;
+        rows[j] = r < t.rows ? gather->row_index[t.a_row + r] : -1;
       }
       bool ok = true;
       for (int kb = 0; kb < k_blocks; ++kb) {
         if (!sm100::mbar_wait(&sh.empty[stage], phase ^ 1u, &sh.abort_flag, WAIT_BUDGET_NS)) { ok = false; break; }
+        unsigned char *sa = smem + stage * STAGE_BYTES;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-          const int r = g + 64 * h;
-          unsigned char *sa = smem + stage * STAGE_BYTES + r * KB;
-          const uint32_t sw = static_cast<uint32_t>(r & 7);
-          const unsigned char *gp = src[h] + static_cast<size_t>(kb) * KB;
-#pragma unroll
-          for (uint32_t c = 0; c < 8; ++c) sm100::cp_async_16(sa + ((c ^ sw) << 4), gp + c * 16, live[h] ? 16u : 0u);
+        for (int j = 0; j < 16; ++j) {
+          const int r = gw * 64 + j * 4 + lane / 8;
+          const bool live = rows[j] >= 0;
+          const unsigned char *gp = gather->base + static_cast<size_t>(live ? rows[j] : 0) * gather->row_bytes +
+                                    static_cast<size_t>(kb) * KB + c * 16;
+          sm100::cp_async_16(sa + r * KB + ((c ^ static_cast<uint32_t>(r & 7)) << 4), gp, live ? 16u : 0u);
         }
         sm100::cp_async_arrive_noinc(&sh.full[stage]);
         if (++stage == STAGES) { stage = 0; phase ^= 1u; }

@@ -172,10 +172,9 @@ grouped_gemm_bf16_kernel(const __grid_constant__ CUtensorMap map_a, const __grid
   gemm::run<false, SWIGLU>(&map_a, &map_b, k * 2, sched, epi, smem_raw, sh);
 }
 
-// Grouped GEMM whose A rows are gathered by index from the buffers an expert-parallel dispatch filled (bf16 rows,
-// or e4m3 rows with 1 x 128 scales that are de-quantised on the way into shared memory): position p of the grouped
-// order reads source row row_index[p]. Replaces a separate gather / de-quantise pass over the activations.
-template <bool SWIGLU, int A_GATHER>
+// Grouped GEMM whose A rows are gathered by index from the bf16 rows an expert-parallel dispatch delivered: position
+// p of the grouped order reads source row row_index[p]. Replaces a separate gather pass over the activations.
+template <bool SWIGLU>
 __global__ void __launch_bounds__(gemm::GATHER_THREADS, 1)
 grouped_gemm_bf16_gather_kernel(const __grid_constant__ CUtensorMap map_b, gemm::GatherSrc src, __nv_bfloat16 *c,
                                 const int *offsets, int groups, int n, int k) {
@@ -190,7 +189,7 @@ grouped_gemm_bf16_gather_kernel(const __grid_constant__ CUtensorMap map_b, gemm:
   sched.n = n;
   sched.tiles_n = SWIGLU ? (n / 2 + gemm::BN / 2 - 1) / (gemm::BN / 2) : (n + gemm::BN - 1) / gemm::BN;
   RowMajorEpilogue epi{c, static_cast<size_t>(SWIGLU ? n / 2 : n)};
-  gemm::run<false, SWIGLU, A_GATHER>(&map_b, &map_b, k * 2, sched, epi, smem_raw, sh, &src);
+  gemm::run<false, SWIGLU, true>(&map_b, &map_b, k * 2, sched, epi, smem_raw, sh, &src);
 }
 
 // Rows of the grouped product are multiplied by a per-position weight and added to row row_index[p] of the
@@ -222,7 +221,7 @@ grouped_gemm_bf16_scatter_kernel(const __grid_constant__ CUtensorMap map_a, cons
   sched.n = n;
   sched.tiles_n = (n + gemm::BN - 1) / gemm::BN;
   ScatterAddEpilogue epi{y, static_cast<size_t>(n), row_index, weight};
-  gemm::run<false, false, 0, true>(&map_a, &map_b, k * 2, sched, epi, smem_raw, sh);
+  gemm::run<false, false, false, true>(&map_a, &map_b, k * 2, sched, epi, smem_raw, sh);
 }
 
 template <typename K>
@@ -308,16 +307,14 @@ int grouped_gemm_bf16(const void *a, const void *b, void *c, const int *offsets,
   return cudaGetLastError();
 }
 
-int grouped_gemm_bf16_gathered(const void *a_rows, int a_is_fp8, const float *a_scales, const int *row_index,
-                               const void *b, void *c, const int *offsets, int groups, int n, int k, int swiglu,
-                               void *stream) {
-  if (groups <= 0 || groups > kMaxGroups || n <= 0 || k <= 0 || (k % 128) != 0) return cudaErrorInvalidValue;
+int grouped_gemm_bf16_gathered(const void *a_rows, const int *row_index, const void *b, void *c, const int *offsets,
+                               int groups, int n, int k, int swiglu, void *stream) {
+  if (groups <= 0 || groups > kMaxGroups || n <= 0 || k <= 0 || (k % 64) != 0) return cudaErrorInvalidValue;
   if (swiglu && (n % 2) != 0) return cudaErrorInvalidValue;
-  if (a_rows == nullptr || row_index == nullptr || (a_is_fp8 && a_scales == nullptr)) return cudaErrorInvalidValue;
+  if (a_rows == nullptr || row_index == nullptr) return cudaErrorInvalidValue;
   CUtensorMap map_b;
   if (!encode_tmap_2d(&map_b, b, static_cast<uint64_t>(groups) * n, k, 2, gemm::BN / 2)) return -1;
-  gemm::GatherSrc src{row_index, static_cast<const unsigned char *>(a_rows),
-                      a_is_fp8 ? static_cast<size_t>(k) : static_cast<size_t>(k) * 2, a_scales, k / 128};
+  gemm::GatherSrc src{row_index, static_cast<const unsigned char *>(a_rows), static_cast<size_t>(k) * 2, nullptr, 0};
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = device_sm_count();
   auto launch = [&](auto kernel) -> int {
@@ -326,10 +323,7 @@ int grouped_gemm_bf16_gathered(const void *a_rows, int a_is_fp8, const float *a_
                                                                 groups, n, k);
     return cudaGetLastError();
   };
-  if (a_is_fp8) {
-    return swiglu ? launch(grouped_gemm_bf16_gather_kernel<true, 2>) : launch(grouped_gemm_bf16_gather_kernel<false, 2>);
-  }
-  return swiglu ? launch(grouped_gemm_bf16_gather_kernel<true, 1>) : launch(grouped_gemm_bf16_gather_kernel<false, 1>);
+  return swiglu ? launch(grouped_gemm_bf16_gather_kernel<true>) : launch(grouped_gemm_bf16_gather_kernel<false>);
 }
 
 int grouped_gemm_bf16_scatter_add(const void *a, const void *b, void *y, const int *offsets, const int *row_index,

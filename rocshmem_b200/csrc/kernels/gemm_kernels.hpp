@@ -31,13 +31,13 @@ int gemm_bf16_one_cta(const void *a, const void *b, void *c, int m, int n, int k
 int grouped_gemm_bf16(const void *a, const void *b, void *c, const int *offsets, int groups, int max_rows,
                       int n, int k, int swiglu, void *stream);
 
-// The grouped GEMM fed directly by the buffers of an expert-parallel dispatch: position p of the grouped order
-// (offsets as above) reads row row_index[p] of `a_rows`, which holds bf16 rows [*, K] or, with a_is_fp8 != 0, e4m3
-// rows [*, K] with one fp32 scale per 128 elements in `a_scales` [*, K / 128] (de-quantised to bf16 on the way
-// into shared memory). K must be a multiple of 128. Output as for grouped_gemm_bf16, in grouped order.
-int grouped_gemm_bf16_gathered(const void *a_rows, int a_is_fp8, const float *a_scales, const int *row_index,
-                               const void *b, void *c, const int *offsets, int groups, int n, int k, int swiglu,
-                               void *stream);
+// The grouped GEMM fed directly by the bf16 rows of an expert-parallel dispatch: position p of the grouped order
+// (offsets as above) reads row row_index[p] of `a_rows` [*, K] (copied into shared memory with cp.async by extra
+// producer warps). K must be a multiple of 64. Output as for grouped_gemm_bf16, in grouped order. (e4m3 rows are
+// gathered by the block-scaled kernel below; de-quantising them inside a bf16 kernel's producer warps was measured
+// slower than a separate gather pass.)
+int grouped_gemm_bf16_gathered(const void *a_rows, const int *row_index, const void *b, void *c, const int *offsets,
+                               int groups, int n, int k, int swiglu, void *stream);
 // The grouped GEMM whose result rows are scaled and summed where they belong: y[row_index[p], :] += weights[p] *
 // (A[p, :] * B[g]^T) for every position p of group g (weights == nullptr: 1). y [*, N] bf16 must hold zeros (or the
 // values to add to) beforehand; sums of several positions into one row are packed bf16 reductions in L2, so the

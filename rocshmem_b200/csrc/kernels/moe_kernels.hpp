@@ -10,15 +10,6 @@ namespace kernels {
 int moe_gather_rows(const void *recv_x, const float *recv_scales, int fp8, const int *offsets, int experts,
                     const int *row_index, int hidden, void *out_bf16, void *stream);
 
-// inverse[row * top_k + k] = pos for every expert-sorted position (entries of unused pairs are left alone).
-int moe_inverse_map(const int *offsets, int experts, const int *row_index, const int *pair_k, int top_k,
-                    int *inverse, void *stream);
-
-// y[row, :] = sum over the row's local experts of (weighted ? gate weight : 1) * pairs[inverse[row, k], :]
-// for every received row listed in recv_info.
-int moe_reduce_pairs(const void *pairs_bf16, const int *inverse, const int *recv_meta, const int *recv_info,
-                     int n_ranks, int top_k, int hidden, int weighted, void *y_bf16, void *stream);
-
 // Zeroes the rows of y [*, hidden] (bf16) that recv_info lists as received (the destination of a scatter-add
 // grouped GEMM must start from zero).
 int moe_zero_rows(const int *recv_info, int n_ranks, int hidden, void *y_bf16, void *stream);

@@ -4,15 +4,15 @@ One call runs, stream-ordered and without a host synchronisation, as four kernel
 side stream)::
 
     dispatch       fp8 1x128 rows over NVLink; its tail groups the received (row, k) pairs by local expert
-    gate/up GEMM   grouped tcgen05 GEMM whose producer warps gather the received rows by index (de-quantising
-                   e4m3 to bf16 on the way into shared memory), SwiGLU in the epilogue
-    down GEMM      grouped tcgen05 GEMM whose epilogue multiplies every row by its gate weight and adds it into
+    gate/up GEMM   grouped block-scaled e4m3 tcgen05 GEMM whose producer warps gather the received rows (and the
+                   accumulate warps their scales) by index; the epilogue applies SwiGLU and quantises the hidden
+                   activation to e4m3 1 x 128 for the next GEMM
+    down GEMM      grouped block-scaled GEMM whose epilogue multiplies every row by its gate weight and adds it into
                    the row's slot of the result buffer (the sum over a token's local experts)
     combine        pull over NVLink, sum over the ranks a token went to
 
-With ``fp8_experts`` both GEMMs are block-scaled e4m3: the received e4m3 rows and their scales are gathered as they
-are, and the first GEMM's epilogue quantises the hidden activation for the second. ``fused=False`` keeps the
-separate gather, quantise and per-row reduction kernels.
+With bf16 experts the GEMMs are the bf16 kernels (bf16 rows gathered inside the GEMM; e4m3 rows de-quantised into
+expert order by one extra kernel first).
 
 Experts are sharded over the team: rank r owns global experts ``[r * E_local, (r + 1) * E_local)``.
 The reference has no model code; its nearest building block is the fixed-size alltoall
@@ -41,6 +41,12 @@ def expert_weights(expert: int, hidden: int, inter: int, seed: int = 0, device="
 class MoEFeedForward:
     """``num_experts`` SwiGLU experts of shape hidden -> inter -> hidden, top-k routing done by the caller.
 
+    ``fp8_experts``: block-scaled e4m3 expert GEMMs (1 x 128 activation scales, 128 x 128 weight scales). ``None``
+    chooses them whenever the dispatch is quantised and the shapes allow (hidden % 512 == 0, inter % 512 == 0): the
+    received e4m3 rows then feed the tensor cores as they are. With bf16 experts behind a quantised dispatch one
+    extra kernel de-quantises the rows into expert order (doing that inside the GEMM's producer warps was measured
+    slower); with a bf16 dispatch the bf16 rows are gathered inside the GEMM.
+
     ``pair_capacity`` bounds the number of (row, expert) pairs this rank can process in one call; the
     default is the worst case ``n_ranks * max_tokens * top_k``. With balanced routing the expected number
     is ``max_tokens * top_k``, and a tighter bound saves memory; exceeding it is the caller's error.
@@ -48,47 +54,39 @@ class MoEFeedForward:
 
     def __init__(self, num_experts: int, top_k: int, hidden: int, inter: int, max_tokens: int,
                  team: Optional[rt.Team] = None, quantize: bool = True, layout: str = "compact", seed: int = 0,
-                 pair_capacity: Optional[int] = None, fp8_experts: bool = False, fused: Optional[bool] = None,
-                 low_latency: bool = False):
+                 pair_capacity: Optional[int] = None, fp8_experts: Optional[bool] = None, low_latency: bool = False):
         if rt.n_local_pes() != 1:
             raise RuntimeError("MoEFeedForward needs one PE per process")
-        self.fused = (hidden % 128 == 0) if fused is None else bool(fused)
-        if self.fused and hidden % 128:
-            raise ValueError("the fused path needs hidden % 128 == 0")
+        if hidden % 64 or inter % 64:
+            raise ValueError("hidden and inter must be multiples of 64")
+        fits_fp8 = quantize and hidden % 512 == 0 and inter % 512 == 0
+        if fp8_experts and not fits_fp8:
+            raise ValueError("fp8 experts need an fp8 dispatch, hidden % 512 == 0 and inter % 512 == 0")
+        self.fp8_experts = fits_fp8 if fp8_experts is None else bool(fp8_experts)
         self.d = moe.EpDispatcher(num_experts, top_k, hidden, max_tokens, team=team, quantize=quantize, layout=layout,
-                                  expert_layout=self.fused, low_latency=low_latency)
+                                  expert_layout=True, low_latency=low_latency)
         self.hidden, self.inter, self.top_k = hidden, inter, top_k
         self.n_ranks, self.e_local = self.d.n_ranks, self.d.experts_per_rank
         dev = rt.device()
         first = self.d.team.my_pe() * self.e_local
         ws = [expert_weights(first + e, hidden, inter, seed) for e in range(self.e_local)]
-        self.w13 = torch.stack([w[0] for w in ws]).to(dev).contiguous()   # [E_local, 2 * inter, hidden]
-        self.w2 = torch.stack([w[1] for w in ws]).to(dev).contiguous()    # [E_local, hidden, inter]
+        w13 = torch.stack([w[0] for w in ws]).to(dev).contiguous()   # [E_local, 2 * inter, hidden]
+        w2 = torch.stack([w[1] for w in ws]).to(dev).contiguous()    # [E_local, hidden, inter]
         cap = pair_capacity or self.n_ranks * max_tokens * top_k
         self.pair_capacity = cap
-        bf = dict(dtype=torch.bfloat16, device=dev)
-        self.h = torch.zeros((cap, inter), **bf)        # silu(gate) * up
-        if self.fused:
-            self.side = torch.cuda.Stream()
-            self.ev_dispatched, self.ev_zeroed = torch.cuda.Event(), torch.cuda.Event()
-        else:
-            self.xs = torch.zeros((cap, hidden), **bf)      # rows in expert order
-            self.yp = torch.zeros((cap, hidden), **bf)      # expert outputs per pair
-            self.inverse = torch.zeros(self.n_ranks * max_tokens * top_k, dtype=torch.int32, device=dev)
+        self.side = torch.cuda.Stream()
+        self.ev_dispatched, self.ev_zeroed = torch.cuda.Event(), torch.cuda.Event()
         self.kernel_launches = 0
-        # Block-scaled e4m3 experts: the received e4m3 rows feed the first grouped GEMM as they are (no
-        # de-quantisation), the hidden activation is re-quantised for the second one.
-        self.fp8_experts = bool(fp8_experts)
         if self.fp8_experts:
-            if not quantize or hidden % 1024 or inter % 512:
-                raise ValueError("fp8 experts need an fp8 dispatch, hidden % 1024 == 0 and inter % 512 == 0")
-            self.w13_q, self.w13_s = gemm.quantize_weight_128x128(self.w13)
-            self.w2_q, self.w2_s = gemm.quantize_weight_128x128(self.w2)
-            if not self.fused:
-                self.xs_q = torch.zeros((cap, hidden), dtype=torch.uint8, device=dev)
-                self.xs_s = torch.zeros((cap, hidden // 128), dtype=torch.float32, device=dev)
+            self.w13_q, self.w13_s = gemm.quantize_weight_128x128(w13)
+            self.w2_q, self.w2_s = gemm.quantize_weight_128x128(w2)
             self.h_q = torch.zeros((cap, inter), dtype=torch.uint8, device=dev)
             self.h_s = torch.zeros((cap, inter // 128), dtype=torch.float32, device=dev)
+        else:
+            self.w13, self.w2 = w13, w2
+            self.h = torch.zeros((cap, inter), dtype=torch.bfloat16, device=dev)        # silu(gate) * up
+            if quantize:
+                self.xs = torch.zeros((cap, hidden), dtype=torch.bfloat16, device=dev)  # de-quantised rows, expert order
 
     def destroy(self) -> None:
         """Collective: free the dispatcher's symmetric buffers (the weights and work buffers are ordinary tensors)."""
@@ -105,87 +103,54 @@ class MoEFeedForward:
         C = rt._C()
         d = self.d
         s = moe._stream(stream)
+        cur = torch.cuda.ExternalStream(stream) if isinstance(stream, int) else (stream or torch.cuda.current_stream())
         before = d.kernel_launches
         marks = []
 
         def mark(name):
             if stage_us is not None:
                 ev = torch.cuda.Event(enable_timing=True)
-                ev.record()
+                ev.record(cur)
                 marks.append((name, ev))
 
         mark("start")
         d.dispatch(x, topk_idx, topk_weights, stream=stream)
         mark("dispatch")
-        if self.fused:
-            cur = torch.cuda.ExternalStream(stream) if isinstance(stream, int) else (stream or torch.cuda.current_stream())
-            offsets, lay_row, _, lay_w = d.expert_pairs()
-            y = d.result_buffer()
-            # The result rows start from zero; clearing them runs beside the first GEMM.
-            self.ev_dispatched.record(cur)
-            self.side.wait_event(self.ev_dispatched)
-            C.moe_zero_rows(d.recv_info.data_ptr(), self.n_ranks, self.hidden, y.data_ptr(), self.side.cuda_stream)
-            self.ev_zeroed.record(self.side)
-            if self.fp8_experts:
-                # Received e4m3 rows and their scales feed the first GEMM as they are; its epilogue quantises the
-                # hidden activation for the second one.
-                gemm.grouped_gemm_fp8_swiglu_quant(d.recv_x, d.recv_scales, self.w13_q, self.w13_s, offsets, self.h_q,
-                                                   self.h_s, row_index=lay_row, stream=stream)
-                mark("gemm_gate_up")
-                cur.wait_event(self.ev_zeroed)
-                gemm.grouped_gemm_fp8_scatter_add(self.h_q, self.h_s, self.w2_q, self.w2_s, offsets, lay_row, y,
-                                                  weights=lay_w, stream=stream)
-            else:
-                gemm.grouped_gemm_bf16_gathered(d.recv_x, lay_row, self.w13, offsets,
-                                                a_scales=d.recv_scales if d.quantize else None, swiglu=True,
-                                                out=self.h, stream=stream)
-                mark("gemm_gate_up")
-                cur.wait_event(self.ev_zeroed)
-                gemm.grouped_gemm_bf16_scatter_add(self.h, self.w2, offsets, lay_row, y, weights=lay_w, stream=stream)
-            mark("gemm_down")
-            out = d.combine(y, topk_idx, topk_weights, x.shape[0], weighted=False, out=out, stream=stream)
-            mark("combine")
-            self.kernel_launches += (d.kernel_launches - before) + 3
-            if stage_us is not None:
-                torch.cuda.synchronize()
-                for (_, a), (name, b) in zip(marks[:-1], marks[1:]):
-                    stage_us[name] = a.elapsed_time(b) * 1e3
-            return out
-        offsets, row_index, pair_k = d.expert_layout(stream=stream)
-        C.moe_inverse_map(offsets.data_ptr(), self.e_local, row_index.data_ptr(), pair_k.data_ptr(), self.top_k,
-                          self.inverse.data_ptr(), s)
-        mark("layout")
-        if self.fp8_experts:
-            # Rows and their scales are copied as raw bytes (the gather kernel's 2-byte element view).
-            C.moe_gather_rows(d.recv_x.data_ptr(), 0, 0, offsets.data_ptr(), self.e_local, row_index.data_ptr(),
-                              self.hidden // 2, self.xs_q.data_ptr(), s)
-            C.moe_gather_rows(d.recv_scales.data_ptr(), 0, 0, offsets.data_ptr(), self.e_local,
-                              row_index.data_ptr(), self.hidden // 128 * 2, self.xs_s.data_ptr(), s)
-            mark("gather")
-            gemm.grouped_gemm_fp8_blockscaled(self.xs_q, self.xs_s, self.w13_q, self.w13_s, offsets, swiglu=True,
-                                              out=self.h, stream=stream)
-            mark("gemm_gate_up")
-            gemm.quantize_1x128_into(self.h, self.h_q, self.h_s, stream)
-            mark("quantize_hidden")
-            gemm.grouped_gemm_fp8_blockscaled(self.h_q, self.h_s, self.w2_q, self.w2_s, offsets, out=self.yp,
-                                              stream=stream)
-            mark("gemm_down")
-            self.kernel_launches += 2
-        else:
-            C.moe_gather_rows(d.recv_x.data_ptr(), d.recv_scales.data_ptr(), int(d.quantize), offsets.data_ptr(),
-                              self.e_local, row_index.data_ptr(), self.hidden, self.xs.data_ptr(), s)
-            mark("gather")
-            gemm.grouped_gemm_bf16(self.xs, self.w13, offsets, swiglu=True, out=self.h, stream=stream)
-            mark("gemm_gate_up")
-            gemm.grouped_gemm_bf16(self.h, self.w2, offsets, out=self.yp, stream=stream)
-            mark("gemm_down")
+        offsets, lay_row, _, lay_w = d.expert_pairs()
         y = d.result_buffer()
-        C.moe_reduce_pairs(self.yp.data_ptr(), self.inverse.data_ptr(), d.recv_meta.data_ptr(),
-                           d.recv_info.data_ptr(), self.n_ranks, self.top_k, self.hidden, 1, y.data_ptr(), s)
-        mark("reduce_pairs")
+        # The down projection adds into the result rows, which therefore start from zero; clearing them runs on a
+        # side stream beside the first GEMM.
+        self.ev_dispatched.record(cur)
+        self.side.wait_event(self.ev_dispatched)
+        C.moe_zero_rows(d.recv_info.data_ptr(), self.n_ranks, self.hidden, y.data_ptr(), self.side.cuda_stream)
+        self.ev_zeroed.record(self.side)
+        launches = 3
+        if self.fp8_experts:
+            # Received e4m3 rows and their scales feed the first GEMM as they are (gathered by its producer warps);
+            # its epilogue quantises the hidden activation for the second one.
+            gemm.grouped_gemm_fp8_swiglu_quant(d.recv_x, d.recv_scales, self.w13_q, self.w13_s, offsets, self.h_q,
+                                               self.h_s, row_index=lay_row, stream=stream)
+            mark("gemm_gate_up")
+            cur.wait_event(self.ev_zeroed)
+            gemm.grouped_gemm_fp8_scatter_add(self.h_q, self.h_s, self.w2_q, self.w2_s, offsets, lay_row, y,
+                                              weights=lay_w, stream=stream)
+        else:
+            if d.quantize:
+                C.moe_gather_rows(d.recv_x.data_ptr(), d.recv_scales.data_ptr(), 1, offsets.data_ptr(), self.e_local,
+                                  lay_row.data_ptr(), self.hidden, self.xs.data_ptr(), s)
+                mark("gather")
+                gemm.grouped_gemm_bf16(self.xs, self.w13, offsets, swiglu=True, out=self.h, stream=stream)
+                launches += 1
+            else:
+                gemm.grouped_gemm_bf16_gathered(d.recv_x, lay_row, self.w13, offsets, swiglu=True, out=self.h,
+                                                stream=stream)
+            mark("gemm_gate_up")
+            cur.wait_event(self.ev_zeroed)
+            gemm.grouped_gemm_bf16_scatter_add(self.h, self.w2, offsets, lay_row, y, weights=lay_w, stream=stream)
+        mark("gemm_down")
         out = d.combine(y, topk_idx, topk_weights, x.shape[0], weighted=False, out=out, stream=stream)
         mark("combine")
-        self.kernel_launches += (d.kernel_launches - before) + 5
+        self.kernel_launches += (d.kernel_launches - before) + launches
         if stage_us is not None:
             torch.cuda.synchronize()
             for (_, a), (name, b) in zip(marks[:-1], marks[1:]):

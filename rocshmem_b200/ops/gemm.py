@@ -73,30 +73,21 @@ def grouped_gemm_bf16(a: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor, s
 
 
 def grouped_gemm_bf16_gathered(a_rows: torch.Tensor, row_index: torch.Tensor, b: torch.Tensor, offsets: torch.Tensor,
-                               a_scales: Optional[torch.Tensor] = None, swiglu: bool = False,
-                               out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
+                               swiglu: bool = False, out: Optional[torch.Tensor] = None, stream=None) -> torch.Tensor:
     """:func:`grouped_gemm_bf16` whose A rows are gathered inside the kernel: position ``p`` of the grouped order
-    reads row ``row_index[p]`` of ``a_rows``. ``a_rows`` is bf16 ``[*, K]``, or e4m3 / uint8 ``[*, K]`` with
-    ``a_scales [*, K / 128]`` (one fp32 scale per 128 elements), de-quantised to bf16 on the way into shared
-    memory. ``out`` must hold at least ``offsets[-1]`` rows (its row count bounds nothing on the device)."""
+    reads row ``row_index[p]`` of ``a_rows [*, K]`` (bf16). ``out`` must hold at least ``offsets[-1]`` rows (its row
+    count bounds nothing on the device)."""
+    _check(a_rows, "a_rows")
     _check(b, "b")
-    fp8 = a_rows.dtype in (torch.uint8, torch.float8_e4m3fn)
-    if not fp8:
-        _check(a_rows, "a_rows")
-    elif a_scales is None or a_scales.dtype != torch.float32 or not a_scales.is_contiguous():
-        raise ValueError("grouped_gemm_bf16_gathered: e4m3 rows need contiguous fp32 scales")
     K = a_rows.shape[1]
     G, N, K2 = b.shape
-    if K != K2 or K % 128 or offsets.dtype != torch.int32 or offsets.numel() != G + 1 or row_index.dtype != torch.int32:
-        raise ValueError("grouped_gemm_bf16_gathered: shape mismatch (K must be a multiple of 128)")
-    if fp8 and tuple(a_scales.shape) != (a_rows.shape[0], K // 128):
-        raise ValueError("grouped_gemm_bf16_gathered: a_scales must be [rows, K / 128]")
+    if K != K2 or K % 64 or offsets.dtype != torch.int32 or offsets.numel() != G + 1 or row_index.dtype != torch.int32:
+        raise ValueError("grouped_gemm_bf16_gathered: shape mismatch (K must be a multiple of 64)")
     width = N // 2 if swiglu else N
     if out is None:
         out = torch.empty((row_index.numel(), width), dtype=torch.bfloat16, device=a_rows.device)
-    rt._C().grouped_gemm_bf16_gathered(a_rows.data_ptr(), int(fp8), a_scales.data_ptr() if fp8 else 0,
-                                       row_index.data_ptr(), b.data_ptr(), out.data_ptr(), offsets.data_ptr(), G, N, K,
-                                       int(swiglu), _stream(stream))
+    rt._C().grouped_gemm_bf16_gathered(a_rows.data_ptr(), row_index.data_ptr(), b.data_ptr(), out.data_ptr(),
+                                       offsets.data_ptr(), G, N, K, int(swiglu), _stream(stream))
     return out
 
 

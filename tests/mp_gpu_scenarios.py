@@ -334,23 +334,26 @@ def gpu_models():
         err = (out.float().cpu() - want8).abs().max().item()
         assert err <= 5e-2 * want8.abs().max().item() + 0.05, ("tp_mlp_fp8", rep, err)
         shm.barrier_all()
-    # -- MoE feed-forward
+    # -- MoE feed-forward: bf16 experts, block-scaled e4m3 experts (the default here), and the low-latency kernels
     E, K, H, I, T = 8 * n, 4, 1024, 512, 160 + 8 * me
-    layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=256, seed=5)
-    for rep in range(2):
-        g = torch.Generator().manual_seed(77 * rep + me)
-        x = torch.randn(T, H, generator=g).to(torch.bfloat16)
-        idx, w = moe.make_routing(T, E, K, 1000 * rep + me)
-        if rep == 1:
-            idx[::9, -1] = -1
-        before = gemm.gemm_error_count()
-        out = layer(x.to(dev), idx.to(dev), w.to(dev))
-        _ok()
-        assert gemm.gemm_error_count() == before
-        want = moe_ffn.reference_forward(x, idx, w, H, I, seed=5)
-        err = (out.float().cpu() - want).abs().max().item()
-        assert err <= 3e-2 * want.abs().max().item() + 0.02, ("moe_ffn", rep, err, want.abs().max().item())
-        shm.barrier_all()
+    for kw, tol in ((dict(fp8_experts=False), (3e-2, 0.02)), (dict(), (5e-2, 0.03)),
+                    (dict(low_latency=True, layout="slotted"), (5e-2, 0.03))):
+        layer = moe_ffn.MoEFeedForward(E, K, H, I, max_tokens=256, seed=5, **kw)
+        for rep in range(2):
+            g = torch.Generator().manual_seed(77 * rep + me)
+            x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+            idx, w = moe.make_routing(T, E, K, 1000 * rep + me)
+            if rep == 1:
+                idx[::9, -1] = -1
+            before = gemm.gemm_error_count()
+            out = layer(x.to(dev), idx.to(dev), w.to(dev))
+            _ok()
+            assert gemm.gemm_error_count() == before
+            want = moe_ffn.reference_forward(x, idx, w, H, I, seed=5, fp8_experts=layer.fp8_experts)
+            err = (out.float().cpu() - want).abs().max().item()
+            assert err <= tol[0] * want.abs().max().item() + tol[1], ("moe_ffn", kw, rep, err, want.abs().max().item())
+            shm.barrier_all()
+        layer.destroy()
     shm.finalize()
 
 

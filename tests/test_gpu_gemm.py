@@ -179,12 +179,11 @@ def test_gemm_bf16_kernel_variants(m, n, k, two_cta):
     assert ok, f"max abs error {err}"
 
 
-@pytest.mark.parametrize("fp8_rows", [False, True])
 @pytest.mark.parametrize("swiglu", [False, True])
-def test_grouped_gemm_with_gathered_rows(fp8_rows, swiglu):
-    """A rows picked by index inside the kernel (bf16 rows, or e4m3 rows de-quantised by the producer warps)
-    against an fp32 matmul of the same rows gathered by PyTorch."""
-    from rocshmem_b200.ops import gemm, moe
+def test_grouped_gemm_with_gathered_rows(swiglu):
+    """A rows picked by index inside the kernel (cp.async producer warps) against an fp32 matmul of the same rows
+    gathered by PyTorch."""
+    from rocshmem_b200.ops import gemm
     G, n, k, src_rows = 4, 512, 1024, 700
     sizes = [150, 0, 333, 129]
     total = sum(sizes)
@@ -193,27 +192,69 @@ def test_grouped_gemm_with_gathered_rows(fp8_rows, swiglu):
     b = (torch.randn(G, n, k, generator=g, device="cuda") * 0.3).to(torch.bfloat16)
     row_index = torch.randint(0, src_rows, (total + 40,), generator=g, device="cuda", dtype=torch.int32)
     offsets = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
-    if fp8_rows:
-        q, sc = moe.fp8_quantize_1x128(src)
-        a_ref = moe.ref_dequantize_1x128(q, sc).to(torch.bfloat16).float()
-        rows_arg, scales = q, sc
-    else:
-        a_ref, rows_arg, scales = src.float(), src, None
     width = n // 2 if swiglu else n
     out = torch.full((total + 40, width), 7.0, dtype=torch.bfloat16, device="cuda")
     before = gemm.gemm_error_count()
-    gemm.grouped_gemm_bf16_gathered(rows_arg, row_index, b, offsets, a_scales=scales, swiglu=swiglu, out=out)
+    gemm.grouped_gemm_bf16_gathered(src, row_index, b, offsets, swiglu=swiglu, out=out)
     torch.cuda.synchronize()
     assert gemm.gemm_error_count() == before
     lo = 0
     for gi, sz in enumerate(sizes):
         if sz:
-            hc = a_ref[row_index[lo:lo + sz].long()] @ b[gi].float().t()
+            hc = src.float()[row_index[lo:lo + sz].long()] @ b[gi].float().t()
             want = torch.nn.functional.silu(hc[:, :n // 2]) * hc[:, n // 2:] if swiglu else hc
             ok, err = close(out[lo:lo + sz], want, k)
             assert ok, (gi, err)
         lo += sz
     assert torch.all(out[lo:] == 7.0), "rows past offsets[-1] were written"
+
+
+def test_block_scaled_moe_gemms_against_fp32():
+    """The two block-scaled MoE GEMMs: gate/up with rows and scales gathered by index, SwiGLU and a quantising
+    epilogue; down projection with the scatter-add epilogue."""
+    from rocshmem_b200.ops import gemm, moe
+    G, H, I, src_rows, dst_rows = 4, 1024, 512, 600, 600
+    sizes = [140, 0, 260, 129]
+    total = sum(sizes)
+    g = torch.Generator(device="cuda").manual_seed(29)
+    x = (torch.randn(src_rows, H, generator=g, device="cuda") * 0.7).to(torch.bfloat16)
+    w13 = (torch.randn(G, 2 * I, H, generator=g, device="cuda") * H ** -0.5).to(torch.bfloat16)
+    w2 = (torch.randn(G, H, I, generator=g, device="cuda") * I ** -0.5).to(torch.bfloat16)
+    row_index = torch.randint(0, src_rows, (total,), generator=g, device="cuda", dtype=torch.int32)
+    weights = torch.rand(total, generator=g, device="cuda")
+    offsets = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32, device="cuda")
+    xq, xs = moe.fp8_quantize_1x128(x)
+    w13q, w13s = gemm.quantize_weight_128x128(w13)
+    w2q, w2s = gemm.quantize_weight_128x128(w2)
+    hq = torch.zeros(total + 8, I, dtype=torch.uint8, device="cuda")
+    hs = torch.zeros(total + 8, I // 128, dtype=torch.float32, device="cuda")
+    before = gemm.gemm_error_count()
+    gemm.grouped_gemm_fp8_swiglu_quant(xq.view(torch.uint8), xs, w13q, w13s, offsets, hq, hs, row_index=row_index)
+    torch.cuda.synchronize()
+    assert gemm.gemm_error_count() == before
+    x_ref = moe.ref_dequantize_1x128(xq, xs)
+    w13_ref, w2_ref = gemm.dequantize_weight_128x128(w13q, w13s), gemm.dequantize_weight_128x128(w2q, w2s)
+    h_got = moe.ref_dequantize_1x128(hq[:total].view(torch.float8_e4m3fn), hs[:total])
+    lo = 0
+    h_ref = torch.zeros(total, I, device="cuda")
+    for gi, sz in enumerate(sizes):
+        hc = x_ref[row_index[lo:lo + sz].long()] @ w13_ref[gi].t()
+        h_ref[lo:lo + sz] = torch.nn.functional.silu(hc[:, :I]) * hc[:, I:]
+        lo += sz
+    # one e4m3 rounding step (2^-4 relative at the top of a block's range) on top of the GEMM's own error
+    assert (h_got - h_ref).abs().max().item() <= 0.07 * h_ref.abs().max().item() + 1e-3
+    assert torch.all(hq[total:] == 0), "rows past offsets[-1] were written"
+    y = torch.zeros(dst_rows, H, dtype=torch.bfloat16, device="cuda")
+    gemm.grouped_gemm_fp8_scatter_add(hq, hs, w2q, w2s, offsets, row_index, y, weights=weights)
+    torch.cuda.synchronize()
+    assert gemm.gemm_error_count() == before
+    want = torch.zeros(dst_rows, H, device="cuda")
+    lo = 0
+    for gi, sz in enumerate(sizes):
+        prod = (h_got[lo:lo + sz] @ w2_ref[gi].t()) * weights[lo:lo + sz].unsqueeze(1)
+        want.index_add_(0, row_index[lo:lo + sz].long(), prod)
+        lo += sz
+    assert (y.float() - want).abs().max().item() <= 2e-2 * want.abs().max().item() + 0.05
 
 
 @pytest.mark.parametrize("weighted", [False, True])
