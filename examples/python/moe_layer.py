@@ -26,9 +26,9 @@ def main() -> int:
     idx, w = moe.make_routing(tokens, experts, top_k, seed=10 + me)
     out = layer(x.cuda(), idx.cuda(), w.cuda())
     torch.cuda.synchronize()
-    want = moe_ffn.reference_forward(x, idx, w, hidden, inter, seed=1)
+    want = moe_ffn.reference_forward(x, idx, w, hidden, inter, seed=1, fp8_experts=layer.fp8_experts)
     err = (out.float().cpu() - want).abs().max().item()
-    ok = err <= 3e-2 * want.abs().max().item() + 0.02 and shm.get_error()["count"] == 0
+    ok = err <= 5e-2 * want.abs().max().item() + 0.03 and shm.get_error()["count"] == 0
     print(f"[PE {me}] moe layer: max abs error {err:.4f}: {'PASS' if ok else 'FAIL'}")
     shm.barrier_all()
     shm.finalize()

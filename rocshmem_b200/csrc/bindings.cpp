@@ -324,6 +324,10 @@ PYBIND11_MODULE(_C, m) {
     HostTeam *ht = live().team_from_handle(team_of(t));
     return ht ? ht->slot : -1;
   });
+  m.def("team_has_nvls", [](uintptr_t t) {
+    HostTeam *ht = live().team_from_handle(team_of(t));
+    return ht != nullptr && ht->mc_window != nullptr;
+  });
   m.def("proxy_inject_drop", [](uintptr_t p, int n) { ptr_of<Proxy>(p)->inject_drop(n); });
   m.def("proxy_inject_delay_ms", [](uintptr_t p, int ms) { ptr_of<Proxy>(p)->inject_delay_ms(ms); });
   m.def("proxy_counts", [](uintptr_t p) {
@@ -395,6 +399,7 @@ PYBIND11_MODULE(_C, m) {
     d["proxy_coalesce"] = c.proxy_coalesce;
     d["proxy_collectives"] = c.proxy_collectives;
     d["enable_nvls"] = c.enable_nvls;
+    d["team_nvls"] = c.team_nvls;
     d["backend"] = c.backend;
     d["bootstrap_dir"] = c.bootstrap_dir;
     return d;

@@ -141,6 +141,8 @@ struct rocshmem_team_dev {
   unsigned long long barrier_epoch;
   // Calls of the flag-in-word small allreduce on this team so far (its words carry the call's number).
   unsigned long long ll_epoch;
+  // NVLink multicast mapping of the heap that spans exactly this team's members (nullptr: none).
+  char *mc_base;
 };
 
 // Context descriptor (device pool entry).

@@ -237,14 +237,15 @@ __device__ __forceinline__ void multimem_st(void *mc, int4 v) {
                ::"l"(mc), "r"(v.x), "r"(v.y), "r"(v.z), "r"(v.w) : "memory");
 }
 
-// World team only: the multicast object spans every PE. Requires 16-byte aligned buffers and a
-// multiple of 16 bytes per slice; the launcher falls back to TWO_SHOT otherwise.
+// Teams with a multicast mapping (the world team, and split teams of one PE per process that got an object of
+// their own): the switch adds the members' copies. Requires 16-byte aligned buffers and a multiple of 16 bytes
+// per slice; the launcher falls back to TWO_SHOT otherwise.
 template <typename T>
 __global__ void __launch_bounds__(kThreads)
 allreduce_nvls_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg, size_t nelems) {
   const rocshmem_device_state &s = st();
   const rocshmem_team_dev *t = detail::team_of(team);
-  if (t->my_pe < 0 || s.mc_base == nullptr) return;
+  if (t->my_pe < 0 || t->mc_base == nullptr) return;
   constexpr size_t VEC = 16 / sizeof(T);
   const size_t n = static_cast<size_t>(t->size);
   const size_t nvec_total = nelems / VEC;  // the launcher guarantees nelems % VEC == 0
@@ -252,8 +253,8 @@ allreduce_nvls_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg, si
   size_t lo = per * static_cast<size_t>(t->my_pe), hi = lo + per;
   if (lo > nvec_total) lo = nvec_total;
   if (hi > nvec_total) hi = nvec_total;
-  const char *src_mc = s.mc_base + (reinterpret_cast<const char *>(detail::local_ptr(const_cast<T *>(source_arg))) - s.heap_base);
-  char *dst_mc = s.mc_base + (reinterpret_cast<char *>(detail::local_ptr(dest_arg)) - s.heap_base);
+  const char *src_mc = t->mc_base + (reinterpret_cast<const char *>(detail::local_ptr(const_cast<T *>(source_arg))) - s.heap_base);
+  char *dst_mc = t->mc_base + (reinterpret_cast<char *>(detail::local_ptr(dest_arg)) - s.heap_base);
   if (!block_pair_barrier(t, blockIdx.x)) return;
   const size_t tid = size_t(blockIdx.x) * blockDim.x + threadIdx.x, nthr = size_t(gridDim.x) * blockDim.x;
   size_t v = lo + tid;
@@ -341,18 +342,18 @@ allreduce_ll_kernel(rocshmem_team_t team, T *dest_arg, const T *source_arg, size
   }
 }
 
-// All-gather through the NVLink multicast mapping (world team, one PE per process): every 16-byte vector of my
+// All-gather through the team's NVLink multicast mapping (one PE per process): every 16-byte vector of my
 // block is stored once to the multicast address of dest[my_pe * bytes] and the switch delivers it to every member,
 // myself included. A member puts `bytes` on its links instead of (n - 1) x bytes.
 __global__ void __launch_bounds__(kThreads)
 fcollect_nvls_kernel(rocshmem_team_t team, char *dest_arg, const char *source_arg, size_t bytes, int pre_sync) {
   const rocshmem_device_state &s = st();
   const rocshmem_team_dev *t = detail::team_of(team);
-  if (t->my_pe < 0 || s.mc_base == nullptr) return;
+  if (t->my_pe < 0 || t->mc_base == nullptr) return;
   char *dest = detail::local_ptr(dest_arg);
   const int4 *src = reinterpret_cast<const int4 *>(detail::local_ptr(const_cast<char *>(source_arg)));
   if (pre_sync && !block_pair_barrier(t, blockIdx.x)) return;
-  char *dst_mc = s.mc_base + (dest - s.heap_base) + size_t(t->my_pe) * bytes;
+  char *dst_mc = t->mc_base + (dest - s.heap_base) + size_t(t->my_pe) * bytes;
   const size_t nvec = bytes / 16, per = (nvec + gridDim.x - 1) / gridDim.x;
   size_t lo = per * blockIdx.x, hi = lo + per;
   if (lo > nvec) lo = nvec;
@@ -473,13 +474,13 @@ broadcast_nvls_kernel(rocshmem_team_t team, char *dest_arg, const char *source_a
                       size_t sub_bytes, int pre_sync) {
   const rocshmem_device_state &s = st();
   const rocshmem_team_dev *t = detail::team_of(team);
-  if (t->my_pe < 0 || s.mc_base == nullptr) return;
+  if (t->my_pe < 0 || t->mc_base == nullptr) return;
   char *dest = detail::local_ptr(dest_arg);
   const char *source = detail::local_ptr(const_cast<char *>(source_arg));
   if (pre_sync && !block_pair_barrier(t, blockIdx.x)) return;
   const bool is_root = t->my_pe == root;
   char *stage = s.scratch;
-  char *stage_mc = s.mc_base + (s.scratch - s.heap_base);  // the same bytes on every member
+  char *stage_mc = t->mc_base + (s.scratch - s.heap_base);  // the same bytes on every member
   int half = 0;
   for (size_t base = 0; base < bytes; base += sub_bytes, half ^= 1) {
     const size_t len = bytes - base < sub_bytes ? bytes - base : sub_bytes;  // a multiple of 16 (launcher)
@@ -525,7 +526,7 @@ broadcast_nvls_kernel(rocshmem_team_t team, char *dest_arg, const char *source_a
   block_pair_barrier(t, blockIdx.x, false);
 }
 
-// ROCSHMEM_BCAST_NVLS=1 lets large broadcasts on the world team use the multicast kernel where the mapping exists.
+// ROCSHMEM_BCAST_NVLS=1 lets large broadcasts use the multicast kernel on teams that have a mapping.
 bool use_bcast_nvls() {
   static const bool on = [] {
     const char *e = std::getenv("ROCSHMEM_BCAST_NVLS");
@@ -559,7 +560,7 @@ int launch_allreduce_typed(rocshmem_team_t team, void *dest, const void *source,
   HostTeam *ht = rt.team_from_handle(team);
   const int n = ht ? ht->world.size : rt.n_pes();
   if (algo == ALLREDUCE_AUTO) {
-    const bool nvls_ok = rt.mc_base() != nullptr && ht == rt.team_world() && op == ROCSHMEM_SUM &&
+    const bool nvls_ok = ht != nullptr && ht->mc_window != nullptr && op == ROCSHMEM_SUM &&
                          (std::is_same<T, float>::value || std::is_same<T, __half>::value ||
                           std::is_same<T, __nv_bfloat16>::value);
     const bool ll_ok = (sizeof(T) == 2 || sizeof(T) == 4) && bytes % 4 == 0 && bytes <= size_t(ROCSHMEM_LL_WORDS) * 4 &&
@@ -588,7 +589,7 @@ int launch_allreduce_typed(rocshmem_team_t team, void *dest, const void *source,
                                std::is_same<T, __nv_bfloat16>::value;
     const bool aligned = ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 15u) == 0 &&
                          bytes % 16 == 0;
-    if (!supported || rt.mc_base() == nullptr || ht != rt.team_world() || op != ROCSHMEM_SUM || !aligned) {
+    if (!supported || ht == nullptr || ht->mc_window == nullptr || op != ROCSHMEM_SUM || !aligned) {
       algo = ALLREDUCE_TWO_SHOT;
     }
   }
@@ -706,7 +707,7 @@ int coll_broadcast(rocshmem_team_t team, void *dest, const void *source, size_t 
   Runtime &rt = Runtime::instance();
   HostTeam *ht = rt.team_from_handle(team);
   const int n = ht ? ht->world.size : 0;
-  if (use_bcast_nvls() && ht != nullptr && ht == rt.team_world() && rt.n_local() == 1 && rt.mc_base() != nullptr &&
+  if (use_bcast_nvls() && ht != nullptr && rt.n_local() == 1 && ht->mc_window != nullptr &&
       n >= 2 && bytes >= (size_t(1) << 20) && bytes % 16 == 0 && reinterpret_cast<uintptr_t>(dest) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(source) % 16 == 0) {
     // Two staging halves of one sub-chunk each; sub-chunks as for the relay (a transfer that dwarfs its barrier).
@@ -740,7 +741,7 @@ int coll_fcollect(rocshmem_team_t team, void *dest, const void *source, size_t b
                   int flags) {
   Runtime &rt = Runtime::instance();
   HostTeam *ht = rt.team_from_handle(team);
-  if (use_fcollect_nvls() && ht != nullptr && ht == rt.team_world() && rt.n_local() == 1 && rt.mc_base() != nullptr &&
+  if (use_fcollect_nvls() && ht != nullptr && rt.n_local() == 1 && ht->mc_window != nullptr &&
       ht->world.size >= 2 && bytes >= 4096 && bytes % 16 == 0 && reinterpret_cast<uintptr_t>(dest) % 16 == 0 &&
       reinterpret_cast<uintptr_t>(source) % 16 == 0) {
     unsigned blocks = clamp_blocks(fcollect_nvls_kernel, static_cast<unsigned>(coll_blocks_for(bytes)));

@@ -298,4 +298,63 @@ std::vector<int> exchange_fds(Bootstrap &bs, const std::string &tag, int my_fd) 
   return fds;
 }
 
+int broadcast_fd_group(Bootstrap &bs, const std::string &tag, const std::vector<int> &members, int my_index,
+                       int root_fd) {
+  const int n = static_cast<int>(members.size());
+  if (my_index == 0 && n == 1) return ::dup(root_fd);
+  // Socket names start with a random word chosen by the sender, so two jobs on one host cannot meet.
+  uint64_t job[2] = {0, 0};
+  if (my_index == 0) {
+    std::random_device rd;
+    job[0] = (static_cast<uint64_t>(rd()) << 32) ^ rd();
+    job[1] = static_cast<uint64_t>(::getpid());
+  }
+  std::vector<uint64_t> jobs(2 * size_t(n));
+  bs.allgather_group("fdg-job:" + tag, members, my_index, job, jobs.data(), sizeof(job));
+  char prefix[96];
+  std::snprintf(prefix, sizeof(prefix), "rocshmem_b200.g.%016llx.%llu.", static_cast<unsigned long long>(jobs[0]),
+                static_cast<unsigned long long>(jobs[1]));
+  int sock = ::socket(AF_UNIX, SOCK_DGRAM | SOCK_CLOEXEC, 0);
+  if (sock < 0) throw BootstrapError("broadcast_fd_group: socket() failed");
+  int result = -1;
+  try {
+    sockaddr_un mine;
+    socklen_t mine_len = abstract_addr(std::string(prefix) + std::to_string(my_index), &mine);
+    if (::bind(sock, reinterpret_cast<sockaddr *>(&mine), mine_len) != 0) {
+      throw BootstrapError(std::string("broadcast_fd_group: bind failed: ") + std::strerror(errno));
+    }
+    char one = 1;
+    std::vector<char> all(static_cast<size_t>(n));
+    bs.allgather_group("fdg-bound:" + tag, members, my_index, &one, all.data(), 1);  // receivers are bound
+    auto deadline = Clock::now() + std::chrono::milliseconds(bs.timeout_ms());
+    if (my_index == 0) {
+      for (int i = 1; i < n; ++i) {
+        sockaddr_un to;
+        socklen_t to_len = abstract_addr(std::string(prefix) + std::to_string(i), &to);
+        while (!send_fd(sock, to, to_len, 0, root_fd)) {
+          if (Clock::now() > deadline) throw BootstrapError("broadcast_fd_group: timed out sending a descriptor");
+          std::this_thread::sleep_for(std::chrono::microseconds(200));
+        }
+      }
+      result = ::dup(root_fd);
+      if (result < 0) throw BootstrapError("broadcast_fd_group: dup failed");
+    } else {
+      int src = -1;
+      while (!recv_fd(sock, 50, &src, &result)) {
+        if (Clock::now() > deadline) throw BootstrapError("broadcast_fd_group: timed out waiting for the descriptor");
+      }
+      if (src != 0) {
+        if (result >= 0) ::close(result);
+        result = -1;
+        throw BootstrapError("broadcast_fd_group: unexpected sender");
+      }
+    }
+  } catch (...) {
+    ::close(sock);
+    throw;
+  }
+  ::close(sock);
+  return result;
+}
+
 }  // namespace rocshmem

@@ -106,4 +106,10 @@ class CallbackBootstrap : public Bootstrap {
 // my_fd). The caller owns and closes the returned descriptors.
 std::vector<int> exchange_fds(Bootstrap &bs, const std::string &tag, int my_fd);
 
+// One descriptor from the first process of `members` (world ranks, the same order on every member) to all the
+// others. Collective over the members; `tag` must be unique per call. Returns a descriptor the caller owns: on
+// the sender a dup of `root_fd`, elsewhere the received one. Throws BootstrapError on a time-out.
+int broadcast_fd_group(Bootstrap &bs, const std::string &tag, const std::vector<int> &members, int my_index,
+                       int root_fd);
+
 }  // namespace rocshmem

@@ -90,6 +90,7 @@ Config Config::from_env(const std::map<std::string, std::string> &ov) {
     if (lookup(ov, "ROCSHMEM_PROXY_COLLECTIVES", &v)) c.proxy_collectives = static_cast<int>(parse_int(v)) != 0;
     if (lookup(ov, "ROCSHMEM_USE_WF_COAL", &v)) c.proxy_coalesce = static_cast<int>(parse_int(v)) != 0;
     if (lookup(ov, "ROCSHMEM_ENABLE_NVLS", &v)) c.enable_nvls = static_cast<int>(parse_int(v));
+    if (lookup(ov, "ROCSHMEM_TEAM_NVLS", &v)) c.team_nvls = static_cast<int>(parse_int(v)) != 0;
     if (lookup(ov, "ROCSHMEM_BACKEND", &v)) c.backend = v;
     if (lookup(ov, "ROCSHMEM_BOOTSTRAP_DIR", &v)) c.bootstrap_dir = v;
   } catch (const std::invalid_argument &e) {

@@ -32,6 +32,7 @@ struct Config {
   int proxy_collectives = 0;                 // ROCSHMEM_PROXY_COLLECTIVES (device collectives run by the proxy)
   int proxy_coalesce = 0;                    // ROCSHMEM_USE_WF_COAL (merge contiguous proxied messages)
   int enable_nvls = 1;                       // ROCSHMEM_ENABLE_NVLS (try multicast mapping)
+  int team_nvls = 1;                         // ROCSHMEM_TEAM_NVLS (a multicast object per split team)
   std::string backend = "auto";              // ROCSHMEM_BACKEND: auto | cuda | host
   std::string bootstrap_dir;                 // ROCSHMEM_BOOTSTRAP_DIR (native file rendezvous)
 

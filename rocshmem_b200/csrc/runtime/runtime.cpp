@@ -176,6 +176,9 @@ void Runtime::init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local
   world->my_pe.resize(n_local_);
   for (int l = 0; l < n_local_; ++l) world->my_pe[l] = first_pe_ + l;
   world->id = 0;
+  world->mc_window = mc_window_;
+  for (int r = 0; r < bs_->size(); ++r) world->procs.push_back(r);
+  world->my_proc = bs_->rank();
   world_team_ = world.get();
   teams_.push_back(std::move(world));
   team_by_slot_[0].store(teams_.back().get(), std::memory_order_release);
@@ -266,6 +269,100 @@ void Runtime::setup_nvls() {
   mc_window_ = va;
   mc_bound_ = true;
   if (cfg_.debug) std::fprintf(stderr, "[rocshmem pe %d] NVLS multicast mapped\n", first_pe_);
+}
+
+// A multicast object of its own for a split team (one PE per process): the same steps as for the world object,
+// agreed on among the team's processes only. Any failure leaves the team without a mapping on every member.
+void Runtime::setup_team_nvls(HostTeam *t, const std::string &tag) {
+  auto *cu = dynamic_cast<CudaVmmProvider *>(mem_.get());
+  if (!cu || !mc_bound_ || !cfg_.team_nvls || n_local_ != 1) return;
+  const int n = static_cast<int>(t->procs.size());
+  if (n < 2) return;
+  if (n == n_pes_) {  // the same members as the world team
+    t->mc_window = mc_window_;
+    return;
+  }
+  auto all_ok = [&](const char *step, bool ok) {
+    std::vector<int> flags(static_cast<size_t>(n));
+    int mine = ok ? 1 : 0;
+    bs_->allgather_group(tag + "/mc-" + step, t->procs, t->my_proc, &mine, flags.data(), sizeof(int));
+    return std::all_of(flags.begin(), flags.end(), [](int f) { return f == 1; });
+  };
+  std::string why;
+  MemHandle mc;
+  char *va = nullptr;
+  bool bound = false;
+  auto undo = [&]() {
+    if (bound) {
+      cu->unmap(va, stride_);
+      cu->mc_unbind(mc, stride_);
+    }
+    if (va) cu->release(va, stride_);
+    if (mc.opaque) cu->destroy(mc);
+    if (mc.fd >= 0) ::close(mc.fd);
+    if (cfg_.debug && !why.empty())
+      std::fprintf(stderr, "[rocshmem pe %d] team multicast unavailable: %s\n", first_pe_, why.c_str());
+  };
+  try {
+    size_t g = cu->mc_granularity(stride_, n);
+    if (!all_ok("gran", g != 0 && stride_ % g == 0)) return;
+    bool ok = true;
+    if (t->my_proc == 0) ok = cu->mc_create(stride_, n, &mc, &why);
+    if (!all_ok("create", ok)) {
+      undo();
+      return;
+    }
+    int fd = broadcast_fd_group(*bs_, tag + "/mc-fd", t->procs, t->my_proc, t->my_proc == 0 ? mc.fd : -1);
+    if (t->my_proc != 0) {
+      ok = cu->mc_import(fd, stride_, &mc, &why);
+      if (!ok) ::close(fd);
+    } else {
+      ::close(fd);
+    }
+    if (!all_ok("import", ok)) {
+      undo();
+      return;
+    }
+    ok = cu->mc_add_device(mc, &why);
+    if (!all_ok("add", ok)) {  // all devices are added before anyone binds
+      undo();
+      return;
+    }
+    try {
+      va = cu->reserve(stride_);
+    } catch (...) {
+      ok = false;
+      why = "no address range for the mapping";
+    }
+    if (ok) {
+      ok = cu->mc_bind_and_map(mc, handles_[first_pe_], va, &why);
+      bound = ok;
+    }
+    if (!all_ok("bind", ok)) {
+      undo();
+      return;
+    }
+  } catch (const std::exception &e) {
+    why = e.what();
+    undo();
+    return;
+  }
+  t->mc_handle = mc;
+  t->mc_window = va;
+  t->mc_owned = true;
+  if (cfg_.debug) std::fprintf(stderr, "[rocshmem pe %d] multicast mapping for a team of %d\n", first_pe_, n);
+}
+
+void Runtime::release_team_nvls(HostTeam *t) {
+  auto *cu = dynamic_cast<CudaVmmProvider *>(mem_.get());
+  if (cu && t->mc_owned) {
+    cu->unmap(t->mc_window, stride_);
+    cu->mc_unbind(t->mc_handle, stride_);
+    cu->release(t->mc_window, stride_);
+    cu->destroy(t->mc_handle);
+  }
+  t->mc_owned = false;
+  t->mc_window = nullptr;
 }
 
 void Runtime::build_states() {
@@ -374,6 +471,10 @@ void Runtime::finalize() {
   ctxs_.clear();
   default_ctx_ = nullptr;
   for (auto &slot : team_by_slot_) slot.store(nullptr, std::memory_order_release);
+  // All ranks have passed the barrier above with their queues drained, so no kernel uses a team's multicast
+  // mapping any more.
+  for (auto &t : teams_)
+    if (t->mc_owned) release_team_nvls(t.get());
   teams_.clear();
   world_team_ = nullptr;
   ops_.reset();
@@ -474,6 +575,7 @@ void Runtime::write_team_descriptor(HostTeam *t) {
     d.my_pe_world = pe;
     d.barrier_epoch = 0;
     d.ll_epoch = 0;
+    d.mc_base = t->mc_window;
     auto *dst = reinterpret_cast<rocshmem_team_dev *>(internal_base(pe) + layout_.teams) + t->slot;
     mem_->write(dst, &d, sizeof(d));
     // A reused slot starts from epoch 0 again, so the arrival flags of the device barrier and the
@@ -547,7 +649,10 @@ int Runtime::team_split_strided(HostTeam *parent, int start, int stride, int siz
   team->id = parent->id * 1000003ull + (seq + 1) * 7919ull + uint64_t(plan.world.pe_start) * 31ull +
              uint64_t(plan.world.stride) * 17ull + uint64_t(plan.world.size);
   HostTeam *raw = team.get();
+  raw->procs = procs;
+  raw->my_proc = my_index;
   teams_.push_back(std::move(team));
+  setup_team_nvls(raw, tag);
   write_team_descriptor(raw);
   team_by_slot_[raw->slot].store(raw, std::memory_order_release);
   // Descriptors and cleared flags are in place on every member before the handle is used.
@@ -561,6 +666,20 @@ int Runtime::team_split_strided(HostTeam *parent, int start, int stride, int siz
 void Runtime::team_destroy(HostTeam *t) {
   std::lock_guard<std::recursive_mutex> g(mu_);
   if (!t || t == world_team_) return;
+  if (t->mc_owned) {
+    // Nobody may unbind its memory while another member's kernel can still store through the multicast object:
+    // every member finishes its own work, then all of them meet, then the mapping goes. (OpenSHMEM makes
+    // team_destroy collective; for teams without a multicast object nothing is exchanged here.)
+    try {
+      ops_->quiet(default_ctx_);
+      char one = 1;
+      std::vector<char> all(t->procs.size());
+      bs_->allgather_group("team-destroy/" + std::to_string(t->id), t->procs, t->my_proc, &one, all.data(), 1);
+    } catch (const std::exception &e) {
+      std::fprintf(stderr, "[rocshmem pe %d] team_destroy: %s\n", first_pe_, e.what());
+    }
+    release_team_nvls(t);
+  }
   for (int l = 0; l < n_local_; ++l) {
     rocshmem_team_dev d;
     std::memset(&d, 0, sizeof(d));

@@ -43,6 +43,14 @@ struct HostTeam {
   uint64_t split_seq = 0;     // number of splits performed with this team as parent
   uint64_t barrier_epoch = 0;  // host-side mirror for the CPU backend
   uint64_t id = 0;
+  // Processes (bootstrap ranks) that host members, in team order, and my position among them.
+  std::vector<int> procs;
+  int my_proc = 0;
+  // NVLink multicast mapping of my heap that spans exactly this team's members (nullptr: none; the team's
+  // collectives then use point-to-point kernels). The world team shares the runtime's mapping (mc_owned false).
+  char *mc_window = nullptr;
+  MemHandle mc_handle;
+  bool mc_owned = false;
 };
 
 struct HostCtx {
@@ -151,6 +159,8 @@ class Runtime {
  private:
   Runtime() = default;
   void setup_nvls();
+  void setup_team_nvls(HostTeam *t, const std::string &tag);
+  void release_team_nvls(HostTeam *t);
   void write_team_descriptor(HostTeam *t);
   void build_states();
 

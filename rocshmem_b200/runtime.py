@@ -335,6 +335,12 @@ class Team:
             raise ValueError(f"rocshmem_b200: invalid team split ({start}, {stride}, {size})")
         return Team(h)
 
+    def has_nvls(self) -> bool:
+        """True when the team has an NVLink multicast mapping of the heap that spans exactly its members (the
+        switch-side allreduce, all-gather and broadcast kernels are then used for it). Split teams get one when
+        every member is a process of its own and ``ROCSHMEM_TEAM_NVLS`` is not 0."""
+        return bool(self.handle) and _C().team_has_nvls(self.handle)
+
     def sync(self) -> int:
         """Host-side team barrier without the completion of outstanding operations; 0 on success."""
         return _C().team_sync(self.handle)

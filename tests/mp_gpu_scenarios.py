@@ -162,6 +162,90 @@ def gpu_library_collectives():
     shm.finalize()
 
 
+def gpu_team_nvls():
+    """Split teams with a multicast mapping of their own: two disjoint halves and the even / odd PEs exist at the
+    same time (every PE is a member of two of them), run the switch-side allreduce, all-gather and broadcast,
+    are destroyed and split again with other members, and one team is still alive at finalize."""
+    os.environ["ROCSHMEM_BCAST_NVLS"] = "1"
+    _init("1G")
+    me, n = RANK, WORLD
+    dev = shm.device()
+    world = shm.team_world()
+    nelem, nbytes = 3 << 20, 5 << 20
+    src = shm.zeros(nelem, torch.float32)
+    dst = shm.zeros(nelem, torch.float32)
+    bsrc = shm.zeros(nelem, torch.bfloat16)
+    bdst = shm.zeros(nelem, torch.bfloat16)
+    gsrc = shm.zeros(nbytes, torch.uint8)
+    gdst = shm.zeros(nbytes * n, torch.uint8)
+    ins = [torch.randn(nelem, generator=torch.Generator().manual_seed(40 + p)) for p in range(n)]
+    src.copy_(ins[me].to(dev))
+    bsrc.copy_(ins[me].to(torch.bfloat16).to(dev))
+    gsrc.fill_(me + 1)
+    torch.cuda.synchronize()
+    shm.barrier_all()
+
+    def check(team, members, tag):
+        if me not in members:
+            return
+        m = len(members)
+        assert team.valid and team.n_pes() == m and team.my_pe() == members.index(me), tag
+        assert team.has_nvls() == (shm.nvls_available() and m >= 2), (tag, team.has_nvls())
+        ref = torch.stack([ins[p].double() for p in members]).sum(0)
+        bref = torch.stack([ins[p].to(torch.bfloat16).double() for p in members]).sum(0)
+        for algo in (shm.ALLREDUCE_AUTO, shm.ALLREDUCE_NVLS, shm.ALLREDUCE_TWO_SHOT):
+            dst.zero_()
+            bdst.zero_()
+            coll.allreduce_async(dst, src, shm.OP_SUM, team=team, algo=algo)
+            coll.allreduce_async(bdst, bsrc, shm.OP_SUM, team=team, algo=algo)
+            _ok()
+            assert torch.allclose(dst.cpu().double(), ref, rtol=1e-5, atol=1e-5 * m), (tag, algo)
+            assert torch.allclose(bdst.cpu().double(), bref, rtol=3e-2, atol=3e-2 * m), (tag, algo, "bf16")
+        gdst.zero_()
+        coll.fcollect_async(gdst[:nbytes * m], gsrc, team=team)
+        _ok()
+        got = gdst.cpu()[:nbytes * m].view(m, nbytes)
+        assert all(torch.all(got[i] == members[i] + 1) for i in range(m)), tag
+        gdst.zero_()
+        torch.cuda.synchronize()
+        team.sync()
+        coll.broadcast_async(gdst[:nbytes], gsrc, m - 1, team=team)
+        _ok()
+        if me != members[-1]:
+            assert torch.all(gdst.cpu()[:nbytes] == members[-1] + 1), tag
+        team.sync()
+
+    half = max(1, n // 2)
+    lower, upper = list(range(half)), list(range(half, n))
+    evens, odds = list(range(0, n, 2)), list(range(1, n, 2))
+    t_lo = world.split_strided(0, 1, half)
+    t_hi = world.split_strided(half, 1, n - half)
+    t_ev = world.split_strided(0, 2, len(evens))
+    t_od = world.split_strided(1, 2, len(odds)) if odds else None
+    for rep in range(2):
+        check(t_lo, lower, "lower")
+        check(t_hi, upper, "upper")
+        check(t_ev, evens, "even")
+        if odds:
+            check(t_od, odds, "odd")
+    check(world, list(range(n)), "world")
+    for t in (t_lo, t_hi, t_ev, t_od):
+        if t is not None and t.valid:
+            t.destroy()
+    shm.barrier_all()
+    # the freed slots are taken by teams with other members
+    if n >= 3:
+        rest = list(range(1, n))
+        t_rest = world.split_strided(1, 1, n - 1)
+        check(t_rest, rest, "all but PE 0")
+        t_ends = world.split_strided(0, n - 1, 2)
+        check(t_ends, [0, n - 1], "first and last")
+    _ok()
+    shm.barrier_all()
+    print(f"nvls={shm.nvls_available()}")
+    shm.finalize()    # with teams (and their mappings) still alive
+
+
 C_BCAST, C_FCOLLECT, C_ALLTOALL, C_SUM = 0, 1, 2, 3
 
 
@@ -357,5 +441,5 @@ def gpu_models():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_proxied_collectives, gpu_moe,
+SCENARIOS = {f.__name__: f for f in (gpu_device_suite, gpu_library_collectives, gpu_team_nvls, gpu_proxied_collectives, gpu_moe,
                                      gpu_tp_fused, gpu_models)}

@@ -24,6 +24,7 @@ CUDA_ENV = {"ROCSHMEM_TEST_BACKEND": "cuda", "NCCL_NVLS_ENABLE": "0"}
 @pytest.mark.parametrize("world", world_sizes())
 @pytest.mark.parametrize("scenario", ["host_plumbing", "store_bootstrap", "teams", "collectives_host",
                                       "wait_and_signal", "gpu_device_suite", "gpu_library_collectives",
+                                      "gpu_team_nvls",
                                       "gpu_proxied_collectives", "gpu_moe", "gpu_tp_fused", "gpu_models",
                                       # the parallelism helpers on their GPU paths (stream-ordered kernels)
                                       "data_parallel", "ulysses", "ring_attention", "pipeline_stages"])
