@@ -205,15 +205,32 @@ void CudaVmmProvider::destroy(MemHandle &h) {
   h.fd = -1;
 }
 
+namespace {
+// The copies below may be the first CUDA call of a user thread, whose current device is 0 by default.
+struct OnDevice {
+  int prev = -1;
+  explicit OnDevice(int want) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur != want && cudaSetDevice(want) == cudaSuccess) prev = cur;
+  }
+  ~OnDevice() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+}  // namespace
+
 void CudaVmmProvider::write(void *dst, const void *src, size_t bytes) {
+  OnDevice on(device_);
   check_rt(cudaMemcpy(dst, src, bytes, cudaMemcpyDefault), "cudaMemcpy to heap");
 }
 
 void CudaVmmProvider::read(void *dst, const void *src, size_t bytes) {
+  OnDevice on(device_);
   check_rt(cudaMemcpy(dst, src, bytes, cudaMemcpyDefault), "cudaMemcpy from heap");
 }
 
 void CudaVmmProvider::zero(void *dst, size_t bytes) {
+  OnDevice on(device_);
   check_rt(cudaMemset(dst, 0, bytes), "cudaMemset");
   check_rt(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
 }

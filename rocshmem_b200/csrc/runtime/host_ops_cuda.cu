@@ -59,6 +59,24 @@ __global__ void host_amo_kernel(int op, int dtype, void *target, unsigned long l
   *result = old;
 }
 
+// Host threads start with device 0 current. Every entry point of the engine may be the first CUDA call of a user
+// thread, so each selects the runtime's device for its own duration and puts the caller's choice back.
+class DeviceScope {
+ public:
+  explicit DeviceScope(int want) {
+    int cur = -1;
+    if (cudaGetDevice(&cur) == cudaSuccess && cur != want && cudaSetDevice(want) == cudaSuccess) prev_ = cur;
+  }
+  ~DeviceScope() {
+    if (prev_ >= 0) cudaSetDevice(prev_);
+  }
+  DeviceScope(const DeviceScope &) = delete;
+  DeviceScope &operator=(const DeviceScope &) = delete;
+
+ private:
+  int prev_ = -1;
+};
+
 class CudaHostOps final : public HostOps {
  public:
   explicit CudaHostOps(Runtime *rt) : rt_(rt) {
@@ -80,11 +98,13 @@ class CudaHostOps final : public HostOps {
   }
 
   void ctx_init(HostCtx *c) override {
+    DeviceScope on_device(rt_->device());
     cudaStream_t s;
     check(cudaStreamCreateWithFlags(&s, cudaStreamNonBlocking), "context stream");
     c->stream = s;
   }
   void ctx_fini(HostCtx *c) override {
+    DeviceScope on_device(rt_->device());
     if (c->stream) {
       cudaStreamSynchronize(stream(c));
       cudaStreamDestroy(stream(c));
@@ -93,15 +113,18 @@ class CudaHostOps final : public HostOps {
   }
 
   void put(HostCtx *c, void *dst, const void *src, size_t bytes, int pe, bool blocking) override {
+    DeviceScope on_device(rt_->device());
     check(cudaMemcpyAsync(rt_->translate(dst, pe), src, bytes, cudaMemcpyDefault, stream(c)), "put");
     if (blocking) check(cudaStreamSynchronize(stream(c)), "put completion");
   }
   void get(HostCtx *c, void *dst, const void *src, size_t bytes, int pe, bool blocking) override {
+    DeviceScope on_device(rt_->device());
     check(cudaMemcpyAsync(dst, rt_->translate(src, pe), bytes, cudaMemcpyDefault, stream(c)), "get");
     if (blocking) check(cudaStreamSynchronize(stream(c)), "get completion");
   }
 
   uint64_t amo(HostCtx *c, AmoOp op, DType t, void *target, uint64_t value, uint64_t cond, int pe) override {
+    DeviceScope on_device(rt_->device());
     std::lock_guard<std::mutex> g(slot_mu_);
     unsigned long long *result = slots_;
     host_amo_kernel<<<1, 1, 0, stream(c)>>>(static_cast<int>(op), static_cast<int>(t),
@@ -113,9 +136,13 @@ class CudaHostOps final : public HostOps {
 
   // Operations of one context are stream-ordered, which is stronger than fence requires.
   void fence(HostCtx *) override {}
-  void quiet(HostCtx *c) override { check(cudaStreamSynchronize(stream(c)), "quiet"); }
+  void quiet(HostCtx *c) override {
+    DeviceScope on_device(rt_->device());
+    check(cudaStreamSynchronize(stream(c)), "quiet");
+  }
 
   int test(void *ivar, DType t, int cmp, uint64_t value) override {
+    DeviceScope on_device(rt_->device());
     uint64_t seen = peek(ivar, dtype_size(t));
     return compare_bits(seen, t, cmp, value) ? 1 : 0;
   }
@@ -123,6 +150,7 @@ class CudaHostOps final : public HostOps {
   // Polls with small device-to-host copies instead of parking a kernel on the GPU: the GPU stays
   // free for the work that will eventually satisfy the wait.
   int wait_until(void *ivar, DType t, int cmp, uint64_t value) override {
+    DeviceScope on_device(rt_->device());
     auto deadline = std::chrono::steady_clock::now() +
                     std::chrono::milliseconds(rt_->config().wait_timeout_ms);
     uint64_t seen = 0;
@@ -148,6 +176,7 @@ class CudaHostOps final : public HostOps {
   }
 
   int barrier(HostCtx *c, HostTeam *team, bool sync_only) override {
+    DeviceScope on_device(rt_->device());
     // barrier_all completes the context's outstanding operations first; stream order does that.
     (void)sync_only;
     unsigned before = error_count();
@@ -157,19 +186,23 @@ class CudaHostOps final : public HostOps {
   }
 
   int broadcast(HostCtx *c, HostTeam *team, void *dst, const void *src, size_t bytes, int root) override {
+    DeviceScope on_device(rt_->device());
     return run(c, kernels::coll_broadcast(team->dev, to_first(dst), to_first(src), bytes, root, stream(c),
                                           kernels::COLL_PRE_SYNC));
   }
   int reduce(HostCtx *c, HostTeam *team, void *dst, const void *src, size_t nelems, DType t,
              ROCSHMEM_OP op) override {
+    DeviceScope on_device(rt_->device());
     return run(c, kernels::coll_allreduce(team->dev, to_first(dst), to_first(src), nelems,
                                           static_cast<int>(t), op, kernels::ALLREDUCE_AUTO, stream(c)));
   }
   int fcollect(HostCtx *c, HostTeam *team, void *dst, const void *src, size_t bytes) override {
+    DeviceScope on_device(rt_->device());
     return run(c, kernels::coll_fcollect(team->dev, to_first(dst), to_first(src), bytes, stream(c),
                                          kernels::COLL_PRE_SYNC));
   }
   int alltoall(HostCtx *c, HostTeam *team, void *dst, const void *src, size_t bytes) override {
+    DeviceScope on_device(rt_->device());
     return run(c, kernels::coll_alltoall(team->dev, to_first(dst), to_first(src), bytes, stream(c),
                                          kernels::COLL_PRE_SYNC));
   }

@@ -4,6 +4,7 @@
 
 #include <algorithm>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <stdexcept>
 
@@ -98,6 +99,13 @@ void Runtime::init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local
   first_pe_ = bs_->rank() * n_local;
   device_ = device;
   t_current_local = 0;
+  if (cfg_.use_proxy) {
+    // A kernel that waits for the proxy must never share a hardware work queue with the kernels the proxy launches
+    // for it: streams beyond the number of queues (8 by default) are multiplexed, and work queued behind the
+    // waiting kernel would start only when it ends. Takes effect when no CUDA context exists yet in this process;
+    // a value the user has set is kept.
+    ::setenv("CUDA_DEVICE_MAX_CONNECTIONS", "32", 0);
+  }
   if (n_pes_ > ROCSHMEM_MAX_PES) throw std::invalid_argument("rocshmem_init: more than 64 PEs");
 
   // Backend selection.

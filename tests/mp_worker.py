@@ -702,13 +702,13 @@ def data_parallel():
         return ((m(x) * m.scale.float() - y) ** 2).mean()
 
     used_before = shm.heap_info()["used"]
-    model = make_model()
+    model = make_model().to(dev())     # on the CUDA backend the model lives on the GPU (stream-ordered kernels)
     dp = GradientBuckets(list(model.parameters()), bucket_bytes=2048)
     assert len(dp.buckets) >= 3
     for step in range(3):
         model.zero_grad(set_to_none=True)
         x, y = batch(me, step)
-        loss_of(model, x, y).backward()
+        loss_of(model, x.to(dev()), y.to(dev())).backward()
         dp.finish()
         ref = make_model()
         for r in range(n):
@@ -716,21 +716,21 @@ def data_parallel():
             (loss_of(ref, xr, yr) / n).backward()
         for (name, p), q in zip(model.named_parameters(), ref.parameters()):
             want = q.grad if q.grad is not None else torch.zeros_like(q)
-            tol = 2e-2 if p.dtype == torch.bfloat16 else 1e-5
-            assert torch.allclose(p.grad.float(), want.float(), rtol=tol, atol=tol), (step, name)
+            tol = 2e-2 if p.dtype == torch.bfloat16 else (1e-4 if shm.is_cuda() else 1e-5)
+            assert torch.allclose(p.grad.float().cpu(), want.float(), rtol=tol, atol=tol), (step, name)
     # without hooks: everything is packed and reduced in finish()
     dp.destroy()
     dp = GradientBuckets(list(model.parameters()), bucket_bytes=1 << 20, average=False, register_hooks=False)
     model.zero_grad(set_to_none=True)
     x, y = batch(me, 9)
-    loss_of(model, x, y).backward()
+    loss_of(model, x.to(dev()), y.to(dev())).backward()
     mine = model[0].weight.grad.clone()
     dp.finish()
     total = shm.zeros(mine.numel(), torch.float32)
     part = shm.zeros(mine.numel(), torch.float32)
     part.copy_(mine.reshape(-1))
     assert coll.reduce(total, part, shm.OP_SUM) == 0
-    assert torch.allclose(model[0].weight.grad.reshape(-1), total.cpu(), rtol=1e-5, atol=1e-6)
+    assert torch.allclose(model[0].weight.grad.reshape(-1).cpu(), total.cpu(), rtol=1e-5, atol=1e-6)
     shm.free(part)
     shm.free(total)
     dp.destroy()
@@ -829,13 +829,14 @@ def pipeline_stages():
     ys = [torch.randn(mb, d, generator=g) for _ in range(micro)]
     loss_fn = lambda out, tgt: ((out - tgt) ** 2).mean()
     used_before = shm.heap_info()["used"]
-    mine = make_layers()[me]
+    mine = make_layers()[me].to(dev())
+    xs_dev, ys_dev = [x.to(dev()) for x in xs], [y.to(dev()) for y in ys]
     stage = PipelineStage(mine, num_stages=n, act_shape=(mb, d))
     assert stage.active and stage.stage == me
     for rep in range(2):
         mine.zero_grad(set_to_none=True)
-        losses = stage.run(micro_batches=xs if me == 0 else None, loss_fn=loss_fn if me == n - 1 else None,
-                           targets=ys if me == n - 1 else None, num_micro=micro)
+        losses = stage.run(micro_batches=xs_dev if me == 0 else None, loss_fn=loss_fn if me == n - 1 else None,
+                           targets=ys_dev if me == n - 1 else None, num_micro=micro)
         ref = make_layers()
         ref_losses = []
         for x, y in zip(xs, ys):
@@ -845,10 +846,11 @@ def pipeline_stages():
             l = loss_fn(h, y)
             l.backward()
             ref_losses.append(l.detach())
+        tol = 1e-4 if shm.is_cuda() else 1e-5
         for p, q in zip(mine.parameters(), ref[me].parameters()):
-            assert torch.allclose(p.grad, q.grad, rtol=1e-5, atol=1e-6), rep
+            assert torch.allclose(p.grad.cpu(), q.grad, rtol=tol, atol=tol / 10), rep
         if me == n - 1:
-            assert torch.allclose(torch.stack(losses).cpu(), torch.stack(ref_losses), rtol=1e-5, atol=1e-6)
+            assert torch.allclose(torch.stack(losses).cpu(), torch.stack(ref_losses), rtol=tol, atol=tol / 10)
         else:
             assert losses is None
         shm.barrier_all()

@@ -1,4 +1,4 @@
-"""Builds the host-only C++ programs tests/cpp/host_api_sos.cpp and host_threads_sos.cpp with g++ against the
+"""Builds the host-only C++ programs tests/cpp/host_api_sos.cpp, host_threads_sos.cpp and host_patterns_sos.cpp with g++ against the
 runtime library and runs them as several processes on the CPU shared-memory backend: the typed C++ host API (put /
 get / p / g, atomics, waits, collectives, teams, contexts, rocshmem_ptr; then several threads per process, each
 with its own context) end to end, as the reference's SOS programs do for its host API."""
@@ -22,7 +22,7 @@ def programs(tmp_path_factory):
     if not _build.is_built():
         _build.build(with_tests=False)
     out = {}
-    for name in ("host_api_sos", "host_threads_sos"):
+    for name in ("host_api_sos", "host_threads_sos", "host_patterns_sos"):
         exe = str(tmp_path_factory.mktemp("sos") / name)
         cmd = ["g++", "-std=c++17", "-O1", "-g", f"-I{INC}", os.path.join(ROOT, "tests", "cpp", name + ".cpp"), "-o", exe,
                f"-L{LIB}", "-lrocshmem_b200", f"-Wl,-rpath,{LIB}", "-lpthread"]
@@ -32,7 +32,8 @@ def programs(tmp_path_factory):
     return out
 
 
-@pytest.mark.parametrize("name,world", [("host_api_sos", 2), ("host_api_sos", 5), ("host_threads_sos", 3)])
+@pytest.mark.parametrize("name,world", [("host_api_sos", 2), ("host_api_sos", 5), ("host_threads_sos", 3),
+                                        ("host_patterns_sos", 2), ("host_patterns_sos", 5)])
 def test_cpp_host_programs_on_the_cpu_backend(programs, name, world, tmp_path):
     program = programs[name]
     kv = tmp_path / "kv"
@@ -40,7 +41,7 @@ def test_cpp_host_programs_on_the_cpu_backend(programs, name, world, tmp_path):
     procs = []
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), ROCSHMEM_BACKEND="host",
-                   ROCSHMEM_HEAP_SIZE="16M", ROCSHMEM_BOOTSTRAP_DIR=str(kv), ROCSHMEM_WAIT_TIMEOUT_MS="30000")
+                   ROCSHMEM_HEAP_SIZE="64M", ROCSHMEM_BOOTSTRAP_DIR=str(kv), ROCSHMEM_WAIT_TIMEOUT_MS="30000")
         procs.append(subprocess.Popen([program], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = []
     try:
@@ -78,6 +79,19 @@ def test_launcher_runs_ranks_tags_output_and_propagates_failures(programs):
     assert rc == 124
     # command line form
     assert launch.main(["-n", "2", "--no-tag", "--", sys.executable, "-c", "import os; assert os.environ['WORLD_SIZE'] == '2'"]) == 0
+
+
+def test_global_exit_ends_every_rank_with_the_status(programs):
+    """One PE calls rocshmem_global_exit(7) while the others wait on a word nobody writes (the reference's
+    global_exit program): the job ends with that status instead of waiting for the time-out."""
+    import io
+    import time
+
+    from rocshmem_b200 import launch
+    t0 = time.time()
+    rc = launch.launch([programs["host_patterns_sos"], "exit"], 3, backend="host", timeout_s=100, out=io.StringIO(),
+                       extra_env={"ROCSHMEM_HEAP_SIZE": "16M", "ROCSHMEM_WAIT_TIMEOUT_MS": "60000"})
+    assert rc == 7 and time.time() - t0 < 40
 
 
 def test_repeated_launches_on_one_port_do_not_see_each_others_rendezvous_files(programs):

@@ -31,13 +31,18 @@ CUDA_ENV = {"ROCSHMEM_TEST_BACKEND": "cuda", "NCCL_NVLS_ENABLE": "0"}
 def test_scenario(scenario, world):
     if world == 0:
         pytest.skip("needs at least two GPUs")
-    results = run_ranks(scenario, world, timeout=300, env_extra=CUDA_ENV)
+    env = dict(CUDA_ENV)
+    if scenario == "gpu_proxied_collectives":
+        # the waiting kernel and the proxy's kernels need hardware queues of their own (the runtime asks for the same
+        # when it is the first to touch CUDA in the process)
+        env["CUDA_DEVICE_MAX_CONNECTIONS"] = "32"
+    results = run_ranks(scenario, world, timeout=300, env_extra=env)
     assert_all_ok(results)
     if scenario in ("gpu_device_suite", "gpu_library_collectives"):
         print(results[0][1][-400:])
 
 
-@pytest.mark.parametrize("name", ["host_api_sos", "host_threads_sos"])
+@pytest.mark.parametrize("name", ["host_api_sos", "host_threads_sos", "host_patterns_sos"])
 def test_cpp_host_programs_on_the_cuda_backend(name, tmp_path):
     """The typed C++ host API (and several host threads per process, each with its own context) over real peer
     mappings: the programs of test_host_cpp_program.py, one process per GPU."""
@@ -66,13 +71,13 @@ def test_cpp_host_programs_on_the_cuda_backend(name, tmp_path):
     procs = []
     for r in range(world):
         env = dict(os.environ, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r), ROCSHMEM_BACKEND="cuda",
-                   ROCSHMEM_HEAP_SIZE="64M", ROCSHMEM_BOOTSTRAP_DIR=str(kv), ROCSHMEM_WAIT_TIMEOUT_MS="30000",
+                   ROCSHMEM_HEAP_SIZE="64M", ROCSHMEM_BOOTSTRAP_DIR=str(kv), ROCSHMEM_WAIT_TIMEOUT_MS="10000",
                    NCCL_NVLS_ENABLE="0")
         procs.append(subprocess.Popen([exe], env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
     outs = []
     try:
         for p in procs:
-            out, _ = p.communicate(timeout=240)
+            out, _ = p.communicate(timeout=90)
             outs.append((p.returncode, out))
     finally:
         for p in procs:
