@@ -168,11 +168,15 @@ __device__ inline int proxy_collective(unsigned type, const rocshmem_team_dev *t
 // ---- barrier ------------------------------------------------------------------------------------------
 
 // Block-collective. Returns ROCSHMEM_SUCCESS or ROCSHMEM_ERROR (a peer did not arrive in time).
-__device__ inline int team_barrier(rocshmem_team_dev *t) {
+// `through_proxy` == false is for the library's own barrier kernel: it is what the host (and the proxy thread, for
+// a proxied barrier) launches, so it must signal over NVLink itself instead of asking the proxy again.
+__device__ inline int team_barrier(rocshmem_team_dev *t, bool through_proxy = true) {
   const rocshmem_device_state &s = st();
   const unsigned tid = block_tid(), nthr = block_threads();
   if (t->my_pe < 0) return ROCSHMEM_ERROR;
-  if (proxy_collectives_on()) return proxy_collective(ROCSHMEM_PROXY_BARRIER, t, nullptr, nullptr, 0, 0, 0, 0);
+  if (through_proxy && proxy_collectives_on()) {
+    return proxy_collective(ROCSHMEM_PROXY_BARRIER, t, nullptr, nullptr, 0, 0, 0, 0);
+  }
   __syncthreads();  // everything the block did before the barrier is ordered before the signals
   if (tid == 0) t->barrier_epoch = t->barrier_epoch + 1;
   __syncthreads();

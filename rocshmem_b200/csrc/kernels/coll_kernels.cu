@@ -167,8 +167,9 @@ __device__ __forceinline__ void reduce_range(const rocshmem_team_dev *t, T *dest
 __global__ void __launch_bounds__(64) barrier_kernel(rocshmem_team_t team) {
   const rocshmem_team_dev *t = detail::team_of(team);
   if (t->my_pe < 0) return;
-  // Reuses the device API's block barrier so host- and device-initiated barriers share one epoch.
-  detail::team_barrier(const_cast<rocshmem_team_dev *>(t));
+  // Reuses the device API's block barrier so host- and device-initiated barriers share one epoch. Never through
+  // the proxy: this kernel is what the proxy launches for a proxied barrier.
+  detail::team_barrier(const_cast<rocshmem_team_dev *>(t), false);
 }
 
 template <typename T, int OP>

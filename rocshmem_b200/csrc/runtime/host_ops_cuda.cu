@@ -3,6 +3,7 @@
 // system-scope semantics as device-initiated ones.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <chrono>
 #include <stdexcept>
 #include <string>
@@ -125,8 +126,10 @@ class CudaHostOps final : public HostOps {
 
   uint64_t amo(HostCtx *c, AmoOp op, DType t, void *target, uint64_t value, uint64_t cond, int pe) override {
     DeviceScope on_device(rt_->device());
-    std::lock_guard<std::mutex> g(slot_mu_);
-    unsigned long long *result = slots_;
+    // One result word per calling thread: threads with contexts of their own do not wait for one another.
+    const unsigned slot = my_slot();
+    std::lock_guard<std::mutex> g(slot_mu_[slot]);
+    unsigned long long *result = slots_ + slot;
     host_amo_kernel<<<1, 1, 0, stream(c)>>>(static_cast<int>(op), static_cast<int>(t),
                                             rt_->translate(target, pe), value, cond, result);
     check(cudaGetLastError(), "atomic launch");
@@ -227,18 +230,27 @@ class CudaHostOps final : public HostOps {
   }
 
   uint64_t peek(const void *p, size_t bytes) {
-    std::lock_guard<std::mutex> g(slot_mu_);
-    unsigned long long *slot = slots_ + 8;
+    const unsigned index = my_slot();
+    std::lock_guard<std::mutex> g(slot_mu_[index]);
+    unsigned long long *slot = slots_ + kSlots + index;
     *slot = 0;
     check(cudaMemcpyAsync(slot, p, bytes, cudaMemcpyDeviceToHost, poll_stream_), "poll copy");
     check(cudaStreamSynchronize(poll_stream_), "poll completion");
     return *slot;
   }
 
+  // Threads take result words round robin; two threads share one (and its lock) only beyond kSlots threads.
+  static constexpr unsigned kSlots = 240;   // 2 x 240 words of 8 bytes fit the 4 KiB allocation
+  unsigned my_slot() {
+    thread_local unsigned mine = next_slot_.fetch_add(1, std::memory_order_relaxed) % kSlots;
+    return mine;
+  }
+
   Runtime *rt_;
   unsigned long long *slots_ = nullptr;
   cudaStream_t poll_stream_ = nullptr;
-  std::mutex slot_mu_;
+  std::mutex slot_mu_[kSlots];
+  std::atomic<unsigned> next_slot_{0};
 };
 
 }  // namespace
