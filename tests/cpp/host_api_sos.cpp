@@ -124,8 +124,8 @@ int main() {
   // wait / test: a ring of flags, started by PE 0
   int *flag = static_cast<int *>(rocshmem_malloc(4 * sizeof(int)));
   fill<int>(flag, 4, 0, 0);
+  CHECK(rocshmem_int_test(flag, ROCSHMEM_CMP_EQ, 0) == 1);   // before the barrier: afterwards the left neighbour may write
   rocshmem_barrier_all();
-  CHECK(rocshmem_int_test(flag, ROCSHMEM_CMP_EQ, 0) == 1);
   if (me != 0) rocshmem_int_wait_until(flag, ROCSHMEM_CMP_EQ, me);
   if (right != 0) rocshmem_int_p(flag, right, right);
   rocshmem_barrier_all();
