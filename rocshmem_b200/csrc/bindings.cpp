@@ -436,6 +436,17 @@ PYBIND11_MODULE(_C, m) {
     py::gil_scoped_release r;
     return exchange_fds(bs, "test", fd);
   });
+  m.def("broadcast_fd_group_file", [](const std::string &dir, int rank, int size, std::vector<int> members, int fd,
+                                      int timeout_ms) {
+    FileBootstrap bs(dir, rank, size);
+    bs.set_timeout_ms(timeout_ms);
+    int my_index = -1;
+    for (size_t i = 0; i < members.size(); ++i)
+      if (members[i] == rank) my_index = static_cast<int>(i);
+    if (my_index < 0) throw std::invalid_argument("broadcast_fd_group_file: the caller is not a member");
+    py::gil_scoped_release r;
+    return broadcast_fd_group(bs, "test-group", members, my_index, fd);
+  });
   m.def("file_bootstrap_allgather", [](const std::string &dir, int rank, int size, py::bytes value, int timeout_ms) {
     FileBootstrap bs(dir, rank, size);
     bs.set_timeout_ms(timeout_ms);

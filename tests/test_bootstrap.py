@@ -49,6 +49,31 @@ def test_descriptor_exchange_three_processes():
         assert got[r] == [f"payload-from-{i}" for i in range(3)]
 
 
+def _fd_group_worker(d, rank, size, members, q):
+    C = _native.load()
+    fd = -1
+    if rank == members[0]:
+        fd = os.memfd_create("group")
+        os.write(fd, b"from-the-first-member")
+    got = C.broadcast_fd_group_file(d, rank, size, members, fd, 20000)
+    q.put((rank, os.pread(got, 64, 0).decode()))
+    os.close(got)
+
+
+def test_descriptor_from_the_first_member_of_a_subgroup():
+    """Four processes, three of them form a group (not in rank order of the job): the first member's descriptor
+    reaches the two others; the process outside the group takes no part."""
+    ctx = mp.get_context("spawn")
+    members = [2, 0, 3]
+    with tempfile.TemporaryDirectory() as d:
+        q = ctx.Queue()
+        procs = [ctx.Process(target=_fd_group_worker, args=(d, r, 4, members, q)) for r in members]
+        [p.start() for p in procs]
+        got = dict(q.get(timeout=60) for _ in members)
+        [p.join(30) for p in procs]
+    assert got == {r: "from-the-first-member" for r in members}
+
+
 def test_missing_rank_times_out_instead_of_hanging():
     C = _native.load()
     import time
