@@ -536,11 +536,14 @@ bool use_bcast_nvls() {
   return on;
 }
 
-// ROCSHMEM_FCOLLECT_NVLS=0 keeps all-gathers on the point-to-point push kernel even where the multicast mapping exists.
+// ROCSHMEM_FCOLLECT_NVLS=1 sends all-gathers through the multicast mapping. Off by default: an all-gather is bound
+// by what a rank receives, and through the switch it receives its own block as well (n blocks instead of n - 1),
+// so the push kernel is faster wherever both were measured (64 MiB per member: 131 us against 208 us on two GPUs,
+// 324 us against 388 us on four); what the switch saves is egress, (n - 1) blocks down to one.
 bool use_fcollect_nvls() {
   static const bool on = [] {
     const char *e = std::getenv("ROCSHMEM_FCOLLECT_NVLS");
-    return e == nullptr || e[0] != '0';
+    return e != nullptr && e[0] != '\0' && e[0] != '0';
   }();
   return on;
 }
@@ -561,7 +564,10 @@ int launch_allreduce_typed(rocshmem_team_t team, void *dest, const void *source,
   HostTeam *ht = rt.team_from_handle(team);
   const int n = ht ? ht->world.size : rt.n_pes();
   if (algo == ALLREDUCE_AUTO) {
-    const bool nvls_ok = ht != nullptr && ht->mc_window != nullptr && op == ROCSHMEM_SUM &&
+    // Through the switch a rank receives bytes * (1 + 1/n) (its reduced slice, then every slice, its own included);
+    // the two-shot kernel receives bytes * 2 (n - 1) / n. The switch wins from four members on (measured: 366 us
+    // against 227 us for 128 MiB on two GPUs, level on four, 1.3 x ahead on eight).
+    const bool nvls_ok = ht != nullptr && ht->mc_window != nullptr && n >= 4 && op == ROCSHMEM_SUM &&
                          (std::is_same<T, float>::value || std::is_same<T, __half>::value ||
                           std::is_same<T, __nv_bfloat16>::value);
     const bool ll_ok = (sizeof(T) == 2 || sizeof(T) == 4) && bytes % 4 == 0 && bytes <= size_t(ROCSHMEM_LL_WORDS) * 4 &&

@@ -95,7 +95,11 @@ def gpu_device_suite():
     _ok()
     assert torch.allclose(y.cpu(), torch.arange(5000, dtype=torch.float32) * (n * (n + 1) // 2))
     shm.barrier_all()
+    before = torch.cuda.current_device()
     shm.finalize()
+    # finalize leaves the caller's current device alone (it clears the modules' state on the heap's device only)
+    assert torch.cuda.current_device() == before == dev.index, (before, torch.cuda.current_device(), dev)
+    assert torch.ones(4, device="cuda").device.index == dev.index
 
 
 def gpu_library_collectives():
@@ -167,6 +171,7 @@ def gpu_team_nvls():
     same time (every PE is a member of two of them), run the switch-side allreduce, all-gather and broadcast,
     are destroyed and split again with other members, and one team is still alive at finalize."""
     os.environ["ROCSHMEM_BCAST_NVLS"] = "1"
+    os.environ["ROCSHMEM_FCOLLECT_NVLS"] = "1"
     _init("1G")
     me, n = RANK, WORLD
     dev = shm.device()
