@@ -247,12 +247,14 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         }
         __syncwarp();
       }
-      if constexpr (gemm::has_final_reduce<Epilogue>::value) {
-        if (!final_tile) epi.tile_done(t, lane);
-      }
+      // The accumulator has been read in full: hand it back before the announcement below, whose system-scope fence
+      // waits for the tile's remote stores to drain.
       sm100::tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa(sm100::smem_u32(&sh.tmem_empty[acc]), 0));
+      if constexpr (gemm::has_final_reduce<Epilogue>::value) {
+        if (!final_tile) epi.tile_done(t, lane);
+      }
     }
   }
   // ---- teardown: nobody leaves while the peer may still signal into, or read from, this CTA -------------------

@@ -402,12 +402,14 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
         }
         __syncwarp();
       }
-      if constexpr (has_final_reduce<Epilogue>::value) {
-        if (!final_tile) epi.tile_done(t, lane);
-      }
+      // The accumulator has been read in full: hand it back before the announcement below, whose system-scope fence
+      // waits for the tile's remote stores to drain.
       sm100::tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&sh.tmem_empty[acc]);
+      if constexpr (has_final_reduce<Epilogue>::value) {
+        if (!final_tile) epi.tile_done(t, lane);
+      }
     }
   }
   // ---- teardown ------------------------------------------------------------------------------------------------
