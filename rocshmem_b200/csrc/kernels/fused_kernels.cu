@@ -9,11 +9,13 @@
 // earlier ones, and remote rows cross NVLink once (every CTA then reads them from local HBM / L2).
 //
 // GEMM -> reduce-scatter (gemm_rs_bf16): the GEMM epilogue stores each finished tile straight into the
-// staging buffer of the rank that owns those rows (16-byte peer stores) and bumps that tile's counter on
-// the owner; tiles are ordered so that the ranks write to different owners at any time and a rank's own
-// rows come last. The epilogue of those last tiles waits for the tile's counter, adds the other ranks'
-// staged partials (fp32) to its accumulators and writes the final bf16 rows: there is no grid barrier and
-// no separate reduction pass. (The e4m3 kernel still stores all tiles first and reduces in a second pass.)
+// staging buffer of the rank that owns those rows (16-byte peer stores), tiles ordered so that the ranks
+// write to different owners at any time and a rank's own rows come last. After a grid barrier and a
+// cross-rank barrier every CTA sums its share of the n_ranks staged partials of the local rows in fp32
+// and writes the bf16 result. (A form that added the partials in the epilogue of the owner's tiles, with
+// one arrival counter per tile and no reduction pass, was measured and removed: the owner's tiles are the
+// last 1 / n of the kernel and four epilogue warps per SM cannot pull n - 1 partial tiles fast enough, so
+// the reduce-scatter alone took 541 us against 409 us on eight GPUs.)
 //
 // Nothing here has a counterpart in the reference; the ingredients it offers are fcollect, reduction
 // and put-with-signal (src/ipc/context_ipc_tmpl_device.hpp:166-531).
@@ -321,56 +323,8 @@ struct RsScheduler {
   __device__ void side_role() const {}
 };
 
-// Tiles of rows that another rank owns are stored into that rank's staging slice and announced on the owner's
-// per-tile counter (one release-ordered remote increment per epilogue warp). Tiles of this rank's own rows, which
-// the schedule leaves for last, wait until all other ranks' partials of the tile have been announced, add them
-// (fp32) to the accumulators on their way out and write the final rows: the reduction needs no pass of its own.
+// Tiles go into the owners' staging slices (my own rows into my slice of my own staging buffer).
 struct RsEpilogue {
-  static constexpr bool kFinalReduce = true;
-  const rocshmem_team_dev *team;
-  __nv_bfloat16 *staging;
-  __nv_bfloat16 *out;
-  unsigned int *tile_ready;   // symmetric [row blocks of a shard * column tiles], monotonic over calls
-  unsigned target;            // value of a tile's counter once every other rank has announced it in this call
-  int me, n_ranks, m_shard, n, tile_rows, tiles_n, tile_cols;
-  __device__ int tile_index(const gemm::Tile &t) const { return (t.c_row / tile_rows) * tiles_n + t.c_col / tile_cols; }
-  __device__ bool is_final(const gemm::Tile &t) const { return t.tag == me; }
-  __device__ int n_partials(const gemm::Tile &) const { return n_ranks - 1; }
-  __device__ __nv_bfloat16 *row_ptr(const gemm::Tile &t, int row) const {
-    if (t.tag == me) return out + static_cast<size_t>(t.c_row + row) * n + t.c_col;
-    __nv_bfloat16 *local = staging + (static_cast<size_t>(me) * m_shard + t.c_row + row) * n + t.c_col;
-    return remote_ptr(local, team_pe_to_world(team, t.tag));
-  }
-  // Partial s of my rows: slices of the ranks other than me, in rank order.
-  __device__ const __nv_bfloat16 *partial(const gemm::Tile &t, int s, int row) const {
-    const int slice = s < me ? s : s + 1;
-    return staging + (static_cast<size_t>(slice) * m_shard + t.c_row + row) * n + t.c_col;
-  }
-  __device__ bool wait_partials(const gemm::Tile &t) const {
-    const unsigned int *p = tile_ready + tile_index(t);
-    if (detail::ld_acquire_sys_u32(p) >= target) return true;
-    detail::SpinBudget budget(gemm::WAIT_BUDGET_NS);
-    while (detail::ld_acquire_sys_u32(p) < target) {
-      if (!budget.keep_going()) {
-        detail::record_error(ROCSHMEM_ERR_KERNEL, -1, 82, p, target, *reinterpret_cast<const volatile unsigned int *>(p));
-        return false;
-      }
-    }
-    return true;
-  }
-  // Called by every lane of an epilogue warp after its stores of a tile that another rank owns.
-  __device__ void tile_done(const gemm::Tile &t, int lane) const {
-    __threadfence_system();
-    __syncwarp();
-    if (lane == 0) {
-      unsigned int *flag = remote_ptr(tile_ready + tile_index(t), team_pe_to_world(team, t.tag));
-      asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(flag), "r"(1u) : "memory");
-    }
-  }
-};
-
-// The e4m3 kernel keeps the two-pass form: tiles into the owners' staging slices, then one reduction pass.
-struct RsStageEpilogue {
   const rocshmem_team_dev *team;
   __nv_bfloat16 *staging;
   int me, m_shard, n;
@@ -380,13 +334,7 @@ struct RsStageEpilogue {
   }
 };
 
-// The per-tile counters share the operation's small symmetric control buffer with the grid counter: the first
-// 128 bytes belong to the latter.
-__device__ __forceinline__ unsigned int *rs_tile_flags(const RsArgs &a) {
-  return reinterpret_cast<unsigned int *>(a.grid_counter + 16);
-}
-
-// Second half of the two-pass GEMM -> reduce-scatter, run by every CTA after its tiles are stored.
+// Second half of GEMM -> reduce-scatter, run by every CTA after its tiles are stored.
 __device__ void rs_reduce(const RsArgs &a, const rocshmem_team_dev *t) {
   // All CTAs of this rank have stored their tiles (grid barrier), then all ranks have (block b pairs
   // with block b of every peer, which has itself passed its rank's grid barrier): every partial of
@@ -445,13 +393,9 @@ gemm_rs_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
   sched.tiles = t->size * sched.tiles_per_shard * sched.tiles_n;
   sched.m_shard = a.m_shard;
   sched.n = a.n;
-  // Every other rank announces a tile once per epilogue warp (four per CTA).
-  RsEpilogue epi{t, a.staging, a.out, rs_tile_flags(a), a.epoch * 4u * static_cast<unsigned>(t->size - 1), t->my_pe,
-                 t->size, a.m_shard, a.n, gemm::BM, sched.tiles_n, gemm::BN};
+  RsEpilogue epi{t, a.staging, t->my_pe, a.m_shard, a.n};
   gemm::run<false, false>(&map_a, &map_b, a.k * 2, sched, epi, smem_raw, sh);
-  // The next call stores tiles into the staging slices as soon as it starts: nobody leaves before every rank has
-  // finished reading its staged partials.
-  block_pair_barrier(t, blockIdx.x, false);
+  rs_reduce(a, t);
 }
 
 struct RsPairScheduler {
@@ -491,11 +435,9 @@ gemm_rs_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   sched.tiles = t->size * sched.tiles_per_shard * sched.tiles_n;
   sched.m_shard = a.m_shard;
   sched.n = a.n;
-  // A 256-row tile is announced by the four epilogue warps of both CTAs of the pair.
-  RsEpilogue epi{t, a.staging, a.out, rs_tile_flags(a), a.epoch * 8u * static_cast<unsigned>(t->size - 1), t->my_pe,
-                 t->size, a.m_shard, a.n, 2 * gemm2::BM, sched.tiles_n, gemm2::BN};
+  RsEpilogue epi{t, a.staging, t->my_pe, a.m_shard, a.n};
   gemm2::run<false>(&map_a, &map_b, a.k * 2, sched, epi, smem_raw, sh);
-  block_pair_barrier(t, blockIdx.x, false);
+  rs_reduce(a, t);
 }
 
 // Kernels with two CTAs per tile are used where the shapes allow; ROCSHMEM_GEMM_TWO_CTA=0 selects the
@@ -567,7 +509,7 @@ gemm_rs_fp8_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
   sched.tiles = t->size * sched.tiles_per_shard * sched.tiles_n;
   sched.m_shard = a.m_shard;
   sched.n = a.n;
-  RsStageEpilogue epi{t, a.staging, t->my_pe, a.m_shard, a.n};
+  RsEpilogue epi{t, a.staging, t->my_pe, a.m_shard, a.n};
   gemm8::run<false, false>(&map_a, &map_b, a_scale, b_scale, a.k / gemm8::KB, sched, epi, smem_raw, sh);
   rs_reduce(a, t);
 }

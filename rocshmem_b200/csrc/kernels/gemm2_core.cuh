@@ -196,19 +196,6 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
       sm100::tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       const int row_base = int(rank) * BM;   // my rows inside the pair's tile
-      bool final_tile = false;
-      if constexpr (gemm::has_final_reduce<Epilogue>::value) {
-        final_tile = epi.is_final(t);
-        if (final_tile) {
-          int ok = 1;
-          if (lane == 0) ok = epi.wait_partials(t) ? 1 : 0;
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) {
-            sh.abort_flag = 1;
-            break;
-          }
-        }
-      }
       constexpr int OUT_CHUNKS = (SWIGLU ? BN / 2 : BN) / EPI_COLS;
 #pragma unroll 1
       for (int c = 0; c < OUT_CHUNKS; ++c) {
@@ -239,22 +226,12 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
           }
         }
         __syncwarp();
-        if constexpr (gemm::has_final_reduce<Epilogue>::value) {
-          if (final_tile) gemm::write_out_block<false, true>(t, epi, stg, row_base + quarter * 32, c * EPI_COLS, lane);
-          else gemm::write_out_block<false, false>(t, epi, stg, row_base + quarter * 32, c * EPI_COLS, lane);
-        } else {
-          gemm::write_out_block<false, false>(t, epi, stg, row_base + quarter * 32, c * EPI_COLS, lane);
-        }
+        gemm::write_out_block<false>(t, epi, stg, row_base + quarter * 32, c * EPI_COLS, lane);
         __syncwarp();
       }
-      // The accumulator has been read in full: hand it back before the announcement below, whose system-scope fence
-      // waits for the tile's remote stores to drain.
       sm100::tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(mapa(sm100::smem_u32(&sh.tmem_empty[acc]), 0));
-      if constexpr (gemm::has_final_reduce<Epilogue>::value) {
-        if (!final_tile) epi.tile_done(t, lane);
-      }
     }
   }
   // ---- teardown: nobody leaves while the peer may still signal into, or read from, this CTA -------------------

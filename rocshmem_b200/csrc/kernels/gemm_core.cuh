@@ -82,97 +82,29 @@ struct GatherSrc {
   int nscale;
 };
 
-// An epilogue policy may declare `static constexpr bool kFinalReduce = true` to take part in a reduction across
-// GPUs: tiles for which is_final(t) holds are not stored as they are but summed (fp32) with n_partials(t) staged
-// partial tiles (partial(t, s, row) points at element (row, t.c_col) of partial s) once wait_partials(t) has seen
-// them arrive, and every other tile is announced to its owner with tile_done(t) after its stores.
-template <class E, class = void>
-struct has_final_reduce : std::false_type {};
-template <class E>
-struct has_final_reduce<E, std::void_t<decltype(E::kFinalReduce)>> : std::true_type {};
-
 // Write-out of one warp's staged 32 x 64 bf16 block (padded rows in shared memory), 8 lanes per row, shared by the
-// one-CTA and the two-CTA cores. FINAL: add the staged partials of the other GPUs before storing (two row groups
-// with all their partials' loads in flight at a time).
-template <bool EPI_ADD, bool FINAL, class Epilogue>
+// one-CTA and the two-CTA cores.
+template <bool EPI_ADD, class Epilogue>
 __device__ __forceinline__ void write_out_block(const Tile &t, Epilogue &epi, const unsigned char *stg, int row0,
                                                 int col0, int lane) {
-  constexpr int MAXP = 7;
-#pragma unroll 1
-  for (int it0 = 0; it0 < 8; it0 += 2) {
-    int4 part[2][MAXP];
-    int np = 0;
-    if constexpr (FINAL) np = epi.n_partials(t);
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int r = (it0 + u) * 4 + lane / 8, seg = lane % 8;
-      const int row = row0 + r, col = col0 + seg * 8;
-      const bool full = row < t.rows && col + 8 <= t.cols;
-      if constexpr (FINAL) {
-#pragma unroll
-        for (int s = 0; s < MAXP; ++s) {
-          if (s < np && full) part[u][s] = __ldcg(reinterpret_cast<const int4 *>(epi.partial(t, s, row) + col));
-        }
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int r = (it0 + u) * 4 + lane / 8, seg = lane % 8;
-      const int row = row0 + r, col = col0 + seg * 8;
-      if (row >= t.rows || col >= t.cols) continue;
-      __nv_bfloat16 *out = epi.row_ptr(t, row);
-      if (out == nullptr) continue;
-      const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
-      __nv_bfloat16 *dst = out + col;
-      if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
-        int4 val = *reinterpret_cast<const int4 *>(src);
-        if constexpr (FINAL) {
-          float acc[8];
-          const __nv_bfloat162 *v2 = reinterpret_cast<const __nv_bfloat162 *>(&val);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const float2 f = __bfloat1622float2(v2[i]);
-            acc[2 * i] = f.x;
-            acc[2 * i + 1] = f.y;
-          }
-#pragma unroll
-          for (int s = 0; s < MAXP; ++s) {
-            if (s < np) {
-              const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&part[u][s]);
-#pragma unroll
-              for (int i = 0; i < 4; ++i) {
-                const float2 f = __bfloat1622float2(p2[i]);
-                acc[2 * i] += f.x;
-                acc[2 * i + 1] += f.y;
-              }
-            }
-          }
-          for (int s = MAXP; s < np; ++s) {   // teams of more than eight: the rest one by one
-            const int4 extra = __ldcg(reinterpret_cast<const int4 *>(epi.partial(t, s, row) + col));
-            const __nv_bfloat162 *p2 = reinterpret_cast<const __nv_bfloat162 *>(&extra);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const float2 f = __bfloat1622float2(p2[i]);
-              acc[2 * i] += f.x;
-              acc[2 * i + 1] += f.y;
-            }
-          }
-          __nv_bfloat162 *o2 = reinterpret_cast<__nv_bfloat162 *>(&val);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) o2[i] = __floats2bfloat162_rn(acc[2 * i], acc[2 * i + 1]);
-        }
-        if (EPI_ADD) sm100::red_add_bf16x8(dst, val);
-        else *reinterpret_cast<int4 *>(dst) = val;
-      } else {
-        const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
-        for (int i = 0; i < 8 && col + i < t.cols; ++i) {
-          float v = __bfloat162float(s16[i]);
-          if constexpr (FINAL) {
-            for (int s = 0; s < np; ++s) v += __bfloat162float(epi.partial(t, s, row)[col + i]);
-          }
-          if (EPI_ADD) atomicAdd(dst + i, __float2bfloat16_rn(v));
-          else dst[i] = __float2bfloat16_rn(v);
-        }
+  for (int it = 0; it < 8; ++it) {
+    const int r = it * 4 + lane / 8, seg = lane % 8;
+    const int row = row0 + r, col = col0 + seg * 8;
+    if (row >= t.rows || col >= t.cols) continue;
+    __nv_bfloat16 *out = epi.row_ptr(t, row);
+    if (out == nullptr) continue;
+    const unsigned char *src = stg + r * EPI_ROW_BYTES + seg * 16;
+    __nv_bfloat16 *dst = out + col;
+    if (col + 8 <= t.cols && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+      const int4 val = *reinterpret_cast<const int4 *>(src);
+      if (EPI_ADD) sm100::red_add_bf16x8(dst, val);
+      else *reinterpret_cast<int4 *>(dst) = val;
+    } else {
+      const __nv_bfloat16 *s16 = reinterpret_cast<const __nv_bfloat16 *>(src);
+      for (int i = 0; i < 8 && col + i < t.cols; ++i) {
+        if (EPI_ADD) atomicAdd(dst + i, s16[i]);
+        else dst[i] = s16[i];
       }
     }
   }
@@ -346,19 +278,6 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
       sm100::tcgen05_fence_after();
       const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + acc * BN;
       constexpr int OUT_CHUNKS = (SWIGLU ? BN / 2 : BN) / EPI_COLS;
-      bool final_tile = false;
-      if constexpr (has_final_reduce<Epilogue>::value) {
-        final_tile = epi.is_final(t);
-        if (final_tile) {
-          int ok = 1;
-          if (lane == 0) ok = epi.wait_partials(t) ? 1 : 0;
-          ok = __shfl_sync(0xffffffffu, ok, 0);
-          if (!ok) {
-            sh.abort_flag = 1;
-            break;
-          }
-        }
-      }
       float row_scale = 1.f;
       if constexpr (EPI_ADD) row_scale = (quarter * 32 + lane) < t.rows ? epi.row_scale(t, quarter * 32 + lane) : 0.f;
 #pragma unroll 1
@@ -394,22 +313,12 @@ __device__ __forceinline__ void run(const CUtensorMap *map_a, const CUtensorMap 
           }
         }
         __syncwarp();
-        if constexpr (has_final_reduce<Epilogue>::value) {
-          if (final_tile) write_out_block<EPI_ADD, true>(t, epi, stg, quarter * 32, c * EPI_COLS, lane);
-          else write_out_block<EPI_ADD, false>(t, epi, stg, quarter * 32, c * EPI_COLS, lane);
-        } else {
-          write_out_block<EPI_ADD, false>(t, epi, stg, quarter * 32, c * EPI_COLS, lane);
-        }
+        write_out_block<EPI_ADD>(t, epi, stg, quarter * 32, c * EPI_COLS, lane);
         __syncwarp();
       }
-      // The accumulator has been read in full: hand it back before the announcement below, whose system-scope fence
-      // waits for the tile's remote stores to drain.
       sm100::tcgen05_fence_before();
       __syncwarp();
       if (lane == 0) sm100::mbar_arrive(&sh.tmem_empty[acc]);
-      if constexpr (has_final_reduce<Epilogue>::value) {
-        if (!final_tile) epi.tile_done(t, lane);
-      }
     }
   }
   // ---- teardown ------------------------------------------------------------------------------------------------

@@ -227,10 +227,8 @@ class TensorParallelLinear:
         if a.shape[0] != self.n_ranks * self.m_shard or a.shape[1] != K:
             raise ValueError("gemm_rs: a must be [n_ranks * m_shard, K_local]")
         if N not in self._rs:
-            # control words: 16 for the grid counter, then one 32-bit arrival counter per (row block, column tile)
-            tiles = (self.m_shard // 128) * ((N + 255) // 256)
-            self._rs[N] = [rt.zeros((self.n_ranks, self.m_shard, N), torch.bfloat16),
-                           rt.zeros(16 + (tiles + 1) // 2 + 1, torch.int64), 0]
+            # staging slices of every rank's partial of my rows, and the grid counter's 128 bytes
+            self._rs[N] = [rt.zeros((self.n_ranks, self.m_shard, N), torch.bfloat16), rt.zeros(16, torch.int64), 0]
         entry = self._rs[N]
         staging, counter = entry[0], entry[1]
         entry[2] += 1
@@ -379,10 +377,8 @@ class TensorParallelLinearFp8:
         if a_q.shape[0] != self.n_ranks * self.m_shard or a_q.shape[1] != K:
             raise ValueError("gemm_rs: a must be [n_ranks * m_shard, K_local]")
         if N not in self._rs:
-            # control words: 16 for the grid counter, then one 32-bit arrival counter per (row block, column tile)
-            tiles = (self.m_shard // 128) * ((N + 255) // 256)
-            self._rs[N] = [rt.zeros((self.n_ranks, self.m_shard, N), torch.bfloat16),
-                           rt.zeros(16 + (tiles + 1) // 2 + 1, torch.int64), 0]
+            # staging slices of every rank's partial of my rows, and the grid counter's 128 bytes
+            self._rs[N] = [rt.zeros((self.n_ranks, self.m_shard, N), torch.bfloat16), rt.zeros(16, torch.int64), 0]
         entry = self._rs[N]
         entry[2] += 1
         if out is None:
