@@ -7,10 +7,20 @@
 
 ``-a`` selects the test by name, or by the reference's number (tests/functional_tests/tester.hpp:36-96) where
 the test has a timed form here:
-put, get (block-scope RMA from PE 0 to PE 1, timed on the device), amo_fadd / amo_finc / amo_fcswap / amo_add
-(int64 atomics on PE 0 from every PE), pingpong (signal round trips), barrier (device barrier_all), and the
-library collectives allreduce, broadcast, fcollect, alltoall (timed with CUDA events on the host, maximum over
-PEs). Message sizes double from ``-m`` to ``-s``; every row prints the columns of the reference's harness
+
+* put, get: block-scope RMA from PE 0 to PE 1, timed on the device;
+* put_thread / put_nbi_thread / get_thread / get_nbi_thread / p / g, the same with ``_wave`` and ``_wg``, and
+  ``ctx_`` + any of them for a context created inside the kernel: every PE moves the message to its right-hand
+  neighbour with one call per thread, warp or block (a kernel per call, timed with CUDA events, so the figure
+  includes the launch and the closing barrier);
+* amo_fadd, amo_finc, amo_fetch, amo_fcswap, amo_cswap, amo_add, amo_inc, amo_set, amo_swap, amo_fetch_and /
+  _or / _xor, amo_and / _or / _xor: int64 atomics on PE 0 from every thread of every PE;
+* put_signal, put_signal_wave, put_signal_wg (and their ``_nbi`` numbers), signal_fetch: a message with a signal
+  to the right-hand neighbour, a wait for the own signal and a ``signal_fetch``;
+* pingpong (signal round trips), pingall (the wait_until_all / any / some family), barrier, sync (device barriers);
+* the library collectives allreduce, broadcast, fcollect, alltoall (timed with CUDA events, maximum over PEs).
+
+Message sizes double from ``-m`` to ``-s``; every row prints the columns of the reference's harness
 (tests/functional_tests/tester.cpp:488-531): size in bytes, timed messages, latency in microseconds,
 bandwidth in GB/s (10^9 bytes) and message rate.
 """
@@ -28,15 +38,42 @@ import rocshmem_b200 as shm  # noqa: E402
 from rocshmem_b200 import _native  # noqa: E402
 from rocshmem_b200.ops import collectives as coll  # noqa: E402
 
-AMO = {"amo_fadd": 0, "amo_finc": 1, "amo_add": 2, "amo_fcswap": 4}
+AMO = {"amo_fadd": 0, "amo_finc": 1, "amo_add": 2, "amo_inc": 3, "amo_fcswap": 4, "amo_cswap": 4, "amo_fetch": 5,
+       "amo_set": 6, "amo_swap": 7, "amo_fetch_and": 8, "amo_and": 9, "amo_fetch_or": 10, "amo_or": 11,
+       "amo_fetch_xor": 12, "amo_xor": 13}
+
+# rma_kernel of the test module: operation and scope codes
+RMA_OPS = {"put": 0, "put_nbi": 1, "get": 2, "get_nbi": 3, "p": 4, "g": 5}
+RMA_SCOPES = {"thread": 0, "wave": 1, "wg": 2}
+
+
+def rma_form(name: str):
+    """(operation, scope, use_ctx) for names like put_nbi_wave, ctx_get_thread, p; None for other tests."""
+    use_ctx = name.startswith("ctx_")
+    base = name[4:] if use_ctx else name
+    if base in ("p", "g"):
+        return RMA_OPS[base], 0, int(use_ctx)
+    op, _, scope = base.rpartition("_")
+    if op in RMA_OPS and op not in ("p", "g") and scope in RMA_SCOPES:
+        return RMA_OPS[op], RMA_SCOPES[scope], int(use_ctx)
+    return None
+
+
+SIGNAL_SCOPES = {"put_signal": 0, "put_signal_wave": 1, "put_signal_wg": 2, "signal_fetch": 0}
 
 # The reference selects tests by number (enum TestType, tests/functional_tests/tester.hpp:36-96). Numbers whose test
 # has a timed form here map to its name; the functional content of all of them is covered by the pytest suite
 # (tests/test_gpu_device_api.py), which is where the others point.
 REFERENCE_NUMBERS = {
-    0: "get", 1: "get", 2: "put", 3: "put", 5: "amo_fadd", 6: "amo_finc", 8: "amo_fcswap", 9: "amo_add",
-    13: "pingpong", 15: "barrier", 16: "barrier", 19: "fcollect", 20: "alltoall", 25: "get", 26: "get", 27: "put",
-    28: "put", 33: "broadcast", 34: "allreduce",
+    0: "get_thread", 1: "get_nbi_thread", 2: "put_thread", 3: "put_nbi_thread", 5: "amo_fadd", 6: "amo_finc",
+    7: "amo_fetch", 8: "amo_fcswap", 9: "amo_add", 10: "amo_inc", 11: "amo_cswap", 13: "pingpong", 15: "barrier",
+    16: "barrier", 17: "barrier", 19: "fcollect", 20: "alltoall", 23: "p", 24: "g", 25: "get_wg", 26: "get_nbi_wg",
+    27: "put_wg", 28: "put_nbi_wg", 29: "get_wave", 30: "get_nbi_wave", 31: "put_wave", 32: "put_nbi_wave",
+    33: "broadcast", 34: "allreduce", 35: "ctx_get_thread", 36: "ctx_get_nbi_thread", 37: "ctx_put_thread",
+    38: "ctx_put_nbi_thread", 41: "amo_set", 42: "amo_swap", 43: "amo_fetch_and", 44: "amo_fetch_or",
+    45: "amo_fetch_xor", 46: "amo_and", 47: "amo_or", 48: "amo_xor", 49: "pingall", 50: "put_signal",
+    51: "put_signal_wg", 52: "put_signal_wave", 53: "put_signal", 54: "put_signal_wg", 55: "put_signal_wave",
+    56: "signal_fetch", 57: "signal_fetch", 58: "signal_fetch",
 }
 REFERENCE_NAMES = [
     "Get", "GetNBI", "Put", "PutNBI", "GetSwarm", "AMO_FAdd", "AMO_FInc", "AMO_Fetch", "AMO_FCswap", "AMO_Add", "AMO_Inc",
@@ -133,6 +170,36 @@ def main() -> int:
                                       stream), 1, 1)
         if not quiet:
             row(8, args.loop * args.blocks * args.threads, us)
+    elif rma_form(args.test) is not None:
+        if n < 2:
+            raise SystemExit("RMA tests need at least two PEs")
+        op, scope, use_ctx = rma_form(args.test)
+        src, dst = shm.zeros(args.max_bytes, torch.uint8), shm.zeros(args.max_bytes, torch.uint8)
+        for size in sizes:
+            size = max(size, 8 * args.threads) if op >= 4 else size       # p / g move 8-byte elements
+            us = event_time(lambda: k.rma(op, scope, dst.data_ptr(), src.data_ptr(), size, 1, use_ctx, args.threads, stream),
+                            args.loop, args.skip)
+            if not quiet:
+                row(size, args.loop, us)
+    elif args.test in SIGNAL_SCOPES:
+        if n < 2:
+            raise SystemExit("signal tests need at least two PEs")
+        src, dst = shm.zeros(args.max_bytes, torch.uint8), shm.zeros(args.max_bytes, torch.uint8)
+        sig, fetched = shm.zeros(1, torch.int64), shm.zeros(2, torch.int64)
+        scope = SIGNAL_SCOPES[args.test]
+        for size in sizes:
+            size = max(size, args.threads)        # a thread's share is size / threads bytes
+            # SET of 1 with a wait for 1: every launch after the first finds the signal already there, so the
+            # figure is the cost of the message, the signal, the check and the closing barrier
+            us = event_time(lambda: k.signal(scope, 0, dst.data_ptr(), src.data_ptr(), size, sig.data_ptr(), 1, 1,
+                                             fetched.data_ptr(), args.threads, stream), args.loop, args.skip)
+            if not quiet:
+                row(size, args.loop, us)
+    elif args.test == "pingall":
+        slots, result = shm.zeros(max(n, 8), torch.int64), shm.zeros(8, torch.int64)
+        us = event_time(lambda: k.pingall(slots.data_ptr(), result.data_ptr(), stream), args.loop, args.skip)
+        if not quiet:
+            row(8, args.loop * n, us)
     elif args.test == "pingpong":
         flag, ns = shm.zeros(1, torch.int32), shm.zeros(1, torch.int64)
         iters = args.loop * 100

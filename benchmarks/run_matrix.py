@@ -33,7 +33,14 @@ MATRIX: List[Tuple[str, int, int, int]] = (
                                           (74, 512, 1 << 26), (128, 1024, 1 << 26))]
     + [(name, b, t, 8) for name in ("amo_fadd", "amo_finc", "amo_add", "amo_fcswap")
        for (b, t) in ((1, 1), (1, 64), (8, 128), (64, 256))]
-    + [("pingpong", 1, 32, 4), ("barrier", 1, 64, 0), ("barrier", 1, 1024, 0)]
+    # one call per thread / warp / block of one block (the reference's launch shapes of its single-work-group runs)
+    + [(f"{op}_{scope}", 1, t, 1 << 20) for op in ("put", "put_nbi", "get", "get_nbi") for scope in ("thread", "wave", "wg")
+       for t in (64, 1024)]
+    + [(name, 1, 256, 1 << 16) for name in ("p", "g", "ctx_put_thread", "ctx_get_thread")]
+    + [(name, 8, 128, 8) for name in ("amo_fetch", "amo_inc", "amo_set", "amo_swap", "amo_fetch_and", "amo_fetch_or",
+                                      "amo_fetch_xor", "amo_and", "amo_or", "amo_xor")]
+    + [(name, 1, 256, 1 << 20) for name in ("put_signal", "put_signal_wave", "put_signal_wg")]
+    + [("pingpong", 1, 32, 4), ("pingall", 1, 32, 8), ("barrier", 1, 64, 0), ("barrier", 1, 1024, 0)]
     + [(name, 1, 512, 1 << 26) for name in ("allreduce", "broadcast", "fcollect", "alltoall")]
 )
 

@@ -55,7 +55,9 @@ def test_python_example(script, tmp_path):
     run(cmd if world > 1 else [sys.executable] + cmd, world, tmp_path)
 
 
-@pytest.mark.parametrize("test", ["put", "get", "amo_fadd", "pingpong", "barrier", "allreduce", "broadcast", "alltoall"])
+@pytest.mark.parametrize("test", ["put", "get", "amo_fadd", "pingpong", "barrier", "allreduce", "broadcast", "alltoall",
+                                  # per-scope forms, selected as the reference does, by number or by name
+                                  "31", "ctx_get_thread", "amo_swap", "put_signal_wg", "pingall"])
 def test_functional_driver(test, tmp_path):
     """The command-line performance driver prints one table row per message size (two PEs on one GPU)."""
     cmd = [sys.executable, os.path.join(ROOT, "benchmarks", "functional_driver.py"), "-a", test, "-s", "65536", "-m", "4096",

@@ -101,8 +101,15 @@ def test_functional_driver_accepts_the_reference_test_numbers():
     fd = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(fd)
     assert len(fd.REFERENCE_NAMES) == 59 and fd.REFERENCE_NAMES[58] == "WAVESignalFetch"
-    assert fd.resolve_test("put") == "put" and fd.resolve_test("2") == "put" and fd.resolve_test("34") == "allreduce"
-    assert fd.resolve_test("13") == "pingpong" and fd.resolve_test("0") == "get"
+    assert fd.resolve_test("put") == "put" and fd.resolve_test("2") == "put_thread" and fd.resolve_test("34") == "allreduce"
+    assert fd.resolve_test("13") == "pingpong" and fd.resolve_test("0") == "get_thread" and fd.resolve_test("31") == "put_wave"
+    # names of the per-scope forms: operation, scope and "context created in the kernel"
+    assert fd.rma_form("put_nbi_wave") == (1, 1, 0) and fd.rma_form("ctx_get_thread") == (2, 0, 1)
+    assert fd.rma_form("g") == (5, 0, 0) and fd.rma_form("put") is None and fd.rma_form("allreduce") is None
+    assert all(name in fd.AMO or name in fd.SIGNAL_SCOPES or fd.rma_form(name) is not None or
+               name in ("pingpong", "pingall", "barrier", "allreduce", "broadcast", "fcollect", "alltoall")
+               for name in fd.REFERENCE_NUMBERS.values())
+    assert len(fd.REFERENCE_NUMBERS) >= 50
     with pytest.raises(SystemExit, match="RandomAccessTestType"):
         fd.resolve_test("14")
     with pytest.raises(SystemExit, match="0 to 58"):
