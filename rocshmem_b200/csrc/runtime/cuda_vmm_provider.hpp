@@ -71,12 +71,12 @@ class CudaVmmProvider final : public MemProvider {
   // NVLS: one multicast object spanning `n_devices` GPUs. The creator exports a descriptor; every
   // participant adds its device, then (after all devices were added) binds its allocation and maps
   // the object. All calls return false with *why set when the platform refuses.
-  bool mc_create(size_t bytes, int n_devices, MemHandle *out, std::string *why);
-  bool mc_import(int fd, size_t bytes, MemHandle *out, std::string *why);
-  bool mc_add_device(const MemHandle &mc, std::string *why);
-  bool mc_bind_and_map(const MemHandle &mc, const MemHandle &mem, char *va, std::string *why);
-  void mc_unbind(const MemHandle &mc, size_t bytes);
-  size_t mc_granularity(size_t bytes, int n_devices) const;
+  bool mc_create(size_t bytes, int n_devices, MemHandle *out, std::string *why) override;
+  bool mc_import(int fd, size_t bytes, MemHandle *out, std::string *why) override;
+  bool mc_add_device(const MemHandle &mc, std::string *why) override;
+  bool mc_bind_and_map(const MemHandle &mc, const MemHandle &mem, char *va, std::string *why) override;
+  void mc_unbind(const MemHandle &mc, size_t bytes) override;
+  size_t mc_granularity(size_t bytes, int n_devices) const override;
 
  private:
   int device_;

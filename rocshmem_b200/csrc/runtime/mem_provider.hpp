@@ -51,8 +51,23 @@ class MemProvider {
   virtual void read(void *dst, const void *src, size_t bytes) = 0;
   virtual void zero(void *dst, size_t bytes) = 0;
 
-  // NVLS. Returns false when multicast is unsupported; never throws for "not available".
+  // NVLS: one multicast object spanning `n_devices` members. The creator exports a descriptor; every participant
+  // adds its device, then (after all devices were added) binds its allocation and maps the object at `va`. The
+  // calls return false (with *why set) when the platform refuses or has no such thing; they never throw for "not
+  // available". The host provider offers a stand-in for tests (see host_shm_provider.cpp).
   virtual bool multicast_supported() const { return false; }
+  virtual size_t mc_granularity(size_t, int) const { return 0; }
+  virtual bool mc_create(size_t, int, MemHandle *, std::string *why) { return unsupported(why); }
+  virtual bool mc_import(int, size_t, MemHandle *, std::string *why) { return unsupported(why); }
+  virtual bool mc_add_device(const MemHandle &, std::string *why) { return unsupported(why); }
+  virtual bool mc_bind_and_map(const MemHandle &, const MemHandle &, char *, std::string *why) { return unsupported(why); }
+  virtual void mc_unbind(const MemHandle &, size_t) {}
+
+ protected:
+  static bool unsupported(std::string *why) {
+    if (why) *why = "multicast not supported by this memory provider";
+    return false;
+  }
 };
 
 std::unique_ptr<MemProvider> make_host_shm_provider();

@@ -172,7 +172,7 @@ void Runtime::init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local
   slots_ = std::make_unique<TeamSlots>(cfg_.max_teams);
   host_stats_ = new std::vector<std::atomic<unsigned long long>>(ROCSHMEM_NUM_STATS);
 
-  if (mem_->is_cuda() && cfg_.enable_nvls && multi_process && n_local_ == 1) setup_nvls();
+  if ((mem_->is_cuda() || mem_->multicast_supported()) && cfg_.enable_nvls && multi_process && n_local_ == 1) setup_nvls();
 
   build_states();
 
@@ -223,8 +223,8 @@ void Runtime::init(std::unique_ptr<Bootstrap> bs, const Config &cfg, int n_local
 }
 
 void Runtime::setup_nvls() {
-  auto *cu = dynamic_cast<CudaVmmProvider *>(mem_.get());
-  if (!cu || !cu->multicast_supported()) {
+  MemProvider *cu = mem_.get();
+  if (!cu->multicast_supported()) {
     if (cfg_.debug) std::fprintf(stderr, "[rocshmem pe %d] NVLS: not supported, P2P only\n", first_pe_);
     return;
   }
@@ -282,8 +282,8 @@ void Runtime::setup_nvls() {
 // A multicast object of its own for a split team (one PE per process): the same steps as for the world object,
 // agreed on among the team's processes only. Any failure leaves the team without a mapping on every member.
 void Runtime::setup_team_nvls(HostTeam *t, const std::string &tag) {
-  auto *cu = dynamic_cast<CudaVmmProvider *>(mem_.get());
-  if (!cu || !mc_bound_ || !cfg_.team_nvls || n_local_ != 1) return;
+  MemProvider *cu = mem_.get();
+  if (!mc_bound_ || !cfg_.team_nvls || n_local_ != 1) return;
   const int n = static_cast<int>(t->procs.size());
   if (n < 2) return;
   if (n == n_pes_) {  // the same members as the world team
@@ -362,8 +362,8 @@ void Runtime::setup_team_nvls(HostTeam *t, const std::string &tag) {
 }
 
 void Runtime::release_team_nvls(HostTeam *t) {
-  auto *cu = dynamic_cast<CudaVmmProvider *>(mem_.get());
-  if (cu && t->mc_owned) {
+  MemProvider *cu = mem_.get();
+  if (t->mc_owned) {
     cu->unmap(t->mc_window, stride_);
     cu->mc_unbind(t->mc_handle, stride_);
     cu->release(t->mc_window, stride_);
@@ -487,13 +487,10 @@ void Runtime::finalize() {
   world_team_ = nullptr;
   ops_.reset();
   if (mc_bound_) {
-    auto *cu = dynamic_cast<CudaVmmProvider *>(mem_.get());
-    if (cu) {
-      cu->unmap(mc_window_, stride_);
-      cu->mc_unbind(mc_handle_, stride_);
-      cu->release(mc_window_, stride_);
-      cu->destroy(mc_handle_);
-    }
+    mem_->unmap(mc_window_, stride_);
+    mem_->mc_unbind(mc_handle_, stride_);
+    mem_->release(mc_window_, stride_);
+    mem_->destroy(mc_handle_);
     mc_bound_ = false;
     mc_window_ = nullptr;
   }

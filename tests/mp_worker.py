@@ -140,6 +140,56 @@ def teams():
     shm.finalize()
 
 
+def team_multicast_standin():
+    """Set-up and tear-down of the world's and of split teams' multicast objects, with the host provider's stand-in for
+    the NVLink object: every member ends with a mapping, or (when one member's step fails) nobody does; destroying
+    such a team is collective; a slot is reused; teams are still alive at finalize. The failing step comes from the
+    environment of one rank (ROCSHMEM_HOST_FAKE_MULTICAST_FAIL, set by the test)."""
+    if os.environ.get("FAKE_MC_FAIL_RANK") == str(RANK):
+        os.environ["ROCSHMEM_HOST_FAKE_MULTICAST_FAIL"] = os.environ["FAKE_MC_FAIL_SPEC"]
+    init("16M")
+    me, n = shm.my_pe(), shm.n_pes()
+    world = shm.team_world()
+    spec = os.environ.get("EXPECT_MULTICAST", "")      # "world,lower,upper,even" : which objects must exist
+    expect = set(spec.split(",")) if spec else set()
+    assert shm.nvls_available() == ("world" in expect), (shm.nvls_available(), expect)
+    assert world.has_nvls() == ("world" in expect)
+    half = n // 2
+    src, dst = shm.zeros(64, torch.int64), shm.zeros(64, torch.int64)
+    src.fill_(me + 1)
+    shm.barrier_all()
+    lower = world.split_strided(0, 1, half)
+    upper = world.split_strided(half, 1, n - half)
+    even = world.split_strided(0, 2, (n + 1) // 2)
+    for name, t, members in (("lower", lower, list(range(half))), ("upper", upper, list(range(half, n))),
+                             ("even", even, list(range(0, n, 2)))):
+        assert t.valid == (me in members), name
+        if not t.valid:
+            continue
+        want = name in expect and len(members) >= 2
+        assert t.has_nvls() == want, (name, t.has_nvls(), want)
+        # the team works either way
+        assert coll.reduce(dst, src, shm.OP_SUM, t) == 0
+        assert int(dst.cpu()[0]) == sum(p + 1 for p in members), name
+    shm.barrier_all()
+    # destroy (collective for teams with an object) and split again into the freed slots, with other members
+    for t in (lower, upper, even):
+        if t.valid:
+            t.destroy()
+    shm.barrier_all()
+    if n >= 3:
+        rest = world.split_strided(1, 1, n - 1)
+        if me >= 1:
+            assert rest.valid and rest.has_nvls() == ("rest" in expect), (rest.has_nvls(), expect)
+            assert coll.reduce(dst, src, shm.OP_MAX, rest) == 0 and int(dst.cpu()[5]) == n
+        else:
+            assert not rest.valid
+    dup = world.split_strided(0, 1, n)          # same members as the world: shares the world's mapping
+    assert dup.valid and dup.has_nvls() == ("world" in expect)
+    shm.barrier_all()
+    shm.finalize()     # "rest" and "dup" are still alive
+
+
 def collectives_host():
     init("64M")
     me, npes = shm.my_pe(), shm.n_pes()
@@ -1042,7 +1092,7 @@ def elastic_grow():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (elastic_grow, reduce_scatter_host, elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, collectives_host, wait_and_signal,
+SCENARIOS = {f.__name__: f for f in (elastic_grow, reduce_scatter_host, elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, team_multicast_standin, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

@@ -18,6 +18,25 @@ def test_teams_split_translate_capacity():
     assert_all_ok(run_ranks("teams", 4))
 
 
+@pytest.mark.parametrize("fail,expect", [
+    (None, "world,lower,upper,even,rest"),
+    # the world object fails on one rank: nobody has a mapping, and no team tries for one
+    ((2, "bind:0"), ""),
+    # rank 2's third object is the even team {0, 2}: both of its members go without, the other teams are untouched
+    ((2, "add:2"), "world,lower,upper,rest"),
+    # rank 0 creates the lower team's object (its second); rank 3 imports the upper team's
+    ((0, "create:1"), "world,upper,even,rest"),
+    ((3, "import:1"), "world,lower,even,rest"),
+])
+def test_multicast_objects_of_world_and_split_teams_are_all_or_nothing(fail, expect):
+    """The host provider's stand-in for the NVLink multicast object: creation on the first member, descriptor to the
+    others, agreement after every step, tear-down at destroy and finalize, as four real processes."""
+    env = {"ROCSHMEM_HOST_FAKE_MULTICAST": "1", "EXPECT_MULTICAST": expect}
+    if fail is not None:
+        env.update(FAKE_MC_FAIL_RANK=fail[0], FAKE_MC_FAIL_SPEC=fail[1])
+    assert_all_ok(run_ranks("team_multicast_standin", 4, env_extra=env))
+
+
 @pytest.mark.parametrize("world", [2, 3])
 def test_host_collectives(world):
     assert_all_ok(run_ranks("collectives_host", world))
