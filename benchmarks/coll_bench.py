@@ -135,7 +135,7 @@ def main():
                          "auto": shm.ALLREDUCE_AUTO}
                 if nbytes <= 2048:
                     algos["ll"] = shm.ALLREDUCE_LL
-                if shm.nvls_available() and tsize == world:
+                if member and team.has_nvls():      # the world team's mapping, or a split team's own object
                     algos["nvls"] = shm.ALLREDUCE_NVLS
                 for name, algo in algos.items():
                     if name == "one_shot" and nbytes > (8 << 20):
