@@ -141,6 +141,28 @@ def all_names() -> List[str]:
     return out
 
 
+# Host-callable launchers of the library kernels with the limits their validators enforce.
+LIBRARY_LAUNCHERS = [
+    ("kernels.hpp", ["coll_barrier", "coll_allreduce", "coll_broadcast", "coll_fcollect", "coll_alltoall", "coll_preload",
+                     "coll_blocks_for", "nvls_available", "host_amo"],
+     "symmetric buffers; allreduce: `ALLREDUCE_LL` up to 2 KiB of 2- or 4-byte elements, `ALLREDUCE_NVLS` sum of fp32 / "
+     "fp16 / bf16 on teams with a multicast mapping, 16-byte aligned"),
+    ("ep_kernels.hpp", ["ep_dispatch", "ep_combine", "ep_combine_fetches", "ep_expert_layout", "ep_default_blocks",
+                        "fp8_quantize_1x128", "fp8_dequantize_1x128"],
+     "teams of at most 32 ranks (`EP_MAX_RANKS`; a destination rank is a lane of a warp), hidden a multiple of 512, at "
+     "most 1024 experts and divisible by the team size, top-k at most `EP_MAX_TOPK`, low-latency mode needs the "
+     "slotted layout"),
+    ("gemm_kernels.hpp", ["gemm_bf16", "gemm_bf16_one_cta", "gemm_bf16_pair", "grouped_gemm_bf16",
+                          "grouped_gemm_bf16_gathered", "grouped_gemm_bf16_scatter_add", "gemm_fp8_blockscaled",
+                          "grouped_gemm_fp8_blockscaled", "grouped_gemm_fp8_swiglu_quant", "grouped_gemm_fp8_scatter_add",
+                          "ag_gemm_bf16", "gemm_rs_bf16", "ag_gemm_fp8", "gemm_rs_fp8", "gemm_error_count"],
+     "row-major operands, 16-byte aligned; bf16: K a multiple of 8 (64 with gathered rows); e4m3: K a multiple of 512, "
+     "N of 128 (256 with SwiGLU); fused kernels: shard rows a multiple of 128"),
+    ("moe_kernels.hpp", ["moe_gather_rows", "moe_zero_rows"], "hidden a multiple of 8 (512 for e4m3 rows)"),
+    ("no_alloc.h", ["rocshmem_b200_expert_layout_noalloc"], "at most 1024 experts per rank; calls must not overlap on a GPU"),
+]
+
+
 def markdown() -> str:
     lines = ["# API listing", "",
              "Generated by `python -m rocshmem_b200.utils.gen_api --markdown`; every name is declared by",
@@ -153,6 +175,12 @@ def markdown() -> str:
     lines += [f"## extensions ({len(ext)} functions, not part of the count above; described in `GUIDE.md`)", "", "```"]
     lines += sorted(ext)
     lines += ["```", ""]
+    lines += ["## library kernels (host-callable launchers, `rocshmem::kernels`, not part of the count above)", "",
+              "Stream-ordered launchers of `rocshmem_b200/csrc/kernels/*.hpp`; the Python layer (`docs/PYTHON_API.md`) wraps",
+              "every one of them. All return 0 or a CUDA error code.", "",
+              "| Header | Launchers | Limits |", "|---|---|---|"]
+    lines += [f"| `{h}` | {', '.join(f'`{n}`' for n in names)} | {limits} |" for h, names, limits in LIBRARY_LAUNCHERS]
+    lines += [""]
     return "\n".join(lines)
 
 
