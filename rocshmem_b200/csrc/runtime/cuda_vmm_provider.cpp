@@ -229,6 +229,11 @@ void CudaVmmProvider::read(void *dst, const void *src, size_t bytes) {
   check_rt(cudaMemcpy(dst, src, bytes, cudaMemcpyDefault), "cudaMemcpy from heap");
 }
 
+void CudaVmmProvider::sync_device() {
+  OnDevice on(device_);
+  check_rt(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+}
+
 void CudaVmmProvider::zero(void *dst, size_t bytes) {
   OnDevice on(device_);
   check_rt(cudaMemset(dst, 0, bytes), "cudaMemset");

@@ -64,6 +64,7 @@ class CudaVmmProvider final : public MemProvider {
   void write(void *dst, const void *src, size_t bytes) override;
   void read(void *dst, const void *src, size_t bytes) override;
   void zero(void *dst, size_t bytes) override;
+  void sync_device() override;
   bool multicast_supported() const override { return multicast_; }
 
   int device() const { return device_; }

@@ -50,6 +50,8 @@ class MemProvider {
   virtual void write(void *dst, const void *src, size_t bytes) = 0;
   virtual void read(void *dst, const void *src, size_t bytes) = 0;
   virtual void zero(void *dst, size_t bytes) = 0;
+  // Returns when all work queued on the provider's device so far has finished (nothing to wait for on the host).
+  virtual void sync_device() {}
 
   // NVLS: one multicast object spanning `n_devices` members. The creator exports a descriptor; every participant
   // adds its device, then (after all devices were added) binds its allocation and maps the object at `va`. The

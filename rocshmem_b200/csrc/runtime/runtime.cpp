@@ -453,6 +453,7 @@ void Runtime::finalize() {
   // Everybody stops using peers' memory before anything is unmapped.
   try {
     ops_->quiet(default_ctx_);
+    mem_->sync_device();   // kernels queued on the caller's own streams may still use peers' memory
     bs_->barrier("finalize");
   } catch (const std::exception &e) {
     std::fprintf(stderr, "[rocshmem pe %d] finalize: %s\n", first_pe_, e.what());
@@ -676,7 +677,7 @@ void Runtime::team_destroy(HostTeam *t) {
     // every member finishes its own work, then all of them meet, then the mapping goes. (OpenSHMEM makes
     // team_destroy collective; for teams without a multicast object nothing is exchanged here.)
     try {
-      ops_->quiet(default_ctx_);
+      mem_->sync_device();   // collectives on the team may have been queued on any stream
       char one = 1;
       std::vector<char> all(t->procs.size());
       bs_->allgather_group("team-destroy/" + std::to_string(t->id), t->procs, t->my_proc, &one, all.data(), 1);
