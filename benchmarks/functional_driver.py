@@ -17,7 +17,8 @@ the test has a timed form here:
   _or / _xor, amo_and / _or / _xor: int64 atomics on PE 0 from every thread of every PE;
 * put_signal, put_signal_wave, put_signal_wg (and their ``_nbi`` numbers), signal_fetch: a message with a signal
   to the right-hand neighbour, a wait for the own signal and a ``signal_fetch``;
-* pingpong (signal round trips), pingall (the wait_until_all / any / some family), barrier, sync (device barriers);
+* pingpong (signal round trips), pingall (the wait_until_all / any / some family), barrier, sync (device barriers),
+  shmem_ptr (a store through ``rocshmem_ptr`` of the neighbour), ctx_infra (creating and destroying ten contexts);
 * the library collectives allreduce, broadcast, fcollect, alltoall (timed with CUDA events, maximum over PEs).
 
 Message sizes double from ``-m`` to ``-s``; every row prints the columns of the reference's harness
@@ -67,10 +68,10 @@ SIGNAL_SCOPES = {"put_signal": 0, "put_signal_wave": 1, "put_signal_wg": 2, "sig
 REFERENCE_NUMBERS = {
     0: "get_thread", 1: "get_nbi_thread", 2: "put_thread", 3: "put_nbi_thread", 5: "amo_fadd", 6: "amo_finc",
     7: "amo_fetch", 8: "amo_fcswap", 9: "amo_add", 10: "amo_inc", 11: "amo_cswap", 13: "pingpong", 15: "barrier",
-    16: "barrier", 17: "barrier", 19: "fcollect", 20: "alltoall", 23: "p", 24: "g", 25: "get_wg", 26: "get_nbi_wg",
+    16: "barrier", 17: "barrier", 19: "fcollect", 20: "alltoall", 22: "shmem_ptr", 23: "p", 24: "g", 25: "get_wg", 26: "get_nbi_wg",
     27: "put_wg", 28: "put_nbi_wg", 29: "get_wave", 30: "get_nbi_wave", 31: "put_wave", 32: "put_nbi_wave",
     33: "broadcast", 34: "allreduce", 35: "ctx_get_thread", 36: "ctx_get_nbi_thread", 37: "ctx_put_thread",
-    38: "ctx_put_nbi_thread", 41: "amo_set", 42: "amo_swap", 43: "amo_fetch_and", 44: "amo_fetch_or",
+    38: "ctx_put_nbi_thread", 39: "ctx_infra", 41: "amo_set", 42: "amo_swap", 43: "amo_fetch_and", 44: "amo_fetch_or",
     45: "amo_fetch_xor", 46: "amo_and", 47: "amo_or", 48: "amo_xor", 49: "pingall", 50: "put_signal",
     51: "put_signal_wg", 52: "put_signal_wave", 53: "put_signal", 54: "put_signal_wg", 55: "put_signal_wave",
     56: "signal_fetch", 57: "signal_fetch", 58: "signal_fetch",
@@ -195,6 +196,16 @@ def main() -> int:
                                              fetched.data_ptr(), args.threads, stream), args.loop, args.skip)
             if not quiet:
                 row(size, args.loop, us)
+    elif args.test == "shmem_ptr":
+        buf = shm.zeros(16, torch.uint8)
+        us = event_time(lambda: k.shmem_ptr(buf.data_ptr(), 4, stream), args.loop, args.skip)
+        if not quiet:
+            row(1, args.loop, us)
+    elif args.test == "ctx_infra":
+        out = shm.zeros(1, torch.int32)
+        us = event_time(lambda: k.ctx_exhaust(10, out.data_ptr(), stream), args.loop, args.skip)
+        if not quiet:
+            row(0, args.loop * 10, us)
     elif args.test == "pingall":
         slots, result = shm.zeros(max(n, 8), torch.int64), shm.zeros(8, torch.int64)
         us = event_time(lambda: k.pingall(slots.data_ptr(), result.data_ptr(), stream), args.loop, args.skip)

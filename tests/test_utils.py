@@ -107,7 +107,8 @@ def test_functional_driver_accepts_the_reference_test_numbers():
     assert fd.rma_form("put_nbi_wave") == (1, 1, 0) and fd.rma_form("ctx_get_thread") == (2, 0, 1)
     assert fd.rma_form("g") == (5, 0, 0) and fd.rma_form("put") is None and fd.rma_form("allreduce") is None
     assert all(name in fd.AMO or name in fd.SIGNAL_SCOPES or fd.rma_form(name) is not None or
-               name in ("pingpong", "pingall", "barrier", "allreduce", "broadcast", "fcollect", "alltoall")
+               name in ("pingpong", "pingall", "barrier", "allreduce", "broadcast", "fcollect", "alltoall", "shmem_ptr",
+                        "ctx_infra")
                for name in fd.REFERENCE_NUMBERS.values())
     assert len(fd.REFERENCE_NUMBERS) >= 50
     with pytest.raises(SystemExit, match="RandomAccessTestType"):
