@@ -16,7 +16,8 @@ pair by writing a 512 MiB buffer (outside the timed events), barrier + synchroni
 measurement, maximum over ranks. One pair is checked on every rank before anything is timed (``verified``).
 The same workload is then run over NCCL all-to-all (``baseline``; ``vs_baseline`` is ours / NCCL). The
 "e2e" figure repeats the measurement through the public API with the step's inputs copied from pinned
-host memory and a result checksum read back every step.
+host memory and a result checksum read back every step. A short run of the low-latency kernels (128 tokens
+per rank) follows and is reported under ``extra`` (``--no-ll-extra`` leaves it out).
 """
 from __future__ import annotations
 
@@ -135,6 +136,8 @@ def main() -> None:
     ap.add_argument("--repeats", type=int, default=0,
                     help="dispatch+combine pairs per step (0: as many as make a step last about 3 ms)")
     ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL all-to-all form of the workload")
+    ap.add_argument("--no-ll-extra", action="store_true",
+                    help="skip the short low-latency measurement (128 tokens per rank) reported under extra")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -361,6 +364,65 @@ def main() -> None:
     # The sampler has been running since before the warm-up: it covers both timed regions.
     clocks = sampler.stop() if rank == 0 else None
 
+    # ---- low-latency kernels, 128 tokens per rank: a short side measurement, reported under "extra" -----------------
+    # It runs after everything the headline needs has been measured; whatever goes wrong in it is reported in its
+    # own entry and leaves the numbers above alone.
+    err = shm.get_error()          # the record of everything measured so far
+    dynamic_handout = bool(d.dynamic)
+    ll_extra = None
+    if not err["count"] and not args.low_latency and not args.no_ll_extra:
+        try:
+            TL = 128
+            d.destroy()                 # one dispatcher at a time, as everywhere else; its numbers are all in hand
+            dl = moe.EpDispatcher(EXPERTS, TOPK, HIDDEN, TL, low_latency=True)
+            xl, il, wl = x[:TL].clone(), idx[:TL].clone(), w[:TL].clone()
+            yl = dl.result_buffer()
+            outl = torch.empty((TL, HIDDEN), dtype=torch.bfloat16, device=dev)
+            rl = dl.dispatch(xl, il, wl)
+            torch.cuda.synchronize()
+            infol = rl.recv_info.cpu().tolist()
+            for s in range(world):
+                first, count = infol[1 + s], infol[1 + world + s]
+                if count:
+                    yl[first:first + count].copy_(moe.fp8_dequantize_1x128(rl.recv_x[first:first + count],
+                                                                           rl.recv_scales[first:first + count]))
+            torch.cuda.synchronize()
+            shm.barrier_all()
+            dl.combine(yl, il, wl, TL, weighted=True, out=outl)
+            torch.cuda.synchronize()
+            xlf = xl.float()
+            ll_bad = float((outl.float() - xlf).abs().max().item() > 0.08 * xlf.abs().max().item() + 2e-2)
+            for _ in range(5):
+                flush.fill_(5)
+                dl.dispatch(xl, il, wl)
+                dl.combine(yl, il, wl, TL, weighted=True, out=outl)
+            torch.cuda.synchronize()
+            shm.barrier_all()
+            n_ll = 40
+            lev = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(n_ll)]
+            for i in range(n_ll):
+                flush.fill_(i & 0xff)
+                lev[i][0].record(stream)
+                dl.dispatch(xl, il, wl)
+                lev[i][1].record(stream)
+                dl.combine(yl, il, wl, TL, weighted=True, out=outl)
+                lev[i][2].record(stream)
+            torch.cuda.synchronize()
+            shm.barrier_all()
+            ld = sum(e[0].elapsed_time(e[1]) for e in lev) / n_ll * 1e3
+            lc = sum(e[1].elapsed_time(e[2]) for e in lev) / n_ll * 1e3
+            ld, lc, ll_bad = max_over_ranks([ld, lc, ll_bad])
+            ll_err = shm.get_error()
+            dl.destroy()
+            if ll_err["count"]:
+                shm.clear_error()
+                ll_extra = {"error": f"a device-side wait timed out: {ll_err}"}
+            else:
+                ll_extra = {"tokens_per_rank": TL, "pairs_timed": n_ll, "dispatch_us": ld, "combine_us": lc,
+                            "verified": ll_bad == 0.0, "layout": "slotted"}
+        except Exception as e:      # noqa: BLE001 - a side measurement must not cost the headline
+            ll_extra = {"error": f"{type(e).__name__}: {e}"}
+
     # traffic accounting for GB/s (per rank, remote destinations only)
     ranks_of = torch.where(idx_cpu >= 0, idx_cpu // epr, torch.full_like(idx_cpu, -1))
     remote_rows = 0
@@ -372,7 +434,6 @@ def main() -> None:
     disp_us = disp_ms / pairs * 1e3
     comb_us = comb_ms / pairs * 1e3
 
-    err = shm.get_error()
     if err["count"]:
         raise SystemExit(f"bench: a device-side wait timed out: {err}")
 
@@ -394,7 +455,7 @@ def main() -> None:
                        "experts_per_rank": epr, "top_k": TOPK, "hidden": HIDDEN, "tokens_per_rank": T,
                        "pairs_per_step": R, "global_batch": world * T * R, "seq_len": 1, "parallelism": f"ep{world}",
                        "layout": "slotted" if args.low_latency else args.layout, "low_latency": bool(args.low_latency),
-                       "dynamic_handout": bool(d.dynamic),
+                       "dynamic_handout": dynamic_handout,
                        "l2": "flushed before every dispatch+combine pair (512 MiB write, outside the timed events)",
                        "dispatch": "fp8 e4m3 + fp32 scale per 128", "combine": "bf16 weighted sum"},
             "clocks": clocks,
@@ -410,6 +471,7 @@ def main() -> None:
                       "combine_remote_gbs_per_rank": comb_bytes / (comb_us * 1e-6) / 1e9 if remote_rows else 0.0,
                       "remote_rows_rank0": remote_rows, "recv_rows_rank0": n_rows,
                       "device_phase_us_last_step": phases,
+                      "low_latency_128_tokens": ll_extra,
                       "nvlink_roofline_frac_dispatch": {"of_measured_770": frac(disp_bytes, disp_us, 770),
                                                         "of_link_rate_900": frac(disp_bytes, disp_us, 900)},
                       "nvlink_roofline_frac_combine": {"of_measured_770": frac(comb_bytes, comb_us, 770),
