@@ -372,7 +372,7 @@ def main() -> None:
     ll_extra = None
     if not err["count"] and not args.low_latency and not args.no_ll_extra:
         try:
-            TL = 128
+            TL = min(128, T)
             d.destroy()                 # one dispatcher at a time, as everywhere else; its numbers are all in hand
             dl = moe.EpDispatcher(EXPERTS, TOPK, HIDDEN, TL, low_latency=True)
             xl, il, wl = x[:TL].clone(), idx[:TL].clone(), w[:TL].clone()

@@ -31,4 +31,6 @@ def test_a_short_run_prints_one_json_line_with_the_contract_keys():
     assert line["n_gpus"] == 1 and line["steps"] == 2 and line["warmup"] == 3 and line["verified"] is True
     assert line["value"] > 0 and line["gpu_launches"] == 2 * 2 * 2          # steps x pairs x (dispatch + combine)
     assert line["e2e"]["h2d_bytes_per_step"] == 256 * 7168 * 2 + 2 * 256 * 8 * 4 and line["e2e"]["value"] > 0
+    ll = line["extra"]["low_latency_128_tokens"]
+    assert ll is not None and "error" not in ll and ll["verified"] is True and ll["dispatch_us"] > 0, ll
     assert line["baseline"]["value"] > 0 and abs(line["vs_baseline"] - line["value"] / line["baseline"]["value"]) < 1e-6
