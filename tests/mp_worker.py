@@ -679,6 +679,34 @@ def threads_host():
     shm.finalize()
 
 
+def collective_baselines():
+    """The torch.distributed wrappers that the benchmarks time against (rocshmem_b200.baselines), over gloo: the same
+    calling conventions as ops.collectives, results against what every rank can compute itself."""
+    import torch.distributed as dist
+    from rocshmem_b200 import baselines
+    dist.init_process_group("gloo", rank=RANK, world_size=WORLD)
+    me, n = RANK, WORLD
+    src = torch.arange(8, dtype=torch.float32) + 10 * me
+    dst = torch.zeros(8)
+    baselines.allreduce(dst, src)
+    assert torch.equal(dst, torch.arange(8, dtype=torch.float32) * n + 10 * sum(range(n)))
+    assert torch.equal(src, torch.arange(8, dtype=torch.float32) + 10 * me)        # the source is left alone
+    baselines.allreduce(src, src)                                                  # in place
+    assert torch.equal(src, dst)
+    gathered = torch.zeros(4 * n)
+    baselines.allgather(gathered, torch.full((4,), float(me)))
+    assert torch.equal(gathered.view(n, 4), torch.arange(n, dtype=torch.float32).view(n, 1).expand(n, 4))
+    a2a = torch.zeros(2 * n)
+    baselines.alltoall(a2a, torch.arange(2 * n, dtype=torch.float32) + 100 * me)
+    want = torch.cat([torch.arange(2 * me, 2 * me + 2, dtype=torch.float32) + 100 * p for p in range(n)])
+    assert torch.equal(a2a, want)
+    buf = torch.full((5,), float(me))
+    baselines.broadcast(buf, n - 1)
+    assert torch.all(buf == n - 1)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
 def ep_collective_baseline():
     """The all-to-all (torch.distributed) baseline of dispatch / combine against the reference routing, and a
     round trip with identity experts against the de-quantised input."""
@@ -1092,7 +1120,7 @@ def elastic_grow():
     shm.finalize()
 
 
-SCENARIOS = {f.__name__: f for f in (elastic_grow, reduce_scatter_host, elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, team_multicast_standin, collectives_host, wait_and_signal,
+SCENARIOS = {f.__name__: f for f in (elastic_grow, reduce_scatter_host, elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, collective_baselines, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, team_multicast_standin, collectives_host, wait_and_signal,
                                      late_rank, rank_leaves)}
 
 if __name__ == "__main__":

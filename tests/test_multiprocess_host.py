@@ -78,6 +78,10 @@ def test_threads_per_process_all_to_all_wait_chain_and_large_transfers():
     assert_all_ok(run_ranks("threads_host", 3, timeout=240))
 
 
+def test_collective_baseline_wrappers_over_gloo():
+    assert_all_ok(run_ranks("collective_baselines", 3))
+
+
 def test_all_to_all_baseline_of_dispatch_and_combine():
     assert_all_ok(run_ranks("ep_collective_baseline", 3, timeout=240))
 
