@@ -17,7 +17,8 @@ measurement, maximum over ranks. One pair is checked on every rank before anythi
 The same workload is then run over NCCL all-to-all (``baseline``; ``vs_baseline`` is ours / NCCL). The
 "e2e" figure repeats the measurement through the public API with the step's inputs copied from pinned
 host memory and a result checksum read back every step. A short run of the low-latency kernels (128 tokens
-per rank) follows and is reported under ``extra`` (``--no-ll-extra`` leaves it out).
+per rank) follows and is reported under ``extra`` (``--no-ll-extra`` leaves it out), and with two or more GPUs a
+short comparison of the library collectives with NCCL (``--no-coll-extra``).
 """
 from __future__ import annotations
 
@@ -138,6 +139,9 @@ def main() -> None:
     ap.add_argument("--no-baseline", action="store_true", help="skip the NCCL all-to-all form of the workload")
     ap.add_argument("--no-ll-extra", action="store_true",
                     help="skip the short low-latency measurement (128 tokens per rank) reported under extra")
+    ap.add_argument("--no-coll-extra", action="store_true",
+                    help="skip the short collective measurements (allreduce, all-gather, all-to-all, broadcast against "
+                         "NCCL) reported under extra when there are two or more GPUs")
     args = ap.parse_args()
     if args.impl == "reference":
         reference_arm(args)
@@ -423,6 +427,77 @@ def main() -> None:
         except Exception as e:      # noqa: BLE001 - a side measurement must not cost the headline
             ll_extra = {"error": f"{type(e).__name__}: {e}"}
 
+    # ---- library collectives against NCCL on the same GPUs: a short side measurement, reported under "extra" --------
+    # Back-to-back launches (no L2 flush: the large messages exceed the L2, the small ones measure latency), three
+    # warm-ups, CUDA events, maximum over ranks; the same rules for both sides. Guarded like the measurement above.
+    coll_extra = None
+    if world >= 2 and not err["count"] and not args.no_coll_extra and not (ll_extra and "error" in ll_extra):
+        try:
+            big = 64 << 20                                   # bytes
+            csrc = shm.zeros(big // 2, torch.bfloat16)
+            cdst = shm.zeros(big // 2, torch.bfloat16)
+            nsrc = torch.empty(big // 2, dtype=torch.bfloat16, device=dev)
+            ndst = torch.empty(big // 2, dtype=torch.bfloat16, device=dev)
+            csrc.normal_()
+            nsrc.copy_(csrc)
+            ndst.zero_()
+            torch.cuda.synchronize()
+            shm.barrier_all()
+
+            def timed(fn, iters):
+                for _ in range(3):
+                    fn()
+                torch.cuda.synchronize()
+                shm.barrier_all()
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                for _ in range(iters):
+                    fn()
+                b.record(stream)
+                torch.cuda.synchronize()
+                return max_over_ranks([a.elapsed_time(b) * 1e3 / iters])[0]
+
+            rows = []
+            busf = 2.0 * (world - 1) / world
+            for nbytes in (1 << 10, 256 << 10, 64 << 20):
+                n, iters = nbytes // 2, (50 if nbytes <= (1 << 20) else 8)
+                ours = timed(lambda: coll.allreduce_async(cdst[:n], csrc[:n], shm.OP_SUM), iters)
+
+                theirs = timed(lambda: dist.all_reduce(ndst[:n]), iters)      # in place, NCCL's own calling form
+                rows.append({"op": "allreduce", "bytes": nbytes, "dtype": "bf16", "us": ours, "nccl_us": theirs,
+                             "busbw_gbs": busf * nbytes / ours / 1e3, "nccl_busbw_gbs": busf * nbytes / theirs / 1e3})
+            # the allreduce is checked once against an fp32 sum gathered over NCCL
+            n_chk = 4096
+            coll.allreduce_async(cdst[:n_chk], csrc[:n_chk], shm.OP_SUM)
+            parts = [torch.empty(n_chk, dtype=torch.bfloat16, device=dev) for _ in range(world)]
+            dist.all_gather(parts, csrc[:n_chk].clone())
+            torch.cuda.synchronize()
+            want = sum(p.float() for p in parts)
+            coll_bad = float((cdst[:n_chk].float() - want).abs().max().item() > 3e-2 * max(1.0, want.abs().max().item()))
+            per = (big // world) // 2 // 8 * 8                # elements per peer, 16-byte multiples
+            for name, ours_fn, nccl_fn, moved in (
+                ("fcollect", lambda: coll.fcollect_async(cdst[:per * world], csrc[:per]),
+                 lambda: dist.all_gather_into_tensor(ndst[:per * world], nsrc[:per]), per * 2 * (world - 1)),
+                ("alltoall", lambda: coll.alltoall_async(cdst[:per * world], csrc[:per * world]),
+                 lambda: dist.all_to_all_single(ndst[:per * world], nsrc[:per * world]), per * 2 * (world - 1)),
+                ("broadcast", lambda: coll.broadcast_async(cdst, csrc, 0), lambda: dist.broadcast(nsrc, 0), big),
+            ):
+                ours = timed(ours_fn, 8)
+                theirs = timed(nccl_fn, 8)
+                rows.append({"op": name, "bytes_per_peer": per * 2 if name != "broadcast" else big, "us": ours,
+                             "nccl_us": theirs, "gbs": moved / ours / 1e3, "nccl_gbs": moved / theirs / 1e3})
+            coll_bad = max_over_ranks([coll_bad])[0]
+            coll_err = shm.get_error()
+            if coll_err["count"]:
+                shm.clear_error()
+                coll_extra = {"error": f"a device-side wait timed out: {coll_err}"}
+            else:
+                coll_extra = {"rows": rows, "allreduce_verified": coll_bad == 0.0, "nvls": bool(shm.nvls_available()),
+                              "note": "back-to-back launches, 3 warm-ups, CUDA events, max over ranks; GB/s of the copy "
+                                      "collectives = bytes entering one rank / time"}
+        except Exception as e:      # noqa: BLE001 - a side measurement must not cost the headline
+            coll_extra = {"error": f"{type(e).__name__}: {e}"}
+
     # traffic accounting for GB/s (per rank, remote destinations only)
     ranks_of = torch.where(idx_cpu >= 0, idx_cpu // epr, torch.full_like(idx_cpu, -1))
     remote_rows = 0
@@ -472,6 +547,7 @@ def main() -> None:
                       "remote_rows_rank0": remote_rows, "recv_rows_rank0": n_rows,
                       "device_phase_us_last_step": phases,
                       "low_latency_128_tokens": ll_extra,
+                      "collectives_vs_nccl": coll_extra,
                       "nvlink_roofline_frac_dispatch": {"of_measured_770": frac(disp_bytes, disp_us, 770),
                                                         "of_link_rate_900": frac(disp_bytes, disp_us, 900)},
                       "nvlink_roofline_frac_combine": {"of_measured_770": frac(comb_bytes, comb_us, 770),
