@@ -355,6 +355,28 @@ def rank_leaves():
         mem.post("survivors-done")
 
 
+def team_member_leaves():
+    """A team with a multicast object of its own (the host provider's stand-in) loses a member between steps: the
+    survivor's collective team_destroy gives up after the rendezvous time-out, releases the object and returns; the
+    process then finishes without the absent rank."""
+    import time
+    init("8M")
+    me, n = shm.my_pe(), shm.n_pes()
+    pair = shm.team_world().split_strided(0, 1, 2)
+    if me < 2:
+        assert pair.valid and pair.has_nvls()
+    shm.barrier_all()
+    if me == 1:
+        return                      # leaves between steps, nothing in flight, without destroying its team
+    if me == 0:
+        t0 = time.time()
+        pair.destroy()              # meets nobody: bounded by the rendezvous time-out, then the mapping goes
+        waited = time.time() - t0
+        assert 1.0 < waited < 40.0, waited
+        assert not pair.valid
+    # PE 2 was never a member and is not involved
+
+
 def proxy_collectives():
     """The reverse-offload command ring executing the host forms of fence, P, broadcast, reduce, fcollect and
     alltoall (each rank submits the command to its own proxy thread, like a device kernel would)."""
@@ -1121,7 +1143,7 @@ def elastic_grow():
 
 
 SCENARIOS = {f.__name__: f for f in (elastic_grow, reduce_scatter_host, elastic_unplanned, elastic_shrink, alltoallv_host, pipeline_stages, ring_attention, ulysses, data_parallel, ep_collective_baseline, collective_baselines, threads_host, host_algorithms, stress_host, parallel_layout, moe_layer_host, ep_host, proxy_collectives, host_plumbing, store_bootstrap, teams, team_multicast_standin, collectives_host, wait_and_signal,
-                                     late_rank, rank_leaves)}
+                                     late_rank, rank_leaves, team_member_leaves)}
 
 if __name__ == "__main__":
     name = sys.argv[1]

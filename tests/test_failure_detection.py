@@ -20,6 +20,17 @@ def test_rank_leaves_between_steps_and_survivors_continue():
     assert_all_ok(run_ranks("rank_leaves", 3, timeout=120))
 
 
+def test_team_destroy_returns_when_a_member_of_a_multicast_team_has_left():
+    """team_destroy of a team with a multicast object is collective; a member that left must cost the survivor the
+    rendezvous time-out and nothing more (host provider's stand-in for the object, three CPU processes)."""
+    t0 = time.time()
+    results = run_ranks("team_member_leaves", 3, timeout=120,
+                        env_extra={"ROCSHMEM_HOST_FAKE_MULTICAST": 1, "ROCSHMEM_TEST_TIMEOUT": 4})
+    assert_all_ok(results)
+    assert "team_destroy" in results[0][1]          # the survivor says what it gave up waiting for
+    assert time.time() - t0 < 90
+
+
 def test_proxy_ring_executes_and_reports_dropped_commands(fresh_runtime):
     shm = fresh_runtime
     shm.init(n_local=2, heap_size="4M", backend="host")
