@@ -74,6 +74,19 @@ def test_descriptor_from_the_first_member_of_a_subgroup():
     assert got == {r: "from-the-first-member" for r in members}
 
 
+def test_descriptor_group_with_an_absent_sender_times_out():
+    C = _native.load()
+    import time
+    with tempfile.TemporaryDirectory() as d:
+        t0 = time.time()
+        try:
+            C.broadcast_fd_group_file(d, 1, 2, [0, 1], -1, 300)      # rank 0, the sender, never shows up
+            raise AssertionError("returned although the sender never joined")
+        except RuntimeError as e:
+            assert "timed out" in str(e)
+        assert time.time() - t0 < 10
+
+
 def test_missing_rank_times_out_instead_of_hanging():
     C = _native.load()
     import time
