@@ -94,11 +94,13 @@ def test_whole_runtime_with_threads_and_proxy_under_sanitizers(mode, tmp_path):
     assert run.returncode == 0 and "PASS" in run.stdout, run.stdout[-2000:] + run.stderr[-4000:]
     assert marker not in run.stderr, run.stderr[-4000:]
     # the host API from one thread (three processes) and from several threads (two processes)
-    for prog, world in (("host_api_sos", 3), ("host_threads_sos", 2)):
+    # (the first with the stand-in for the NVLink multicast object: set-up and release of the world's and of split
+    # teams' objects run under the sanitizers too)
+    for prog, world, extra in (("host_api_sos", 3, {"ROCSHMEM_HOST_FAKE_MULTICAST": "1"}), ("host_threads_sos", 2, {})):
         kv = tmp_path / ("kv_" + prog)
         kv.mkdir()
         procs = [subprocess.Popen([exes[prog]], env=dict(base, RANK=str(r), WORLD_SIZE=str(world), LOCAL_RANK=str(r),
-                                                         ROCSHMEM_BOOTSTRAP_DIR=str(kv)),
+                                                         ROCSHMEM_BOOTSTRAP_DIR=str(kv), **extra),
                                   stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True) for r in range(world)]
         try:
             for r, p in enumerate(procs):
