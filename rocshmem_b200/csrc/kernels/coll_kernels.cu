@@ -22,6 +22,7 @@
 
 #include <cstdlib>
 
+#include "coll_select.hpp"
 #include "kernels.hpp"
 #include "launch.cuh"
 #include "lib_common.cuh"
@@ -563,41 +564,20 @@ int launch_allreduce_typed(rocshmem_team_t team, void *dest, const void *source,
   Runtime &rt = Runtime::instance();
   HostTeam *ht = rt.team_from_handle(team);
   const int n = ht ? ht->world.size : rt.n_pes();
-  if (algo == ALLREDUCE_AUTO) {
-    // Through the switch a rank receives bytes * (1 + 1/n) (its reduced slice, then every slice, its own included);
-    // the two-shot kernel receives bytes * 2 (n - 1) / n. The switch wins from four members on (measured: 366 us
-    // against 227 us for 128 MiB on two GPUs, level on four, 1.3 x ahead on eight).
-    const bool nvls_ok = ht != nullptr && ht->mc_window != nullptr && n >= 4 && op == ROCSHMEM_SUM &&
-                         (std::is_same<T, float>::value || std::is_same<T, __half>::value ||
-                          std::is_same<T, __nv_bfloat16>::value);
-    const bool ll_ok = (sizeof(T) == 2 || sizeof(T) == 4) && bytes % 4 == 0 && bytes <= size_t(ROCSHMEM_LL_WORDS) * 4 &&
-                       ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 3u) == 0;
-    if (ll_ok) algo = ALLREDUCE_LL;
-    else if (bytes <= (size_t(256) << 10) && dest != source) algo = ALLREDUCE_ONE_SHOT;
-    else algo = nvls_ok ? ALLREDUCE_NVLS : ALLREDUCE_TWO_SHOT;
-  }
+  constexpr bool kMultimem = std::is_same<T, float>::value || std::is_same<T, __half>::value ||
+                             std::is_same<T, __nv_bfloat16>::value;
+  AllreduceRequest req{algo, bytes, sizeof(T), n, ht != nullptr && ht->mc_window != nullptr, op == ROCSHMEM_SUM, kMultimem,
+                       reinterpret_cast<uintptr_t>(dest), reinterpret_cast<uintptr_t>(source)};
+  algo = select_allreduce(req);
   if (algo == ALLREDUCE_LL) {
     if constexpr (sizeof(T) == 2 || sizeof(T) == 4) {
-      const bool fits = bytes % 4 == 0 && bytes <= size_t(ROCSHMEM_LL_WORDS) * 4 &&
-                        ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 3u) == 0;
-      if (fits) {
-        const unsigned words = static_cast<unsigned>(bytes / 4);
-        const unsigned threads = std::min(kThreads, std::max(32u, (words + 31) / 32 * 32));
-        auto k = op == ROCSHMEM_SUM ? allreduce_ll_kernel<T, ROCSHMEM_SUM> : allreduce_ll_kernel<T, OP_RUNTIME>;
-        return launch_pes(k, 1, threads, 0, stream, false, team, static_cast<T *>(dest), static_cast<const T *>(source),
-                          nelems, op);
-      }
-    }
-    algo = dest != source ? ALLREDUCE_ONE_SHOT : ALLREDUCE_TWO_SHOT;
-  }
-  if (algo == ALLREDUCE_ONE_SHOT && dest == source) algo = ALLREDUCE_TWO_SHOT;
-  if (algo == ALLREDUCE_NVLS) {
-    constexpr bool supported = std::is_same<T, float>::value || std::is_same<T, __half>::value ||
-                               std::is_same<T, __nv_bfloat16>::value;
-    const bool aligned = ((reinterpret_cast<uintptr_t>(dest) | reinterpret_cast<uintptr_t>(source)) & 15u) == 0 &&
-                         bytes % 16 == 0;
-    if (!supported || ht == nullptr || ht->mc_window == nullptr || op != ROCSHMEM_SUM || !aligned) {
-      algo = ALLREDUCE_TWO_SHOT;
+      const unsigned words = static_cast<unsigned>(bytes / 4);
+      const unsigned threads = std::min(kThreads, std::max(32u, (words + 31) / 32 * 32));
+      auto k = op == ROCSHMEM_SUM ? allreduce_ll_kernel<T, ROCSHMEM_SUM> : allreduce_ll_kernel<T, OP_RUNTIME>;
+      return launch_pes(k, 1, threads, 0, stream, false, team, static_cast<T *>(dest), static_cast<const T *>(source),
+                        nelems, op);
+    } else {
+      return cudaErrorInvalidValue;   // select_allreduce never picks it for other element sizes
     }
   }
   const unsigned want = static_cast<unsigned>(coll_blocks_for(algo == ALLREDUCE_ONE_SHOT ? bytes : bytes / n));

@@ -19,6 +19,7 @@
 #include "rocshmem/coalesce.h"
 #include "rocshmem/slab.h"
 #include "team.hpp"
+#include "../kernels/coll_select.hpp"
 
 using namespace rocshmem;
 
@@ -232,6 +233,45 @@ static void test_slab_place() {
   EXPECT(detail::slab_place(s, 0, ~0ull, 16) == ~0ull);    // no overflow in the fit test
 }
 
+static void test_allreduce_selection() {
+  using namespace rocshmem::kernels;
+  auto pick = [](int algo, size_t bytes, size_t esz, int n, bool mc, bool sum = true, bool mm = true, uintptr_t dst = 0x1000,
+                 uintptr_t src = 0x200000) {
+    return select_allreduce(AllreduceRequest{algo, bytes, esz, n, mc, sum, mm, dst, src});
+  };
+  // automatic choice by size: flag-in-word up to 2 KiB of 2- or 4-byte elements, one-shot up to 256 KiB, then the
+  // switch for teams of four or more with a multicast mapping, else two-shot
+  EXPECT(pick(ALLREDUCE_AUTO, 1024, 2, 8, true) == ALLREDUCE_LL);
+  EXPECT(pick(ALLREDUCE_AUTO, ROCSHMEM_LL_WORDS * 4, 4, 2, false) == ALLREDUCE_LL);
+  EXPECT(pick(ALLREDUCE_AUTO, ROCSHMEM_LL_WORDS * 4 + 4, 4, 2, false) == ALLREDUCE_ONE_SHOT);
+  EXPECT(pick(ALLREDUCE_AUTO, 1024, 8, 8, true) == ALLREDUCE_ONE_SHOT);            // 8-byte elements have no mailbox form
+  EXPECT(pick(ALLREDUCE_AUTO, 1022, 2, 8, true) == ALLREDUCE_ONE_SHOT);            // not whole words
+  EXPECT(pick(ALLREDUCE_AUTO, 1024, 2, 8, true, true, true, 0x1002) == ALLREDUCE_ONE_SHOT);   // not 4-byte aligned
+  EXPECT(pick(ALLREDUCE_AUTO, size_t(256) << 10, 2, 8, true) == ALLREDUCE_ONE_SHOT);
+  EXPECT(pick(ALLREDUCE_AUTO, (size_t(256) << 10) + 16, 2, 8, true) == ALLREDUCE_NVLS);
+  EXPECT(pick(ALLREDUCE_AUTO, size_t(64) << 20, 2, 4, true) == ALLREDUCE_NVLS);
+  EXPECT(pick(ALLREDUCE_AUTO, size_t(64) << 20, 2, 3, true) == ALLREDUCE_TWO_SHOT);  // fewer than four members
+  EXPECT(pick(ALLREDUCE_AUTO, size_t(64) << 20, 2, 2, true) == ALLREDUCE_TWO_SHOT);
+  EXPECT(pick(ALLREDUCE_AUTO, size_t(64) << 20, 2, 8, false) == ALLREDUCE_TWO_SHOT); // no mapping
+  EXPECT(pick(ALLREDUCE_AUTO, size_t(64) << 20, 2, 8, true, false) == ALLREDUCE_TWO_SHOT);   // not a sum
+  EXPECT(pick(ALLREDUCE_AUTO, size_t(64) << 20, 4, 8, true, true, false) == ALLREDUCE_TWO_SHOT);  // int32: no multimem add
+  EXPECT(pick(ALLREDUCE_AUTO, (size_t(64) << 20) + 8, 2, 8, true) == ALLREDUCE_TWO_SHOT);    // not whole 16-byte vectors
+  EXPECT(pick(ALLREDUCE_AUTO, size_t(64) << 20, 2, 8, true, true, true, 0x1008) == ALLREDUCE_TWO_SHOT);  // not 16-byte aligned
+  // in place: never the one-shot kernel (it reads the sources while other members write their results)
+  EXPECT(pick(ALLREDUCE_AUTO, 4096, 4, 8, true, true, true, 0x4000, 0x4000) == ALLREDUCE_NVLS);
+  EXPECT(pick(ALLREDUCE_AUTO, 4096, 4, 2, false, true, true, 0x4000, 0x4000) == ALLREDUCE_TWO_SHOT);
+  EXPECT(pick(ALLREDUCE_AUTO, 512, 4, 2, false, true, true, 0x4000, 0x4000) == ALLREDUCE_LL);   // mailboxes: in place is fine
+  // explicit requests run when their conditions hold and fall back otherwise
+  EXPECT(pick(ALLREDUCE_NVLS, size_t(1) << 20, 2, 2, true) == ALLREDUCE_NVLS);        // asked for: any team size
+  EXPECT(pick(ALLREDUCE_NVLS, size_t(1) << 20, 2, 8, false) == ALLREDUCE_TWO_SHOT);
+  EXPECT(pick(ALLREDUCE_NVLS, size_t(1) << 20, 8, 8, true, true, false) == ALLREDUCE_TWO_SHOT);
+  EXPECT(pick(ALLREDUCE_LL, 4096, 4, 8, true) == ALLREDUCE_ONE_SHOT);                 // too large for the mailboxes
+  EXPECT(pick(ALLREDUCE_LL, 4096, 4, 8, true, true, true, 0x4000, 0x4000) == ALLREDUCE_TWO_SHOT);
+  EXPECT(pick(ALLREDUCE_ONE_SHOT, size_t(8) << 20, 4, 8, true) == ALLREDUCE_ONE_SHOT);
+  EXPECT(pick(ALLREDUCE_ONE_SHOT, 4096, 4, 8, true, true, true, 0x4000, 0x4000) == ALLREDUCE_TWO_SHOT);
+  EXPECT(pick(ALLREDUCE_TWO_SHOT, 64, 4, 8, true) == ALLREDUCE_TWO_SHOT);
+}
+
 int main(int argc, char **argv) {
   if (argc < 2) {
     std::fprintf(stderr, "usage: %s <scratch directory>\n", argv[0]);
@@ -244,6 +284,7 @@ int main(int argc, char **argv) {
   test_config();
   test_coalesce();
   test_slab_place();
+  test_allreduce_selection();
   test_file_bootstrap_between_threads(argv[1]);
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);
