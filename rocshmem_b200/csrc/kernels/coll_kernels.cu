@@ -694,32 +694,21 @@ int coll_broadcast(rocshmem_team_t team, void *dest, const void *source, size_t 
   Runtime &rt = Runtime::instance();
   HostTeam *ht = rt.team_from_handle(team);
   const int n = ht ? ht->world.size : 0;
-  if (use_bcast_nvls() && ht != nullptr && rt.n_local() == 1 && ht->mc_window != nullptr &&
-      n >= 2 && bytes >= (size_t(1) << 20) && bytes % 16 == 0 && reinterpret_cast<uintptr_t>(dest) % 16 == 0 &&
-      reinterpret_cast<uintptr_t>(source) % 16 == 0) {
-    // Two staging halves of one sub-chunk each; sub-chunks as for the relay (a transfer that dwarfs its barrier).
-    size_t sub = std::max<size_t>(size_t(4) << 20, bytes / 8);
-    sub = std::min<size_t>(sub, size_t(16) << 20);
-    sub = std::min<size_t>(sub, rt.config().scratch_size / 2);
-    sub = sub / 4096 * 4096;
-    if (sub >= (size_t(1) << 20)) {
-      unsigned blocks = clamp_blocks(broadcast_nvls_kernel, static_cast<unsigned>(coll_blocks_for(sub)));
-      return launch_pes(broadcast_nvls_kernel, blocks, kThreads, 0, static_cast<cudaStream_t>(stream), false, team,
-                        static_cast<char *>(dest), static_cast<const char *>(source), bytes, root, sub,
-                        (flags & COLL_PRE_SYNC) ? 1 : 0);
-    }
+  const bool aligned16 = reinterpret_cast<uintptr_t>(dest) % 16 == 0 && reinterpret_cast<uintptr_t>(source) % 16 == 0;
+  const BroadcastPlan plan = plan_broadcast(bytes, n, use_bcast_nvls(), ht != nullptr && ht->mc_window != nullptr,
+                                            rt.n_local(), aligned16, rt.config().scratch_size);
+  if (plan.kind == BROADCAST_NVLS) {
+    // Two staging halves of one sub-chunk each.
+    unsigned blocks = clamp_blocks(broadcast_nvls_kernel, static_cast<unsigned>(coll_blocks_for(plan.sub_bytes)));
+    return launch_pes(broadcast_nvls_kernel, blocks, kThreads, 0, static_cast<cudaStream_t>(stream), false, team,
+                      static_cast<char *>(dest), static_cast<const char *>(source), bytes, root, plan.sub_bytes,
+                      (flags & COLL_PRE_SYNC) ? 1 : 0);
   }
-  if (n >= 3 && bytes >= (size_t(512) << 10)) {
-    // Sub-chunks large enough that a sub-chunk's transfer time dwarfs the barrier that ends it.
-    size_t sub = bytes;
-    if (bytes > (size_t(4) << 20)) {
-      sub = std::max<size_t>(size_t(4) << 20, bytes / 8);
-      sub = std::min<size_t>(sub, size_t(16) << 20);
-      sub = (sub + 4095) / 4096 * 4096;
-    }
-    unsigned blocks = clamp_blocks(broadcast_relay_kernel, static_cast<unsigned>(coll_blocks_for(sub / (n - 1))));
+  if (plan.kind == BROADCAST_RELAY) {
+    unsigned blocks = clamp_blocks(broadcast_relay_kernel,
+                                   static_cast<unsigned>(coll_blocks_for(plan.sub_bytes / (n - 1))));
     return launch_pes(broadcast_relay_kernel, blocks, kThreads, 0, static_cast<cudaStream_t>(stream), false, team,
-                      static_cast<char *>(dest), static_cast<const char *>(source), bytes, root, sub,
+                      static_cast<char *>(dest), static_cast<const char *>(source), bytes, root, plan.sub_bytes,
                       (flags & COLL_PRE_SYNC) ? 1 : 0);
   }
   return launch_push(team, dest, source, bytes, root, 0, stream, flags);

@@ -52,5 +52,39 @@ inline int select_allreduce(const AllreduceRequest &r) {
   return algo;
 }
 
+// How a broadcast travels: pushed by the root to every member, relayed (the root sends each member one part,
+// members forward; teams of three or more, 512 KiB and more), or written once through the switch into a staging
+// half that the members copy out of (opt-in, teams with a multicast mapping, one PE per process, 1 MiB and more,
+// 16-byte aligned). `sub_bytes` is the sub-chunk of the relayed and the switch forms: a multiple of 4096 (the
+// switch form: two of them fit the staging area), large enough that its transfer dwarfs the barrier that ends it.
+enum BroadcastKind { BROADCAST_PUSH = 0, BROADCAST_RELAY = 1, BROADCAST_NVLS = 2 };
+
+struct BroadcastPlan {
+  int kind;
+  size_t sub_bytes;   // 0 for BROADCAST_PUSH
+};
+
+inline BroadcastPlan plan_broadcast(size_t bytes, int team_size, bool nvls_requested, bool team_has_multicast,
+                                    int n_local, bool aligned16, size_t scratch_bytes) {
+  if (nvls_requested && team_has_multicast && n_local == 1 && team_size >= 2 && bytes >= (size_t(1) << 20) &&
+      bytes % 16 == 0 && aligned16) {
+    size_t sub = bytes / 8 > (size_t(4) << 20) ? bytes / 8 : (size_t(4) << 20);
+    if (sub > (size_t(16) << 20)) sub = size_t(16) << 20;
+    if (sub > scratch_bytes / 2) sub = scratch_bytes / 2;
+    sub = sub / 4096 * 4096;
+    if (sub >= (size_t(1) << 20)) return BroadcastPlan{BROADCAST_NVLS, sub};
+  }
+  if (team_size >= 3 && bytes >= (size_t(512) << 10)) {
+    size_t sub = bytes;
+    if (bytes > (size_t(4) << 20)) {
+      sub = bytes / 8 > (size_t(4) << 20) ? bytes / 8 : (size_t(4) << 20);
+      if (sub > (size_t(16) << 20)) sub = size_t(16) << 20;
+      sub = (sub + 4095) / 4096 * 4096;
+    }
+    return BroadcastPlan{BROADCAST_RELAY, sub};
+  }
+  return BroadcastPlan{BROADCAST_PUSH, 0};
+}
+
 }  // namespace kernels
 }  // namespace rocshmem

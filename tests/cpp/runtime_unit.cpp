@@ -272,6 +272,50 @@ static void test_allreduce_selection() {
   EXPECT(pick(ALLREDUCE_TWO_SHOT, 64, 4, 8, true) == ALLREDUCE_TWO_SHOT);
 }
 
+static void test_broadcast_plan() {
+  using namespace rocshmem::kernels;
+  const size_t KiB = 1024, MiB = 1024 * KiB, scratch = 64 * MiB;
+  // small or two members: the root pushes
+  EXPECT(plan_broadcast(4 * KiB, 8, false, true, 1, true, scratch).kind == BROADCAST_PUSH);
+  EXPECT(plan_broadcast(64 * MiB, 2, false, true, 1, true, scratch).kind == BROADCAST_PUSH);
+  EXPECT(plan_broadcast(512 * KiB - 1, 8, false, false, 1, true, scratch).kind == BROADCAST_PUSH);
+  // three or more members from 512 KiB on: relayed; up to 4 MiB in one piece, beyond in 4 - 16 MiB sub-chunks
+  BroadcastPlan p = plan_broadcast(512 * KiB, 3, false, false, 1, true, scratch);
+  EXPECT(p.kind == BROADCAST_RELAY && p.sub_bytes == 512 * KiB);
+  p = plan_broadcast(4 * MiB, 8, false, false, 4, false, scratch);                // several PEs per process, unaligned: fine
+  EXPECT(p.kind == BROADCAST_RELAY && p.sub_bytes == 4 * MiB);
+  p = plan_broadcast(4 * MiB + 16, 8, false, false, 1, true, scratch);
+  EXPECT(p.kind == BROADCAST_RELAY && p.sub_bytes == 4 * MiB);
+  p = plan_broadcast(64 * MiB, 8, false, true, 1, true, scratch);
+  EXPECT(p.kind == BROADCAST_RELAY && p.sub_bytes == 8 * MiB);
+  p = plan_broadcast(size_t(1) << 30, 8, false, true, 1, true, scratch);
+  EXPECT(p.kind == BROADCAST_RELAY && p.sub_bytes == 16 * MiB);
+  p = plan_broadcast(40 * MiB + 8, 4, false, false, 1, true, scratch);             // bytes / 8 is not a multiple of 4096
+  EXPECT(p.kind == BROADCAST_RELAY && p.sub_bytes % 4096 == 0 && p.sub_bytes >= (40 * MiB + 8) / 8);
+  // through the switch only on request, with a mapping, one PE per process, 16-byte alignment and 1 MiB or more
+  p = plan_broadcast(64 * MiB, 8, true, true, 1, true, scratch);
+  EXPECT(p.kind == BROADCAST_NVLS && p.sub_bytes == 8 * MiB);
+  p = plan_broadcast(64 * MiB, 2, true, true, 1, true, scratch);
+  EXPECT(p.kind == BROADCAST_NVLS && p.sub_bytes == 8 * MiB);
+  p = plan_broadcast(64 * MiB, 8, true, true, 1, true, 6 * MiB);                   // two sub-chunks must fit the staging area
+  EXPECT(p.kind == BROADCAST_NVLS && p.sub_bytes == 3 * MiB);
+  EXPECT(plan_broadcast(64 * MiB, 8, true, true, 1, true, MiB).kind == BROADCAST_RELAY);        // staging too small
+  EXPECT(plan_broadcast(64 * MiB, 8, true, false, 1, true, scratch).kind == BROADCAST_RELAY);   // no mapping
+  EXPECT(plan_broadcast(64 * MiB, 8, true, true, 2, true, scratch).kind == BROADCAST_RELAY);    // several PEs per process
+  EXPECT(plan_broadcast(64 * MiB, 8, true, true, 1, false, scratch).kind == BROADCAST_RELAY);   // unaligned
+  EXPECT(plan_broadcast(64 * MiB + 8, 8, true, true, 1, true, scratch).kind == BROADCAST_RELAY);
+  EXPECT(plan_broadcast(MiB - 16, 2, true, true, 1, true, scratch).kind == BROADCAST_PUSH);
+  // every plan with sub-chunks: whole pages, and the switch form's two halves fit the staging area
+  for (size_t bytes = 512 * KiB; bytes <= (size_t(2) << 30); bytes = bytes * 3 / 2 / 16 * 16) {
+    for (int nvls = 0; nvls < 2; ++nvls) {
+      p = plan_broadcast(bytes, 8, nvls != 0, true, 1, true, scratch);
+      EXPECT(p.kind != BROADCAST_PUSH && p.sub_bytes > 0);
+      if (p.kind == BROADCAST_NVLS) EXPECT(p.sub_bytes % 4096 == 0 && 2 * p.sub_bytes <= scratch && p.sub_bytes >= MiB);
+      if (p.kind == BROADCAST_RELAY && bytes > 4 * MiB) EXPECT(p.sub_bytes % 4096 == 0 && p.sub_bytes <= 16 * MiB);
+    }
+  }
+}
+
 int main(int argc, char **argv) {
   if (argc < 2) {
     std::fprintf(stderr, "usage: %s <scratch directory>\n", argv[0]);
@@ -285,6 +329,7 @@ int main(int argc, char **argv) {
   test_coalesce();
   test_slab_place();
   test_allreduce_selection();
+  test_broadcast_plan();
   test_file_bootstrap_between_threads(argv[1]);
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);
