@@ -970,24 +970,10 @@ __global__ void ep_expert_layout_kernel(const int *recv_meta_a, const int *recv_
 }
 
 int validate(const EpConfig &cfg, int team_size, int num_tokens) {
-  // Destinations live in the lanes of a warp (slot shuffles, per-lane weights), hence at most 32 ranks.
-  if (team_size < 1 || team_size > EP_MAX_RANKS) return cudaErrorInvalidValue;
-  if (cfg.num_experts < team_size || cfg.num_experts % team_size || cfg.num_experts > 1024) return cudaErrorInvalidValue;
-  if (cfg.top_k < 1 || cfg.top_k > EP_MAX_TOPK) return cudaErrorInvalidValue;
-  if (cfg.hidden < 512 || cfg.hidden % 512 || cfg.hidden > EP_MAX_HIDDEN) return cudaErrorInvalidValue;
-  if (num_tokens < 0 || num_tokens > cfg.max_tokens) return cudaErrorInvalidValue;
-  // block_pair_barrier keeps one flag row per block.
-  if (cfg.blocks < 1 || cfg.blocks > ROCSHMEM_LIB_MAX_BLOCKS) return cudaErrorInvalidValue;
-  if (cfg.low_latency && cfg.layout != EP_LAYOUT_SLOTTED) return cudaErrorInvalidValue;
-  return 0;
+  return ep_config_error(cfg, team_size, num_tokens) ? cudaErrorInvalidValue : 0;
 }
 
-// Blocks of a low-latency combine: a function of the configuration only, because every member must launch the
-// same number (block b pairs with block b of the peers) while their token counts may differ.
-int ll_combine_blocks(const EpConfig &cfg) {
-  const int warps = cfg.max_tokens * 4;
-  return std::max(1, std::min<int>(ROCSHMEM_LIB_MAX_BLOCKS, (warps + 3) / 4));
-}
+int ll_combine_blocks(const EpConfig &cfg) { return ep_ll_combine_blocks(cfg); }
 
 }  // namespace
 

@@ -45,6 +45,29 @@ struct EpConfig {
   int low_latency;     // 1: one non-cooperative launch, a block per token, slotted layout, per-source signals
 };
 
+// What dispatch and combine accept (0) or refuse (1 = cudaErrorInvalidValue). Pure host logic, shared by the
+// launchers and the CPU unit tests.
+inline int ep_config_error(const EpConfig &cfg, int team_size, int num_tokens) {
+  // Destinations live in the lanes of a warp (slot shuffles, per-lane weights), hence at most 32 ranks.
+  if (team_size < 1 || team_size > EP_MAX_RANKS) return 1;
+  if (cfg.num_experts < team_size || cfg.num_experts % team_size || cfg.num_experts > 1024) return 1;
+  if (cfg.top_k < 1 || cfg.top_k > EP_MAX_TOPK) return 1;
+  if (cfg.hidden < 512 || cfg.hidden % 512 || cfg.hidden > EP_MAX_HIDDEN) return 1;
+  if (num_tokens < 0 || num_tokens > cfg.max_tokens) return 1;
+  // block_pair_barrier keeps one flag row per block.
+  if (cfg.blocks < 1 || cfg.blocks > ROCSHMEM_LIB_MAX_BLOCKS) return 1;
+  if (cfg.low_latency && cfg.layout != EP_LAYOUT_SLOTTED) return 1;
+  return 0;
+}
+
+// Blocks of a low-latency combine: a function of the configuration only, because every member must launch the
+// same number (block b pairs with block b of the peers) while their token counts may differ.
+inline int ep_ll_combine_blocks(const EpConfig &cfg) {
+  const int warps = cfg.max_tokens * 4;
+  const int blocks = (warps + 3) / 4;
+  return blocks < 1 ? 1 : (blocks > ROCSHMEM_LIB_MAX_BLOCKS ? ROCSHMEM_LIB_MAX_BLOCKS : blocks);
+}
+
 // Words of EpBuffers::work_counter.
 constexpr int EP_WORK_DISPATCH = 0;    // [2][EP_MAX_RANKS]: next item per destination, by call parity
 constexpr int EP_WORK_COMBINE = 64;    // tokens handed out by all combine calls so far (never reset)

@@ -20,6 +20,7 @@
 #include "rocshmem/slab.h"
 #include "team.hpp"
 #include "../kernels/coll_select.hpp"
+#include "../kernels/ep_kernels.hpp"
 
 using namespace rocshmem;
 
@@ -316,6 +317,45 @@ static void test_broadcast_plan() {
   }
 }
 
+static void test_ep_config_limits() {
+  using namespace rocshmem::kernels;
+  EpConfig ok{256, 8, 7168, 4096, 1, EP_LAYOUT_COMPACT, 148, 1, 0, 0};
+  EXPECT(ep_config_error(ok, 8, 4096) == 0 && ep_config_error(ok, 1, 0) == 0 && ep_config_error(ok, 32, 4096) == 0);
+  EXPECT(ep_config_error(ok, 33, 4096) != 0);            // a destination rank is a lane of a warp
+  EXPECT(ep_config_error(ok, 0, 4096) != 0);
+  EXPECT(ep_config_error(ok, 3, 4096) != 0);             // 256 experts do not divide over three ranks
+  EXPECT(ep_config_error(ok, 8, 4097) != 0 && ep_config_error(ok, 8, -1) != 0);
+  EpConfig c = ok;
+  c.num_experts = 4;
+  EXPECT(ep_config_error(c, 8, 16) != 0);                // fewer experts than ranks
+  c = ok; c.num_experts = 2048;
+  EXPECT(ep_config_error(c, 8, 16) != 0);
+  c = ok; c.top_k = 9;
+  EXPECT(ep_config_error(c, 8, 16) != 0);
+  c = ok; c.top_k = 0;
+  EXPECT(ep_config_error(c, 8, 16) != 0);
+  c = ok; c.hidden = 7168 + 128;
+  EXPECT(ep_config_error(c, 8, 16) != 0);                // whole 512-element groups (four scale blocks per lane)
+  c = ok; c.hidden = 256;
+  EXPECT(ep_config_error(c, 8, 16) != 0);
+  c = ok; c.hidden = 8192 + 512;
+  EXPECT(ep_config_error(c, 8, 16) != 0);
+  c = ok; c.blocks = ROCSHMEM_LIB_MAX_BLOCKS + 1;
+  EXPECT(ep_config_error(c, 8, 16) != 0);                // one flag row per block in the cross-PE barrier
+  c = ok; c.blocks = 0;
+  EXPECT(ep_config_error(c, 8, 16) != 0);
+  c = ok; c.low_latency = 1;
+  EXPECT(ep_config_error(c, 8, 16) != 0);                // the low-latency kernels need the slotted layout
+  c.layout = EP_LAYOUT_SLOTTED; c.max_tokens = 128;
+  EXPECT(ep_config_error(c, 8, 128) == 0);
+  // every member launches the same number of combine blocks whatever its own token count
+  EXPECT(ep_ll_combine_blocks(c) == 128);
+  c.max_tokens = 1;
+  EXPECT(ep_ll_combine_blocks(c) == 1);
+  c.max_tokens = 4096;
+  EXPECT(ep_ll_combine_blocks(c) == ROCSHMEM_LIB_MAX_BLOCKS);
+}
+
 int main(int argc, char **argv) {
   if (argc < 2) {
     std::fprintf(stderr, "usage: %s <scratch directory>\n", argv[0]);
@@ -330,6 +370,7 @@ int main(int argc, char **argv) {
   test_slab_place();
   test_allreduce_selection();
   test_broadcast_plan();
+  test_ep_config_limits();
   test_file_bootstrap_between_threads(argv[1]);
   if (g_failures) {
     std::fprintf(stderr, "%d check(s) failed\n", g_failures);
