@@ -10,7 +10,7 @@ from rocshmem_b200 import launch
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("script,world", [("data_parallel.py", 3), ("ring_attention.py", 4)])
+@pytest.mark.parametrize("script,world", [("data_parallel.py", 3), ("ring_attention.py", 4), ("team_allreduce.py", 5)])
 def test_example_passes_on_every_rank(script, world):
     out = io.StringIO()
     rc = launch.launch([sys.executable, os.path.join(ROOT, "examples", "python", script)], world, backend="host",
