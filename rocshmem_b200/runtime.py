@@ -346,7 +346,9 @@ class Team:
         return _C().team_sync(self.handle)
 
     def destroy(self) -> None:
-        """Release the team's slot (collective over its members)."""
+        """Release the team's slot. Collective over the members when the team has a multicast object of its own
+        (:meth:`has_nvls` on a split team): the call waits for the GPU's queued work and for the other members,
+        so every member destroys its teams in the same order; local otherwise."""
         if self.handle:
             _C().team_destroy(self.handle)
             self.handle = 0
